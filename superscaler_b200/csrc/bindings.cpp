@@ -1,0 +1,419 @@
+// Python bindings (module superscaler_b200._C): thin, allocation-light wrappers that check
+// shapes / dtypes, pick the current CUDA stream and call the kernel launchers.  Every launcher
+// returns 0 or an error code; a non-zero code raises, so a missing or failing native path is
+// never silent.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "attention_sm100.cuh"
+#include "gemm_sm100.cuh"
+
+namespace ssb {
+int gemm_bf16_launch(const void* A, int lda, int a_mn_major, const void* B, int ldb, int b_mn_major,
+                     const GemmParams& p, int num_sms, cudaStream_t stream);
+int layernorm_fwd_launch(const void* x, const void* residual, const float* gamma, const float* beta, void* y,
+                         void* sum_out, float* mean, float* rstd, int rows, int H, float eps, int num_sms,
+                         cudaStream_t stream);
+int ln_bwd_slices(int rows);
+int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                         const void* dres, void* dx, float* dgamma, float* dbeta, float* part_g, float* part_b,
+                         int accumulate_wgrad, int rows, int H, int num_sms, cudaStream_t stream);
+int colsum_launch(const void* a, int lda, float* out, float* part, int accumulate, int rows, int N,
+                  cudaStream_t stream);
+int elementwise_launch(int op, const void* x, const void* a, const void* bias, void* out, long long rows, int N,
+                       float dropout_p, unsigned long long seed, int num_sms, cudaStream_t stream);
+int cast_f32_to_bf16_launch(const float* in, void* out, long long n, int num_sms, cudaStream_t stream);
+int softmax_fwd_launch(const void* x, const void* mask, void* y, long long rows, int sq, int sk, int heads,
+                       int mask_broadcast_batch, float scale, int mode, int num_sms, cudaStream_t stream);
+int softmax_bwd_launch(const void* g, const void* y, void* dx, long long rows, int sk, float scale, int num_sms,
+                       cudaStream_t stream);
+int sumsq_launch(const float* g, long long n, float* partials, float* out, int accumulate, cudaStream_t stream);
+int adam_launch(float* p, float* m, float* v, float* g, void* p16, long long n, const float* sumsq, int* skipped,
+                float lr, float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale,
+                float max_norm, long long wd_end, int zero_grad, int num_sms, cudaStream_t stream);
+int sgd_launch(float* p, float* mom, float* g, void* p16, long long n, const float* sumsq, int* skipped, float lr,
+               float momentum, float weight_decay, float grad_scale, float max_norm, long long wd_end, int zero_grad,
+               int first_step, int num_sms, cudaStream_t stream);
+int embedding_fwd_launch(const long long* ids, const long long* pos, const void* W, const void* P, void* out,
+                         long long tokens, int H, long long v0, long long v1, float dropout_p,
+                         unsigned long long seed, int num_sms, cudaStream_t stream);
+int embedding_bwd_launch(const long long* ids, const long long* pos, const void* g, float* dW, float* dP,
+                         long long tokens, int H, long long v0, long long v1, float dropout_p,
+                         unsigned long long seed, int num_sms, cudaStream_t stream);
+int ce_stats_launch(const void* logits, int ld, const long long* targets, float* row_max, float* row_sum,
+                    float* row_tgt, long long rows, int V, long long v0, cudaStream_t stream);
+int ce_finalize_launch(void* logits, int ld, const long long* targets, const float* gmax, const float* gsum,
+                       const float* gtgt, const float* loss_mask, float* loss, long long rows, int V, long long v0,
+                       float grad_scale, int write_grad, cudaStream_t stream);
+int attn_fwd_launch(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const AttnParams& p,
+                    cudaStream_t stream);
+int attn_bwd_launch(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const void* dout,
+                    int lddo, const AttnParams& p, float* delta_scratch, cudaStream_t stream);
+}  // namespace ssb
+
+namespace {
+
+using torch::Tensor;
+using OptTensor = c10::optional<Tensor>;
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int num_sms() {
+  static int n[64] = {0};
+  int dev = at::cuda::current_device();
+  if (n[dev] == 0) n[dev] = at::cuda::getDeviceProperties(dev)->multiProcessorCount;
+  return n[dev];
+}
+
+// One status word per device, written by kernels whose bounded waits run out.
+Tensor& status_tensor() {
+  static std::vector<Tensor> st(64);
+  int dev = at::cuda::current_device();
+  if (!st[dev].defined()) st[dev] = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA, dev));
+  return st[dev];
+}
+
+void check_launch(int rc, const char* what) { TORCH_CHECK(rc == 0, what, ": native launcher failed with code ", rc); }
+
+void check_bf16_2d(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16, name, " must be a CUDA bf16 tensor");
+  TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1, name, " must be 2-D with unit inner stride");
+}
+
+const void* opt_ptr(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+// D = epilogue(alpha * A op B); see gemm_sm100.cuh for the operand conventions.
+void gemm(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, const OptTensor& bias, int64_t act,
+          const OptTensor& aux, const OptTensor& preact_out, const OptTensor& residual, bool accumulate, double alpha,
+          double dropout_p, int64_t seed) {
+  check_bf16_2d(a, "a");
+  check_bf16_2d(b, "b");
+  TORCH_CHECK(d.is_cuda() && d.dim() == 2 && d.stride(1) == 1, "d must be 2-D with unit inner stride");
+  TORCH_CHECK(d.scalar_type() == torch::kBFloat16 || d.scalar_type() == torch::kFloat32, "d must be bf16 or fp32");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a_mn ? a.size(1) : a.size(0);
+  const int64_t K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  const int64_t Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm: reduction sizes differ: ", K, " vs ", Kb);
+  TORCH_CHECK(d.size(0) == M && d.size(1) == N, "gemm: output must be [", M, ", ", N, "]");
+  ssb::GemmParams p{};
+  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
+  p.D = d.data_ptr(); p.ldd = static_cast<int>(d.stride(0));
+  p.out_fp32 = d.scalar_type() == torch::kFloat32;
+  p.accumulate = accumulate; p.alpha = static_cast<float>(alpha);
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "bias must be contiguous [N]");
+    TORCH_CHECK(bias->scalar_type() == torch::kBFloat16 || bias->scalar_type() == torch::kFloat32, "bias dtype");
+    p.bias = bias->data_ptr(); p.bias_fp32 = bias->scalar_type() == torch::kFloat32;
+  }
+  p.act = static_cast<int>(act);
+  if (aux.has_value()) { check_bf16_2d(*aux, "aux"); p.aux = aux->data_ptr(); p.ldaux = static_cast<int>(aux->stride(0)); }
+  TORCH_CHECK(!(act == ssb::kActDGelu || act == ssb::kActDRelu) || aux.has_value(), "derivative epilogues need aux");
+  if (preact_out.has_value()) {
+    check_bf16_2d(*preact_out, "preact_out");
+    p.preact_out = preact_out->data_ptr(); p.ldpre = static_cast<int>(preact_out->stride(0));
+  }
+  if (residual.has_value()) {
+    check_bf16_2d(*residual, "residual");
+    p.residual = residual->data_ptr(); p.ldres = static_cast<int>(residual->stride(0));
+  }
+  for (const OptTensor* t : {&aux, &preact_out, &residual})
+    if (t->has_value()) TORCH_CHECK((*t)->size(0) == M && (*t)->size(1) == N && (*t)->stride(0) % 8 == 0, "epilogue operand shape");
+  p.dropout_p = static_cast<float>(dropout_p);
+  p.dropout_seed = static_cast<unsigned long long>(seed);
+  TORCH_CHECK(dropout_p == 0.0 || d.stride(0) == N, "dropout epilogue needs a dense output");
+  p.status = status_tensor().data_ptr<int>();
+  check_launch(ssb::gemm_bf16_launch(a.data_ptr(), static_cast<int>(a.stride(0)), a_mn, b.data_ptr(),
+                                     static_cast<int>(b.stride(0)), b_mn, p, num_sms(), cur_stream()),
+               "gemm");
+}
+
+std::vector<Tensor> layernorm_fwd(const Tensor& x, const OptTensor& residual, const Tensor& gamma, const Tensor& beta,
+                                  double eps) {
+  check_bf16_2d(x, "x");
+  TORCH_CHECK(x.is_contiguous() && gamma.scalar_type() == torch::kFloat32 && beta.scalar_type() == torch::kFloat32);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rows = static_cast<int>(x.size(0)), H = static_cast<int>(x.size(1));
+  Tensor y = torch::empty_like(x);
+  Tensor sum_out;
+  if (residual.has_value()) { TORCH_CHECK(residual->is_contiguous() && residual->sizes() == x.sizes()); sum_out = torch::empty_like(x); }
+  auto fopt = torch::dtype(torch::kFloat32).device(x.device());
+  Tensor mean = torch::empty({rows}, fopt), rstd = torch::empty({rows}, fopt);
+  check_launch(ssb::layernorm_fwd_launch(x.data_ptr(), opt_ptr(residual), gamma.data_ptr<float>(), beta.data_ptr<float>(),
+                                         y.data_ptr(), sum_out.defined() ? sum_out.data_ptr() : nullptr,
+                                         mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, H,
+                                         static_cast<float>(eps), num_sms(), cur_stream()),
+               "layernorm_fwd");
+  if (sum_out.defined()) return {y, mean, rstd, sum_out};
+  return {y, mean, rstd};
+}
+
+Tensor layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const Tensor& mean, const Tensor& rstd,
+                     const OptTensor& dres, Tensor& dgamma, Tensor& dbeta, bool accumulate) {
+  check_bf16_2d(dy, "dy"); check_bf16_2d(x, "x");
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous());
+  TORCH_CHECK(dgamma.scalar_type() == torch::kFloat32 && dbeta.scalar_type() == torch::kFloat32);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rows = static_cast<int>(x.size(0)), H = static_cast<int>(x.size(1));
+  Tensor dx = torch::empty_like(x);
+  Tensor part = torch::empty({2, ssb::ln_bwd_slices(rows), H}, torch::dtype(torch::kFloat32).device(x.device()));
+  check_launch(ssb::layernorm_bwd_launch(dy.data_ptr(), x.data_ptr(), gamma.data_ptr<float>(), mean.data_ptr<float>(),
+                                         rstd.data_ptr<float>(), opt_ptr(dres), dx.data_ptr(), dgamma.data_ptr<float>(),
+                                         dbeta.data_ptr<float>(), part[0].data_ptr<float>(), part[1].data_ptr<float>(),
+                                         accumulate, rows, H, num_sms(), cur_stream()),
+               "layernorm_bwd");
+  return dx;
+}
+
+void colsum(const Tensor& a, Tensor& out, bool accumulate) {
+  check_bf16_2d(a, "a");
+  TORCH_CHECK(out.scalar_type() == torch::kFloat32 && out.numel() == a.size(1) && out.is_contiguous());
+  c10::cuda::CUDAGuard guard(a.device());
+  const int rows = static_cast<int>(a.size(0)), N = static_cast<int>(a.size(1));
+  Tensor part = torch::empty({ssb::ln_bwd_slices(rows), N}, torch::dtype(torch::kFloat32).device(a.device()));
+  check_launch(ssb::colsum_launch(a.data_ptr(), static_cast<int>(a.stride(0)), out.data_ptr<float>(),
+                                  part.data_ptr<float>(), accumulate, rows, N, cur_stream()),
+               "colsum");
+}
+
+Tensor elementwise(int64_t op, const Tensor& x, const OptTensor& a, const OptTensor& bias, double dropout_p,
+                   int64_t seed) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous());
+  if (a.has_value()) TORCH_CHECK(a->is_contiguous() && a->numel() == x.numel() && a->scalar_type() == torch::kBFloat16);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int N = static_cast<int>(x.size(-1));
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == torch::kBFloat16 && bias->numel() == N && bias->is_contiguous());
+  Tensor out = torch::empty_like(x);
+  check_launch(ssb::elementwise_launch(static_cast<int>(op), x.data_ptr(), opt_ptr(a), opt_ptr(bias), out.data_ptr(),
+                                       x.numel() / N, N, static_cast<float>(dropout_p),
+                                       static_cast<unsigned long long>(seed), num_sms(), cur_stream()),
+               "elementwise");
+  return out;
+}
+
+void cast_f32_to_bf16(const Tensor& in, Tensor& out) {
+  TORCH_CHECK(in.scalar_type() == torch::kFloat32 && out.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(in.is_contiguous() && out.is_contiguous() && in.numel() == out.numel());
+  c10::cuda::CUDAGuard guard(in.device());
+  check_launch(ssb::cast_f32_to_bf16_launch(in.data_ptr<float>(), out.data_ptr(), in.numel(), num_sms(), cur_stream()),
+               "cast");
+}
+
+// x: [..., sq, sk] bf16 contiguous.  mode 0 plain, 1 causal, 2 masked (mask uint8 [b|1, 1, sq, sk]).
+Tensor softmax_fwd(const Tensor& x, const OptTensor& mask, double scale, int64_t mode, int64_t heads) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() >= 2);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int sk = static_cast<int>(x.size(-1)), sq = static_cast<int>(x.size(-2));
+  const long long rows = x.numel() / sk;
+  int bcast = 1;
+  if (mode == 2) {
+    TORCH_CHECK(mask.has_value() && mask->scalar_type() == torch::kUInt8 && mask->is_contiguous());
+    bcast = mask->numel() == static_cast<int64_t>(sq) * sk;
+  }
+  Tensor y = torch::empty_like(x);
+  check_launch(ssb::softmax_fwd_launch(x.data_ptr(), opt_ptr(mask), y.data_ptr(), rows, sq, sk, static_cast<int>(heads),
+                                       bcast, static_cast<float>(scale), static_cast<int>(mode), num_sms(), cur_stream()),
+               "softmax_fwd");
+  return y;
+}
+
+Tensor softmax_bwd(const Tensor& g, const Tensor& y, double scale) {
+  TORCH_CHECK(g.is_contiguous() && y.is_contiguous() && g.scalar_type() == torch::kBFloat16 && y.scalar_type() == torch::kBFloat16);
+  c10::cuda::CUDAGuard guard(g.device());
+  const int sk = static_cast<int>(g.size(-1));
+  Tensor dx = torch::empty_like(g);
+  check_launch(ssb::softmax_bwd_launch(g.data_ptr(), y.data_ptr(), dx.data_ptr(), g.numel() / sk, sk,
+                                       static_cast<float>(scale), num_sms(), cur_stream()),
+               "softmax_bwd");
+  return dx;
+}
+
+void sumsq(const Tensor& g, Tensor& out, bool accumulate) {
+  TORCH_CHECK(g.scalar_type() == torch::kFloat32 && g.is_contiguous() && out.scalar_type() == torch::kFloat32);
+  c10::cuda::CUDAGuard guard(g.device());
+  Tensor part = torch::empty({1024}, torch::dtype(torch::kFloat32).device(g.device()));
+  check_launch(ssb::sumsq_launch(g.data_ptr<float>(), g.numel(), part.data_ptr<float>(), out.data_ptr<float>(),
+                                 accumulate, cur_stream()),
+               "sumsq");
+}
+
+void adam_step(Tensor& p, Tensor& m, Tensor& v, Tensor& g, Tensor& p16, const OptTensor& sumsq_t, const OptTensor& skipped,
+               double lr, double beta1, double beta2, double eps, double wd, int64_t step, double grad_scale,
+               double max_norm, int64_t wd_end, bool zero_grad) {
+  TORCH_CHECK(p.is_contiguous() && m.is_contiguous() && v.is_contiguous() && g.is_contiguous() && p16.is_contiguous());
+  TORCH_CHECK(p.scalar_type() == torch::kFloat32 && g.scalar_type() == torch::kFloat32 && p16.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(m.numel() == p.numel() && v.numel() == p.numel() && g.numel() == p.numel() && p16.numel() == p.numel());
+  c10::cuda::CUDAGuard guard(p.device());
+  check_launch(ssb::adam_launch(p.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), g.data_ptr<float>(),
+                                p16.data_ptr(), p.numel(), sumsq_t.has_value() ? sumsq_t->data_ptr<float>() : nullptr,
+                                skipped.has_value() ? skipped->data_ptr<int>() : nullptr, static_cast<float>(lr),
+                                static_cast<float>(beta1), static_cast<float>(beta2), static_cast<float>(eps),
+                                static_cast<float>(wd), static_cast<int>(step), static_cast<float>(grad_scale),
+                                static_cast<float>(max_norm), wd_end, zero_grad, num_sms(), cur_stream()),
+               "adam");
+}
+
+void sgd_step(Tensor& p, Tensor& mom, Tensor& g, Tensor& p16, const OptTensor& sumsq_t, const OptTensor& skipped,
+              double lr, double momentum, double wd, double grad_scale, double max_norm, int64_t wd_end,
+              bool zero_grad, bool first_step) {
+  TORCH_CHECK(p.is_contiguous() && mom.is_contiguous() && g.is_contiguous() && p16.is_contiguous());
+  c10::cuda::CUDAGuard guard(p.device());
+  check_launch(ssb::sgd_launch(p.data_ptr<float>(), mom.data_ptr<float>(), g.data_ptr<float>(), p16.data_ptr(), p.numel(),
+                               sumsq_t.has_value() ? sumsq_t->data_ptr<float>() : nullptr,
+                               skipped.has_value() ? skipped->data_ptr<int>() : nullptr, static_cast<float>(lr),
+                               static_cast<float>(momentum), static_cast<float>(wd), static_cast<float>(grad_scale),
+                               static_cast<float>(max_norm), wd_end, zero_grad, first_step, num_sms(), cur_stream()),
+               "sgd");
+}
+
+Tensor embedding_fwd(const Tensor& ids, const OptTensor& pos, const Tensor& W, const OptTensor& P, int64_t v0,
+                     double dropout_p, int64_t seed) {
+  TORCH_CHECK(ids.scalar_type() == torch::kInt64 && ids.is_contiguous() && W.scalar_type() == torch::kBFloat16 && W.is_contiguous());
+  c10::cuda::CUDAGuard guard(W.device());
+  const int H = static_cast<int>(W.size(1));
+  Tensor out = torch::empty({ids.numel(), H}, W.options());
+  if (P.has_value()) TORCH_CHECK(pos.has_value() && pos->numel() == ids.numel() && pos->scalar_type() == torch::kInt64 && P->is_contiguous());
+  check_launch(ssb::embedding_fwd_launch(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()),
+                                         pos.has_value() ? reinterpret_cast<const long long*>(pos->data_ptr<int64_t>()) : nullptr,
+                                         W.data_ptr(), opt_ptr(P), out.data_ptr(), ids.numel(), H, v0, v0 + W.size(0),
+                                         static_cast<float>(dropout_p), static_cast<unsigned long long>(seed), num_sms(),
+                                         cur_stream()),
+               "embedding_fwd");
+  return out;
+}
+
+void embedding_bwd(const Tensor& ids, const OptTensor& pos, const Tensor& g, const OptTensor& dW, const OptTensor& dP,
+                   int64_t v0, double dropout_p, int64_t seed) {
+  TORCH_CHECK(g.scalar_type() == torch::kBFloat16 && g.is_contiguous());
+  c10::cuda::CUDAGuard guard(g.device());
+  const int H = static_cast<int>(g.size(-1));
+  const int64_t v1 = dW.has_value() ? v0 + dW->size(0) : v0;
+  if (dW.has_value()) TORCH_CHECK(dW->scalar_type() == torch::kFloat32 && dW->is_contiguous());
+  if (dP.has_value()) TORCH_CHECK(dP->scalar_type() == torch::kFloat32 && dP->is_contiguous() && pos.has_value());
+  check_launch(ssb::embedding_bwd_launch(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()),
+                                         pos.has_value() ? reinterpret_cast<const long long*>(pos->data_ptr<int64_t>()) : nullptr,
+                                         g.data_ptr(), dW.has_value() ? dW->data_ptr<float>() : nullptr,
+                                         dP.has_value() ? dP->data_ptr<float>() : nullptr, ids.numel(), H, v0, v1,
+                                         static_cast<float>(dropout_p), static_cast<unsigned long long>(seed), num_sms(),
+                                         cur_stream()),
+               "embedding_bwd");
+}
+
+// returns [3, rows] fp32: local max, sum exp(x - max), target logit (0 when the target is not local)
+Tensor ce_stats(const Tensor& logits, const Tensor& targets, int64_t v0) {
+  check_bf16_2d(logits, "logits");
+  TORCH_CHECK(targets.scalar_type() == torch::kInt64 && targets.is_contiguous() && targets.numel() == logits.size(0));
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor st = torch::empty({3, logits.size(0)}, torch::dtype(torch::kFloat32).device(logits.device()));
+  check_launch(ssb::ce_stats_launch(logits.data_ptr(), static_cast<int>(logits.stride(0)),
+                                    reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), st[0].data_ptr<float>(),
+                                    st[1].data_ptr<float>(), st[2].data_ptr<float>(), logits.size(0),
+                                    static_cast<int>(logits.size(1)), v0, cur_stream()),
+               "ce_stats");
+  return st;
+}
+
+// stats: [3, rows] (group max, group sum w.r.t. that max, group target logit).  Returns per-row loss;
+// overwrites logits with d loss_sum / d logits * grad_scale when write_grad.
+Tensor ce_finalize(Tensor& logits, const Tensor& targets, const Tensor& stats, const OptTensor& loss_mask, int64_t v0,
+                   double grad_scale, bool write_grad) {
+  check_bf16_2d(logits, "logits");
+  TORCH_CHECK(stats.scalar_type() == torch::kFloat32 && stats.is_contiguous() && stats.size(0) == 3);
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor loss = torch::empty({logits.size(0)}, torch::dtype(torch::kFloat32).device(logits.device()));
+  if (loss_mask.has_value()) TORCH_CHECK(loss_mask->scalar_type() == torch::kFloat32 && loss_mask->is_contiguous());
+  check_launch(ssb::ce_finalize_launch(logits.data_ptr(), static_cast<int>(logits.stride(0)),
+                                       reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()),
+                                       stats[0].data_ptr<float>(), stats[1].data_ptr<float>(), stats[2].data_ptr<float>(),
+                                       loss_mask.has_value() ? loss_mask->data_ptr<float>() : nullptr, loss.data_ptr<float>(),
+                                       logits.size(0), static_cast<int>(logits.size(1)), v0,
+                                       static_cast<float>(grad_scale), write_grad, cur_stream()),
+               "ce_finalize");
+  return loss;
+}
+
+ssb::AttnParams attn_params(int64_t B, int64_t NH, int64_t SQ, int64_t SK, int64_t HD, int64_t q_col0, int64_t k_col0,
+                            int64_t v_col0, double scale, bool causal, const OptTensor& kv_lens, double dropout_p,
+                            int64_t seed) {
+  ssb::AttnParams p{};
+  p.B = static_cast<int>(B); p.NH = static_cast<int>(NH); p.SQ = static_cast<int>(SQ); p.SK = static_cast<int>(SK);
+  p.HD = static_cast<int>(HD);
+  p.q_col0 = static_cast<int>(q_col0); p.k_col0 = static_cast<int>(k_col0); p.v_col0 = static_cast<int>(v_col0);
+  p.scale = static_cast<float>(scale); p.causal = causal;
+  if (kv_lens.has_value()) {
+    TORCH_CHECK(kv_lens->scalar_type() == torch::kInt32 && kv_lens->numel() == B && kv_lens->is_contiguous());
+    p.kv_lens = kv_lens->data_ptr<int>();
+  }
+  p.dropout_p = static_cast<float>(dropout_p);
+  p.dropout_seed = static_cast<unsigned long long>(seed);
+  p.status = status_tensor().data_ptr<int>();
+  return p;
+}
+
+// q, k, v: 2-D bf16 matrices [B*S, ld] holding the heads at columns col0 + head*HD.
+// Returns (O [B*SQ, NH*HD], LSE [B, NH, SQ]).
+std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, int64_t B, int64_t NH, int64_t SQ,
+                             int64_t SK, int64_t HD, int64_t q_col0, int64_t k_col0, int64_t v_col0, double scale,
+                             bool causal, const OptTensor& kv_lens, double dropout_p, int64_t seed) {
+  check_bf16_2d(q, "q"); check_bf16_2d(k, "k"); check_bf16_2d(v, "v");
+  TORCH_CHECK(q.size(0) == B * SQ && k.size(0) == B * SK && v.size(0) == B * SK, "attention: row counts");
+  c10::cuda::CUDAGuard guard(q.device());
+  ssb::AttnParams p = attn_params(B, NH, SQ, SK, HD, q_col0, k_col0, v_col0, scale, causal, kv_lens, dropout_p, seed);
+  Tensor o = torch::empty({B * SQ, NH * HD}, q.options());
+  Tensor lse = torch::empty({B, NH, SQ}, torch::dtype(torch::kFloat32).device(q.device()));
+  p.O = o.data_ptr(); p.ldo = static_cast<int>(o.stride(0)); p.o_col0 = 0; p.LSE = lse.data_ptr<float>();
+  check_launch(ssb::attn_fwd_launch(q.data_ptr(), static_cast<int>(q.stride(0)), k.data_ptr(), static_cast<int>(k.stride(0)),
+                                    v.data_ptr(), static_cast<int>(v.stride(0)), p, cur_stream()),
+               "attn_fwd");
+  return {o, lse};
+}
+
+// dq, dk, dv are written into caller-provided 2-D matrices (same conventions as q, k, v).
+void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& lse, const Tensor& dout,
+              Tensor& dq, Tensor& dk, Tensor& dv, int64_t B, int64_t NH, int64_t SQ, int64_t SK, int64_t HD,
+              int64_t q_col0, int64_t k_col0, int64_t v_col0, int64_t dq_col0, int64_t dk_col0, int64_t dv_col0,
+              double scale, bool causal, const OptTensor& kv_lens, double dropout_p, int64_t seed) {
+  check_bf16_2d(q, "q"); check_bf16_2d(k, "k"); check_bf16_2d(v, "v"); check_bf16_2d(o, "o"); check_bf16_2d(dout, "dout");
+  check_bf16_2d(dq, "dq"); check_bf16_2d(dk, "dk"); check_bf16_2d(dv, "dv");
+  TORCH_CHECK(o.stride(0) == dout.stride(0), "o and dout must share a layout");
+  TORCH_CHECK(lse.scalar_type() == torch::kFloat32 && lse.is_contiguous());
+  c10::cuda::CUDAGuard guard(q.device());
+  ssb::AttnParams p = attn_params(B, NH, SQ, SK, HD, q_col0, k_col0, v_col0, scale, causal, kv_lens, dropout_p, seed);
+  p.O = o.data_ptr(); p.ldo = static_cast<int>(o.stride(0)); p.o_col0 = 0;
+  p.LSE = lse.data_ptr<float>();
+  p.dQ = dq.data_ptr(); p.lddq = static_cast<int>(dq.stride(0)); p.dq_col0 = static_cast<int>(dq_col0);
+  p.dK = dk.data_ptr(); p.lddk = static_cast<int>(dk.stride(0)); p.dk_col0 = static_cast<int>(dk_col0);
+  p.dV = dv.data_ptr(); p.lddv = static_cast<int>(dv.stride(0)); p.dv_col0 = static_cast<int>(dv_col0);
+  Tensor delta = torch::empty({B, NH, SQ}, torch::dtype(torch::kFloat32).device(q.device()));
+  check_launch(ssb::attn_bwd_launch(q.data_ptr(), static_cast<int>(q.stride(0)), k.data_ptr(), static_cast<int>(k.stride(0)),
+                                    v.data_ptr(), static_cast<int>(v.stride(0)), dout.data_ptr(),
+                                    static_cast<int>(dout.stride(0)), p, delta.data_ptr<float>(), cur_stream()),
+               "attn_bwd");
+}
+
+Tensor status() { return status_tensor(); }
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm);
+  m.def("layernorm_fwd", &layernorm_fwd);
+  m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("colsum", &colsum);
+  m.def("elementwise", &elementwise);
+  m.def("cast_f32_to_bf16", &cast_f32_to_bf16);
+  m.def("softmax_fwd", &softmax_fwd);
+  m.def("softmax_bwd", &softmax_bwd);
+  m.def("sumsq", &sumsq);
+  m.def("adam_step", &adam_step);
+  m.def("sgd_step", &sgd_step);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("ce_stats", &ce_stats);
+  m.def("ce_finalize", &ce_finalize);
+  m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
+  m.def("status", &status);
+}

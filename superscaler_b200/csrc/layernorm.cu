@@ -1,0 +1,346 @@
+// LayerNorm forward / backward for bf16 activations with fp32 statistics, one warp per row.
+// Covers the role of the reference's mixed-precision fused LayerNorm extension
+// (runtime/megatron/fused_kernels/layer_norm_cuda_kernel.cu:290-334 forward,
+// :415-651 backward): y = (x - mean) * rstd * gamma + beta, saving mean and rstd;
+// backward produces dx and per-column partial sums for dgamma / dbeta that a
+// second small kernel folds (deterministic, no atomics).
+//
+// HBM-bound: every kernel moves 16 bytes per lane per access and keeps the row in
+// registers between the statistics pass and the normalisation pass.
+#include "common.cuh"
+
+namespace ssb {
+namespace {
+
+constexpr int kLnWarpsPerBlock = 4;
+
+// VPL = uint4 vectors (8 bf16) per lane; H = VPL * 256.  VPL == 0 selects the generic
+// path that re-reads the row (any H that is a multiple of 8).
+template <int VPL>
+__global__ void __launch_bounds__(kLnWarpsPerBlock * 32)
+ln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+              const float* __restrict__ gamma, const float* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+              __nv_bfloat16* __restrict__ sum_out, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+              int rows, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * kLnWarpsPerBlock + (threadIdx.x >> 5);
+  const int warps_total = gridDim.x * kLnWarpsPerBlock;
+  const int nvec = H / 8;
+  for (int row = warp_global; row < rows; row += warps_total) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
+    const uint4* rr = residual ? reinterpret_cast<const uint4*>(residual + static_cast<size_t>(row) * H) : nullptr;
+    uint4* sr = sum_out ? reinterpret_cast<uint4*>(sum_out + static_cast<size_t>(row) * H) : nullptr;
+    constexpr int NV = VPL > 0 ? VPL : 1;
+    float vals[NV][8];
+    float s = 0.f;
+    if (VPL > 0) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        uint4 q = xr[i * 32 + lane];
+        float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
+        vals[i][0] = f0.x; vals[i][1] = f0.y; vals[i][2] = f1.x; vals[i][3] = f1.y;
+        vals[i][4] = f2.x; vals[i][5] = f2.y; vals[i][6] = f3.x; vals[i][7] = f3.y;
+        if (rr) {
+          uint4 r = rr[i * 32 + lane];
+          float2 g0 = unpack_bf16x2(r.x), g1 = unpack_bf16x2(r.y), g2 = unpack_bf16x2(r.z), g3 = unpack_bf16x2(r.w);
+          vals[i][0] += g0.x; vals[i][1] += g0.y; vals[i][2] += g1.x; vals[i][3] += g1.y;
+          vals[i][4] += g2.x; vals[i][5] += g2.y; vals[i][6] += g3.x; vals[i][7] += g3.y;
+          uint4 o;
+          o.x = pack_bf16x2(vals[i][0], vals[i][1]); o.y = pack_bf16x2(vals[i][2], vals[i][3]);
+          o.z = pack_bf16x2(vals[i][4], vals[i][5]); o.w = pack_bf16x2(vals[i][6], vals[i][7]);
+          if (sr) sr[i * 32 + lane] = o;
+          // statistics are taken on the rounded sum so that forward and backward see the same x
+          float2 h0 = unpack_bf16x2(o.x), h1 = unpack_bf16x2(o.y), h2 = unpack_bf16x2(o.z), h3 = unpack_bf16x2(o.w);
+          vals[i][0] = h0.x; vals[i][1] = h0.y; vals[i][2] = h1.x; vals[i][3] = h1.y;
+          vals[i][4] = h2.x; vals[i][5] = h2.y; vals[i][6] = h3.x; vals[i][7] = h3.y;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += vals[i][j];
+      }
+    } else {
+      for (int v = lane; v < nvec; v += 32) {
+        uint4 q = xr[v];
+        float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
+        float e[8] = {f0.x, f0.y, f1.x, f1.y, f2.x, f2.y, f3.x, f3.y};
+        if (rr) {
+          uint4 r = rr[v];
+          float2 g0 = unpack_bf16x2(r.x), g1 = unpack_bf16x2(r.y), g2 = unpack_bf16x2(r.z), g3 = unpack_bf16x2(r.w);
+          e[0] += g0.x; e[1] += g0.y; e[2] += g1.x; e[3] += g1.y; e[4] += g2.x; e[5] += g2.y; e[6] += g3.x; e[7] += g3.y;
+          uint4 o;
+          o.x = pack_bf16x2(e[0], e[1]); o.y = pack_bf16x2(e[2], e[3]);
+          o.z = pack_bf16x2(e[4], e[5]); o.w = pack_bf16x2(e[6], e[7]);
+          if (sr) sr[v] = o;
+          float2 h0 = unpack_bf16x2(o.x), h1 = unpack_bf16x2(o.y), h2 = unpack_bf16x2(o.z), h3 = unpack_bf16x2(o.w);
+          e[0] = h0.x; e[1] = h0.y; e[2] = h1.x; e[3] = h1.y; e[4] = h2.x; e[5] = h2.y; e[6] = h3.x; e[7] = h3.y;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += e[j];
+      }
+    }
+    const float mean = warp_sum(s) / static_cast<float>(H);
+    float sq = 0.f;
+    // The generic path reads the (possibly just written) sum back; make the stores visible to the warp.
+    const uint4* src = (VPL == 0 && rr && sr) ? reinterpret_cast<const uint4*>(sr) : xr;
+    if (VPL == 0 && rr && sr) __syncwarp();
+    if (VPL > 0) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = vals[i][j] - mean;
+          sq += d * d;
+        }
+    } else {
+      for (int v = lane; v < nvec; v += 32) {
+        uint4 q = src[v];
+        float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
+        float e[8] = {f0.x, f0.y, f1.x, f1.y, f2.x, f2.y, f3.x, f3.y};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = e[j] - mean;
+          sq += d * d;
+        }
+      }
+    }
+    const float var = warp_sum(sq) / static_cast<float>(H);
+    const float rstd = rsqrtf(var + eps);
+    if (lane == 0) {
+      mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+    uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * H);
+    if (VPL > 0) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int v = i * 32 + lane;
+        const float4 g0 = reinterpret_cast<const float4*>(gamma)[2 * v], g1 = reinterpret_cast<const float4*>(gamma)[2 * v + 1];
+        const float4 b0 = reinterpret_cast<const float4*>(beta)[2 * v], b1 = reinterpret_cast<const float4*>(beta)[2 * v + 1];
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (vals[i][j] - mean) * rstd * g[j] + b[j];
+        uint4 q;
+        q.x = pack_bf16x2(o[0], o[1]); q.y = pack_bf16x2(o[2], o[3]);
+        q.z = pack_bf16x2(o[4], o[5]); q.w = pack_bf16x2(o[6], o[7]);
+        yr[v] = q;
+      }
+    } else {
+      for (int v = lane; v < nvec; v += 32) {
+        uint4 q = src[v];
+        float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
+        float e[8] = {f0.x, f0.y, f1.x, f1.y, f2.x, f2.y, f3.x, f3.y};
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (e[j] - mean) * rstd * gamma[v * 8 + j] + beta[v * 8 + j];
+        uint4 w;
+        w.x = pack_bf16x2(o[0], o[1]); w.y = pack_bf16x2(o[2], o[3]);
+        w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
+        yr[v] = w;
+      }
+    }
+  }
+}
+
+// dx = rstd * (dy*gamma - mean_H(dy*gamma) - xhat * mean_H(dy*gamma*xhat)) (+ dresidual)
+__global__ void __launch_bounds__(kLnWarpsPerBlock * 32)
+ln_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                 const float* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ rstd,
+                 const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, int rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * kLnWarpsPerBlock + (threadIdx.x >> 5);
+  const int warps_total = gridDim.x * kLnWarpsPerBlock;
+  const int nvec = H / 8;
+  for (int row = warp_global; row < rows; row += warps_total) {
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * H);
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
+    const float mu = mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 qd = dyr[v], qx = xr[v];
+      const float2 d0 = unpack_bf16x2(qd.x), d1 = unpack_bf16x2(qd.y), d2 = unpack_bf16x2(qd.z), d3 = unpack_bf16x2(qd.w);
+      const float2 x0 = unpack_bf16x2(qx.x), x1 = unpack_bf16x2(qx.y), x2 = unpack_bf16x2(qx.z), x3 = unpack_bf16x2(qx.w);
+      const float d[8] = {d0.x, d0.y, d1.x, d1.y, d2.x, d2.y, d3.x, d3.y};
+      const float xv[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float dg = d[j] * gamma[v * 8 + j];
+        s1 += dg;
+        s2 += dg * (xv[j] - mu) * rs;
+      }
+    }
+    s1 = warp_sum(s1) / static_cast<float>(H);
+    s2 = warp_sum(s2) / static_cast<float>(H);
+    uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * H);
+    const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * H) : nullptr;
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 qd = dyr[v], qx = xr[v];
+      const float2 d0 = unpack_bf16x2(qd.x), d1 = unpack_bf16x2(qd.y), d2 = unpack_bf16x2(qd.z), d3 = unpack_bf16x2(qd.w);
+      const float2 x0 = unpack_bf16x2(qx.x), x1 = unpack_bf16x2(qx.y), x2 = unpack_bf16x2(qx.z), x3 = unpack_bf16x2(qx.w);
+      const float d[8] = {d0.x, d0.y, d1.x, d1.y, d2.x, d2.y, d3.x, d3.y};
+      const float xv[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xhat = (xv[j] - mu) * rs;
+        o[j] = rs * (d[j] * gamma[v * 8 + j] - s1 - xhat * s2);
+      }
+      if (drr) {
+        const uint4 qr = drr[v];
+        const float2 r0 = unpack_bf16x2(qr.x), r1 = unpack_bf16x2(qr.y), r2 = unpack_bf16x2(qr.z), r3 = unpack_bf16x2(qr.w);
+        o[0] += r0.x; o[1] += r0.y; o[2] += r1.x; o[3] += r1.y; o[4] += r2.x; o[5] += r2.y; o[6] += r3.x; o[7] += r3.y;
+      }
+      uint4 w;
+      w.x = pack_bf16x2(o[0], o[1]); w.y = pack_bf16x2(o[2], o[3]);
+      w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
+      dxr[v] = w;
+    }
+  }
+}
+
+// Partial column sums over a slice of rows: part_g[slice][h] = sum dy*xhat, part_b[slice][h] = sum dy.
+// Block = 32 columns-pairs x 8 row lanes: thread (tx, ty) owns columns 2*(bx*32+tx), +1 and rows ty, ty+8, ...
+__global__ void __launch_bounds__(256)
+ln_bwd_gb_partial_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                         const float* __restrict__ mean, const float* __restrict__ rstd, float* __restrict__ part_g,
+                         float* __restrict__ part_b, int rows, int H, int rows_per_slice) {
+  __shared__ float sg[8][64], sb[8][64];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = (blockIdx.x * 32 + tx) * 2;
+  const int r0 = blockIdx.y * rows_per_slice;
+  const int r1 = min(rows, r0 + rows_per_slice);
+  float g0 = 0.f, g1 = 0.f, b0 = 0.f, b1 = 0.f;
+  if (col < H) {
+    for (int r = r0 + ty; r < r1; r += 8) {
+      const uint32_t qd = *reinterpret_cast<const uint32_t*>(dy + static_cast<size_t>(r) * H + col);
+      const uint32_t qx = *reinterpret_cast<const uint32_t*>(x + static_cast<size_t>(r) * H + col);
+      const float2 d = unpack_bf16x2(qd), xv = unpack_bf16x2(qx);
+      const float mu = mean[r], rs = rstd[r];
+      g0 += d.x * (xv.x - mu) * rs;
+      g1 += d.y * (xv.y - mu) * rs;
+      b0 += d.x;
+      b1 += d.y;
+    }
+  }
+  sg[ty][tx * 2] = g0; sg[ty][tx * 2 + 1] = g1;
+  sb[ty][tx * 2] = b0; sb[ty][tx * 2 + 1] = b1;
+  __syncthreads();
+  if (ty == 0 && col < H) {
+    float a0 = 0.f, a1 = 0.f, c0 = 0.f, c1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      a0 += sg[k][tx * 2]; a1 += sg[k][tx * 2 + 1];
+      c0 += sb[k][tx * 2]; c1 += sb[k][tx * 2 + 1];
+    }
+    part_g[static_cast<size_t>(blockIdx.y) * H + col] = a0;
+    part_g[static_cast<size_t>(blockIdx.y) * H + col + 1] = a1;
+    part_b[static_cast<size_t>(blockIdx.y) * H + col] = c0;
+    part_b[static_cast<size_t>(blockIdx.y) * H + col + 1] = c1;
+  }
+}
+
+// out[h] (+)= sum_slices part[slice][h]
+__global__ void fold_partials_kernel(const float* __restrict__ part, float* __restrict__ out, int slices, int H,
+                                     int accumulate) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= H) return;
+  float s = 0.f;
+  for (int k = 0; k < slices; ++k) s += part[static_cast<size_t>(k) * H + h];
+  out[h] = accumulate ? out[h] + s : s;
+}
+
+// Column sum of a bf16 matrix [rows, N] into partials[slice][N] (bias gradients).
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const __nv_bfloat16* __restrict__ a, int lda, float* __restrict__ part, int rows, int N,
+                      int rows_per_slice) {
+  __shared__ float sm[8][64];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = (blockIdx.x * 32 + tx) * 2;
+  const int r0 = blockIdx.y * rows_per_slice;
+  const int r1 = min(rows, r0 + rows_per_slice);
+  float s0 = 0.f, s1 = 0.f;
+  if (col < N) {
+    for (int r = r0 + ty; r < r1; r += 8) {
+      const float2 d = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(a + static_cast<size_t>(r) * lda + col));
+      s0 += d.x;
+      s1 += d.y;
+    }
+  }
+  sm[ty][tx * 2] = s0;
+  sm[ty][tx * 2 + 1] = s1;
+  __syncthreads();
+  if (ty == 0 && col < N) {
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      a0 += sm[k][tx * 2];
+      a1 += sm[k][tx * 2 + 1];
+    }
+    part[static_cast<size_t>(blockIdx.y) * N + col] = a0;
+    part[static_cast<size_t>(blockIdx.y) * N + col + 1] = a1;
+  }
+}
+
+}  // namespace
+
+int layernorm_fwd_launch(const void* x, const void* residual, const float* gamma, const float* beta, void* y,
+                         void* sum_out, float* mean, float* rstd, int rows, int H, float eps, int num_sms,
+                         cudaStream_t stream) {
+  if (H % 8) return -3;
+  const int blocks = min((rows + kLnWarpsPerBlock - 1) / kLnWarpsPerBlock, num_sms * 16);
+  const dim3 grid(blocks), block(kLnWarpsPerBlock * 32);
+  const auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  const auto* rb = reinterpret_cast<const __nv_bfloat16*>(residual);
+  auto* yb = reinterpret_cast<__nv_bfloat16*>(y);
+  auto* sb = reinterpret_cast<__nv_bfloat16*>(sum_out);
+#define SSB_LN_CASE(V)                                                                                       \
+  ln_fwd_kernel<V><<<grid, block, 0, stream>>>(xb, rb, gamma, beta, yb, sb, mean, rstd, rows, H, eps)
+  switch (H) {
+    case 512: SSB_LN_CASE(2); break;
+    case 1024: SSB_LN_CASE(4); break;
+    case 2048: SSB_LN_CASE(8); break;
+    case 4096: SSB_LN_CASE(16); break;
+    default: SSB_LN_CASE(0); break;
+  }
+#undef SSB_LN_CASE
+  return static_cast<int>(cudaGetLastError());
+}
+
+// part_g / part_b: scratch of `slices` x H floats each (slices = ln_bwd_slices(rows)).
+int ln_bwd_slices(int rows) {
+  int s = (rows + 255) / 256;
+  return s < 1 ? 1 : (s > 128 ? 128 : s);
+}
+
+int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                         const void* dres, void* dx, float* dgamma, float* dbeta, float* part_g, float* part_b,
+                         int accumulate_wgrad, int rows, int H, int num_sms, cudaStream_t stream) {
+  if (H % 8) return -3;
+  const int blocks = min((rows + kLnWarpsPerBlock - 1) / kLnWarpsPerBlock, num_sms * 16);
+  ln_bwd_dx_kernel<<<blocks, kLnWarpsPerBlock * 32, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x), gamma, mean, rstd,
+      reinterpret_cast<const __nv_bfloat16*>(dres), reinterpret_cast<__nv_bfloat16*>(dx), rows, H);
+  const int slices = ln_bwd_slices(rows);
+  const int rps = (rows + slices - 1) / slices;
+  dim3 grid((H / 2 + 31) / 32, slices);
+  ln_bwd_gb_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
+                                                     reinterpret_cast<const __nv_bfloat16*>(x), mean, rstd, part_g,
+                                                     part_b, rows, H, rps);
+  fold_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(part_g, dgamma, slices, H, accumulate_wgrad);
+  fold_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(part_b, dbeta, slices, H, accumulate_wgrad);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out[N] (+)= column sums of a[rows, N]; `part` is scratch of ln_bwd_slices(rows) x N floats.
+int colsum_launch(const void* a, int lda, float* out, float* part, int accumulate, int rows, int N,
+                  cudaStream_t stream) {
+  if (N % 2 || lda % 2) return -3;
+  const int slices = ln_bwd_slices(rows);
+  const int rps = (rows + slices - 1) / slices;
+  dim3 grid((N / 2 + 31) / 32, slices);
+  colsum_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(a), lda, part, rows, N, rps);
+  fold_partials_kernel<<<(N + 255) / 256, 256, 0, stream>>>(part, out, slices, N, accumulate);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace ssb
