@@ -83,13 +83,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait on an mbarrier phase.  Returns false when the limit ran out or
 // when another role of the CTA already raised `*abort_flag` (shared memory).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = global_timer_ns();
+  // The global timer is slow to read (microseconds), so it is only consulted once in a while and
+  // never on the fast path; the iteration limit alone already bounds the loop.
+  uint64_t t0 = 0;
   for (uint32_t it = 0; it < kMbarSpinLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 1023u) == 1023u) {
+    if ((it & 8191u) == 8191u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kMbarTimeLimitNs) break;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kMbarTimeLimitNs) break;
     }
   }
   *abort_flag = 1;

@@ -42,12 +42,49 @@ def available() -> bool:
     return _mod is not None and torch.cuda.is_available()
 
 
+# kernels launched by one call of each binding (for launch accounting in benchmarks)
+KERNELS_PER_CALL = {"gemm": 1, "layernorm_fwd": 1, "layernorm_bwd": 4, "colsum": 2, "elementwise": 1,
+                    "cast_f32_to_bf16": 1, "softmax_fwd": 1, "softmax_bwd": 1, "sumsq": 2, "adam_step": 1,
+                    "sgd_step": 1, "embedding_fwd": 1, "embedding_bwd": 1, "ce_stats": 1, "ce_finalize": 1,
+                    "attn_fwd": 1, "attn_bwd": 3}
+launch_counter = {"kernels": 0, "calls": 0}
+
+
+class _Counting:
+    """Proxy over the extension module that counts kernel launches issued through it."""
+
+    def __init__(self, mod):
+        self._mod = mod
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._mod, name)
+            n = KERNELS_PER_CALL.get(name, 0)
+            if n == 0:
+                fn = raw
+            else:
+                def fn(*a, _raw=raw, _n=n):
+                    launch_counter["kernels"] += _n
+                    launch_counter["calls"] += 1
+                    return _raw(*a)
+            self._cache[name] = fn
+        return fn
+
+
+_proxy = None
+
+
 def ext():
-    """The extension module; raises when it cannot be loaded."""
+    """The extension module (behind a launch-counting proxy); raises when it cannot be loaded."""
+    global _proxy
     _load()
     if _mod is None:
         raise RuntimeError(f"superscaler_b200 native extension unavailable: {_err}")
-    return _mod
+    if _proxy is None:
+        _proxy = _Counting(_mod)
+    return _proxy
 
 
 def check_status() -> int:

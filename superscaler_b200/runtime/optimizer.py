@@ -1,0 +1,149 @@
+"""Stage optimizer over the flat parameter buffers: data-parallel gradient reduction, global gradient
+norm, clipping, Adam / SGD update and bf16 copy-out in fused kernels, with no host synchronisation.
+
+Replaces the reference chain LocalDDP.allreduce_gradients -> copy model grads to main grads ->
+unscale / inf check -> clip_grad_norm_fp32 -> apex FusedAdam -> copy main params to model params
+(runtime/megatron/model/distributed.py:195-263, runtime/megatron/optimizer/optimizer.py:348-443,
+runtime/megatron/optimizer/clip_grads.py:29-120).
+
+Gradient norm: every unique parameter element must be counted once.  A parameter replicated over a TP
+group of size t and a DP group of size d exists t * d times in the job, a TP-sharded one d times, so each
+rank weights its local sum of squares by 1 / copies before the all-reduce over the whole job.  (The
+reference all-reduces unweighted sums over the world group, clip_grads.py:79-81,106-108.)
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+from .params import ParamStore
+
+
+def _merge(ranges: List[Tuple[int, int]]) -> List[Tuple[int, int]]:
+    out: List[Tuple[int, int]] = []
+    for off, n in sorted(ranges):
+        if out and out[-1][0] + out[-1][1] == off:
+            out[-1] = (out[-1][0], out[-1][1] + n)
+        else:
+            out.append((off, n))
+    return out
+
+
+class StageOptimizer:
+    def __init__(self, store: ParamStore, pstate, *, lr=1.5e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
+                 clip_grad=1.0, kind="adam", momentum=0.9):
+        self.store, self.pstate = store, pstate
+        self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
+        self.clip_grad, self.kind, self.momentum = clip_grad, kind, momentum
+        self.step_count = 0
+        dev = store.device
+        self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.skipped = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.grad_norm_sq = self.sumsq
+        # ranges grouped by the number of copies of the parameter in the job
+        groups: Dict[int, List[Tuple[int, int]]] = {}
+        for s in store.specs:
+            off, n = store.offsets[s.name]
+            replicated_over_tp = s.tp > 1 and s.shard_dim is None
+            copies = s.dp * (s.tp if replicated_over_tp else 1)
+            groups.setdefault(copies, []).append((off, (n + 127) // 128 * 128))
+        self.norm_groups = {c: _merge(r) for c, r in groups.items()}
+        self.dp_buckets = store.buckets_by_dp()
+
+    # ---- data-parallel gradient reduction (NCCL path) -----------------------------------------
+    def reduce_gradients(self) -> None:
+        """Average gradients over each op's DP group, one all-reduce per contiguous (tp, dp) range."""
+        for (tp, dp), ranges in self.dp_buckets.items():
+            if dp == 1:
+                continue
+            pl = self.pstate.placement(tp, dp)
+            group = self.pstate.group(pl.dp_ranks)
+            for off, n in ranges:
+                buf = self.store.grad[off:off + n]
+                buf.mul_(1.0 / dp)
+                dist.all_reduce(buf, group=group)
+
+    # ---- norm + update ----------------------------------------------------------------------
+    def _global_sumsq(self) -> torch.Tensor:
+        g = self.store.grad
+        first = True
+        if g.is_cuda:
+            ext = native.ext()
+            for copies, ranges in self.norm_groups.items():
+                for off, n in ranges:
+                    if copies == 1:
+                        ext.sumsq(g[off:off + n], self.sumsq, not first)
+                    else:
+                        tmp = torch.zeros(1, dtype=torch.float32, device=g.device)
+                        ext.sumsq(g[off:off + n], tmp, False)
+                        if first:
+                            self.sumsq.copy_(tmp / copies)
+                        else:
+                            self.sumsq.add_(tmp / copies)
+                    first = False
+        else:
+            total = torch.zeros(1, dtype=torch.float32)
+            for copies, ranges in self.norm_groups.items():
+                for off, n in ranges:
+                    total += (g[off:off + n] ** 2).sum() / copies
+            self.sumsq.copy_(total)
+        if self.pstate.world_size > 1:
+            dist.all_reduce(self.sumsq)
+        return self.sumsq
+
+    def step(self, lr: Optional[float] = None, grad_scale: float = 1.0, zero_grad: bool = True) -> None:
+        lr = self.lr if lr is None else lr
+        self.step_count += 1
+        st = self.store
+        sumsq = self._global_sumsq()
+        if st.grad.is_cuda:
+            ext = native.ext()
+            if self.kind == "adam":
+                ext.adam_step(st.master, st.exp_avg, st.exp_avg_sq, st.grad, st.model16, sumsq, self.skipped, lr,
+                              self.betas[0], self.betas[1], self.eps, self.wd, self.step_count, grad_scale,
+                              self.clip_grad, st.wd_end, zero_grad)
+            else:
+                ext.sgd_step(st.master, st.exp_avg, st.grad, st.model16, sumsq, self.skipped, lr, self.momentum,
+                             self.wd, grad_scale, self.clip_grad, st.wd_end, zero_grad, self.step_count == 1)
+            return
+        # CPU restatement
+        norm = float(sumsq.sqrt()) * grad_scale
+        clip = min(1.0, self.clip_grad / (norm + 1e-6)) if self.clip_grad > 0 else 1.0
+        g = st.grad * (grad_scale * clip)
+        wd = torch.zeros_like(g)
+        wd[:st.wd_end] = self.wd
+        if self.kind == "adam":
+            b1, b2 = self.betas
+            st.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
+            st.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+            bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
+            denom = st.exp_avg_sq.sqrt() / (bc2 ** 0.5) + self.eps
+            st.master.sub_(lr * ((st.exp_avg / bc1) / denom + wd * st.master))
+        else:
+            g = g + wd * st.master
+            if self.step_count == 1:
+                st.exp_avg.copy_(g)
+            else:
+                st.exp_avg.mul_(self.momentum).add_(g)
+            st.master.sub_(lr * st.exp_avg)
+        st.model16.copy_(st.master.to(torch.bfloat16))
+        if zero_grad:
+            st.grad.zero_()
+
+    def grad_norm(self) -> float:
+        """Host read of the last global gradient norm (synchronises)."""
+        return float(self.sumsq.sqrt())
+
+    def state_dict(self) -> dict:
+        return {"step": self.step_count, "exp_avg": self.store.exp_avg.clone(), "exp_avg_sq": self.store.exp_avg_sq.clone(),
+                "master": self.store.master.clone()}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.step_count = sd["step"]
+        self.store.exp_avg.copy_(sd["exp_avg"])
+        self.store.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        self.store.master.copy_(sd["master"])
+        self.store.model16.copy_(self.store.master.to(torch.bfloat16))

@@ -1,0 +1,131 @@
+"""A pipeline stage: the ops [start, end) of the flat op list, their parameters, op fusion and per-op
+recompute.
+
+Counterpart of the reference's FlexPipeModel (runtime/megatron/model/flex_model.py:361-609): consecutive ops
+whose plan says recompute = 1 form a checkpointed segment, with forced breaks before every
+`*-1st-layernorm` and `*-conv1` (flex_model.py:564-588).  A checkpointed segment stores only its input
+tensors and the dropout seed counter; backward replays it with gradients enabled.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..models.base import Env, Op, OpInfo
+from ..ops import functional as F
+
+
+class _CheckpointFn(torch.autograd.Function):
+    """Recompute-in-backward for a run of ops operating on a dict of named tensors.  The dropout seed counter
+    is saved before the segment and replayed for the recomputation (the role of CheckpointFunction's RNG
+    bookkeeping, runtime/megatron/mpu/random.py:246-326)."""
+
+    @staticmethod
+    def forward(ctx, run, in_keys, holder, *tensors):
+        ctx.run, ctx.in_keys = run, in_keys
+        ctx.seed_state = F.seed_state().get_state()
+        ctx.save_for_backward(*tensors)
+        ctx.req = [t.requires_grad for t in tensors]
+        with torch.no_grad():
+            st = dict(zip(in_keys, tensors))
+            run(st)
+        out_keys = [k for k, v in st.items() if isinstance(v, torch.Tensor)]
+        holder["out_keys"] = out_keys
+        ctx.out_keys = out_keys
+        outs = tuple(st[k] for k in out_keys)
+        # inputs passed through unchanged must not be returned as the same tensor object
+        ids_in = {id(t) for t in tensors}
+        return tuple(o.view_as(o) if id(o) in ids_in else o for o in outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        tensors = ctx.saved_tensors
+        ins = []
+        for t, r in zip(tensors, ctx.req):
+            d = t.detach()
+            d.requires_grad_(r and t.is_floating_point())
+            ins.append(d)
+        saved = F.seed_state().get_state()
+        F.seed_state().set_state(ctx.seed_state)
+        with torch.enable_grad():
+            st = dict(zip(ctx.in_keys, ins))
+            ctx.run(st)
+        F.seed_state().set_state(saved)
+        outs, gs = [], []
+        for k, g in zip(ctx.out_keys, grads):
+            o = st[k]
+            if g is not None and isinstance(o, torch.Tensor) and o.requires_grad:
+                outs.append(o)
+                gs.append(g)
+        if outs:
+            torch.autograd.backward(outs, gs)
+        return (None, None, None) + tuple(i.grad if i.requires_grad else None for i in ins)
+
+
+class Segment:
+    def __init__(self, ops: List[Op], recompute: bool):
+        self.ops, self.recompute = ops, recompute
+
+    def _run(self, st):
+        for op in self.ops:
+            op.forward(st)
+
+    def forward(self, st: Dict[str, torch.Tensor]) -> None:
+        if not self.recompute or not torch.is_grad_enabled():
+            self._run(st)
+            return
+        in_keys = [k for k, v in st.items() if isinstance(v, torch.Tensor)]
+        extras = {k: v for k, v in st.items() if not isinstance(v, torch.Tensor)}
+
+        def run(inner):
+            inner.update(extras)  # plain Python values (scales, flags) are visible inside the segment too
+            self._run(inner)
+
+        holder: dict = {}
+        outs = _CheckpointFn.apply(run, in_keys, holder, *[st[k] for k in in_keys])
+        for k in in_keys:
+            st.pop(k)
+        for k, v in zip(holder["out_keys"], outs):
+            st[k] = v
+
+
+def split_segments(ops: List[Op]) -> List[Segment]:
+    """Maximal runs of equal recompute flag; a recomputed run is cut before each layer's first op."""
+    segs: List[Segment] = []
+    cur: List[Op] = []
+    cur_flag = None
+    for op in ops:
+        flag = bool(op.info.recompute)
+        name = op.info.name
+        new_layer = name.endswith("1st-layernorm") or name.endswith("-conv1")
+        if cur and (flag != cur_flag or (flag and new_layer)):
+            segs.append(Segment(cur, cur_flag))
+            cur = []
+        cur.append(op)
+        cur_flag = flag
+    if cur:
+        segs.append(Segment(cur, cur_flag))
+    return segs
+
+
+class Stage:
+    """Ops + parameters of this rank's pipeline stage."""
+
+    def __init__(self, infos: Sequence[OpInfo], env: Env, build_op: Callable[[OpInfo, Env], Op], fuse=None):
+        self.env = env
+        env.stage_ops = infos
+        self.raw_ops: List[Op] = [build_op(i, env) for i in infos]
+        for op in self.raw_ops:
+            op.declare()
+        env.store.materialize()
+        self.ops = fuse(self.raw_ops) if fuse is not None else list(self.raw_ops)
+        self.segments = split_segments(self.ops)
+
+    def forward(self, st: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        for seg in self.segments:
+            seg.forward(st)
+        return st
+
+    def kernel_launch_estimate(self) -> int:
+        return len(self.ops)

@@ -1,0 +1,187 @@
+"""Training driver: builds this rank's stage from a plan JSON and runs iterations.
+
+Public API (what a user calls):
+
+    trainer = Trainer.from_plan("plan.json", model_overrides={...})
+    for batch in loader:                      # pinned host tensors, one global batch
+        stats = trainer.train_step(batch)     # -> {"loss": float, ...}
+
+Counterpart of the reference's pretrain / train_step (runtime/megatron/training.py:83-168,656-752) with
+these differences: gradients accumulate in fp32 directly from the wgrad kernels; the optimizer step,
+clipping and the inf/nan skip run on the device without a host sync; timing uses CUDA events.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from typing import Any, Callable, Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..models.base import Env, OpInfo
+from ..ops import functional as F
+from ..parallel.state import ParallelState
+from .lr import LRSchedule
+from .optimizer import StageOptimizer
+from .params import ParamStore
+from .stage import Stage
+
+
+def _model_factory(model_name: str):
+    if model_name == "gpt":
+        from ..models import gpt as m
+        from ..models.fused import fuse_ops
+        return (m.gpt_config_from_plan, lambda c: m.gpt_op_names(c.num_layers),
+                lambda i, c: m.gpt_layer_of(i, c.num_layers), m.build_gpt_op, fuse_ops)
+    if model_name == "t5":
+        from ..models import t5 as m
+        from ..models.fused import fuse_ops
+        return (m.t5_config_from_plan, lambda c: m.t5_op_names(c.num_layers),
+                lambda i, c: m.t5_layer_of(i, c.num_layers), m.build_t5_op, fuse_ops)
+    if model_name == "resnet":
+        from ..models import resnet as m
+        return (m.resnet_config_from_plan, m.resnet_op_names, m.resnet_layer_of, m.build_resnet_op,
+                m.fuse_resnet_ops)
+    raise ValueError(f"unknown model {model_name}")
+
+
+class Trainer:
+    def __init__(self, plan: dict, *, rank: int = 0, world_size: int = 1, device=None, seed: int = 1234,
+                 model_overrides: Optional[dict] = None, lr: float = 1.5e-4, min_lr: float = 1e-5,
+                 weight_decay: float = 0.01, clip_grad: float = 1.0, lr_decay_steps: int = 320000,
+                 lr_warmup_steps: int = 3200, lr_style: str = "cosine", optimizer: str = "adam",
+                 fuse: bool = True, fused_comm: bool = False, training: bool = True):
+        self.plan = plan
+        self.rank, self.world_size = rank, world_size
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = torch.device(device)
+        self.model_name = plan["model_name"]
+        cfg_fn, names_fn, layer_fn, build_fn, fuse_fn = _model_factory(self.model_name)
+        self.cfg = cfg_fn(plan, **(model_overrides or {}))
+        self.global_bs = plan["global_batch_size"]
+        self.micro_bs = plan["micro_batch_size"]
+        self.num_microbatches = self.global_bs // self.micro_bs
+        self.pstate = ParallelState(plan["num_gpus"], rank, world_size)
+        names = names_fn(self.cfg)
+        counts = plan["num_ops_in_each_stage"]
+        assert sum(counts) == len(names), f"plan covers {sum(counts)} ops, model has {len(names)}"
+        self.op_names = names
+        self.stage_bounds = [(sum(counts[:i]), sum(counts[:i + 1])) for i in range(len(counts))]
+        # every process group any op needs, created in the same order on all ranks
+        if world_size > 1:
+            pairs = [list(zip(plan["model_parallel_size_of_each_op"][s], plan["data_parallel_size_of_each_op"][s]))
+                     for s in range(len(counts))]
+            self.pstate.ensure_groups(self.pstate.all_op_groups(pairs))
+        s = self.pstate.stage
+        lo, hi = self.stage_bounds[s]
+        infos = [OpInfo(name=names[i], index=i, layer=layer_fn(i, self.cfg),
+                        tp=plan["model_parallel_size_of_each_op"][s][i - lo],
+                        dp=plan["data_parallel_size_of_each_op"][s][i - lo],
+                        algo=plan["algo_of_each_op"][s][i - lo],
+                        recompute=plan["recompute_ops"][s][i - lo]) for i in range(lo, hi)]
+        self.infos = infos
+        F.manual_seed(seed + 100 * s)
+        self.store = ParamStore(self.device, base_seed=seed)
+        self.env = Env(cfg=self.cfg, pstate=self.pstate, store=self.store, micro_bs=self.micro_bs,
+                       fused_comm=fused_comm)
+        self.env.training = training
+        self.stage = Stage(infos, self.env, build_fn, fuse_fn if fuse else None)
+        self.optimizer = StageOptimizer(self.store, self.pstate, lr=lr, weight_decay=weight_decay, clip_grad=clip_grad,
+                                        kind=optimizer)
+        self.lr_schedule = LRSchedule(lr, min_lr, lr_warmup_steps, lr_decay_steps, lr_style)
+        self.iteration = 0
+        self.pipeline = None
+        if self.pstate.num_stages > 1:
+            from .schedules import PipelineRunner
+            self.pipeline = PipelineRunner(self)
+        self._loss_buf = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._tied = None
+        if self.pstate.num_stages > 1:
+            from .tied import TiedWeights
+            self._tied = TiedWeights(self)
+        self.timers: Dict[str, float] = {}
+
+    @classmethod
+    def from_plan(cls, path: str, **kw) -> "Trainer":
+        with open(path) as f:
+            plan = json.load(f)
+        return cls(plan, **kw)
+
+    # ---- batches ----------------------------------------------------------------------------
+    def first_op_dp(self):
+        return self.infos[0].dp
+
+    def local_rows(self, info: OpInfo, total: int) -> slice:
+        """Rows of the stage-aggregate micro-batch that belong to this rank for an op with degree dp."""
+        pl = self.pstate.placement(info.tp, info.dp)
+        per = total // info.dp
+        return slice(pl.dp_rank * per, (pl.dp_rank + 1) * per)
+
+    def microbatch_inputs(self, batch: Dict[str, torch.Tensor], mb: int) -> Dict[str, Any]:
+        """Device-side slice of micro-batch `mb` for this rank (first stage: inputs, last stage: labels)."""
+        st: Dict[str, Any] = {}
+        lo = mb * self.micro_bs
+        first, last = self.infos[0], self.infos[-1]
+        for k, v in batch.items():
+            info = last if k in ("labels", "loss_mask") else first
+            rows = self.local_rows(info, self.micro_bs)
+            st[k] = v[lo + rows.start: lo + rows.stop]
+        st["loss_scale"] = 1.0 / self.num_microbatches
+        return st
+
+    def to_device(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        return {k: (v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v)
+                for k, v in batch.items()}
+
+    # ---- one iteration ----------------------------------------------------------------------
+    def forward_backward(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
+        """Runs all micro-batches; returns the summed (already averaged-per-micro-batch) loss on device."""
+        self._loss_buf.zero_()
+        if self.pipeline is not None:
+            return self.pipeline.run(batch, self._loss_buf)
+        for mb in range(self.num_microbatches):
+            st = self.microbatch_inputs(batch, mb)
+            self.stage.forward(st)
+            loss = st["loss"]
+            loss.backward()
+            self._loss_buf += loss.detach()
+        return self._loss_buf
+
+    def _fold_autograd_grads(self) -> None:
+        """Gradients that reached a parameter through plain autograd (not a fused wgrad kernel)."""
+        for p in self.store.params.values():
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(torch.float32))
+                p.grad = None
+
+    def train_step(self, batch: Dict[str, torch.Tensor]) -> Dict[str, Any]:
+        """One optimizer step on one global batch.  `batch` may live in pinned host memory."""
+        batch = self.to_device(batch)
+        loss = self.forward_backward(batch)
+        self._fold_autograd_grads()
+        self.optimizer.reduce_gradients()
+        if self._tied is not None:
+            self._tied.sync_grads()
+        lr = self.lr_schedule.step()
+        self.optimizer.step(lr=lr)
+        self.iteration += 1
+        return {"loss_tensor": loss, "lr": lr, "iteration": self.iteration}
+
+    def loss_value(self, stats: Dict[str, Any]) -> float:
+        """Host read of the iteration loss (synchronises); averaged over the last stage's DP group."""
+        t = stats["loss_tensor"].clone()
+        if self.world_size > 1:
+            last = self.pstate.num_stages - 1
+            src_dp = self.plan["data_parallel_size_of_each_op"][last][-1]
+            if not self.pstate.is_last_stage():
+                t.zero_()
+            dist.all_reduce(t)
+            g = self.plan["num_gpus"][last]
+            t /= g  # every rank of the last stage holds its DP shard's mean; TP replicas repeat it
+        return float(t.item())
+
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.store.params.values())

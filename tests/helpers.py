@@ -1,0 +1,29 @@
+"""Shared builders for tiny plans used by the tests."""
+from superscaler_b200.models.gpt import gpt_op_names
+
+
+def tiny_gpt_plan(layers=2, seq=128, hidden=128, heads=2, head_dim=64, vocab=512, global_bs=4, micro_bs=2,
+                  recompute=0, num_gpus=(1,), ops_per_stage=None, tp=None, dp=None):
+    names = gpt_op_names(layers)
+    n = len(names)
+    stages = len(num_gpus)
+    if ops_per_stage is None:
+        per = n // stages
+        ops_per_stage = [per] * stages
+        ops_per_stage[-1] += n - per * stages
+    tp = tp or [1] * stages
+    dp = dp or [g // t for g, t in zip(num_gpus, tp)]
+    rc_flat = [0] + [recompute] * (n - 3) + [0, 0]
+    rc, start = [], 0
+    for c in ops_per_stage:
+        rc.append(rc_flat[start:start + c])
+        start += c
+    return {"model_name": "gpt", "model_size": "tiny", "num_layers": layers, "seq_length": seq,
+            "max_position_embeddings": seq, "num_attention_heads": heads, "hidden_size": hidden,
+            "kv_channels": head_dim, "vocab_size": vocab, "global_batch_size": global_bs,
+            "micro_batch_size": micro_bs, "num_stages": stages, "num_gpus": list(num_gpus),
+            "checkpoint_activations": [bool(recompute)] * stages, "resharding_stages": [False] * stages,
+            "num_ops_in_each_stage": list(ops_per_stage),
+            "model_parallel_size_of_each_op": [[tp[s]] * ops_per_stage[s] for s in range(stages)],
+            "data_parallel_size_of_each_op": [[dp[s]] * ops_per_stage[s] for s in range(stages)],
+            "recompute_ops": rc, "algo_of_each_op": [[0] * c for c in ops_per_stage]}

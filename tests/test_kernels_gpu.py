@@ -1,0 +1,286 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+from superscaler_b200.ops import functional as F
+from superscaler_b200.ops import native
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).abs().max() / (b.abs().max() + 1e-6)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    torch.cuda.synchronize()
+    assert native.check_status() == 0, "a kernel's bounded wait ran out"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 512, 256), (1000, 776, 520), (4096, 2048, 2048), (64, 96, 72)])
+def test_gemm_variants(a_mn, b_mn, shape):
+    M, N, K = shape
+    torch.manual_seed(0)
+    A = torch.randn(M, K, device=DEV).bfloat16()
+    B = torch.randn(N, K, device=DEV).bfloat16()
+    ref = A.float() @ B.float().t()
+    a_in = A.t().contiguous() if a_mn else A
+    b_in = B.t().contiguous() if b_mn else B
+    out = F.gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn)
+    assert rel(out, ref) < 6e-3
+    acc = torch.ones(M, N, device=DEV)
+    F.gemm(a_in, b_in, out=acc, a_mn=a_mn, b_mn=b_mn, accumulate=True)
+    assert rel(acc, ref + 1) < 1e-4
+
+
+def test_gemm_strided_operands():
+    torch.manual_seed(1)
+    big = torch.randn(300, 1024, device=DEV).bfloat16()
+    A = big[:, 256:512]          # leading dimension 1024, 256 columns
+    B = torch.randn(192, 256, device=DEV).bfloat16()
+    out = torch.zeros(300, 384, device=DEV, dtype=torch.bfloat16)
+    F.gemm(A, B, out=out[:, 64:256])
+    assert rel(out[:, 64:256], A.float() @ B.float().t()) < 6e-3
+    assert out[:, :64].abs().max() == 0 and out[:, 256:].abs().max() == 0
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(2)
+    M, N, K = 512, 768, 256
+    A = torch.randn(M, K, device=DEV).bfloat16()
+    B = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    bias = torch.randn(N, device=DEV).bfloat16()
+    res = torch.randn(M, N, device=DEV).bfloat16()
+    pre = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    v = A.float() @ B.float().t() + bias.float()
+    out = F.gemm(A, B, bias=bias, act=F.ACT_GELU, preact_out=pre, residual=res)
+    assert rel(pre, v) < 6e-3
+    assert rel(out, F._gelu_tanh(v) + res.float()) < 6e-3
+    out = F.gemm(A, B, bias=bias, act=F.ACT_RELU)
+    assert rel(out, torch.relu(v)) < 6e-3
+    aux = torch.randn(M, N, device=DEV).bfloat16()
+    out = F.gemm(A, B, act=F.ACT_DGELU, aux=aux)
+    assert rel(out, (A.float() @ B.float().t()) * F._gelu_tanh_grad(aux.float())) < 6e-3
+    out = F.gemm(A, B, act=F.ACT_DRELU, aux=aux)
+    assert rel(out, (A.float() @ B.float().t()) * (aux.float() > 0)) < 6e-3
+    out = F.gemm(A, B, alpha=0.5, bias=bias.float())
+    assert rel(out, 0.5 * (A.float() @ B.float().t()) + bias.float()) < 6e-3
+
+
+def test_gemm_dropout_matches_elementwise_mask():
+    torch.manual_seed(3)
+    M, N, K = 256, 512, 128
+    A = torch.randn(M, K, device=DEV).bfloat16()
+    B = torch.randn(N, K, device=DEV).bfloat16()
+    v = A.float() @ B.float().t()
+    out = F.gemm(A, B, dropout_p=0.1, seed=77)
+    kept = out != 0
+    frac = kept.float().mean().item()
+    assert abs(frac - 0.9) < 0.01
+    assert rel(out[kept], (v / (58982 / 65536))[kept]) < 6e-3
+    ones = torch.ones(M, N, device=DEV, dtype=torch.bfloat16)
+    m_fwd = native.ext().elementwise(F.EW_DROPOUT, ones, None, None, 0.1, 77) != 0
+    m_bwd = native.ext().elementwise(F.EW_DROPOUT_BWD, ones, None, None, 0.1, 77) != 0
+    assert bool((m_fwd == kept).all()) and bool((m_bwd == kept).all())
+    other = native.ext().elementwise(F.EW_DROPOUT, ones, None, None, 0.1, 78) != 0
+    assert not bool((other == kept).all())
+
+
+@pytest.mark.parametrize("H", [512, 1024, 2048, 4096, 1536])
+def test_layernorm(H):
+    torch.manual_seed(4)
+    x = torch.randn(777, H, device=DEV).bfloat16()
+    gam, bet = torch.randn(H, device=DEV), torch.randn(H, device=DEV)
+    y, mean, rstd = native.ext().layernorm_fwd(x, None, gam, bet, 1e-5)
+    ref = torch.nn.functional.layer_norm(x.float(), (H,), gam, bet, 1e-5)
+    assert rel(y, ref) < 6e-3
+    dy = torch.randn_like(x)
+    xr, gr, br = x.float().requires_grad_(True), gam.clone().requires_grad_(True), bet.clone().requires_grad_(True)
+    torch.nn.functional.layer_norm(xr, (H,), gr, br, 1e-5).backward(dy.float())
+    dg, db = torch.zeros(H, device=DEV), torch.zeros(H, device=DEV)
+    dx = native.ext().layernorm_bwd(dy, x, gam, mean, rstd, None, dg, db, False)
+    assert rel(dx, xr.grad) < 6e-3 and rel(dg, gr.grad) < 1e-4 and rel(db, br.grad) < 1e-4
+    native.ext().layernorm_bwd(dy, x, gam, mean, rstd, None, dg, db, True)
+    assert rel(dg, 2 * gr.grad) < 1e-4
+
+
+def test_layernorm_residual_prologue():
+    torch.manual_seed(5)
+    H = 2048
+    x, r = torch.randn(100, H, device=DEV).bfloat16(), torch.randn(100, H, device=DEV).bfloat16()
+    gam, bet = torch.ones(H, device=DEV), torch.zeros(H, device=DEV)
+    y, mean, rstd, s = native.ext().layernorm_fwd(x, r, gam, bet, 1e-5)
+    sref = (x.float() + r.float()).bfloat16()
+    assert torch.equal(s, sref)
+    assert rel(y, torch.nn.functional.layer_norm(sref.float(), (H,), gam, bet, 1e-5)) < 6e-3
+
+
+def test_colsum_and_elementwise():
+    torch.manual_seed(6)
+    a = torch.randn(1000, 512, device=DEV).bfloat16()
+    out = torch.zeros(512, device=DEV)
+    native.ext().colsum(a, out, False)
+    assert rel(out, a.float().sum(0)) < 1e-5
+    x = torch.randn(300, 1024, device=DEV).bfloat16()
+    b = torch.randn(1024, device=DEV).bfloat16()
+    r, g = torch.randn_like(x), torch.randn_like(x)
+    e = native.ext().elementwise
+    assert rel(e(F.EW_BIAS_GELU, x, None, b, 0.0, 0), F._gelu_tanh(x.float() + b.float())) < 6e-3
+    assert rel(e(F.EW_BIAS_GELU_BWD, x, g, b, 0.0, 0), g.float() * F._gelu_tanh_grad(x.float() + b.float())) < 6e-3
+    assert rel(e(F.EW_BIAS_DROP_ADD, x, r, b, 0.0, 0), x.float() + b.float() + r.float()) < 6e-3
+    assert rel(e(F.EW_RELU, x, None, b, 0.0, 0), torch.relu(x.float() + b.float())) < 6e-3
+    assert rel(e(F.EW_RELU_BWD, x, g, b, 0.0, 0), g.float() * ((x.float() + b.float()) > 0)) < 6e-3
+    assert rel(e(F.EW_ADD, x, r, None, 0.0, 0), x.float() + r.float()) < 6e-3
+    keep = (e(F.EW_DROPOUT, x, None, None, 0.25, 5) != 0).float().mean().item()
+    assert abs(keep - 0.75) < 0.01
+
+
+def test_softmax_family():
+    torch.manual_seed(7)
+    x = torch.randn(2, 4, 256, 256, device=DEV).bfloat16()
+    tri = torch.ones(256, 256, dtype=torch.bool, device=DEV).tril()
+    y = F.scaled_softmax(x, 0.5, 1)
+    ref = torch.softmax((x.float() * 0.5).masked_fill(~tri, float("-inf")), -1)
+    assert rel(y, ref) < 6e-3
+    g = torch.randn_like(x)
+    dx = native.ext().softmax_bwd(g, y, 0.5)
+    yf = y.float()
+    assert rel(dx, 0.5 * (g.float() * yf - yf * (g.float() * yf).sum(-1, keepdim=True))) < 6e-3
+    mask = (torch.rand(2, 1, 256, 256, device=DEV) < 0.2).to(torch.uint8)
+    y = F.scaled_softmax(x, 0.5, 2, mask)
+    assert rel(y, torch.softmax((x.float() * 0.5).masked_fill(mask.bool(), -10000.0), -1)) < 6e-3
+    y = F.scaled_softmax(x, 0.5, 0)
+    assert rel(y, torch.softmax(x.float() * 0.5, -1)) < 6e-3
+
+
+def test_adam_and_sumsq():
+    torch.manual_seed(8)
+    n = 1_000_003
+    p, g = torch.randn(n, device=DEV), torch.randn(n, device=DEV)
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    p16 = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    ss = torch.zeros(1, device=DEV)
+    native.ext().sumsq(g, ss, False)
+    assert rel(ss, (g.double() ** 2).sum()[None]) < 1e-5
+    pr = p.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([pr], lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    for step in (1, 2):
+        gg = torch.randn(n, device=DEV)
+        g.copy_(gg)
+        native.ext().sumsq(g, ss, False)
+        clip = min(1.0, 1.0 / (gg.norm().item() + 1e-6))
+        pr.grad = gg * clip
+        opt.step()
+        native.ext().adam_step(p, m, v, g, p16, ss, None, 1e-2, 0.9, 0.999, 1e-8, 0.01, step, 1.0, 1.0, n, True)
+    assert rel(p, pr.detach()) < 1e-5 and rel(p16, pr.detach()) < 6e-3 and float(g.abs().max()) == 0.0
+    # non-finite gradients: the step is skipped on the device and reported
+    skipped = torch.zeros(1, device=DEV, dtype=torch.int32)
+    before = p.clone()
+    ss.fill_(float("inf"))
+    native.ext().adam_step(p, m, v, g, p16, ss, skipped, 1e-2, 0.9, 0.999, 1e-8, 0.01, 3, 1.0, 1.0, n, True)
+    assert torch.equal(p, before) and int(skipped.item()) == 1
+
+
+def test_embedding_and_cross_entropy():
+    torch.manual_seed(9)
+    V, H, T = 1000, 512, 300
+    W, P = torch.randn(V, H, device=DEV).bfloat16(), torch.randn(64, H, device=DEV).bfloat16()
+    ids, pos = torch.randint(0, V, (T,), device=DEV), torch.randint(0, 64, (T,), device=DEV)
+    out = native.ext().embedding_fwd(ids, pos, W, P, 0, 0.0, 0)
+    assert rel(out, W.float()[ids] + P.float()[pos]) < 6e-3
+    half = native.ext().embedding_fwd(ids, None, W[500:].contiguous(), None, 500, 0.0, 0)
+    refh = torch.where((ids >= 500)[:, None], W.float()[ids], torch.zeros(1, device=DEV))
+    assert rel(half, refh) < 6e-3
+    g = torch.randn(T, H, device=DEV).bfloat16()
+    dW, dP = torch.zeros(V, H, device=DEV), torch.zeros(64, H, device=DEV)
+    native.ext().embedding_bwd(ids, pos, g, dW, dP, 0, 0.0, 0)
+    assert rel(dW, torch.zeros(V, H, device=DEV).index_add_(0, ids, g.float())) < 1e-5
+    assert rel(dP, torch.zeros(64, H, device=DEV).index_add_(0, pos, g.float())) < 1e-5
+    Vv = 5000
+    logits = (torch.randn(T, Vv, device=DEV) * 3).bfloat16()
+    tg = torch.randint(0, Vv, (T,), device=DEV)
+    lf = logits.float().clone().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lf, tg, reduction="none")
+    ref.sum().backward()
+    st = native.ext().ce_stats(logits, tg, 0)
+    loss = native.ext().ce_finalize(logits, tg, st, None, 0, 1.0, True)
+    assert rel(loss, ref) < 1e-4 and rel(logits, lf.grad) < 6e-3
+
+
+@pytest.mark.parametrize("cfg", [(1, 1, 128, 128, False), (1, 2, 256, 128, True), (2, 3, 512, 128, True),
+                                 (2, 2, 256, 64, True), (1, 2, 384, 64, False), (1, 2, 200, 128, False)])
+def test_flash_attention_fwd_bwd(cfg):
+    B, NH, S, HD, causal = cfg
+    torch.manual_seed(10)
+    h = NH * HD
+    qkv = (torch.randn(B * S, 3 * h, device=DEV) * 0.5).bfloat16()
+    scale = 1.0 / math.sqrt(HD)
+    qr = qkv.float().clone().requires_grad_(True)
+    ref = F._attn_reference(qr[:, :h], qr[:, h:2 * h], qr[:, 2 * h:], B, NH, S, S, HD, scale, causal, None)
+    do = torch.randn(B * S, h, device=DEV).bfloat16()
+    ref.backward(do.float())
+    x = qkv.clone().requires_grad_(True)
+    o = F.fused_qkv_attention(x, B, NH, S, HD, causal=causal)
+    o.backward(do)
+    assert rel(o, ref) < 8e-3
+    for lo in (0, h, 2 * h):
+        assert rel(x.grad[:, lo:lo + h], qr.grad[:, lo:lo + h]) < 1.5e-2
+
+
+def test_flash_attention_cross_and_kv_lens():
+    torch.manual_seed(11)
+    B, NH, SQ, SK, HD = 2, 2, 128, 384, 64
+    h = NH * HD
+    q = (torch.randn(B * SQ, h, device=DEV) * 0.5).bfloat16().requires_grad_(True)
+    kv = (torch.randn(B * SK, 2 * h, device=DEV) * 0.5).bfloat16().requires_grad_(True)
+    lens = torch.tensor([384, 250], device=DEV, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(HD)
+    o = F.flash_attention(q, kv, kv, B, NH, SQ, SK, HD, cols=(0, 0, h), scale=scale, kv_lens=lens)
+    do = torch.randn_like(o)
+    o.backward(do)
+    qr, kvr = q.detach().float().requires_grad_(True), kv.detach().float().requires_grad_(True)
+    ref = F._attn_reference(qr, kvr[:, :h], kvr[:, h:], B, NH, SQ, SK, HD, scale, False, lens)
+    ref.backward(do.float())
+    assert rel(o, ref) < 8e-3 and rel(q.grad, qr.grad) < 1.5e-2 and rel(kv.grad, kvr.grad) < 1.5e-2
+
+
+def test_flash_attention_dropout_consistency():
+    """With dropout the three kernels must regenerate one mask: check dV = P_drop^T dO through linearity in V."""
+    torch.manual_seed(12)
+    B, NH, S, HD = 1, 2, 256, 128
+    h = NH * HD
+    qkv = (torch.randn(B * S, 3 * h, device=DEV) * 0.5).bfloat16()
+    x = qkv.clone().requires_grad_(True)
+    o = F.fused_qkv_attention(x, B, NH, S, HD, causal=True, dropout_p=0.2, seed=99)
+    o2 = F.fused_qkv_attention(qkv, B, NH, S, HD, causal=True, dropout_p=0.2, seed=99)
+    assert torch.equal(o, o2)
+    do = torch.randn_like(o)
+    o.backward(do)
+    # O is linear in V for a fixed mask: <dO, O(V)> = <dV, V>
+    lhs = (do.float() * o.float()).sum()
+    rhs = (x.grad[:, 2 * h:].float() * qkv[:, 2 * h:].float()).sum()
+    assert abs(lhs - rhs) / (abs(lhs) + 1e-6) < 2e-2
+    o_nodrop = F.fused_qkv_attention(qkv, B, NH, S, HD, causal=True)
+    assert rel(o, o_nodrop) > 0.05  # dropout really changes the output
+
+
+def test_lm_head_cross_entropy_autograd():
+    torch.manual_seed(13)
+    T, H, V = 256, 256, 1024
+    x = torch.randn(T, H, device=DEV).bfloat16().requires_grad_(True)
+    W = (torch.randn(V, H, device=DEV) * 0.05).bfloat16().requires_grad_(True)
+    tg = torch.randint(0, V, (T,), device=DEV)
+    loss = F.lm_head_cross_entropy(x, W, tg, None, 0, 1.0 / T)
+    loss.backward()
+    xr, wr = x.detach().float().requires_grad_(True), W.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(xr @ wr.t(), tg)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 2e-2
+    assert rel(x.grad, xr.grad) < 3e-2 and rel(W.grad, wr.grad) < 3e-2

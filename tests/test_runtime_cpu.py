@@ -1,0 +1,57 @@
+"""Single-process runtime tests on CPU (plain PyTorch restatements of the kernels)."""
+import pytest
+import torch
+
+from superscaler_b200.data.synthetic import gpt_batch
+from superscaler_b200.runtime.lr import LRSchedule
+from superscaler_b200.runtime.trainer import Trainer
+
+from helpers import tiny_gpt_plan
+
+NODROP = dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=1)
+
+
+def _run(plan, steps=3, **kw):
+    t = Trainer(plan, model_overrides=NODROP, lr_warmup_steps=0, device="cpu", **kw)
+    out = []
+    for _ in range(steps):
+        out.append(t.loss_value(t.train_step(gpt_batch(plan["global_batch_size"], plan["seq_length"], 512, seed=1))))
+    return out, t
+
+
+def test_tiny_gpt_trains_and_variants_agree():
+    base, t = _run(tiny_gpt_plan())
+    assert base[-1] < base[0] and abs(base[0] - 6.24) < 0.1
+    unfused, _ = _run(tiny_gpt_plan(), fuse=False)
+    recomp, _ = _run(tiny_gpt_plan(recompute=1))
+    recomp_unfused, _ = _run(tiny_gpt_plan(recompute=1), fuse=False)
+    for other in (unfused, recomp, recomp_unfused):
+        assert max(abs(a - b) for a, b in zip(base, other)) < 2e-3
+    names = [type(o).__name__ for o in t.stage.ops]
+    assert "FusedAttention" in names and "FusedMLP" in names and "FusedDenseDropAdd" in names
+
+
+def test_microbatching_is_equivalent():
+    a, _ = _run(tiny_gpt_plan(global_bs=4, micro_bs=4))
+    b, _ = _run(tiny_gpt_plan(global_bs=4, micro_bs=1))
+    assert max(abs(x - y) for x, y in zip(a, b)) < 2e-3
+
+
+def test_recompute_segments_break_at_layers():
+    _, t = _run(tiny_gpt_plan(recompute=1), steps=1)
+    segs = t.stage.segments
+    assert [s.recompute for s in segs] == [False, True, True, False]
+    assert segs[1].ops[0].info.name == "enc-1st-layernorm" and segs[2].ops[0].info.name == "enc-1st-layernorm"
+
+
+def test_lr_schedule():
+    s = LRSchedule(1.0, 0.1, warmup_steps=10, decay_steps=110, style="cosine")
+    lrs = [s.step() for _ in range(120)]
+    assert abs(lrs[4] - 0.5) < 1e-9 and abs(lrs[9] - 1.0) < 1e-9
+    assert abs(lrs[59] - 0.55) < 1e-6 and lrs[-1] == 0.1
+    sd = s.state_dict()
+    s2 = LRSchedule(2.0, 0.0, 1, 2)
+    s2.load_state_dict(sd)
+    assert s2.get_lr() == s.get_lr()
+    lin = LRSchedule(1.0, 0.0, warmup_steps=0, decay_steps=100, style="linear")
+    assert abs(lin.step(50) - 0.5) < 1e-9
