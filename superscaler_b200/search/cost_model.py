@@ -1,0 +1,419 @@
+"""Cost model: predicts per-stage time and memory of a plan from the profiled database.
+
+Reproduces the reference model term by term (search/aceso_cost_model.py) -- the arithmetic order is kept
+so that predictions on the reference's committed databases are bit-identical -- and extends it with one
+term: when the database carries the overlap columns written by this framework's profiler, the part of
+an op's own collective that the fused compute+collective kernels hide is subtracted (priced as
+max(compute, comm) instead of compute + comm).  Databases without those columns predict as before.
+
+  stage time      = (sum fwd + sum bwd + boundary-in comm + boundary-out comm + recompute fwd) / 1000  [ms]
+  pipeline time_i = stage_time_i * (num_microbatches - 1) + sum_j stage_time_j
+  stage memory    = weights * (1 + main params) + grads + optimizer
+                    + (inputs + activations - saved by recompute) * stages_behind + peak + reserved
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+from .config import Plan, StagePlan
+from .database import ProfileDB
+from .opinfo import op_spec, reshard_primitives
+
+
+@dataclass
+class CostOptions:
+    memory_limit: float = 28000
+    num_gpus_per_node: int = 8
+    main_params_factor: float = 2       # fp32 master copy, in units of the weight bytes
+    optimizer_factor: float = 4
+    resharding: bool = True
+    consider_shared_space: bool = True
+    consider_reserved_space: bool = True
+    consider_collective_memory: bool = False
+    support_comm_predict: bool = False
+    memory_pred_type: str = "MAX"
+    flex_recompute: bool = True
+    peak_mem_in_backward: float = 0
+    price_overlap: bool = True
+    never_recompute: Sequence[str] = ()
+
+
+_SHARED_ZERO = ("enc-attention-softmax", "bn1")
+
+
+def _shares_buffer(op: str) -> bool:
+    """Ops whose saved activation aliases a neighbour's (softmax / in-place BN / downsample add)."""
+    return op in _SHARED_ZERO or "-bn3" in op or ("-downsample" in op and "0-0" not in op)
+
+
+class CostModel:
+    def __init__(self, db: ProfileDB, opt: CostOptions):
+        self.db, self.opt = db, opt
+        self._mem_cache: Dict[tuple, float] = {}
+        self._time_cache: Dict[tuple, float] = {}
+        t = db.table
+        self._fwd, self._bwd, self._in, self._out = t["fwd"], t["bwd"], t["in_mb"], t["out_mb"]
+        self._w, self._a, self._rf, self._rb = t["weights"], t["acts"], t["res_fwd"], t["res_bwd"]
+        self._fo, self._bo = t["fwd_ovl"], t["bwd_ovl"]
+        self._mi = db.mbs_index
+        self._overlap = opt.price_overlap and db.has_overlap_columns
+
+    # ---- time -------------------------------------------------------------------------------
+    def stage_time_terms(self, ops, mbs, tp, algo, dp, in_cross_node, out_cross_node):
+        """(fwd us, bwd us, boundary-in us, boundary-out us, tp/reshard comm us)."""
+        if len(ops) == 0:
+            return 0, 0, 0, 0, 0
+        mi, db = self._mi, self.db
+        fwd = bwd = 0
+        tp_comm = 0
+        log2 = math.log
+        for i in range(len(ops)):
+            op = ops[i]
+            a, b, c = mi[mbs[i]], int(log2(tp[i], 2)), algo[i]
+            fwd += self._fwd[op][a][b][c]
+            bwd += self._bwd[op][a][b][c]
+            if self._overlap:
+                fwd -= self._fo[op][a][b][c]
+                bwd -= self._bo[op][a][b][c]
+            if self.opt.support_comm_predict:
+                for suffix in ("qkv", "dense", "GEMM", "conv", "downsample"):
+                    if suffix in op:
+                        tp_comm += db.collective_time("all_reduce", tp[i], self._out[op][a][b][c]) * 1000
+        in_size = self._in[ops[0]][mi[mbs[0]]][int(log2(tp[0], 2))][algo[0]]
+        out_size = self._out[ops[-1]][mi[mbs[-1]]][int(log2(tp[0], 2))][algo[-1]]
+        in_comm = in_size / (db.inter_bandwidth(in_size) if in_cross_node else db.intra_bandwidth(in_size))
+        out_comm = out_size / (db.inter_bandwidth(out_size) if out_cross_node else db.intra_bandwidth(out_size))
+        fwd_rs = bwd_rs = 0
+        if self.opt.resharding:
+            for i in range(1, len(ops)):
+                if tp[i] == tp[i - 1] and dp[i] == dp[i - 1] and algo[i] == algo[i - 1] and tp[i] == 1:
+                    continue  # single-device layouts are always identical
+                src = op_spec(ops[i - 1], tp[i - 1], dp[i - 1], algo[i - 1], as_input=False)
+                dst = op_spec(ops[i], tp[i], dp[i], algo[i], as_input=True)
+                f, b, n = reshard_primitives(src, dst)
+                if f is None and b is None:
+                    continue
+                size = self._in[ops[i]][mi[mbs[i]]][int(log2(tp[i], 2))][algo[i]]
+                if f is not None:
+                    fwd_rs += db.collective_time(f, n, size)
+                if b is not None:
+                    bwd_rs += db.collective_time(b, n, size)
+        in_comm += fwd_rs * 1000
+        out_comm += bwd_rs * 1000
+        tp_comm += fwd_rs * 1000 + bwd_rs * 1000
+        return fwd, bwd, in_comm, out_comm, tp_comm
+
+    def recompute_time(self, ops, recompute, mbs, tp, algo):
+        if len(ops) == 0 or sum(recompute) == 0:
+            return 0
+        total = 0
+        for i in range(len(ops)):
+            if recompute[i] == 1:
+                total += self._fwd[ops[i]][self._mi[mbs[i]]][int(math.log(tp[i], 2))][algo[i]]
+        return total
+
+    def stage_time(self, ops, recompute, tp, dp, micro_bs, algo) -> float:
+        mbs = [micro_bs // dp[j] for j in range(len(ops))]
+        fwd, bwd, cin, cout, _ = self.stage_time_terms(ops, mbs, tp, algo, dp, False, False)
+        rc = self.recompute_time(ops, recompute, mbs, tp, algo)
+        return (fwd + bwd + cin + cout + rc) / 1000
+
+    def stage_time_cached(self, plan: Plan, s: int) -> float:
+        st = plan.stages[s]
+        key = (st.ops[0], len(st.ops), tuple(st.tp_size), tuple(st.dp_size), tuple(st.recompute_ops),
+               tuple(st.algo), plan.micro_bs)
+        v = self._time_cache.get(key)
+        if v is None:
+            v = self.stage_time(st.ops, st.recompute_ops, st.tp_size, st.dp_size, plan.micro_bs, st.algo)
+            self._time_cache[key] = v
+        return v
+
+    # ---- memory -----------------------------------------------------------------------------
+    def _act(self, op, mbs, tp, algo):
+        return self._a[op][self._mi[mbs]][int(math.log(tp, 2))][algo]
+
+    def activation_size(self, op, mbs, tp, algo=0):
+        return self._act(op, mbs, tp, algo)
+
+    def _memory_terms(self, ops, mbs, tp, algo):
+        inputs = self._in[ops[0]][self._mi[mbs[0]]][int(math.log(tp[0], 2))][algo[0]]
+        acts = 0
+        weights = 0
+        shared = self.opt.consider_shared_space
+        for i in range(len(ops)):
+            op = ops[i]
+            if shared and op == "enc-attention-dropout":
+                acts += self._act(op, mbs[i], tp[i], algo[i]) * 1.5
+            elif shared and _shares_buffer(op):
+                acts += 0
+            else:
+                acts += self._act(op, mbs[i], tp[i], algo[i])
+            weights += self._w[op][self._mi[mbs[i]]][int(math.log(tp[i], 2))][algo[i]]
+        return weights, inputs, acts
+
+    def _saved_by_recompute(self, ops, recompute, mbs, tp, algo):
+        if len(ops) <= 1 or sum(recompute) == 0:
+            return 0
+        saved = 0
+        shared = self.opt.consider_shared_space
+        for i in range(len(ops) - 1):
+            if recompute[i] == 1 and recompute[i + 1] == 1:
+                op = ops[i]
+                if shared and op == "enc-attention-dropout":
+                    saved += self._act(op, mbs[i], tp[i], algo[i]) * 1.5
+                elif shared and _shares_buffer(op):
+                    saved += 0
+                elif ops[i + 1] in ("enc-1st-layernorm",) or "-conv1" in ops[i + 1]:
+                    saved += 0
+                else:
+                    saved += self._act(op, mbs[i], tp[i], algo[i])
+        return saved
+
+    def _peak_recompute(self, ops, recompute, mbs, tp, algo):
+        """Largest activation footprint of any single recomputed segment while it is being replayed."""
+        if len(ops) <= 1 or sum(recompute) == 0:
+            return 0
+        run = 0
+        peaks = [0]
+        shared = self.opt.consider_shared_space
+        last = len(ops) - 1
+        for i in range(last):
+            if recompute[i] == 1 and recompute[i + 1] == 1:
+                op = ops[i]
+                if shared and _shares_buffer(op):
+                    run += 0
+                elif shared and op == "enc-attention-dropout":
+                    run += self._act(op, mbs[i], tp[i], algo[i]) * 1.5
+                else:
+                    run += self._act(op, mbs[i], tp[i], algo[i])
+                    if ops[i + 1] in ("enc-1st-layernorm",) or "-conv1" in ops[i + 1] or i + 1 == last:
+                        peaks.append(run)
+                        run = 0
+            else:
+                if run > 0:
+                    peaks.append(run)
+                    run = 0
+        return max(peaks)
+
+    def _reserved(self, ops, mbs, tp, dp, algo, weight_mb):
+        rf = rb = 0
+        for i in range(len(ops) - 1):
+            a, b, c = self._mi[mbs[i]], int(math.log(tp[i], 2)), algo[i]
+            v = self._rf[ops[i]][a][b][c]
+            if v > rf:
+                rf = v
+            v = self._rb[ops[i]][a][b][c]
+            if v > rb:
+                rb = v
+        coll = 0
+        if self.opt.consider_collective_memory and self.opt.resharding:
+            for i in range(1, len(ops)):
+                src = op_spec(ops[i - 1], tp[i - 1], dp[i - 1], algo[i - 1], as_input=False)
+                dst = op_spec(ops[i], tp[i], dp[i], algo[i], as_input=True)
+                f, b, n = reshard_primitives(src, dst)
+                size = self._in[ops[i]][self._mi[mbs[i]]][int(math.log(tp[i], 2))][algo[i]]
+                for prim in (f, b):
+                    if prim is not None:
+                        m = size * n if prim in ("all_gather", "all_to_all") else size
+                        if m > coll:
+                            coll = m
+        if self.opt.memory_pred_type == "MAX":
+            return max(rf + rb, weight_mb) + coll
+        if self.opt.memory_pred_type == "MIN":
+            return max(rf, rb, weight_mb, coll)
+        raise RuntimeError(f"unknown memory_pred_type {self.opt.memory_pred_type}")
+
+    def stage_memory(self, ops, recompute, tp, dp, micro_bs, stages_behind, algo, breakdown=False):
+        mbs = [micro_bs // dp[j] for j in range(len(ops))]
+        w, inputs, acts = self._memory_terms(ops, mbs, tp, algo)
+        grads = w
+        main = w * self.opt.main_params_factor
+        optim = w * self.opt.optimizer_factor
+        saved = self._saved_by_recompute(ops, recompute, mbs, tp, algo)
+        peak_rc = self._peak_recompute(ops, recompute, mbs, tp, algo)
+        reserved = self._reserved(ops, mbs, tp, dp, algo, w) if self.opt.consider_reserved_space else 0
+        in_flight = (inputs + acts - saved) * stages_behind
+        peak = inputs + acts - saved + peak_rc
+        w += main
+        if breakdown:
+            return w, grads, optim, in_flight, peak, reserved
+        return w + grads + optim + in_flight + peak + reserved
+
+    def stage_memory_cached(self, ops, recompute, tp, dp, micro_bs, stages_behind, algo) -> float:
+        key = (ops[0], len(ops), tuple(tp), tuple(dp), tuple(recompute), tuple(algo), micro_bs, stages_behind)
+        v = self._mem_cache.get(key)
+        if v is None:
+            v = self.stage_memory(ops, recompute, tp, dp, micro_bs, stages_behind, algo)
+            self._mem_cache[key] = v
+        return v
+
+    def reserved_list(self, plan: Optional[Plan]) -> List[float]:
+        if plan is None:
+            return []
+        return [self.stage_memory(s.ops, s.recompute_ops, s.tp_size, s.dp_size, plan.micro_bs, s.num_stages_behind,
+                                  s.algo, breakdown=True)[5] for s in plan.stages]
+
+    # ---- recompute selection ----------------------------------------------------------------
+    def choose_recompute(self, ops, micro_bs, tp, dp, stages_behind, algo) -> List[int]:
+        """Greedy: while the stage exceeds the memory limit, recompute the op kind that frees the most
+        activation memory (together with the op that follows it)."""
+        n = len(ops)
+        if not self.opt.flex_recompute:
+            return [1] * n
+        rc = [0] * n
+        mem = self.stage_memory_cached(ops, rc, tp, dp, micro_bs, stages_behind, algo) + self.opt.peak_mem_in_backward
+        limit = self.opt.memory_limit
+        if mem - limit <= 0:
+            return rc
+        groups: Dict[str, dict] = {}
+        for i in range(n):
+            g = groups.setdefault(ops[i], {"index": [], "size": [], "done": False, "sum": 0})
+            sz = self._act(ops[i], micro_bs // dp[i], tp[i], algo[i]) * (stages_behind + 1)
+            g["index"].append(i)
+            g["size"].append(sz)
+            g["sum"] += sz
+        mbs = [micro_bs // dp[i] for i in range(len(dp))]
+        saved0 = 0
+        peak0 = self._peak_recompute(ops, rc, mbs, tp, algo)
+        never = self.opt.never_recompute
+        while mem - limit > 0:
+            # pick the not-yet-recomputed op kind with the largest total activation
+            best, best_sz = None, 0
+            for name, g in groups.items():
+                if not g["done"] and g["sum"] > best_sz and name not in ("enc-1st-layernorm",) \
+                        and "-conv1" not in name and "-relu" not in name and name not in never:
+                    best, best_sz = name, g["sum"]
+            if best_sz == 0:
+                break
+            g = groups[best]
+            g["done"] = True
+            nxt = g["index"][0] + 1
+            if nxt >= n:
+                break
+            groups[ops[nxt]]["done"] = True
+            exceed = mem - limit
+            if best_sz < exceed:
+                idxs = g["index"]
+            else:
+                acc, k = 0, 0
+                while acc <= exceed and k < len(g["size"]):
+                    acc += g["size"][k]
+                    k += 1
+                idxs = list(g["index"][:k])
+            for i in idxs:
+                if i >= 0:
+                    rc[i] = 1
+                    if i < n - 1:
+                        rc[i + 1] = 1
+                else:
+                    break
+            saved1 = self._saved_by_recompute(ops, rc, mbs, tp, algo)
+            mem -= (saved1 - saved0) * (stages_behind + 1)
+            saved0 = saved1
+            peak1 = self._peak_recompute(ops, rc, mbs, tp, algo)
+            mem += peak1 - peak0
+            peak0 = peak1
+        return rc
+
+    def refresh_recompute(self, plan: Plan, stage: Optional[int] = None) -> None:
+        for i in ([stage] if stage is not None else range(plan.num_stages)):
+            s = plan.stages[i]
+            s.recompute_ops = self.choose_recompute(s.ops, plan.micro_bs, s.tp_size, s.dp_size, s.num_stages_behind,
+                                                    s.algo)
+
+    # ---- whole-plan evaluation --------------------------------------------------------------
+    def evaluate(self, plan: Plan, report: Optional[list] = None) -> None:
+        """Fills the plan's time / memory lists and the per-GPU breakdown the policy reads."""
+        micro_bs = plan.micro_bs
+        nb = plan.global_bs // micro_bs
+        per_node = self.opt.num_gpus_per_node
+        raw, mem, comp, eff, gpu_t, ideal_l, loss_l, rc_l = [], [], [], [], [], [], [], []
+        seen = 0
+        for i, s in enumerate(plan.stages):
+            ops, g = s.ops, s.num_gpus
+            mbs = [micro_bs // s.dp_size[j] for j in range(len(ops))]
+            in_x = (seen % per_node) == 0 and seen > 0
+            seen += g
+            out_x = (seen % per_node) == 0
+            fwd, bwd, cin, cout, tpc = self.stage_time_terms(ops, mbs, s.tp_size, s.algo, s.dp_size, in_x, out_x)
+            rc = self.recompute_time(ops, s.recompute_ops, mbs, s.tp_size, s.algo)
+            t = (fwd + bwd + cin + cout + rc) / 1000
+            raw.append(t)
+            comp.append((fwd + bwd + rc) / 1000)
+            gpu_t.append(t * g)
+            one = [1] * len(ops)
+            f1, b1, ci1, co1, _ = self.stage_time_terms(ops, [micro_bs] * len(ops), one, s.algo, one, in_x, out_x)
+            ideal = (f1 + b1 + ci1 + co1) / 1000
+            loss = (fwd + bwd) - (f1 + b1) / g
+            ideal_l.append(((f1 + b1) / g) / 1000)
+            loss_l.append(loss / 1000)
+            rc_l.append(rc / 1000)
+            parts = self.stage_memory(ops, s.recompute_ops, s.tp_size, s.dp_size, micro_bs, s.num_stages_behind,
+                                      s.algo, breakdown=True)
+            w, gr, op_, infl, peak, res = parts
+            mem.append(w + gr + op_ + infl + peak + res)
+            eff.append(ideal / (t * g))
+            if report is not None:
+                report.append({"stage": i, "fwd_ms": fwd / 1000 * nb, "bwd_ms": (bwd + rc) / 1000 * nb,
+                               "recompute_ms": rc / 1000 * nb, "in_comm_ms": cin / 1000 * nb,
+                               "out_comm_ms": cout / 1000 * nb, "reshard_ms": tpc / 1000 * nb, "weights_mb": w,
+                               "grads_mb": gr, "optimizer_mb": op_, "activations_mb": infl, "peak_mb": peak,
+                               "reserved_mb": res})
+        total = sum(raw)
+        times = [raw[i] * (nb - 1) + total for i in range(plan.num_stages)]
+        plan.time_list = times
+        plan.memory_list = mem
+        plan.compute_time_list = comp
+        plan.total_gpu_time = sum(gpu_t) * (nb - 1)
+        plan.ideal_time_per_gpu = ideal_l
+        plan.eff_loss_time_per_gpu = loss_l
+        plan.recomp_time_per_gpu = rc_l
+        tmax = max(times)
+        limit = self.opt.memory_limit
+        idle_eff = []
+        for i, s in enumerate(plan.stages):
+            used_t, used_m = times[i], mem[i]
+            if sum(s.recompute_ops) > 0:
+                idle = (tmax - used_t) / 2
+            else:
+                by_time = tmax - used_t
+                by_mem = ((limit - used_m) / used_m) * used_t
+                idle = by_time if by_mem > by_time else by_mem + (by_time - by_mem) / 2
+            idle_eff.append(idle * s.num_gpus * eff[i])
+        plan.efficient_time_list = idle_eff
+        if report is not None:
+            for i, r in enumerate(report):
+                r["pipeline_time_ms"] = times[i]
+                r["memory_mb"] = mem[i]
+
+    # ---- what-if for op migration -----------------------------------------------------------
+    def value_after_move(self, plan: Plan, stage: int, partner, n_moved: int, metric: str, inc_gpus=False,
+                         dec_gpus=False, dim=None):
+        """Predicted time (ms) or memory (MB) of `stage` after moving `n_moved` ops towards `partner` and/or
+        doubling / halving its tp or dp; also returns the recompute flags that go with it."""
+        s = plan.stages[stage]
+        ops, tp, dp, algo, rc = list(s.ops), list(s.tp_size), list(s.dp_size), list(s.algo), list(s.recompute_ops)
+        if n_moved > 0:
+            if stage < partner:
+                ops, tp, dp, algo = ops[:-n_moved], tp[:-n_moved], dp[:-n_moved], algo[:-n_moved]
+            else:
+                ops, tp, dp, algo = ops[n_moved:], tp[n_moved:], dp[n_moved:], algo[n_moved:]
+        if inc_gpus:
+            if dim == "tp":
+                tp = [x * 2 for x in tp]
+            elif dim == "dp":
+                dp = [x * 2 for x in dp]
+        if dec_gpus:
+            if dim == "tp":
+                tp = [x // 2 for x in tp]
+            elif dim == "dp":
+                dp = [x // 2 for x in dp]
+        if n_moved > 0 or inc_gpus or dec_gpus:
+            rc = self.choose_recompute(ops, plan.micro_bs, tp, dp, s.num_stages_behind, algo)
+        if metric in ("time", "time_with_efficiency"):
+            return self.stage_time(ops, rc, tp, dp, plan.micro_bs, algo), rc
+        if metric == "memory":
+            return self.stage_memory(ops, rc, tp, dp, plan.micro_bs, s.num_stages_behind, algo), rc
+        raise RuntimeError(f"metric {metric} not implemented.")
