@@ -1,0 +1,69 @@
+"""The plan search must take the same decisions as the reference on the reference's committed database.
+
+Golden plans and per-stage predictions come from running the reference search
+(`aceso_search.py`, flags of scripts/aceso_{gpt,resnet}_search.sh small) on profiled-time-miniset.
+The database itself is read from the reference tree when it is mounted, else the test is skipped.
+"""
+import csv
+import json
+import os
+
+import pytest
+
+from superscaler_b200.search.context import SearchArgs, SearchContext
+from superscaler_b200.search.search import Searcher
+
+DB = "/root/reference/profiler/profiled-time-miniset/"
+GOLD = os.path.join(os.path.dirname(__file__), "golden", "reference_search")
+pytestmark = pytest.mark.skipif(not os.path.isdir(DB), reason="reference database not mounted")
+
+
+def _search(tmp_path, model, size, gbs, mbs, stages, **kw):
+    out = str(tmp_path) + "/"
+    for sub in ("csv", "top_configs", "trends"):
+        os.makedirs(out + sub, exist_ok=True)
+    args = SearchArgs(model_name=model, model_size=size, global_batch_size=gbs, micro_batch_size=mbs, num_nodes=1,
+                      num_gpus_per_node=4, memory_limit=12000, profiled_time_path=DB, config_save_path=out,
+                      log_path=out, config_suffix="t", max_num_hops=7, time_budget_total=200, multi_process=False,
+                      **kw).finalize()
+    res = Searcher(SearchContext(args, verbose=False)).run(stages)
+    with open(f"{out}{model}_{size}_{stages}stages_t.json") as f:
+        plan = json.load(f)
+    with open(f"{out}csv/info_{model}_{size}_{stages}stages_t.csv") as f:
+        info = list(csv.reader(f))
+    return res, plan, info
+
+
+def _golden(model, size, stages):
+    with open(f"{GOLD}/{model}_{size}_{stages}stages.json") as f:
+        plan = json.load(f)
+    with open(f"{GOLD}/info_{model}_{size}_{stages}stages.csv") as f:
+        info = list(csv.reader(f))
+    return plan, info
+
+
+@pytest.mark.parametrize("stages", [1, 2, 4])
+def test_gpt_1_3b_matches_reference(tmp_path, stages):
+    res, plan, info = _search(tmp_path, "gpt", "1_3B", 512, [1, 2, 4, 8], stages)
+    gplan, ginfo = _golden("gpt", "1_3B", stages)
+    assert plan == gplan
+    assert info == ginfo
+    if stages == 4:
+        assert abs(res[0] - 58760.92) < 0.01 and res[2] == 975  # README "Predict" column, explored plans
+
+
+@pytest.mark.parametrize("stages", [2, 4])
+def test_wide_resnet_1b_matches_reference(tmp_path, stages):
+    res, plan, info = _search(tmp_path, "resnet", "1B", 768, [16, 32, 48, 64], stages, finetune_after_trial=1)
+    gplan, ginfo = _golden("resnet", "1B", stages)
+    assert plan == gplan
+    assert info == ginfo
+    if stages == 2:
+        assert abs(res[0] - 17672.05) < 0.01
+        assert any(plan["resharding_stages"])  # the winner switches dp2 -> tp2 inside stage 1
+
+
+def test_explored_budget_is_deterministic(tmp_path):
+    a = _search(tmp_path / "a", "gpt", "1_3B", 512, [1, 2, 4, 8], 3, explored_budget=300)
+    b = _search(tmp_path / "b", "gpt", "1_3B", 512, [1, 2, 4, 8], 3, explored_budget=300)
+    assert a[1] == b[1] and a[0][0] == b[0][0]
