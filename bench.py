@@ -158,9 +158,15 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    verbose = os.environ.get("SSB_BENCH_VERBOSE") == "1" and rank == 0
+
     def timed(step_fn, n_warm, n_steps):
         for i in range(n_warm):
+            t_w = time.perf_counter()
             step_fn(i)
+            if verbose:
+                torch.cuda.synchronize()
+                print(f"[bench] warm-up step {i}: {time.perf_counter() - t_w:.2f} s", file=sys.stderr, flush=True)
         barrier()
         sampler = ClockSampler(local)
         sampler.start()
