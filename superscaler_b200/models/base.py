@@ -77,6 +77,15 @@ class Op:
     def p(self, key: str) -> torch.nn.Parameter:
         return self.env.store[self._names[key]]
 
+    # -- layouts (see models/static_info.py) ---------------------------------------------------
+    def required(self) -> Dict[str, Any]:
+        from .static_info import required_layouts
+        return required_layouts(self.info.name, self.info.algo)
+
+    def produced(self) -> Dict[str, Any]:
+        from .static_info import produced_layouts
+        return produced_layouts(self.info.name, self.info.algo)
+
     # -- execution ----------------------------------------------------------------------------
     def forward(self, st: Dict[str, torch.Tensor]) -> None:
         raise NotImplementedError

@@ -45,6 +45,22 @@ class FusedGroup(Op):
     def declare(self):
         pass  # members declare their own parameters
 
+    def required(self):
+        out, produced = {}, set()
+        for m in self.members:
+            req = m.required()
+            for k in m.reads:
+                if k not in produced and k not in out and k in req:
+                    out[k] = req[k]
+            produced.update(m.writes)
+        return out
+
+    def produced(self):
+        out = {}
+        for m in self.members:
+            out.update(m.produced())
+        return out
+
 
 class FusedAttention(FusedGroup):
     def __init__(self, members):

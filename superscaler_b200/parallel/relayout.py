@@ -108,8 +108,8 @@ def plan_transfer(src: Side, src_lay: Layout, dst: Side, dst_lay: Layout, gshape
                   sum_row_replicas: bool = False) -> List[Message]:
     """Messages that give every rank of `dst` its region under `dst_lay` from the owners under `src_lay`.
 
-    sum_row_replicas (gradient direction only): when the rows are replicated, the requester adds the
-    contributions of ALL data-parallel ranks of `src`, each scaled by 1 / src.dp."""
+    sum_row_replicas marks the gradient direction: row-replicated tensors add the contributions of ALL
+    data-parallel ranks of `src`, each scaled by 1 / src.dp; row-split tensors are scaled by dst.dp / src.dp."""
     rows = gshape[0]
     cols = gshape[1] if len(gshape) > 1 else 1
     groups = src_lay.groups
@@ -126,7 +126,10 @@ def plan_transfer(src: Side, src_lay: Layout, dst: Side, dst_lay: Layout, gshape
                 per = rows // src.dp
                 row_src = [(k, max(r0, k * per), min(r1, (k + 1) * per)) for k in range(src.dp)
                            if max(r0, k * per) < min(r1, (k + 1) * per)]
-                scale = 1.0
+                # Every rank differentiates the MEAN loss of its own rows.  Where the data-parallel degree
+                # changes, the gradient is rescaled so that the usual 1/dp averaging of the parameter
+                # gradients on the receiving side still yields the gradient of the global mean.
+                scale = (dst.dp / src.dp) if sum_row_replicas else 1.0
             elif sum_row_replicas:
                 row_src = [(k, r0, r1) for k in range(src.dp)]
                 scale = 1.0 / src.dp
@@ -229,7 +232,9 @@ class Transfer:
         self.accumulate = sum_row_replicas and src_lay.row == "rep" and src.dp > 1
         self.is_receiver = dst.contains(my_rank)
 
-    def post(self, t: Optional[torch.Tensor]):
+    def prepare(self, t: Optional[torch.Tensor]):
+        """Returns (P2POps of this rank, assemble()).  The caller batches the ops of several transfers into one
+        group call, waits for the requests and then calls assemble()."""
         ops, recv_bufs, local = [], [], []
         for m in self.sends:
             buf = _pack(t, self.src, self.src_lay, self.rank, m, self.gshape)
@@ -243,11 +248,8 @@ class Transfer:
             buf = torch.empty(_msg_numel(m, self.gshape), dtype=self.dtype, device=self.device)
             recv_bufs.append((m, buf))
             ops.append(dist.P2POp(dist.irecv, buf, m.src))
-        reqs = dist.batch_isend_irecv(ops) if ops else []
 
-        def finish() -> Optional[torch.Tensor]:
-            for r in reqs:
-                r.wait()
+        def assemble() -> Optional[torch.Tensor]:
             if not self.is_receiver:
                 return None
             shape = local_shape(self.dst, self.dst_lay, self.gshape)
@@ -255,6 +257,17 @@ class Transfer:
             for m, buf in local + recv_bufs:
                 _unpack(buf, out, self.dst, self.dst_lay, self.rank, m, self.gshape, self.accumulate)
             return out
+
+        return ops, assemble
+
+    def post(self, t: Optional[torch.Tensor]):
+        ops, assemble = self.prepare(t)
+        reqs = dist.batch_isend_irecv(ops) if ops else []
+
+        def finish() -> Optional[torch.Tensor]:
+            for r in reqs:
+                r.wait()
+            return assemble()
 
         return finish
 

@@ -34,7 +34,7 @@ def _merge(ranges: List[Tuple[int, int]]) -> List[Tuple[int, int]]:
 
 class StageOptimizer:
     def __init__(self, store: ParamStore, pstate, *, lr=1.5e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
-                 clip_grad=1.0, kind="adam", momentum=0.9):
+                 clip_grad=1.0, kind="adam", momentum=0.9, norm_exclude=()):
         self.store, self.pstate = store, pstate
         self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
         self.clip_grad, self.kind, self.momentum = clip_grad, kind, momentum
@@ -46,6 +46,8 @@ class StageOptimizer:
         # ranges grouped by the number of copies of the parameter in the job
         groups: Dict[int, List[Tuple[int, int]]] = {}
         for s in store.specs:
+            if s.name in norm_exclude:
+                continue  # a non-root copy of a tied weight: its (identical) gradient is counted at the root
             off, n = store.offsets[s.name]
             replicated_over_tp = s.tp > 1 and s.shard_dim is None
             copies = s.dp * (s.tp if replicated_over_tp else 1)

@@ -1,0 +1,271 @@
+"""Pipeline execution: non-interleaved 1F1B over stages with different GPU counts.
+
+Schedule (same as the reference's forward_backward_pipelining_without_interleaving,
+runtime/megatron/schedules.py:533-646): stage s of P runs min(P - s - 1, M) warm-up forwards, then
+alternates one forward and one backward, then drains the remaining backwards.  Send and receive of one
+step are issued as ONE batched group call per stage so neighbouring stages never wait on each other's
+sends.
+
+Stage-to-stage exchange (reference: _communicate_flexpipe, runtime/megatron/p2p_communication.py:203-337):
+the tensors that are live across the boundary (found by the liveness pass over the op list) travel
+through the relayout engine, which re-chunks each of them from the producer's (tp, dp) to the consumer's.
+Shapes are exchanged once, on the first micro-batch.  There is no host synchronisation besides waiting
+for the requests of the current step (the reference also calls torch.cuda.synchronize(),
+p2p_communication.py:317-318).
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..models.static_info import live_keys_before, op_io, produced_layouts
+from ..parallel.relayout import Layout, Side, Transfer, global_shape, local_shape
+
+_DTYPES = [torch.bfloat16, torch.float32, torch.int64, torch.float16, torch.uint8, torch.int32]
+_META_WORDS = 12  # per key: ndim, dtype, row, col, groups, requires_grad, then up to 6 dims
+
+
+class Boundary:
+    """One side's view of the boundary between stage `up` (producer) and stage `up + 1` (consumer)."""
+
+    def __init__(self, trainer, up: int):
+        ps, plan = trainer.pstate, trainer.plan
+        self.trainer, self.rank = trainer, ps.rank
+        lo_next = trainer.stage_bounds[up + 1][0]
+        self.keys = live_keys_before(trainer.op_names, lo_next)
+        tp_a = plan["model_parallel_size_of_each_op"][up][-1]
+        dp_a = plan["data_parallel_size_of_each_op"][up][-1]
+        tp_b = plan["model_parallel_size_of_each_op"][up + 1][0]
+        dp_b = plan["data_parallel_size_of_each_op"][up + 1][0]
+        self.src = Side(ps.stage_start[up], tp_a, dp_a)
+        self.dst = Side(ps.stage_start[up + 1], tp_b, dp_b)
+        self.i_am_src = ps.stage == up
+        self.meta: Optional[Dict[str, tuple]] = None   # key -> (gshape, dtype, Layout, needs_grad, one_d)
+        self.device = trainer.device
+
+    # ---- one-time shape handshake ---------------------------------------------------------------
+    def _encode(self, st: Dict[str, Any], sides: Dict[str, tuple]) -> torch.Tensor:
+        words = torch.zeros(len(self.keys) * _META_WORDS, dtype=torch.int64)
+        for i, k in enumerate(self.keys):
+            t = st[k]
+            side, lay = sides[k]
+            one_d = t.dim() == 1
+            shape = global_shape(side, lay, (1,) + tuple(t.shape) if one_d else tuple(t.shape))
+            base = i * _META_WORDS
+            words[base + 0] = len(shape) | (64 if one_d else 0)
+            words[base + 1] = _DTYPES.index(t.dtype)
+            words[base + 2] = 1 if lay.row == "split" else 0
+            words[base + 3] = 1 if lay.col == "split" else 0
+            words[base + 4] = lay.groups
+            words[base + 5] = 1 if (t.is_floating_point() and t.requires_grad) else 0
+            for j, d in enumerate(shape):
+                words[base + 6 + j] = d
+        return words
+
+    def _decode(self, words: torch.Tensor) -> None:
+        self.meta = {}
+        w = words.tolist()
+        for i, k in enumerate(self.keys):
+            base = i * _META_WORDS
+            nd, one_d = w[base] & 63, bool(w[base] & 64)
+            lay = Layout("split" if w[base + 2] else "rep", "split" if w[base + 3] else "rep", w[base + 4])
+            self.meta[k] = (tuple(w[base + 6: base + 6 + nd]), _DTYPES[w[base + 1]], lay, bool(w[base + 5]), one_d)
+
+    def handshake_send(self, st, sides) -> None:
+        words = self._encode(st, sides)
+        self._decode(words)
+        dev_words = words.to(self.device)
+        # source rank i informs the destination ranks i, i + |src|, ...
+        mine = [r for j, r in enumerate(range(self.dst.first_rank, self.dst.first_rank + self.dst.size))
+                if j % self.src.size == self.rank - self.src.first_rank]
+        reqs = [dist.isend(dev_words, r) for r in mine]
+        for r in reqs:
+            r.wait()
+
+    def handshake_recv(self) -> None:
+        words = torch.zeros(len(self.keys) * _META_WORDS, dtype=torch.int64, device=self.device)
+        j = self.rank - self.dst.first_rank
+        dist.recv(words, self.src.first_rank + j % self.src.size)
+        self._decode(words.cpu())
+
+    # ---- transfers ------------------------------------------------------------------------------
+    def forward_ops(self, st: Optional[Dict[str, Any]], sides: Optional[Dict[str, tuple]]):
+        """P2P ops that move the boundary tensors downstream; returns (ops, assemble() -> (state, sides))."""
+        all_ops, parts = [], []
+        for k in self.keys:
+            gshape, dtype, lay, _, one_d = self.meta[k]
+            src_side, src_lay = (sides[k] if self.i_am_src else (self.src, lay))
+            t = None
+            if self.i_am_src:
+                t = st[k].detach()
+                t = (t.unsqueeze(0) if one_d else t).contiguous()
+            tr = Transfer(self.rank, src_side, src_lay, self.dst, lay, gshape, dtype, self.device)
+            ops, asm = tr.prepare(t)
+            all_ops += ops
+            parts.append((k, asm))
+
+        def assemble():
+            out, out_sides = {}, {}
+            for k, asm in parts:
+                t = asm()
+                if t is None:
+                    continue
+                gshape, dtype, lay, needs_grad, one_d = self.meta[k]
+                t = t.squeeze(0) if one_d else t
+                if needs_grad and t.is_floating_point():
+                    t.requires_grad_(True)
+                out[k] = t
+                out_sides[k] = (self.dst, lay)
+            return out, out_sides
+
+        return all_ops, assemble
+
+    def backward_ops(self, grads: Optional[Dict[str, torch.Tensor]], src_sides: Optional[Dict[str, tuple]]):
+        """P2P ops that return the gradients of the boundary tensors upstream; assemble() -> {key: grad}."""
+        all_ops, parts = [], []
+        for k in self.keys:
+            gshape, dtype, lay, needs_grad, one_d = self.meta[k]
+            if not needs_grad:
+                continue
+            up_side, up_lay = (src_sides[k] if self.i_am_src else (self.src, lay))
+            g = None
+            if not self.i_am_src:
+                g = grads[k]
+                g = (g.unsqueeze(0) if one_d else g).contiguous()
+            tr = Transfer(self.rank, self.dst, lay, up_side, up_lay, gshape, dtype, self.device,
+                          sum_row_replicas=True)
+            ops, asm = tr.prepare(g)
+            all_ops += ops
+            parts.append((k, asm, one_d))
+
+        def assemble():
+            out = {}
+            for k, asm, one_d in parts:
+                t = asm()
+                if t is not None:
+                    out[k] = t.squeeze(0) if one_d else t
+            return out
+
+        return all_ops, assemble
+
+
+def _run_batch(ops):
+    reqs = dist.batch_isend_irecv(ops) if ops else []
+    for r in reqs:
+        r.wait()
+
+
+class PipelineRunner:
+    def __init__(self, trainer):
+        self.t = trainer
+        ps = trainer.pstate
+        self.stage, self.P = ps.stage, ps.num_stages
+        self.prev = Boundary(trainer, self.stage - 1) if self.stage > 0 else None
+        self.next = Boundary(trainer, self.stage) if self.stage < self.P - 1 else None
+        self._next_sides: List[Dict[str, tuple]] = []
+
+    # ---- single steps ---------------------------------------------------------------------------
+    def _forward(self, batch, mb: int, received) -> Tuple[Dict[str, Any], Dict[str, Any]]:
+        st = self.t.microbatch_inputs(batch, mb)
+        st["_meta"] = {}
+        inputs = {}
+        if received is not None:
+            tensors, sides = received
+            st.update(tensors)
+            st["_meta"].update(sides)
+            inputs = tensors
+        self.t.stage.forward(st)
+        return st, inputs
+
+    def _exchange(self, send_fwd=None, recv_fwd=False, send_bwd=None, recv_bwd=False):
+        """One batched group call with every send / receive of this step."""
+        ops, got_fwd, got_bwd = [], None, None
+        if recv_fwd:
+            if self.prev.meta is None:
+                self.prev.handshake_recv()
+            o, asm_f = self.prev.forward_ops(None, None)
+            ops += o
+        if send_bwd is not None:
+            o, _ = self.prev.backward_ops(send_bwd, None)
+            ops += o
+        if send_fwd is not None:
+            st, sides = send_fwd
+            if self.next.meta is None:
+                self.next.handshake_send(st, sides)
+            o, _ = self.next.forward_ops(st, sides)
+            ops += o
+        if recv_bwd:
+            o, asm_b = self.next.backward_ops(None, recv_bwd)
+            ops += o
+        _run_batch(ops)
+        if recv_fwd:
+            got_fwd = asm_f()
+        if recv_bwd:
+            got_bwd = asm_b()
+        return got_fwd, got_bwd
+
+    def _outputs(self, st) -> Tuple[Dict[str, Any], Dict[str, tuple]]:
+        keys = self.next.keys
+        return {k: st[k] for k in keys}, {k: st["_meta"][k] for k in keys}
+
+    def _backward(self, st, inputs, out_grads, loss_buf) -> Dict[str, torch.Tensor]:
+        if self.next is None:
+            loss = st["loss"]
+            loss.backward()
+            loss_buf += loss.detach()
+        else:
+            outs, gs = [], []
+            for k, g in out_grads.items():
+                o = st[k]
+                if isinstance(o, torch.Tensor) and o.requires_grad:
+                    outs.append(o)
+                    gs.append(g.to(o.dtype))
+            torch.autograd.backward(outs, gs)
+        grads = {}
+        for k, t in inputs.items():
+            if t.is_floating_point() and t.requires_grad:
+                grads[k] = t.grad if t.grad is not None else torch.zeros_like(t)
+        return grads
+
+    # ---- the schedule ---------------------------------------------------------------------------
+    def run(self, batch, loss_buf: torch.Tensor) -> torch.Tensor:
+        M = self.t.num_microbatches
+        warm = min(self.P - self.stage - 1, M)
+        steady = M - warm
+        first, last = self.prev is None, self.next is None
+        pending: List[tuple] = []   # (state, inputs, sides of the sent tensors)
+        mb = 0
+        received = None
+        if not first:
+            received, _ = self._exchange(recv_fwd=True)
+        for i in range(warm):
+            st, inputs = self._forward(batch, mb, received)
+            mb += 1
+            outs = self._outputs(st)
+            pending.append((st, inputs, outs[1]))
+            more_fwd = (i + 1 < warm) or steady > 0
+            received, _ = self._exchange(send_fwd=outs, recv_fwd=(not first) and more_fwd)
+        for i in range(steady):
+            st, inputs = self._forward(batch, mb, received)
+            mb += 1
+            out_grads = None
+            if not last:
+                outs = self._outputs(st)
+                pending.append((st, inputs, outs[1]))
+                _, out_grads = self._exchange(send_fwd=outs, recv_bwd=pending[0][2])
+            else:
+                pending.append((st, inputs, None))
+            st_b, in_b, _ = pending.pop(0)
+            grads = self._backward(st_b, in_b, out_grads, loss_buf)
+            more_fwd = i + 1 < steady
+            if not first:
+                received, _ = self._exchange(send_bwd=grads, recv_fwd=more_fwd)
+        for i in range(warm):
+            _, out_grads = self._exchange(recv_bwd=pending[0][2])
+            st_b, in_b, _ = pending.pop(0)
+            grads = self._backward(st_b, in_b, out_grads, loss_buf)
+            if not first:
+                self._exchange(send_bwd=grads)
+        return loss_buf

@@ -14,6 +14,7 @@ import torch
 
 from ..models.base import Env, Op, OpInfo
 from ..ops import functional as F
+from ..parallel.relayout import Layout, Side, relayout
 
 
 class _CheckpointFn(torch.autograd.Function):
@@ -63,24 +64,71 @@ class _CheckpointFn(torch.autograd.Function):
         return (None, None, None) + tuple(i.grad if i.requires_grad else None for i in ins)
 
 
+def _same_layout(side_a: Side, lay_a: Layout, side_b: Side, lay_b: Layout) -> bool:
+    """True when no data has to move: equal sides and layouts that only differ along an undivided axis."""
+    if side_a != side_b:
+        return False
+    if lay_a.row != lay_b.row and side_a.dp > 1:
+        return False
+    if side_a.tp > 1 and (lay_a.col != lay_b.col or (lay_a.col == "split" and lay_a.groups != lay_b.groups)):
+        return False
+    return True
+
+
+def run_op(op: Op, st: Dict[str, torch.Tensor]) -> None:
+    """Brings every tensor the op reads to the layout it requires under the op's own (tp, dp) -- the in-stage
+    resharding of the reference's pre_forward_tensor_adapter_hook (flex_model.py:250-300) -- then runs it."""
+    meta = st.get("_meta")
+    if meta is None:
+        op.forward(st)
+        return
+    ps = op.env.pstate
+    side = Side(ps.stage_start[ps.stage], op.info.tp, op.info.dp)
+    if side.size > 1:
+        req = op.required()
+        for k in op.reads:
+            t = st.get(k)
+            if k in req and k in meta and isinstance(t, torch.Tensor):
+                cur_side, cur_lay = meta[k]
+                want = req[k]
+                if cur_lay.groups != want.groups:
+                    want = Layout(want.row, want.col, cur_lay.groups)
+                if not _same_layout(cur_side, cur_lay, side, want):
+                    one_d = t.dim() == 1
+                    moved = relayout(t.unsqueeze(0) if one_d else t, ps.rank, cur_side, cur_lay, side, want)
+                    st[k] = moved.squeeze(0) if one_d else moved
+                meta[k] = (side, want)
+    op.forward(st)
+    for k, lay in op.produced().items():
+        if k in st:
+            meta[k] = (side, lay)
+
+
 class Segment:
     def __init__(self, ops: List[Op], recompute: bool):
         self.ops, self.recompute = ops, recompute
 
     def _run(self, st):
         for op in self.ops:
-            op.forward(st)
+            run_op(op, st)
 
     def forward(self, st: Dict[str, torch.Tensor]) -> None:
         if not self.recompute or not torch.is_grad_enabled():
             self._run(st)
             return
         in_keys = [k for k, v in st.items() if isinstance(v, torch.Tensor)]
-        extras = {k: v for k, v in st.items() if not isinstance(v, torch.Tensor)}
+        extras = {k: v for k, v in st.items() if not isinstance(v, torch.Tensor) and k != "_meta"}
+        meta_in = dict(st["_meta"]) if "_meta" in st else None
+        meta_out: dict = {}
 
         def run(inner):
             inner.update(extras)  # plain Python values (scales, flags) are visible inside the segment too
+            if meta_in is not None:
+                inner["_meta"] = dict(meta_in)  # the replay starts from the same layouts as the first run
             self._run(inner)
+            if meta_in is not None:
+                meta_out.clear()
+                meta_out.update(inner["_meta"])
 
         holder: dict = {}
         outs = _CheckpointFn.apply(run, in_keys, holder, *[st[k] for k in in_keys])
@@ -88,6 +136,8 @@ class Segment:
             st.pop(k)
         for k, v in zip(holder["out_keys"], outs):
             st[k] = v
+        if meta_in is not None:
+            st["_meta"] = dict(meta_out)
 
 
 def split_segments(ops: List[Op]) -> List[Segment]:

@@ -89,8 +89,13 @@ class Trainer:
                        fused_comm=fused_comm)
         self.env.training = training
         self.stage = Stage(infos, self.env, build_fn, fuse_fn if fuse else None)
+        self._tied = None
+        if self.pstate.num_stages > 1:
+            from .tied import TiedWeights
+            self._tied = TiedWeights(self)
         self.optimizer = StageOptimizer(self.store, self.pstate, lr=lr, weight_decay=weight_decay, clip_grad=clip_grad,
-                                        kind=optimizer)
+                                        kind=optimizer,
+                                        norm_exclude=self._tied.duplicate_param_names() if self._tied else ())
         self.lr_schedule = LRSchedule(lr, min_lr, lr_warmup_steps, lr_decay_steps, lr_style)
         self.iteration = 0
         self.pipeline = None
@@ -98,10 +103,6 @@ class Trainer:
             from .schedules import PipelineRunner
             self.pipeline = PipelineRunner(self)
         self._loss_buf = torch.zeros(1, dtype=torch.float32, device=self.device)
-        self._tied = None
-        if self.pstate.num_stages > 1:
-            from .tied import TiedWeights
-            self._tied = TiedWeights(self)
         self.timers: Dict[str, float] = {}
 
     @classmethod
@@ -144,6 +145,8 @@ class Trainer:
             return self.pipeline.run(batch, self._loss_buf)
         for mb in range(self.num_microbatches):
             st = self.microbatch_inputs(batch, mb)
+            if self.world_size > 1:
+                st["_meta"] = {}
             self.stage.forward(st)
             loss = st["loss"]
             loss.backward()

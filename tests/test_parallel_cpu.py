@@ -1,0 +1,62 @@
+"""Multi-rank training on CPU (gloo): pipeline, tensor and data parallel plans must reproduce the losses of
+the single-process run of the same model (constant seed, dropout off) -- the DEBUG_FIX_WEIGHT-style
+cross-configuration check of the reference (runtime/megatron/training.py:215-217)."""
+import pytest
+import torch
+
+from superscaler_b200.data.synthetic import gpt_batch
+from superscaler_b200.runtime.trainer import Trainer
+
+from dist_utils import run_ranks
+from helpers import tiny_gpt_plan
+
+NODROP = dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2)
+KW = dict(layers=2, seq=64, hidden=64, heads=2, head_dim=32, vocab=256, global_bs=8, micro_bs=4)
+
+
+def _losses(plan, rank=0, world=1, steps=3):
+    t = Trainer(plan, rank=rank, world_size=world, model_overrides=NODROP, lr_warmup_steps=0, device="cpu", lr=1e-3)
+    out = []
+    for _ in range(steps):
+        out.append(t.loss_value(t.train_step(gpt_batch(8, 64, 256, seed=1))))
+    return out
+
+
+def _worker(rank, world, plan, want):
+    got = _losses(plan, rank, world)
+    assert max(abs(a - b) for a, b in zip(got, want)) < 3e-3, (rank, got, want)
+
+
+BASE = None
+
+
+def _base():
+    global BASE
+    if BASE is None:
+        BASE = _losses(tiny_gpt_plan(**KW))
+    return BASE
+
+
+@pytest.mark.parametrize("name,plan_kw,world", [
+    ("dp2", dict(num_gpus=(2,), tp=[1]), 2),
+    ("tp2", dict(num_gpus=(2,), tp=[2]), 2),
+    ("pp2", dict(num_gpus=(1, 1)), 2),
+    ("pp2_tp2_dp2", dict(num_gpus=(2, 2), tp=[2, 1]), 4),
+    ("pp3_uneven", dict(num_gpus=(1, 2, 1), tp=[1, 2, 1], ops_per_stage=[9, 12, 8]), 4),
+])
+def test_parallel_plans_match_single_process(name, plan_kw, world):
+    plan = tiny_gpt_plan(**KW, **plan_kw)
+    run_ranks(_worker, world, plan, _base())
+
+
+def test_in_stage_resharding_matches_single_process():
+    # one stage of 2 GPUs whose ops switch from tp2 to dp2 in the middle of a layer and back
+    plan = tiny_gpt_plan(**KW, num_gpus=(2,), tp=[2])
+    n = plan["num_ops_in_each_stage"][0]
+    tp = [2] * n
+    for i in range(9, 20):
+        tp[i] = 1
+    plan["model_parallel_size_of_each_op"] = [tp]
+    plan["data_parallel_size_of_each_op"] = [[2 // t for t in tp]]
+    plan["resharding_stages"] = [True]
+    run_ranks(_worker, 2, plan, _base())

@@ -79,7 +79,9 @@ def _grad_worker(rank, world):
     x = _local(G, src, Layout("split", "rep"), rank).clone().requires_grad_(True)
     y = relayout(x, rank, src, Layout("split", "rep"), dst, Layout("split", "rep"))
     (y * _local(W, dst, Layout("split", "rep"), rank)).sum().backward()
-    assert torch.allclose(x.grad, W)          # every replica receives the full gradient
+    # every replica receives the full gradient, scaled by dp_src / dp_dst = 1/2 (each destination rank
+    # differentiates the mean over HALF of the rows)
+    assert torch.allclose(x.grad, 0.5 * W)
     # column split over tp2 <-> replicated: conjugate pair gather / slice
     x2 = _local(G, src, Layout("split", "split"), rank).clone().requires_grad_(True)
     y2 = relayout(x2, rank, src, Layout("split", "split"), src, Layout("split", "rep"))
