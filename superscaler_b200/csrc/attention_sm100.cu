@@ -98,11 +98,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* q_full = bars;          // 1
   uint64_t* k_full = bars + 1;      // 2
   uint64_t* v_full = bars + 3;      // 2
-  uint64_t* kv_empty = bars + 5;    // 2
-  uint64_t* s_full = bars + 7;      // 2
-  uint64_t* p_full = bars + 9;      // 1 (128 arrivals)
-  uint64_t* o_full = bars + 10;     // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* k_empty = bars + 5;     // 2  (K is free as soon as Q.K^T of its block retired)
+  uint64_t* v_empty = bars + 7;     // 2  (V is free after P.V of its block)
+  uint64_t* s_full = bars + 9;      // 2
+  uint64_t* p_full = bars + 11;     // 1 (128 arrivals)
+  uint64_t* o_full = bars + 12;     // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -118,7 +119,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int s = 0; s < 2; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&v_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
     }
     mbar_init(p_full, 128);
@@ -148,12 +150,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       Pipe pp;
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
-        if (!mbar_wait(&kv_empty[pp.stage], pp.phase ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&k_empty[pp.stage], pp.phase ^ 1, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(&k_full[pp.stage], Cfg::kTile);
 #pragma unroll
         for (int c = 0; c < CH; ++c)
           tma_load_2d(sK + pp.stage * Cfg::kTile + c * 16384, &tm_k, &k_full[pp.stage],
                       p.k_col0 + head * HD + c * 64, b * p.SK + j * 128);
+        if (!mbar_wait(&v_empty[pp.stage], pp.phase ^ 1, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(&v_full[pp.stage], Cfg::kTile);
 #pragma unroll
         for (int c = 0; c < CH; ++c)
@@ -185,6 +188,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_f16_ss(tmem_base + st * 128, umma_desc_sw128(a + off, 16, 1024), umma_desc_sw128(bb + off, 16, 1024),
                       idesc_s, k != 0);
         }
+        umma_commit(&k_empty[st]);
         umma_commit(&s_full[st]);
       };
       if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
@@ -210,7 +214,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const uint64_t db = umma_desc_sw128(bb + k * 2048, 16384, 1024);
           umma_f16_ss(tmem_o, da, db, idesc_o, k != 0);
         }
-        umma_commit(&kv_empty[st]);
+        umma_commit(&v_empty[st]);
         umma_commit(o_full);
       }
     }
@@ -303,8 +307,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       fence_proxy_async_smem();
       mbar_arrive(p_full);
     }
+    ok = __all_sync(0xffffffffu, ok);
     if (ok && n_kv > 0) {
-      if (mbar_wait(o_full, (n_kv - 1) & 1, abort_flag)) {
+      if (__all_sync(0xffffffffu, mbar_wait(o_full, (n_kv - 1) & 1, abort_flag))) {
         tc_fence_after_sync();
 #pragma unroll
         for (int cc = 0; cc < HD / 32; ++cc) {
@@ -352,9 +357,10 @@ template <int HD>
 struct DkvCfg {
   static constexpr int kCh = HD / 64;
   static constexpr int kKvTile = 128 * HD * 2;  // K_j / V_j, resident
-  static constexpr int kQTile = 64 * HD * 2;    // Q_i / dO_i, 2 stages each
-  static constexpr int kPBytes = 128 * 64 * 2;  // P^T / dS^T [128 keys][64 queries], 2 buffers each
-  static constexpr int kSmem = 2 * kKvTile + 4 * kQTile + 4 * kPBytes + 1024 + 256;
+  static constexpr int kQStages = 3;
+  static constexpr int kQTile = 64 * HD * 2;    // Q_i / dO_i, kQStages stages each
+  static constexpr int kPBytes = 128 * 64 * 2;  // P^T / dS^T [128 keys][64 queries], one buffer each
+  static constexpr int kSmem = 2 * kKvTile + 2 * kQStages * kQTile + 2 * kPBytes + 1024 + 256;
   // TMEM: S^T0 [0,64) S^T1 [64,128) dP^T0 [128,192) dP^T1 [192,256) dV [256,256+HD) dK [384,384+HD)
   static constexpr int kTmemCols = 512;
 };
@@ -370,17 +376,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + Cfg::kKvTile;
-  uint8_t* sQ = sV + Cfg::kKvTile;      // 2 stages
-  uint8_t* sdO = sQ + 2 * Cfg::kQTile;  // 2 stages
-  uint8_t* sPt = sdO + 2 * Cfg::kQTile; // 2 buffers
-  uint8_t* sdSt = sPt + 2 * Cfg::kPBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sdSt + 2 * Cfg::kPBytes);
+  constexpr int QS = Cfg::kQStages;
+  uint8_t* sQ = sV + Cfg::kKvTile;       // QS stages
+  uint8_t* sdO = sQ + QS * Cfg::kQTile;  // QS stages
+  uint8_t* sPt = sdO + QS * Cfg::kQTile;
+  uint8_t* sdSt = sPt + Cfg::kPBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdSt + Cfg::kPBytes);
   uint64_t* kv_full = bars;          // 1
-  uint64_t* qdo_full = bars + 1;     // 2
-  uint64_t* qdo_empty = bars + 3;    // 2
-  uint64_t* s_full = bars + 5;       // 2
-  uint64_t* p_full = bars + 7;       // 2 (128 arrivals)
-  uint64_t* p_empty = bars + 9;      // 2
+  uint64_t* qdo_full = bars + 1;     // 3
+  uint64_t* qdo_empty = bars + 4;    // 3
+  uint64_t* s_full = bars + 7;       // 2
+  uint64_t* p_full = bars + 9;       // 1 (128 arrivals)
+  uint64_t* p_empty = bars + 10;     // 1
   uint64_t* acc_full = bars + 11;    // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -396,13 +403,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < QS; ++s) {
       mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_empty[s], 1);
-      mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 128);
-      mbar_init(&p_empty[s], 1);
     }
+    for (int s = 0; s < 2; ++s) mbar_init(&s_full[s], 1);
+    mbar_init(p_full, 128);
+    mbar_init(p_empty, 1);
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -442,12 +449,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           tma_load_2d(sdO + pp.stage * Cfg::kQTile + c * 8192, &tm_do, &qdo_full[pp.stage],
                       p.o_col0 + head * HD + c * 64, row);
         }
-        pp.advance(2);
+        pp.advance(QS);
       }
       if (!ok) {
         for (uint32_t it = 0; it < (1u << 20); ++it)
           if (mbar_try_wait(kv_full, 0)) break;
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < QS; ++s) {
           const uint32_t armed = (s < pp.stage) ? pp.phase : (pp.phase ^ 1);
           for (uint32_t it = 0; it < (1u << 20); ++it)
             if (mbar_try_wait(&qdo_full[s], armed)) break;
@@ -460,9 +467,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, false, true);  // [keys x HD], reduce over queries
       bool ok = mbar_wait(kv_full, 0, abort_flag);
       auto issue_sdp = [&](int it) {
-        const int st = it & 1;
+        const int st = it & 1;     // TMEM buffer
+        const int qs = it % QS;    // Q / dO stage
         const uint32_t k = smem_u32(sK), v = smem_u32(sV);
-        const uint32_t qq = smem_u32(sQ + st * Cfg::kQTile), dd = smem_u32(sdO + st * Cfg::kQTile);
+        const uint32_t qq = smem_u32(sQ + qs * Cfg::kQTile), dd = smem_u32(sdO + qs * Cfg::kQTile);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t offa = (kk >> 2) * 16384 + (kk & 3) * 32;
@@ -485,17 +493,16 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         issue_sdp(0);
       }
       for (int it = 0; it < n_it && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int qs = it % QS;
         if (it + 1 < n_it) {
-          if (!mbar_wait(&qdo_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&qdo_full[(it + 1) % QS], ((it + 1) / QS) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
           issue_sdp(it + 1);
         }
-        if (!mbar_wait(&p_full[st], ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(p_full, it & 1, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t pt = smem_u32(sPt + st * Cfg::kPBytes), dst = smem_u32(sdSt + st * Cfg::kPBytes);
-        const uint32_t qq = smem_u32(sQ + st * Cfg::kQTile), dd = smem_u32(sdO + st * Cfg::kQTile);
+        const uint32_t pt = smem_u32(sPt), dst = smem_u32(sdSt);
+        const uint32_t qq = smem_u32(sQ + qs * Cfg::kQTile), dd = smem_u32(sdO + qs * Cfg::kQTile);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // 64 queries = 4 steps of 16
           umma_f16_ss(tmem_dv, umma_desc_sw128(pt + kk * 32, 16, 1024), umma_desc_sw128(dd + kk * 2048, 8192, 1024),
@@ -504,8 +511,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         for (int kk = 0; kk < 4; ++kk)
           umma_f16_ss(tmem_dk, umma_desc_sw128(dst + kk * 32, 16, 1024), umma_desc_sw128(qq + kk * 2048, 8192, 1024),
                       idesc_acc, (it | kk) != 0);
-        umma_commit(&qdo_empty[st]);
-        umma_commit(&p_empty[st]);
+        umma_commit(&qdo_empty[qs]);
+        umma_commit(p_empty);
       }
       if (ok) umma_commit(acc_full);
     }
@@ -527,7 +534,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const int st = it & 1;
       const uint32_t ph = (it >> 1) & 1;
       if (!mbar_wait(&s_full[st], ph, abort_flag)) { ok = false; break; }
-      if (!mbar_wait(&p_empty[st], ph ^ 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const int qbase = (i0 + it) * 64;
 #pragma unroll 1
@@ -564,15 +570,21 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           wp[i >> 1] = pack_bf16x2(pv[0], pv[1]);
           wd[i >> 1] = pack_bf16x2(dv[0], dv[1]);
         }
-        store_row32_sw128(sPt + st * Cfg::kPBytes, r, cc * 4, wp);
-        store_row32_sw128(sdSt + st * Cfg::kPBytes, r, cc * 4, wd);
+        // the single P^T / dS^T buffer is free once the accumulating MMAs of the previous block retired
+        if (cc == 0 && it > 0 && !mbar_wait(p_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
+        store_row32_sw128(sPt, r, cc * 4, wp);
+        store_row32_sw128(sdSt, r, cc * 4, wd);
       }
+      if (!ok) break;
       tc_fence_before_sync();
       fence_proxy_async_smem();
-      mbar_arrive(&p_full[st]);
+      mbar_arrive(p_full);
     }
     if (ok && n_it > 0) ok = mbar_wait(acc_full, 0, abort_flag);
-    if (ok && kv < p.SK) {
+    // tcgen05.ld is warp-collective: the whole warp runs the loads, only the stores are predicated
+    ok = __all_sync(0xffffffffu, ok);
+    const bool store_row = kv < p.SK;
+    if (ok) {
       tc_fence_after_sync();
       __nv_bfloat16* dvrow = reinterpret_cast<__nv_bfloat16*>(p.dV) +
                              (static_cast<size_t>(b) * p.SK + kv) * p.lddv + p.dv_col0 + head * HD;
@@ -600,8 +612,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           wk.y = pack_bf16x2(__uint_as_float(rk[8 * i + 2]), __uint_as_float(rk[8 * i + 3]));
           wk.z = pack_bf16x2(__uint_as_float(rk[8 * i + 4]), __uint_as_float(rk[8 * i + 5]));
           wk.w = pack_bf16x2(__uint_as_float(rk[8 * i + 6]), __uint_as_float(rk[8 * i + 7]));
-          reinterpret_cast<uint4*>(dvrow + cc * 32)[i] = wv;
-          reinterpret_cast<uint4*>(dkrow + cc * 32)[i] = wk;
+          if (store_row) {
+            reinterpret_cast<uint4*>(dvrow + cc * 32)[i] = wv;
+            reinterpret_cast<uint4*>(dkrow + cc * 32)[i] = wk;
+          }
         }
       }
     }
@@ -623,9 +637,10 @@ template <int HD>
 struct DqCfg {
   static constexpr int kCh = HD / 64;
   static constexpr int kQTile = 128 * HD * 2;   // Q_i / dO_i resident
-  static constexpr int kKvTile = 64 * HD * 2;   // K_j / V_j, 2 stages each
+  static constexpr int kKvStages = 3;
+  static constexpr int kKvTile = 64 * HD * 2;   // K_j / V_j, kKvStages stages each
   static constexpr int kSBytes = 128 * 64 * 2;  // dS [128 queries][64 keys], 2 buffers
-  static constexpr int kSmem = 2 * kQTile + 4 * kKvTile + 2 * kSBytes + 1024 + 256;
+  static constexpr int kSmem = 2 * kQTile + 2 * kKvStages * kKvTile + 2 * kSBytes + 1024 + 256;
   // TMEM: S0 [0,64) S1 [64,128) dP0 [128,192) dP1 [192,256) dQ [256, 256+HD)
   static constexpr int kTmemCols = 512;
 };
@@ -641,18 +656,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + Cfg::kQTile;
-  uint8_t* sK = sdO + Cfg::kQTile;      // 2 stages
-  uint8_t* sV = sK + 2 * Cfg::kKvTile;  // 2 stages
-  uint8_t* sdS = sV + 2 * Cfg::kKvTile; // 2 buffers
+  constexpr int KS = Cfg::kKvStages;
+  uint8_t* sK = sdO + Cfg::kQTile;       // KS stages
+  uint8_t* sV = sK + KS * Cfg::kKvTile;  // KS stages
+  uint8_t* sdS = sV + KS * Cfg::kKvTile; // 2 buffers
   uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 2 * Cfg::kSBytes);
   uint64_t* q_full = bars;          // 1
-  uint64_t* kv_full = bars + 1;     // 2
-  uint64_t* kv_empty = bars + 3;    // 2
-  uint64_t* s_full = bars + 5;      // 2
-  uint64_t* ds_full = bars + 7;     // 2 (128 arrivals)
-  uint64_t* ds_empty = bars + 9;    // 2
-  uint64_t* acc_full = bars + 11;   // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* kv_full = bars + 1;     // 3
+  uint64_t* kv_empty = bars + 4;    // 3
+  uint64_t* s_full = bars + 7;      // 2
+  uint64_t* ds_full = bars + 9;     // 2 (128 arrivals)
+  uint64_t* ds_empty = bars + 11;   // 2
+  uint64_t* acc_full = bars + 13;   // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -665,9 +681,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < KS; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
       mbar_init(&ds_full[s], 128);
       mbar_init(&ds_empty[s], 1);
@@ -711,12 +729,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           tma_load_2d(sV + pp.stage * Cfg::kKvTile + c * 8192, &tm_v, &kv_full[pp.stage],
                       p.v_col0 + head * HD + c * 64, row);
         }
-        pp.advance(2);
+        pp.advance(KS);
       }
       if (!ok) {
         for (uint32_t it = 0; it < (1u << 20); ++it)
           if (mbar_try_wait(q_full, 0)) break;
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < KS; ++s) {
           const uint32_t armed = (s < pp.stage) ? pp.phase : (pp.phase ^ 1);
           for (uint32_t it = 0; it < (1u << 20); ++it)
             if (mbar_try_wait(&kv_full[s], armed)) break;
@@ -729,9 +747,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, HD, false, true);   // [queries x HD], reduce over keys
       bool ok = mbar_wait(q_full, 0, abort_flag);
       auto issue_sdp = [&](int it) {
-        const int st = it & 1;
+        const int st = it & 1;     // TMEM buffer
+        const int ks = it % KS;    // K / V stage
         const uint32_t qq = smem_u32(sQ), dd = smem_u32(sdO);
-        const uint32_t k = smem_u32(sK + st * Cfg::kKvTile), v = smem_u32(sV + st * Cfg::kKvTile);
+        const uint32_t k = smem_u32(sK + ks * Cfg::kKvTile), v = smem_u32(sV + ks * Cfg::kKvTile);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t offa = (kk >> 2) * 16384 + (kk & 3) * 32;
@@ -757,19 +776,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
         if (it + 1 < n_it) {
-          if (!mbar_wait(&kv_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&kv_full[(it + 1) % KS], ((it + 1) / KS) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
           issue_sdp(it + 1);
         }
         if (!mbar_wait(&ds_full[st], ph, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t ds = smem_u32(sdS + st * Cfg::kSBytes);
-        const uint32_t k = smem_u32(sK + st * Cfg::kKvTile);
+        const uint32_t k = smem_u32(sK + (it % KS) * Cfg::kKvTile);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // 64 keys = 4 steps of 16
           umma_f16_ss(tmem_dq, umma_desc_sw128(ds + kk * 32, 16, 1024), umma_desc_sw128(k + kk * 2048, 8192, 1024),
                       idesc_dq, (it | kk) != 0);
-        umma_commit(&kv_empty[st]);
+        umma_commit(&kv_empty[it % KS]);
         umma_commit(&ds_empty[st]);
       }
       if (ok) umma_commit(acc_full);
@@ -833,7 +852,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_arrive(&ds_full[st]);
     }
     if (ok && n_it > 0) ok = mbar_wait(acc_full, 0, abort_flag);
-    if (ok && q_ok) {
+    ok = __all_sync(0xffffffffu, ok);  // warp-collective loads below; stores are predicated per row
+    if (ok) {
       tc_fence_after_sync();
       __nv_bfloat16* dqrow = reinterpret_cast<__nv_bfloat16*>(p.dQ) +
                              (static_cast<size_t>(b) * p.SQ + q) * p.lddq + p.dq_col0 + head * HD;
@@ -854,7 +874,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           w.y = pack_bf16x2(__uint_as_float(rq[8 * i + 2]), __uint_as_float(rq[8 * i + 3]));
           w.z = pack_bf16x2(__uint_as_float(rq[8 * i + 4]), __uint_as_float(rq[8 * i + 5]));
           w.w = pack_bf16x2(__uint_as_float(rq[8 * i + 6]), __uint_as_float(rq[8 * i + 7]));
-          reinterpret_cast<uint4*>(dqrow + cc * 32)[i] = w;
+          if (q_ok) reinterpret_cast<uint4*>(dqrow + cc * 32)[i] = w;
         }
       }
     }

@@ -71,7 +71,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n"  // suspend-time hint: 2 us
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
@@ -88,7 +88,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   uint64_t t0 = 0;
   for (uint32_t it = 0; it < kMbarSpinLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 8191u) == 8191u) {
+    if ((it & 1023u) == 1023u) {
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;

@@ -27,3 +27,32 @@ def tiny_gpt_plan(layers=2, seq=128, hidden=128, heads=2, head_dim=64, vocab=512
             "model_parallel_size_of_each_op": [[tp[s]] * ops_per_stage[s] for s in range(stages)],
             "data_parallel_size_of_each_op": [[dp[s]] * ops_per_stage[s] for s in range(stages)],
             "recompute_ops": rc, "algo_of_each_op": [[0] * c for c in ops_per_stage]}
+
+
+def tiny_t5_plan(layers=1, enc_seq=64, dec_seq=32, hidden=64, heads=2, head_dim=32, ffn=128, vocab=256, global_bs=4,
+                 micro_bs=2, recompute=0, num_gpus=(1,), ops_per_stage=None, tp=None):
+    from superscaler_b200.models.t5 import t5_op_names
+    names = t5_op_names(layers)
+    n = len(names)
+    stages = len(num_gpus)
+    if ops_per_stage is None:
+        per = n // stages
+        ops_per_stage = [per] * stages
+        ops_per_stage[-1] += n - per * stages
+    tp = tp or [1] * stages
+    dp = [g // t for g, t in zip(num_gpus, tp)]
+    never = ("encoder-embedding", "decoder-embedding", "t5-post-process")
+    rc_flat = [0 if nm in never else recompute for nm in names]
+    rc, start = [], 0
+    for c in ops_per_stage:
+        rc.append(rc_flat[start:start + c])
+        start += c
+    return {"model_name": "t5", "model_size": "tiny", "num_layers": layers, "encoder_seq_length": enc_seq,
+            "decoder_seq_length": dec_seq, "max_position_embeddings": enc_seq, "num_attention_heads": heads,
+            "kv_channels": head_dim, "hidden_size": hidden, "ffn_hidden_size": ffn, "vocab_size": vocab,
+            "global_batch_size": global_bs, "micro_batch_size": micro_bs, "num_stages": stages,
+            "num_gpus": list(num_gpus), "checkpoint_activations": [bool(recompute)] * stages,
+            "resharding_stages": [False] * stages, "num_ops_in_each_stage": list(ops_per_stage),
+            "model_parallel_size_of_each_op": [[tp[s]] * ops_per_stage[s] for s in range(stages)],
+            "data_parallel_size_of_each_op": [[dp[s]] * ops_per_stage[s] for s in range(stages)],
+            "recompute_ops": rc, "algo_of_each_op": [[0] * c for c in ops_per_stage]}
