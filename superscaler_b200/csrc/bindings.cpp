@@ -50,6 +50,23 @@ int attn_fwd_launch(const void* q, int ldq, const void* k, int ldk, const void* 
                     cudaStream_t stream);
 int attn_bwd_launch(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const void* dout,
                     int lddo, const AttnParams& p, float* delta_scratch, cudaStream_t stream);
+int bn_slices(long long rows);
+int im2col_launch(const void* x, void* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Kpad,
+                  int num_sms, cudaStream_t stream);
+int col2im_launch(const void* dcols, void* dx, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Kpad,
+                  int num_sms, cudaStream_t stream);
+int subsample_launch(const void* in, void* out, int N, int H, int W, int C, int stride, int scatter, int num_sms,
+                     cudaStream_t stream);
+int bn_fwd_launch(const void* x, const void* residual, const float* gamma, const float* beta, void* y, float* mean,
+                  float* rstd, float* run_mean, float* run_var, float* part, long long rows, int C, float eps,
+                  float momentum, int relu, int num_sms, cudaStream_t stream);
+int bn_bwd_launch(const void* dy, const void* x, const void* y, const float* mean, const float* rstd,
+                  const float* gamma, void* dx, void* dres, float* dgamma, float* dbeta, float* part, float* sums,
+                  int accumulate, long long rows, int C, int relu, int num_sms, cudaStream_t stream);
+int maxpool_fwd_launch(const void* x, void* y, void* idx, int N, int H, int W, int C, int num_sms, cudaStream_t stream);
+int maxpool_bwd_launch(const void* dy, const void* idx, void* dx, int N, int H, int W, int C, int num_sms,
+                       cudaStream_t stream);
+int avgpool_launch(const void* in, void* out, int N, int HW, int C, int backward, int num_sms, cudaStream_t stream);
 }  // namespace ssb
 
 namespace {
@@ -393,6 +410,116 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
                "attn_bwd");
 }
 
+// ------------------------------ convolution / batch-norm / pooling ------------------------------
+// x: NHWC bf16 [N, H, W, C] contiguous -> patch matrix [N*Ho*Wo, Kpad]
+Tensor im2col(const Tensor& x, int64_t KH, int64_t KW, int64_t stride, int64_t pad, int64_t Kpad) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() == 4);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int N = x.size(0), H = x.size(1), W = x.size(2), C = x.size(3);
+  const int Ho = (H + 2 * pad - KH) / stride + 1, Wo = (W + 2 * pad - KW) / stride + 1;
+  TORCH_CHECK(Kpad >= KH * KW * C && Kpad % 8 == 0);
+  Tensor cols = torch::empty({static_cast<int64_t>(N) * Ho * Wo, Kpad}, x.options());
+  check_launch(ssb::im2col_launch(x.data_ptr(), cols.data_ptr(), N, H, W, C, KH, KW, stride, pad, Kpad, num_sms(),
+                                  cur_stream()), "im2col");
+  return cols;
+}
+
+Tensor col2im(const Tensor& dcols, int64_t N, int64_t H, int64_t W, int64_t C, int64_t KH, int64_t KW, int64_t stride,
+              int64_t pad) {
+  TORCH_CHECK(dcols.is_cuda() && dcols.scalar_type() == torch::kBFloat16 && dcols.is_contiguous());
+  c10::cuda::CUDAGuard guard(dcols.device());
+  Tensor dx = torch::empty({N, H, W, C}, dcols.options());
+  check_launch(ssb::col2im_launch(dcols.data_ptr(), dx.data_ptr(), N, H, W, C, KH, KW, stride, pad, dcols.size(1),
+                                  num_sms(), cur_stream()), "col2im");
+  return dx;
+}
+
+// scatter = false: [N,H,W,C] -> [N,ceil(H/s),ceil(W/s),C]; scatter = true: the transpose, given the full H, W
+Tensor subsample(const Tensor& in, int64_t H, int64_t W, int64_t stride, bool scatter) {
+  TORCH_CHECK(in.is_cuda() && in.scalar_type() == torch::kBFloat16 && in.is_contiguous() && in.dim() == 4);
+  c10::cuda::CUDAGuard guard(in.device());
+  const int64_t N = in.size(0), C = in.size(3);
+  const int64_t Ho = (H + stride - 1) / stride, Wo = (W + stride - 1) / stride;
+  Tensor out = scatter ? torch::empty({N, H, W, C}, in.options()) : torch::empty({N, Ho, Wo, C}, in.options());
+  check_launch(ssb::subsample_launch(in.data_ptr(), out.data_ptr(), N, H, W, C, stride, scatter, num_sms(), cur_stream()),
+               "subsample");
+  return out;
+}
+
+// x: [rows, C] bf16.  Returns (y, mean, rstd).
+std::vector<Tensor> bn_fwd(const Tensor& x, const OptTensor& residual, const Tensor& gamma, const Tensor& beta,
+                           const OptTensor& run_mean, const OptTensor& run_var, double eps, double momentum, bool relu) {
+  check_bf16_2d(x, "x");
+  TORCH_CHECK(x.is_contiguous() && gamma.scalar_type() == torch::kFloat32 && beta.scalar_type() == torch::kFloat32);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0);
+  const int C = x.size(1);
+  auto fopt = torch::dtype(torch::kFloat32).device(x.device());
+  Tensor y = torch::empty_like(x), mean = torch::empty({C}, fopt), rstd = torch::empty({C}, fopt);
+  Tensor part = torch::empty({ssb::bn_slices(rows), 2, C}, fopt);
+  check_launch(ssb::bn_fwd_launch(x.data_ptr(), opt_ptr(residual), gamma.data_ptr<float>(), beta.data_ptr<float>(),
+                                  y.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                                  run_mean.has_value() ? run_mean->data_ptr<float>() : nullptr,
+                                  run_var.has_value() ? run_var->data_ptr<float>() : nullptr, part.data_ptr<float>(),
+                                  rows, C, static_cast<float>(eps), static_cast<float>(momentum), relu, num_sms(),
+                                  cur_stream()), "bn_fwd");
+  return {y, mean, rstd};
+}
+
+// Returns (dx, dresidual or undefined); dgamma / dbeta are written (or accumulated) in place.
+std::vector<Tensor> bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, const Tensor& mean, const Tensor& rstd,
+                           const Tensor& gamma, Tensor& dgamma, Tensor& dbeta, bool accumulate, bool relu,
+                           bool has_residual) {
+  check_bf16_2d(dy, "dy"); check_bf16_2d(x, "x");
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && y.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0);
+  const int C = x.size(1);
+  auto fopt = torch::dtype(torch::kFloat32).device(x.device());
+  Tensor dx = torch::empty_like(x);
+  Tensor dres;
+  if (has_residual) dres = torch::empty_like(x);
+  Tensor part = torch::empty({ssb::bn_slices(rows), 2, C}, fopt), sums = torch::empty({2, C}, fopt);
+  check_launch(ssb::bn_bwd_launch(dy.data_ptr(), x.data_ptr(), y.data_ptr(), mean.data_ptr<float>(),
+                                  rstd.data_ptr<float>(), gamma.data_ptr<float>(), dx.data_ptr(),
+                                  has_residual ? dres.data_ptr() : nullptr, dgamma.data_ptr<float>(),
+                                  dbeta.data_ptr<float>(), part.data_ptr<float>(), sums.data_ptr<float>(), accumulate,
+                                  rows, C, relu, num_sms(), cur_stream()), "bn_bwd");
+  if (has_residual) return {dx, dres};
+  return {dx};
+}
+
+std::vector<Tensor> maxpool_fwd(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() == 4);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t N = x.size(0), H = x.size(1), W = x.size(2), C = x.size(3);
+  Tensor y = torch::empty({N, (H + 1) / 2, (W + 1) / 2, C}, x.options());
+  Tensor idx = torch::empty({N, (H + 1) / 2, (W + 1) / 2, C}, torch::dtype(torch::kUInt8).device(x.device()));
+  check_launch(ssb::maxpool_fwd_launch(x.data_ptr(), y.data_ptr(), idx.data_ptr(), N, H, W, C, num_sms(), cur_stream()),
+               "maxpool_fwd");
+  return {y, idx};
+}
+
+Tensor maxpool_bwd(const Tensor& dy, const Tensor& idx, int64_t H, int64_t W) {
+  TORCH_CHECK(dy.is_contiguous() && idx.is_contiguous());
+  c10::cuda::CUDAGuard guard(dy.device());
+  const int64_t N = dy.size(0), C = dy.size(3);
+  Tensor dx = torch::empty({N, H, W, C}, dy.options());
+  check_launch(ssb::maxpool_bwd_launch(dy.data_ptr(), idx.data_ptr(), dx.data_ptr(), N, H, W, C, num_sms(), cur_stream()),
+               "maxpool_bwd");
+  return dx;
+}
+
+// forward: x [N, HW, C] -> [N, C]; backward: dy [N, C] -> [N, HW, C]
+Tensor avgpool(const Tensor& in, int64_t HW, bool backward) {
+  TORCH_CHECK(in.is_cuda() && in.scalar_type() == torch::kBFloat16 && in.is_contiguous());
+  c10::cuda::CUDAGuard guard(in.device());
+  const int64_t N = in.size(0), C = in.size(-1);
+  Tensor out = backward ? torch::empty({N, HW, C}, in.options()) : torch::empty({N, C}, in.options());
+  check_launch(ssb::avgpool_launch(in.data_ptr(), out.data_ptr(), N, HW, C, backward, num_sms(), cur_stream()), "avgpool");
+  return out;
+}
+
 Tensor status() { return status_tensor(); }
 
 }  // namespace
@@ -415,5 +542,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_finalize", &ce_finalize);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
+  m.def("im2col", &im2col);
+  m.def("col2im", &col2im);
+  m.def("subsample", &subsample);
+  m.def("bn_fwd", &bn_fwd);
+  m.def("bn_bwd", &bn_bwd);
+  m.def("maxpool_fwd", &maxpool_fwd);
+  m.def("maxpool_bwd", &maxpool_bwd);
+  m.def("avgpool", &avgpool);
   m.def("status", &status);
 }

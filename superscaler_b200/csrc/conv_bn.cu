@@ -1,0 +1,507 @@
+// Convolution support kernels and BatchNorm / pooling for the Wide-ResNet family (NHWC, bf16).
+//
+// Convolutions run as GEMMs on the tcgen05 kernel of gemm_sm100.cu:
+//   1x1 stride 1 : the NHWC activation IS the [N*H*W, C] GEMM operand (no copy);
+//   1x1 stride s : `subsample` gathers the strided pixels first;
+//   k x k        : `im2col` writes the patch matrix [N*Ho*Wo, k*k*C] (tap-major, channel-minor), the
+//                  filter is stored [Cout, k*k*C]; dgrad is a GEMM followed by `col2im` (gather form,
+//                  no atomics), wgrad is the MN-major GEMM of the output gradient with the patch matrix.
+// They replace cuDNN behind torch.nn.Conv2d / BatchNorm2d / MaxPool2d / AdaptiveAvgPool2d in the
+// reference's ParallelConvOp ... ParallelAdapAvgPoolOp (runtime/megatron/model/flex_ops.py:1423-1719).
+//
+// BatchNorm uses batch statistics of the local micro-batch only (the reference does not synchronise
+// them across data-parallel ranks either) with fp32 accumulation; ReLU and the residual add are fused
+// into the normalisation pass.
+#include "common.cuh"
+
+namespace ssb {
+namespace {
+
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 q = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 q;
+  q.x = pack_bf16x2(f[0], f[1]); q.y = pack_bf16x2(f[2], f[3]);
+  q.z = pack_bf16x2(f[4], f[5]); q.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = q;
+}
+
+struct ConvGeom {
+  int N, H, W, C, KH, KW, stride, pad, Ho, Wo, Kpad;  // Kpad = row length of the patch matrix (>= KH*KW*C)
+};
+
+// cols[(n, ho, wo), (r, s, c)] = x[n, ho*stride + r - pad, wo*stride + s - pad, c]  (0 outside)
+// C % 8 == 0: one thread moves 8 channels of one tap.  The small-C variant handles the 3-channel stem.
+__global__ void __launch_bounds__(256)
+im2col_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ cols, ConvGeom g) {
+  const int cvec = g.C / 8;
+  const long long per_row = static_cast<long long>(g.KH) * g.KW * cvec;
+  const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / per_row;
+    int rem = static_cast<int>(i % per_row);
+    const int c8 = rem % cvec; rem /= cvec;
+    const int s = rem % g.KW, r = rem / g.KW;
+    const int wo = static_cast<int>(row % g.Wo);
+    const int ho = static_cast<int>((row / g.Wo) % g.Ho);
+    const int n = static_cast<int>(row / (static_cast<long long>(g.Wo) * g.Ho));
+    const int h = ho * g.stride + r - g.pad, w = wo * g.stride + s - g.pad;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (h >= 0 && h < g.H && w >= 0 && w < g.W)
+      v = *reinterpret_cast<const uint4*>(x + ((static_cast<long long>(n) * g.H + h) * g.W + w) * g.C + c8 * 8);
+    *reinterpret_cast<uint4*>(cols + row * g.Kpad + (static_cast<long long>(r) * g.KW + s) * g.C + c8 * 8) = v;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+im2col_small_c_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ cols, ConvGeom g) {
+  const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * g.Kpad;
+  const int kreal = g.KH * g.KW * g.C;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / g.Kpad;
+    const int k = static_cast<int>(i % g.Kpad);
+    __nv_bfloat16 v = __float2bfloat16(0.f);
+    if (k < kreal) {
+      const int c = k % g.C, s = (k / g.C) % g.KW, r = k / (g.C * g.KW);
+      const int wo = static_cast<int>(row % g.Wo);
+      const int ho = static_cast<int>((row / g.Wo) % g.Ho);
+      const int n = static_cast<int>(row / (static_cast<long long>(g.Wo) * g.Ho));
+      const int h = ho * g.stride + r - g.pad, w = wo * g.stride + s - g.pad;
+      if (h >= 0 && h < g.H && w >= 0 && w < g.W) v = x[((static_cast<long long>(n) * g.H + h) * g.W + w) * g.C + c];
+    }
+    cols[i] = v;
+  }
+}
+
+// dx[n, h, w, c] = sum over taps (r, s) with (h + pad - r) % stride == 0 ... of dcols[(n, ho, wo), (r, s, c)]
+__global__ void __launch_bounds__(256)
+col2im_kernel(const __nv_bfloat16* __restrict__ dcols, __nv_bfloat16* __restrict__ dx, ConvGeom g) {
+  const int cvec = g.C / 8;
+  const long long total = static_cast<long long>(g.N) * g.H * g.W * cvec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c8 = static_cast<int>(i % cvec);
+    long long pix = i / cvec;
+    const int w = static_cast<int>(pix % g.W);
+    const int h = static_cast<int>((pix / g.W) % g.H);
+    const int n = static_cast<int>(pix / (static_cast<long long>(g.W) * g.H));
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < g.KH; ++r) {
+      const int hn = h + g.pad - r;
+      if (hn < 0 || hn % g.stride) continue;
+      const int ho = hn / g.stride;
+      if (ho >= g.Ho) continue;
+      for (int s = 0; s < g.KW; ++s) {
+        const int wn = w + g.pad - s;
+        if (wn < 0 || wn % g.stride) continue;
+        const int wo = wn / g.stride;
+        if (wo >= g.Wo) continue;
+        float f[8];
+        ld8(dcols + ((static_cast<long long>(n) * g.Ho + ho) * g.Wo + wo) * g.Kpad +
+                (static_cast<long long>(r) * g.KW + s) * g.C + c8 * 8, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+    }
+    st8(dx + pix * g.C + c8 * 8, acc);
+  }
+}
+
+// y[n, ho, wo, :] = x[n, ho*s, wo*s, :]   (scatter = 1: the transpose, dx zero elsewhere)
+__global__ void __launch_bounds__(256)
+subsample_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int N, int H, int W, int C,
+                 int stride, int scatter) {
+  const int cvec = C / 8;
+  const int Ho = (H + stride - 1) / stride, Wo = (W + stride - 1) / stride;
+  if (!scatter) {
+    const long long total = static_cast<long long>(N) * Ho * Wo * cvec;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const int c8 = static_cast<int>(i % cvec);
+      long long pix = i / cvec;
+      const int wo = static_cast<int>(pix % Wo), ho = static_cast<int>((pix / Wo) % Ho);
+      const long long n = pix / (static_cast<long long>(Wo) * Ho);
+      *reinterpret_cast<uint4*>(out + pix * C + c8 * 8) =
+          *reinterpret_cast<const uint4*>(in + ((n * H + ho * stride) * W + wo * stride) * C + c8 * 8);
+    }
+  } else {
+    const long long total = static_cast<long long>(N) * H * W * cvec;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const int c8 = static_cast<int>(i % cvec);
+      long long pix = i / cvec;
+      const int w = static_cast<int>(pix % W), h = static_cast<int>((pix / W) % H);
+      const long long n = pix / (static_cast<long long>(W) * H);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (h % stride == 0 && w % stride == 0)
+        v = *reinterpret_cast<const uint4*>(in + ((n * Ho + h / stride) * Wo + w / stride) * C + c8 * 8);
+      *reinterpret_cast<uint4*>(out + pix * C + c8 * 8) = v;
+    }
+  }
+}
+
+// ------------------------------------ BatchNorm ---------------------------------------------
+// part[slice][0][c] = sum x, part[slice][1][c] = sum x^2 over the slice's rows; x is [rows, C].
+__global__ void __launch_bounds__(256)
+bn_stats_partial_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ part, long long rows, int C,
+                        int rows_per_slice) {
+  __shared__ float s1[8][64], s2[8][64];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = (blockIdx.x * 32 + tx) * 2;
+  const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_slice;
+  const long long r1 = min(rows, r0 + rows_per_slice);
+  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+  if (col < C) {
+    for (long long r = r0 + ty; r < r1; r += 8) {
+      const float2 v = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + r * C + col));
+      a0 += v.x; a1 += v.y; b0 += v.x * v.x; b1 += v.y * v.y;
+    }
+  }
+  s1[ty][tx * 2] = a0; s1[ty][tx * 2 + 1] = a1; s2[ty][tx * 2] = b0; s2[ty][tx * 2 + 1] = b1;
+  __syncthreads();
+  if (ty == 0 && col < C) {
+    float c0 = 0.f, c1 = 0.f, d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      c0 += s1[k][tx * 2]; c1 += s1[k][tx * 2 + 1]; d0 += s2[k][tx * 2]; d1 += s2[k][tx * 2 + 1];
+    }
+    float* p = part + static_cast<long long>(blockIdx.y) * 2 * C;
+    p[col] = c0; p[col + 1] = c1; p[C + col] = d0; p[C + col + 1] = d1;
+  }
+}
+
+// mean / rstd per channel from the partials; also updates the running statistics.
+__global__ void bn_stats_final_kernel(const float* __restrict__ part, int slices, int C, long long rows, float eps,
+                                      float momentum, float* __restrict__ mean, float* __restrict__ rstd,
+                                      float* __restrict__ run_mean, float* __restrict__ run_var) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s = 0.0, q = 0.0;
+  for (int k = 0; k < slices; ++k) {
+    s += part[static_cast<long long>(k) * 2 * C + c];
+    q += part[static_cast<long long>(k) * 2 * C + C + c];
+  }
+  const double m = s / static_cast<double>(rows);
+  double var = q / static_cast<double>(rows) - m * m;
+  if (var < 0.0) var = 0.0;
+  mean[c] = static_cast<float>(m);
+  rstd[c] = rsqrtf(static_cast<float>(var) + eps);
+  if (run_mean != nullptr) {
+    const double unbiased = rows > 1 ? var * static_cast<double>(rows) / static_cast<double>(rows - 1) : var;
+    run_mean[c] = (1.f - momentum) * run_mean[c] + momentum * static_cast<float>(m);
+    run_var[c] = (1.f - momentum) * run_var[c] + momentum * static_cast<float>(unbiased);
+  }
+}
+
+// y = [relu]((x - mean) * rstd * gamma + beta [+ residual])
+__global__ void __launch_bounds__(256)
+bn_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ gamma,
+                const float* __restrict__ beta, __nv_bfloat16* __restrict__ y, long long rows, int C, int relu) {
+  const int cvec = C / 8;
+  const long long total = rows * cvec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c0 = static_cast<int>(i % cvec) * 8;
+    float f[8], o[8];
+    ld8(x + i * 8, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = (f[j] - mean[c0 + j]) * rstd[c0 + j] * gamma[c0 + j] + beta[c0 + j];
+    if (residual != nullptr) {
+      float r[8];
+      ld8(residual + i * 8, r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] += r[j];
+    }
+    if (relu) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = fmaxf(o[j], 0.f);
+    }
+    st8(y + i * 8, o);
+  }
+}
+
+// Backward partials over a row slice: sum g and sum g * xhat, with g = dy masked by (y > 0) when relu.
+__global__ void __launch_bounds__(256)
+bn_bwd_partial_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
+                      const float* __restrict__ rstd, float* __restrict__ part, long long rows, int C,
+                      int rows_per_slice, int relu) {
+  __shared__ float s1[8][64], s2[8][64];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = (blockIdx.x * 32 + tx) * 2;
+  const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_slice;
+  const long long r1 = min(rows, r0 + rows_per_slice);
+  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+  if (col < C) {
+    const float m0 = mean[col], m1 = mean[col + 1], q0 = rstd[col], q1 = rstd[col + 1];
+    for (long long r = r0 + ty; r < r1; r += 8) {
+      float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dy + r * C + col));
+      const float2 v = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + r * C + col));
+      if (relu) {
+        const float2 o = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(y + r * C + col));
+        if (!(o.x > 0.f)) g.x = 0.f;
+        if (!(o.y > 0.f)) g.y = 0.f;
+      }
+      a0 += g.x; a1 += g.y;
+      b0 += g.x * (v.x - m0) * q0; b1 += g.y * (v.y - m1) * q1;
+    }
+  }
+  s1[ty][tx * 2] = a0; s1[ty][tx * 2 + 1] = a1; s2[ty][tx * 2] = b0; s2[ty][tx * 2 + 1] = b1;
+  __syncthreads();
+  if (ty == 0 && col < C) {
+    float c0 = 0.f, c1 = 0.f, d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      c0 += s1[k][tx * 2]; c1 += s1[k][tx * 2 + 1]; d0 += s2[k][tx * 2]; d1 += s2[k][tx * 2 + 1];
+    }
+    float* p = part + static_cast<long long>(blockIdx.y) * 2 * C;
+    p[col] = c0; p[col + 1] = c1; p[C + col] = d0; p[C + col + 1] = d1;
+  }
+}
+
+// sums[0][c] = sum g, sums[1][c] = sum g*xhat; dgamma (+)= sums[1], dbeta (+)= sums[0]
+__global__ void bn_bwd_final_kernel(const float* __restrict__ part, int slices, int C, float* __restrict__ sums,
+                                    float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0.f, q = 0.f;
+  for (int k = 0; k < slices; ++k) {
+    s += part[static_cast<long long>(k) * 2 * C + c];
+    q += part[static_cast<long long>(k) * 2 * C + C + c];
+  }
+  sums[c] = s;
+  sums[C + c] = q;
+  dbeta[c] = accumulate ? dbeta[c] + s : s;
+  dgamma[c] = accumulate ? dgamma[c] + q : q;
+}
+
+// dx = gamma * rstd * (g - mean(g) - xhat * mean(g * xhat)); dres = g (when a residual was added)
+__global__ void __launch_bounds__(256)
+bn_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                 const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean, const float* __restrict__ rstd,
+                 const float* __restrict__ gamma, const float* __restrict__ sums, __nv_bfloat16* __restrict__ dx,
+                 __nv_bfloat16* __restrict__ dres, long long rows, int C, int relu) {
+  const int cvec = C / 8;
+  const long long total = rows * cvec;
+  const float inv_n = 1.0f / static_cast<float>(rows);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c0 = static_cast<int>(i % cvec) * 8;
+    float g[8], v[8], o[8];
+    ld8(dy + i * 8, g);
+    ld8(x + i * 8, v);
+    if (relu) {
+      float yy[8];
+      ld8(y + i * 8, yy);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (!(yy[j] > 0.f)) g[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + j;
+      const float xhat = (v[j] - mean[c]) * rstd[c];
+      o[j] = gamma[c] * rstd[c] * (g[j] - sums[c] * inv_n - xhat * sums[C + c] * inv_n);
+    }
+    st8(dx + i * 8, o);
+    if (dres != nullptr) st8(dres + i * 8, g);
+  }
+}
+
+// ------------------------------------- pooling ----------------------------------------------
+// 3x3 / stride 2 / pad 1 max pooling; idx stores the winning tap (0..8) for the backward pass.
+__global__ void __launch_bounds__(256)
+maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ idx,
+                   int N, int H, int W, int C) {
+  const int Ho = (H + 1) / 2, Wo = (W + 1) / 2;
+  const long long total = static_cast<long long>(N) * Ho * Wo * C;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % C);
+    long long pix = i / C;
+    const int wo = static_cast<int>(pix % Wo), ho = static_cast<int>((pix / Wo) % Ho);
+    const long long n = pix / (static_cast<long long>(Wo) * Ho);
+    float best = -INFINITY;
+    int arg = 4;
+    for (int r = 0; r < 3; ++r)
+      for (int s = 0; s < 3; ++s) {
+        const int h = ho * 2 + r - 1, w = wo * 2 + s - 1;
+        if (h < 0 || h >= H || w < 0 || w >= W) continue;
+        const float v = __bfloat162float(x[((n * H + h) * W + w) * C + c]);
+        if (v > best) { best = v; arg = r * 3 + s; }
+      }
+    y[i] = __float2bfloat16(best);
+    idx[i] = static_cast<uint8_t>(arg);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+maxpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const uint8_t* __restrict__ idx,
+                   __nv_bfloat16* __restrict__ dx, int N, int H, int W, int C) {
+  const int Ho = (H + 1) / 2, Wo = (W + 1) / 2;
+  const long long total = static_cast<long long>(N) * H * W * C;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % C);
+    long long pix = i / C;
+    const int w = static_cast<int>(pix % W), h = static_cast<int>((pix / W) % H);
+    const long long n = pix / (static_cast<long long>(W) * H);
+    float acc = 0.f;
+    // output windows (ho, wo) that contain (h, w): ho*2 - 1 <= h <= ho*2 + 1
+    for (int ho = (h) / 2; ho <= (h + 1) / 2; ++ho) {
+      if (ho < 0 || ho >= Ho) continue;
+      const int r = h - ho * 2 + 1;
+      if (r < 0 || r > 2) continue;
+      for (int wo = (w) / 2; wo <= (w + 1) / 2; ++wo) {
+        if (wo < 0 || wo >= Wo) continue;
+        const int s = w - wo * 2 + 1;
+        if (s < 0 || s > 2) continue;
+        const long long o = ((n * Ho + ho) * Wo + wo) * C + c;
+        if (idx[o] == r * 3 + s) acc += __bfloat162float(dy[o]);
+      }
+    }
+    dx[i] = __float2bfloat16(acc);
+  }
+}
+
+// y[n, c] = mean over hw of x[n, hw, c]; backward broadcasts dy / HW.
+__global__ void __launch_bounds__(256)
+avgpool_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int N, int HW, int C) {
+  const long long total = static_cast<long long>(N) * C;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % C);
+    const long long n = i / C;
+    float s = 0.f;
+    for (int p = 0; p < HW; ++p) s += __bfloat162float(x[(n * HW + p) * C + c]);
+    y[i] = __float2bfloat16(s / static_cast<float>(HW));
+  }
+}
+__global__ void __launch_bounds__(256)
+avgpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx, int N, int HW, int C) {
+  const long long total = static_cast<long long>(N) * HW * C;
+  const float inv = 1.0f / static_cast<float>(HW);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % C);
+    const long long n = i / (static_cast<long long>(HW) * C);
+    dx[i] = __float2bfloat16(__bfloat162float(dy[n * C + c]) * inv);
+  }
+}
+
+int grid_for(long long work, int num_sms) {
+  long long want = (work + 255) / 256;
+  return static_cast<int>(want < 1 ? 1 : (want > num_sms * 32LL ? num_sms * 32LL : want));
+}
+
+}  // namespace
+
+int bn_slices(long long rows) {
+  long long s = (rows + 511) / 512;
+  return static_cast<int>(s < 1 ? 1 : (s > 256 ? 256 : s));
+}
+
+int im2col_launch(const void* x, void* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Kpad,
+                  int num_sms, cudaStream_t stream) {
+  ConvGeom g{N, H, W, C, KH, KW, stride, pad, (H + 2 * pad - KH) / stride + 1, (W + 2 * pad - KW) / stride + 1, Kpad};
+  const auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto* cb = reinterpret_cast<__nv_bfloat16*>(cols);
+  if (C % 8 == 0 && Kpad == KH * KW * C) {
+    const long long work = static_cast<long long>(N) * g.Ho * g.Wo * KH * KW * (C / 8);
+    im2col_kernel<<<grid_for(work, num_sms), 256, 0, stream>>>(xb, cb, g);
+  } else {
+    const long long work = static_cast<long long>(N) * g.Ho * g.Wo * Kpad;
+    im2col_small_c_kernel<<<grid_for(work, num_sms), 256, 0, stream>>>(xb, cb, g);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+int col2im_launch(const void* dcols, void* dx, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Kpad,
+                  int num_sms, cudaStream_t stream) {
+  if (C % 8) return -3;
+  ConvGeom g{N, H, W, C, KH, KW, stride, pad, (H + 2 * pad - KH) / stride + 1, (W + 2 * pad - KW) / stride + 1, Kpad};
+  const long long work = static_cast<long long>(N) * H * W * (C / 8);
+  col2im_kernel<<<grid_for(work, num_sms), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dcols),
+                                                             reinterpret_cast<__nv_bfloat16*>(dx), g);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int subsample_launch(const void* in, void* out, int N, int H, int W, int C, int stride, int scatter, int num_sms,
+                     cudaStream_t stream) {
+  if (C % 8) return -3;
+  const long long work = static_cast<long long>(N) * H * W * (C / 8);
+  subsample_kernel<<<grid_for(work, num_sms), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(in),
+                                                                reinterpret_cast<__nv_bfloat16*>(out), N, H, W, C,
+                                                                stride, scatter);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// part: scratch of bn_slices(rows) * 2 * C floats.
+int bn_fwd_launch(const void* x, const void* residual, const float* gamma, const float* beta, void* y, float* mean,
+                  float* rstd, float* run_mean, float* run_var, float* part, long long rows, int C, float eps,
+                  float momentum, int relu, int num_sms, cudaStream_t stream) {
+  if (C % 8) return -3;
+  const int slices = bn_slices(rows);
+  const int rps = static_cast<int>((rows + slices - 1) / slices);
+  dim3 grid((C / 2 + 31) / 32, slices);
+  bn_stats_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), part, rows, C, rps);
+  bn_stats_final_kernel<<<(C + 255) / 256, 256, 0, stream>>>(part, slices, C, rows, eps, momentum, mean, rstd,
+                                                             run_mean, run_var);
+  bn_apply_kernel<<<grid_for(rows * (C / 8), num_sms), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(residual), mean, rstd, gamma,
+      beta, reinterpret_cast<__nv_bfloat16*>(y), rows, C, relu);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// sums: scratch of 2 * C floats; part as above.
+int bn_bwd_launch(const void* dy, const void* x, const void* y, const float* mean, const float* rstd,
+                  const float* gamma, void* dx, void* dres, float* dgamma, float* dbeta, float* part, float* sums,
+                  int accumulate, long long rows, int C, int relu, int num_sms, cudaStream_t stream) {
+  if (C % 8) return -3;
+  const int slices = bn_slices(rows);
+  const int rps = static_cast<int>((rows + slices - 1) / slices);
+  dim3 grid((C / 2 + 31) / 32, slices);
+  bn_bwd_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
+                                                  reinterpret_cast<const __nv_bfloat16*>(x),
+                                                  reinterpret_cast<const __nv_bfloat16*>(y), mean, rstd, part, rows,
+                                                  C, rps, relu);
+  bn_bwd_final_kernel<<<(C + 255) / 256, 256, 0, stream>>>(part, slices, C, sums, dgamma, dbeta, accumulate);
+  bn_bwd_dx_kernel<<<grid_for(rows * (C / 8), num_sms), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
+      reinterpret_cast<const __nv_bfloat16*>(y), mean, rstd, gamma, sums, reinterpret_cast<__nv_bfloat16*>(dx),
+      reinterpret_cast<__nv_bfloat16*>(dres), rows, C, relu);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int maxpool_fwd_launch(const void* x, void* y, void* idx, int N, int H, int W, int C, int num_sms, cudaStream_t stream) {
+  const long long work = static_cast<long long>(N) * ((H + 1) / 2) * ((W + 1) / 2) * C;
+  maxpool_fwd_kernel<<<grid_for(work, num_sms), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x),
+                                                                  reinterpret_cast<__nv_bfloat16*>(y),
+                                                                  reinterpret_cast<uint8_t*>(idx), N, H, W, C);
+  return static_cast<int>(cudaGetLastError());
+}
+int maxpool_bwd_launch(const void* dy, const void* idx, void* dx, int N, int H, int W, int C, int num_sms,
+                       cudaStream_t stream) {
+  const long long work = static_cast<long long>(N) * H * W * C;
+  maxpool_bwd_kernel<<<grid_for(work, num_sms), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
+                                                                  reinterpret_cast<const uint8_t*>(idx),
+                                                                  reinterpret_cast<__nv_bfloat16*>(dx), N, H, W, C);
+  return static_cast<int>(cudaGetLastError());
+}
+int avgpool_launch(const void* in, void* out, int N, int HW, int C, int backward, int num_sms, cudaStream_t stream) {
+  if (!backward)
+    avgpool_fwd_kernel<<<grid_for(static_cast<long long>(N) * C, num_sms), 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), N, HW, C);
+  else
+    avgpool_bwd_kernel<<<grid_for(static_cast<long long>(N) * HW * C, num_sms), 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), N, HW, C);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace ssb

@@ -31,8 +31,27 @@ def _strip(name: str) -> str:
     return name
 
 
+def _resnet_kind(name: str):
+    if name in ("conv1", "bn1", "relu1", "maxpool", "avgpool", "fc"):
+        return name
+    if name.startswith("block-"):
+        return "block-" + name.split("-")[3]
+    return None
+
+
 def op_io(name: str) -> Tuple[Tuple[str, ...], Tuple[str, ...]]:
     """(reads, writes) of an op."""
+    rk = _resnet_kind(name)
+    if rk is not None:
+        if rk == "block-conv1":
+            return ("x",), ("x", "residual")
+        if rk == "block-downsample":
+            return ("x", "residual"), ("x",)
+        if rk == "fc":
+            return ("x", "labels"), ("loss",)
+        if rk == "conv1":
+            return ("images",), ("x",)
+        return ("x",), ("x",)
     n = _strip(name)
     if name == "encoder-embedding":
         return ("ids",), ("x",)
@@ -67,6 +86,11 @@ def op_io(name: str) -> Tuple[Tuple[str, ...], Tuple[str, ...]]:
 
 def required_layouts(name: str, algo: int) -> Dict[str, Layout]:
     """Layout each read key must have when the op starts (keys fed by the data loader are absent)."""
+    rk = _resnet_kind(name)
+    if rk is not None:
+        if rk == "conv1":
+            return {}
+        return {"x": ROWS, "residual": ROWS} if rk == "block-downsample" else {"x": ROWS}
     n = _strip(name)
     if name == "encoder-embedding":
         return {}
@@ -100,6 +124,11 @@ def required_layouts(name: str, algo: int) -> Dict[str, Layout]:
 
 
 def produced_layouts(name: str, algo: int) -> Dict[str, Layout]:
+    rk = _resnet_kind(name)
+    if rk is not None:
+        if rk == "fc":
+            return {}
+        return {"x": ROWS, "residual": ROWS} if rk == "block-conv1" else {"x": ROWS}
     n = _strip(name)
     if name == "encoder-embedding":
         return {"x": ROWS}

@@ -628,3 +628,33 @@ class LMHeadCrossEntropyFn(torch.autograd.Function):
 
 def lm_head_cross_entropy(x, W, targets, loss_mask=None, v0=0, loss_scale=1.0, group=None):
     return LMHeadCrossEntropyFn.apply(x, W, targets, loss_mask, v0, float(loss_scale), group)
+
+
+class CrossEntropyFn(torch.autograd.Function):
+    """sum_rows CE(logits, target) * loss_scale on given logits (used by classifiers whose head has a bias).
+    Must be the last op of the graph: backward ignores the incoming gradient value (taken as 1)."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, loss_scale):
+        tflat = targets.contiguous().view(-1)
+        if logits.is_cuda:
+            work = logits.contiguous().clone()
+            st = native.ext().ce_stats(work, tflat, 0)
+            losses = native.ext().ce_finalize(work, tflat, st, None, 0, loss_scale, True)
+            ctx.save_for_backward(work)
+            return losses.sum() * loss_scale
+        lf = logits.float()
+        losses = F.cross_entropy(lf, tflat, reduction="none")
+        prob = torch.softmax(lf, -1)
+        prob[torch.arange(lf.shape[0]), tflat] -= 1.0
+        ctx.save_for_backward((prob * loss_scale).to(logits.dtype))
+        return losses.sum() * loss_scale
+
+    @staticmethod
+    def backward(ctx, g):
+        (dlogits,) = ctx.saved_tensors
+        return dlogits, None, None
+
+
+def cross_entropy_sum(logits, targets, loss_scale=1.0):
+    return CrossEntropyFn.apply(logits, targets, float(loss_scale))

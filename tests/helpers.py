@@ -56,3 +56,27 @@ def tiny_t5_plan(layers=1, enc_seq=64, dec_seq=32, hidden=64, heads=2, head_dim=
             "model_parallel_size_of_each_op": [[tp[s]] * ops_per_stage[s] for s in range(stages)],
             "data_parallel_size_of_each_op": [[dp[s]] * ops_per_stage[s] for s in range(stages)],
             "recompute_ops": rc, "algo_of_each_op": [[0] * c for c in ops_per_stage]}
+
+
+def tiny_resnet_plan(blocks=(1, 1, 1, 1), in_channels=8, width_factor=2, global_bs=4, micro_bs=2, recompute=0,
+                     num_gpus=(1,), ops_per_stage=None, tp=None):
+    n = 4 + 8 * sum(blocks) + 2
+    stages = len(num_gpus)
+    if ops_per_stage is None:
+        per = n // stages
+        ops_per_stage = [per] * stages
+        ops_per_stage[-1] += n - per * stages
+    tp = tp or [1] * stages
+    dp = [g // t for g, t in zip(num_gpus, tp)]
+    rc_flat = [0] + [recompute] * (n - 2) + [0]
+    rc, start = [], 0
+    for c in ops_per_stage:
+        rc.append(rc_flat[start:start + c])
+        start += c
+    return {"model_name": "resnet", "model_size": "tiny", "num_layers": list(blocks), "in_channels": in_channels,
+            "width_factor": width_factor, "global_batch_size": global_bs, "micro_batch_size": micro_bs,
+            "num_stages": stages, "num_gpus": list(num_gpus), "checkpoint_activations": [bool(recompute)] * stages,
+            "resharding_stages": [False] * stages, "num_ops_in_each_stage": list(ops_per_stage),
+            "model_parallel_size_of_each_op": [[tp[s]] * ops_per_stage[s] for s in range(stages)],
+            "data_parallel_size_of_each_op": [[dp[s]] * ops_per_stage[s] for s in range(stages)],
+            "recompute_ops": rc, "algo_of_each_op": [[0] * c for c in ops_per_stage]}
