@@ -45,6 +45,14 @@ T5_SIZES: Dict[str, tuple] = {
     "11B": (24, 2048, 512, 1024, 65536, 128, 128, 30592, "fp16"),
     "22B": (48, 2048, 512, 1024, 65536, 128, 128, 30592, "fp16"),
 }
+# Shapes profiled on B200 under the same database file names (the benchmark's model definitions differ from the
+# reference tables above: GPT-3 1.3B uses 16 heads of 128; T5 770M uses encoder 512 / decoder 128 tokens, vocab 32128)
+B200_GPT_SIZES: Dict[str, tuple] = {
+    "1_3B": (24, 2048, 2048, 8192, 16, 128, 51200, "bf16"),
+}
+B200_T5_SIZES: Dict[str, tuple] = {
+    "770M": (24, 512, 128, 1024, 4096, 16, 64, 32128, "bf16"),
+}
 # multiples of the weight bytes held besides weights and gradients: (fp32 main params, optimizer state)
 STATE_MULTIPLIERS = {"resnet": (0, 2), "gpt": (2, 4), "t5": (2, 4)}
 

@@ -45,3 +45,17 @@ def test_recompute_replays_dropout_exactly():
     a, _ = _run(_plan(recompute=0))
     b, _ = _run(_plan(recompute=1))
     assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5
+
+
+def test_t5_and_resnet_train_on_gpu():
+    from superscaler_b200.data.synthetic import resnet_batch, t5_batch
+    from helpers import tiny_resnet_plan, tiny_t5_plan
+    t = Trainer(tiny_t5_plan(layers=1, enc_seq=256, dec_seq=128, hidden=256, heads=4, head_dim=64, ffn=512, vocab=2048,
+                             global_bs=4, micro_bs=2), lr_warmup_steps=0)
+    l = [t.loss_value(t.train_step(t5_batch(4, 256, 128, 2048, seed=1))) for _ in range(4)]
+    assert all(x == x for x in l) and l[-1] < l[0]
+    r = Trainer(tiny_resnet_plan(in_channels=32, global_bs=16, micro_bs=8), model_overrides=dict(image_size=64, num_classes=16),
+                lr_warmup_steps=0, lr=1e-3)
+    l = [r.loss_value(r.train_step(resnet_batch(16, 64, 16, seed=1))) for _ in range(4)]
+    torch.cuda.synchronize()
+    assert all(x == x for x in l) and l[-1] < l[0] and native.check_status() == 0
