@@ -50,6 +50,9 @@ int attn_fwd_launch(const void* q, int ldq, const void* k, int ldk, const void* 
                     cudaStream_t stream);
 int attn_bwd_launch(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const void* dout,
                     int lddo, const AttnParams& p, float* delta_scratch, cudaStream_t stream);
+int comm_max_blocks();
+int allreduce_scale_f32_launch(void* const* peer_ptrs, void* mc_ptr, void* const* flag_ptrs, int rank, int world,
+                               long long n, float scale, unsigned epoch, int* status, cudaStream_t stream);
 int bn_slices(long long rows);
 int im2col_launch(const void* x, void* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Kpad,
                   int num_sms, cudaStream_t stream);
@@ -520,6 +523,23 @@ Tensor avgpool(const Tensor& in, int64_t HW, bool backward) {
   return out;
 }
 
+// In-place sum over the ranks of a symmetric fp32 buffer, times `scale`.  peer_ptrs / flag_ptrs: int64 device tensors
+// holding the per-rank addresses; mc_ptr: multicast address or 0.  `epoch` must advance by 2 per call on every rank.
+void allreduce_scale_f32(const Tensor& peer_ptrs, int64_t mc_ptr, const Tensor& flag_ptrs, int64_t rank, int64_t world,
+                         int64_t n, double scale, int64_t epoch) {
+  TORCH_CHECK(peer_ptrs.is_cuda() && peer_ptrs.scalar_type() == torch::kInt64 && peer_ptrs.numel() == world);
+  TORCH_CHECK(flag_ptrs.is_cuda() && flag_ptrs.scalar_type() == torch::kInt64 && flag_ptrs.numel() == world);
+  c10::cuda::CUDAGuard guard(peer_ptrs.device());
+  check_launch(ssb::allreduce_scale_f32_launch(reinterpret_cast<void* const*>(peer_ptrs.data_ptr<int64_t>()),
+                                               reinterpret_cast<void*>(mc_ptr),
+                                               reinterpret_cast<void* const*>(flag_ptrs.data_ptr<int64_t>()), rank, world,
+                                               n, static_cast<float>(scale), static_cast<unsigned>(epoch),
+                                               status_tensor().data_ptr<int>(), cur_stream()),
+               "allreduce_scale_f32");
+}
+
+int64_t comm_max_blocks() { return ssb::comm_max_blocks(); }
+
 Tensor status() { return status_tensor(); }
 
 }  // namespace
@@ -550,5 +570,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("maxpool_fwd", &maxpool_fwd);
   m.def("maxpool_bwd", &maxpool_bwd);
   m.def("avgpool", &avgpool);
+  m.def("allreduce_scale_f32", &allreduce_scale_f32);
+  m.def("comm_max_blocks", &comm_max_blocks);
   m.def("status", &status);
 }

@@ -57,7 +57,12 @@ class StageOptimizer:
 
     # ---- data-parallel gradient reduction (NCCL path) -----------------------------------------
     def reduce_gradients(self) -> None:
-        """Average gradients over each op's DP group, one all-reduce per contiguous (tp, dp) range."""
+        """Average gradients over each op's DP group.  With a peer-mapped gradient buffer (pure data-parallel
+        stage) ONE fused kernel sums over the ranks and applies 1/dp through NVSwitch; otherwise one NCCL
+        all-reduce per contiguous (tp, dp) range."""
+        if self.store.symm_grad is not None:
+            self.store.symm_grad.allreduce_scale_(self.store.total, 1.0 / self.store.symm_grad.world)
+            return
         for (tp, dp), ranges in self.dp_buckets.items():
             if dp == 1:
                 continue

@@ -52,6 +52,8 @@ class ParamStore:
         self.wd_end = 0
         self.total = 0
         self._shared: Dict[str, str] = {}
+        self.grad_allocator = None      # optional: numel -> (tensor, owner) for a peer-mapped gradient buffer
+        self.symm_grad = None
 
     def declare(self, spec: ParamSpec) -> str:
         """Registers a parameter; tied parameters (same shared_key) resolve to the first declaration."""
@@ -96,7 +98,11 @@ class ParamStore:
         self.total = max(off, 128)
         f32 = dict(dtype=torch.float32, device=self.device)
         self.master = torch.zeros(self.total, **f32)
-        self.grad = torch.zeros(self.total, **f32)
+        if self.grad_allocator is not None:
+            self.symm_grad = self.grad_allocator(self.total)
+            self.grad = self.symm_grad.tensor
+        else:
+            self.grad = torch.zeros(self.total, **f32)
         self.exp_avg = torch.zeros(self.total, **f32)
         self.exp_avg_sq = torch.zeros(self.total, **f32)
         self.model16 = torch.zeros(self.total, dtype=torch.bfloat16, device=self.device)

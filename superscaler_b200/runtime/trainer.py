@@ -85,6 +85,12 @@ class Trainer:
         self.infos = infos
         F.manual_seed(seed + 100 * s)
         self.store = ParamStore(self.device, base_seed=seed)
+        pure_dp = (len(counts) == 1 and world_size > 1 and self.device.type == "cuda" and
+                   all(t == 1 for t in plan["model_parallel_size_of_each_op"][0]) and
+                   all(d == world_size for d in plan["data_parallel_size_of_each_op"][0]))
+        if fused_comm and pure_dp:
+            from ..parallel.symm import SymmetricBuffer
+            self.store.grad_allocator = lambda n: SymmetricBuffer(n, torch.float32, None, self.device)
         self.env = Env(cfg=self.cfg, pstate=self.pstate, store=self.store, micro_bs=self.micro_bs,
                        fused_comm=fused_comm)
         self.env.training = training
