@@ -1,0 +1,126 @@
+"""Training entry point: `python -m torch.distributed.run ... -m superscaler_b200.runtime.pretrain
+--flexpipe-config plan.json --train-iters 3 --log-path logs/` (one rank per GPU).
+
+Counterpart of the reference's pretrain_gpt.py / pretrain_t5.py / pretrain_resnet.py + training loop
+(runtime/pretrain_gpt.py, runtime/megatron/training.py:83-168,925-1018): the model family comes from the plan
+JSON, batches are synthetic, and at the last iteration every rank writes
+`{log-path}/csv/{config}_stage{s}_rank{r}.csv` with the per-region times (ms) and memory (MB) that the
+result-collection tools read (training.py:903-908).
+"""
+from __future__ import annotations
+
+import argparse
+import csv
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..data import synthetic
+from ..parallel.state import init_distributed
+from . import checkpointing
+from .timers import Timers
+from .trainer import Trainer
+
+
+def make_batch_fn(trainer: Trainer):
+    plan, cfg = trainer.plan, trainer.cfg
+    gbs = plan["global_batch_size"]
+    if trainer.model_name == "gpt":
+        return lambda i: synthetic.gpt_batch(gbs, cfg.seq_length, cfg.vocab, seed=1234 + i)
+    if trainer.model_name == "t5":
+        return lambda i: synthetic.t5_batch(gbs, cfg.seq_length, cfg.dec_seq_length, cfg.vocab, seed=1234 + i)
+    return lambda i: synthetic.resnet_batch(gbs, cfg.image_size, cfg.num_classes, seed=1234 + i)
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--flexpipe-config", required=True)
+    ap.add_argument("--train-iters", type=int, default=3)
+    ap.add_argument("--log-interval", type=int, default=1)
+    ap.add_argument("--log-path", default=None)
+    ap.add_argument("--lr", type=float, default=1.5e-4)
+    ap.add_argument("--min-lr", type=float, default=1.0e-5)
+    ap.add_argument("--lr-decay-style", default="cosine", choices=["constant", "linear", "cosine"])
+    ap.add_argument("--lr-decay-iters", type=int, default=320000)
+    ap.add_argument("--lr-warmup-fraction", type=float, default=0.01)
+    ap.add_argument("--weight-decay", type=float, default=0.01)
+    ap.add_argument("--clip-grad", type=float, default=1.0)
+    ap.add_argument("--optimizer", default="adam", choices=["adam", "sgd"])
+    ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--hidden-dropout", type=float, default=None)
+    ap.add_argument("--attention-dropout", type=float, default=None)
+    ap.add_argument("--save", default=None)
+    ap.add_argument("--load", default=None)
+    ap.add_argument("--save-interval", type=int, default=None)
+    ap.add_argument("--exit-interval", type=int, default=None)
+    ap.add_argument("--no-fused-comm", action="store_true")
+    ap.add_argument("--distributed-backend", default=None, choices=[None, "nccl", "gloo"])
+    args = ap.parse_args(argv)
+    rank, world, _ = init_distributed(args.distributed_backend)
+    with open(args.flexpipe_config) as f:
+        plan = json.load(f)
+    overrides = {}
+    if args.hidden_dropout is not None:
+        overrides["hidden_dropout"] = args.hidden_dropout
+    if args.attention_dropout is not None:
+        overrides["attention_dropout"] = args.attention_dropout
+    trainer = Trainer(plan, model_overrides=overrides, rank=rank, world_size=world, seed=args.seed, lr=args.lr, min_lr=args.min_lr,
+                      weight_decay=args.weight_decay, clip_grad=args.clip_grad, lr_decay_steps=args.lr_decay_iters,
+                      lr_warmup_steps=int(args.lr_warmup_fraction * args.lr_decay_iters), lr_style=args.lr_decay_style,
+                      optimizer=args.optimizer, fused_comm=not args.no_fused_comm)
+    if args.load:
+        checkpointing.load_checkpoint(trainer, args.load)
+    batch_fn = make_batch_fn(trainer)
+    timers = Timers(trainer.device.type == "cuda")
+    config_name = os.path.splitext(os.path.basename(args.flexpipe_config))[0]
+    regions = ["iteration", "forward-backward", "backward-params-all-reduce", "optimizer"]
+    for it in range(trainer.iteration, args.train_iters):
+        timers("iteration").start()
+        batch = trainer.to_device(batch_fn(it))
+        timers("forward-backward").start()
+        loss = trainer.forward_backward(batch)
+        trainer._fold_autograd_grads()
+        timers("forward-backward").stop()
+        timers("backward-params-all-reduce").start()
+        trainer.optimizer.reduce_gradients()
+        if trainer._tied is not None:
+            trainer._tied.sync_grads()
+        timers("backward-params-all-reduce").stop()
+        timers("optimizer").start()
+        lr = trainer.lr_schedule.step()
+        trainer.optimizer.step(lr=lr)
+        trainer.iteration += 1
+        timers("optimizer").stop()
+        timers("iteration").stop()
+        if (it + 1) % args.log_interval == 0:
+            row = timers.row(regions)
+            lv = trainer.loss_value({"loss_tensor": loss})
+            mem = torch.cuda.max_memory_allocated() / 2 ** 20 if trainer.device.type == "cuda" else 0.0
+            if rank == world - 1:
+                print(f" iteration {it + 1:8d}/{args.train_iters:8d} | elapsed time per iteration (ms): "
+                      f"{row['iteration']:.1f} | learning rate: {lr:.3E} | global batch size: "
+                      f"{plan['global_batch_size']:5d} | lm loss: {lv:.6E} | grad norm: {trainer.optimizer.grad_norm():.3f}",
+                      flush=True)
+            if it == args.train_iters - 1 and args.log_path:
+                os.makedirs(os.path.join(args.log_path, "csv"), exist_ok=True)
+                path = os.path.join(args.log_path, "csv", f"{config_name}_stage{trainer.pstate.stage}_rank{rank}.csv")
+                with open(path, "w", newline="") as f:
+                    w = csv.writer(f)
+                    w.writerow(["global_batch_size", "time"] + regions[1:] + ["max_allocated_memory(MB)"])
+                    w.writerow([plan["global_batch_size"], f"{row['iteration']:.2f}"] +
+                               [f"{row[r]:.2f}" for r in regions[1:]] + [f"{mem:.0f}"])
+        if args.save and args.save_interval and (it + 1) % args.save_interval == 0:
+            checkpointing.save_checkpoint(trainer, args.save)
+        if args.exit_interval and (it + 1) % args.exit_interval == 0:
+            break
+    if args.save:
+        checkpointing.save_checkpoint(trainer, args.save)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

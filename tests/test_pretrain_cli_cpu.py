@@ -1,0 +1,43 @@
+"""The training entry point writes the per-rank CSVs, and the result-collection helpers read them."""
+import json
+import os
+
+from helpers import tiny_gpt_plan
+from superscaler_b200.runtime import pretrain
+from superscaler_b200.utils import results
+
+
+def test_pretrain_writes_csv_and_results_read_it(tmp_path):
+    plan_path = tmp_path / "gpt_tiny_1stages_demo.json"
+    plan_path.write_text(json.dumps(tiny_gpt_plan()))
+    log = tmp_path / "logs"
+    pretrain.main(["--flexpipe-config", str(plan_path), "--train-iters", "2", "--log-path", str(log),
+                   "--lr-decay-iters", "10", "--hidden-dropout", "0", "--attention-dropout", "0", "--save", str(tmp_path / "ckpt")])
+    csv_path = log / "csv" / "gpt_tiny_1stages_demo_stage0_rank0.csv"
+    assert csv_path.is_file()
+    row = results.read_runtime_csv(str(csv_path))
+    assert row["global_batch_size"] == 4 and row["time"] > 0
+    thpt = results.throughput(str(log), "gpt_tiny_1stages_demo")
+    assert abs(thpt - 4 / (row["time"] / 1000.0)) < 1e-6
+    name, best = results.best_throughput(str(log))
+    assert name == "gpt_tiny_1stages_demo" and best == thpt
+    assert os.path.isfile(tmp_path / "ckpt" / "latest_checkpointed_iteration.txt")
+    # resume: a second run starts from iteration 2 and performs one more
+    pretrain.main(["--flexpipe-config", str(plan_path), "--train-iters", "3", "--lr-decay-iters", "10", "--hidden-dropout", "0", "--attention-dropout", "0",
+                   "--load", str(tmp_path / "ckpt"), "--save", str(tmp_path / "ckpt")])
+    assert (tmp_path / "ckpt" / "latest_checkpointed_iteration.txt").read_text().strip() == "3"
+
+
+def test_cost_model_accuracy(tmp_path):
+    log = tmp_path / "logs"
+    os.makedirs(log / "csv")
+    for r, t in enumerate([100.0, 110.0]):
+        (log / "csv" / f"cfg_stage{r}_rank{r}.csv").write_text(
+            "global_batch_size,time,forward-backward,backward-params-all-reduce,optimizer,max_allocated_memory(MB)\n"
+            f"8,{t},90,5,5,{1000 + r}\n")
+    pred = tmp_path / "info.csv"
+    pred.write_text("stage,time,memory\n0,99.0,900\n1,104.5,950\n")
+    acc = results.cost_model_accuracy(str(pred), str(log), "cfg")
+    assert acc["actual_time_ms"] == 110.0 and abs(acc["time_error_pct"] - 5.0) < 1e-9
+    assert acc["actual_memory_mb"] == 1001
+    assert abs(results.throughput(str(log), "cfg") - 8 / 0.110) < 1e-9
