@@ -27,7 +27,8 @@ int make_tma_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
 
 namespace {
 
-constexpr int kAttnThreads = 192;
+constexpr int kMathThreads = 512;               // 4 column groups x 4 warps
+constexpr int kAttnThreads = 64 + kMathThreads;  // + TMA warp + MMA warp
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -59,6 +60,22 @@ __device__ __forceinline__ void store_row32_sw128(uint8_t* chunk, int r, int pie
   }
 }
 
+// Writes 16 consecutive bf16 columns (8 packed words) of row r; piece0 = first 16-byte piece (even).
+__device__ __forceinline__ void store_row16_sw128(uint8_t* chunk, int r, int piece0, const uint32_t (&w)[8]) {
+  uint8_t* row = chunk + r * 128;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int piece = (piece0 + i) ^ (r & 7);
+    *reinterpret_cast<uint4*>(row + piece * 16) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+  }
+}
+
+// Bounded wait whose outcome is the same for every lane of the warp, so that the warp-collective
+// tcgen05.ld that follows is never executed by a part of the warp only.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
+
 struct Pipe {
   int stage = 0;
   uint32_t phase = 0;
@@ -73,14 +90,28 @@ struct Pipe {
 // =============================================================================================
 //                                         FORWARD
 // =============================================================================================
+// Math work is split by COLUMNS over four groups of four warps: the four warps of a group cover the 128
+// accumulator rows (a warp may only read the TMEM lanes 32*(warp%4)..+31), and group g owns columns
+// [32g, 32g+32) of every S tile and columns [g*HD/4, (g+1)*HD/4) of the output.  One thread therefore
+// handles a quarter of a row; the row maximum is exchanged between the four owners of a row through shared
+// memory (bounded mbarrier wait), the row sum is kept as per-thread partials and combined once at the end.
+// Sixteen math warps give every SM sub-partition four warps to interleave, which hides the latency of
+// the dependent ex2 / convert / pack chains that a single warp per sub-partition cannot.
 template <int HD>
 struct FwdCfg {
   static constexpr int kCh = HD / 64;
   static constexpr int kTile = 128 * HD * 2;  // Q / K / V tile of 128 rows
   static constexpr int kPBytes = 128 * 128 * 2;
-  static constexpr int kSmem = kTile * 5 + kPBytes + 1024 + 256;
-  static constexpr int kTmemCols = 512;  // S0 [0,128) S1 [128,256) O [256, 256+HD)
+  static constexpr int kXBytes = (2 * 4 * 128 + 4 * 128) * 4;  // row-max exchange (2 buffers) + row-sum partials
+  static constexpr int kSmem = kTile * 5 + kPBytes + kXBytes + 1024 + 256;
+  static constexpr int kTmemCols = 512;  // S0 [0,128) S1 [128,256) O0 [256,256+HD) O1 [384,384+HD)
 };
+
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
+  if constexpr (N == 32) tmem_ld_32x32(taddr, r);
+  else tmem_ld_32x16(taddr, r);
+}
 
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -88,22 +119,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   using Cfg = FwdCfg<HD>;
   constexpr int CH = Cfg::kCh;
+  constexpr int OC = HD / 4;  // output columns per math group
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + Cfg::kTile;       // 2 stages
   uint8_t* sV = sK + 2 * Cfg::kTile;   // 2 stages
   uint8_t* sP = sV + 2 * Cfg::kTile;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::kPBytes);
+  float* xmax = reinterpret_cast<float*>(sP + Cfg::kPBytes);  // [2][4 groups][128 rows]
+  float* xsum = xmax + 2 * 4 * 128;                           // [4 groups][128 rows]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xmax) + Cfg::kXBytes);
   uint64_t* q_full = bars;          // 1
   uint64_t* k_full = bars + 1;      // 2
   uint64_t* v_full = bars + 3;      // 2
   uint64_t* k_empty = bars + 5;     // 2  (K is free as soon as Q.K^T of its block retired)
   uint64_t* v_empty = bars + 7;     // 2  (V is free after P.V of its block)
   uint64_t* s_full = bars + 9;      // 2
-  uint64_t* p_full = bars + 11;     // 1 (128 arrivals)
-  uint64_t* o_full = bars + 12;     // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* p_full = bars + 11;     // 1 (kMathThreads arrivals)
+  uint64_t* o_full = bars + 12;     // 2
+  uint64_t* o_empty = bars + 14;    // 2 (kMathThreads arrivals)
+  uint64_t* x_bar = bars + 16;      // [2][4 quarters], 128 arrivals each
+  uint64_t* l_bar = bars + 24;      // [4 quarters], 128 arrivals each
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 28);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -122,9 +159,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
+      mbar_init(&o_full[s], 1);
+      mbar_init(&o_empty[s], kMathThreads);
     }
-    mbar_init(p_full, 128);
-    mbar_init(o_full, 1);
+    for (int s = 0; s < 8; ++s) mbar_init(&x_bar[s], 128);
+    for (int s = 0; s < 4; ++s) mbar_init(&l_bar[s], 128);
+    mbar_init(p_full, kMathThreads);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_q);
@@ -139,7 +179,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;
+  const uint32_t tmem_o = tmem_base + 256;  // two buffers, 128 columns apart
 
   if (warp == 0) {
     if (elect_one()) {
@@ -204,6 +244,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tc_fence_after_sync();
           issue_s(j + 1);
         }
+        // the output buffer of this block was last used by block j-2: wait until the math warps folded it
+        if (j >= 2 && !mbar_wait(&o_empty[st], ((j - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
         if (!mbar_wait(p_full, j & 1, abort_flag)) { ok = false; break; }
         if (!mbar_wait(&v_full[st], ph, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
@@ -212,15 +254,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int k = 0; k < 8; ++k) {  // 128 keys = 8 steps of 16
           const uint64_t da = umma_desc_sw128(a + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
           const uint64_t db = umma_desc_sw128(bb + k * 2048, 16384, 1024);
-          umma_f16_ss(tmem_o, da, db, idesc_o, k != 0);
+          umma_f16_ss(tmem_o + st * 128, da, db, idesc_o, k != 0);
         }
         umma_commit(&v_empty[st]);
-        umma_commit(o_full);
+        umma_commit(&o_full[st]);
       }
     }
   } else {
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;  // row inside the query tile
+    const int quarter = warp & 3;        // TMEM lane quarter this warp may read
+    const int g = (warp - 2) >> 2;       // column group
+    const int r = quarter * 32 + lane;   // row inside the query tile
     const int q = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float c = p.scale * kLog2e;
@@ -229,106 +272,97 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t bh_seed = static_cast<uint32_t>(hash64(p.dropout_seed, static_cast<uint64_t>(b) * p.NH + head));
     const uint32_t pairs_per_row = (p.SK + 1) >> 1;
     float m = -INFINITY, l = 0.f, alpha_pending = 1.f;
-    float o[HD];
+    float o[OC];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    for (int i = 0; i < OC; ++i) o[i] = 0.f;
+    auto fold = [&](int jj) {  // o = o * alpha_pending + P.V of block jj (already complete)
+      uint32_t rr[OC];
+      tmem_ld_cols<OC>(tmem_o + (jj & 1) * 128 + lane_addr + g * OC, rr);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < OC; ++i) o[i] = o[i] * alpha_pending + __uint_as_float(rr[i]);
+    };
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int st = j & 1;
-      if (!mbar_wait(&s_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(&s_full[st], (j >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
-      const uint32_t ts = tmem_base + lane_addr + st * 128;
-      const int kv0 = j * 128;
-      const bool need_mask = (p.causal && kv0 + 127 > q0) || (kv0 + 128 > kv_len);
-      // pass 1: running maximum
-      float mx = m;
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t rr[32];
-        tmem_ld_32x32(ts + cc * 32, rr);
-        tmem_ld_wait();
+      const int kv0 = j * 128 + g * 32;
+      const bool need_mask = (p.causal && kv0 + 31 > q0) || (kv0 + 32 > kv_len);
+      uint32_t rr[32];
+      tmem_ld_32x32(tmem_base + lane_addr + st * 128 + g * 32, rr);
+      tmem_ld_wait();
+      float mx = -INFINITY;
+      if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(rr[i]);
-          if (need_mask) {
-            const int kv = kv0 + cc * 32 + i;
-            if (kv >= kv_len || (p.causal && kv > q)) s = -INFINITY;
-          }
-          mx = fmaxf(mx, s);
+          const int kv = kv0 + i;
+          if (kv >= kv_len || (p.causal && kv > q)) rr[i] = 0xff800000u;  // -inf
         }
       }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(rr[i]));
+      // exchange the partial maxima of the four owners of this row
+      float* xm = xmax + st * 512;
+      xm[g * 128 + r] = mx;
+      mbar_arrive(&x_bar[st * 4 + quarter]);
+      if (!mbar_wait_warp(&x_bar[st * 4 + quarter], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      mx = fmaxf(fmaxf(xm[r], xm[128 + r]), fmaxf(xm[256 + r], xm[384 + r]));
+      mx = fmaxf(mx, m);
       const float m_use = (mx == -INFINITY) ? 0.f : mx;  // fully masked so far: keep exponents finite
       const float alpha = ex2((m - m_use) * c);         // m = -inf -> 0
-      // fold the previous block's P.V (in the frame of the previous maximum) into the registers
-      if (j > 0) {
-        if (!mbar_wait(o_full, (j - 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after_sync();
-#pragma unroll
-        for (int cc = 0; cc < HD / 32; ++cc) {
-          uint32_t rr[32];
-          tmem_ld_32x32(tmem_o + lane_addr + cc * 32, rr);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[cc * 32 + i] = o[cc * 32 + i] * alpha_pending + __uint_as_float(rr[i]);
-        }
-      }
-      alpha_pending = alpha;
-      // pass 2: probabilities -> shared memory (bf16, swizzled), row sum
-      float rowsum = 0.f;
       const float mc = m_use * c;
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t rr[32];
-        tmem_ld_32x32(ts + cc * 32, rr);
-        tmem_ld_wait();
-        uint32_t w[16];
+      float rowsum = 0.f;
+      uint32_t w[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int kv = kv0 + cc * 32 + i;
-          float p0 = ex2(__uint_as_float(rr[i]) * c - mc);
-          float p1 = ex2(__uint_as_float(rr[i + 1]) * c - mc);
-          if (need_mask) {
-            if (kv >= kv_len || (p.causal && kv > q)) p0 = 0.f;
-            if (kv + 1 >= kv_len || (p.causal && kv + 1 > q)) p1 = 0.f;
-          }
-          rowsum += p0 + p1;
-          if (p.dropout_p > 0.f) {
-            const uint32_t h = attn_pair_hash(bh_seed, q, pairs_per_row, kv >> 1);
-            p0 = ((h & 0xFFFFu) < keep16) ? p0 * inv_keep : 0.f;
-            p1 = ((h >> 16) < keep16) ? p1 * inv_keep : 0.f;
-          }
-          w[i >> 1] = pack_bf16x2(p0, p1);
+      for (int i = 0; i < 32; i += 2) {
+        float p0 = ex2(__uint_as_float(rr[i]) * c - mc);      // masked entries: ex2(-inf) = 0
+        float p1 = ex2(__uint_as_float(rr[i + 1]) * c - mc);
+        rowsum += p0 + p1;
+        if (p.dropout_p > 0.f) {
+          const uint32_t h = attn_pair_hash(bh_seed, q, pairs_per_row, (kv0 + i) >> 1);
+          p0 = ((h & 0xFFFFu) < keep16) ? p0 * inv_keep : 0.f;
+          p1 = ((h >> 16) < keep16) ? p1 * inv_keep : 0.f;
         }
-        store_row32_sw128(sP + (cc >> 1) * 16384, r, (cc & 1) * 4, w);
+        w[i >> 1] = pack_bf16x2(p0, p1);
       }
-      l = l * alpha + rowsum;
-      m = mx;
+      // the single P buffer is free once P.V of the previous block retired
+      if (j > 0 && !mbar_wait_warp(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+      store_row32_sw128(sP + (g >> 1) * 16384, r, (g & 1) * 4, w);
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(p_full);
+      // fold the previous block's P.V (in the frame of the previous maximum) while the tensor core runs this one
+      if (j > 0) {
+        tc_fence_after_sync();
+        fold(j - 1);
+        tc_fence_before_sync();
+        mbar_arrive(&o_empty[(j - 1) & 1]);
+      }
+      alpha_pending = alpha;
+      l = l * alpha + rowsum;
+      m = mx;
     }
     ok = __all_sync(0xffffffffu, ok);
     if (ok && n_kv > 0) {
-      if (__all_sync(0xffffffffu, mbar_wait(o_full, (n_kv - 1) & 1, abort_flag))) {
+      if (__all_sync(0xffffffffu, mbar_wait(&o_full[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag))) {
         tc_fence_after_sync();
-#pragma unroll
-        for (int cc = 0; cc < HD / 32; ++cc) {
-          uint32_t rr[32];
-          tmem_ld_32x32(tmem_o + lane_addr + cc * 32, rr);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[cc * 32 + i] = o[cc * 32 + i] * alpha_pending + __uint_as_float(rr[i]);
-        }
+        fold(n_kv - 1);
       } else {
         ok = false;
       }
     }
+    // combine the four partial row sums
+    xsum[g * 128 + r] = l;
+    mbar_arrive(&l_bar[quarter]);
+    if (!mbar_wait(&l_bar[quarter], 0, abort_flag)) ok = false;
+    l = (xsum[r] + xsum[128 + r]) + (xsum[256 + r] + xsum[384 + r]);
     if (ok && q < p.SQ) {
       const float inv_l = l > 0.f ? 1.0f / l : 0.f;
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.O) +
-                            (static_cast<size_t>(b) * p.SQ + q) * p.ldo + p.o_col0 + head * HD;
+                            (static_cast<size_t>(b) * p.SQ + q) * p.ldo + p.o_col0 + head * HD + g * OC;
 #pragma unroll
-      for (int i = 0; i < HD / 8; ++i) {
+      for (int i = 0; i < OC / 8; ++i) {
         uint4 w;
         w.x = pack_bf16x2(o[8 * i + 0] * inv_l, o[8 * i + 1] * inv_l);
         w.y = pack_bf16x2(o[8 * i + 2] * inv_l, o[8 * i + 3] * inv_l);
@@ -337,7 +371,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         reinterpret_cast<uint4*>(orow)[i] = w;
       }
       // rows with no visible key get +inf so that the backward probabilities exp(s - lse) vanish
-      p.LSE[(static_cast<size_t>(b) * p.NH + head) * p.SQ + q] = l > 0.f ? m * p.scale + logf(l) : INFINITY;
+      if (g == 0)
+        p.LSE[(static_cast<size_t>(b) * p.NH + head) * p.SQ + q] = l > 0.f ? m * p.scale + logf(l) : INFINITY;
     }
   }
 
@@ -408,7 +443,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_init(&qdo_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) mbar_init(&s_full[s], 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, kMathThreads);
     mbar_init(p_empty, 1);
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -518,8 +553,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
   } else {
     const int quarter = warp & 3;
+    const int g = (warp - 2) >> 2;      // column group: 16 of the 64 queries of a block, HD/4 output columns
     const int r = quarter * 32 + lane;  // key row inside the tile
     const int kv = kv0 + r;
+    constexpr int OC = HD / 4;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float c = p.scale * kLog2e;
     const uint32_t keep16 = dropout_keep16(p.dropout_p);
@@ -529,53 +566,62 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const float* lse_row = p.LSE + (static_cast<size_t>(b) * p.NH + head) * p.SQ;
     const float* delta_row = p.delta + (static_cast<size_t>(b) * p.NH + head) * p.SQ;
     const bool kv_ok = kv < kv_len;
+    const int odd = lane & 1;  // kv parity: lanes 2t and 2t+1 share the dropout hash of their key pair
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int st = it & 1;
       const uint32_t ph = (it >> 1) & 1;
-      if (!mbar_wait(&s_full[st], ph, abort_flag)) { ok = false; break; }
-      tc_fence_after_sync();
-      const int qbase = (i0 + it) * 64;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tmem_base + lane_addr + st * 64 + cc * 32, rs);
-        tmem_ld_32x32(tmem_base + lane_addr + 128 + st * 64 + cc * 32, rp);
-        tmem_ld_wait();
-        uint32_t wp[16], wd[16];
+      const int qbase = (i0 + it) * 64 + g * 16;
+      // statistics of this thread's 16 queries, requested before the accumulators are ready
+      float lse2[16], dl[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int q = qbase + cc * 32 + i + e;
-            const bool valid = kv_ok && q < p.SQ && !(p.causal && kv > q);
-            float pr = 0.f, ds = 0.f;
-            if (valid) {
-              pr = ex2(__uint_as_float(rs[i + e]) * c - __ldg(lse_row + q) * kLog2e);
-              float dp = __uint_as_float(rp[i + e]);
-              float pd = pr;
-              if (p.dropout_p > 0.f) {
-                const uint32_t h = attn_pair_hash(bh_seed, q, pairs_per_row, kv >> 1);
-                const bool keep = ((kv & 1) ? (h >> 16) : (h & 0xFFFFu)) < keep16;
-                pd = keep ? pr * inv_keep : 0.f;
-                dp = keep ? dp * inv_keep : 0.f;
-              }
-              ds = pr * (dp - __ldg(delta_row + q)) * p.scale;
-              pr = pd;
-            }
-            pv[e] = pr;
-            dv[e] = ds;
-          }
-          wp[i >> 1] = pack_bf16x2(pv[0], pv[1]);
-          wd[i >> 1] = pack_bf16x2(dv[0], dv[1]);
-        }
-        // the single P^T / dS^T buffer is free once the accumulating MMAs of the previous block retired
-        if (cc == 0 && it > 0 && !mbar_wait(p_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
-        store_row32_sw128(sPt, r, cc * 4, wp);
-        store_row32_sw128(sdSt, r, cc * 4, wd);
+      for (int i = 0; i < 16; ++i) {
+        const bool in = qbase + i < p.SQ;
+        lse2[i] = in ? __ldg(lse_row + qbase + i) * kLog2e : INFINITY;
+        dl[i] = in ? __ldg(delta_row + qbase + i) : 0.f;
       }
-      if (!ok) break;
+      if (!mbar_wait_warp(&s_full[st], ph, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      uint32_t rs[16], rp[16];
+      tmem_ld_32x16(tmem_base + lane_addr + st * 64 + g * 16, rs);
+      tmem_ld_32x16(tmem_base + lane_addr + 128 + st * 64 + g * 16, rp);
+      tmem_ld_wait();
+      uint32_t wp[8], wd[8];
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) {
+        bool keep0 = true, keep1 = true;
+        if (p.dropout_p > 0.f) {
+          // each lane hashes one of the two queries, its neighbour (same key pair) the other
+          const uint32_t h_mine = attn_pair_hash(bh_seed, qbase + i + odd, pairs_per_row, kv >> 1);
+          const uint32_t h_other = __shfl_xor_sync(0xffffffffu, h_mine, 1);
+          const uint32_t h0 = odd ? h_other : h_mine, h1 = odd ? h_mine : h_other;
+          keep0 = (odd ? (h0 >> 16) : (h0 & 0xFFFFu)) < keep16;
+          keep1 = (odd ? (h1 >> 16) : (h1 & 0xFFFFu)) < keep16;
+        }
+        float pv[2], dv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int q = qbase + i + e;
+          const bool valid = kv_ok && q < p.SQ && !(p.causal && kv > q);
+          const bool keep = e ? keep1 : keep0;
+          float pr = ex2(__uint_as_float(rs[i + e]) * c - lse2[i + e]);
+          float dp = __uint_as_float(rp[i + e]);
+          float pd = pr;
+          if (p.dropout_p > 0.f) {
+            pd = keep ? pr * inv_keep : 0.f;
+            dp = keep ? dp * inv_keep : 0.f;
+          }
+          const float ds = pr * (dp - dl[i + e]) * p.scale;
+          pv[e] = valid ? pd : 0.f;
+          dv[e] = valid ? ds : 0.f;
+        }
+        wp[i >> 1] = pack_bf16x2(pv[0], pv[1]);
+        wd[i >> 1] = pack_bf16x2(dv[0], dv[1]);
+      }
+      // the single P^T / dS^T buffer is free once the accumulating MMAs of the previous block retired
+      if (it > 0 && !mbar_wait_warp(p_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
+      store_row16_sw128(sPt, r, g * 2, wp);
+      store_row16_sw128(sdSt, r, g * 2, wd);
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(p_full);
@@ -587,35 +633,32 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (ok) {
       tc_fence_after_sync();
       __nv_bfloat16* dvrow = reinterpret_cast<__nv_bfloat16*>(p.dV) +
-                             (static_cast<size_t>(b) * p.SK + kv) * p.lddv + p.dv_col0 + head * HD;
+                             (static_cast<size_t>(b) * p.SK + kv) * p.lddv + p.dv_col0 + head * HD + g * OC;
       __nv_bfloat16* dkrow = reinterpret_cast<__nv_bfloat16*>(p.dK) +
-                             (static_cast<size_t>(b) * p.SK + kv) * p.lddk + p.dk_col0 + head * HD;
-#pragma unroll 1
-      for (int cc = 0; cc < HD / 32; ++cc) {
-        uint32_t rv[32], rk[32];
-        if (n_it > 0) {
-          tmem_ld_32x32(tmem_dv + lane_addr + cc * 32, rv);
-          tmem_ld_32x32(tmem_dk + lane_addr + cc * 32, rk);
-          tmem_ld_wait();
-        } else {
+                             (static_cast<size_t>(b) * p.SK + kv) * p.lddk + p.dk_col0 + head * HD + g * OC;
+      uint32_t rv[OC], rk[OC];
+      if (n_it > 0) {
+        tmem_ld_cols<OC>(tmem_dv + lane_addr + g * OC, rv);
+        tmem_ld_cols<OC>(tmem_dk + lane_addr + g * OC, rk);
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) rv[i] = rk[i] = 0u;
-        }
+        for (int i = 0; i < OC; ++i) rv[i] = rk[i] = 0u;
+      }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 wv, wk;
-          wv.x = pack_bf16x2(__uint_as_float(rv[8 * i + 0]), __uint_as_float(rv[8 * i + 1]));
-          wv.y = pack_bf16x2(__uint_as_float(rv[8 * i + 2]), __uint_as_float(rv[8 * i + 3]));
-          wv.z = pack_bf16x2(__uint_as_float(rv[8 * i + 4]), __uint_as_float(rv[8 * i + 5]));
-          wv.w = pack_bf16x2(__uint_as_float(rv[8 * i + 6]), __uint_as_float(rv[8 * i + 7]));
-          wk.x = pack_bf16x2(__uint_as_float(rk[8 * i + 0]), __uint_as_float(rk[8 * i + 1]));
-          wk.y = pack_bf16x2(__uint_as_float(rk[8 * i + 2]), __uint_as_float(rk[8 * i + 3]));
-          wk.z = pack_bf16x2(__uint_as_float(rk[8 * i + 4]), __uint_as_float(rk[8 * i + 5]));
-          wk.w = pack_bf16x2(__uint_as_float(rk[8 * i + 6]), __uint_as_float(rk[8 * i + 7]));
-          if (store_row) {
-            reinterpret_cast<uint4*>(dvrow + cc * 32)[i] = wv;
-            reinterpret_cast<uint4*>(dkrow + cc * 32)[i] = wk;
-          }
+      for (int i = 0; i < OC / 8; ++i) {
+        uint4 wv, wk;
+        wv.x = pack_bf16x2(__uint_as_float(rv[8 * i + 0]), __uint_as_float(rv[8 * i + 1]));
+        wv.y = pack_bf16x2(__uint_as_float(rv[8 * i + 2]), __uint_as_float(rv[8 * i + 3]));
+        wv.z = pack_bf16x2(__uint_as_float(rv[8 * i + 4]), __uint_as_float(rv[8 * i + 5]));
+        wv.w = pack_bf16x2(__uint_as_float(rv[8 * i + 6]), __uint_as_float(rv[8 * i + 7]));
+        wk.x = pack_bf16x2(__uint_as_float(rk[8 * i + 0]), __uint_as_float(rk[8 * i + 1]));
+        wk.y = pack_bf16x2(__uint_as_float(rk[8 * i + 2]), __uint_as_float(rk[8 * i + 3]));
+        wk.z = pack_bf16x2(__uint_as_float(rk[8 * i + 4]), __uint_as_float(rk[8 * i + 5]));
+        wk.w = pack_bf16x2(__uint_as_float(rk[8 * i + 6]), __uint_as_float(rk[8 * i + 7]));
+        if (store_row) {
+          reinterpret_cast<uint4*>(dvrow)[i] = wv;
+          reinterpret_cast<uint4*>(dkrow)[i] = wk;
         }
       }
     }
@@ -687,7 +730,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&ds_full[s], 128);
+      mbar_init(&ds_full[s], kMathThreads);
       mbar_init(&ds_empty[s], 1);
     }
     mbar_init(acc_full, 1);
@@ -795,8 +838,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   } else {
     const int quarter = warp & 3;
+    const int g = (warp - 2) >> 2;  // column group: 16 of the 64 keys of a block, HD/4 output columns
     const int r = quarter * 32 + lane;
     const int q = q0 + r;
+    constexpr int OC = HD / 4;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float c = p.scale * kLog2e;
     const uint32_t keep16 = dropout_keep16(p.dropout_p);
@@ -811,42 +856,36 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (int it = 0; it < n_it && ok; ++it) {
       const int st = it & 1;
       const uint32_t ph = (it >> 1) & 1;
-      if (!mbar_wait(&s_full[st], ph, abort_flag)) { ok = false; break; }
-      if (!mbar_wait(&ds_empty[st], ph ^ 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(&s_full[st], ph, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
-      const int kvb = it * 64;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tmem_base + lane_addr + st * 64 + cc * 32, rs);
-        tmem_ld_32x32(tmem_base + lane_addr + 128 + st * 64 + cc * 32, rp);
-        tmem_ld_wait();
-        uint32_t wd[16];
+      const int kvb = it * 64 + g * 16;
+      uint32_t rs[16], rp[16];
+      tmem_ld_32x16(tmem_base + lane_addr + st * 64 + g * 16, rs);
+      tmem_ld_32x16(tmem_base + lane_addr + 128 + st * 64 + g * 16, rp);
+      tmem_ld_wait();
+      uint32_t wd[8];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int kv = kvb + cc * 32 + i;
-          uint32_t h = 0;
-          if (p.dropout_p > 0.f) h = attn_pair_hash(bh_seed, q, pairs_per_row, kv >> 1);
-          float dsv[2];
+      for (int i = 0; i < 16; i += 2) {
+        const int kv = kvb + i;
+        uint32_t h = 0;
+        if (p.dropout_p > 0.f) h = attn_pair_hash(bh_seed, q, pairs_per_row, kv >> 1);
+        float dsv[2];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const bool valid = q_ok && (kv + e) < kv_len && !(p.causal && (kv + e) > q);
-            float ds = 0.f;
-            if (valid) {
-              const float pr = ex2(__uint_as_float(rs[i + e]) * c - lse2);
-              float dp = __uint_as_float(rp[i + e]);
-              if (p.dropout_p > 0.f) {
-                const bool keep = (e ? (h >> 16) : (h & 0xFFFFu)) < keep16;
-                dp = keep ? dp * inv_keep : 0.f;
-              }
-              ds = pr * (dp - delta) * p.scale;
-            }
-            dsv[e] = ds;
+        for (int e = 0; e < 2; ++e) {
+          const bool valid = q_ok && (kv + e) < kv_len && !(p.causal && (kv + e) > q);
+          const float pr = ex2(__uint_as_float(rs[i + e]) * c - lse2);
+          float dp = __uint_as_float(rp[i + e]);
+          if (p.dropout_p > 0.f) {
+            const bool keep = (e ? (h >> 16) : (h & 0xFFFFu)) < keep16;
+            dp = keep ? dp * inv_keep : 0.f;
           }
-          wd[i >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+          const float ds = pr * (dp - delta) * p.scale;
+          dsv[e] = valid ? ds : 0.f;
         }
-        store_row32_sw128(sdS + st * Cfg::kSBytes, r, cc * 4, wd);
+        wd[i >> 1] = pack_bf16x2(dsv[0], dsv[1]);
       }
+      if (!mbar_wait_warp(&ds_empty[st], ph ^ 1, abort_flag)) { ok = false; break; }
+      store_row16_sw128(sdS + st * Cfg::kSBytes, r, g * 2, wd);
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(&ds_full[st]);
@@ -856,26 +895,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (ok) {
       tc_fence_after_sync();
       __nv_bfloat16* dqrow = reinterpret_cast<__nv_bfloat16*>(p.dQ) +
-                             (static_cast<size_t>(b) * p.SQ + q) * p.lddq + p.dq_col0 + head * HD;
-#pragma unroll 1
-      for (int cc = 0; cc < HD / 32; ++cc) {
-        uint32_t rq[32];
-        if (n_it > 0) {
-          tmem_ld_32x32(tmem_dq + lane_addr + cc * 32, rq);
-          tmem_ld_wait();
-        } else {
+                             (static_cast<size_t>(b) * p.SQ + q) * p.lddq + p.dq_col0 + head * HD + g * OC;
+      uint32_t rq[OC];
+      if (n_it > 0) {
+        tmem_ld_cols<OC>(tmem_dq + lane_addr + g * OC, rq);
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) rq[i] = 0u;
-        }
+        for (int i = 0; i < OC; ++i) rq[i] = 0u;
+      }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(rq[8 * i + 0]), __uint_as_float(rq[8 * i + 1]));
-          w.y = pack_bf16x2(__uint_as_float(rq[8 * i + 2]), __uint_as_float(rq[8 * i + 3]));
-          w.z = pack_bf16x2(__uint_as_float(rq[8 * i + 4]), __uint_as_float(rq[8 * i + 5]));
-          w.w = pack_bf16x2(__uint_as_float(rq[8 * i + 6]), __uint_as_float(rq[8 * i + 7]));
-          if (q_ok) reinterpret_cast<uint4*>(dqrow + cc * 32)[i] = w;
-        }
+      for (int i = 0; i < OC / 8; ++i) {
+        uint4 w;
+        w.x = pack_bf16x2(__uint_as_float(rq[8 * i + 0]), __uint_as_float(rq[8 * i + 1]));
+        w.y = pack_bf16x2(__uint_as_float(rq[8 * i + 2]), __uint_as_float(rq[8 * i + 3]));
+        w.z = pack_bf16x2(__uint_as_float(rq[8 * i + 4]), __uint_as_float(rq[8 * i + 5]));
+        w.w = pack_bf16x2(__uint_as_float(rq[8 * i + 6]), __uint_as_float(rq[8 * i + 7]));
+        if (q_ok) reinterpret_cast<uint4*>(dqrow)[i] = w;
       }
     }
   }
