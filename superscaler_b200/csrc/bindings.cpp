@@ -12,6 +12,8 @@
 namespace ssb {
 int gemm_bf16_launch(const void* A, int lda, int a_mn_major, const void* B, int ldb, int b_mn_major,
                      const GemmParams& p, int num_sms, cudaStream_t stream);
+void gemm_set_pair_mode(int mode);
+int gemm_get_pair_mode();
 int layernorm_fwd_launch(const void* x, const void* residual, const float* gamma, const float* beta, void* y,
                          void* sum_out, float* mean, float* rstd, int rows, int H, float eps, int num_sms,
                          cudaStream_t stream);
@@ -546,6 +548,8 @@ Tensor status() { return status_tensor(); }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("gemm_set_pair_mode", &ssb::gemm_set_pair_mode);
+  m.def("gemm_get_pair_mode", &ssb::gemm_get_pair_mode);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("colsum", &colsum);

@@ -1,0 +1,374 @@
+// Two-SM ("cta_group::2") variant of the bf16 GEMM: a cluster of two CTAs on one SM pair computes a
+// 256 x 256 output tile.  Each CTA stages its own 128 rows of A and its own 128 of the tile's 256 B rows
+// (columns of the output), the leader CTA issues tcgen05.mma.cta_group::2 instructions that read both
+// CTAs' shared memory, and each CTA ends up with its 128 x 256 half of the accumulator in its own TMEM.
+//
+// Why: with one CTA per 128 x 256 tile the tensor core reads 12 KB of operands from shared memory per
+// 128 x 256 x 16 step while TMA writes the same amount, which exceeds what one SM's shared memory delivers
+// (measured: tensor pipe 65 % busy, L1/shared pipe 80 %).  Pairing halves the B traffic per SM.
+//
+//   warp 0     : TMA producer (one elected lane), in both CTAs
+//   warp 1     : TMEM allocator in both CTAs; MMA issuer in the leader (cluster rank 0)
+//   warps 2..9 : epilogue; warp w reads TMEM lanes 32*(w%4)..+31, columns 128*((w-2)/4)..+127
+//
+// Barriers: `full` lives in the leader and counts the bytes of both CTAs' loads (the peer's TMA signals it
+// through the cluster address); `empty` and `tmem_full` exist in both CTAs and are signalled together by a
+// multicast tcgen05.commit; `tmem_empty` lives in the leader and collects the epilogue warps of both CTAs.
+// Same operation and epilogue as gemm_bf16_kernel (runtime/megatron/mpu/layers.py:363,459,532,593 of the
+// reference are the call sites this replaces).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_epilogue.cuh"
+#include "gemm_sm100.cuh"
+
+namespace ssb {
+
+int make_tma_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                     uint32_t box_rows, uint32_t box_cols);
+
+namespace {
+
+constexpr int BM2 = 128;   // rows per CTA (256 per cluster)
+constexpr int BNH = 128;   // B rows staged per CTA (256 output columns per cluster)
+constexpr int BN2 = 256;
+constexpr int BK2 = 64;
+constexpr int kStages2 = 6;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads2 = 64 + kEpiWarps * 32;
+constexpr int kGroupM2 = 8;
+constexpr int kABytes2 = BM2 * BK2 * 2;
+constexpr int kBBytes2 = BNH * BK2 * 2;
+constexpr int kStageBytes2 = kABytes2 + kBBytes2;
+constexpr int kSmem2 = kStages2 * kStageBytes2 + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_smem(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory whose completion bytes are counted on an mbarrier that may live in
+// the other CTA of the pair (no multicast: every CTA fetches its own tile).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival on the barrier at this offset in BOTH CTAs once all MMAs issued so far have retired.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(mask)
+      : "memory");
+}
+
+// TMEM allocation for a CTA pair: warp 1 of BOTH CTAs executes these, with the same shared-memory offset.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+struct TileCoord2 {
+  int m_blk, n_blk;
+};
+__device__ __forceinline__ TileCoord2 tile_coord2(int tile, int num_m, int num_n) {
+  const int per_group = kGroupM2 * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * kGroupM2;
+  const int gsize = min(num_m - first_m, kGroupM2);
+  const int in_group = tile - group * per_group;
+  TileCoord2 c;
+  c.m_blk = first_m + in_group % gsize;
+  c.n_blk = in_group / gsize;
+  return c;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads2, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                  const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + kStages2 * kABytes2;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * kStageBytes2);
+  uint64_t* full_bar = bars;                       // leader's are used
+  uint64_t* empty_bar = bars + kStages2;           // both CTAs
+  uint64_t* tmem_full_bar = bars + 2 * kStages2;   // both CTAs
+  uint64_t* tmem_empty_bar = bars + 2 * kStages2 + 2;  // leader's are used
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages2 + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  const int num_m = (p.M + 2 * BM2 - 1) / (2 * BM2);
+  const int num_n = (p.N + BN2 - 1) / BN2;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK2 - 1) / BK2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tmem_full_bar[s], 1);
+      mbar_init(&tmem_empty_bar[s], 2 * kEpiWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const TileCoord2 tc = tile_coord2(tile, num_m, num_n);
+        const int m0 = tc.m_blk * 2 * BM2 + static_cast<int>(cta_rank) * BM2;
+        const int n0 = tc.n_blk * BN2 + static_cast<int>(cta_rank) * BNH;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes2);
+          const uint32_t bar = mapa_smem(smem_u32(&full_bar[stage]), 0);
+          uint8_t* sa = smem_a + stage * kABytes2;
+          uint8_t* sb = smem_b + stage * kBBytes2;
+          if (!A_MN) {
+            tma_load_2d_pair(sa, &tma_a, bar, kb * BK2, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM2 / 64; ++c) tma_load_2d_pair(sa + c * (64 * BK2 * 2), &tma_a, bar, m0 + c * 64, kb * BK2);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sb, &tma_b, bar, kb * BK2, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BNH / 64; ++c) tma_load_2d_pair(sb + c * (64 * BK2 * 2), &tma_b, bar, n0 + c * 64, kb * BK2);
+          }
+          if (++stage == kStages2) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      // The copies issued by this thread have landed once the MMAs that consume them retired, which the
+      // epilogue of the last tile waits for; on an aborted run the teardown below waits for them instead.
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (leader && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM2, BN2, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++iter) {
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (iter >> 1) & 1;
+        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * BN2;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem_a + stage * kABytes2);
+          const uint32_t sb = smem_u32(smem_b + stage * kBBytes2);
+#pragma unroll
+          for (int k = 0; k < BK2 / 16; ++k) {
+            const uint64_t da = A_MN ? umma_desc_sw128(sa + k * 2048, 64 * BK2 * 2, 1024)
+                                     : umma_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? umma_desc_sw128(sb + k * 2048, 64 * BK2 * 2, 1024)
+                                     : umma_desc_sw128(sb + k * 32, 16, 1024);
+            umma_f16_ss_pair(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage]);
+          if (++stage == kStages2) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit_pair(&tmem_full_bar[acc]);
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const uint32_t keep16 = dropout_keep16(p.dropout_p);
+    const float drop_scale = p.dropout_p > 0.f ? 65536.0f / static_cast<float>(keep16) : 1.0f;
+    int iter = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++iter) {
+      const TileCoord2 tc = tile_coord2(tile, num_m, num_n);
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (iter >> 1) & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag))) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = tc.m_blk * 2 * BM2 + static_cast<int>(cta_rank) * BM2 + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + half * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        const int n0 = tc.n_blk * BN2 + half * 128 + c * 32;
+        if (n0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        gemm_epilogue_chunk(p, row, n0, r, keep16, drop_scale);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_smem(smem_u32(&tmem_empty_bar[acc]), 0));
+    }
+  }
+
+  // ------------------------------- teardown ----------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // Aborted: give the copies in flight into this CTA's shared memory a bounded time to land.
+    if (threadIdx.x == 0) {
+      if (p.status != nullptr) atomicMax(p.status, static_cast<int>(kStatusMbarTimeout));
+      const uint64_t t0 = global_timer_ns();
+      for (uint32_t it = 0; it < (1u << 22); ++it)
+        if (global_timer_ns() - t0 > 2000000ull) break;
+    }
+    __syncthreads();
+  }
+  cluster_sync_all();  // neither CTA leaves (or frees TMEM) while the other may still address it
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+int launch_pair(const void* A, int lda, const void* B, int ldb, const GemmParams& p, int num_sms, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  int rc;
+  rc = !A_MN ? make_tma_2d_bf16(&ta, A, p.M, p.K, lda, BM2, BK2) : make_tma_2d_bf16(&ta, A, p.K, p.M, lda, BK2, 64);
+  if (rc != 0) return rc;
+  rc = !B_MN ? make_tma_2d_bf16(&tb, B, p.N, p.K, ldb, BNH, BK2) : make_tma_2d_bf16(&tb, B, p.K, p.N, ldb, BK2, 64);
+  if (rc != 0) return rc;
+  auto kernel = gemm2_bf16_kernel<A_MN, B_MN>;
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3(num_sms & ~1);
+    q.blockDim = dim3(kThreads2);
+    q.dynamicSmemBytes = kSmem2;
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = 2;
+    qa[0].val.clusterDim.y = 1;
+    qa[0].val.clusterDim.z = 1;
+    q.attrs = qa;
+    q.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kernel, &q);
+    if (e != cudaSuccess || n < 1) {
+      (void)cudaGetLastError();
+      return -5;
+    }
+    max_clusters = n;
+  }
+  const int num_tiles = ((p.M + 2 * BM2 - 1) / (2 * BM2)) * ((p.N + BN2 - 1) / BN2);
+  int clusters = num_sms / 2;
+  if (clusters > max_clusters) clusters = max_clusters;
+  if (clusters > num_tiles) clusters = num_tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(kThreads2);
+  cfg.dynamicSmemBytes = kSmem2;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p));
+}
+
+}  // namespace
+
+// Same contract as gemm_bf16_launch; callers pick this variant for outputs of at least 256 x 256.
+int gemm2_bf16_launch(const void* A, int lda, int a_mn_major, const void* B, int ldb, int b_mn_major,
+                      const GemmParams& p, int num_sms, cudaStream_t stream) {
+  if (!a_mn_major && !b_mn_major) return launch_pair<false, false>(A, lda, B, ldb, p, num_sms, stream);
+  if (!a_mn_major && b_mn_major) return launch_pair<false, true>(A, lda, B, ldb, p, num_sms, stream);
+  if (a_mn_major && b_mn_major) return launch_pair<true, true>(A, lda, B, ldb, p, num_sms, stream);
+  return launch_pair<true, false>(A, lda, B, ldb, p, num_sms, stream);
+}
+
+}  // namespace ssb

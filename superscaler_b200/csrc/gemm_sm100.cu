@@ -15,6 +15,7 @@
 // epilogue of tile i overlaps the main loop of tile i+1.
 #include "common.cuh"
 #include "gemm_sm100.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace ssb {
 
@@ -219,142 +220,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
         if (!row_ok) continue;
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        const bool full = (n0 + 32 <= p.N);
-
-        if (p.bias != nullptr) {
-          if (p.bias_fp32) {
-            const float* b = reinterpret_cast<const float*>(p.bias) + n0;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (full || n0 + i < p.N) v[i] += __ldg(b + i);
-          } else {
-            const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + n0;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (full || n0 + i < p.N) v[i] += __bfloat162float(b[i]);
-          }
-        }
-        if (p.preact_out != nullptr) {
-          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.preact_out) + static_cast<size_t>(row) * p.ldpre + n0;
-          if (full) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 q;
-              q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
-              q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-              q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-              q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-              reinterpret_cast<uint4*>(o)[i] = q;
-            }
-          } else {
-            for (int i = 0; i < 32 && n0 + i < p.N; ++i) o[i] = __float2bfloat16(v[i]);
-          }
-        }
-        if (p.act == kActGelu) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
-        } else if (p.act == kActRelu) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
-        } else if (p.act == kActDGelu || p.act == kActDRelu) {
-          const __nv_bfloat16* a =
-              reinterpret_cast<const __nv_bfloat16*>(p.aux) + static_cast<size_t>(row) * p.ldaux + n0;
-          float x[32];
-          if (full) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint4 q = __ldg(reinterpret_cast<const uint4*>(a) + i);
-              float2 f;
-              f = unpack_bf16x2(q.x); x[8 * i + 0] = f.x; x[8 * i + 1] = f.y;
-              f = unpack_bf16x2(q.y); x[8 * i + 2] = f.x; x[8 * i + 3] = f.y;
-              f = unpack_bf16x2(q.z); x[8 * i + 4] = f.x; x[8 * i + 5] = f.y;
-              f = unpack_bf16x2(q.w); x[8 * i + 6] = f.x; x[8 * i + 7] = f.y;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) x[i] = (n0 + i < p.N) ? __bfloat162float(a[i]) : 0.f;
-          }
-          if (p.act == kActDGelu) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= gelu_tanh_grad(x[i]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = x[i] > 0.f ? v[i] : 0.f;
-          }
-        }
-        if (p.dropout_p > 0.f) {
-          // flat index = row * N + col; groups of 4 consecutive columns (n0 is a multiple of 32)
-          const uint64_t g0 = (static_cast<uint64_t>(row) * static_cast<uint64_t>(p.N) + n0) >> 2;
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const uint32_t m = dropout_keep4(p.dropout_seed, g0 + g, keep16);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) v[4 * g + i] = ((m >> i) & 1u) ? v[4 * g + i] * drop_scale : 0.f;
-          }
-        }
-        if (p.residual != nullptr) {
-          const __nv_bfloat16* a =
-              reinterpret_cast<const __nv_bfloat16*>(p.residual) + static_cast<size_t>(row) * p.ldres + n0;
-          if (full) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint4 q = __ldg(reinterpret_cast<const uint4*>(a) + i);
-              float2 f;
-              f = unpack_bf16x2(q.x); v[8 * i + 0] += f.x; v[8 * i + 1] += f.y;
-              f = unpack_bf16x2(q.y); v[8 * i + 2] += f.x; v[8 * i + 3] += f.y;
-              f = unpack_bf16x2(q.z); v[8 * i + 4] += f.x; v[8 * i + 5] += f.y;
-              f = unpack_bf16x2(q.w); v[8 * i + 6] += f.x; v[8 * i + 7] += f.y;
-            }
-          } else {
-            for (int i = 0; i < 32 && n0 + i < p.N; ++i) v[i] += __bfloat162float(a[i]);
-          }
-        }
-        if (p.out_fp32) {
-          float* o = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + n0;
-          if (full) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              float4 q = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-              if (p.accumulate) {
-                const float4 old = reinterpret_cast<const float4*>(o)[i];
-                q.x += old.x; q.y += old.y; q.z += old.z; q.w += old.w;
-              }
-              reinterpret_cast<float4*>(o)[i] = q;
-            }
-          } else {
-            for (int i = 0; i < 32 && n0 + i < p.N; ++i) o[i] = p.accumulate ? o[i] + v[i] : v[i];
-          }
-        } else {
-          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.ldd + n0;
-          if (full) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              if (p.accumulate) {
-                const uint4 old = reinterpret_cast<const uint4*>(o)[i];
-                float2 f;
-                f = unpack_bf16x2(old.x); v[8 * i + 0] += f.x; v[8 * i + 1] += f.y;
-                f = unpack_bf16x2(old.y); v[8 * i + 2] += f.x; v[8 * i + 3] += f.y;
-                f = unpack_bf16x2(old.z); v[8 * i + 4] += f.x; v[8 * i + 5] += f.y;
-                f = unpack_bf16x2(old.w); v[8 * i + 6] += f.x; v[8 * i + 7] += f.y;
-              }
-              uint4 q;
-              q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
-              q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-              q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-              q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-              reinterpret_cast<uint4*>(o)[i] = q;
-            }
-          } else {
-            for (int i = 0; i < 32 && n0 + i < p.N; ++i) {
-              float w = v[i];
-              if (p.accumulate) w += __bfloat162float(o[i]);
-              o[i] = __float2bfloat16(w);
-            }
-          }
-        }
+        gemm_epilogue_chunk(p, row, n0, r, keep16, drop_scale);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -449,6 +315,14 @@ int launch_variant(const void* A, int lda, const void* B, int ldb, const GemmPar
 
 }  // namespace
 
+int gemm2_bf16_launch(const void* A, int lda, int a_mn_major, const void* B, int ldb, int b_mn_major,
+                      const GemmParams& p, int num_sms, cudaStream_t stream);
+
+// 0 = always the one-CTA kernel, 1 = two-SM kernel where the output has enough 256 x 256 tiles.
+static int g_pair_mode = 1;
+void gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
+int gemm_get_pair_mode() { return g_pair_mode; }
+
 // Launches the GEMM on `stream`.  Returns 0 or a CUDA / driver error code; argument errors are negative.
 int gemm_bf16_launch(const void* A, int lda, int a_mn_major, const void* B, int ldb, int b_mn_major,
                      const GemmParams& p, int num_sms, cudaStream_t stream) {
@@ -457,6 +331,11 @@ int gemm_bf16_launch(const void* A, int lda, int a_mn_major, const void* B, int 
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(p.D) & 15))
     return -4;
+  if (g_pair_mode) {
+    const int tiles_pair = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+    if (p.M >= 256 && p.N >= 256 && tiles_pair >= num_sms / 4)
+      return gemm2_bf16_launch(A, lda, a_mn_major, B, ldb, b_mn_major, p, num_sms, stream);
+  }
   // Narrow outputs use the 128-wide tile so fewer columns are wasted and more CTAs are busy.
   const int tiles256 = ((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
   const bool bn128 = (p.N <= 128) || (tiles256 < num_sms);

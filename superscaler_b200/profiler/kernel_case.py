@@ -1,0 +1,81 @@
+"""Runs ONE kernel family on a small, fixed case: the command to put under a kernel profiler, and a quick timing
+check.  Inputs exceed the L2 cache so that memory counters stay meaningful, but stay far below a GB.
+
+    python -m superscaler_b200.profiler.kernel_case gemm 16384 8192 2048 [--a-mn] [--b-mn] [--single]
+    python -m superscaler_b200.profiler.kernel_case attention 2 16 2048 128 [--dropout 0.1]
+
+Prints one line per kernel family: milliseconds per call (CUDA events, after warm-up) and TFLOP/s.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from ..ops import functional as F
+from ..ops import native
+
+
+def _time(fn, warmup: int, iters: int) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run_gemm(a) -> None:
+    ext = native.ext()
+    ext.gemm_set_pair_mode(0 if a.single else 1)
+    torch.manual_seed(0)
+    A = torch.randn((a.K, a.M) if a.a_mn else (a.M, a.K), device="cuda").bfloat16()
+    B = torch.randn((a.K, a.N) if a.b_mn else (a.N, a.K), device="cuda").bfloat16()
+    out = torch.empty(a.M, a.N, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: F.gemm(A, B, out, a_mn=a.a_mn, b_mn=a.b_mn), a.warmup, a.iters)
+    print(f"gemm {a.M}x{a.N}x{a.K} a_mn={a.a_mn} b_mn={a.b_mn} pair={not a.single}: {ms:.4f} ms "
+          f"{2 * a.M * a.N * a.K / ms / 1e9:.0f} TFLOP/s status {int(ext.status().item())}")
+
+
+def run_attention(a) -> None:
+    ext = native.ext()
+    B_, NH, S, HD = a.B, a.NH, a.S, a.HD
+    h = NH * HD
+    torch.manual_seed(0)
+    qkv = (torch.randn(B_ * S, 3 * h, device="cuda") * 0.5).bfloat16()
+    sc = HD ** -0.5
+    fwd = lambda: ext.attn_fwd(qkv, qkv, qkv, B_, NH, S, S, HD, 0, h, 2 * h, sc, True, None, a.dropout, 1234)
+    o, lse = fwd()
+    do = torch.randn_like(o)
+    dqkv = torch.empty_like(qkv)
+    bwd = lambda: ext.attn_bwd(qkv, qkv, qkv, o, lse, do, dqkv, dqkv, dqkv, B_, NH, S, S, HD, 0, h, 2 * h, 0, h, 2 * h,
+                               sc, True, None, a.dropout, 1234)
+    flops = 4 * B_ * NH * S * S * HD * 0.5    # causal
+    for name, fn, mult in (("fwd", fwd, 1.0), ("bwd", bwd, 2.5)):
+        ms = _time(fn, a.warmup, a.iters)
+        print(f"attention {name} B{B_} NH{NH} S{S} HD{HD} causal dropout={a.dropout}: {ms:.4f} ms "
+              f"{flops * mult / ms / 1e9:.0f} TFLOP/s status {int(ext.status().item())}")
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="kind", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("M", type=int), g.add_argument("N", type=int), g.add_argument("K", type=int)
+    g.add_argument("--a-mn", action="store_true"), g.add_argument("--b-mn", action="store_true")
+    g.add_argument("--single", action="store_true", help="one-CTA kernel only")
+    t = sub.add_parser("attention")
+    t.add_argument("B", type=int), t.add_argument("NH", type=int), t.add_argument("S", type=int)
+    t.add_argument("HD", type=int), t.add_argument("--dropout", type=float, default=0.0)
+    for p in (g, t):
+        p.add_argument("--warmup", type=int, default=3), p.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args(argv)
+    (run_gemm if a.kind == "gemm" else run_attention)(a)
+
+
+if __name__ == "__main__":
+    main()
