@@ -8,6 +8,7 @@
 
 #include "attention_sm100.cuh"
 #include "gemm_sm100.cuh"
+#include "gemm_ar_sm100.cuh"
 
 namespace ssb {
 int gemm_bf16_launch(const void* A, int lda, int a_mn_major, const void* B, int ldb, int b_mn_major,
@@ -540,6 +541,52 @@ void allreduce_scale_f32(const Tensor& peer_ptrs, int64_t mc_ptr, const Tensor& 
                "allreduce_scale_f32");
 }
 
+// out = bias / dropout / residual epilogue of the SUM over the tp ranks of (a . b^T), on every rank, in one kernel
+// (csrc/gemm_ar_sm100.cu).  partial_ptrs / result_ptrs / flag_ptrs: int64 device tensors [tp] with every rank's
+// address of the symmetric partial scratch, of this call's result buffer and of the flag table.
+void gemm_allreduce(const Tensor& a, const Tensor& b, bool b_mn, Tensor& d, const OptTensor& bias,
+                    const OptTensor& residual, double alpha, double dropout_p, int64_t seed, const Tensor& partial_ptrs,
+                    const Tensor& result_ptrs, const Tensor& flag_ptrs, int64_t partial_mc, int64_t rank, int64_t tp,
+                    int64_t epoch, int64_t max_tiles) {
+  check_bf16_2d(a, "a");
+  check_bf16_2d(b, "b");
+  check_bf16_2d(d, "d");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a.size(0), K = a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K, "gemm_allreduce: reduction sizes differ");
+  TORCH_CHECK(d.size(0) == M && d.size(1) == N, "gemm_allreduce: output must be [", M, ", ", N, "]");
+  for (const Tensor* t : {&partial_ptrs, &result_ptrs, &flag_ptrs})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kInt64 && t->numel() == tp, "pointer tables must be int64 [tp]");
+  ssb::GemmParams p{};
+  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
+  p.D = d.data_ptr(); p.ldd = static_cast<int>(d.stride(0));
+  p.alpha = static_cast<float>(alpha);
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "bias must be contiguous [N]");
+    TORCH_CHECK(bias->scalar_type() == torch::kBFloat16 || bias->scalar_type() == torch::kFloat32, "bias dtype");
+    p.bias = bias->data_ptr(); p.bias_fp32 = bias->scalar_type() == torch::kFloat32;
+  }
+  if (residual.has_value()) {
+    check_bf16_2d(*residual, "residual");
+    TORCH_CHECK(residual->size(0) == M && residual->size(1) == N && residual->stride(0) % 8 == 0, "residual shape");
+    p.residual = residual->data_ptr(); p.ldres = static_cast<int>(residual->stride(0));
+  }
+  p.dropout_p = static_cast<float>(dropout_p);
+  p.dropout_seed = static_cast<unsigned long long>(seed);
+  p.status = status_tensor().data_ptr<int>();
+  ssb::GemmArComm cm{};
+  cm.partial_ptrs = reinterpret_cast<const void* const*>(partial_ptrs.data_ptr<int64_t>());
+  cm.result_ptrs = reinterpret_cast<const void* const*>(result_ptrs.data_ptr<int64_t>());
+  cm.flag_ptrs = reinterpret_cast<uint32_t* const*>(flag_ptrs.data_ptr<int64_t>());
+  cm.partial_mc = reinterpret_cast<const void*>(partial_mc);
+  cm.rank = static_cast<int>(rank); cm.tp = static_cast<int>(tp);
+  cm.epoch = static_cast<uint32_t>(epoch); cm.max_tiles = static_cast<int>(max_tiles);
+  check_launch(ssb::gemm_ar_launch(a.data_ptr(), static_cast<int>(a.stride(0)), b.data_ptr(),
+                                   static_cast<int>(b.stride(0)), b_mn, p, cm, num_sms(), cur_stream()),
+               "gemm_allreduce");
+}
+
 int64_t comm_max_blocks() { return ssb::comm_max_blocks(); }
 
 Tensor status() { return status_tensor(); }
@@ -548,6 +595,7 @@ Tensor status() { return status_tensor(); }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("gemm_allreduce", &gemm_allreduce);
   m.def("gemm_set_pair_mode", &ssb::gemm_set_pair_mode);
   m.def("gemm_get_pair_mode", &ssb::gemm_get_pair_mode);
   m.def("layernorm_fwd", &layernorm_fwd);

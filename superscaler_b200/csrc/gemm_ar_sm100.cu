@@ -1,0 +1,457 @@
+// GEMM fused with the tensor-parallel all-reduce that follows it, in ONE persistent kernel over peer memory.
+//
+//   out = epilogue( sum over tp ranks r of  A_r . B_r^T )       (every rank ends up with the full `out`)
+//
+// Replaces RowParallelLinear.forward = F.linear + torch.distributed.all_reduce and the all-reduce of the
+// input gradient of ColumnParallelLinear (runtime/megatron/mpu/layers.py:459-470,593-604,
+// runtime/megatron/mpu/mappings.py:23-40 of the reference), which run the GEMM to completion and only then start
+// the collective.  Here the reduction of output tile t overlaps the tensor-core work of tile t+1:
+//
+//   warp 0      TMA producer                         (as in gemm_bf16_kernel)
+//   warp 1      TMEM allocator + MMA issuer
+//   warps 2..5  partial epilogue: accumulator -> bf16 partial tile in this rank's symmetric scratch, then one
+//               release-store per (tile, 32-row quarter) into the flag table of the tile's OWNER rank
+//   warps 6..9  collective: for a tile this rank owns (tile % tp == rank) wait until every rank's partial quarter
+//               is flagged, read the tp partials through the peer pointers (coalesced 512-byte rows; or ONE
+//               multimem.ld_reduce per 16 bytes when an NVLS multicast mapping of the scratch is given), apply bias /
+//               dropout / residual, write the final rows to the local output and to the local symmetric result
+//               buffer, and flag the quarter as final on every peer; for a tile owned by a peer wait for that flag
+//               and pull the final rows from the owner's result buffer into the local output.
+//
+// Traffic per rank is the two-shot optimum, 2 (tp-1)/tp x M x N x 2 bytes, all of it peer LOADS.
+// There is no grid-wide or cross-rank barrier: a rank leaves the kernel only after it pulled every tile it does
+// not own, i.e. after every owner finished reading this rank's partials; results alternate between two buffers
+// so that a rank that is one call ahead never overwrites rows a peer is still pulling.  Flags carry a
+// monotonically growing epoch, so they are never reset.  Every wait is bounded: on a timeout the kernel records
+// kStatusPeerTimeout and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_ar_sm100.cuh"
+#include "gemm_sm100.cuh"
+
+namespace ssb {
+
+int make_tma_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                     uint32_t box_rows, uint32_t box_cols);
+
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kThreads = 64 + 128 + 128;
+constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kGroupM = 8;
+constexpr uint64_t kPeerLimitNs = 20ull * 1000 * 1000 * 1000;
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait until *flag >= epoch.  Warp-uniform result.
+__device__ __forceinline__ bool wait_flag_warp(const uint32_t* flag, bool active, uint32_t epoch, volatile int* abort_flag,
+                                               int* status) {
+  bool ok = true;
+  if (active) {
+    ok = false;
+    uint64_t t0 = 0;
+    for (uint32_t it = 0; it < (1u << 30); ++it) {
+      if (ld_acquire_sys_u32(flag) >= epoch) { ok = true; break; }
+      if ((it & 1023u) == 1023u) {
+        if (*abort_flag) break;
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kPeerLimitNs) break;
+      }
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      if (status != nullptr) atomicMax(status, static_cast<int>(kStatusPeerTimeout));
+    }
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  __syncwarp();  // orders the other lanes' data reads after the polling lanes' acquire
+  return ok;
+}
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+
+struct TileCoord {
+  int m_blk, n_blk;
+};
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) {
+  const int per_group = kGroupM * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * kGroupM;
+  const int gsize = min(num_m - first_m, kGroupM);
+  const int in_group = tile - group * per_group;
+  TileCoord c;
+  c.m_blk = first_m + in_group % gsize;
+  c.n_blk = in_group / gsize;
+  return c;
+}
+
+// Final epilogue on 8 consecutive columns [n0, n0+8) of row `row`: bias, dropout, residual (see GemmParams).
+__device__ __forceinline__ uint4 final_epilogue8(const GemmParams& p, int row, int n0, float (&v)[8], uint32_t keep16,
+                                                 float drop_scale) {
+  if (p.bias != nullptr) {
+    if (p.bias_fp32) {
+      const float4 b0 = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + n0));
+      const float4 b1 = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + n0) + 1);
+      v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+      v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+    } else {
+      const uint4 q = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.bias) + n0));
+      float2 f;
+      f = unpack_bf16x2(q.x); v[0] += f.x; v[1] += f.y;
+      f = unpack_bf16x2(q.y); v[2] += f.x; v[3] += f.y;
+      f = unpack_bf16x2(q.z); v[4] += f.x; v[5] += f.y;
+      f = unpack_bf16x2(q.w); v[6] += f.x; v[7] += f.y;
+    }
+  }
+  if (p.dropout_p > 0.f) {
+    const uint64_t g0 = (static_cast<uint64_t>(row) * static_cast<uint64_t>(p.N) + n0) >> 2;
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      const uint32_t m = dropout_keep4(p.dropout_seed, g0 + g, keep16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[4 * g + i] = ((m >> i) & 1u) ? v[4 * g + i] * drop_scale : 0.f;
+    }
+  }
+  if (p.residual != nullptr) {
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.residual) +
+                                                         static_cast<size_t>(row) * p.ldres + n0));
+    float2 f;
+    f = unpack_bf16x2(q.x); v[0] += f.x; v[1] += f.y;
+    f = unpack_bf16x2(q.y); v[2] += f.x; v[3] += f.y;
+    f = unpack_bf16x2(q.z); v[4] += f.x; v[5] += f.y;
+    f = unpack_bf16x2(q.w); v[6] += f.x; v[7] += f.y;
+  }
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]);
+  o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]);
+  o.w = pack_bf16x2(v[6], v[7]);
+  return o;
+}
+
+template <bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+               const GemmParams p, const GemmArComm cm) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + kStages * kABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* tmem_full_bar = bars + 2 * kStages;
+  uint64_t* tmem_empty_bar = bars + 2 * kStages + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  // flag table of a rank: [max_tiles][tp][4] "partial quarter written", then [max_tiles][4] "quarter final"
+  const int part_flags_per_tile = cm.tp * 4;
+  const size_t final_base = static_cast<size_t>(cm.max_tiles) * part_flags_per_tile;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tmem_full_bar[s], 1);
+      mbar_init(&tmem_empty_bar[s], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, num_m, num_n);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+          uint8_t* sa = smem_a + stage * kABytes;
+          uint8_t* sb = smem_b + stage * kBBytes;
+          tma_load_2d(sa, &tma_a, &full_bar[stage], kb * BK, tc.m_blk * BM);
+          if (!B_MN) {
+            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * BK, tc.n_blk * BN);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (64 * BK * 2), &tma_b, &full_bar[stage], tc.n_blk * BN + c * 64, kb * BK);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        for (int s = 0; s < kStages; ++s) {
+          const uint32_t armed_phase = (s < stage) ? phase : (phase ^ 1);
+          for (uint32_t it = 0; it < (1u << 20); ++it)
+            if (mbar_try_wait(&full_bar[s], armed_phase)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, false, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+        const int acc = iter & 1;
+        if (!mbar_wait(&tmem_empty_bar[acc], ((iter >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem_a + stage * kABytes);
+          const uint32_t sb = smem_u32(smem_b + stage * kBBytes);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = umma_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? umma_desc_sw128(sb + k * 2048, 64 * BK * 2, 1024)
+                                     : umma_desc_sw128(sb + k * 32, 16, 1024);
+            umma_f16_ss(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full_bar[acc]);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------ partial epilogue: TMEM -> bf16 partial tile in the local scratch ------------------
+    const int quarter = warp & 3;
+    __nv_bfloat16* part = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(cm.partial_ptrs[cm.rank]));
+    int iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+      const TileCoord tc = tile_coord(tile, num_m, num_n);
+      const int acc = iter & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], (iter >> 1) & 1, abort_flag))) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = tc.m_blk * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int n0 = tc.n_blk * BN + c * 32;
+        if (n0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        __nv_bfloat16* o = part + static_cast<size_t>(row) * p.N + n0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 q;
+          q.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * p.alpha, __uint_as_float(r[8 * i + 1]) * p.alpha);
+          q.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * p.alpha, __uint_as_float(r[8 * i + 3]) * p.alpha);
+          q.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * p.alpha, __uint_as_float(r[8 * i + 5]) * p.alpha);
+          q.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * p.alpha, __uint_as_float(r[8 * i + 7]) * p.alpha);
+          reinterpret_cast<uint4*>(o)[i] = q;
+        }
+      }
+      tc_fence_before_sync();
+      __threadfence_system();  // this lane's partial rows are visible to every GPU before the flag
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&tmem_empty_bar[acc]);
+        const int owner = tile % cm.tp;
+        st_release_sys_u32(cm.flag_ptrs[owner] + static_cast<size_t>(tile) * part_flags_per_tile + cm.rank * 4 + quarter,
+                           cm.epoch);
+      }
+    }
+  } else {
+    // ----------------------------- collective warps -----------------------------
+    const int quarter = warp & 3;  // warps 6..9 -> quarters 2,3,0,1: any bijection works
+    const uint32_t keep16 = dropout_keep16(p.dropout_p);
+    const float drop_scale = p.dropout_p > 0.f ? 65536.0f / static_cast<float>(keep16) : 1.0f;
+    uint32_t* my_flags = cm.flag_ptrs[cm.rank];
+    __nv_bfloat16* my_result = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(cm.result_ptrs[cm.rank]));
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const TileCoord tc = tile_coord(tile, num_m, num_n);
+      const int owner = tile % cm.tp;
+      const int row0 = tc.m_blk * BM + quarter * 32;
+      const int col = tc.n_blk * BN + lane * 8;  // this lane's 8 columns of every row
+      const bool col_ok = col < p.N;             // N is a multiple of 8
+      const int rows = min(32, p.M - row0);      // may be <= 0 on the ragged edge
+      if (owner == cm.rank) {
+        ok = wait_flag_warp(my_flags + static_cast<size_t>(tile) * part_flags_per_tile + lane * 4 + quarter,
+                            lane < cm.tp, cm.epoch, abort_flag, p.status);
+        if (!ok) break;
+        constexpr int R = 8;  // rows in flight per lane: remote loads are latency-bound otherwise
+#pragma unroll 1
+        for (int rb = 0; rb < 32; rb += R) {
+          if (rb >= rows) break;
+          float v[R][8];
+          if (cm.partial_mc != nullptr) {
+            uint4 q[R];
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+              q[i] = make_uint4(0u, 0u, 0u, 0u);
+              if (col_ok && rb + i < rows)
+                q[i] = multimem_ld_reduce_bf16x8(reinterpret_cast<const __nv_bfloat16*>(cm.partial_mc) +
+                                                 static_cast<size_t>(row0 + rb + i) * p.N + col);
+            }
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+              float2 f;
+              f = unpack_bf16x2(q[i].x); v[i][0] = f.x; v[i][1] = f.y;
+              f = unpack_bf16x2(q[i].y); v[i][2] = f.x; v[i][3] = f.y;
+              f = unpack_bf16x2(q[i].z); v[i][4] = f.x; v[i][5] = f.y;
+              f = unpack_bf16x2(q[i].w); v[i][6] = f.x; v[i][7] = f.y;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+            for (int r = 0; r < cm.tp; ++r) {
+              const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(cm.partial_ptrs[r]);
+              uint4 q[R];
+#pragma unroll
+              for (int i = 0; i < R; ++i) {
+                q[i] = make_uint4(0u, 0u, 0u, 0u);
+                if (col_ok && rb + i < rows) q[i] = ld_nc_v4(src + static_cast<size_t>(row0 + rb + i) * p.N + col);
+              }
+#pragma unroll
+              for (int i = 0; i < R; ++i) {
+                float2 f;
+                f = unpack_bf16x2(q[i].x); v[i][0] += f.x; v[i][1] += f.y;
+                f = unpack_bf16x2(q[i].y); v[i][2] += f.x; v[i][3] += f.y;
+                f = unpack_bf16x2(q[i].z); v[i][4] += f.x; v[i][5] += f.y;
+                f = unpack_bf16x2(q[i].w); v[i][6] += f.x; v[i][7] += f.y;
+              }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < R; ++i) {
+            const int row = row0 + rb + i;
+            if (col_ok && rb + i < rows) {
+              const uint4 o = final_epilogue8(p, row, col, v[i], keep16, drop_scale);
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.ldd + col) = o;
+              *reinterpret_cast<uint4*>(my_result + static_cast<size_t>(row) * p.N + col) = o;
+            }
+          }
+        }
+        __threadfence_system();
+        __syncwarp();
+        if (lane < cm.tp && lane != cm.rank)
+          st_release_sys_u32(cm.flag_ptrs[lane] + final_base + static_cast<size_t>(tile) * 4 + quarter, cm.epoch);
+      } else {
+        ok = wait_flag_warp(my_flags + final_base + static_cast<size_t>(tile) * 4 + quarter, lane == 0, cm.epoch,
+                            abort_flag, p.status);
+        if (!ok) break;
+        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(cm.result_ptrs[owner]);
+        constexpr int R = 8;
+#pragma unroll 1
+        for (int rb = 0; rb < 32; rb += R) {
+          if (rb >= rows) break;
+          uint4 q[R];
+#pragma unroll
+          for (int i = 0; i < R; ++i)
+            if (col_ok && rb + i < rows) q[i] = ld_nc_v4(src + static_cast<size_t>(row0 + rb + i) * p.N + col);
+#pragma unroll
+          for (int i = 0; i < R; ++i)
+            if (col_ok && rb + i < rows)
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) +
+                                        static_cast<size_t>(row0 + rb + i) * p.ldd + col) = q[i];
+        }
+      }
+    }
+  }
+
+  // ------------------------------- teardown ----------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicMax(p.status, static_cast<int>(kStatusMbarTimeout));
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+}  // namespace
+
+// A [M][K] bf16 (K contiguous); B [N][K] (b_mn_major = 0) or [K][N] (1).  p describes the FINAL epilogue
+// (alpha, bias, dropout, residual) and the local bf16 output; activation / pre-activation / accumulate / fp32
+// outputs are not available in the fused form.  N must be a multiple of 32.
+int gemm_ar_launch(const void* A, int lda, const void* B, int ldb, int b_mn_major, const GemmParams& p,
+                   const GemmArComm& cm, int num_sms, cudaStream_t stream) {
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0 || (p.N % 32)) return -2;
+  if (p.act != kActNone || p.preact_out != nullptr || p.accumulate || p.out_fp32) return -2;
+  if ((lda % 8) || (ldb % 8) || (p.ldd % 8)) return -3;
+  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  if (num_tiles > cm.max_tiles || cm.tp < 1 || cm.tp > 32) return -6;
+  CUtensorMap ta, tb;
+  int rc = make_tma_2d_bf16(&ta, A, p.M, p.K, lda, BM, BK);
+  if (rc != 0) return rc;
+  rc = !b_mn_major ? make_tma_2d_bf16(&tb, B, p.N, p.K, ldb, BN, BK) : make_tma_2d_bf16(&tb, B, p.K, p.N, ldb, BK, 64);
+  if (rc != 0) return rc;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_ar_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_ar_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_done = true;
+  }
+  const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+  if (b_mn_major)
+    gemm_ar_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, p, cm);
+  else
+    gemm_ar_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, p, cm);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace ssb

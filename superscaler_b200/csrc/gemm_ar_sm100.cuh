@@ -1,0 +1,26 @@
+// Communication arguments of the fused GEMM + tensor-parallel all-reduce kernel (gemm_ar_sm100.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gemm_sm100.cuh"
+
+namespace ssb {
+
+struct GemmArComm {
+  const void* const* partial_ptrs;  // device array [tp]: bf16 [M x N] scratch of every rank (dense, ld = N)
+  const void* const* result_ptrs;   // device array [tp]: bf16 [M x N] result buffer of every rank (this call's parity)
+  uint32_t* const* flag_ptrs;       // device array [tp]: flag table of every rank
+  const void* partial_mc;           // multicast address of the partial scratch, or null
+  int rank, tp;
+  uint32_t epoch;                   // grows by 1 per call on every rank
+  int max_tiles;                    // capacity of the flag table (tiles)
+};
+
+// Size (in 32-bit words) of one rank's flag table for `max_tiles` output tiles of 128 x 256.
+inline long long gemm_ar_flag_words(int max_tiles, int tp) { return static_cast<long long>(max_tiles) * (tp * 4 + 4); }
+
+int gemm_ar_launch(const void* A, int lda, const void* B, int ldb, int b_mn_major, const GemmParams& p,
+                   const GemmArComm& cm, int num_sms, cudaStream_t stream);
+
+}  // namespace ssb

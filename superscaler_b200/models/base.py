@@ -40,6 +40,23 @@ class Env:
     micro_bs: int                    # stage-aggregate micro batch size of the plan
     fused_comm: bool = False         # use the in-kernel peer-memory collectives where available
     stage_ops: Sequence[OpInfo] = ()
+    tp_contexts: Dict[Tuple[int, ...], Any] = field(default_factory=dict)
+
+    def tp_context(self, pl: OpPlacement, local_bs: int):
+        """Symmetric scratch for the fused GEMM + all-reduce kernel of this op's tensor-parallel group, or None
+        when the NCCL path is to be used (tp == 1, CPU tensors, or fused communication switched off).  Created
+        on first use; all ranks of the group reach that point together because they execute the same plan."""
+        if not self.fused_comm or pl.tp == 1 or self.store.device.type != "cuda":
+            return None
+        key = tuple(pl.tp_ranks)
+        ctx = self.tp_contexts.get(key)
+        if ctx is None:
+            from ..parallel.symm import FusedTPContext
+            c = self.cfg
+            seq = max(getattr(c, "seq_length", 1), getattr(c, "dec_seq_length", 1))
+            ctx = FusedTPContext(self.group(pl.tp_ranks), local_bs * seq * c.hidden, self.store.device)
+            self.tp_contexts[key] = ctx
+        return ctx
 
     def placement(self, info: OpInfo) -> OpPlacement:
         return self.pstate.placement(info.tp, info.dp)
@@ -89,6 +106,9 @@ class Op:
     # -- execution ----------------------------------------------------------------------------
     def forward(self, st: Dict[str, torch.Tensor]) -> None:
         raise NotImplementedError
+
+    def tpctx(self):
+        return self.env.tp_context(self.pl, self.local_bs)
 
     def seed(self, sharded: bool = False) -> int:
         """Dropout seed: equal across a TP group for replicated tensors, distinct across DP ranks."""

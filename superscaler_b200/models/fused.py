@@ -86,6 +86,8 @@ class FusedDenseDropAdd(FusedGroup):
         x, res = st["x"], st.pop("residual")
         if self.pl.tp == 1:
             st["x"] = F.linear(x, w, b, residual=res, dropout_p=p_drop, seed=self.seed())
+        elif dense.info.algo == 0 and self.tpctx() is not None:
+            st["x"] = F.row_parallel_linear_fused(x, w, b, res, p_drop, self.seed(), self.tpctx())
         elif dense.info.algo == 0:
             y = M.reduce_from_group(F.linear(x, w, None), self.tp_group)
             st["x"] = F.bias_dropout_add(y, b, res, p_drop, self.seed())
@@ -99,7 +101,9 @@ class FusedUpAct(FusedGroup):
         up: MLPUpOp = self.members[0]
         w, b = up.p("dense_h_to_4h.weight"), up.p("dense_h_to_4h.bias")
         x = st["x"]
-        if up.info.algo == 0:
+        if up.info.algo == 0 and self.tpctx() is not None:
+            st["x"] = F.column_parallel_linear_fused(x, w, b, self.env.cfg.activation, self.tpctx())
+        elif up.info.algo == 0:
             st["x"] = F.linear(M.copy_to_group(x, self.tp_group), w, b, act=self.env.cfg.activation)
         else:
             y = M.reduce_from_group(F.linear(x, w, None), self.tp_group)
@@ -119,6 +123,9 @@ class FusedMLP(FusedGroup):
         x, res = st["x"], st.pop("residual")
         if self.pl.tp == 1:
             st["x"] = F.mlp(x, w1, b1, w2, b2, residual=res, act=c.activation, dropout_p=p_drop, seed=self.seed())
+        elif self.tpctx() is not None:
+            h = F.column_parallel_linear_fused(x, w1, b1, c.activation, self.tpctx())
+            st["x"] = F.row_parallel_linear_fused(h, w2, b2, res, p_drop, self.seed(), self.tpctx())
         else:
             h = F.linear(M.copy_to_group(x, self.tp_group), w1, b1, act=c.activation)
             y = M.reduce_from_group(F.linear(h, w2, None), self.tp_group)

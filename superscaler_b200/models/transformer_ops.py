@@ -123,7 +123,11 @@ class QKVOp(Op):
 
     def forward(self, st):
         x = st["x"]
-        if self.info.algo == 0:
+        if self.info.algo == 0 and self.kind == "self" and self.tpctx() is not None:
+            w = self.p("query_key_value.weight")
+            st["x"] = F.column_parallel_linear_fused(x, w.view(-1, w.shape[-1]), self.p("query_key_value.bias").view(-1),
+                                                     F.ACT_NONE, self.tpctx())
+        elif self.info.algo == 0:
             xin = M.copy_to_group(x, self.tp_group)
             if self.kind == "self":
                 w = self.p("query_key_value.weight")

@@ -204,6 +204,71 @@ def linear(x, weight, bias=None, residual=None, act=ACT_NONE, dropout_p=0.0, see
     return LinearFn.apply(x, weight, bias, residual, act, dropout_p, seed)
 
 
+class RowParallelLinearFusedFn(torch.autograd.Function):
+    """y = residual + dropout(all_reduce_tp(x_r W_r^T) + b) with the all-reduce INSIDE the GEMM kernel
+    (csrc/gemm_ar_sm100.cu).  Backward needs no collective: dx_r = g W_r, dW_r = g^T x_r with g the masked dy.
+
+    Reference counterpart: RowParallelLinear + reduce_from_tensor_model_parallel_region + bias-dropout-add
+    (runtime/megatron/mpu/layers.py:532-604, runtime/megatron/mpu/mappings.py:23-40)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual, dropout_p, seed, tpctx):
+        y = tpctx.linear_allreduce(x, weight, bias=bias, residual=residual, dropout_p=dropout_p, seed=seed)
+        ctx.save_for_backward(x, weight)
+        ctx.bias_ref = bias
+        ctx.has_res = residual is not None
+        ctx.dropout_p, ctx.seed = dropout_p, seed
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy = dy.contiguous()
+        dres = dy if ctx.has_res else None
+        g = dropout_bwd(dy, ctx.dropout_p, ctx.seed)
+        dx = gemm(g, weight, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(weight, g, x) if ctx.needs_input_grad[1] else None
+        db = _bgrad(ctx.bias_ref, g) if (ctx.bias_ref is not None and ctx.needs_input_grad[2]) else None
+        return dx, dw, db, dres, None, None, None
+
+
+def row_parallel_linear_fused(x, weight, bias, residual, dropout_p, seed, tpctx):
+    return RowParallelLinearFusedFn.apply(x, weight, bias, residual, dropout_p, seed, tpctx)
+
+
+class ColumnParallelLinearFusedFn(torch.autograd.Function):
+    """y_r = act(x W_r^T + b_r) on a replicated input; the backward all-reduce of the input gradient
+    (sum over the tp ranks of g_r W_r) runs inside the dgrad GEMM kernel.
+
+    Reference counterpart: copy_to_tensor_model_parallel_region + ColumnParallelLinear
+    (runtime/megatron/mpu/layers.py:459-470, runtime/megatron/mpu/mappings.py:79-93)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, act, tpctx):
+        need_pre = act in (ACT_GELU, ACT_RELU)
+        preact = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device) if need_pre else None
+        y = gemm(x, weight, bias=bias, act=act, preact_out=preact)
+        ctx.save_for_backward(x, weight, preact)
+        ctx.bias_ref, ctx.act, ctx.tpctx = bias, act, tpctx
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, preact = ctx.saved_tensors
+        g = dy.contiguous()
+        if ctx.act in (ACT_GELU, ACT_RELU):
+            op = EW_BIAS_GELU_BWD if ctx.act == ACT_GELU else EW_RELU_BWD
+            g = native.ext().elementwise(op, preact, g, None, 0.0, 0)
+        dx = ctx.tpctx.linear_allreduce(g, weight, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(weight, g, x) if ctx.needs_input_grad[1] else None
+        db = _bgrad(ctx.bias_ref, g) if (ctx.bias_ref is not None and ctx.needs_input_grad[2]) else None
+        return dx, dw, db, None, None
+
+
+def column_parallel_linear_fused(x, weight, bias, act, tpctx):
+    return ColumnParallelLinearFusedFn.apply(x, weight, bias, act, tpctx)
+
+
 class MLPFn(torch.autograd.Function):
     """y = residual + dropout(act(x W1^T + b1) W2^T + b2) with the activation derivative folded into the
     dgrad GEMM epilogue of the second layer (4 ops of the reference op list in 2 forward / 4 backward GEMMs:

@@ -28,3 +28,8 @@ def test_fused_allreduce_matches_nccl():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_dp_tp_pp_training_on_two_gpus():
     assert "TRAIN_OK" in _launch("train")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_gemm_allreduce_matches_gemm_plus_nccl():
+    assert "GEMM_AR_OK" in _launch("gemm_ar")
