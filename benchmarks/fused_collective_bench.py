@@ -65,8 +65,7 @@ def main():
     rank, world, local = init_distributed()
     dev = torch.device("cuda", local)
     peak_tf, peak_src = peaks()
-    ctx = FusedTPContext(None, max(a.mbs) * a.seq * max(a.hidden), dev)
-    mc_addr = ctx.partial_mc
+    ctx = FusedTPContext(None, max(a.mbs) * a.seq, max(a.hidden), dev)
     for h in a.hidden:
         for mbs in a.mbs:
             M, N, K = mbs * a.seq, h, 4 * h // world
@@ -88,10 +87,7 @@ def main():
             row = {"case": "gemm_allreduce", "tp": world, "M": M, "N": N, "K_per_rank": K}
             row["gemm_only_ms"] = timed(gemm_only, a.warmup, a.iters)
             row["nccl_path_ms"] = timed(nccl_path, a.warmup, a.iters)
-            for name, mc in (("fused_peer_ms", 0), ("fused_multimem_ms", mc_addr)):
-                if name == "fused_multimem_ms" and not mc_addr:
-                    continue
-                ctx.partial_mc = mc
+            for name in ("fused_ms",):
                 row[name] = timed(lambda: ctx.linear_allreduce(x, w, bias=bias, residual=res, dropout_p=0.1, seed=7,
                                                                out=out), a.warmup, a.iters)
             best = min(v for k, v in row.items() if k.startswith("fused_"))

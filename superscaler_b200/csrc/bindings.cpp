@@ -546,8 +546,8 @@ void allreduce_scale_f32(const Tensor& peer_ptrs, int64_t mc_ptr, const Tensor& 
 // address of the symmetric partial scratch, of this call's result buffer and of the flag table.
 void gemm_allreduce(const Tensor& a, const Tensor& b, bool b_mn, Tensor& d, const OptTensor& bias,
                     const OptTensor& residual, double alpha, double dropout_p, int64_t seed, const Tensor& partial_ptrs,
-                    const Tensor& result_ptrs, const Tensor& flag_ptrs, int64_t partial_mc, int64_t rank, int64_t tp,
-                    int64_t epoch, int64_t max_tiles) {
+                    const Tensor& result_ptrs, const Tensor& flag_ptrs, int64_t rank, int64_t tp,
+                    int64_t epoch, int64_t max_tiles, int64_t capacity_elems) {
   check_bf16_2d(a, "a");
   check_bf16_2d(b, "b");
   check_bf16_2d(d, "d");
@@ -579,7 +579,8 @@ void gemm_allreduce(const Tensor& a, const Tensor& b, bool b_mn, Tensor& d, cons
   cm.partial_ptrs = reinterpret_cast<const void* const*>(partial_ptrs.data_ptr<int64_t>());
   cm.result_ptrs = reinterpret_cast<const void* const*>(result_ptrs.data_ptr<int64_t>());
   cm.flag_ptrs = reinterpret_cast<uint32_t* const*>(flag_ptrs.data_ptr<int64_t>());
-  cm.partial_mc = reinterpret_cast<const void*>(partial_mc);
+  cm.capacity_elems = capacity_elems;
+
   cm.rank = static_cast<int>(rank); cm.tp = static_cast<int>(tp);
   cm.epoch = static_cast<uint32_t>(epoch); cm.max_tiles = static_cast<int>(max_tiles);
   check_launch(ssb::gemm_ar_launch(a.data_ptr(), static_cast<int>(a.stride(0)), b.data_ptr(),

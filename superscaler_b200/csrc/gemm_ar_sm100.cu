@@ -9,19 +9,24 @@
 //
 //   warp 0      TMA producer                         (as in gemm_bf16_kernel)
 //   warp 1      TMEM allocator + MMA issuer
-//   warps 2..5  partial epilogue: accumulator -> bf16 partial tile in this rank's symmetric scratch, then one
-//               release-store per (tile, 32-row quarter) into the flag table of the tile's OWNER rank
-//   warps 6..9  collective: for a tile this rank owns (tile % tp == rank) wait until every rank's partial quarter
-//               is flagged, read the tp partials through the peer pointers (coalesced 512-byte rows; or ONE
-//               multimem.ld_reduce per 16 bytes when an NVLS multicast mapping of the scratch is given), apply bias /
-//               dropout / residual, write the final rows to the local output and to the local symmetric result
-//               buffer, and flag the quarter as final on every peer; for a tile owned by a peer wait for that flag
-//               and pull the final rows from the owner's result buffer into the local output.
+//   warps 2..5  partial epilogue: accumulator -> bf16 -> a 2 KB staging buffer in shared memory -> bulk asynchronous
+//               copy (cp.async.bulk shared -> global) into the scratch of the tile's OWNER rank (tile % tp; the
+//               owner's own partial goes the same way into local memory), then one release-store per
+//               (tile, 32-row quarter) into the owner's flag table
+//   warps 6..9  collective: for a tile this rank owns, wait until every rank's partial quarter is flagged, add the
+//               tp partial tiles (all local by now), apply bias / dropout / residual, write the rows to the local
+//               output, stage them in shared memory and bulk-copy them into every peer's result buffer, then flag
+//               the quarter as final on every peer; for a tile owned by a peer, wait for that flag and copy the rows
+//               from the local result buffer into the local output.
 //
-// Traffic per rank is the two-shot optimum, 2 (tp-1)/tp x M x N x 2 bytes, all of it peer LOADS.
-// There is no grid-wide or cross-rank barrier: a rank leaves the kernel only after it pulled every tile it does
+// Everything that crosses NVLink is a bulk copy issued to the copy engine of the SM followed by a flag: no warp
+// waits for a remote load, and the load/store unit never queues remote stores.  (Measured on two B200: the same
+// kernel with ordinary remote stores, or with remote loads, took GEMM time PLUS transfer time, because remote
+// accesses queued in the load/store unit delay the local stores of the epilogue warps.)
+// Traffic per rank is the two-shot optimum, 2 (tp-1)/tp x M x N x 2 bytes.
+// There is no grid-wide or cross-rank barrier: a rank leaves the kernel only after it received every tile it does
 // not own, i.e. after every owner finished reading this rank's partials; results alternate between two buffers
-// so that a rank that is one call ahead never overwrites rows a peer is still pulling.  Flags carry a
+// so that an owner that is one call ahead never overwrites rows a peer is still copying.  Flags carry a
 // monotonically growing epoch, so they are never reset.  Every wait is bounded: on a timeout the kernel records
 // kStatusPeerTimeout and returns.
 #include <cuda.h>
@@ -42,8 +47,12 @@ constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int kStages = 4;
 constexpr int kThreads = 64 + 128 + 128;
 constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kChunkBytes = 32 * 32 * 2;            // one 32-row x 32-column bf16 piece of a partial tile
+constexpr int kStageEBytes = 4 * 2 * kChunkBytes;  // partial-epilogue staging: 4 warps x 2 buffers
+constexpr int kStageCBytes = 4 * 8 * BN * 2;        // collective staging: 4 warps x 8 rows x 512 B
+constexpr int kSmemBytes = kStages * kStageBytes + kStageEBytes + kStageCBytes + 1024 + 256;
 constexpr int kGroupM = 8;
+constexpr int kTileElems = BM * BN;
 constexpr uint64_t kPeerLimitNs = 20ull * 1000 * 1000 * 1000;
 
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
@@ -87,15 +96,13 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
                : "memory");
   return v;
 }
-__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
-  uint4 v;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
+// Asynchronous copy shared memory -> global memory (this GPU's or a peer's), tracked by the bulk async-group of the
+// issuing thread.  Both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_copy_s2g(void* gdst, const void* ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(ssrc)), "r"(bytes)
                : "memory");
-  return v;
 }
-
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 struct TileCoord {
   int m_blk, n_blk;
 };
@@ -163,7 +170,9 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kStages * kABytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint8_t* stage_e = smem + kStages * kStageBytes;
+  uint8_t* stage_c = stage_e + kStageEBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_c + kStageCBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
   uint64_t* tmem_full_bar = bars + 2 * kStages;
@@ -180,6 +189,7 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   // flag table of a rank: [max_tiles][tp][4] "partial quarter written", then [max_tiles][4] "quarter final"
   const int part_flags_per_tile = cm.tp * 4;
   const size_t final_base = static_cast<size_t>(cm.max_tiles) * part_flags_per_tile;
+  const int slots = (num_tiles + cm.tp - 1) / cm.tp;  // tiles owned by one rank
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -268,28 +278,34 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       }
     }
   } else if (warp < 6) {
-    // ------------------ partial epilogue: TMEM -> bf16 partial tile in the local scratch ------------------
+    // ---------- partial epilogue: TMEM -> bf16 -> staging in shared memory -> bulk copy into the owner's scratch ----------
     const int quarter = warp & 3;
-    __nv_bfloat16* part = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(cm.partial_ptrs[cm.rank]));
+    uint8_t* stage = stage_e + (warp - 2) * (2 * kChunkBytes);  // two 2 KB buffers per warp
     int iter = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
-      const TileCoord tc = tile_coord(tile, num_m, num_n);
       const int acc = iter & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], (iter >> 1) & 1, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
-      const int row = tc.m_blk * BM + quarter * 32 + lane;
-      const bool row_ok = row < p.M;
+      const int owner = tile % cm.tp;
+      // slot of this (source rank, tile) in the owner's scratch; inside a slot: [quarter][32-column chunk][32 rows][64 B]
+      uint8_t* dst = reinterpret_cast<uint8_t*>(const_cast<void*>(cm.partial_ptrs[owner])) +
+                     ((static_cast<size_t>(cm.rank) * slots + tile / cm.tp) * kTileElems) * 2 +
+                     static_cast<size_t>(quarter) * (32 * BN * 2);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
-        const int n0 = tc.n_blk * BN + c * 32;
-        if (n0 >= p.N) break;
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        if (!row_ok) continue;
-        __nv_bfloat16* o = part + static_cast<size_t>(row) * p.N + n0;
+        if (c == BN / 32 - 1) {  // the accumulator stage is free as soon as its last columns are in registers
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+        }
+        uint8_t* buf = stage + (c & 1) * kChunkBytes;
+        if (lane == 0) tma_store_wait_read<1>();  // the copy that last read this buffer has fetched it
+        __syncwarp();
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           uint4 q;
@@ -297,18 +313,23 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           q.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * p.alpha, __uint_as_float(r[8 * i + 3]) * p.alpha);
           q.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * p.alpha, __uint_as_float(r[8 * i + 5]) * p.alpha);
           q.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * p.alpha, __uint_as_float(r[8 * i + 7]) * p.alpha);
-          reinterpret_cast<uint4*>(o)[i] = q;
+          *reinterpret_cast<uint4*>(buf + lane * 64 + i * 16) = q;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          bulk_copy_s2g(dst + c * kChunkBytes, buf, kChunkBytes);
+          tma_store_commit();
         }
       }
-      tc_fence_before_sync();
-      __threadfence_system();  // this lane's partial rows are visible to every GPU before the flag
-      __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&tmem_empty_bar[acc]);
-        const int owner = tile % cm.tp;
+        tma_store_wait<0>();       // every chunk of this quarter has been written to the owner's memory
+        fence_proxy_async_all();
+        __threadfence_system();
         st_release_sys_u32(cm.flag_ptrs[owner] + static_cast<size_t>(tile) * part_flags_per_tile + cm.rank * 4 + quarter,
                            cm.epoch);
       }
+      __syncwarp();
     }
   } else {
     // ----------------------------- collective warps -----------------------------
@@ -316,7 +337,10 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const uint32_t keep16 = dropout_keep16(p.dropout_p);
     const float drop_scale = p.dropout_p > 0.f ? 65536.0f / static_cast<float>(keep16) : 1.0f;
     uint32_t* my_flags = cm.flag_ptrs[cm.rank];
-    __nv_bfloat16* my_result = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(cm.result_ptrs[cm.rank]));
+    const __nv_bfloat16* my_partial = reinterpret_cast<const __nv_bfloat16*>(cm.partial_ptrs[cm.rank]);
+    const __nv_bfloat16* my_result = reinterpret_cast<const __nv_bfloat16*>(cm.result_ptrs[cm.rank]);
+    constexpr int R = 8;  // rows per batch
+    uint8_t* stage = stage_c + (warp - 6) * (R * BN * 2);  // 4 KB per warp
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const TileCoord tc = tile_coord(tile, num_m, num_n);
@@ -329,78 +353,77 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         ok = wait_flag_warp(my_flags + static_cast<size_t>(tile) * part_flags_per_tile + lane * 4 + quarter,
                             lane < cm.tp, cm.epoch, abort_flag, p.status);
         if (!ok) break;
-        constexpr int R = 8;  // rows in flight per lane: remote loads are latency-bound otherwise
+        // partial slots are stored [quarter][chunk][row][64 B]: this lane's 8 columns sit in chunk lane / 4
+        const size_t slot_off = static_cast<size_t>(tile / cm.tp) * kTileElems + static_cast<size_t>(quarter) * (32 * BN) +
+                                (lane >> 2) * (32 * 32) + (lane & 3) * 8;
+        const size_t res_off = static_cast<size_t>(tile) * kTileElems + static_cast<size_t>(quarter) * (32 * BN);
 #pragma unroll 1
         for (int rb = 0; rb < 32; rb += R) {
           if (rb >= rows) break;
           float v[R][8];
-          if (cm.partial_mc != nullptr) {
+#pragma unroll
+          for (int i = 0; i < R; ++i)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+          for (int r = 0; r < cm.tp; ++r) {
+            const __nv_bfloat16* src = my_partial + static_cast<size_t>(r) * slots * kTileElems + slot_off;
             uint4 q[R];
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-              q[i] = make_uint4(0u, 0u, 0u, 0u);
-              if (col_ok && rb + i < rows)
-                q[i] = multimem_ld_reduce_bf16x8(reinterpret_cast<const __nv_bfloat16*>(cm.partial_mc) +
-                                                 static_cast<size_t>(row0 + rb + i) * p.N + col);
-            }
+            for (int i = 0; i < R; ++i) q[i] = ld_nc_v4(src + (rb + i) * 32);
 #pragma unroll
             for (int i = 0; i < R; ++i) {
               float2 f;
-              f = unpack_bf16x2(q[i].x); v[i][0] = f.x; v[i][1] = f.y;
-              f = unpack_bf16x2(q[i].y); v[i][2] = f.x; v[i][3] = f.y;
-              f = unpack_bf16x2(q[i].z); v[i][4] = f.x; v[i][5] = f.y;
-              f = unpack_bf16x2(q[i].w); v[i][6] = f.x; v[i][7] = f.y;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < R; ++i)
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
-            for (int r = 0; r < cm.tp; ++r) {
-              const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(cm.partial_ptrs[r]);
-              uint4 q[R];
-#pragma unroll
-              for (int i = 0; i < R; ++i) {
-                q[i] = make_uint4(0u, 0u, 0u, 0u);
-                if (col_ok && rb + i < rows) q[i] = ld_nc_v4(src + static_cast<size_t>(row0 + rb + i) * p.N + col);
-              }
-#pragma unroll
-              for (int i = 0; i < R; ++i) {
-                float2 f;
-                f = unpack_bf16x2(q[i].x); v[i][0] += f.x; v[i][1] += f.y;
-                f = unpack_bf16x2(q[i].y); v[i][2] += f.x; v[i][3] += f.y;
-                f = unpack_bf16x2(q[i].z); v[i][4] += f.x; v[i][5] += f.y;
-                f = unpack_bf16x2(q[i].w); v[i][6] += f.x; v[i][7] += f.y;
-              }
+              f = unpack_bf16x2(q[i].x); v[i][0] += f.x; v[i][1] += f.y;
+              f = unpack_bf16x2(q[i].y); v[i][2] += f.x; v[i][3] += f.y;
+              f = unpack_bf16x2(q[i].z); v[i][4] += f.x; v[i][5] += f.y;
+              f = unpack_bf16x2(q[i].w); v[i][6] += f.x; v[i][7] += f.y;
             }
           }
+          if (lane == 0) tma_store_wait_read<0>();  // the previous batch has left the staging buffer
+          __syncwarp();
 #pragma unroll
           for (int i = 0; i < R; ++i) {
             const int row = row0 + rb + i;
+            uint4 o = make_uint4(0u, 0u, 0u, 0u);
             if (col_ok && rb + i < rows) {
-              const uint4 o = final_epilogue8(p, row, col, v[i], keep16, drop_scale);
+              o = final_epilogue8(p, row, col, v[i], keep16, drop_scale);
               *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.ldd + col) = o;
-              *reinterpret_cast<uint4*>(my_result + static_cast<size_t>(row) * p.N + col) = o;
             }
+            *reinterpret_cast<uint4*>(stage + i * (BN * 2) + lane * 16) = o;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            // push the batch (8 rows x 512 B, contiguous in the row-major result tile) to every peer
+            for (int pr = 0; pr < cm.tp; ++pr)
+              if (pr != cm.rank)
+                bulk_copy_s2g(reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(cm.result_ptrs[pr])) + res_off +
+                                  static_cast<size_t>(rb) * BN,
+                              stage, R * BN * 2);
+            tma_store_commit();
           }
         }
-        __threadfence_system();
+        if (lane == 0) {
+          tma_store_wait<0>();
+          fence_proxy_async_all();
+          __threadfence_system();
+          for (int pr = 0; pr < cm.tp; ++pr)
+            if (pr != cm.rank)
+              st_release_sys_u32(cm.flag_ptrs[pr] + final_base + static_cast<size_t>(tile) * 4 + quarter, cm.epoch);
+        }
         __syncwarp();
-        if (lane < cm.tp && lane != cm.rank)
-          st_release_sys_u32(cm.flag_ptrs[lane] + final_base + static_cast<size_t>(tile) * 4 + quarter, cm.epoch);
       } else {
         ok = wait_flag_warp(my_flags + final_base + static_cast<size_t>(tile) * 4 + quarter, lane == 0, cm.epoch,
                             abort_flag, p.status);
         if (!ok) break;
-        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(cm.result_ptrs[owner]);
-        constexpr int R = 8;
+        const __nv_bfloat16* src = my_result + static_cast<size_t>(tile) * kTileElems +
+                                   static_cast<size_t>(quarter * 32) * BN + lane * 8;
 #pragma unroll 1
         for (int rb = 0; rb < 32; rb += R) {
           if (rb >= rows) break;
           uint4 q[R];
 #pragma unroll
-          for (int i = 0; i < R; ++i)
-            if (col_ok && rb + i < rows) q[i] = ld_nc_v4(src + static_cast<size_t>(row0 + rb + i) * p.N + col);
+          for (int i = 0; i < R; ++i) q[i] = ld_nc_v4(src + static_cast<size_t>(rb + i) * BN);
 #pragma unroll
           for (int i = 0; i < R; ++i)
             if (col_ok && rb + i < rows)
@@ -409,6 +432,7 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         }
       }
     }
+    if (lane == 0) tma_store_wait<0>();
   }
 
   // ------------------------------- teardown ----------------------------------
@@ -433,6 +457,7 @@ int gemm_ar_launch(const void* A, int lda, const void* B, int ldb, int b_mn_majo
   if ((lda % 8) || (ldb % 8) || (p.ldd % 8)) return -3;
   const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   if (num_tiles > cm.max_tiles || cm.tp < 1 || cm.tp > 32) return -6;
+  if (static_cast<long long>(num_tiles + cm.tp) * kTileElems > cm.capacity_elems) return -6;
   CUtensorMap ta, tb;
   int rc = make_tma_2d_bf16(&ta, A, p.M, p.K, lda, BM, BK);
   if (rc != 0) return rc;

@@ -8,13 +8,14 @@
 namespace ssb {
 
 struct GemmArComm {
-  const void* const* partial_ptrs;  // device array [tp]: bf16 [M x N] scratch of every rank (dense, ld = N)
-  const void* const* result_ptrs;   // device array [tp]: bf16 [M x N] result buffer of every rank (this call's parity)
-  uint32_t* const* flag_ptrs;       // device array [tp]: flag table of every rank
-  const void* partial_mc;           // multicast address of the partial scratch, or null
+  // device arrays [tp] with every rank's address of the same symmetric buffer:
+  const void* const* partial_ptrs;  // bf16 [tp source ranks][tiles / tp][4 quarters][8 chunks][32 rows][32 cols]: partial tiles pushed by every rank
+  const void* const* result_ptrs;   // bf16 [tiles][128 x 256]: final tiles pushed by their owners (this call's parity)
+  uint32_t* const* flag_ptrs;       // flag table
   int rank, tp;
   uint32_t epoch;                   // grows by 1 per call on every rank
   int max_tiles;                    // capacity of the flag table (tiles)
+  long long capacity_elems;         // elements in each of the partial / result buffers
 };
 
 // Size (in 32-bit words) of one rank's flag table for `max_tiles` output tiles of 128 x 256.

@@ -54,7 +54,7 @@ class Env:
             from ..parallel.symm import FusedTPContext
             c = self.cfg
             seq = max(getattr(c, "seq_length", 1), getattr(c, "dec_seq_length", 1))
-            ctx = FusedTPContext(self.group(pl.tp_ranks), local_bs * seq * c.hidden, self.store.device)
+            ctx = FusedTPContext(self.group(pl.tp_ranks), local_bs * seq, c.hidden, self.store.device)
             self.tp_contexts[key] = ctx
         return ctx
 

@@ -59,43 +59,42 @@ class SymmetricBuffer:
 
 class FusedTPContext:
     """Symmetric scratch of one tensor-parallel group for the fused GEMM + all-reduce kernel
-    (csrc/gemm_ar_sm100.cu): a bf16 partial buffer, two alternating result buffers and the flag table, each
-    rendezvoused once; `linear_allreduce` launches the kernel.  All ranks of the group must issue the same
-    sequence of calls (shapes included), which SPMD execution of one plan guarantees."""
+    (csrc/gemm_ar_sm100.cu): a bf16 buffer that receives the partial tiles this rank owns, two alternating result
+    buffers that receive the final tiles of the other owners, and the flag table, each rendezvoused once;
+    `linear_allreduce` launches the kernel.  All ranks of the group must issue the same sequence of calls
+    (shapes included), which SPMD execution of one plan guarantees."""
 
     TILE_M, TILE_N = 128, 256
 
-    def __init__(self, group, max_elems: int, device, max_tiles: Optional[int] = None):
+    def __init__(self, group, max_rows: int, max_cols: int, device):
         import torch.distributed._symmetric_memory as symm
         self.group = group if group is not None else dist.group.WORLD
         self.tp = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.device = device
-        self.max_elems = int(max_elems)
-        self.max_tiles = int(max_tiles or (max_elems // (self.TILE_M * self.TILE_N) * 4 + 1024))
+        tiles = -(-max_rows // self.TILE_M) * -(-max_cols // self.TILE_N)
+        self.max_tiles = tiles
+        self.capacity = (tiles + self.tp) * self.TILE_M * self.TILE_N     # buffers hold whole (padded) tiles
         name = self.group.group_name
 
         def table(t):
             h = symm.rendezvous(t, name)
             return h, torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=device)
 
-        self.partial = symm.empty(self.max_elems, dtype=torch.bfloat16, device=device)
-        self.results = [symm.empty(self.max_elems, dtype=torch.bfloat16, device=device) for _ in range(2)]
+        self.partial = symm.empty(self.capacity, dtype=torch.bfloat16, device=device)
+        self.results = [symm.empty(self.capacity, dtype=torch.bfloat16, device=device) for _ in range(2)]
         self.flags = symm.empty(self.max_tiles * (self.tp * 4 + 4), dtype=torch.int32, device=device)
         self.flags.zero_()
-        self.partial_handle, self.partial_ptrs = table(self.partial)
-        self.result_ptrs = [table(r)[1] for r in self.results]
+        _, self.partial_ptrs = table(self.partial)
+        handles = [table(r) for r in self.results]
+        self.result_ptrs = [h[1] for h in handles]
         _, self.flag_ptrs = table(self.flags)
-        mc = 0
-        if os.environ.get("SSB_DISABLE_MULTIMEM", "0") != "1":
-            try:
-                mc = int(self.partial_handle.multicast_ptr or 0)
-            except Exception:  # noqa: BLE001 - no multicast support on this fabric
-                mc = 0
-        self.partial_mc = mc
         self.epoch = 0
         torch.cuda.synchronize(device)
         dist.barrier(self.group)
+
+    def fits(self, rows: int, cols: int) -> bool:
+        return -(-rows // self.TILE_M) * -(-cols // self.TILE_N) <= self.max_tiles
 
     def linear_allreduce(self, x: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, bias=None, residual=None,
                          alpha: float = 1.0, dropout_p: float = 0.0, seed: int = 0, out=None) -> torch.Tensor:
@@ -103,11 +102,12 @@ class FusedTPContext:
         from ..ops import native
         M = x.shape[0]
         N = w.shape[1] if b_mn else w.shape[0]
-        assert M * N <= self.max_elems, f"fused TP scratch too small: {M}x{N} > {self.max_elems}"
+        assert self.fits(M, N), f"fused TP scratch too small for {M}x{N}"
         if out is None:
             out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
         self.epoch += 1
+        par = self.epoch & 1
         native.ext().gemm_allreduce(x, w, b_mn, out, bias, residual, alpha, dropout_p, seed, self.partial_ptrs,
-                                    self.result_ptrs[self.epoch & 1], self.flag_ptrs, self.partial_mc, self.rank,
-                                    self.tp, self.epoch, self.max_tiles)
+                                    self.result_ptrs[par], self.flag_ptrs, self.rank, self.tp, self.epoch,
+                                    self.max_tiles, self.capacity)
         return out
