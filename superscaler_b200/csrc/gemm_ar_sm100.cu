@@ -13,11 +13,13 @@
 //               copy (cp.async.bulk shared -> global) into the scratch of the tile's OWNER rank (tile % tp; the
 //               owner's own partial goes the same way into local memory), then one release-store per
 //               (tile, 32-row quarter) into the owner's flag table
-//   warps 6..9  collective: for a tile this rank owns, wait until every rank's partial quarter is flagged, add the
+//   warps 6..9  owner role: for a tile this rank owns, wait until every rank's partial quarter is flagged, add the
 //               tp partial tiles (all local by now), apply bias / dropout / residual, write the rows to the local
 //               output, stage them in shared memory and bulk-copy them into every peer's result buffer, then flag
-//               the quarter as final on every peer; for a tile owned by a peer, wait for that flag and copy the rows
-//               from the local result buffer into the local output.
+//               the quarter as final on every peer
+//   warps 10..13 receiver role: for a tile owned by a peer, wait for that flag and copy the rows from the local
+//               result buffer into the local output.  (Two separate warp sets: with one set the ranks took turns,
+//               each waiting for the other's owner work before starting its own.)
 //
 // Everything that crosses NVLink is a bulk copy issued to the copy engine of the SM followed by a flag: no warp
 // waits for a remote load, and the load/store unit never queues remote stores.  (Measured on two B200: the same
@@ -28,7 +30,10 @@
 // not own, i.e. after every owner finished reading this rank's partials; results alternate between two buffers
 // so that an owner that is one call ahead never overwrites rows a peer is still copying.  Flags carry a
 // monotonically growing epoch, so they are never reset.  Every wait is bounded: on a timeout the kernel records
-// kStatusPeerTimeout and returns.
+// kStatusPeerTimeout and returns.  The signalling store is a plain st.release.sys after cp.async.bulk.wait_group 0:
+// an extra __threadfence_system() in front of it cost 10-25 us per tile while TMA loads were in flight.
+// Built with -DSSB_AR_TRACE the kernel records %globaltimer at its hand-over points for the first 16 tiles of every CTA
+// into a buffer set with ssb_ar_set_trace() (a development aid; off in normal builds).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -45,7 +50,7 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int kStages = 4;
-constexpr int kThreads = 64 + 128 + 128;
+constexpr int kThreads = 64 + 128 + 128 + 128;  // TMA, MMA | partial epilogue | owner role | receiver role
 constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
 constexpr int kChunkBytes = 32 * 32 * 2;            // one 32-row x 32-column bf16 piece of a partial tile
 constexpr int kStageEBytes = 4 * 2 * kChunkBytes;  // partial-epilogue staging: 4 warps x 2 buffers
@@ -102,7 +107,13 @@ __device__ __forceinline__ void bulk_copy_s2g(void* gdst, const void* ssrc, uint
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(ssrc)), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+#ifdef SSB_AR_TRACE
+__device__ unsigned long long* g_trace = nullptr;  // [cta][tile iter][16 events]
+#define TRACE(ev) do { if (g_trace && lane == 0 && (warp == 2 || warp == 8 || warp == 12) && titer < 16) g_trace[(blockIdx.x * 16 + titer) * 16 + (ev)] = global_timer_ns(); } while (0)
+#else
+#define TRACE(ev) do {} while (0)
+#endif
+
 struct TileCoord {
   int m_blk, n_blk;
 };
@@ -190,6 +201,11 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const int part_flags_per_tile = cm.tp * 4;
   const size_t final_base = static_cast<size_t>(cm.max_tiles) * part_flags_per_tile;
   const int slots = (num_tiles + cm.tp - 1) / cm.tp;  // tiles owned by one rank
+  // Owner of a tile: inside every group of tp consecutive tiles the owners are a rotation of 0..tp-1 (so slot =
+  // tile / tp is unique per owner), and the rotation advances once per sweep of the grid, so a CTA alternates
+  // between owned and foreign tiles instead of owning all of its tiles.
+  const int rot_div = max(1, cm.grid / cm.tp);
+  auto owner_of = [&](int tile) { return (tile % cm.tp + (tile / cm.tp) / rot_div) % cm.tp; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -287,7 +303,9 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const int acc = iter & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], (iter >> 1) & 1, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
-      const int owner = tile % cm.tp;
+      const int titer = iter;
+      TRACE(0);
+      const int owner = owner_of(tile);
       // slot of this (source rank, tile) in the owner's scratch; inside a slot: [quarter][32-column chunk][32 rows][64 B]
       uint8_t* dst = reinterpret_cast<uint8_t*>(const_cast<void*>(cm.partial_ptrs[owner])) +
                      ((static_cast<size_t>(cm.rank) * slots + tile / cm.tp) * kTileElems) * 2 +
@@ -322,12 +340,13 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           tma_store_commit();
         }
       }
+      TRACE(8);
       if (lane == 0) {
         tma_store_wait<0>();       // every chunk of this quarter has been written to the owner's memory
-        fence_proxy_async_all();
-        __threadfence_system();
+        TRACE(9);
         st_release_sys_u32(cm.flag_ptrs[owner] + static_cast<size_t>(tile) * part_flags_per_tile + cm.rank * 4 + quarter,
                            cm.epoch);
+        TRACE(1);
       }
       __syncwarp();
     }
@@ -340,19 +359,25 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const __nv_bfloat16* my_partial = reinterpret_cast<const __nv_bfloat16*>(cm.partial_ptrs[cm.rank]);
     const __nv_bfloat16* my_result = reinterpret_cast<const __nv_bfloat16*>(cm.result_ptrs[cm.rank]);
     constexpr int R = 8;  // rows per batch
-    uint8_t* stage = stage_c + (warp - 6) * (R * BN * 2);  // 4 KB per warp
+    const bool owner_role = warp < 10;  // warps 6..9 reduce and publish owned tiles, warps 10..13 receive foreign ones
+    uint8_t* stage = stage_c + (quarter) * (R * BN * 2);  // 4 KB per owner-role warp
     bool ok = true;
+    int titer = -1;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      ++titer;
+      TRACE(2);
       const TileCoord tc = tile_coord(tile, num_m, num_n);
-      const int owner = tile % cm.tp;
+      const int owner = owner_of(tile);
       const int row0 = tc.m_blk * BM + quarter * 32;
       const int col = tc.n_blk * BN + lane * 8;  // this lane's 8 columns of every row
       const bool col_ok = col < p.N;             // N is a multiple of 8
       const int rows = min(32, p.M - row0);      // may be <= 0 on the ragged edge
-      if (owner == cm.rank) {
+      if ((owner == cm.rank) != owner_role) continue;
+      if (owner_role) {
         ok = wait_flag_warp(my_flags + static_cast<size_t>(tile) * part_flags_per_tile + lane * 4 + quarter,
                             lane < cm.tp, cm.epoch, abort_flag, p.status);
         if (!ok) break;
+        TRACE(3);
         // partial slots are stored [quarter][chunk][row][64 B]: this lane's 8 columns sit in chunk lane / 4
         const size_t slot_off = static_cast<size_t>(tile / cm.tp) * kTileElems + static_cast<size_t>(quarter) * (32 * BN) +
                                 (lane >> 2) * (32 * 32) + (lane & 3) * 8;
@@ -379,8 +404,10 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               f = unpack_bf16x2(q[i].w); v[i][6] += f.x; v[i][7] += f.y;
             }
           }
+          if (rb == 0) TRACE(5);
           if (lane == 0) tma_store_wait_read<0>();  // the previous batch has left the staging buffer
           __syncwarp();
+          if (rb == 8) TRACE(6);
 #pragma unroll
           for (int i = 0; i < R; ++i) {
             const int row = row0 + rb + i;
@@ -403,19 +430,21 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             tma_store_commit();
           }
         }
+        TRACE(7);
         if (lane == 0) {
           tma_store_wait<0>();
-          fence_proxy_async_all();
-          __threadfence_system();
+          TRACE(11);
           for (int pr = 0; pr < cm.tp; ++pr)
             if (pr != cm.rank)
               st_release_sys_u32(cm.flag_ptrs[pr] + final_base + static_cast<size_t>(tile) * 4 + quarter, cm.epoch);
+          TRACE(4);
         }
         __syncwarp();
       } else {
         ok = wait_flag_warp(my_flags + final_base + static_cast<size_t>(tile) * 4 + quarter, lane == 0, cm.epoch,
                             abort_flag, p.status);
         if (!ok) break;
+        TRACE(5);
         const __nv_bfloat16* src = my_result + static_cast<size_t>(tile) * kTileElems +
                                    static_cast<size_t>(quarter * 32) * BN + lane * 8;
 #pragma unroll 1
@@ -430,6 +459,7 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) +
                                         static_cast<size_t>(row0 + rb + i) * p.ldd + col) = q[i];
         }
+        TRACE(6);
       }
     }
     if (lane == 0) tma_store_wait<0>();
@@ -446,6 +476,12 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 }
 
 }  // namespace
+
+#ifdef SSB_AR_TRACE
+extern "C" int ssb_ar_set_trace(unsigned long long* buf) {
+  return (int)cudaMemcpyToSymbol(g_trace, &buf, sizeof(buf));
+}
+#endif
 
 // A [M][K] bf16 (K contiguous); B [N][K] (b_mn_major = 0) or [K][N] (1).  p describes the FINAL epilogue
 // (alpha, bias, dropout, residual) and the local bf16 output; activation / pre-activation / accumulate / fp32
@@ -472,10 +508,12 @@ int gemm_ar_launch(const void* A, int lda, const void* B, int ldb, int b_mn_majo
     attr_done = true;
   }
   const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+  GemmArComm c2 = cm;
+  c2.grid = grid;  // the same on every rank: it enters the tile -> owner map
   if (b_mn_major)
-    gemm_ar_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, p, cm);
+    gemm_ar_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, p, c2);
   else
-    gemm_ar_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, p, cm);
+    gemm_ar_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, p, c2);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -16,6 +16,7 @@ struct GemmArComm {
   uint32_t epoch;                   // grows by 1 per call on every rank
   int max_tiles;                    // capacity of the flag table (tiles)
   long long capacity_elems;         // elements in each of the partial / result buffers
+  int grid;                         // filled by the launcher: CTAs of the launch (equal on all ranks)
 };
 
 // Size (in 32-bit words) of one rank's flag table for `max_tiles` output tiles of 128 x 256.
