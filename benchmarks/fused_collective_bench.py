@@ -1,5 +1,9 @@
-"""Fused compute + collective micro-benchmark: GEMM -> all-reduce in one kernel (csrc/gemm_ar_sm100.cu) against
-the same GEMM followed by an NCCL all-reduce and the bias / dropout / residual kernel.
+"""Fused compute + collective micro-benchmark.
+
+  gemm_allreduce : GEMM -> all-reduce in one kernel (csrc/gemm_ar_sm100.cu) against the same GEMM followed by an
+                   NCCL all-reduce and the bias / dropout / residual kernel;
+  allgather_gemm : all-gather -> GEMM in one kernel (csrc/gemm_ag_sm100.cu) against an NCCL all-gather followed by
+                   the same GEMM (activations [mbs x 2048 / tp rows per rank, hidden] times [4 x hidden / tp, hidden]).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         benchmarks/fused_collective_bench.py [--mbs 1 4 8] [--hidden 2048 4096 8192] [--iters 20]
@@ -98,6 +102,38 @@ def main():
                        roofline_ms=max(t_flops, t_link), roofline_fraction=max(t_flops, t_link) / best,
                        speedup_vs_nccl_path=row["nccl_path_ms"] / best, gemm_peak=f"{peak_tf} TFLOP/s ({peak_src})",
                        kernel_status=native.check_status())
+            if rank == 0:
+                print(json.dumps(row), flush=True)
+    # ---- all-gather -> GEMM -----------------------------------------------------------------------------
+    ctx.enable_allgather(max(a.mbs) * a.seq, max(a.hidden))
+    for h in a.hidden:
+        for mbs in a.mbs:
+            M, N, K = mbs * a.seq, 4 * h // world, h
+            if (M // world) % 128:
+                continue
+            g = torch.Generator(device=dev).manual_seed(99 + rank)
+            x = torch.randn(M // world, K, device=dev, generator=g).bfloat16()
+            w = (torch.randn(N, K, device=dev, generator=g) * 0.02).bfloat16()
+            bias = torch.zeros(N, device=dev, dtype=torch.bfloat16)
+            full = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+
+            def nccl_path():
+                dist.all_gather_into_tensor(full, x)
+                return F.gemm(full, w, out, bias=bias, act=F.ACT_GELU)
+
+            row = {"case": "allgather_gemm", "tp": world, "M": M, "N_per_rank": N, "K": K}
+            row["gemm_only_ms"] = timed(lambda: F.gemm(full, w, out, bias=bias, act=F.ACT_GELU), a.warmup, a.iters)
+            row["nccl_path_ms"] = timed(nccl_path, a.warmup, a.iters)
+            row["fused_ms"] = timed(lambda: ctx.allgather_linear(x, w, bias=bias, act=F.ACT_GELU, out=out), a.warmup,
+                                    a.iters)
+            nv_bytes = (world - 1) / world * M * K * 2          # received (and sent) per GPU
+            t_flops = 2 * M * N * K / (peak_tf * 1e12) * 1e3
+            t_link = nv_bytes / (LINK_GBS * 1e9) * 1e3
+            row.update(nvlink_bytes_per_gpu=int(nv_bytes), fused_gbs=nv_bytes / row["fused_ms"] / 1e6,
+                       roofline_ms=max(t_flops, t_link), roofline_fraction=max(t_flops, t_link) / row["fused_ms"],
+                       speedup_vs_nccl_path=row["nccl_path_ms"] / row["fused_ms"],
+                       gemm_peak=f"{peak_tf} TFLOP/s ({peak_src})", kernel_status=native.check_status())
             if rank == 0:
                 print(json.dumps(row), flush=True)
     dist.barrier()

@@ -9,6 +9,7 @@
 #include "attention_sm100.cuh"
 #include "gemm_sm100.cuh"
 #include "gemm_ar_sm100.cuh"
+#include "gemm_ag_sm100.cuh"
 
 namespace ssb {
 int gemm_bf16_launch(const void* A, int lda, int a_mn_major, const void* B, int ldb, int b_mn_major,
@@ -588,6 +589,48 @@ void gemm_allreduce(const Tensor& a, const Tensor& b, bool b_mn, Tensor& d, cons
                "gemm_allreduce");
 }
 
+// y = epilogue(concat over the tp ranks of x_r . w^T) in one kernel (csrc/gemm_ag_sm100.cu).  x: this rank's rows
+// [M / tp, K]; gather_ptrs / flag_ptrs: int64 device tensors [tp]; gather_local: this rank's gather buffer address.
+void allgather_gemm(const Tensor& x, const Tensor& w, Tensor& d, const OptTensor& bias, int64_t act,
+                    const OptTensor& preact_out, const Tensor& gather_ptrs, int64_t gather_local, const Tensor& flag_ptrs,
+                    int64_t rank, int64_t tp, int64_t epoch, int64_t max_blocks, int64_t capacity_elems) {
+  check_bf16_2d(x, "x");
+  check_bf16_2d(w, "w");
+  check_bf16_2d(d, "d");
+  TORCH_CHECK(x.is_contiguous(), "x must be dense");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t M = x.size(0) * tp, K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K, "allgather_gemm: reduction sizes differ");
+  TORCH_CHECK(d.size(0) == M && d.size(1) == N, "allgather_gemm: output must be [", M, ", ", N, "]");
+  for (const Tensor* t : {&gather_ptrs, &flag_ptrs})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kInt64 && t->numel() == tp, "pointer tables must be int64 [tp]");
+  ssb::GemmParams p{};
+  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
+  p.D = d.data_ptr(); p.ldd = static_cast<int>(d.stride(0));
+  p.alpha = 1.0f;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "bias must be contiguous [N]");
+    p.bias = bias->data_ptr(); p.bias_fp32 = bias->scalar_type() == torch::kFloat32;
+  }
+  p.act = static_cast<int>(act);
+  if (preact_out.has_value()) {
+    check_bf16_2d(*preact_out, "preact_out");
+    TORCH_CHECK(preact_out->size(0) == M && preact_out->size(1) == N, "preact_out shape");
+    p.preact_out = preact_out->data_ptr(); p.ldpre = static_cast<int>(preact_out->stride(0));
+  }
+  p.status = status_tensor().data_ptr<int>();
+  ssb::GemmAgComm cm{};
+  cm.x_local = x.data_ptr();
+  cm.gather_ptrs = reinterpret_cast<void* const*>(gather_ptrs.data_ptr<int64_t>());
+  cm.gather_ptrs_host_local = reinterpret_cast<const void*>(gather_local);
+  cm.flag_ptrs = reinterpret_cast<uint32_t* const*>(flag_ptrs.data_ptr<int64_t>());
+  cm.rank = static_cast<int>(rank); cm.tp = static_cast<int>(tp);
+  cm.epoch = static_cast<uint32_t>(epoch); cm.max_blocks = static_cast<int>(max_blocks);
+  cm.capacity_elems = capacity_elems;
+  check_launch(ssb::gemm_ag_launch(w.data_ptr(), static_cast<int>(w.stride(0)), p, cm, num_sms(), cur_stream()),
+               "allgather_gemm");
+}
+
 int64_t comm_max_blocks() { return ssb::comm_max_blocks(); }
 
 Tensor status() { return status_tensor(); }
@@ -597,6 +640,7 @@ Tensor status() { return status_tensor(); }
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_allreduce", &gemm_allreduce);
+  m.def("allgather_gemm", &allgather_gemm);
   m.def("gemm_set_pair_mode", &ssb::gemm_set_pair_mode);
   m.def("gemm_get_pair_mode", &ssb::gemm_get_pair_mode);
   m.def("layernorm_fwd", &layernorm_fwd);

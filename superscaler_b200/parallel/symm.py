@@ -111,3 +111,41 @@ class FusedTPContext:
                                     self.result_ptrs[par], self.flag_ptrs, self.rank, self.tp, self.epoch,
                                     self.max_tiles, self.capacity)
         return out
+
+    # ---- all-gather fused into the consuming GEMM (csrc/gemm_ag_sm100.cu) -------------------------------------
+    def enable_allgather(self, max_rows_total: int, max_k: int) -> None:
+        """Allocates (collectively, once) the two alternating gather buffers [rows, K] and their flag table."""
+        import torch.distributed._symmetric_memory as symm
+        name = self.group.group_name
+        self.ag_capacity = int(max_rows_total) * int(max_k)
+        self.ag_max_blocks = -(-int(max_rows_total) // self.TILE_M)
+        self.ag_bufs = [symm.empty(self.ag_capacity, dtype=torch.bfloat16, device=self.device) for _ in range(2)]
+        self.ag_flags = symm.empty(self.ag_max_blocks, dtype=torch.int32, device=self.device)
+        self.ag_flags.zero_()
+        self.ag_ptrs, self.ag_local = [], []
+        for b in self.ag_bufs:
+            h = symm.rendezvous(b, name)
+            self.ag_ptrs.append(torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=self.device))
+            self.ag_local.append(int(h.buffer_ptrs[self.rank]))
+        h = symm.rendezvous(self.ag_flags, name)
+        self.ag_flag_ptrs = torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=self.device)
+        self.ag_epoch = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def allgather_linear(self, x_local: torch.Tensor, w: torch.Tensor, *, bias=None, act: int = 0, preact_out=None,
+                         out=None) -> torch.Tensor:
+        """act(concat over the group of x_r . w^T + bias): rows of rank r land at [r * rows, (r + 1) * rows)."""
+        from ..ops import native
+        rows, K = x_local.shape
+        M, N = rows * self.tp, w.shape[0]
+        assert rows % self.TILE_M == 0 and K % 64 == 0, "rows per rank must be a multiple of 128, K of 64"
+        assert M * K <= self.ag_capacity and M // self.TILE_M <= self.ag_max_blocks, "gather scratch too small"
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=x_local.device)
+        self.ag_epoch += 1
+        par = self.ag_epoch & 1
+        native.ext().allgather_gemm(x_local.contiguous(), w, out, bias, act, preact_out, self.ag_ptrs[par],
+                                    self.ag_local[par], self.ag_flag_ptrs, self.rank, self.tp, self.ag_epoch,
+                                    self.ag_max_blocks, self.ag_capacity)
+        return out

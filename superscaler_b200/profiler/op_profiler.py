@@ -78,8 +78,9 @@ def profile_plan(plan: dict, rank: int, world: int, overrides: dict, repeat: int
     for op in trainer.stage.ops:
         members = getattr(op, "members", [op])
         names = [m.info.name for m in members]
-        snapshot = {k: (v.detach().clone().requires_grad_(v.is_floating_point()) if isinstance(v, torch.Tensor) else v)
-                    for k, v in st.items()}
+        # tensors that come from the data loader (images, ids, labels) never receive a gradient in training
+        snapshot = {k: (v.detach().clone().requires_grad_(v.is_floating_point() and k not in batch)
+                        if isinstance(v, torch.Tensor) else v) for k, v in st.items()}
 
         def fwd(keep=None):
             local = dict(snapshot)

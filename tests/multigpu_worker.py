@@ -94,6 +94,30 @@ def main():
         assert all(abs(v - gathered[0]) < 1e-3 * max(1.0, abs(gathered[0])) for v in gathered), gathered
         if rank == 0:
             print("GEMM_AR_OK worst rel err", round(worst, 5), flush=True)
+    elif mode == "ag_gemm":
+        from superscaler_b200.ops import functional as F
+        from superscaler_b200.parallel.symm import FusedTPContext
+        ctx = FusedTPContext(None, 256, 256, dev)
+        ctx.enable_allgather(2048 * world, 1024)
+        worst = 0.0
+        for rep in range(3):
+            for (rows, N, K, act) in [(128, 256, 64, 0), (2048, 1024, 1024, 1), (512, 776 // 8 * 8, 256, 0), (1024, 4096, 512, 1)]:
+                g = torch.Generator(device=dev).manual_seed(50 * rank + rows + rep)
+                x = torch.randn(rows, K, device=dev, generator=g).bfloat16()
+                g2 = torch.Generator(device=dev).manual_seed(3 + rep)          # same on every rank
+                w = (torch.randn(N, K, device=dev, generator=g2) * 0.05).bfloat16()
+                bias = torch.randn(N, device=dev, generator=g2).bfloat16()
+                out = ctx.allgather_linear(x, w, bias=bias, act=act)
+                full = [torch.empty_like(x) for _ in range(world)]
+                dist.all_gather(full, x)
+                ref = F.gemm(torch.cat(full, 0), w, bias=bias, act=act)
+                torch.cuda.synchronize()
+                err = (out.float() - ref.float()).abs().max().item()
+                worst = max(worst, err)
+                assert err <= 1e-2 * ref.float().abs().max().item(), f"rank {rank} case {(rows, N, K, act)} rep {rep}: max err {err}"
+        assert native.check_status() == 0
+        if rank == 0:
+            print("AG_GEMM_OK", worst, flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -33,3 +33,8 @@ def test_dp_tp_pp_training_on_two_gpus():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_gemm_allreduce_matches_gemm_plus_nccl():
     assert "GEMM_AR_OK" in _launch("gemm_ar")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_allgather_gemm_matches_allgather_plus_gemm():
+    assert "AG_GEMM_OK" in _launch("ag_gemm")
