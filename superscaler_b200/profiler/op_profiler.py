@@ -68,7 +68,8 @@ def _event_ms(fn, repeat: int, warmup: int) -> float:
 
 def profile_plan(plan: dict, rank: int, world: int, overrides: dict, repeat: int, warmup: int, batch_fn) -> List[list]:
     """Returns the CSV rows (one per op name of the one-layer model)."""
-    trainer = Trainer(plan, rank=rank, world_size=world, model_overrides=overrides, lr_warmup_steps=0)
+    trainer = Trainer(plan, rank=rank, world_size=world, model_overrides=overrides, lr_warmup_steps=0,
+                      fused_comm=True)
     batch = trainer.to_device(batch_fn(plan))
     st = trainer.microbatch_inputs(batch, 0)
     if world > 1:
