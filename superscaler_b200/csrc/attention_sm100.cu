@@ -44,9 +44,17 @@ __device__ __forceinline__ uint32_t fmix32(uint32_t x) {
   x ^= x >> 16;
   return x;
 }
-// One 32-bit hash decides the two keys (kv even, kv odd) of a pair for query q.
-__device__ __forceinline__ uint32_t attn_pair_hash(uint32_t bh_seed, uint32_t q, uint32_t pairs_per_row, uint32_t pair) {
-  return fmix32((q * pairs_per_row + pair) * 0x9E3779B1u + bh_seed);
+// Dropout mask: one 32-bit hash decides the four keys 4g .. 4g+3 of query q; key 4g+i is kept when byte i of the
+// hash is below keep8 = round(256 (1 - p)).  The dropout probability is therefore quantised to 1/256 (the scale
+// applied to the kept values is the exact 256 / keep8), which makes the mask four times cheaper to generate than
+// one 16-bit lane per element.
+__device__ __forceinline__ uint32_t attn_quad_hash(uint32_t bh_seed, uint32_t q, uint32_t quads_per_row, uint32_t quad) {
+  return fmix32((q * quads_per_row + quad) * 0x9E3779B1u + bh_seed);
+}
+__device__ __forceinline__ bool keep_byte(uint32_t h, int i, uint32_t keep8) { return ((h >> (8 * i)) & 0xFFu) < keep8; }
+__host__ __device__ __forceinline__ uint32_t dropout_keep8(float p) {
+  const int k = static_cast<int>((1.0f - p) * 256.0f + 0.5f);
+  return static_cast<uint32_t>(k < 1 ? 1 : (k > 256 ? 256 : k));
 }
 
 // Writes 32 consecutive bf16 columns (16 packed words) of row r into a [rows][128 B] swizzled chunk.
@@ -267,10 +275,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int q = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float c = p.scale * kLog2e;
-    const uint32_t keep16 = dropout_keep16(p.dropout_p);
-    const float inv_keep = p.dropout_p > 0.f ? 65536.0f / static_cast<float>(keep16) : 1.0f;
+    const uint32_t keep8 = dropout_keep8(p.dropout_p);
+    const float inv_keep = p.dropout_p > 0.f ? 256.0f / static_cast<float>(keep8) : 1.0f;  // applied once, to O
     const uint32_t bh_seed = static_cast<uint32_t>(hash64(p.dropout_seed, static_cast<uint64_t>(b) * p.NH + head));
-    const uint32_t pairs_per_row = (p.SK + 1) >> 1;
+    const uint32_t quads_per_row = (p.SK + 3) >> 2;
     float m = -INFINITY, l = 0.f, alpha_pending = 1.f;
     float o[OC];
 #pragma unroll
@@ -315,16 +323,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       float rowsum = 0.f;
       uint32_t w[16];
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        float p0 = ex2(__uint_as_float(rr[i]) * c - mc);      // masked entries: ex2(-inf) = 0
-        float p1 = ex2(__uint_as_float(rr[i + 1]) * c - mc);
-        rowsum += p0 + p1;
-        if (p.dropout_p > 0.f) {
-          const uint32_t h = attn_pair_hash(bh_seed, q, pairs_per_row, (kv0 + i) >> 1);
-          p0 = ((h & 0xFFFFu) < keep16) ? p0 * inv_keep : 0.f;
-          p1 = ((h >> 16) < keep16) ? p1 * inv_keep : 0.f;
+      for (int i = 0; i < 32; i += 4) {
+        float pe[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          pe[e] = ex2(__uint_as_float(rr[i + e]) * c - mc);  // masked entries: ex2(-inf) = 0
+          rowsum += pe[e];
         }
-        w[i >> 1] = pack_bf16x2(p0, p1);
+        if (p.dropout_p > 0.f) {
+          const uint32_t h = attn_quad_hash(bh_seed, q, quads_per_row, (kv0 + i) >> 2);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) pe[e] = keep_byte(h, e, keep8) ? pe[e] : 0.f;
+        }
+        w[i >> 1] = pack_bf16x2(pe[0], pe[1]);
+        w[(i >> 1) + 1] = pack_bf16x2(pe[2], pe[3]);
       }
       // the single P buffer is free once P.V of the previous block retired
       if (j > 0 && !mbar_wait_warp(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
@@ -358,7 +370,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (!mbar_wait(&l_bar[quarter], 0, abort_flag)) ok = false;
     l = (xsum[r] + xsum[128 + r]) + (xsum[256 + r] + xsum[384 + r]);
     if (ok && q < p.SQ) {
-      const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+      const float inv_l = l > 0.f ? inv_keep / l : 0.f;
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.O) +
                             (static_cast<size_t>(b) * p.SQ + q) * p.ldo + p.o_col0 + head * HD + g * OC;
 #pragma unroll
@@ -559,14 +571,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     constexpr int OC = HD / 4;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float c = p.scale * kLog2e;
-    const uint32_t keep16 = dropout_keep16(p.dropout_p);
-    const float inv_keep = p.dropout_p > 0.f ? 65536.0f / static_cast<float>(keep16) : 1.0f;
+    const uint32_t keep8 = dropout_keep8(p.dropout_p);
+    const float inv_keep = p.dropout_p > 0.f ? 256.0f / static_cast<float>(keep8) : 1.0f;
     const uint32_t bh_seed = static_cast<uint32_t>(hash64(p.dropout_seed, static_cast<uint64_t>(b) * p.NH + head));
-    const uint32_t pairs_per_row = (p.SK + 1) >> 1;
+    const uint32_t quads_per_row = (p.SK + 3) >> 2;
     const float* lse_row = p.LSE + (static_cast<size_t>(b) * p.NH + head) * p.SQ;
     const float* delta_row = p.delta + (static_cast<size_t>(b) * p.NH + head) * p.SQ;
     const bool kv_ok = kv < kv_len;
-    const int odd = lane & 1;  // kv parity: lanes 2t and 2t+1 share the dropout hash of their key pair
+    const int sub = lane & 3;  // position of this key in its quad: lanes 4t .. 4t+3 share the hash of (query, quad)
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int st = it & 1;
@@ -587,28 +599,27 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tmem_ld_32x16(tmem_base + lane_addr + 128 + st * 64 + g * 16, rp);
       tmem_ld_wait();
       uint32_t wp[8], wd[8];
+      // dropout: each lane of a quad hashes 4 of the 16 queries (query index = 4 j + sub), the quad exchanges them
+      uint32_t hq[4] = {0u, 0u, 0u, 0u};
+      if (p.dropout_p > 0.f) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) hq[j] = attn_quad_hash(bh_seed, qbase + 4 * j + sub, quads_per_row, kv >> 2);
+      }
 #pragma unroll
       for (int i = 0; i < 16; i += 2) {
-        bool keep0 = true, keep1 = true;
-        if (p.dropout_p > 0.f) {
-          // each lane hashes one of the two queries, its neighbour (same key pair) the other
-          const uint32_t h_mine = attn_pair_hash(bh_seed, qbase + i + odd, pairs_per_row, kv >> 1);
-          const uint32_t h_other = __shfl_xor_sync(0xffffffffu, h_mine, 1);
-          const uint32_t h0 = odd ? h_other : h_mine, h1 = odd ? h_mine : h_other;
-          keep0 = (odd ? (h0 >> 16) : (h0 & 0xFFFFu)) < keep16;
-          keep1 = (odd ? (h1 >> 16) : (h1 & 0xFFFFu)) < keep16;
-        }
         float pv[2], dv[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int q = qbase + i + e;
           const bool valid = kv_ok && q < p.SQ && !(p.causal && kv > q);
-          const bool keep = e ? keep1 : keep0;
-          float pr = ex2(__uint_as_float(rs[i + e]) * c - lse2[i + e]);
+          const float pr = ex2(__uint_as_float(rs[i + e]) * c - lse2[i + e]);
           float dp = __uint_as_float(rp[i + e]);
           float pd = pr;
           if (p.dropout_p > 0.f) {
-            pd = keep ? pr * inv_keep : 0.f;
+            // hash of query i + e: held by the lane of this quad whose sub equals (i + e) & 3
+            const uint32_t h = __shfl_sync(0xffffffffu, hq[(i + e) >> 2], (lane & ~3) | ((i + e) & 3));
+            const bool keep = keep_byte(h, sub, keep8);
+            pd = keep ? pr : 0.f;                  // unscaled: dV is multiplied by 256 / keep8 once, at the end
             dp = keep ? dp * inv_keep : 0.f;
           }
           const float ds = pr * (dp - dl[i + e]) * p.scale;
@@ -648,10 +659,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
       for (int i = 0; i < OC / 8; ++i) {
         uint4 wv, wk;
-        wv.x = pack_bf16x2(__uint_as_float(rv[8 * i + 0]), __uint_as_float(rv[8 * i + 1]));
-        wv.y = pack_bf16x2(__uint_as_float(rv[8 * i + 2]), __uint_as_float(rv[8 * i + 3]));
-        wv.z = pack_bf16x2(__uint_as_float(rv[8 * i + 4]), __uint_as_float(rv[8 * i + 5]));
-        wv.w = pack_bf16x2(__uint_as_float(rv[8 * i + 6]), __uint_as_float(rv[8 * i + 7]));
+        wv.x = pack_bf16x2(__uint_as_float(rv[8 * i + 0]) * inv_keep, __uint_as_float(rv[8 * i + 1]) * inv_keep);
+        wv.y = pack_bf16x2(__uint_as_float(rv[8 * i + 2]) * inv_keep, __uint_as_float(rv[8 * i + 3]) * inv_keep);
+        wv.z = pack_bf16x2(__uint_as_float(rv[8 * i + 4]) * inv_keep, __uint_as_float(rv[8 * i + 5]) * inv_keep);
+        wv.w = pack_bf16x2(__uint_as_float(rv[8 * i + 6]) * inv_keep, __uint_as_float(rv[8 * i + 7]) * inv_keep);
         wk.x = pack_bf16x2(__uint_as_float(rk[8 * i + 0]), __uint_as_float(rk[8 * i + 1]));
         wk.y = pack_bf16x2(__uint_as_float(rk[8 * i + 2]), __uint_as_float(rk[8 * i + 3]));
         wk.z = pack_bf16x2(__uint_as_float(rk[8 * i + 4]), __uint_as_float(rk[8 * i + 5]));
@@ -844,10 +855,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     constexpr int OC = HD / 4;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float c = p.scale * kLog2e;
-    const uint32_t keep16 = dropout_keep16(p.dropout_p);
-    const float inv_keep = p.dropout_p > 0.f ? 65536.0f / static_cast<float>(keep16) : 1.0f;
+    const uint32_t keep8 = dropout_keep8(p.dropout_p);
+    const float inv_keep = p.dropout_p > 0.f ? 256.0f / static_cast<float>(keep8) : 1.0f;
     const uint32_t bh_seed = static_cast<uint32_t>(hash64(p.dropout_seed, static_cast<uint64_t>(b) * p.NH + head));
-    const uint32_t pairs_per_row = (p.SK + 1) >> 1;
+    const uint32_t quads_per_row = (p.SK + 3) >> 2;
     const bool q_ok = q < p.SQ;
     const size_t stat_idx = (static_cast<size_t>(b) * p.NH + head) * p.SQ + (q_ok ? q : 0);
     const float lse2 = p.LSE[stat_idx] * kLog2e;
@@ -865,24 +876,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tmem_ld_wait();
       uint32_t wd[8];
 #pragma unroll
-      for (int i = 0; i < 16; i += 2) {
+      for (int i = 0; i < 16; i += 4) {
         const int kv = kvb + i;
         uint32_t h = 0;
-        if (p.dropout_p > 0.f) h = attn_pair_hash(bh_seed, q, pairs_per_row, kv >> 1);
-        float dsv[2];
+        if (p.dropout_p > 0.f) h = attn_quad_hash(bh_seed, q, quads_per_row, kv >> 2);
+        float dsv[4];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
+        for (int e = 0; e < 4; ++e) {
           const bool valid = q_ok && (kv + e) < kv_len && !(p.causal && (kv + e) > q);
           const float pr = ex2(__uint_as_float(rs[i + e]) * c - lse2);
           float dp = __uint_as_float(rp[i + e]);
-          if (p.dropout_p > 0.f) {
-            const bool keep = (e ? (h >> 16) : (h & 0xFFFFu)) < keep16;
-            dp = keep ? dp * inv_keep : 0.f;
-          }
+          if (p.dropout_p > 0.f) dp = keep_byte(h, e, keep8) ? dp * inv_keep : 0.f;
           const float ds = pr * (dp - delta) * p.scale;
           dsv[e] = valid ? ds : 0.f;
         }
         wd[i >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+        wd[(i >> 1) + 1] = pack_bf16x2(dsv[2], dsv[3]);
       }
       if (!mbar_wait_warp(&ds_empty[st], ph ^ 1, abort_flag)) { ok = false; break; }
       store_row16_sw128(sdS + st * Cfg::kSBytes, r, g * 2, wd);

@@ -156,12 +156,15 @@ def fuse_ops(ops: List[Op]) -> List[Op]:
             out.append(FusedMLP(ops[i:i + 4]))
             i += 4
             continue
-        if isinstance(o, MLPUpOp) and i + 1 < n and isinstance(ops[i + 1], BiasActOp) and _same_place(ops[i:i + 2]):
+        # at tp > 1 the alternative partitioning (algo 1) leaves x in a layout the next op does not accept, so a
+        # relayout has to run between the two ops and they cannot share a kernel
+        if isinstance(o, MLPUpOp) and i + 1 < n and isinstance(ops[i + 1], BiasActOp) and _same_place(ops[i:i + 2]) \
+                and (o.info.algo == 0 or o.info.tp == 1):
             out.append(FusedUpAct(ops[i:i + 2]))
             i += 2
             continue
         if isinstance(o, DenseOp) and i + 1 < n and isinstance(ops[i + 1], BiasDropoutAddOp) and \
-                _same_place(ops[i:i + 2]):
+                _same_place(ops[i:i + 2]) and (o.info.algo == 0 or o.info.tp == 1):
             out.append(FusedDenseDropAdd(ops[i:i + 2]))
             i += 2
             continue

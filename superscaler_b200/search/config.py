@@ -122,7 +122,10 @@ def build_plan(num_ops_list: Sequence[int], tp_flat: Sequence[int], dp_flat: Seq
     return Plan(global_bs=global_bs, micro_bs=micro_bs, stages=stages, num_stages=n)
 
 
-def plan_to_dict(plan: Plan, model_name: str, model_size: str, num_layers: int) -> dict:
+def plan_to_dict(plan: Plan, model_name: str, model_size: str, num_layers: int, shapes: str = "reference") -> dict:
+    """Plan JSON.  shapes = "reference": the model dimensions of the reference's size tables (byte-compatible with
+    its plan files); "b200": the B200_* tables (e.g. GPT-3 1.3B with 16 heads of 128) with every dimension the
+    runtime needs spelled out."""
     if model_name == "scale-layer":
         model_name, model_size = "gpt", "scale-layer"
     d: dict = {"model_name": model_name, "model_size": model_size}
@@ -138,8 +141,13 @@ def plan_to_dict(plan: Plan, model_name: str, model_size: str, num_layers: int) 
         d["max_position_embeddings"] = seq
         d["num_attention_heads"] = heads
         d["hidden_size"] = hidden
+        if shapes == "b200" and model_size in B200_GPT_SIZES:
+            _, seq, hidden, ffn, heads, kv, vocab, _ = B200_GPT_SIZES[model_size]
+            d.update(num_attention_heads=heads, kv_channels=kv, ffn_hidden_size=ffn, vocab_size=vocab)
     elif model_name == "t5":
         _, enc_seq, dec_seq, hidden, ffn, heads, kv, _vocab, _ = T5_SIZES[model_size]
+        if shapes == "b200" and model_size in B200_T5_SIZES:
+            _, enc_seq, dec_seq, hidden, ffn, heads, kv, _vocab, _ = B200_T5_SIZES[model_size]
         d["num_layers"] = num_layers
         d["encoder_seq_length"] = enc_seq
         d["decoder_seq_length"] = dec_seq
@@ -148,6 +156,8 @@ def plan_to_dict(plan: Plan, model_name: str, model_size: str, num_layers: int) 
         d["kv_channels"] = kv
         d["hidden_size"] = hidden
         d["ffn_hidden_size"] = ffn
+        if shapes == "b200":
+            d["vocab_size"] = _vocab
     else:
         raise ValueError(f"unsupported model {model_name}")
     d["global_batch_size"] = plan.global_bs
@@ -166,9 +176,10 @@ def plan_to_dict(plan: Plan, model_name: str, model_size: str, num_layers: int) 
     return d
 
 
-def save_plan(plan: Plan, path: str, model_name: str, model_size: str, num_layers: int) -> None:
+def save_plan(plan: Plan, path: str, model_name: str, model_size: str, num_layers: int,
+              shapes: str = "reference") -> None:
     with open(path, "w") as f:
-        json.dump(plan_to_dict(plan, model_name, model_size, num_layers), f, indent=4)
+        json.dump(plan_to_dict(plan, model_name, model_size, num_layers, shapes), f, indent=4)
 
 
 def plan_from_dict(d: dict, full_op_list: Sequence[str]) -> Plan:

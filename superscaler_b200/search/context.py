@@ -71,6 +71,7 @@ class SearchArgs:
     only_top_1_target: bool = False
     consider_collective_memory: bool = False
     price_overlap: bool = True
+    shapes: str = "reference"
     save_to_csv: Optional[str] = None
     # derived
     num_gpus: int = 0
@@ -162,6 +163,8 @@ def add_cli_arguments(p: argparse.ArgumentParser) -> None:
     a("--consider-collective-memory", action="store_true")
     a("--no-price-overlap", action="store_false", dest="price_overlap")
     a("--save-to-csv", type=str, default=None)
+    a("--shapes", type=str, default="reference", choices=["reference", "b200"],
+      help="model dimensions written into the plan JSON: the reference's size tables or the B200 ones")
 
 
 def args_from_namespace(ns: argparse.Namespace) -> SearchArgs:

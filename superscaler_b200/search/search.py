@@ -228,7 +228,7 @@ class Searcher:
                 break
         if best is not None and a.config_save_path is not None:
             path = f"{a.config_save_path}{a.model_name}_{a.model_size}_{best.num_stages}stages_{a.config_suffix}.json"
-            save_plan(best, path, a.model_name, a.model_size, a.num_layers)
+            save_plan(best, path, a.model_name, a.model_size, a.num_layers, getattr(a, "shapes", "reference"))
             print(f"config has been saved to {path}")
         self._report(best, num_stages, targets_hist, hops_hist, search_times, trend)
         mem = max(best.memory_list) if best is not None else 0

@@ -271,6 +271,42 @@ def test_flash_attention_dropout_consistency():
     assert rel(o, o_nodrop) > 0.05  # dropout really changes the output
 
 
+def test_flash_attention_dropout_grads_with_extracted_mask():
+    """Reads the dropout mask out of the forward kernel (V = one-hot blocks gives P_drop itself), then checks dQ, dK,
+    dV of the backward kernels against autograd through plain fp32 attention that uses that mask."""
+    torch.manual_seed(21)
+    B, NH, S, HD, pdrop, seed = 1, 2, 256, 128, 0.25, 5
+    h = NH * HD
+    qkv = (torch.randn(B * S, 3 * h, device=DEV) * 0.5).bfloat16()
+    pd = torch.zeros(NH, S, S, device=DEV)
+    eye = torch.eye(HD, device=DEV)
+    for blk in range(S // HD):
+        v = torch.zeros(S, NH, HD, device=DEV)
+        v[blk * HD:(blk + 1) * HD] = eye[:, None, :]
+        x = qkv.clone()
+        x[:, 2 * h:] = v.reshape(S, h).bfloat16()
+        o = F.fused_qkv_attention(x, B, NH, S, HD, causal=True, dropout_p=pdrop, seed=seed)
+        pd[:, :, blk * HD:(blk + 1) * HD] = o.float().view(S, NH, HD).permute(1, 0, 2)
+    mask = (pd != 0).float()
+    causal = torch.tril(torch.ones(S, S, device=DEV))
+    kept = (mask * causal).sum() / causal.sum() / NH
+    assert abs(kept.item() - 0.75) < 0.02, kept          # 192 / 256 of the visible entries survive
+    x = qkv.clone().requires_grad_(True)
+    o = F.fused_qkv_attention(x, B, NH, S, HD, causal=True, dropout_p=pdrop, seed=seed)
+    do = torch.randn_like(o)
+    o.backward(do)
+    xr = qkv.float().clone().requires_grad_(True)
+    q, k, v = (xr[:, i * h:(i + 1) * h].view(S, NH, HD).permute(1, 0, 2) for i in range(3))
+    sc = (q @ k.transpose(1, 2)) * HD ** -0.5
+    sc = sc.masked_fill(causal == 0, float("-inf"))
+    pr = torch.softmax(sc, -1) * mask * (256.0 / 192.0)
+    ref = (pr @ v).permute(1, 0, 2).reshape(S, h)
+    ref.backward(do.float())
+    assert rel(o, ref) < 1e-2
+    for i, name in enumerate("qkv"):
+        assert rel(x.grad[:, i * h:(i + 1) * h], xr.grad[:, i * h:(i + 1) * h]) < 2e-2, name
+
+
 def test_lm_head_cross_entropy_autograd():
     torch.manual_seed(13)
     T, H, V = 256, 256, 1024
