@@ -9,7 +9,10 @@
 //
 //   warp 0     : TMA producer (one elected lane), in both CTAs
 //   warp 1     : TMEM allocator in both CTAs; MMA issuer in the leader (cluster rank 0)
-//   warps 2..9 : epilogue; warp w reads TMEM lanes 32*(w%4)..+31, columns 128*((w-2)/4)..+127
+//   warps 2..17: epilogue; warp w reads TMEM lanes 32*(w%4)..+31, columns 64*((w-2)/4)..+63 in chunks of 16.
+//                Sixteen warps (four per SM sub-partition): with eight, bias + GeLU + pre-activation epilogues took
+//                longer than the K = 2048 main loop of the next tile (measured 643 us against 407 us for the same
+//                GEMM with a plain epilogue)
 //
 // Barriers: `full` lives in the leader and counts the bytes of both CTAs' loads (the peer's TMA signals it
 // through the cluster address); `empty` and `tmem_full` exist in both CTAs and are signalled together by a
@@ -34,7 +37,7 @@ constexpr int BNH = 128;   // B rows staged per CTA (256 output columns per clus
 constexpr int BN2 = 256;
 constexpr int BK2 = 64;
 constexpr int kStages2 = 6;
-constexpr int kEpiWarps = 8;
+constexpr int kEpiWarps = 16;
 constexpr int kThreads2 = 64 + kEpiWarps * 32;
 constexpr int kGroupM2 = 8;
 constexpr int kABytes2 = BM2 * BK2 * 2;
@@ -256,7 +259,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   } else {
     // -------------------------------- epilogue --------------------------------
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int grp = (warp - 2) >> 2;  // 64-column group of the 256-column tile
     const uint32_t keep16 = dropout_keep16(p.dropout_p);
     const float drop_scale = p.dropout_p > 0.f ? 65536.0f / static_cast<float>(keep16) : 1.0f;
     int iter = 0;
@@ -272,16 +275,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       tc_fence_after_sync();
       const int row = tc.m_blk * 2 * BM2 + static_cast<int>(cta_rank) * BM2 + quarter * 32 + lane;
       const bool row_ok = row < p.M;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + half * 128;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + grp * 64;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
-        const int n0 = tc.n_blk * BN2 + half * 128 + c * 32;
+        const int n0 = tc.n_blk * BN2 + grp * 64 + c * 16;
         if (n0 >= p.N) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
+        uint32_t r[16];
+        tmem_ld_32x16(taddr + c * 16, r);
         tmem_ld_wait();
         if (!row_ok) continue;
-        gemm_epilogue_chunk(p, row, n0, r, keep16, drop_scale);
+        gemm_epilogue_chunk<16>(p, row, n0, r, keep16, drop_scale);
       }
       tc_fence_before_sync();
       __syncwarp();

@@ -234,7 +234,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tma_local, const __grid_const
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        gemm_epilogue_chunk(p, row, n0, r, keep16, drop_scale);
+        gemm_epilogue_chunk<32>(p, row, n0, r, keep16, drop_scale);
       }
       tc_fence_before_sync();
       __syncwarp();

@@ -220,7 +220,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
         if (!row_ok) continue;
-        gemm_epilogue_chunk(p, row, n0, r, keep16, drop_scale);
+        gemm_epilogue_chunk<32>(p, row, n0, r, keep16, drop_scale);
       }
       tc_fence_before_sync();
       __syncwarp();

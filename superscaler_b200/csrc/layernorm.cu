@@ -198,6 +198,77 @@ ln_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
   }
 }
 
+// Same as ln_bwd_dx_kernel for H = VPL * 256: the packed dy and x rows stay in registers between the two passes
+// (one read of each from memory) and gamma is read in 16-byte pieces.
+template <int VPL>
+__global__ void __launch_bounds__(kLnWarpsPerBlock * 32)
+ln_bwd_dx_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                     const float* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ rstd,
+                     const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, int rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * kLnWarpsPerBlock + (threadIdx.x >> 5);
+  const int warps_total = gridDim.x * kLnWarpsPerBlock;
+  for (int row = warp_global; row < rows; row += warps_total) {
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * H);
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
+    const float mu = mean[row], rs = rstd[row];
+    uint4 qd[VPL], qx[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      qd[i] = dyr[i * 32 + lane];
+      qx[i] = xr[i * 32 + lane];
+    }
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = i * 32 + lane;
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * v);
+      const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * v + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      const float2 d0 = unpack_bf16x2(qd[i].x), d1 = unpack_bf16x2(qd[i].y), d2 = unpack_bf16x2(qd[i].z), d3 = unpack_bf16x2(qd[i].w);
+      const float2 x0 = unpack_bf16x2(qx[i].x), x1 = unpack_bf16x2(qx[i].y), x2 = unpack_bf16x2(qx[i].z), x3 = unpack_bf16x2(qx[i].w);
+      const float d[8] = {d0.x, d0.y, d1.x, d1.y, d2.x, d2.y, d3.x, d3.y};
+      const float xv[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float dg = d[j] * g[j];
+        s1 += dg;
+        s2 += dg * (xv[j] - mu) * rs;
+      }
+    }
+    s1 = warp_sum(s1) / static_cast<float>(H);
+    s2 = warp_sum(s2) / static_cast<float>(H);
+    uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * H);
+    const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * H) : nullptr;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = i * 32 + lane;
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * v);
+      const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * v + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      const float2 d0 = unpack_bf16x2(qd[i].x), d1 = unpack_bf16x2(qd[i].y), d2 = unpack_bf16x2(qd[i].z), d3 = unpack_bf16x2(qd[i].w);
+      const float2 x0 = unpack_bf16x2(qx[i].x), x1 = unpack_bf16x2(qx[i].y), x2 = unpack_bf16x2(qx[i].z), x3 = unpack_bf16x2(qx[i].w);
+      const float d[8] = {d0.x, d0.y, d1.x, d1.y, d2.x, d2.y, d3.x, d3.y};
+      const float xv[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xhat = (xv[j] - mu) * rs;
+        o[j] = rs * (d[j] * g[j] - s1 - xhat * s2);
+      }
+      if (drr) {
+        const uint4 qr = drr[v];
+        const float2 r0 = unpack_bf16x2(qr.x), r1 = unpack_bf16x2(qr.y), r2 = unpack_bf16x2(qr.z), r3 = unpack_bf16x2(qr.w);
+        o[0] += r0.x; o[1] += r0.y; o[2] += r1.x; o[3] += r1.y; o[4] += r2.x; o[5] += r2.y; o[6] += r3.x; o[7] += r3.y;
+      }
+      uint4 w;
+      w.x = pack_bf16x2(o[0], o[1]); w.y = pack_bf16x2(o[2], o[3]);
+      w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
+      dxr[v] = w;
+    }
+  }
+}
+
 // Partial column sums over a slice of rows: part_g[slice][h] = sum dy*xhat, part_b[slice][h] = sum dy.
 // Block = 32 columns-pairs x 8 row lanes: thread (tx, ty) owns columns 2*(bx*32+tx), +1 and rows ty, ty+8, ...
 __global__ void __launch_bounds__(256)
@@ -317,9 +388,16 @@ int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, cons
                          int accumulate_wgrad, int rows, int H, int num_sms, cudaStream_t stream) {
   if (H % 8) return -3;
   const int blocks = min((rows + kLnWarpsPerBlock - 1) / kLnWarpsPerBlock, num_sms * 16);
-  ln_bwd_dx_kernel<<<blocks, kLnWarpsPerBlock * 32, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x), gamma, mean, rstd,
-      reinterpret_cast<const __nv_bfloat16*>(dres), reinterpret_cast<__nv_bfloat16*>(dx), rows, H);
+  const auto* dyb = reinterpret_cast<const __nv_bfloat16*>(dy);
+  const auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  const auto* drb = reinterpret_cast<const __nv_bfloat16*>(dres);
+  auto* dxb = reinterpret_cast<__nv_bfloat16*>(dx);
+  const dim3 g(blocks), b(kLnWarpsPerBlock * 32);
+  switch (H) {  // rows that fit in registers are read once
+    case 1024: ln_bwd_dx_reg_kernel<4><<<g, b, 0, stream>>>(dyb, xb, gamma, mean, rstd, drb, dxb, rows, H); break;
+    case 2048: ln_bwd_dx_reg_kernel<8><<<g, b, 0, stream>>>(dyb, xb, gamma, mean, rstd, drb, dxb, rows, H); break;
+    default: ln_bwd_dx_kernel<<<g, b, 0, stream>>>(dyb, xb, gamma, mean, rstd, drb, dxb, rows, H);
+  }
   const int slices = ln_bwd_slices(rows);
   const int rps = (rows + slices - 1) / slices;
   dim3 grid((H / 2 + 31) / 32, slices);
