@@ -23,6 +23,8 @@ CSRC = PKG / "csrc"
 OBJ = CSRC / "build"
 EXT_SUFFIX = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
 TARGET = PKG / f"_C{EXT_SUFFIX}"
+HOST_SRC = PKG / "csrc_host"                      # host-only helpers (no CUDA, no torch): loadable on CPU boxes
+HOST_TARGET = PKG / f"_data_helpers{EXT_SUFFIX}"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -90,7 +92,19 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         link += ["-L/usr/local/cuda/lib64", "-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python", "-lc10_cuda",
                  "-ltorch_cuda", "-lcudart"]
         _run(link)
+    build_host_helpers(force)
     return TARGET
+
+
+def build_host_helpers(force: bool = False) -> Path:
+    """Dataset index builders: one pybind11 module compiled with the host compiler only."""
+    import pybind11
+    srcs = sorted(HOST_SRC.glob("*.cpp"))
+    if force or _newer(srcs, HOST_TARGET):
+        py_inc = sysconfig.get_paths()["include"]
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", f"-I{py_inc}", f"-I{pybind11.get_include()}",
+              *map(str, srcs), "-o", str(HOST_TARGET)])
+    return HOST_TARGET
 
 
 if __name__ == "__main__":

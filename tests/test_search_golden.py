@@ -67,3 +67,17 @@ def test_explored_budget_is_deterministic(tmp_path):
     a = _search(tmp_path / "a", "gpt", "1_3B", 512, [1, 2, 4, 8], 3, explored_budget=300)
     b = _search(tmp_path / "b", "gpt", "1_3B", 512, [1, 2, 4, 8], 3, explored_budget=300)
     assert a[1] == b[1] and a[0][0] == b[0][0]
+
+
+def test_b200_shapes_in_plan_json():
+    """--shapes b200 writes the 16 x 128-head GPT-3 1.3B dimensions; the default keeps the reference's table."""
+    from superscaler_b200.models.gpt import gpt_op_names
+    from superscaler_b200.search.config import plan_to_dict, single_gpu_plan
+    names = gpt_op_names(24)
+    plan = single_gpu_plan(names, global_bs=512, micro_bs=8)
+    ref = plan_to_dict(plan, "gpt", "1_3B", 24)
+    b200 = plan_to_dict(plan, "gpt", "1_3B", 24, shapes="b200")
+    assert ref["num_attention_heads"] == 32 and "kv_channels" not in ref
+    assert (b200["num_attention_heads"], b200["kv_channels"], b200["ffn_hidden_size"], b200["vocab_size"]) == \
+        (16, 128, 8192, 51200)
+    assert b200["num_ops_in_each_stage"] == ref["num_ops_in_each_stage"] == [len(names)]
