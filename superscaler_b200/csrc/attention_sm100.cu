@@ -579,6 +579,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const float* delta_row = p.delta + (static_cast<size_t>(b) * p.NH + head) * p.SQ;
     const bool kv_ok = kv < kv_len;
     const int sub = lane & 3;  // position of this key in its quad: lanes 4t .. 4t+3 share the hash of (query, quad)
+    const bool stats_vec = (p.SQ & 3) == 0;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int st = it & 1;
@@ -586,12 +587,25 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const int qbase = (i0 + it) * 64 + g * 16;
       // statistics of this thread's 16 queries, requested before the accumulators are ready
       float lse2[16], dl[16];
+      if (stats_vec && qbase + 16 <= p.SQ) {  // 16-byte loads when the rows of LSE / delta are 16-byte aligned
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const bool in = qbase + i < p.SQ;
-        lse2[i] = in ? __ldg(lse_row + qbase + i) * kLog2e : INFINITY;
-        dl[i] = in ? __ldg(delta_row + qbase + i) : 0.f;
+        for (int i = 0; i < 4; ++i) {
+          const float4 a = __ldg(reinterpret_cast<const float4*>(lse_row + qbase) + i);
+          const float4 d = __ldg(reinterpret_cast<const float4*>(delta_row + qbase) + i);
+          lse2[4 * i] = a.x * kLog2e; lse2[4 * i + 1] = a.y * kLog2e; lse2[4 * i + 2] = a.z * kLog2e; lse2[4 * i + 3] = a.w * kLog2e;
+          dl[4 * i] = d.x; dl[4 * i + 1] = d.y; dl[4 * i + 2] = d.z; dl[4 * i + 3] = d.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const bool in = qbase + i < p.SQ;
+          lse2[i] = in ? __ldg(lse_row + qbase + i) * kLog2e : INFINITY;
+          dl[i] = in ? __ldg(delta_row + qbase + i) : 0.f;
+        }
       }
+      // blocks strictly below the diagonal and inside both sequences need no per-element validity test
+      const int qblk0 = (i0 + it) * 64;
+      const bool need_mask = (p.causal && kv0 + 127 > qblk0) || qblk0 + 64 > p.SQ || kv0 + 128 > kv_len;
       if (!mbar_wait_warp(&s_full[st], ph, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       uint32_t rs[16], rp[16];
@@ -610,8 +624,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         float pv[2], dv[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int q = qbase + i + e;
-          const bool valid = kv_ok && q < p.SQ && !(p.causal && kv > q);
           const float pr = ex2(__uint_as_float(rs[i + e]) * c - lse2[i + e]);
           float dp = __uint_as_float(rp[i + e]);
           float pd = pr;
@@ -622,9 +634,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             pd = keep ? pr : 0.f;                  // unscaled: dV is multiplied by 256 / keep8 once, at the end
             dp = keep ? dp * inv_keep : 0.f;
           }
-          const float ds = pr * (dp - dl[i + e]) * p.scale;
-          pv[e] = valid ? pd : 0.f;
-          dv[e] = valid ? ds : 0.f;
+          pv[e] = pd;
+          dv[e] = pr * (dp - dl[i + e]) * p.scale;
+        }
+        if (need_mask) {  // uniform branch: only blocks on the diagonal or at the ragged ends pay for the tests
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int q = qbase + i + e;
+            if (!(kv_ok && q < p.SQ && !(p.causal && kv > q))) pv[e] = dv[e] = 0.f;
+          }
         }
         wp[i >> 1] = pack_bf16x2(pv[0], pv[1]);
         wd[i >> 1] = pack_bf16x2(dv[0], dv[1]);
@@ -870,6 +888,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (!mbar_wait_warp(&s_full[st], ph, abort_flag)) { ok = false; break; }
       tc_fence_after_sync();
       const int kvb = it * 64 + g * 16;
+      const bool need_mask = (p.causal && it * 64 + 63 > q0) || q0 + 128 > p.SQ || it * 64 + 64 > kv_len;
       uint32_t rs[16], rp[16];
       tmem_ld_32x16(tmem_base + lane_addr + st * 64 + g * 16, rs);
       tmem_ld_32x16(tmem_base + lane_addr + 128 + st * 64 + g * 16, rp);
@@ -883,12 +902,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         float dsv[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const bool valid = q_ok && (kv + e) < kv_len && !(p.causal && (kv + e) > q);
           const float pr = ex2(__uint_as_float(rs[i + e]) * c - lse2);
           float dp = __uint_as_float(rp[i + e]);
           if (p.dropout_p > 0.f) dp = keep_byte(h, e, keep8) ? dp * inv_keep : 0.f;
-          const float ds = pr * (dp - delta) * p.scale;
-          dsv[e] = valid ? ds : 0.f;
+          dsv[e] = pr * (dp - delta) * p.scale;
+        }
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (!(q_ok && (kv + e) < kv_len && !(p.causal && (kv + e) > q))) dsv[e] = 0.f;
         }
         wd[i >> 1] = pack_bf16x2(dsv[0], dsv[1]);
         wd[(i >> 1) + 1] = pack_bf16x2(dsv[2], dsv[3]);

@@ -77,3 +77,28 @@ def cost_model_accuracy(pred_csv: str, log_path: str, config_name: str) -> Dict[
     if mem:
         out["actual_memory_mb"] = max(mem.values())
     return out
+
+
+def main(argv=None) -> None:
+    """`python -m superscaler_b200.utils.results --log-path logs/ [--config NAME] [--pred-csv info.csv]`:
+    throughput of every run under logs/csv (or of one), and the cost-model error when a prediction CSV is given."""
+    import argparse
+    import json
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--log-path", required=True)
+    ap.add_argument("--config", default=None)
+    ap.add_argument("--pred-csv", default=None)
+    a = ap.parse_args(argv)
+    if a.config is None:
+        name, t = best_throughput(a.log_path)
+        print(json.dumps({"best_config": name, "samples_per_s": t}))
+        return
+    out = {"config": a.config, "samples_per_s": throughput(a.log_path, a.config),
+           "iteration_ms": run_iteration_time_ms(a.log_path, a.config), "memory_mb": stage_memory_mb(a.log_path, a.config)}
+    if a.pred_csv:
+        out["cost_model"] = cost_model_accuracy(a.pred_csv, a.log_path, a.config)
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
