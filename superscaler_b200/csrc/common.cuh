@@ -228,38 +228,57 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn_m
 }
 
 // ------------------------------- numerics ------------------------------------
+// tanh on the special-function unit (one MUFU; relative error about 2^-11, far below bf16 resolution)
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float gelu_tanh(float x) {
   // 0.5 x (1 + tanh(0.79788456 x (1 + 0.044715 x^2))): the form used by Megatron's fused bias-gelu.
   float u = 0.7978845608028654f * x * (1.0f + 0.044715f * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
+  return 0.5f * x * (1.0f + tanh_fast(u));
 }
 __device__ __forceinline__ float gelu_tanh_grad(float x) {
   float u = 0.7978845608028654f * x * (1.0f + 0.044715f * x * x);
-  float t = tanhf(u);
+  float t = tanh_fast(u);
   return 0.5f * x * ((1.0f - t * t) * (0.7978845608028654f + 0.1070322243f * x * x)) + 0.5f * (1.0f + t);
 }
 
-// Counter-based dropout: one 64-bit hash decides 4 consecutive elements (16 bits each).
+// Counter-based dropout: one 32-bit hash decides 4 consecutive elements (one byte each).
 // Stateless, so backward and recompute regenerate the same mask without storing it.
 // `group` is (flat element index / 4); bit i of the result says element 4*group+i is kept.
-// keep16 = round(keep_prob * 65536); the effective keep probability is keep16 / 65536.
+// keep16 = 256 * round(keep_prob * 256): the keep probability is quantised to 1/256 and the scale that callers
+// apply to kept values, 65536 / keep16, is exact for the quantised probability.
 __device__ __forceinline__ uint64_t hash64(uint64_t seed, uint64_t ctr) {
   uint64_t z = seed + ctr * 0x9E3779B97F4A7C15ull;
   z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
   z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
   return z ^ (z >> 31);
 }
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x85EBCA6Bu;
+  x ^= x >> 13;
+  x *= 0xC2B2AE35u;
+  x ^= x >> 16;
+  return x;
+}
 __device__ __forceinline__ uint32_t dropout_keep4(uint64_t seed, uint64_t group, uint32_t keep16) {
-  uint64_t h = hash64(seed, group);
+  const uint32_t s32 = static_cast<uint32_t>(seed) ^ (static_cast<uint32_t>(seed >> 32) * 0x85EBCA6Bu);
+  const uint32_t g32 = static_cast<uint32_t>(group) + static_cast<uint32_t>(group >> 32) * 0xC2B2AE35u;
+  const uint32_t h = mix32(g32 * 0x9E3779B1u + s32);
+  const uint32_t keep8 = keep16 >> 8;
   uint32_t m = 0;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) m |= ((static_cast<uint32_t>(h >> (16 * i)) & 0xFFFFu) < keep16) ? (1u << i) : 0u;
+  for (int i = 0; i < 4; ++i) m |= (((h >> (8 * i)) & 0xFFu) < keep8) ? (1u << i) : 0u;
   return m;
 }
 __host__ __device__ __forceinline__ uint32_t dropout_keep16(float p) {
   float keep = 1.0f - p;
-  int k = static_cast<int>(keep * 65536.0f + 0.5f);
-  return static_cast<uint32_t>(k < 1 ? 1 : (k > 65536 ? 65536 : k));
+  int k = static_cast<int>(keep * 256.0f + 0.5f);
+  k = k < 1 ? 1 : (k > 256 ? 256 : k);
+  return static_cast<uint32_t>(k) * 256u;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

@@ -36,8 +36,17 @@ def run_gemm(a) -> None:
     A = torch.randn((a.K, a.M) if a.a_mn else (a.M, a.K), device="cuda").bfloat16()
     B = torch.randn((a.K, a.N) if a.b_mn else (a.N, a.K), device="cuda").bfloat16()
     out = torch.empty(a.M, a.N, device="cuda", dtype=torch.bfloat16)
-    ms = _time(lambda: F.gemm(A, B, out, a_mn=a.a_mn, b_mn=a.b_mn), a.warmup, a.iters)
-    print(f"gemm {a.M}x{a.N}x{a.K} a_mn={a.a_mn} b_mn={a.b_mn} pair={not a.single}: {ms:.4f} ms "
+    kw = {}
+    if a.epilogue == "gelu":      # bias + pre-activation store + GeLU (MLP up-projection forward)
+        kw = dict(bias=torch.zeros(a.N, device="cuda", dtype=torch.bfloat16), act=F.ACT_GELU,
+                  preact_out=torch.empty_like(out))
+    elif a.epilogue == "dgelu":   # GeLU derivative from the saved pre-activation (MLP down-projection dgrad)
+        kw = dict(act=F.ACT_DGELU, aux=torch.randn(a.M, a.N, device="cuda").bfloat16())
+    elif a.epilogue == "dropadd":  # bias + dropout + residual (attention output / MLP down-projection forward)
+        kw = dict(bias=torch.zeros(a.N, device="cuda", dtype=torch.bfloat16), dropout_p=0.1, seed=7,
+                  residual=torch.randn(a.M, a.N, device="cuda").bfloat16())
+    ms = _time(lambda: F.gemm(A, B, out, a_mn=a.a_mn, b_mn=a.b_mn, **kw), a.warmup, a.iters)
+    print(f"gemm {a.M}x{a.N}x{a.K} a_mn={a.a_mn} b_mn={a.b_mn} pair={not a.single} epilogue={a.epilogue}: {ms:.4f} ms "
           f"{2 * a.M * a.N * a.K / ms / 1e9:.0f} TFLOP/s status {int(ext.status().item())}")
 
 
@@ -68,6 +77,7 @@ def main(argv=None) -> None:
     g.add_argument("M", type=int), g.add_argument("N", type=int), g.add_argument("K", type=int)
     g.add_argument("--a-mn", action="store_true"), g.add_argument("--b-mn", action="store_true")
     g.add_argument("--single", action="store_true", help="one-CTA kernel only")
+    g.add_argument("--epilogue", default="none", choices=["none", "gelu", "dgelu", "dropadd"])
     t = sub.add_parser("attention")
     t.add_argument("B", type=int), t.add_argument("NH", type=int), t.add_argument("S", type=int)
     t.add_argument("HD", type=int), t.add_argument("--dropout", type=float, default=0.0)

@@ -11,8 +11,9 @@ bwd_reserved (MB)`` (profiler/op_profiler.py:461-487) plus ``fwd_overlap_comm, b
 How it measures (reference: profiler/op_profiler.py:283-459 uses wall clock around N calls and one sync):
   * a one-layer instance of the model is built for world size = tp (every op at (tp, dp = 1));
   * ops are visited in order; each op's inputs are the detached outputs of its predecessor;
-  * forward and backward are timed separately with CUDA events on the launching stream, after warm-up, median
-    of `--prof-repeat-times` runs; at tp > 1 the op's own collectives are inside the timed region;
+  * forward and backward are timed separately with CUDA events on the launching stream, after warm-up, as the
+    device time per call of `--prof-repeat-times` calls launched back to back (the queue stays full, as in a
+    training step); at tp > 1 the op's own collectives are inside the timed region;
   * ops that the runtime executes as one fused kernel when co-located (flash attention; GEMM + epilogue) are
     timed fused: the first member carries the time, the others carry 0, which is what the runtime will see;
   * memory columns come from torch.cuda.memory_allocated / max_memory_allocated deltas around the calls.
@@ -22,7 +23,6 @@ from __future__ import annotations
 import argparse
 import csv
 import os
-import statistics
 from typing import Dict, List
 
 import torch
@@ -53,17 +53,18 @@ def _tensor_mb(t) -> float:
 
 
 def _event_ms(fn, repeat: int, warmup: int) -> float:
+    """Device time per call of `repeat` calls launched back to back (the queue stays full, as in a training step,
+    so the launch latency of short kernels is not charged to the op)."""
     for _ in range(warmup):
         fn()
-    times = []
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
     for _ in range(repeat):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
         fn()
-        e1.record()
-        e1.synchronize()
-        times.append(e0.elapsed_time(e1))
-    return statistics.median(times)
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) / repeat
 
 
 def profile_plan(plan: dict, rank: int, world: int, overrides: dict, repeat: int, warmup: int, batch_fn) -> List[list]:
@@ -100,21 +101,23 @@ def profile_plan(plan: dict, rank: int, world: int, overrides: dict, repeat: int
             outs = [out[k] for k in op.writes if isinstance(out.get(k), torch.Tensor) and out[k].requires_grad]
             return out, outs
 
-        def timed_bwd():
-            out, outs = fwd_bwd_setup()
-            if not outs:
+        def timed_bwd(n):
+            """n backward passes launched back to back over n separately prepared forward graphs."""
+            prepared = [fwd_bwd_setup() for _ in range(n)]
+            if not prepared[0][1]:
                 return 0.0
-            grads = [torch.ones_like(o) if o.dim() == 0 else torch.randn_like(o) for o in outs]
+            grads = [[torch.ones_like(o) if o.dim() == 0 else torch.randn_like(o) for o in outs] for _, outs in prepared]
+            torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            torch.autograd.backward(outs, grads)
+            for (_, outs), g in zip(prepared, grads):
+                torch.autograd.backward(outs, g)
             e1.record()
             e1.synchronize()
-            return e0.elapsed_time(e1)
+            return e0.elapsed_time(e1) / n
 
-        for _ in range(warmup):
-            timed_bwd()
-        t_bwd = statistics.median([timed_bwd() for _ in range(repeat)])
+        timed_bwd(min(warmup, 2))
+        t_bwd = timed_bwd(repeat)
         store.zero_grad()
         # memory
         torch.cuda.synchronize()
