@@ -55,6 +55,7 @@ int attn_fwd_launch(const void* q, int ldq, const void* k, int ldk, const void* 
 int attn_bwd_launch(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const void* dout,
                     int lddo, const AttnParams& p, float* delta_scratch, cudaStream_t stream);
 int comm_max_blocks();
+void comm_set_peer_timeout_ns(unsigned long long ns);
 int allreduce_scale_f32_launch(void* const* peer_ptrs, void* mc_ptr, void* const* flag_ptrs, int rank, int world,
                                long long n, float scale, unsigned epoch, int* status, cudaStream_t stream);
 int bn_slices(long long rows);
@@ -670,4 +671,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("allreduce_scale_f32", &allreduce_scale_f32);
   m.def("comm_max_blocks", &comm_max_blocks);
   m.def("status", &status);
+  m.def("comm_set_peer_timeout_ms", [](double ms) { ssb::comm_set_peer_timeout_ns(static_cast<unsigned long long>(ms * 1e6)); });
 }

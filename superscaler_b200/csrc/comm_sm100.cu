@@ -18,7 +18,7 @@
 namespace ssb {
 namespace {
 
-constexpr uint64_t kPeerTimeLimitNs = 20ull * 1000 * 1000 * 1000;
+constexpr uint64_t kPeerTimeLimitNs = 20ull * 1000 * 1000 * 1000;  // default; see comm_set_peer_timeout_ns
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -30,7 +30,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 }
 
 // Returns false on timeout.  Called by every thread of the block (threads < world do the work).
-__device__ bool block_barrier(uint32_t* const* flag_ptrs, int rank, int world, uint32_t epoch, int* status) {
+__device__ bool block_barrier(uint32_t* const* flag_ptrs, int rank, int world, uint32_t epoch, int* status,
+                              uint64_t limit_ns) {
   __shared__ int failed;
   if (threadIdx.x == 0) failed = 0;
   __syncthreads();          // all data accesses of this block are issued
@@ -46,7 +47,7 @@ __device__ bool block_barrier(uint32_t* const* flag_ptrs, int rank, int world, u
       if ((it & 4095u) == 4095u) {
         const uint64_t now = global_timer_ns();
         if (t0 == 0) t0 = now;
-        else if (now - t0 > kPeerTimeLimitNs) break;
+        else if (now - t0 > limit_ns) break;
       }
     }
     if (!ok) {
@@ -80,13 +81,14 @@ struct AllReduceArgs {
   long long n;                 // elements (multiple of 4)
   float scale;
   uint32_t epoch;              // this call uses epoch and epoch + 1
+  uint64_t limit_ns;           // how long a block waits for a peer before it gives up
   int* status;
 };
 
 __global__ void __launch_bounds__(512)
 allreduce_scale_f32_kernel(AllReduceArgs a) {
   // every rank finished producing its buffer (stream order locally, flags across ranks)
-  if (!block_barrier(a.flag_ptrs, a.rank, a.world, a.epoch, a.status)) return;
+  if (!block_barrier(a.flag_ptrs, a.rank, a.world, a.epoch, a.status, a.limit_ns)) return;
   const long long n4 = a.n / 4;
   const long long per = (n4 + a.world - 1) / a.world;
   const long long lo = a.rank * per, hi = min(n4, lo + per);
@@ -109,13 +111,17 @@ allreduce_scale_f32_kernel(AllReduceArgs a) {
     }
   }
   // every rank finished writing its slice everywhere
-  block_barrier(a.flag_ptrs, a.rank, a.world, a.epoch + 1, a.status);
+  block_barrier(a.flag_ptrs, a.rank, a.world, a.epoch + 1, a.status, a.limit_ns);
 }
 
 }  // namespace
 
 constexpr int kCommBlocks = 64;
 int comm_max_blocks() { return kCommBlocks; }
+
+// Time a kernel waits for a peer before it records kStatusPeerTimeout and returns (process-wide; default 20 s).
+static uint64_t g_peer_limit_ns = kPeerTimeLimitNs;
+void comm_set_peer_timeout_ns(unsigned long long ns) { g_peer_limit_ns = ns ? ns : kPeerTimeLimitNs; }
 
 // peer_ptrs / flag_ptrs: device arrays of `world` pointers.  Flag buffers hold kCommBlocks * world uint32, zeroed
 // once at creation.  `epoch` must grow by 2 per call on every rank.
@@ -127,6 +133,7 @@ int allreduce_scale_f32_launch(void* const* peer_ptrs, void* mc_ptr, void* const
   a.mc_ptr = reinterpret_cast<float*>(mc_ptr);
   a.flag_ptrs = reinterpret_cast<uint32_t* const*>(flag_ptrs);
   a.rank = rank; a.world = world; a.n = n; a.scale = scale; a.epoch = epoch; a.status = status;
+  a.limit_ns = g_peer_limit_ns;
   allreduce_scale_f32_kernel<<<kCommBlocks, 512, 0, stream>>>(a);
   return static_cast<int>(cudaGetLastError());
 }

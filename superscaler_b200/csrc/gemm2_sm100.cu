@@ -36,14 +36,15 @@ constexpr int BM2 = 128;   // rows per CTA (256 per cluster)
 constexpr int BNH = 128;   // B rows staged per CTA (256 output columns per cluster)
 constexpr int BN2 = 256;
 constexpr int BK2 = 64;
-constexpr int kStages2 = 6;
+constexpr int kStages2 = 5;
 constexpr int kEpiWarps = 16;
 constexpr int kThreads2 = 64 + kEpiWarps * 32;
 constexpr int kGroupM2 = 8;
 constexpr int kABytes2 = BM2 * BK2 * 2;
 constexpr int kBBytes2 = BNH * BK2 * 2;
 constexpr int kStageBytes2 = kABytes2 + kBBytes2;
-constexpr int kSmem2 = kStages2 * kStageBytes2 + 1024 + 256;
+constexpr int kEpiStage = 32 * 128;                 // per epilogue warp: 32 rows x 64 bf16 columns, 128-byte swizzle
+constexpr int kSmem2 = kStages2 * kStageBytes2 + kEpiWarps * kEpiStage + 1024 + 256;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -130,7 +131,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kStages2 * kABytes2;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * kStageBytes2);
+  uint8_t* epi_stage = smem + kStages2 * kStageBytes2;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + kEpiWarps * kEpiStage);
   uint64_t* full_bar = bars;                       // leader's are used
   uint64_t* empty_bar = bars + kStages2;           // both CTAs
   uint64_t* tmem_full_bar = bars + 2 * kStages2;   // both CTAs
@@ -260,6 +262,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     // -------------------------------- epilogue --------------------------------
     const int quarter = warp & 3;
     const int grp = (warp - 2) >> 2;  // 64-column group of the 256-column tile
+    uint8_t* stg = epi_stage + (warp - 2) * kEpiStage;
     const uint32_t keep16 = dropout_keep16(p.dropout_p);
     const float drop_scale = p.dropout_p > 0.f ? 65536.0f / static_cast<float>(keep16) : 1.0f;
     int iter = 0;
@@ -268,17 +271,94 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       const TileCoord2 tc = tile_coord2(tile, num_m, num_n);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
+      const int row0 = tc.m_blk * 2 * BM2 + static_cast<int>(cta_rank) * BM2 + quarter * 32;  // first row of this warp
+      const int col0 = tc.n_blk * BN2 + grp * 64;                                              // first column
+      const int row = row0 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + grp * 64;
+      // Staged path: bf16 output, no accumulate, the warp's 64 columns inside the matrix, at most one row operand.
+      // Row operands enter and results leave through a 4 KB swizzled staging tile, so every global access of the
+      // warp is four full 128-byte row segments instead of 32 scattered 32-byte pieces.
+      const bool has_operand = p.residual != nullptr || p.act == kActDGelu || p.act == kActDRelu;
+      const bool staged = !p.out_fp32 && !p.accumulate && col0 + 64 <= p.N &&
+                          !(p.residual != nullptr && (p.act == kActDGelu || p.act == kActDRelu)) &&
+                          !(p.preact_out != nullptr && has_operand);
+      if (staged) {
+        const int srow = lane >> 3, spiece = lane & 7;  // coalesced phase: 4 rows x 8 sixteen-byte pieces per pass
+        auto cell = [&](int rr, int piece) { return stg + rr * 128 + ((piece ^ (rr & 7)) << 4); };
+        if (has_operand) {  // fetched while the tensor cores still work on this tile
+          const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.residual != nullptr ? p.residual : p.aux);
+          const int ld = p.residual != nullptr ? p.ldres : p.ldaux;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + srow;
+            if (row0 + rr < p.M)
+              *reinterpret_cast<uint4*>(cell(rr, spiece)) =
+                  __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(row0 + rr) * ld + col0) + spiece);
+          }
+          __syncwarp();
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        auto flush = [&](void* base, int ld) {  // staging tile -> global, 4 rows x 128 bytes per instruction
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + srow;
+            if (row0 + rr < p.M)
+              *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + static_cast<size_t>(row0 + rr) * ld + col0) +
+                spiece) = *reinterpret_cast<const uint4*>(cell(rr, spiece));
+          }
+          __syncwarp();
+        };
+        if (p.preact_out != nullptr) {  // first pass: the pre-activation tile
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[16];
+            tmem_ld_32x16(taddr + c * 16, r);
+            tmem_ld_wait();
+            const uint4 none[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+            float pre[16], v[16];
+            gemm_epilogue_math16(p, row, col0 + c * 16, r, none, keep16, drop_scale, pre, v);
+            *reinterpret_cast<uint4*>(cell(lane, 2 * c)) = pack8(pre);
+            *reinterpret_cast<uint4*>(cell(lane, 2 * c + 1)) = pack8(pre + 8);
+          }
+          flush(p.preact_out, p.ldpre);
+        }
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[16];
+          tmem_ld_32x16(taddr + c * 16, r);
+          tmem_ld_wait();
+          if (c == 3) {  // the accumulator stage is free once its last columns are in registers
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_smem(smem_u32(&tmem_empty_bar[acc]), 0));
+          }
+          uint4 operand[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+          if (has_operand) {
+            operand[0] = *reinterpret_cast<const uint4*>(cell(lane, 2 * c));
+            operand[1] = *reinterpret_cast<const uint4*>(cell(lane, 2 * c + 1));
+          }
+          float pre[16], v[16];
+          gemm_epilogue_math16(p, row, col0 + c * 16, r, operand, keep16, drop_scale, pre, v);
+          *reinterpret_cast<uint4*>(cell(lane, 2 * c)) = pack8(v);
+          *reinterpret_cast<uint4*>(cell(lane, 2 * c + 1)) = pack8(v + 8);
+        }
+        flush(p.D, p.ldd);
+        continue;
+      }
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag))) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      const int row = tc.m_blk * 2 * BM2 + static_cast<int>(cta_rank) * BM2 + quarter * 32 + lane;
-      const bool row_ok = row < p.M;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN2 + grp * 64;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
-        const int n0 = tc.n_blk * BN2 + grp * 64 + c * 16;
+        const int n0 = col0 + c * 16;
         if (n0 >= p.N) break;  // uniform across the warp
         uint32_t r[16];
         tmem_ld_32x16(taddr + c * 16, r);

@@ -161,4 +161,66 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& p, int row
   }
 }
 
+// Arithmetic part of the epilogue for 16 columns when the row operands (derivative input `aux` or `residual`) have
+// already been brought on chip: v = epilogue(acc) with the same order of operations as gemm_epilogue_chunk.
+// `operand` holds the 16 bf16 values of aux (for the derivative activations) or of the residual, or is unused.
+__device__ __forceinline__ void gemm_epilogue_math16(const GemmParams& p, int row, int n0, const uint32_t (&r)[16],
+                                                     const uint4 (&operand)[2], uint32_t keep16, float drop_scale,
+                                                     float (&pre)[16], float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+  if (p.bias != nullptr) {
+    if (p.bias_fp32) {
+      const float* b = reinterpret_cast<const float*>(p.bias) + n0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(b) + i);
+        v[4 * i] += q.x; v[4 * i + 1] += q.y; v[4 * i + 2] += q.z; v[4 * i + 3] += q.w;
+      }
+    } else {
+      const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + n0;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        float f[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(b) + i), f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[8 * i + e] += f[e];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) pre[i] = v[i];
+  float x[16];
+  if (p.act == kActDGelu || p.act == kActDRelu || p.residual != nullptr) {
+    unpack8(operand[0], x);
+    unpack8(operand[1], x + 8);
+  }
+  if (p.act == kActGelu) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = gelu_tanh(v[i]);
+  } else if (p.act == kActRelu) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
+  } else if (p.act == kActDGelu) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] *= gelu_tanh_grad(x[i]);
+  } else if (p.act == kActDRelu) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = x[i] > 0.f ? v[i] : 0.f;
+  }
+  if (p.dropout_p > 0.f) {
+    const uint64_t g0 = (static_cast<uint64_t>(row) * static_cast<uint64_t>(p.N) + n0) >> 2;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint32_t m = dropout_keep4(p.dropout_seed, g0 + g, keep16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[4 * g + i] = ((m >> i) & 1u) ? v[4 * g + i] * drop_scale : 0.f;
+    }
+  }
+  if (p.residual != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] += x[i];
+  }
+}
+
 }  // namespace ssb

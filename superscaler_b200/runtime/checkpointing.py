@@ -27,6 +27,17 @@ from ..ops import functional as F
 TRACKER = "latest_checkpointed_iteration.txt"
 
 
+class CheckpointError(RuntimeError):
+    """A checkpoint file is missing, truncated or unreadable; the message names the file."""
+
+
+def _load_file(path: str):
+    try:
+        return torch.load(path, map_location="cpu", weights_only=False)
+    except Exception as e:  # noqa: BLE001 - zip / pickle errors of a damaged shard
+        raise CheckpointError(f"cannot read checkpoint shard {path}: {type(e).__name__}: {e}") from e
+
+
 def checkpoint_dir(root: str, iteration, tp_rank: int, pp_rank: int, pp_size: int) -> str:
     tag = "release" if iteration == "release" else "iter_{:07d}".format(iteration)
     sub = "mp_rank_{:02d}".format(tp_rank) if pp_size == 1 else "mp_rank_{:02d}_{:03d}".format(tp_rank, pp_rank)
@@ -98,7 +109,7 @@ def load_checkpoint(trainer, root: str, load_optim: bool = True, load_rng: bool 
     first = trainer.infos[0]
     pl = ps.placement(first.tp, first.dp)
     path = os.path.join(checkpoint_dir(root, it, pl.tp_rank, ps.stage, ps.num_stages), "model_optim_rng.pt")
-    sd = torch.load(path, map_location="cpu", weights_only=False)
+    sd = _load_file(path)
     if sd.get("plan") is not None and sd["plan"]["num_ops_in_each_stage"] != trainer.plan["num_ops_in_each_stage"]:
         raise RuntimeError("checkpoint was written under a different stage split; use load_under_plan()")
     names = _local_names(trainer)
@@ -126,7 +137,7 @@ def merge_tp_shards(root: str, iteration) -> Dict[str, torch.Tensor]:
     pieces: Dict[str, Dict[int, torch.Tensor]] = {}
     meta: Dict[str, dict] = {}
     for sub in sorted(os.listdir(base)):
-        sd = torch.load(os.path.join(base, sub, "model_optim_rng.pt", ), map_location="cpu", weights_only=False)
+        sd = _load_file(os.path.join(base, sub, "model_optim_rng.pt"))
         lo = min(sd["op_names"])
         for name, t in sd["model"].items():
             _, _, idx, rest = name.split(".", 3)

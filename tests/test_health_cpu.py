@@ -1,0 +1,95 @@
+"""Failure detection without any GPU fault: host-side heartbeat / failure store, a rank that raises in a gloo job,
+a dropped flag in the model of the kernels' epoch-flag protocol, a corrupted checkpoint shard."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from dist_utils import run_ranks
+from helpers import tiny_gpt_plan
+from superscaler_b200.parallel import flag_protocol as fp
+from superscaler_b200.runtime import checkpointing
+from superscaler_b200.runtime.health import DictStore, HealthMonitor, PeerFailure
+
+
+def test_monitor_reports_published_failure_and_stale_heartbeat():
+    store, now = DictStore(), [0.0]
+    a = HealthMonitor(store, 0, 2, stale_after_s=10, clock=lambda: now[0])
+    b = HealthMonitor(store, 1, 2, stale_after_s=10, clock=lambda: now[0])
+    a.beat(0)
+    b.beat(0)
+    now[0] = 5.0
+    b.beat(1)
+    a.beat(1)                       # peer made progress: fine
+    now[0] = 30.0
+    with pytest.raises(PeerFailure, match="stuck at step 1"):
+        a.beat(2)                   # rank 1 silent for 25 s
+    with pytest.raises(ValueError):
+        with b.guard():
+            raise ValueError("boom")
+    with pytest.raises(PeerFailure, match="ValueError: boom") as e:
+        a.check_peers()
+    assert e.value.rank == 1
+
+
+def test_monitor_reports_rank_that_never_joins():
+    store, now = DictStore(), [0.0]
+    a = HealthMonitor(store, 0, 2, stale_after_s=10, clock=lambda: now[0])
+    a.beat(0)
+    now[0] = 11.0
+    with pytest.raises(PeerFailure, match="never published"):
+        a.beat(1)
+
+
+def _failing_job(rank, world, fail_rank):
+    store = dist.distributed_c10d._get_default_store()
+    mon = HealthMonitor(store, rank, world, stale_after_s=30)
+    x = torch.ones(4)
+    seen = None
+    try:
+        for step in range(6):
+            mon.beat(step)                       # before the collective of this step
+            with mon.guard():
+                if rank == fail_rank and step == 2:
+                    raise RuntimeError("injected failure")
+                # the failing rank leaves between steps; the others must not enter the next collective with it
+                if step < 2:
+                    dist.all_reduce(x)
+                else:
+                    import time
+                    time.sleep(0.3)              # give the failure time to be published
+    except PeerFailure as e:
+        seen = (e.rank, e.reason)
+    except RuntimeError as e:
+        assert rank == fail_rank and "injected" in str(e)
+        seen = "self"
+    assert seen == "self" if rank == fail_rank else (seen is not None and seen[0] == fail_rank and "injected" in seen[1]), seen
+
+
+def test_survivors_learn_of_a_failed_rank_before_the_next_collective():
+    run_ranks(_failing_job, 3, 1, timeout=120)
+
+
+def test_dropped_flag_times_out_and_later_epochs_recover():
+    lost = {(1, 0, 0, 3)}          # rank 0's arrival at rank 1 is lost in epoch 3
+    board = fp.FlagBoard(drop=lambda o, s, p, e: (o, s, p, e) in lost)
+    assert fp.barrier(board, 2, 0, 1) == {0: fp.OK, 1: fp.OK}
+    st = fp.barrier(board, 2, 0, 3, limit=50)
+    assert st == {0: fp.OK, 1: fp.PEER_TIMEOUT}
+    # a stale flag (epoch 1) never satisfied the wait for epoch 3, and epoch 5 works again
+    assert fp.barrier(board, 2, 0, 5) == {0: fp.OK, 1: fp.OK}
+    # a late flag of an old epoch is harmless
+    board.post(1, 0, 0, 3)
+    assert board.flags[(1, 0, 0)] == 5
+
+
+def test_corrupted_checkpoint_shard_is_reported(tmp_path):
+    from superscaler_b200.runtime.trainer import Trainer
+    t = Trainer(tiny_gpt_plan(), model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0), lr_warmup_steps=0,
+                device="cpu")
+    path = checkpointing.save_checkpoint(t, str(tmp_path))
+    with open(path, "r+b") as f:
+        f.truncate(os.path.getsize(path) // 2)
+    with pytest.raises(checkpointing.CheckpointError, match="model_optim_rng.pt"):
+        checkpointing.load_checkpoint(t, str(tmp_path))

@@ -74,6 +74,49 @@ def test_gemm_epilogues():
     assert rel(out, 0.5 * (A.float() @ B.float().t()) + bias.float()) < 6e-3
 
 
+@pytest.mark.parametrize("epi", ["plain", "bias_gelu_preact", "dgelu", "drop_residual", "fp32_accumulate"])
+def test_pair_gemm_epilogues_match_one_cta_kernel(epi):
+    """The two-SM kernel (staged, coalesced epilogue) against the one-CTA kernel on a ragged shape that exercises
+    full 64-column groups, a partly filled last N tile and a partly filled last M tile."""
+    ext = native.ext()
+    torch.manual_seed(31)
+    M, N, K = 2500, 2112, 512
+    A = torch.randn(M, K, device=DEV).bfloat16()
+    B = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    kw, outs = {}, ["out"]
+    if epi == "bias_gelu_preact":
+        kw = dict(bias=torch.randn(N, device=DEV).bfloat16(), act=F.ACT_GELU)
+        outs.append("pre")
+    elif epi == "dgelu":
+        kw = dict(act=F.ACT_DGELU, aux=torch.randn(M, N, device=DEV).bfloat16())
+    elif epi == "drop_residual":
+        kw = dict(bias=torch.randn(N, device=DEV), dropout_p=0.1, seed=5, residual=torch.randn(M, N, device=DEV).bfloat16())
+    res = {}
+    try:
+        for mode in (0, 1):
+            ext.gemm_set_pair_mode(mode)
+            if epi == "fp32_accumulate":
+                out = torch.ones(M, N, device=DEV, dtype=torch.float32)
+                F.gemm(A, B, out, accumulate=True)
+            else:
+                pre = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16) if "pre" in outs else None
+                out = F.gemm(A, B, preact_out=pre, **kw)
+                if pre is not None:
+                    res[("pre", mode)] = pre
+            res[("out", mode)] = out
+    finally:
+        ext.gemm_set_pair_mode(1)
+    torch.cuda.synchronize()
+    assert native.check_status() == 0
+    for name in outs:
+        a, b = res[(name, 0)].float(), res[(name, 1)].float()
+        # same math, but the compiler may contract multiply-adds differently in the two kernels
+        assert (a - b).abs().max().item() <= 4e-3 * b.abs().max().item(), f"{epi}/{name}: {(a - b).abs().max().item()}"
+    ref = A.float() @ B.float().t()
+    if epi == "plain":
+        assert rel(res[("out", 1)], ref) < 1e-2
+
+
 def test_gemm_dropout_matches_elementwise_mask():
     torch.manual_seed(3)
     M, N, K = 256, 512, 128
@@ -320,3 +363,31 @@ def test_lm_head_cross_entropy_autograd():
     ref.backward()
     assert abs(loss.item() - ref.item()) < 2e-2
     assert rel(x.grad, xr.grad) < 3e-2 and rel(W.grad, wr.grad) < 3e-2
+
+
+def test_peer_wait_times_out_with_status_when_signal_is_withheld():
+    """A collective kernel whose peer never posts its flag must return within its time limit and report
+    kStatusPeerTimeout; the context stays usable.  The 'peer' is a second set of local buffers that nothing writes."""
+    import time
+    ext = native.ext()
+    n = 1 << 16
+    bufs = [torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)]
+    flags = [torch.zeros(ext.comm_max_blocks() * 2, device=DEV, dtype=torch.int32) for _ in range(2)]
+    peer_ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=DEV)
+    flag_ptrs = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=DEV)
+    torch.cuda.synchronize()
+    assert native.check_status() == 0
+    ext.comm_set_peer_timeout_ms(200.0)
+    try:
+        t0 = time.time()
+        ext.allreduce_scale_f32(peer_ptrs, 0, flag_ptrs, 0, 2, n, 1.0, 1)     # rank 0 of 2; rank 1 never arrives
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 10.0
+        assert int(ext.status().item()) == 2                                   # kStatusPeerTimeout
+    finally:
+        ext.comm_set_peer_timeout_ms(0.0)                                      # back to the default
+        ext.status().zero_()
+    # the context is intact: a normal kernel still runs
+    a = torch.randn(256, 128, device=DEV).bfloat16()
+    assert torch.isfinite(F.gemm(a, a).float()).all()
+    assert native.check_status() == 0
