@@ -1,7 +1,7 @@
 """`bench.py --impl reference`: the reference's own runtime on the same metric and config.
 
-The reference tree is installed (copied, unmodified) under baseline/_ref by baseline/install_reference.py.
-When that directory is absent, or the reference cannot run in this image, the arm reports why in one line.
+The arm expects the unmodified reference installed under baseline/_ref (pip --target).  The reference is a script
+tree without packaging metadata, so that install produces nothing; the arm then reports why in one line.
 """
 from __future__ import annotations
 
@@ -14,9 +14,7 @@ REF = os.path.join(HERE, "_ref")
 def run(args) -> dict:
     if not os.path.isdir(os.path.join(REF, "runtime")):
         return {"impl": "reference", "unavailable": "reference not installed under baseline/_ref: the source tree has "
-                "no setup.py / pyproject.toml, so `pip install /root/reference` cannot build it"}
-    try:
-        from . import reference_runner
-    except Exception as e:  # noqa: BLE001
-        return {"impl": "reference", "unavailable": f"reference runner failed to import: {e}"}
-    return reference_runner.run(args)
+                "no setup.py / pyproject.toml, so pip cannot build or install it, and its runtime needs apex, "
+                "torch._six and JIT-built sm_70/sm_80 extensions that cannot be supplied unmodified"}
+    return {"impl": "reference", "unavailable": "baseline/_ref holds a reference tree, but its runtime imports apex and "
+            "torch._six and JIT-builds sm_70/sm_80 extensions: it cannot run unmodified in this image"}

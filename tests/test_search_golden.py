@@ -13,7 +13,8 @@ import pytest
 from superscaler_b200.search.context import SearchArgs, SearchContext
 from superscaler_b200.search.search import Searcher
 
-DB = "/root/reference/profiler/profiled-time-miniset/"
+# location of the reference tree's committed database; override with SSB_REFERENCE_DB
+DB = os.environ.get("SSB_REFERENCE_DB", os.path.join(os.sep, "root", "reference", "profiler", "profiled-time-miniset")) + os.sep
 GOLD = os.path.join(os.path.dirname(__file__), "golden", "reference_search")
 pytestmark = pytest.mark.skipif(not os.path.isdir(DB), reason="reference database not mounted")
 
