@@ -308,8 +308,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (kv >= kv_len || (p.causal && kv > q)) rr[i] = 0xff800000u;  // -inf
         }
       }
+      {  // four independent chains: a single running maximum would serialise 32 dependent instructions
+        float m0 = __uint_as_float(rr[0]), m1 = __uint_as_float(rr[1]), m2 = __uint_as_float(rr[2]), m3 = __uint_as_float(rr[3]);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(rr[i]));
+        for (int i = 4; i < 32; i += 4) {
+          m0 = fmaxf(m0, __uint_as_float(rr[i]));
+          m1 = fmaxf(m1, __uint_as_float(rr[i + 1]));
+          m2 = fmaxf(m2, __uint_as_float(rr[i + 2]));
+          m3 = fmaxf(m3, __uint_as_float(rr[i + 3]));
+        }
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      }
       // exchange the partial maxima of the four owners of this row
       float* xm = xmax + st * 512;
       xm[g * 128 + r] = mx;
@@ -320,7 +329,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const float m_use = (mx == -INFINITY) ? 0.f : mx;  // fully masked so far: keep exponents finite
       const float alpha = ex2((m - m_use) * c);         // m = -inf -> 0
       const float mc = m_use * c;
-      float rowsum = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t w[16];
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
@@ -328,7 +337,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           pe[e] = ex2(__uint_as_float(rr[i + e]) * c - mc);  // masked entries: ex2(-inf) = 0
-          rowsum += pe[e];
+          rs4[e] += pe[e];                                   // four partial sums: no 32-long dependent chain
         }
         if (p.dropout_p > 0.f) {
           const uint32_t h = attn_quad_hash(bh_seed, q, quads_per_row, (kv0 + i) >> 2);
@@ -352,7 +361,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_arrive(&o_empty[(j - 1) & 1]);
       }
       alpha_pending = alpha;
-      l = l * alpha + rowsum;
+      l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
       m = mx;
     }
     ok = __all_sync(0xffffffffu, ok);
