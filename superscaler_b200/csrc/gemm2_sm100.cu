@@ -22,6 +22,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "gemm_ag_sm100.cuh"
 #include "gemm_epilogue.cuh"
 #include "gemm_sm100.cuh"
 
@@ -36,15 +37,18 @@ constexpr int BM2 = 128;   // rows per CTA (256 per cluster)
 constexpr int BNH = 128;   // B rows staged per CTA (256 output columns per cluster)
 constexpr int BN2 = 256;
 constexpr int BK2 = 64;
-constexpr int kStages2 = 5;
+constexpr int kStagesPlain = 5;
+constexpr int kStagesGather = 4;                 // one stage (32 KB) becomes the pusher's staging area
+constexpr int kPushChunk2 = 16384;
 constexpr int kEpiWarps = 16;
 constexpr int kThreads2 = 64 + kEpiWarps * 32;
+constexpr int kThreadsGather = kThreads2 + 32;    // + pusher warp
 constexpr int kGroupM2 = 8;
 constexpr int kABytes2 = BM2 * BK2 * 2;
 constexpr int kBBytes2 = BNH * BK2 * 2;
 constexpr int kStageBytes2 = kABytes2 + kBBytes2;
 constexpr int kEpiStage = 32 * 128;                 // per epilogue warp: 32 rows x 64 bf16 columns, 128-byte swizzle
-constexpr int kSmem2 = kStages2 * kStageBytes2 + kEpiWarps * kEpiStage + 1024 + 256;
+constexpr int kSmem2 = kStagesPlain * kStageBytes2 + kEpiWarps * kEpiStage + 1024 + 256;  // both variants
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -108,6 +112,25 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
+// Bounded wait (one thread) until *flag >= epoch.
+__device__ __forceinline__ bool wait_flag_one(const uint32_t* flag, uint32_t epoch, volatile int* abort_flag, int* status) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0; it < (1u << 30); ++it) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= epoch) return true;
+    if ((it & 1023u) == 1023u) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 20ull * 1000 * 1000 * 1000) break;
+    }
+  }
+  *abort_flag = 1;
+  if (status != nullptr) atomicMax(status, static_cast<int>(kStatusPeerTimeout));
+  return false;
+}
+
 struct TileCoord2 {
   int m_blk, n_blk;
 };
@@ -123,21 +146,28 @@ __device__ __forceinline__ TileCoord2 tile_coord2(int tile, int num_m, int num_n
   return c;
 }
 
-template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kThreads2, 1)
-gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                  const GemmParams p) {
+// GATHER = true: the all-gather of A's rows over the tensor-parallel group is part of the kernel (see
+// gemm_ag_sm100.cu for the protocol): tma_a addresses this rank's own rows, tma_a2 the local gather buffer, output
+// tiles are ordered own rows first, the producer waits for the "arrived" flag of a 128-row block before loading it,
+// and warp 18 pushes this rank's rows to every peer.
+template <bool A_MN, bool B_MN, bool GATHER>
+__global__ void __launch_bounds__(GATHER ? kThreadsGather : kThreads2, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_a2,
+                  const __grid_constant__ CUtensorMap tma_b, const GemmParams p, const GemmAgComm cm) {
+  constexpr int kStages2 = GATHER ? kStagesGather : kStagesPlain;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kStages2 * kABytes2;
-  uint8_t* epi_stage = smem + kStages2 * kStageBytes2;
+  uint8_t* push_buf = smem + kStages2 * kStageBytes2;              // GATHER only: 2 x 16 KB
+  uint8_t* epi_stage = push_buf + (GATHER ? 2 * kPushChunk2 : 0);
   uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + kEpiWarps * kEpiStage);
   uint64_t* full_bar = bars;                       // leader's are used
   uint64_t* empty_bar = bars + kStages2;           // both CTAs
   uint64_t* tmem_full_bar = bars + 2 * kStages2;   // both CTAs
   uint64_t* tmem_empty_bar = bars + 2 * kStages2 + 2;  // leader's are used
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages2 + 4);
+  uint64_t* push_bar = bars + 2 * kStages2 + 4;  // 2 (GATHER only)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages2 + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -160,6 +190,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tmem_full_bar[s], 1);
       mbar_init(&tmem_empty_bar[s], 2 * kEpiWarps);
+      mbar_init(&push_bar[s], 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -176,6 +207,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // GATHER: logical pair-block i (the order tiles are computed in) -> source rank and actual pair-block
+  const int pb_per_rank = GATHER ? max(1, num_m / cm.tp) : 1;
+  auto src_of = [&](int i) { return GATHER ? (cm.rank + i / pb_per_rank) % cm.tp : 0; };
+  auto pblk_of = [&](int i) { return GATHER ? src_of(i) * pb_per_rank + i % pb_per_rank : i; };
+
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (elect_one()) {
@@ -184,8 +220,19 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const TileCoord2 tc = tile_coord2(tile, num_m, num_n);
-        const int m0 = tc.m_blk * 2 * BM2 + static_cast<int>(cta_rank) * BM2;
+        int m0 = pblk_of(tc.m_blk) * 2 * BM2 + static_cast<int>(cta_rank) * BM2;
         const int n0 = tc.n_blk * BN2 + static_cast<int>(cta_rank) * BNH;
+        const CUtensorMap* ta = &tma_a;
+        if (GATHER) {
+          if (src_of(tc.m_blk) == cm.rank) {
+            m0 -= cm.rank * pb_per_rank * 2 * BM2;  // own rows: read straight from the local shard
+          } else {
+            // rows pushed by another rank: wait for this CTA's 128-row block, then order the TMA reads after it
+            if (!wait_flag_one(cm.flag_ptrs[cm.rank] + m0 / BM2, cm.epoch, abort_flag, p.status)) { ok = false; break; }
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            ta = &tma_a2;
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             ok = false;
@@ -196,10 +243,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           uint8_t* sa = smem_a + stage * kABytes2;
           uint8_t* sb = smem_b + stage * kBBytes2;
           if (!A_MN) {
-            tma_load_2d_pair(sa, &tma_a, bar, kb * BK2, m0);
+            tma_load_2d_pair(sa, ta, bar, kb * BK2, m0);
           } else {
 #pragma unroll
-            for (int c = 0; c < BM2 / 64; ++c) tma_load_2d_pair(sa + c * (64 * BK2 * 2), &tma_a, bar, m0 + c * 64, kb * BK2);
+            for (int c = 0; c < BM2 / 64; ++c) tma_load_2d_pair(sa + c * (64 * BK2 * 2), ta, bar, m0 + c * 64, kb * BK2);
           }
           if (!B_MN) {
             tma_load_2d_pair(sb, &tma_b, bar, kb * BK2, n0);
@@ -258,7 +305,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         if (ok) umma_commit_pair(&tmem_full_bar[acc]);
       }
     }
-  } else {
+  } else if (warp < 2 + kEpiWarps) {
     // -------------------------------- epilogue --------------------------------
     const int quarter = warp & 3;
     const int grp = (warp - 2) >> 2;  // 64-column group of the 256-column tile
@@ -271,7 +318,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       const TileCoord2 tc = tile_coord2(tile, num_m, num_n);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
-      const int row0 = tc.m_blk * 2 * BM2 + static_cast<int>(cta_rank) * BM2 + quarter * 32;  // first row of this warp
+      const int row0 = pblk_of(tc.m_blk) * 2 * BM2 + static_cast<int>(cta_rank) * BM2 + quarter * 32;  // first row of this warp
       const int col0 = tc.n_blk * BN2 + grp * 64;                                              // first column
       const int row = row0 + lane;
       const bool row_ok = row < p.M;
@@ -370,6 +417,56 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_smem(smem_u32(&tmem_empty_bar[acc]), 0));
     }
+  } else if (GATHER) {
+    // --------------------------------- pusher ---------------------------------
+    // Copies this rank's rows, 128-row block by block (CTA c takes blocks c, c + grid, ...), through a double-
+    // buffered 16 KB staging area into the same rows of every peer's gather buffer, then flags the block there.
+    if (lane == 0 && cm.tp > 1) {
+      const size_t blk_bytes = static_cast<size_t>(BM2) * p.K * 2;  // shard and gather buffers are dense
+      const uint8_t* x = reinterpret_cast<const uint8_t*>(cm.x_local);
+      const int blocks_per_rank = pb_per_rank * 2;
+      const int pieces_per_blk = static_cast<int>(blk_bytes / kPushChunk2);
+      int my_blocks = 0;
+      for (int b = blockIdx.x; b < blocks_per_rank; b += gridDim.x) ++my_blocks;
+      const int total = my_blocks * pieces_per_blk;
+      auto issue_load = [&](int j) {
+        const int b = blockIdx.x + (j / pieces_per_blk) * gridDim.x;
+        mbar_arrive_expect_tx(&push_bar[j & 1], kPushChunk2);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         smem_u32(push_buf + (j & 1) * kPushChunk2)),
+                     "l"(x + static_cast<size_t>(b) * blk_bytes + static_cast<size_t>(j % pieces_per_blk) * kPushChunk2),
+                     "r"(kPushChunk2), "r"(smem_u32(&push_bar[j & 1]))
+                     : "memory");
+      };
+      bool okp = true;
+      if (total > 0) issue_load(0);
+      for (int j = 0; j < total && okp; ++j) {
+        if (j + 1 < total) {
+          tma_store_wait_read<0>();  // the stores of piece j - 1 have left the other buffer
+          issue_load(j + 1);
+        }
+        if (!mbar_wait(&push_bar[j & 1], (j >> 1) & 1, abort_flag)) { okp = false; break; }
+        const int b = blockIdx.x + (j / pieces_per_blk) * gridDim.x;
+        const size_t dst_off = (static_cast<size_t>(cm.rank) * blocks_per_rank + b) * blk_bytes +
+                               static_cast<size_t>(j % pieces_per_blk) * kPushChunk2;
+        for (int pr = 0; pr < cm.tp; ++pr)
+          if (pr != cm.rank)
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                             reinterpret_cast<uint8_t*>(cm.gather_ptrs[pr]) + dst_off),
+                         "r"(smem_u32(push_buf + (j & 1) * kPushChunk2)), "r"(kPushChunk2)
+                         : "memory");
+        tma_store_commit();
+        if (j % pieces_per_blk == pieces_per_blk - 1) {
+          tma_store_wait<0>();  // the whole block has been written on every peer
+          for (int pr = 0; pr < cm.tp; ++pr)
+            if (pr != cm.rank)
+              asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(cm.flag_ptrs[pr] + cm.rank * blocks_per_rank + b),
+                           "r"(cm.epoch)
+                           : "memory");
+        }
+      }
+      tma_store_wait<0>();
+    }
   }
 
   // ------------------------------- teardown ----------------------------------
@@ -392,29 +489,38 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   }
 }
 
-template <bool A_MN, bool B_MN>
-int launch_pair(const void* A, int lda, const void* B, int ldb, const GemmParams& p, int num_sms, cudaStream_t stream) {
-  CUtensorMap ta, tb;
+template <bool A_MN, bool B_MN, bool GATHER>
+int launch_pair(const void* A, int lda, const void* B, int ldb, const GemmParams& p, const GemmAgComm& cm, int num_sms,
+                cudaStream_t stream) {
+  CUtensorMap ta, ta2, tb;
   int rc;
-  rc = !A_MN ? make_tma_2d_bf16(&ta, A, p.M, p.K, lda, BM2, BK2) : make_tma_2d_bf16(&ta, A, p.K, p.M, lda, BK2, 64);
+  if (GATHER) {  // A = this rank's rows [M / tp][K]; the gather buffer holds all M rows
+    rc = make_tma_2d_bf16(&ta, A, p.M / cm.tp, p.K, lda, BM2, BK2);
+    if (rc != 0) return rc;
+    rc = make_tma_2d_bf16(&ta2, cm.gather_ptrs_host_local, p.M, p.K, p.K, BM2, BK2);
+  } else {
+    rc = !A_MN ? make_tma_2d_bf16(&ta, A, p.M, p.K, lda, BM2, BK2) : make_tma_2d_bf16(&ta, A, p.K, p.M, lda, BK2, 64);
+    ta2 = ta;
+  }
   if (rc != 0) return rc;
   rc = !B_MN ? make_tma_2d_bf16(&tb, B, p.N, p.K, ldb, BNH, BK2) : make_tma_2d_bf16(&tb, B, p.K, p.N, ldb, BK2, 64);
   if (rc != 0) return rc;
-  auto kernel = gemm2_bf16_kernel<A_MN, B_MN>;
+  auto kernel = gemm2_bf16_kernel<A_MN, B_MN, GATHER>;
+  constexpr int threads = GATHER ? kThreadsGather : kThreads2;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
   static int max_clusters = 0;
   if (max_clusters == 0) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
     if (e != cudaSuccess) return static_cast<int>(e);
     cudaLaunchConfig_t q = {};
     q.gridDim = dim3(num_sms & ~1);
-    q.blockDim = dim3(kThreads2);
+    q.blockDim = dim3(threads);
     q.dynamicSmemBytes = kSmem2;
-    cudaLaunchAttribute qa[1];
-    qa[0].id = cudaLaunchAttributeClusterDimension;
-    qa[0].val.clusterDim.x = 2;
-    qa[0].val.clusterDim.y = 1;
-    qa[0].val.clusterDim.z = 1;
-    q.attrs = qa;
+    q.attrs = attr;
     q.numAttrs = 1;
     int n = 0;
     e = cudaOccupancyMaxActiveClusters(&n, kernel, &q);
@@ -430,17 +536,12 @@ int launch_pair(const void* A, int lda, const void* B, int ldb, const GemmParams
   if (clusters > num_tiles) clusters = num_tiles;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * clusters);
-  cfg.blockDim = dim3(kThreads2);
+  cfg.blockDim = dim3(threads);
   cfg.dynamicSmemBytes = kSmem2;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p));
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, ta, ta2, tb, p, cm));
 }
 
 }  // namespace
@@ -448,10 +549,19 @@ int launch_pair(const void* A, int lda, const void* B, int ldb, const GemmParams
 // Same contract as gemm_bf16_launch; callers pick this variant for outputs of at least 256 x 256.
 int gemm2_bf16_launch(const void* A, int lda, int a_mn_major, const void* B, int ldb, int b_mn_major,
                       const GemmParams& p, int num_sms, cudaStream_t stream) {
-  if (!a_mn_major && !b_mn_major) return launch_pair<false, false>(A, lda, B, ldb, p, num_sms, stream);
-  if (!a_mn_major && b_mn_major) return launch_pair<false, true>(A, lda, B, ldb, p, num_sms, stream);
-  if (a_mn_major && b_mn_major) return launch_pair<true, true>(A, lda, B, ldb, p, num_sms, stream);
-  return launch_pair<true, false>(A, lda, B, ldb, p, num_sms, stream);
+  const GemmAgComm none{};
+  if (!a_mn_major && !b_mn_major) return launch_pair<false, false, false>(A, lda, B, ldb, p, none, num_sms, stream);
+  if (!a_mn_major && b_mn_major) return launch_pair<false, true, false>(A, lda, B, ldb, p, none, num_sms, stream);
+  if (a_mn_major && b_mn_major) return launch_pair<true, true, false>(A, lda, B, ldb, p, none, num_sms, stream);
+  return launch_pair<true, false, false>(A, lda, B, ldb, p, none, num_sms, stream);
+}
+
+// All-gather fused into the GEMM on the two-SM kernel.  Returns -100 when the shape does not fit this variant
+// (rows per rank not a multiple of 256, narrow output): the caller then uses the one-CTA kernel of gemm_ag_sm100.cu.
+int gemm2_ag_launch(const void* W, int ldw, const GemmParams& p, const GemmAgComm& cm, int num_sms, cudaStream_t stream) {
+  const int rows_local = p.M / cm.tp;
+  if (rows_local % (2 * BM2) || p.N < BN2 || (static_cast<size_t>(BM2) * p.K * 2) % kPushChunk2) return -100;
+  return launch_pair<false, false, true>(cm.x_local, p.K, W, ldw, p, cm, num_sms, stream);
 }
 
 }  // namespace ssb

@@ -304,10 +304,16 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tma_local, const __grid_const
 // x_local: this rank's rows [M / tp][K] bf16, dense.  W: [N][K] bf16 (K contiguous).  p.M is the gathered row count
 // (tp x rows per rank, rows per rank a multiple of 128); p describes the epilogue and the local output [M][N].
 // K must be a multiple of 64 and the rows of a 128-row block (128 x K x 2 bytes) a multiple of 16 KB.
+int gemm2_ag_launch(const void* W, int ldw, const GemmParams& p, const GemmAgComm& cm, int num_sms, cudaStream_t stream);
+
 int gemm_ag_launch(const void* W, int ldw, const GemmParams& p, const GemmAgComm& cm, int num_sms, cudaStream_t stream) {
   if (p.M <= 0 || p.N <= 0 || p.K <= 0 || cm.tp < 1 || cm.tp > 32) return -2;
   if (p.M % (BM * cm.tp) || (p.K % 64) || (ldw % 8)) return -3;
   if (static_cast<long long>(p.M) * p.K > cm.capacity_elems || p.M / BM > cm.max_blocks) return -6;
+  {  // large shapes run on the two-SM kernel
+    const int rc2 = gemm2_ag_launch(W, ldw, p, cm, num_sms, stream);
+    if (rc2 != -100) return rc2;
+  }
   const int rows_local = p.M / cm.tp;
   CUtensorMap tl, tg, tb;
   int rc = make_tma_2d_bf16(&tl, cm.x_local, rows_local, p.K, p.K, BM, BK);

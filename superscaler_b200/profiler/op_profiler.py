@@ -13,6 +13,7 @@ How it measures (reference: profiler/op_profiler.py:283-459 uses wall clock arou
   * ops are visited in order; each op's inputs are the detached outputs of its predecessor;
   * forward and backward are timed separately with CUDA events on the launching stream, after warm-up, as the
     device time per call of `--prof-repeat-times` calls launched back to back (the queue stays full, as in a
+    training step) with the L2 cache flushed before every call (inputs and weights come from HBM, as in a
     training step); at tp > 1 the op's own collectives are inside the timed region;
   * ops that the runtime executes as one fused kernel when co-located (flash attention; GEMM + epilogue) are
     timed fused: the first member carries the time, the others carry 0, which is what the runtime will see;
@@ -52,19 +53,38 @@ def _tensor_mb(t) -> float:
     return t.numel() * t.element_size() / MB if isinstance(t, torch.Tensor) else 0.0
 
 
-def _event_ms(fn, repeat: int, warmup: int) -> float:
-    """Device time per call of `repeat` calls launched back to back (the queue stays full, as in a training step,
-    so the launch latency of short kernels is not charged to the op)."""
-    for _ in range(warmup):
-        fn()
+_L2_FLUSH = None
+
+
+def _flush_l2() -> None:
+    """Overwrites a buffer twice the size of the L2 cache, so that the next call finds its inputs and weights in
+    HBM as it does inside a training step (where thousands of other kernels ran since they were produced)."""
+    global _L2_FLUSH
+    if _L2_FLUSH is None:
+        _L2_FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _L2_FLUSH.zero_()
+
+
+def _span_ms(body, n: int) -> float:
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(repeat):
-        fn()
+    for i in range(n):
+        body(i)
     e1.record()
     e1.synchronize()
-    return e0.elapsed_time(e1) / repeat
+    return e0.elapsed_time(e1) / n
+
+
+def _event_ms(fn, repeat: int, warmup: int) -> float:
+    """Device time per call of `repeat` calls launched back to back (the queue stays full, as in a training step,
+    so the launch latency of short kernels is not charged to the op), each preceded by an L2 flush whose own time
+    is measured the same way and subtracted."""
+    for _ in range(warmup):
+        fn()
+    flush = _span_ms(lambda i: _flush_l2(), repeat)
+    both = _span_ms(lambda i: (_flush_l2(), fn()), repeat)
+    return max(both - flush, 0.0)
 
 
 def profile_plan(plan: dict, rank: int, world: int, overrides: dict, repeat: int, warmup: int, batch_fn) -> List[list]:
@@ -102,19 +122,19 @@ def profile_plan(plan: dict, rank: int, world: int, overrides: dict, repeat: int
             return out, outs
 
         def timed_bwd(n):
-            """n backward passes launched back to back over n separately prepared forward graphs."""
+            """n backward passes launched back to back over n separately prepared forward graphs (L2 flushed
+            before each, flush time subtracted)."""
             prepared = [fwd_bwd_setup() for _ in range(n)]
             if not prepared[0][1]:
                 return 0.0
             grads = [[torch.ones_like(o) if o.dim() == 0 else torch.randn_like(o) for o in outs] for _, outs in prepared]
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for (_, outs), g in zip(prepared, grads):
-                torch.autograd.backward(outs, g)
-            e1.record()
-            e1.synchronize()
-            return e0.elapsed_time(e1) / n
+            flush = _span_ms(lambda i: _flush_l2(), n)
+
+            def one(i):
+                _flush_l2()
+                torch.autograd.backward(prepared[i][1], grads[i])
+
+            return max(_span_ms(one, n) - flush, 0.0)
 
         timed_bwd(min(warmup, 2))
         t_bwd = timed_bwd(repeat)
