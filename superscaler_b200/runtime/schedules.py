@@ -34,14 +34,15 @@ class Boundary:
         ps, plan = trainer.pstate, trainer.plan
         self.trainer, self.rank = trainer, ps.rank
         lo_next = trainer.stage_bounds[up + 1][0]
+        P = ps.num_stages   # `up` counts virtual stages; virtual stage s runs on physical stage s % P
         self.keys = live_keys_before(trainer.op_names, lo_next)
         tp_a = plan["model_parallel_size_of_each_op"][up][-1]
         dp_a = plan["data_parallel_size_of_each_op"][up][-1]
         tp_b = plan["model_parallel_size_of_each_op"][up + 1][0]
         dp_b = plan["data_parallel_size_of_each_op"][up + 1][0]
-        self.src = Side(ps.stage_start[up], tp_a, dp_a)
-        self.dst = Side(ps.stage_start[up + 1], tp_b, dp_b)
-        self.i_am_src = ps.stage == up
+        self.src = Side(ps.stage_start[up % P], tp_a, dp_a)
+        self.dst = Side(ps.stage_start[(up + 1) % P], tp_b, dp_b)
+        self.i_am_src = ps.stage == up % P
         self.meta: Optional[Dict[str, tuple]] = None   # key -> (gshape, dtype, Layout, needs_grad, one_d)
         self.device = trainer.device
 
@@ -269,3 +270,145 @@ class PipelineRunner:
             if not first:
                 self._exchange(send_bwd=grads)
         return loss_buf
+
+
+# ---- interleaved (virtual-stage) 1F1B ---------------------------------------------------------------
+
+def interleaved_program(P: int, v: int, M: int, p: int) -> List[tuple]:
+    """The ordered program of physical stage `p` for one iteration of interleaved 1F1B with P physical stages,
+    v model chunks per stage and M micro-batches (M a multiple of P).
+
+    Entries: ("F", chunk, mb), ("B", chunk, mb) and ("X", [(kind, chunk, mb), ...]) with kind one of send_fwd /
+    recv_fwd / send_bwd / recv_bwd; all transfers of one X entry are issued as one batched group call.  Compute
+    order (reference: forward_backward_pipelining_with_interleaving, runtime/megatron/schedules.py:232-522):
+    micro-batches advance in groups of P through chunk 0, 1, ... v-1; a stage runs
+    min(2 (P - p - 1) + (v - 1) P, M v) warm-up forwards (all M v when M == P), then forward / backward pairs, then
+    the remaining backwards; backward step k belongs to chunk v - 1 - (k mod P v) // P.  After every compute
+    step the stage sends what it produced and receives exactly what its NEXT forward and backward steps consume.
+    """
+    assert v >= 1 and P >= 1 and M % P == 0, "the number of micro-batches must be a multiple of the stage count"
+    T = M * v
+    first, last = p == 0, p == P - 1
+
+    def fwd(k):
+        return (k % (P * v)) // P, (k // (P * v)) * P + k % P
+
+    def bwd(k):
+        c, mb = fwd(k)
+        return v - 1 - c, mb
+
+    def recv_fwd(k):   # input of forward step k arrives over the network unless it is the data loader's
+        return [("recv_fwd",) + fwd(k)] if k < T and not (first and fwd(k)[0] == 0) else []
+
+    def send_fwd(k):
+        return [("send_fwd",) + fwd(k)] if not (last and fwd(k)[0] == v - 1) else []
+
+    def recv_bwd(k):
+        return [("recv_bwd",) + bwd(k)] if k < T and not (last and bwd(k)[0] == v - 1) else []
+
+    def send_bwd(k):
+        return [("send_bwd",) + bwd(k)] if not (first and bwd(k)[0] == 0) else []
+
+    warm = T if M == P else min(2 * (P - p - 1) + (v - 1) * P, T)
+    rem = T - warm
+    prog: List[tuple] = [("X", recv_fwd(0))]
+    for k in range(warm):
+        prog.append(("F",) + fwd(k))
+        ops = send_fwd(k) + recv_fwd(k + 1)
+        if k == warm - 1:
+            ops += recv_bwd(0)
+        prog.append(("X", ops))
+    for k in range(rem):
+        fk = k + warm
+        prog.append(("F",) + fwd(fk))
+        prog.append(("B",) + bwd(k))
+        prog.append(("X", send_fwd(fk) + send_bwd(k) + recv_fwd(fk + 1) + recv_bwd(k + 1)))
+    for k in range(rem, T):
+        prog.append(("B",) + bwd(k))
+        prog.append(("X", send_bwd(k) + recv_bwd(k + 1)))
+    return [e for e in prog if e[0] != "X" or e[1]]
+
+
+def simulate_programs(P: int, v: int, M: int, t_fwd: float = 1.0, t_bwd: float = 2.0):
+    """Runs the P programs of interleaved_program against each other on a model of batched point-to-point
+    calls: a batch completes when each of its transfers has met the matching transfer of the peer, transfers
+    between one pair of stages in one direction match in the order they were posted, and a stage does nothing
+    else while a batch is pending.  Returns (finish time, bubble fraction) or raises on a deadlock, on a
+    transfer that meets the wrong partner, or on a compute step whose input never arrived.
+    """
+    progs = [interleaved_program(P, v, M, p) for p in range(P)]
+    pc = [0] * P
+    clock = [0.0] * P
+    busy = [0.0] * P
+    posted: Dict[tuple, List[tuple]] = {}    # (src stage, dst stage) -> [(payload tag, time posted)] sends
+    wanted: Dict[tuple, List[tuple]] = {}    # (src stage, dst stage) -> [(payload tag, time posted)] receives
+    have = [set() for _ in range(P)]         # ("act" | "grad", chunk, mb) available at a stage
+    done_f = [set() for _ in range(P)]
+    pending: List[Optional[list]] = [None] * P   # transfers of the current batch that are still unmatched
+
+    def tag_of(p, kind, c, mb):
+        # the payload is named after the virtual boundary it crosses
+        s = c * P + p
+        if kind == "send_fwd":
+            return ("act", s, mb), (p, (p + 1) % P)
+        if kind == "recv_fwd":
+            return ("act", s - 1, mb), ((p - 1) % P, p)
+        if kind == "send_bwd":
+            return ("grad", s - 1, mb), (p, (p - 1) % P)
+        return ("grad", s, mb), ((p + 1) % P, p)
+
+    progress = True
+    while progress:
+        progress = False
+        for p in range(P):
+            while pc[p] < len(progs[p]):
+                e = progs[p][pc[p]]
+                if e[0] == "F":
+                    _, c, mb = e
+                    if c * P + p > 0 and ("act", c * P + p - 1, mb) not in have[p]:
+                        raise RuntimeError(f"stage {p}: forward of chunk {c} micro-batch {mb} has no input")
+                    done_f[p].add((c, mb))
+                    clock[p] += t_fwd
+                    busy[p] += t_fwd
+                elif e[0] == "B":
+                    _, c, mb = e
+                    if (c, mb) not in done_f[p]:
+                        raise RuntimeError(f"stage {p}: backward before forward for chunk {c} micro-batch {mb}")
+                    if c * P + p < P * v - 1 and ("grad", c * P + p, mb) not in have[p]:
+                        raise RuntimeError(f"stage {p}: backward of chunk {c} micro-batch {mb} has no gradient")
+                    clock[p] += t_bwd
+                    busy[p] += t_bwd
+                else:
+                    if pending[p] is None:
+                        pending[p] = []
+                        for kind, c, mb in e[1]:
+                            tag, pair = tag_of(p, kind, c, mb)
+                            q = posted if kind.startswith("send") else wanted
+                            q.setdefault(pair, []).append((tag, clock[p], p))
+                            pending[p].append((kind.startswith("send"), pair, tag))
+                    # a transfer is complete when both queues of its pair hold it at matching positions
+                    still = []
+                    t_done = clock[p]
+                    for is_send, pair, tag in pending[p]:
+                        mine = posted.get(pair, []) if is_send else wanted.get(pair, [])
+                        theirs = wanted.get(pair, []) if is_send else posted.get(pair, [])
+                        idx = [i for i, x in enumerate(mine) if x[0] == tag][0]
+                        if idx >= len(theirs):
+                            still.append((is_send, pair, tag))
+                            continue
+                        if theirs[idx][0] != tag:
+                            raise RuntimeError(f"stage {p}: transfer {tag} met {theirs[idx][0]} on {pair}")
+                        t_done = max(t_done, theirs[idx][1])
+                        if not is_send:
+                            have[p].add(tag)
+                    if still:
+                        pending[p] = still
+                        break
+                    pending[p] = None
+                    clock[p] = max(clock[p], t_done)
+                pc[p] += 1
+                progress = True
+    if any(pc[p] < len(progs[p]) for p in range(P)):
+        raise RuntimeError(f"deadlock at program counters {pc}")
+    finish = max(clock)
+    return finish, 1.0 - (sum(busy) / P) / finish

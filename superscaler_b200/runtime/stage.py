@@ -160,20 +160,25 @@ def split_segments(ops: List[Op]) -> List[Segment]:
 
 
 class Stage:
-    """Ops + parameters of this rank's pipeline stage."""
+    """Ops + parameters of this rank's pipeline stage.  With interleaving a stage owns several model chunks
+    (non-adjacent slices of the op list); all chunks share one parameter store and one optimizer launch."""
 
-    def __init__(self, infos: Sequence[OpInfo], env: Env, build_op: Callable[[OpInfo, Env], Op], fuse=None):
+    def __init__(self, infos, env: Env, build_op: Callable[[OpInfo, Env], Op], fuse=None):
         self.env = env
-        env.stage_ops = infos
-        self.raw_ops: List[Op] = [build_op(i, env) for i in infos]
+        chunks: List[Sequence[OpInfo]] = list(infos) if infos and isinstance(infos[0], (list, tuple)) else [infos]
+        env.stage_ops = [i for c in chunks for i in c]
+        self.raw_chunks: List[List[Op]] = [[build_op(i, env) for i in c] for c in chunks]
+        self.raw_ops: List[Op] = [op for c in self.raw_chunks for op in c]
         for op in self.raw_ops:
             op.declare()
         env.store.materialize()
-        self.ops = fuse(self.raw_ops) if fuse is not None else list(self.raw_ops)
-        self.segments = split_segments(self.ops)
+        self.chunk_ops = [fuse(c) if fuse is not None else list(c) for c in self.raw_chunks]
+        self.chunk_segments = [split_segments(c) for c in self.chunk_ops]
+        self.ops = [op for c in self.chunk_ops for op in c]
+        self.segments = self.chunk_segments[0]
 
-    def forward(self, st: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
-        for seg in self.segments:
+    def forward(self, st: Dict[str, torch.Tensor], chunk: int = 0) -> Dict[str, torch.Tensor]:
+        for seg in self.chunk_segments[chunk]:
             seg.forward(st)
         return st
 

@@ -64,26 +64,39 @@ class Trainer:
         self.global_bs = plan["global_batch_size"]
         self.micro_bs = plan["micro_batch_size"]
         self.num_microbatches = self.global_bs // self.micro_bs
-        self.pstate = ParallelState(plan["num_gpus"], rank, world_size)
         names = names_fn(self.cfg)
         counts = plan["num_ops_in_each_stage"]
         assert sum(counts) == len(names), f"plan covers {sum(counts)} ops, model has {len(names)}"
+        # Interleaving: the plan lists P * v virtual stages in model order; virtual stage s runs on the GPUs of
+        # physical stage s % P, so every physical stage owns v model chunks (reference: --interleave-factor,
+        # runtime/megatron/arguments.py:778, and get_op_start_index, runtime/megatron/mpu/initialize.py:451-461).
+        self.interleave = v = int(plan.get("interleave_factor", 1))
+        assert len(counts) % v == 0, "interleave_factor must divide the number of (virtual) stages"
+        P = len(counts) // v
+        gpus = list(plan["num_gpus"])
+        assert len(gpus) == len(counts) and all(gpus[s] == gpus[s % P] for s in range(len(counts))), \
+            "every chunk of a physical stage must use that stage's GPUs"
+        self.pstate = ParallelState(gpus[:P], rank, world_size)
         self.op_names = names
         self.stage_bounds = [(sum(counts[:i]), sum(counts[:i + 1])) for i in range(len(counts))]
         # every process group any op needs, created in the same order on all ranks
         if world_size > 1:
-            pairs = [list(zip(plan["model_parallel_size_of_each_op"][s], plan["data_parallel_size_of_each_op"][s]))
-                     for s in range(len(counts))]
+            pairs = [[] for _ in range(P)]
+            for s in range(len(counts)):
+                pairs[s % P] += list(zip(plan["model_parallel_size_of_each_op"][s],
+                                         plan["data_parallel_size_of_each_op"][s]))
             self.pstate.ensure_groups(self.pstate.all_op_groups(pairs))
-        s = self.pstate.stage
-        lo, hi = self.stage_bounds[s]
-        infos = [OpInfo(name=names[i], index=i, layer=layer_fn(i, self.cfg),
-                        tp=plan["model_parallel_size_of_each_op"][s][i - lo],
-                        dp=plan["data_parallel_size_of_each_op"][s][i - lo],
-                        algo=plan["algo_of_each_op"][s][i - lo],
-                        recompute=plan["recompute_ops"][s][i - lo]) for i in range(lo, hi)]
-        self.infos = infos
-        F.manual_seed(seed + 100 * s)
+        self.virtual_stages = [c * P + self.pstate.stage for c in range(v)]
+        chunks = []
+        for s in self.virtual_stages:
+            lo, hi = self.stage_bounds[s]
+            chunks.append([OpInfo(name=names[i], index=i, layer=layer_fn(i, self.cfg),
+                                  tp=plan["model_parallel_size_of_each_op"][s][i - lo],
+                                  dp=plan["data_parallel_size_of_each_op"][s][i - lo],
+                                  algo=plan["algo_of_each_op"][s][i - lo],
+                                  recompute=plan["recompute_ops"][s][i - lo]) for i in range(lo, hi)])
+        self.infos = [i for c in chunks for i in c]
+        F.manual_seed(seed + 100 * self.pstate.stage)
         self.store = ParamStore(self.device, base_seed=seed)
         pure_dp = (len(counts) == 1 and world_size > 1 and self.device.type == "cuda" and
                    all(t == 1 for t in plan["model_parallel_size_of_each_op"][0]) and
@@ -94,7 +107,7 @@ class Trainer:
         self.env = Env(cfg=self.cfg, pstate=self.pstate, store=self.store, micro_bs=self.micro_bs,
                        fused_comm=fused_comm)
         self.env.training = training
-        self.stage = Stage(infos, self.env, build_fn, fuse_fn if fuse else None)
+        self.stage = Stage(chunks, self.env, build_fn, fuse_fn if fuse else None)
         self._tied = None
         if self.pstate.num_stages > 1:
             from .tied import TiedWeights
@@ -106,8 +119,8 @@ class Trainer:
         self.iteration = 0
         self.pipeline = None
         if self.pstate.num_stages > 1:
-            from .schedules import PipelineRunner
-            self.pipeline = PipelineRunner(self)
+            from .schedules import InterleavedRunner, PipelineRunner
+            self.pipeline = InterleavedRunner(self) if v > 1 else PipelineRunner(self)
         self._loss_buf = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.timers: Dict[str, float] = {}
 
@@ -183,7 +196,7 @@ class Trainer:
         """Host read of the iteration loss (synchronises); averaged over the last stage's DP group."""
         t = stats["loss_tensor"].clone()
         if self.world_size > 1:
-            last = self.pstate.num_stages - 1
+            last = len(self.stage_bounds) - 1
             src_dp = self.plan["data_parallel_size_of_each_op"][last][-1]
             if not self.pstate.is_last_stage():
                 t.zero_()
@@ -191,6 +204,10 @@ class Trainer:
             g = self.plan["num_gpus"][last]
             t /= g  # every rank of the last stage holds its DP shard's mean; TP replicas repeat it
         return float(t.item())
+
+    def owned_op_indices(self) -> List[int]:
+        """Global indices of the ops this rank's physical stage runs (all of its model chunks)."""
+        return [i.index for i in self.infos]
 
     def num_parameters(self) -> int:
         return sum(p.numel() for p in self.store.params.values())
