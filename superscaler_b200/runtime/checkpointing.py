@@ -8,7 +8,8 @@ with the keys ``args, checkpoint_version (3.0), iteration, model, optimizer, lr_
 addition, ``plan`` (the plan JSON the run used) and ``op_names`` (index -> op name), so a checkpoint written under
 one plan can be re-assembled under another.  Only data-parallel rank 0 of each (stage, tp rank) writes.  Parameter
 names inside ``model`` follow the reference's ``language_model.ops.{i}.{module}.{weight|bias}`` convention with
-i = the op's index inside its stage (runtime/megatron/model/flex_model.py:378).
+i = the op's index inside its stage (runtime/megatron/model/flex_model.py:378); with interleaving a stage's later
+chunks continue the numbering from the global op indices (i = global index - first op of the stage's chunk 0).
 
 `merge_tp_shards` / `load_under_plan` rebuild full (unsharded) tensors from the tp shards of a checkpoint and
 re-slice them for a new plan.
@@ -78,7 +79,7 @@ def save_checkpoint(trainer, root: str, iteration: Optional[int] = None) -> Opti
             "torch_rng_state": torch.get_rng_state(),
             "rng_tracker_states": {"dropout_seed_state": F.seed_state().get_state()},
             "plan": trainer.plan,
-            "op_names": {i: trainer.op_names[i] for i in range(*trainer.stage_bounds[ps.stage])},
+            "op_names": {i: trainer.op_names[i] for i in trainer.owned_op_indices()},
             "param_specs": {names[s.name]: {"full_shape": s.full_shape, "shard_dim": s.shard_dim, "tp": s.tp,
                                             "tp_rank": s.tp_rank} for s in trainer.store.specs},
         }

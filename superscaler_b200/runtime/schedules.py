@@ -1,4 +1,5 @@
-"""Pipeline execution: non-interleaved 1F1B over stages with different GPU counts.
+"""Pipeline execution: 1F1B over stages with different GPU counts, plain (PipelineRunner) and interleaved with
+several model chunks per stage (InterleavedRunner, program built by interleaved_program).
 
 Schedule (same as the reference's forward_backward_pipelining_without_interleaving,
 runtime/megatron/schedules.py:533-646): stage s of P runs min(P - s - 1, M) warm-up forwards, then
@@ -412,3 +413,150 @@ def simulate_programs(P: int, v: int, M: int, t_fwd: float = 1.0, t_bwd: float =
         raise RuntimeError(f"deadlock at program counters {pc}")
     finish = max(clock)
     return finish, 1.0 - (sum(busy) / P) / finish
+
+
+class InterleavedRunner:
+    """Executes interleaved_program: every physical stage owns v model chunks; chunk c of stage p is virtual
+    stage c * P + p and exchanges with virtual stages c * P + p - 1 and c * P + p + 1 (the last stage's chunk c
+    feeds the first stage's chunk c + 1).  Activation memory per stage peaks at the warm-up depth of the
+    program; the pipeline bubble shrinks by the factor v against plain 1F1B."""
+
+    def __init__(self, trainer):
+        self.t = trainer
+        ps = trainer.pstate
+        self.stage, self.P, self.v = ps.stage, ps.num_stages, trainer.interleave
+        total = self.P * self.v
+        self.prev: List[Optional[Boundary]] = []
+        self.next: List[Optional[Boundary]] = []
+        for c in range(self.v):
+            s = c * self.P + self.stage
+            self.prev.append(Boundary(trainer, s - 1) if s > 0 else None)
+            self.next.append(Boundary(trainer, s) if s < total - 1 else None)
+        self.program = None
+
+    def _exchange(self, ops_spec, outputs, in_grads, sent_sides):
+        """One batched group call.  outputs[(c, mb)] = (tensors, sides) to send downstream, in_grads[(c, mb)] =
+        gradients to send upstream, sent_sides[(c, mb)] = layouts of what was sent downstream earlier."""
+        ops, fwd_asm, bwd_asm = [], [], []
+        for kind, c, mb in ops_spec:
+            if kind == "send_fwd":
+                st, sides = outputs.pop((c, mb))
+                b = self.next[c]
+                if b.meta is None:
+                    b.handshake_send(st, sides)
+                ops += b.forward_ops(st, sides)[0]
+            elif kind == "send_bwd":
+                ops += self.prev[c].backward_ops(in_grads.pop((c, mb)), None)[0]
+            elif kind == "recv_fwd":
+                b = self.prev[c]
+                if b.meta is None:
+                    b.handshake_recv()
+                o, asm = b.forward_ops(None, None)
+                ops += o
+                fwd_asm.append(((c, mb), asm))
+            else:
+                o, asm = self.next[c].backward_ops(None, sent_sides[(c, mb)])
+                ops += o
+                bwd_asm.append(((c, mb), asm))
+        _run_batch(ops)
+        return {k: asm() for k, asm in fwd_asm}, {k: asm() for k, asm in bwd_asm}
+
+    def run(self, batch, loss_buf: torch.Tensor) -> torch.Tensor:
+        t = self.t
+        M = t.num_microbatches
+        assert M % self.P == 0, "interleaved 1F1B needs a micro-batch count that is a multiple of the stage count"
+        if self.program is None:
+            self.program = interleaved_program(self.P, self.v, M, self.stage)
+        received: Dict[tuple, tuple] = {}      # (chunk, mb) -> (tensors, sides) from upstream
+        out_grads: Dict[tuple, dict] = {}      # (chunk, mb) -> gradients from downstream
+        outputs: Dict[tuple, tuple] = {}
+        in_grads: Dict[tuple, dict] = {}
+        sent_sides: Dict[tuple, dict] = {}
+        live: Dict[tuple, tuple] = {}          # (chunk, mb) -> (state, inputs) between forward and backward
+        for e in self.program:
+            if e[0] == "X":
+                got_f, got_b = self._exchange(e[1], outputs, in_grads, sent_sides)
+                received.update(got_f)
+                out_grads.update(got_b)
+            elif e[0] == "F":
+                _, c, mb = e
+                st = t.microbatch_inputs(batch, mb)
+                st["_meta"] = {}
+                inputs = {}
+                if self.prev[c] is not None:
+                    tensors, sides = received.pop((c, mb))
+                    st.update(tensors)
+                    st["_meta"].update(sides)
+                    inputs = tensors
+                t.stage.forward(st, chunk=c)
+                live[(c, mb)] = (st, inputs)
+                if self.next[c] is not None:
+                    keys = self.next[c].keys
+                    outputs[(c, mb)] = ({k: st[k] for k in keys}, {k: st["_meta"][k] for k in keys})
+                    sent_sides[(c, mb)] = outputs[(c, mb)][1]
+            else:
+                _, c, mb = e
+                st, inputs = live.pop((c, mb))
+                if self.next[c] is None:
+                    loss = st["loss"]
+                    loss.backward()
+                    loss_buf += loss.detach()
+                else:
+                    outs, gs = [], []
+                    for k, g in out_grads.pop((c, mb)).items():
+                        o = st[k]
+                        if isinstance(o, torch.Tensor) and o.requires_grad:
+                            outs.append(o)
+                            gs.append(g.to(o.dtype))
+                    torch.autograd.backward(outs, gs)
+                    sent_sides.pop((c, mb))
+                if self.prev[c] is not None:
+                    in_grads[(c, mb)] = {k: (x.grad if x.grad is not None else torch.zeros_like(x))
+                                         for k, x in inputs.items() if x.is_floating_point() and x.requires_grad}
+        return loss_buf
+
+
+def interleave_plan(plan: dict, v: int, ops_per_virtual_stage: Optional[List[int]] = None) -> dict:
+    """Re-cuts a P-stage plan into P * v virtual stages for the interleaved schedule (the role of the reference's
+    --interleave-factor, runtime/megatron/arguments.py:778-779, whose plans list the virtual stages explicitly).
+
+    The op list is cut into P * v consecutive slices (equal op counts unless `ops_per_virtual_stage` is given);
+    slice s runs on the GPUs of stage s % P and takes that stage's tensor / data parallel degrees, so every stage
+    of the input plan must use one (tp, dp) for all of its ops.  Per-op recompute and algorithm choices are kept.
+    """
+    if v <= 1:
+        return plan
+    P = len(plan["num_ops_in_each_stage"])
+    assert int(plan.get("interleave_factor", 1)) == 1, "plan is already interleaved"
+    assert P >= 2, "interleaving needs at least two pipeline stages"
+    tps, dps = [], []
+    for s in range(P):
+        tp, dp = set(plan["model_parallel_size_of_each_op"][s]), set(plan["data_parallel_size_of_each_op"][s])
+        assert len(tp) == 1 and len(dp) == 1, f"stage {s} mixes parallel degrees; it cannot be interleaved"
+        tps.append(tp.pop())
+        dps.append(dp.pop())
+    n = sum(plan["num_ops_in_each_stage"])
+    total = P * v
+    if ops_per_virtual_stage is None:
+        per = n // total
+        ops_per_virtual_stage = [per + (1 if i < n - per * total else 0) for i in range(total)]
+    assert len(ops_per_virtual_stage) == total and sum(ops_per_virtual_stage) == n
+
+    def recut(key):
+        flat = [x for stage in plan[key] for x in stage]
+        out, at = [], 0
+        for c in ops_per_virtual_stage:
+            out.append(flat[at:at + c])
+            at += c
+        return out
+
+    new = dict(plan)
+    new.update(
+        interleave_factor=v, num_stages=total, num_ops_in_each_stage=list(ops_per_virtual_stage),
+        num_gpus=[plan["num_gpus"][s % P] for s in range(total)],
+        model_parallel_size_of_each_op=[[tps[s % P]] * c for s, c in enumerate(ops_per_virtual_stage)],
+        data_parallel_size_of_each_op=[[dps[s % P]] * c for s, c in enumerate(ops_per_virtual_stage)],
+        recompute_ops=recut("recompute_ops"), algo_of_each_op=recut("algo_of_each_op"),
+        checkpoint_activations=[any(r) for r in recut("recompute_ops")],
+        resharding_stages=[False] * total)
+    return new

@@ -29,11 +29,16 @@ class TiedWeights:
         self.links: List[Tuple[str, Side, Side]] = []   # (shared key, root side, other side)
         for key, op_names in DECLARING_OPS.items():
             holders: List[Side] = []
+            seen = set()   # physical stages that already hold a copy (one copy per stage, shared by its chunks)
             for s, (lo, hi) in enumerate(trainer.stage_bounds):
+                phys = s % ps.num_stages
+                if phys in seen:
+                    continue
                 for i in range(lo, hi):
                     if trainer.op_names[i] in op_names:
-                        holders.append(Side(ps.stage_start[s], plan["model_parallel_size_of_each_op"][s][i - lo],
+                        holders.append(Side(ps.stage_start[phys], plan["model_parallel_size_of_each_op"][s][i - lo],
                                             plan["data_parallel_size_of_each_op"][s][i - lo]))
+                        seen.add(phys)
                         break
             for other in holders[1:]:
                 self.links.append((key, holders[0], other))

@@ -42,6 +42,9 @@ def main():
         plans = {"dp": tiny_gpt_plan(**kw, num_gpus=(world,), tp=[1]),
                  "tp": tiny_gpt_plan(**kw, num_gpus=(world,), tp=[world]),
                  "pp": tiny_gpt_plan(**kw, num_gpus=tuple([1] * world))}
+        if (kw["global_bs"] // kw["micro_bs"]) % world == 0:
+            from superscaler_b200.runtime.schedules import interleave_plan
+            plans["pp_interleaved"] = interleave_plan(plans["pp"], 2)
         out = {}
         for name, plan in plans.items():
             for fused in ((True, False) if name in ("dp", "tp") else (False,)):

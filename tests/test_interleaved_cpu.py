@@ -1,0 +1,83 @@
+"""Interleaved (virtual-stage) 1F1B: the per-stage programs are checked against each other on a model of batched
+point-to-point calls (matching, input availability, absence of deadlock, pipeline bubble), and multi-rank runs on
+CPU (gloo) must reproduce the losses of the single-process run -- the reference's interleaved schedule is
+runtime/megatron/schedules.py:232-522."""
+import pytest
+import torch
+
+from superscaler_b200.data.synthetic import gpt_batch
+from superscaler_b200.runtime import checkpointing
+from superscaler_b200.runtime.schedules import interleave_plan, interleaved_program, simulate_programs
+from superscaler_b200.runtime.trainer import Trainer
+
+from dist_utils import run_ranks
+from helpers import tiny_gpt_plan
+
+NODROP = dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2)
+KW = dict(layers=4, seq=32, hidden=64, heads=2, head_dim=32, vocab=256, global_bs=12, micro_bs=2)
+
+
+@pytest.mark.parametrize("P", [2, 3, 4, 8])
+@pytest.mark.parametrize("v", [1, 2, 3, 4])
+def test_programs_match_and_reach_the_ideal_bubble(P, v):
+    for M in (P, 2 * P, 4 * P):
+        finish, bubble = simulate_programs(P, v, M, t_fwd=1.0, t_bwd=2.0)
+        # bubble of interleaved 1F1B: (P - 1) / v micro-batch times out of M + (P - 1) / v
+        ideal = ((P - 1) / v) / (M + (P - 1) / v)
+        assert abs(bubble - ideal) < 1e-9, (P, v, M, bubble, ideal)
+        assert abs(finish - 3.0 * (M * v + P - 1)) < 1e-9
+
+
+def test_program_runs_every_chunk_of_every_microbatch_once_and_bounds_live_activations():
+    P, v, M = 4, 2, 8
+    for p in range(P):
+        prog = interleaved_program(P, v, M, p)
+        fwd = [e[1:] for e in prog if e[0] == "F"]
+        bwd = [e[1:] for e in prog if e[0] == "B"]
+        assert sorted(fwd) == sorted(bwd) == sorted((c, mb) for c in range(v) for mb in range(M))
+        live = peak = 0
+        for e in prog:
+            live += {"F": 1, "B": -1}.get(e[0], 0)
+            peak = max(peak, live)
+        assert peak == min(2 * (P - p - 1) + (v - 1) * P, M * v) + 1
+
+
+def test_interleave_plan_recuts_the_stages():
+    plan = tiny_gpt_plan(**KW, num_gpus=(1, 2, 1), tp=[1, 2, 1], recompute=1)
+    new = interleave_plan(plan, 2)
+    assert new["interleave_factor"] == 2 and new["num_gpus"] == [1, 2, 1, 1, 2, 1]
+    assert sum(new["num_ops_in_each_stage"]) == sum(plan["num_ops_in_each_stage"])
+    assert [t[0] for t in new["model_parallel_size_of_each_op"]] == [1, 2, 1, 1, 2, 1]
+    flat = lambda p: [x for s in p["recompute_ops"] for x in s]
+    assert flat(new) == flat(plan)
+    mixed = tiny_gpt_plan(**KW, num_gpus=(2, 2), tp=[2, 1])
+    mixed["model_parallel_size_of_each_op"][0][3] = 1
+    with pytest.raises(AssertionError):
+        interleave_plan(mixed, 2)
+
+
+def _losses(plan, rank=0, world=1, steps=2, save=None):
+    t = Trainer(plan, rank=rank, world_size=world, model_overrides=NODROP, lr_warmup_steps=0, device="cpu", lr=1e-3)
+    out = [t.loss_value(t.train_step(gpt_batch(12, 32, 256, seed=1))) for _ in range(steps)]
+    if save is not None:
+        checkpointing.save_checkpoint(t, save)
+        t2 = Trainer(plan, rank=rank, world_size=world, model_overrides=NODROP, lr_warmup_steps=0, device="cpu",
+                     lr=1e-3, seed=99)
+        assert checkpointing.load_checkpoint(t2, save) == steps
+        a = t.loss_value(t.train_step(gpt_batch(12, 32, 256, seed=2)))
+        b = t2.loss_value(t2.train_step(gpt_batch(12, 32, 256, seed=2)))
+        assert abs(a - b) < 1e-5, (a, b)
+    return out
+
+
+def _worker(rank, world, plan, want, save):
+    got = _losses(plan, rank, world, save=save)
+    assert max(abs(a - b) for a, b in zip(got, want)) < 3e-3, (rank, got, want)
+
+
+@pytest.mark.parametrize("gpus,tp,v,ckpt", [((1, 1, 1), [1, 1, 1], 2, True), ((1, 1), [1, 1], 3, False),
+                                            ((1, 2, 1), [1, 2, 1], 2, False)])
+def test_interleaved_training_matches_single_process(tmp_path, gpus, tp, v, ckpt):
+    base = _losses(tiny_gpt_plan(**KW))
+    plan = interleave_plan(tiny_gpt_plan(**KW, num_gpus=gpus, tp=tp), v)
+    run_ranks(_worker, sum(gpus), plan, base, str(tmp_path / "ckpt") if ckpt else None)
