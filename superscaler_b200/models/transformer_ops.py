@@ -266,7 +266,7 @@ class LMHeadLossOp(Op):
     """Tied-embedding LM head + vocab-parallel cross entropy -> scalar loss for this micro-batch.
     Reference: GPTPostProcess / T5PostProcess, flex_ops.py:1283-1419."""
     reads = ("x", "labels", "loss_mask")
-    writes = ("loss",)
+    writes = ("loss", "logits")
 
     def declare(self):
         c = self.env.cfg
@@ -277,6 +277,11 @@ class LMHeadLossOp(Op):
 
     def forward(self, st):
         x = M.copy_to_group(st["x"], self.tp_group)
+        if "labels" not in st:
+            # inference: full-vocabulary logits [tokens, padded vocab] instead of a loss (text generation, scoring)
+            logits = F.linear(x, self.p("word_embeddings.weight"))
+            st["logits"] = M.gather_from_group(logits, -1, self.tp_group)
+            return
         labels = st["labels"]
         mask = st.get("loss_mask")
         ntok = labels.numel()

@@ -1,0 +1,79 @@
+"""Text generation with a GPT plan: temperature / top-k / top-p (nucleus) sampling or greedy decoding.
+
+Counterpart of the reference's sampling utilities (runtime/megatron/text_generation_utils.py: top_k_logits,
+sample_sequence_batch, generate_samples_*).  The op-list model has no key / value cache (neither have the
+reference's flex ops), so every new token re-runs the causal forward over the whole window of `seq_length`
+positions: prompts are right-padded, and because attention is causal the padding cannot influence the position
+that is read.  Runs single-stage plans (one GPU, or a tensor-parallel group in which every rank calls generate
+with the same arguments and seed).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+
+def filter_logits(logits: torch.Tensor, top_k: int = 0, top_p: float = 0.0) -> torch.Tensor:
+    """Sets to -inf every logit outside the k largest and outside the smallest set whose probability mass
+    reaches top_p (the most likely token always survives).  logits: [batch, vocab]."""
+    out = logits.clone()
+    if top_k > 0:
+        kth = torch.topk(out, min(top_k, out.shape[-1]), dim=-1).values[..., -1:]
+        out[out < kth] = float("-inf")
+    if top_p > 0.0:
+        sorted_logits, order = torch.sort(out, dim=-1, descending=True)
+        mass = torch.softmax(sorted_logits, dim=-1).cumsum(dim=-1)
+        drop = mass - torch.softmax(sorted_logits, dim=-1) >= top_p     # mass BEFORE this token already enough
+        drop[..., 0] = False
+        sorted_logits[drop] = float("-inf")
+        out = torch.full_like(out, float("-inf")).scatter(-1, order, sorted_logits)
+    return out
+
+
+def sample_next(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p: float = 0.0,
+                greedy: bool = False, generator: Optional[torch.Generator] = None) -> torch.Tensor:
+    """One token id per row of logits [batch, vocab]."""
+    logits = logits.float()
+    if greedy or temperature == 0.0:
+        return logits.argmax(dim=-1)
+    probs = torch.softmax(filter_logits(logits / temperature, top_k, top_p), dim=-1)
+    return torch.multinomial(probs, 1, generator=generator).squeeze(-1)
+
+
+@torch.no_grad()
+def generate(trainer, prompts: Sequence[Sequence[int]], max_new_tokens: int, eod: Optional[int] = None,
+             temperature: float = 1.0, top_k: int = 0, top_p: float = 0.0, greedy: bool = False, seed: int = 1234,
+             vocab_size: Optional[int] = None, pad: int = 0) -> List[List[int]]:
+    """Continues every prompt by up to max_new_tokens tokens (stops a sequence at `eod`).  `vocab_size` cuts the
+    padded part of the vocabulary off before sampling.  Returns prompt + continuation per sequence."""
+    S = trainer.cfg.seq_length
+    seqs = [list(map(int, p)) for p in prompts]
+    assert all(0 < len(p) < S for p in seqs), "prompts must be non-empty and shorter than the model's window"
+    done = [False] * len(seqs)
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    for _ in range(max_new_tokens):
+        active = [i for i, d in enumerate(done) if not d and len(seqs[i]) < S]
+        if not active:
+            break
+        ids = torch.full((len(seqs), S), pad, dtype=torch.int64)
+        for i, s in enumerate(seqs):
+            ids[i, : min(len(s), S)] = torch.tensor(s[:S])
+        logits = trainer.logits(ids)
+        last = torch.stack([logits[i, min(len(seqs[i]), S) - 1] for i in range(len(seqs))]).float().cpu()
+        if vocab_size is not None:
+            last = last[:, :vocab_size]
+        nxt = sample_next(last, temperature, top_k, top_p, greedy, gen).tolist()
+        for i in active:
+            seqs[i].append(int(nxt[i]))
+            if eod is not None and nxt[i] == eod:
+                done[i] = True
+    return seqs
+
+
+def generate_text(trainer, tokenizer, texts: Sequence[str], max_new_tokens: int, **kw) -> List[str]:
+    """Tokenize, generate, detokenize (the continuation stops at the tokenizer's end-of-document id)."""
+    eod = getattr(tokenizer, "eod", None)
+    out = generate(trainer, [tokenizer.tokenize(t) for t in texts], max_new_tokens, eod=eod,
+                   vocab_size=tokenizer.vocab_size, **kw)
+    return [tokenizer.detokenize([i for i in s if i != eod]) for s in out]

@@ -205,6 +205,49 @@ class Trainer:
             t /= g  # every rank of the last stage holds its DP shard's mean; TP replicas repeat it
         return float(t.item())
 
+    @torch.no_grad()
+    def logits(self, ids: torch.Tensor) -> torch.Tensor:
+        """Inference forward of a single-stage GPT plan: token ids [b, seq_length] -> logits [b, seq_length,
+        padded vocabulary].  Dropout is off; nothing is kept for a backward pass."""
+        assert self.pstate.num_stages == 1, "logits() runs single-stage plans (tensor / data parallel or 1 GPU)"
+        was = self.env.training
+        self.env.training = False
+        try:
+            st: Dict[str, Any] = {"ids": ids.to(self.device)}
+            if self.world_size > 1:
+                st["_meta"] = {}
+            self.stage.forward(st)
+        finally:
+            self.env.training = was
+        b, s = ids.shape
+        return st["logits"].view(b, s, -1)
+
+    @torch.no_grad()
+    def evaluate(self, batches) -> Dict[str, float]:
+        """Mean loss over an iterable of global batches without touching gradients or optimizer state
+        (reference: evaluate / evaluate_and_print_results, runtime/megatron/training.py:1021-1098)."""
+        was = self.env.training
+        self.env.training = False
+        total, n = 0.0, 0
+        try:
+            for batch in batches:
+                batch = self.to_device(batch)
+                self._loss_buf.zero_()
+                if self.pipeline is not None:
+                    raise NotImplementedError("evaluate() runs single-stage plans")
+                for mb in range(self.num_microbatches):
+                    st = self.microbatch_inputs(batch, mb)
+                    if self.world_size > 1:
+                        st["_meta"] = {}
+                    self.stage.forward(st)
+                    self._loss_buf += st["loss"]
+                total += self.loss_value({"loss_tensor": self._loss_buf})
+                n += 1
+        finally:
+            self.env.training = was
+        mean = total / max(n, 1)
+        return {"lm loss": mean, "lm loss ppl": float(torch.exp(torch.tensor(min(mean, 20.0))))}
+
     def owned_op_indices(self) -> List[int]:
         """Global indices of the ops this rank's physical stage runs (all of its model chunks)."""
         return [i.index for i in self.infos]

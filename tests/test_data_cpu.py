@@ -57,3 +57,25 @@ def test_batches_layout():
     batch = next(indexed.batches(ds, global_bs=4, steps=1))
     assert batch["ids"].shape == (4, 8) and batch["labels"].shape == (4, 8)
     assert (batch["ids"][:, 1:] == batch["labels"][:, :-1]).all()
+
+
+def test_samplers_resume_and_shard():
+    from superscaler_b200.data.samplers import (SequentialBatchSampler, ShuffledBatchSampler, build_data_loader,
+                                                stack_samples)
+    s = SequentialBatchSampler(22, 4)
+    all_b = list(s)
+    assert len(all_b) == 5 and all_b[0] == [0, 1, 2, 3] and all_b[-1] == [16, 17, 18, 19] and s.consumed == 20
+    assert list(SequentialBatchSampler(22, 4, consumed_samples=8))[0] == [8, 9, 10, 11]
+    assert list(SequentialBatchSampler(22, 4, drop_last=False))[-1] == [20, 21]
+    assert list(SequentialBatchSampler(22, 4, rows=slice(2, 4)))[1] == [6, 7]
+    a = ShuffledBatchSampler(22, 4, seed=3, epochs=2)
+    seq = list(a)
+    assert len(seq) == 10
+    assert len(set(sum(seq[:5], []))) == 20 and len(set(sum(seq[5:], []))) == 20 and seq[:5] != seq[5:]
+    b = ShuffledBatchSampler(22, 4, seed=3, consumed_samples=12, epochs=2)
+    assert list(b) == seq[3:]
+    import numpy as np
+    data = [np.arange(i, i + 9) for i in range(22)]
+    loader = build_data_loader(data, SequentialBatchSampler(22, 4), stack_samples)
+    first = next(iter(loader))
+    assert first["ids"].shape == (4, 8) and (first["labels"][:, :-1] == first["ids"][:, 1:]).all()

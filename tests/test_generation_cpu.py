@@ -1,0 +1,49 @@
+"""Sampling filters and the generation loop on a tiny GPT (reference: runtime/megatron/text_generation_utils.py)."""
+import torch
+
+from superscaler_b200.data.synthetic import gpt_batch
+from superscaler_b200.runtime.generation import filter_logits, generate, sample_next
+from superscaler_b200.runtime.trainer import Trainer
+
+from helpers import tiny_gpt_plan
+
+
+def test_top_k_and_top_p_filters():
+    logits = torch.log(torch.tensor([[0.5, 0.25, 0.15, 0.07, 0.03]]))
+    k2 = filter_logits(logits, top_k=2)
+    assert torch.isfinite(k2[0]).tolist() == [True, True, False, False, False]
+    p = filter_logits(logits, top_p=0.8)           # 0.5 + 0.25 < 0.8 <= 0.5 + 0.25 + 0.15
+    assert torch.isfinite(p[0]).tolist() == [True, True, True, False, False]
+    tiny = filter_logits(logits, top_p=1e-6)
+    assert torch.isfinite(tiny[0]).tolist() == [True, False, False, False, False]
+    shuffled = logits[:, [3, 0, 4, 2, 1]]
+    assert torch.isfinite(filter_logits(shuffled, top_p=0.8)[0]).tolist() == [False, True, False, True, True]
+    assert sample_next(logits, greedy=True).tolist() == [0]
+    g = torch.Generator().manual_seed(0)
+    draws = [int(sample_next(logits, top_k=2, generator=g)) for _ in range(200)]
+    assert set(draws) == {0, 1} and draws.count(0) > draws.count(1)
+
+
+def test_generation_on_a_tiny_gpt_learns_a_repeating_pattern():
+    kw = dict(layers=2, seq=32, hidden=64, heads=2, head_dim=32, vocab=64, global_bs=8, micro_bs=8)
+    t = Trainer(tiny_gpt_plan(**kw), model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0),
+                lr_warmup_steps=0, device="cpu", lr=3e-3, lr_style="constant")
+    # the corpus is the periodic sequence 5, 6, ..., 12, 5, 6, ...; the model learns next = f(previous)
+    period = torch.arange(5, 13)
+    rows = torch.stack([period.roll(-i).repeat(5)[:33] for i in range(8)])
+    batch = {"ids": rows[:, :-1].contiguous(), "labels": rows[:, 1:].contiguous()}
+    first = t.loss_value(t.train_step(batch))
+    for _ in range(60):
+        last = t.loss_value(t.train_step(batch))
+    assert last < 0.2 * first
+    ev = t.evaluate([batch])
+    assert abs(ev["lm loss"] - last) < 0.5 and ev["lm loss ppl"] >= 1.0
+    lg = t.logits(batch["ids"])
+    assert lg.shape[:2] == (8, 32) and lg.shape[2] >= 64
+    out = generate(t, [[5, 6, 7], [9, 10]], max_new_tokens=6, greedy=True, vocab_size=64)
+    assert out[0] == [5, 6, 7, 8, 9, 10, 11, 12, 5] and out[1] == [9, 10, 11, 12, 5, 6, 7, 8]
+    stop = generate(t, [[5, 6, 7]], max_new_tokens=6, greedy=True, eod=9, vocab_size=64)
+    assert stop[0] == [5, 6, 7, 8, 9]
+    # sampling with a tiny nucleus equals greedy decoding
+    same = generate(t, [[5, 6, 7]], max_new_tokens=4, top_p=1e-4, vocab_size=64)
+    assert same[0] == out[0][:7]

@@ -55,3 +55,32 @@ def test_lr_schedule():
     assert s2.get_lr() == s.get_lr()
     lin = LRSchedule(1.0, 0.0, warmup_steps=0, decay_steps=100, style="linear")
     assert abs(lin.step(50) - 0.5) < 1e-9
+
+
+def test_memory_buffers_and_reports():
+    import torch
+    from superscaler_b200.runtime.memory import MemoryBuffer, RingMemBuffer, debug_mem_report, report_memory
+    buf = MemoryBuffer("act", 64, torch.float32, track_usage=True, device="cpu")
+    a = buf.get((4, 4))
+    b = buf.add(torch.arange(8, dtype=torch.float32))
+    assert a.shape == (4, 4) and b.tolist() == list(range(8)) and buf.numel_in_use() == 24
+    assert a.data_ptr() == buf.data.data_ptr() and b.data_ptr() == buf.data[16:].data_ptr()
+    assert buf.get_data().numel() == 24 and abs(buf.usage() - 24 / 64) < 1e-9
+    import pytest
+    with pytest.raises(AssertionError):
+        buf.get((41,))
+    buf.reset()
+    assert not buf.is_in_use()
+    ring = RingMemBuffer("ckpt", 2, 16, torch.float32, device="cpu")
+    first, second = ring.get_next_buffer(), ring.get_next_buffer()
+    assert first is not second and ring.get_next_buffer() is first
+    first.get((4,))
+    ring.get_next_buffer()
+    with pytest.raises(AssertionError):
+        ring.get_next_buffer()      # back at `first`, which is still in use
+    text, vals = report_memory("stage 0", get_list=True)
+    assert text.startswith("stage 0 memory (MB) | allocated:") and len(vals) == 4
+    big = torch.zeros(1 << 18)
+    rows = debug_mem_report(min_mb=0.5)
+    assert any(r[1] == (1 << 18,) and r[3] >= 1.0 for r in rows)
+    del big
