@@ -49,6 +49,8 @@ T5_SIZES: Dict[str, tuple] = {
 # reference tables above: GPT-3 1.3B uses 16 heads of 128; T5 770M uses encoder 512 / decoder 128 tokens, vocab 32128)
 B200_GPT_SIZES: Dict[str, tuple] = {
     "1_3B": (24, 2048, 2048, 8192, 16, 128, 51200, "bf16"),
+    # the attention kernels take heads of 64 or 128: 2.6B runs 20 heads of 128 instead of 32 of 80
+    "2_6B": (32, 2048, 2560, 10240, 20, 128, 51200, "bf16"),
 }
 B200_T5_SIZES: Dict[str, tuple] = {
     "770M": (24, 512, 128, 1024, 4096, 16, 64, 32128, "bf16"),
