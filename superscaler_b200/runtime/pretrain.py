@@ -13,6 +13,7 @@ import argparse
 import csv
 import json
 import os
+import time
 
 import torch
 import torch.distributed as dist
@@ -55,6 +56,14 @@ def main(argv=None) -> None:
     ap.add_argument("--load", default=None)
     ap.add_argument("--save-interval", type=int, default=None)
     ap.add_argument("--exit-interval", type=int, default=None)
+    ap.add_argument("--exit-duration-in-mins", type=float, default=None,
+                    help="save a checkpoint and stop once the run has lasted this long")
+    ap.add_argument("--finetune", action="store_true", help="load the weights only and restart at iteration 0")
+    ap.add_argument("--no-load-optim", action="store_true")
+    ap.add_argument("--no-load-rng", action="store_true")
+    ap.add_argument("--eval-interval", type=int, default=None, help="evaluate every this many iterations")
+    ap.add_argument("--eval-iters", type=int, default=2, help="batches per evaluation")
+    ap.add_argument("--tensorboard-dir", default=None, help="scalar logs (written by the last rank)")
     ap.add_argument("--no-fused-comm", action="store_true")
     ap.add_argument("--interleave-factor", type=int, default=1,
                     help="model chunks per pipeline stage (interleaved 1F1B); re-cuts the plan's stages evenly")
@@ -76,7 +85,13 @@ def main(argv=None) -> None:
                       lr_warmup_steps=int(args.lr_warmup_fraction * args.lr_decay_iters), lr_style=args.lr_decay_style,
                       optimizer=args.optimizer, fused_comm=not args.no_fused_comm)
     if args.load:
-        checkpointing.load_checkpoint(trainer, args.load)
+        checkpointing.load_checkpoint(trainer, args.load, load_optim=not args.no_load_optim,
+                                      load_rng=not args.no_load_rng, finetune=args.finetune)
+    writer = None
+    if args.tensorboard_dir and rank == world - 1:
+        from torch.utils.tensorboard import SummaryWriter
+        writer = SummaryWriter(log_dir=args.tensorboard_dir)
+    t_start = time.time()
     batch_fn = make_batch_fn(trainer)
     # synthetic batches are generated on the host before the loop (a pool of up to 4, reused in turn): building
     # a 768-image batch takes longer than a training step and is not part of what an iteration measures
@@ -112,6 +127,13 @@ def main(argv=None) -> None:
                       f"{row['iteration']:.1f} | learning rate: {lr:.3E} | global batch size: "
                       f"{plan['global_batch_size']:5d} | lm loss: {lv:.6E} | grad norm: {trainer.optimizer.grad_norm():.3f}",
                       flush=True)
+            if writer is not None:
+                writer.add_scalar("learning-rate", lr, it + 1)
+                writer.add_scalar("lm loss", lv, it + 1)
+                writer.add_scalar("grad-norm", trainer.optimizer.grad_norm(), it + 1)
+                writer.add_scalar("samples per second", plan["global_batch_size"] / (row["iteration"] / 1e3), it + 1)
+                for r in regions:
+                    writer.add_scalar(f"{r}-time", row[r], it + 1)
             if it == args.train_iters - 1 and args.log_path:
                 os.makedirs(os.path.join(args.log_path, "csv"), exist_ok=True)
                 path = os.path.join(args.log_path, "csv", f"{config_name}_stage{trainer.pstate.stage}_rank{rank}.csv")
@@ -122,10 +144,30 @@ def main(argv=None) -> None:
                                [f"{row[r]:.2f}" for r in regions[1:]] + [f"{mem:.0f}"])
         if args.save and args.save_interval and (it + 1) % args.save_interval == 0:
             checkpointing.save_checkpoint(trainer, args.save)
+        if args.eval_interval and (it + 1) % args.eval_interval == 0:
+            ev = trainer.evaluate(batch_fn(10 ** 6 + it * args.eval_iters + j) for j in range(args.eval_iters))
+            if rank == world - 1:
+                print(f" validation loss at iteration {it + 1} | " +
+                      " | ".join(f"{k} value: {v:.6E}" for k, v in ev.items()), flush=True)
+            if writer is not None:
+                for k, v in ev.items():
+                    writer.add_scalar(f"{k} validation", v, it + 1)
         if args.exit_interval and (it + 1) % args.exit_interval == 0:
             break
+        if args.exit_duration_in_mins is not None:
+            # every rank must take the same decision: the slowest clock decides
+            over = torch.tensor([float((time.time() - t_start) / 60.0 > args.exit_duration_in_mins)],
+                                device=trainer.device)
+            if world > 1:
+                dist.all_reduce(over, op=dist.ReduceOp.MAX)
+            if over.item() > 0:
+                if rank == 0:
+                    print(f"exiting after {(time.time() - t_start) / 60.0:.1f} minutes at iteration {it + 1}", flush=True)
+                break
     if args.save:
         checkpointing.save_checkpoint(trainer, args.save)
+    if writer is not None:
+        writer.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -41,3 +41,24 @@ def test_cost_model_accuracy(tmp_path):
     assert acc["actual_time_ms"] == 110.0 and abs(acc["time_error_pct"] - 5.0) < 1e-9
     assert acc["actual_memory_mb"] == 1001
     assert abs(results.throughput(str(log), "cfg") - 8 / 0.110) < 1e-9
+
+
+def test_pretrain_eval_tensorboard_finetune_and_timed_exit(tmp_path, capsys):
+    plan_path = tmp_path / "gpt_tiny_1stages_demo.json"
+    plan_path.write_text(json.dumps(tiny_gpt_plan()))
+    common = ["--flexpipe-config", str(plan_path), "--lr-decay-iters", "10", "--hidden-dropout", "0",
+              "--attention-dropout", "0"]
+    pretrain.main(common + ["--train-iters", "2", "--eval-interval", "1", "--eval-iters", "1", "--tensorboard-dir",
+                            str(tmp_path / "tb"), "--save", str(tmp_path / "ckpt")])
+    out = capsys.readouterr().out
+    assert out.count("validation loss at iteration") == 2 and "lm loss ppl value" in out
+    assert any(f.startswith("events.out.tfevents") for f in os.listdir(tmp_path / "tb"))
+    # --finetune loads the weights and restarts the iteration count: two more iterations run
+    pretrain.main(common + ["--train-iters", "2", "--load", str(tmp_path / "ckpt"), "--finetune", "--no-load-rng"])
+    out = capsys.readouterr().out
+    assert "iteration        1/       2" in out and "iteration        2/       2" in out
+    # a run past its time budget stops after the first iteration and still saves
+    pretrain.main(common + ["--train-iters", "50", "--exit-duration-in-mins", "0", "--save", str(tmp_path / "ckpt2")])
+    out = capsys.readouterr().out
+    assert "exiting after" in out and "iteration        2/" not in out
+    assert (tmp_path / "ckpt2" / "latest_checkpointed_iteration.txt").read_text().strip() == "1"
