@@ -45,6 +45,9 @@ int embedding_fwd_launch(const long long* ids, const long long* pos, const void*
 int embedding_bwd_launch(const long long* ids, const long long* pos, const void* g, float* dW, float* dP,
                          long long tokens, int H, long long v0, long long v1, float dropout_p,
                          unsigned long long seed, int num_sms, cudaStream_t stream);
+int embedding_bwd_sorted_launch(const long long* keys, const long long* order, const void* g, float* dst,
+                                long long tokens, int H, long long k0, long long k1, float dropout_p,
+                                unsigned long long seed, cudaStream_t stream);
 int ce_stats_launch(const void* logits, int ld, const long long* targets, float* row_max, float* row_sum,
                     float* row_tgt, long long rows, int V, long long v0, cudaStream_t stream);
 int ce_finalize_launch(void* logits, int ld, const long long* targets, const float* gmax, const float* gsum,
@@ -324,6 +327,23 @@ void embedding_bwd(const Tensor& ids, const OptTensor& pos, const Tensor& g, con
                                          static_cast<float>(dropout_p), static_cast<unsigned long long>(seed), num_sms(),
                                          cur_stream()),
                "embedding_bwd");
+}
+
+// dst[key - k0] += sum of the (dropout-masked) rows of g whose key equals `key`; keys ascending, order[p] = token of keys[p]
+void embedding_bwd_sorted(const Tensor& keys, const Tensor& order, const Tensor& g, const Tensor& dst, int64_t k0,
+                          double dropout_p, int64_t seed) {
+  TORCH_CHECK(g.scalar_type() == torch::kBFloat16 && g.is_contiguous() && g.is_cuda());
+  TORCH_CHECK(keys.scalar_type() == torch::kInt64 && order.scalar_type() == torch::kInt64 && keys.is_contiguous() &&
+              order.is_contiguous() && keys.numel() == order.numel() && keys.numel() * g.size(-1) == g.numel());
+  TORCH_CHECK(dst.scalar_type() == torch::kFloat32 && dst.is_contiguous() && dst.size(-1) == g.size(-1));
+  c10::cuda::CUDAGuard guard(g.device());
+  check_launch(ssb::embedding_bwd_sorted_launch(reinterpret_cast<const long long*>(keys.data_ptr<int64_t>()),
+                                                reinterpret_cast<const long long*>(order.data_ptr<int64_t>()),
+                                                g.data_ptr(), dst.data_ptr<float>(), keys.numel(),
+                                                static_cast<int>(g.size(-1)), k0, k0 + dst.size(0),
+                                                static_cast<float>(dropout_p), static_cast<unsigned long long>(seed),
+                                                cur_stream()),
+               "embedding_bwd_sorted");
 }
 
 // returns [3, rows] fp32: local max, sum exp(x - max), target logit (0 when the target is not local)
@@ -656,6 +676,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sgd_step", &sgd_step);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
+  m.def("embedding_bwd_sorted", &embedding_bwd_sorted);
   m.def("ce_stats", &ce_stats);
   m.def("ce_finalize", &ce_finalize);
   m.def("attn_fwd", &attn_fwd);

@@ -93,6 +93,49 @@ embedding_bwd_kernel(const long long* __restrict__ ids, const long long* __restr
   }
 }
 
+// Order-independent variant of the scatter above: `keys` are the row indices (token ids, or positions) in
+// ascending order and `order[p]` is the token that holds keys[p].  Block p works only if it is the first of its
+// run of equal keys; it then sums the run's rows in the order given and adds the total to row keys[p] - k0 of dst
+// with plain stores (no other block touches that row), so repeated runs give bitwise equal results.
+__global__ void __launch_bounds__(256)
+embedding_bwd_sorted_kernel(const long long* __restrict__ keys, const long long* __restrict__ order,
+                            const __nv_bfloat16* __restrict__ g, float* __restrict__ dst, long long tokens, int H,
+                            long long k0, long long k1, float dropout_p, unsigned long long seed) {
+  const long long p = blockIdx.x;
+  const long long key = keys[p];
+  if (key < k0 || key >= k1) return;
+  if (p > 0 && keys[p - 1] == key) return;
+  const uint32_t keep16 = dropout_keep16(dropout_p);
+  const float scale = dropout_p > 0.f ? 65536.0f / static_cast<float>(keep16) : 1.0f;
+  const int nvec = H / 8;
+  for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (long long j = p; j < tokens && keys[j] == key; ++j) {
+      const long long v = order[j] * nvec + c;
+      const uint4 q = *reinterpret_cast<const uint4*>(g + v * 8);
+      float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), cc = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+      float f[8] = {a.x, a.y, b.x, b.y, cc.x, cc.y, d.x, d.y};
+      if (dropout_p > 0.f) {
+        const uint32_t m0 = dropout_keep4(seed, static_cast<uint64_t>(v) * 2, keep16);
+        const uint32_t m1 = dropout_keep4(seed, static_cast<uint64_t>(v) * 2 + 1, keep16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          f[i] = ((m0 >> i) & 1u) ? f[i] * scale : 0.f;
+          f[4 + i] = ((m1 >> i) & 1u) ? f[4 + i] * scale : 0.f;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    float4* out = reinterpret_cast<float4*>(dst + (key - k0) * H + c * 8);
+    float4 lo = out[0], hi = out[1];
+    lo.x += acc[0]; lo.y += acc[1]; lo.z += acc[2]; lo.w += acc[3];
+    hi.x += acc[4]; hi.y += acc[5]; hi.z += acc[6]; hi.w += acc[7];
+    out[0] = lo;
+    out[1] = hi;
+  }
+}
+
 __device__ __forceinline__ float block_reduce(float v, bool is_max, float* sm) {
   v = is_max ? warp_max(v) : warp_sum(v);
   __syncthreads();  // protects `sm` between successive calls
@@ -200,6 +243,16 @@ int embedding_bwd_launch(const long long* ids, const long long* pos, const void*
   const int blocks = static_cast<int>(want < 1 ? 1 : (want > num_sms * 32LL ? num_sms * 32LL : want));
   embedding_bwd_kernel<<<blocks, 256, 0, stream>>>(ids, pos, reinterpret_cast<const __nv_bfloat16*>(g), dW, dP,
                                                    tokens, H, v0, v1, dropout_p, seed);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int embedding_bwd_sorted_launch(const long long* keys, const long long* order, const void* g, float* dst,
+                                long long tokens, int H, long long k0, long long k1, float dropout_p,
+                                unsigned long long seed, cudaStream_t stream) {
+  if (H % 8) return -3;
+  if (tokens < 1 || tokens > 0x7fffffffLL) return -4;
+  embedding_bwd_sorted_kernel<<<static_cast<unsigned>(tokens), 256, 0, stream>>>(
+      keys, order, reinterpret_cast<const __nv_bfloat16*>(g), dst, tokens, H, k0, k1, dropout_p, seed);
   return static_cast<int>(cudaGetLastError());
 }
 

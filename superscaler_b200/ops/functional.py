@@ -12,6 +12,7 @@ numerics oracles use.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -582,6 +583,9 @@ def scaled_softmax(x, scale=1.0, mode=0, mask=None):
 # --------------------------------------------------------------------------------------------
 # Embedding and LM head + cross entropy
 # --------------------------------------------------------------------------------------------
+_DETERMINISTIC_EMBEDDING_GRAD = [os.environ.get("SSB_EMBEDDING_GRAD_ATOMICS", "0") != "1"]
+
+
 class EmbeddingFn(torch.autograd.Function):
     """dropout(W[ids - v0] (0 outside the local vocab range) + P[pos]).  Vocab-parallel ranks all-reduce the
     result outside (reference: runtime/megatron/mpu/layers.py:136-205, flex_ops.py:229-380)."""
@@ -617,8 +621,15 @@ class EmbeddingFn(torch.autograd.Function):
             dP = None
             if P is not None:
                 dP = mgP if mgP is not None else torch.zeros(P.shape, dtype=torch.float32, device=g.device)
-            native.ext().embedding_bwd(ids.contiguous().view(-1), pos.contiguous().view(-1) if pos is not None
-                                       else None, g, dW, dP, v0, dropout_p, seed)
+            if _DETERMINISTIC_EMBEDDING_GRAD[0]:
+                # rows are summed run by run in token order: repeated runs give bitwise equal gradients
+                for keys_t, dst, k0 in ((ids, dW, v0), (pos, dP, 0)):
+                    if keys_t is not None and dst is not None:
+                        keys, order = torch.sort(keys_t.contiguous().view(-1), stable=True)
+                        native.ext().embedding_bwd_sorted(keys, order, g, dst, k0, dropout_p, seed)
+            else:
+                native.ext().embedding_bwd(ids.contiguous().view(-1), pos.contiguous().view(-1) if pos is not None
+                                           else None, g, dW, dP, v0, dropout_p, seed)
             return (None, None, None if mgW is not None else dW.to(W.dtype),
                     None if (P is None or mgP is not None) else dP.to(P.dtype), None, None, None)
         flat = ids.view(-1)
@@ -630,6 +641,12 @@ class EmbeddingFn(torch.autograd.Function):
             dP = torch.zeros(P.shape, dtype=torch.float32)
             dP.index_add_(0, pos.view(-1), g.float())
         return (None, None, _vec_grad(W, dW), _vec_grad(P, dP) if P is not None else None, None, None, None)
+
+
+def set_deterministic_embedding_grad(on: bool) -> None:
+    """Selects how the embedding gradient is scattered on the GPU: sorted runs with plain stores (order
+    independent, the default) or float atomics (order dependent in the last bit)."""
+    _DETERMINISTIC_EMBEDDING_GRAD[0] = bool(on)
 
 
 def embedding(ids, pos, W, P=None, v0=0, dropout_p=0.0, seed=0):

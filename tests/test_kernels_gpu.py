@@ -257,6 +257,35 @@ def test_embedding_and_cross_entropy():
     assert rel(loss, ref) < 1e-4 and rel(logits, lf.grad) < 6e-3
 
 
+def test_sorted_embedding_backward_is_exact_and_repeatable():
+    """The run-by-run scatter equals the fp32 index_add, also with dropout (against the atomic kernel, which draws
+    the same mask), for a vocabulary shard, and gives bitwise equal results when repeated."""
+    torch.manual_seed(12)
+    V, H, T = 700, 2048, 4096
+    ids = torch.randint(0, V, (T,), device=DEV)
+    ids[::7] = 3                                    # one heavily repeated token
+    pos = torch.arange(T, device=DEV) % 128
+    g = torch.randn(T, H, device=DEV).bfloat16()
+
+    def sorted_grad(keys_t, rows, k0, p, seed):
+        out = torch.zeros(rows, H, device=DEV)
+        keys, order = torch.sort(keys_t, stable=True)
+        native.ext().embedding_bwd_sorted(keys, order, g, out, k0, p, seed)
+        return out
+
+    dW = sorted_grad(ids, V, 0, 0.0, 0)
+    assert rel(dW, torch.zeros(V, H, device=DEV).index_add_(0, ids, g.float())) < 1e-6
+    dP = sorted_grad(pos, 128, 0, 0.0, 0)
+    assert rel(dP, torch.zeros(128, H, device=DEV).index_add_(0, pos, g.float())) < 1e-6
+    shard = sorted_grad(ids, 300, 400, 0.0, 0)      # rows 400..699 only
+    assert rel(shard, torch.zeros(V, H, device=DEV).index_add_(0, ids, g.float())[400:]) < 1e-6
+    aW, aP = torch.zeros(V, H, device=DEV), torch.zeros(128, H, device=DEV)
+    native.ext().embedding_bwd(ids, pos, g, aW, aP, 0, 0.1, 77)
+    assert rel(sorted_grad(ids, V, 0, 0.1, 77), aW) < 1e-5 and rel(sorted_grad(pos, 128, 0, 0.1, 77), aP) < 1e-5
+    assert torch.equal(sorted_grad(ids, V, 0, 0.1, 77), sorted_grad(ids, V, 0, 0.1, 77))
+    assert native.check_status() == 0
+
+
 @pytest.mark.parametrize("cfg", [(1, 1, 128, 128, False), (1, 2, 256, 128, True), (2, 3, 512, 128, True),
                                  (2, 2, 256, 64, True), (1, 2, 384, 64, False), (1, 2, 200, 128, False)])
 def test_flash_attention_fwd_bwd(cfg):

@@ -47,6 +47,19 @@ def test_recompute_replays_dropout_exactly():
     assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5
 
 
+def test_replays_from_one_seed_are_bitwise_equal():
+    """Race smoke test: three runs from the same seed (dropout on, recompute on for one layer) must agree bit for
+    bit in every loss and in every parameter; no kernel of the training step may depend on execution order."""
+    runs = []
+    for _ in range(3):
+        losses, t = _run(_plan(recompute=1), steps=3, seed=4321)
+        runs.append((losses, t.store.master.clone()))
+        del t
+    for losses, master in runs[1:]:
+        assert losses == runs[0][0]
+        assert torch.equal(master, runs[0][1])
+
+
 def test_t5_and_resnet_train_on_gpu():
     from superscaler_b200.data.synthetic import resnet_batch, t5_batch
     from helpers import tiny_resnet_plan, tiny_t5_plan
