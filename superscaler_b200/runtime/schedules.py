@@ -231,6 +231,29 @@ class PipelineRunner:
                 grads[k] = t.grad if t.grad is not None else torch.zeros_like(t)
         return grads
 
+    def run_forward_only(self, batch, loss_buf: torch.Tensor) -> torch.Tensor:
+        """Evaluation: every micro-batch flows through the stages once, nothing is kept (call under no_grad).
+        Uses boundaries of its own, because the tensor descriptions exchanged on first use record whether a
+        gradient flows back, which differs between training and evaluation."""
+        if not hasattr(self, "_eval_bounds"):
+            self._eval_bounds = (Boundary(self.t, self.stage - 1) if self.stage > 0 else None,
+                                 Boundary(self.t, self.stage) if self.stage < self.P - 1 else None)
+        train_bounds = (self.prev, self.next)
+        self.prev, self.next = self._eval_bounds
+        try:
+            for mb in range(self.t.num_microbatches):
+                received = None
+                if self.prev is not None:
+                    received, _ = self._exchange(recv_fwd=True)
+                st, _ = self._forward(batch, mb, received)
+                if self.next is None:
+                    loss_buf += st["loss"]
+                else:
+                    self._exchange(send_fwd=self._outputs(st))
+        finally:
+            self.prev, self.next = train_bounds
+        return loss_buf
+
     # ---- the schedule ---------------------------------------------------------------------------
     def run(self, batch, loss_buf: torch.Tensor) -> torch.Tensor:
         M = self.t.num_microbatches
@@ -275,7 +298,7 @@ class PipelineRunner:
 
 # ---- interleaved (virtual-stage) 1F1B ---------------------------------------------------------------
 
-def interleaved_program(P: int, v: int, M: int, p: int) -> List[tuple]:
+def interleaved_program(P: int, v: int, M: int, p: int, forward_only: bool = False) -> List[tuple]:
     """The ordered program of physical stage `p` for one iteration of interleaved 1F1B with P physical stages,
     v model chunks per stage and M micro-batches (M a multiple of P).
 
@@ -286,6 +309,7 @@ def interleaved_program(P: int, v: int, M: int, p: int) -> List[tuple]:
     min(2 (P - p - 1) + (v - 1) P, M v) warm-up forwards (all M v when M == P), then forward / backward pairs, then
     the remaining backwards; backward step k belongs to chunk v - 1 - (k mod P v) // P.  After every compute
     step the stage sends what it produced and receives exactly what its NEXT forward and backward steps consume.
+    With forward_only (evaluation) the program is the chain of forward steps alone.
     """
     assert v >= 1 and P >= 1 and M % P == 0, "the number of micro-batches must be a multiple of the stage count"
     T = M * v
@@ -310,15 +334,17 @@ def interleaved_program(P: int, v: int, M: int, p: int) -> List[tuple]:
     def send_bwd(k):
         return [("send_bwd",) + bwd(k)] if not (first and bwd(k)[0] == 0) else []
 
-    warm = T if M == P else min(2 * (P - p - 1) + (v - 1) * P, T)
+    warm = T if (M == P or forward_only) else min(2 * (P - p - 1) + (v - 1) * P, T)
     rem = T - warm
     prog: List[tuple] = [("X", recv_fwd(0))]
     for k in range(warm):
         prog.append(("F",) + fwd(k))
         ops = send_fwd(k) + recv_fwd(k + 1)
-        if k == warm - 1:
+        if k == warm - 1 and not forward_only:
             ops += recv_bwd(0)
         prog.append(("X", ops))
+    if forward_only:
+        return [e for e in prog if e[0] != "X" or e[1]]
     for k in range(rem):
         fk = k + warm
         prog.append(("F",) + fwd(fk))
@@ -330,14 +356,14 @@ def interleaved_program(P: int, v: int, M: int, p: int) -> List[tuple]:
     return [e for e in prog if e[0] != "X" or e[1]]
 
 
-def simulate_programs(P: int, v: int, M: int, t_fwd: float = 1.0, t_bwd: float = 2.0):
+def simulate_programs(P: int, v: int, M: int, t_fwd: float = 1.0, t_bwd: float = 2.0, forward_only: bool = False):
     """Runs the P programs of interleaved_program against each other on a model of batched point-to-point
     calls: a batch completes when each of its transfers has met the matching transfer of the peer, transfers
     between one pair of stages in one direction match in the order they were posted, and a stage does nothing
     else while a batch is pending.  Returns (finish time, bubble fraction) or raises on a deadlock, on a
     transfer that meets the wrong partner, or on a compute step whose input never arrived.
     """
-    progs = [interleaved_program(P, v, M, p) for p in range(P)]
+    progs = [interleaved_program(P, v, M, p, forward_only) for p in range(P)]
     pc = [0] * P
     clock = [0.0] * P
     busy = [0.0] * P
@@ -425,14 +451,30 @@ class InterleavedRunner:
         self.t = trainer
         ps = trainer.pstate
         self.stage, self.P, self.v = ps.stage, ps.num_stages, trainer.interleave
+        self.prev, self.next = self._boundaries()
+        self.program = None
+
+    def _boundaries(self):
         total = self.P * self.v
-        self.prev: List[Optional[Boundary]] = []
-        self.next: List[Optional[Boundary]] = []
+        prev: List[Optional[Boundary]] = []
+        nxt: List[Optional[Boundary]] = []
         for c in range(self.v):
             s = c * self.P + self.stage
-            self.prev.append(Boundary(trainer, s - 1) if s > 0 else None)
-            self.next.append(Boundary(trainer, s) if s < total - 1 else None)
-        self.program = None
+            prev.append(Boundary(self.t, s - 1) if s > 0 else None)
+            nxt.append(Boundary(self.t, s) if s < total - 1 else None)
+        return prev, nxt
+
+    def run_forward_only(self, batch, loss_buf: torch.Tensor) -> torch.Tensor:
+        """Evaluation pass (call under no_grad); see PipelineRunner.run_forward_only for the separate boundaries."""
+        if not hasattr(self, "_eval_bounds"):
+            self._eval_bounds = self._boundaries()
+            self._eval_program = interleaved_program(self.P, self.v, self.t.num_microbatches, self.stage, True)
+        train = (self.prev, self.next, self.program)
+        (self.prev, self.next), self.program = self._eval_bounds, self._eval_program
+        try:
+            return self.run(batch, loss_buf, forward_only=True)
+        finally:
+            self.prev, self.next, self.program = train
 
     def _exchange(self, ops_spec, outputs, in_grads, sent_sides):
         """One batched group call.  outputs[(c, mb)] = (tensors, sides) to send downstream, in_grads[(c, mb)] =
@@ -461,7 +503,7 @@ class InterleavedRunner:
         _run_batch(ops)
         return {k: asm() for k, asm in fwd_asm}, {k: asm() for k, asm in bwd_asm}
 
-    def run(self, batch, loss_buf: torch.Tensor) -> torch.Tensor:
+    def run(self, batch, loss_buf: torch.Tensor, forward_only: bool = False) -> torch.Tensor:
         t = self.t
         M = t.num_microbatches
         assert M % self.P == 0, "interleaved 1F1B needs a micro-batch count that is a multiple of the stage count"
@@ -489,10 +531,15 @@ class InterleavedRunner:
                     st["_meta"].update(sides)
                     inputs = tensors
                 t.stage.forward(st, chunk=c)
-                live[(c, mb)] = (st, inputs)
                 if self.next[c] is not None:
                     keys = self.next[c].keys
                     outputs[(c, mb)] = ({k: st[k] for k in keys}, {k: st["_meta"][k] for k in keys})
+                if forward_only:
+                    if self.next[c] is None:
+                        loss_buf += st["loss"]
+                    continue
+                live[(c, mb)] = (st, inputs)
+                if self.next[c] is not None:
                     sent_sides[(c, mb)] = outputs[(c, mb)][1]
             else:
                 _, c, mb = e

@@ -234,13 +234,14 @@ class Trainer:
                 batch = self.to_device(batch)
                 self._loss_buf.zero_()
                 if self.pipeline is not None:
-                    raise NotImplementedError("evaluate() runs single-stage plans")
-                for mb in range(self.num_microbatches):
-                    st = self.microbatch_inputs(batch, mb)
-                    if self.world_size > 1:
-                        st["_meta"] = {}
-                    self.stage.forward(st)
-                    self._loss_buf += st["loss"]
+                    self.pipeline.run_forward_only(batch, self._loss_buf)
+                else:
+                    for mb in range(self.num_microbatches):
+                        st = self.microbatch_inputs(batch, mb)
+                        if self.world_size > 1:
+                            st["_meta"] = {}
+                        self.stage.forward(st)
+                        self._loss_buf += st["loss"]
                 total += self.loss_value({"loss_tensor": self._loss_buf})
                 n += 1
         finally:

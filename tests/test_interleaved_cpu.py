@@ -81,3 +81,25 @@ def test_interleaved_training_matches_single_process(tmp_path, gpus, tp, v, ckpt
     base = _losses(tiny_gpt_plan(**KW))
     plan = interleave_plan(tiny_gpt_plan(**KW, num_gpus=gpus, tp=tp), v)
     run_ranks(_worker, sum(gpus), plan, base, str(tmp_path / "ckpt") if ckpt else None)
+
+
+def _eval_then_train(plan, rank=0, world=1):
+    t = Trainer(plan, rank=rank, world_size=world, model_overrides=NODROP, lr_warmup_steps=0, device="cpu", lr=1e-3)
+    batch = gpt_batch(12, 32, 256, seed=1)
+    before = t.evaluate([batch, gpt_batch(12, 32, 256, seed=2)])["lm loss"]   # evaluation first: own boundaries
+    losses = [t.loss_value(t.train_step(batch)) for _ in range(2)]
+    after = t.evaluate([batch])["lm loss"]
+    return [before] + losses + [after]
+
+
+def _eval_worker(rank, world, plan, want):
+    got = _eval_then_train(plan, rank, world)
+    assert max(abs(a - b) for a, b in zip(got, want)) < 3e-3, (rank, got, want)
+
+
+@pytest.mark.parametrize("v", [1, 2])
+def test_pipeline_evaluation_matches_single_process(v):
+    base = _eval_then_train(tiny_gpt_plan(**KW))
+    assert base[3] < base[1]           # evaluating after two steps sees the trained weights
+    plan = interleave_plan(tiny_gpt_plan(**KW, num_gpus=(1, 1), tp=[1, 1]), v)
+    run_ranks(_eval_worker, 2, plan, base)
