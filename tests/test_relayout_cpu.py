@@ -97,3 +97,26 @@ def _grad_worker(rank, world):
 
 def test_backward_is_the_conjugate_transfer():
     run_ranks(_grad_worker, 2)
+
+
+def _bcast_worker(rank, world):
+    import torch
+    import torch.distributed as dist
+    from superscaler_b200.parallel.data import broadcast_batch
+    group = dist.new_group([1, 2])
+    other = dist.new_group([0, 3])
+    keys = ["ids", "labels", "mask"]
+    src = {"ids": torch.arange(12).view(3, 4), "labels": torch.arange(12).view(3, 4) + 1,
+           "mask": torch.ones(3, 4, 2, dtype=torch.int64)}
+    if rank in (1, 2):
+        got = broadcast_batch(keys, src if rank == 1 else None, torch.int64, 1, group)
+    else:
+        got = broadcast_batch(keys, {k: v * 10 for k, v in src.items()} if rank == 3 else None, torch.int64, 3, other)
+    scale = 1 if rank in (1, 2) else 10
+    for k in keys:
+        assert got[k].shape == src[k].shape and (got[k] == src[k] * scale).all(), (rank, k)
+
+
+def test_broadcast_batch_inside_sub_groups():
+    from dist_utils import run_ranks
+    run_ranks(_bcast_worker, 4)
