@@ -32,9 +32,17 @@ if [ $N -gt 1 ]; then
   $RUN --nproc-per-node 2 -m superscaler_b200.profiler.p2p_profiler --prof-path "$DB"
 fi
 
-# 2. search (CPU only); micro-batch candidates up to the largest per-GPU size times N
-MBS=""; for m in $PER_GPU; do MBS="$MBS $m"; done
-last=${PER_GPU##* }; m=$((last * 2)); while [ $m -le $((last * N)) ]; do MBS="$MBS $m"; m=$((m * 2)); done
+# 2. search (CPU only); micro-batch candidates: every per-GPU size times 1, 2, 4 ... N that divides the global batch
+MBS=$(python - "$GBS" "$N" $PER_GPU <<'PY'
+import sys
+gbs, n, per = int(sys.argv[1]), int(sys.argv[2]), [int(x) for x in sys.argv[3:]]
+cands, k = set(), 1
+while k <= n:
+    cands.update(p * k for p in per if gbs % (p * k) == 0)
+    k *= 2
+print(" ".join(map(str, sorted(cands))))
+PY
+)
 python -m superscaler_b200.search.search --model-name $MODEL --model-size $SIZE --global-batch-size $GBS \
     --micro-batch-size $MBS --max-tp $N --num-nodes 1 --num-gpus-per-node $N --memory-limit 170000 \
     --profiled-time-path "$DB" --config-save-path "$WORK/plans/" --log-path "$WORK/logs/" --shapes b200 \

@@ -97,6 +97,13 @@ class SearchArgs:
                 raise RuntimeError("should provide --num-layers for scale-layer exp")
         if self.micro_batch_size is None:
             self.micro_batch_size = [16, 32, 48, 64] if self.model_name == "resnet" else [1, 2, 4, 8]
+        # a micro-batch size that does not divide the global batch would be priced for fewer samples than the batch
+        # holds (the number of micro-batches is an integer division); such candidates are dropped
+        bad = [m for m in self.micro_batch_size if self.global_batch_size % m]
+        if bad:
+            print(f"micro-batch sizes {bad} do not divide the global batch {self.global_batch_size}: ignored")
+            self.micro_batch_size = [m for m in self.micro_batch_size if m not in bad]
+            assert self.micro_batch_size, "no micro-batch size divides the global batch"
         if self.start_num_stages is None or self.end_num_stages is None:
             self.start_num_stages, self.end_num_stages = 1, min(self.num_gpus, 16)
         if self.max_tp is None:
