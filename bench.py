@@ -219,7 +219,8 @@ def main():
                        "global_batch": gbs, "seq_len": seq, "parallelism": describe_parallelism(plan),
                        "num_microbatches": trainer.num_microbatches, "l2": "inputs_exceed_l2 (2.6 GB of weights + "
                        "activations stream through every step)", "layers": layers,
-                       "params": trainer.num_parameters(), "kernel_status": status, "last_loss": round(last_loss[0], 4)},
+                       "params": trainer.num_parameters(), "kernel_status": status, "last_loss": round(last_loss[0], 4),
+                       "max_allocated_mb": round(torch.cuda.max_memory_allocated() / 2 ** 20)},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 3), "unit": "samples/s", "ms_per_step": round(max(ms_e2e, wall_e2e), 2),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "clocks": clocks_e2e},
