@@ -67,6 +67,8 @@ def main(argv=None) -> None:
     ap.add_argument("--no-fused-comm", action="store_true")
     ap.add_argument("--interleave-factor", type=int, default=1,
                     help="model chunks per pipeline stage (interleaved 1F1B); re-cuts the plan's stages evenly")
+    ap.add_argument("--interleave-ops", type=int, nargs="+", default=None,
+                    help="ops of every virtual stage (stages x interleave-factor numbers) instead of the even cut")
     ap.add_argument("--distributed-backend", default=None, choices=[None, "nccl", "gloo"])
     args = ap.parse_args(argv)
     rank, world, _ = init_distributed(args.distributed_backend)
@@ -74,7 +76,7 @@ def main(argv=None) -> None:
         plan = json.load(f)
     if args.interleave_factor > 1:
         from .schedules import interleave_plan
-        plan = interleave_plan(plan, args.interleave_factor)
+        plan = interleave_plan(plan, args.interleave_factor, args.interleave_ops)
     overrides = {}
     if args.hidden_dropout is not None:
         overrides["hidden_dropout"] = args.hidden_dropout

@@ -50,6 +50,11 @@ def test_interleave_plan_recuts_the_stages():
     assert [t[0] for t in new["model_parallel_size_of_each_op"]] == [1, 2, 1, 1, 2, 1]
     flat = lambda p: [x for s in p["recompute_ops"] for x in s]
     assert flat(new) == flat(plan)
+    n = sum(plan["num_ops_in_each_stage"])
+    explicit = interleave_plan(plan, 2, [5, 9, 7, 11, 13, n - 45])
+    assert explicit["num_ops_in_each_stage"] == [5, 9, 7, 11, 13, n - 45] and flat(explicit) == flat(plan)
+    with pytest.raises(AssertionError):
+        interleave_plan(plan, 2, [5, 9, 7])
     mixed = tiny_gpt_plan(**KW, num_gpus=(2, 2), tp=[2, 1])
     mixed["model_parallel_size_of_each_op"][0][3] = 1
     with pytest.raises(AssertionError):
