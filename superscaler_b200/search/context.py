@@ -210,9 +210,16 @@ class SearchContext:
         self.db = ProfileDB(db_model, args.model_size, args.profiled_time_path, args.micro_batch_size, args.max_tp,
                             self.unique_ops, use_reserved=args.consider_reserved_space, verbose=verbose)
         main_f, opt_f = STATE_MULTIPLIERS["gpt" if args.model_name == "scale-layer" else args.model_name]
+        shared_space = args.consider_shared_space
+        if getattr(args, "shapes", "reference") == "b200" and args.model_name == "resnet":
+            # tables measured with this framework's runtime: the Wide-ResNet trains in bf16 with fp32 master weights
+            # like the transformers (the weights column holds bf16 bytes), and its fused BatchNorm + add + ReLU op
+            # keeps activations of its own, so the reference's aliasing rule for bn3 / downsample does not apply
+            main_f, opt_f = STATE_MULTIPLIERS["gpt"]
+            shared_space = False
         self.cost = CostModel(self.db, CostOptions(
             memory_limit=args.memory_limit, num_gpus_per_node=args.num_gpus_per_node, main_params_factor=main_f,
-            optimizer_factor=opt_f, resharding=args.resharding, consider_shared_space=args.consider_shared_space,
+            optimizer_factor=opt_f, resharding=args.resharding, consider_shared_space=shared_space,
             consider_reserved_space=args.consider_reserved_space,
             consider_collective_memory=args.consider_collective_memory, support_comm_predict=args.support_comm_predict,
             memory_pred_type=args.memory_pred_type, flex_recompute=args.flex_recompute,
