@@ -47,6 +47,29 @@ def _model_factory(model_name: str):
     raise ValueError(f"unknown model {model_name}")
 
 
+def _validate_plan(plan: dict) -> None:
+    """Shape checks of a plan JSON with messages that name the offending stage (a wrong plan otherwise fails deep
+    inside group creation or a kernel launch)."""
+    counts = plan["num_ops_in_each_stage"]
+    keys = ("model_parallel_size_of_each_op", "data_parallel_size_of_each_op", "algo_of_each_op", "recompute_ops")
+    for k in keys:
+        if len(plan[k]) != len(counts):
+            raise ValueError(f"plan[{k!r}] lists {len(plan[k])} stages, num_ops_in_each_stage lists {len(counts)}")
+    if len(plan["num_gpus"]) != len(counts):
+        raise ValueError(f"num_gpus lists {len(plan['num_gpus'])} stages, num_ops_in_each_stage lists {len(counts)}")
+    for s, n in enumerate(counts):
+        for k in keys:
+            if len(plan[k][s]) != n:
+                raise ValueError(f"stage {s}: {k} has {len(plan[k][s])} entries for {n} ops")
+        g = plan["num_gpus"][s]
+        for i, (tp, dp) in enumerate(zip(plan["model_parallel_size_of_each_op"][s],
+                                         plan["data_parallel_size_of_each_op"][s])):
+            if tp * dp != g:
+                raise ValueError(f"stage {s} op {i}: tp {tp} x dp {dp} does not equal the stage's {g} GPUs")
+            if plan["micro_batch_size"] % dp:
+                raise ValueError(f"stage {s} op {i}: dp {dp} does not divide the micro batch {plan['micro_batch_size']}")
+
+
 class Trainer:
     def __init__(self, plan: dict, *, rank: int = 0, world_size: int = 1, device=None, seed: int = 1234,
                  model_overrides: Optional[dict] = None, lr: float = 1.5e-4, min_lr: float = 1e-5,
@@ -63,7 +86,10 @@ class Trainer:
         self.cfg = cfg_fn(plan, **(model_overrides or {}))
         self.global_bs = plan["global_batch_size"]
         self.micro_bs = plan["micro_batch_size"]
+        if self.global_bs % self.micro_bs:
+            raise ValueError(f"micro batch size {self.micro_bs} does not divide the global batch {self.global_bs}")
         self.num_microbatches = self.global_bs // self.micro_bs
+        _validate_plan(plan)
         names = names_fn(self.cfg)
         counts = plan["num_ops_in_each_stage"]
         assert sum(counts) == len(names), f"plan covers {sum(counts)} ops, model has {len(names)}"

@@ -84,3 +84,23 @@ def test_memory_buffers_and_reports():
     rows = debug_mem_report(min_mb=0.5)
     assert any(r[1] == (1 << 18,) and r[3] >= 1.0 for r in rows)
     del big
+
+
+def test_plan_validation_messages():
+    import copy
+    import pytest
+    from superscaler_b200.runtime.trainer import Trainer
+    from helpers import tiny_gpt_plan
+    good = tiny_gpt_plan()
+    bad = copy.deepcopy(good)
+    bad["micro_batch_size"] = 3
+    with pytest.raises(ValueError, match="does not divide the global batch"):
+        Trainer(bad, device="cpu")
+    bad = copy.deepcopy(good)
+    bad["model_parallel_size_of_each_op"][0][4] = 2
+    with pytest.raises(ValueError, match="stage 0 op 4: tp 2 x dp 1"):
+        Trainer(bad, device="cpu")
+    bad = copy.deepcopy(good)
+    bad["recompute_ops"][0].pop()
+    with pytest.raises(ValueError, match="recompute_ops has"):
+        Trainer(bad, device="cpu")
