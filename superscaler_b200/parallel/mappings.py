@@ -69,6 +69,12 @@ def _all_to_all(t, split_dim, cat_dim, group):
     if n == 1:
         return t
     ins = [p.contiguous() for p in t.chunk(n, dim=split_dim)]
+    if dist.get_backend(group) == "gloo":
+        # gloo has no all-to-all: every rank gathers all inputs and keeps the pieces addressed to it (CPU tests)
+        everything = [torch.empty_like(t) for _ in range(n)]
+        dist.all_gather(everything, t.contiguous(), group=group)
+        outs = [e.chunk(n, dim=split_dim)[_rank(group)] for e in everything]
+        return torch.cat(outs, dim=cat_dim)
     outs = [torch.empty_like(ins[0]) for _ in range(n)]
     dist.all_to_all(outs, ins, group=group)
     return torch.cat(outs, dim=cat_dim)
