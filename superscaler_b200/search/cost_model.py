@@ -59,12 +59,30 @@ class CostModel:
         self._fo, self._bo = t["fwd_ovl"], t["bwd_ovl"]
         self._mi = db.mbs_index
         self._overlap = opt.price_overlap and db.has_overlap_columns
+        # per-name facts and the tp -> table index map, computed once (the search calls these millions of times)
+        self._lg = {1 << k: int(math.log(1 << k, 2)) for k in range(16)}
+        self._rc_cache: Dict[tuple, tuple] = {}
+        self._terms_cache: Dict[tuple, tuple] = {}
+        self._exact_mem_cache: Dict[tuple, object] = {}
+        self._kind: Dict[str, int] = {}          # 0 plain, 1 counted 1.5x (attention dropout), 2 aliases a neighbour
+        self._starts_layer: Dict[str, bool] = {}
 
     # ---- time -------------------------------------------------------------------------------
     def stage_time_terms(self, ops, mbs, tp, algo, dp, in_cross_node, out_cross_node):
-        """(fwd us, bwd us, boundary-in us, boundary-out us, tp/reshard comm us)."""
+        """(fwd us, bwd us, boundary-in us, boundary-out us, tp/reshard comm us).  Memoised on its exact
+        arguments: the search prices the same stage slice many times."""
         if len(ops) == 0:
             return 0, 0, 0, 0, 0
+        key = (tuple(ops), tuple(mbs), tuple(tp), tuple(algo), tuple(dp), in_cross_node, out_cross_node)
+        hit = self._terms_cache.get(key)
+        if hit is None:
+            if len(self._terms_cache) > 50000:
+                self._terms_cache.clear()
+            hit = self._terms_cache[key] = self._stage_time_terms(ops, mbs, tp, algo, dp, in_cross_node,
+                                                                  out_cross_node)
+        return hit
+
+    def _stage_time_terms(self, ops, mbs, tp, algo, dp, in_cross_node, out_cross_node):
         mi, db = self._mi, self.db
         fwd = bwd = 0
         tp_comm = 0
@@ -132,70 +150,88 @@ class CostModel:
 
     # ---- memory -----------------------------------------------------------------------------
     def _act(self, op, mbs, tp, algo):
-        return self._a[op][self._mi[mbs]][int(math.log(tp, 2))][algo]
+        return self._a[op][self._mi[mbs]][self._lg[tp]][algo]
+
+    def _act_arrays(self, ops, mbs, tp, algo):
+        """Per op of a stage: its activation size, its accounting kind (see _kind) and whether the NEXT op starts a
+        layer (recompute segments end there).  The three passes below walk these lists instead of the tables."""
+        kind_of, starts = self._kind, self._starts_layer
+        shared = self.opt.consider_shared_space
+        a, mi, lg = self._a, self._mi, self._lg
+        acts, kinds, ends = [], [], []
+        n = len(ops)
+        for i in range(n):
+            op = ops[i]
+            acts.append(a[op][mi[mbs[i]]][lg[tp[i]]][algo[i]])
+            k = kind_of.get(op)
+            if k is None:
+                k = kind_of[op] = 1 if op == "enc-attention-dropout" else (2 if _shares_buffer(op) else 0)
+            kinds.append(k if shared else 0)
+            if i + 1 < n:
+                nxt = ops[i + 1]
+                e = starts.get(nxt)
+                if e is None:
+                    e = starts[nxt] = nxt in ("enc-1st-layernorm",) or "-conv1" in nxt
+                ends.append(e)
+        return acts, kinds, ends
+
+    @staticmethod
+    def _saved_fast(recompute, acts, kinds, ends):
+        n = len(acts)
+        if n <= 1 or sum(recompute) == 0:
+            return 0
+        saved = 0
+        for i in range(n - 1):
+            if recompute[i] == 1 and recompute[i + 1] == 1:
+                k = kinds[i]
+                if k == 1:
+                    saved += acts[i] * 1.5
+                elif k == 0 and not ends[i]:
+                    saved += acts[i]
+        return saved
+
+    @staticmethod
+    def _peak_fast(recompute, acts, kinds, ends):
+        n = len(acts)
+        if n <= 1 or sum(recompute) == 0:
+            return 0
+        run = 0
+        best = 0
+        last = n - 1
+        for i in range(last):
+            if recompute[i] == 1 and recompute[i + 1] == 1:
+                k = kinds[i]
+                if k == 1:
+                    run += acts[i] * 1.5
+                elif k == 0:
+                    run += acts[i]
+                    if ends[i] or i + 1 == last:
+                        if run > best:
+                            best = run
+                        run = 0
+            elif run > 0:
+                if run > best:
+                    best = run
+                run = 0
+        return best
 
     def activation_size(self, op, mbs, tp, algo=0):
         return self._act(op, mbs, tp, algo)
 
-    def _memory_terms(self, ops, mbs, tp, algo):
-        inputs = self._in[ops[0]][self._mi[mbs[0]]][int(math.log(tp[0], 2))][algo[0]]
+    def _memory_terms(self, ops, mbs, tp, algo, arrays=None):
+        inputs = self._in[ops[0]][self._mi[mbs[0]]][self._lg[tp[0]]][algo[0]]
+        act_of, kinds, _ = arrays if arrays is not None else self._act_arrays(ops, mbs, tp, algo)
         acts = 0
         weights = 0
-        shared = self.opt.consider_shared_space
+        w, mi, lg = self._w, self._mi, self._lg
         for i in range(len(ops)):
-            op = ops[i]
-            if shared and op == "enc-attention-dropout":
-                acts += self._act(op, mbs[i], tp[i], algo[i]) * 1.5
-            elif shared and _shares_buffer(op):
-                acts += 0
-            else:
-                acts += self._act(op, mbs[i], tp[i], algo[i])
-            weights += self._w[op][self._mi[mbs[i]]][int(math.log(tp[i], 2))][algo[i]]
+            k = kinds[i]
+            if k == 1:
+                acts += act_of[i] * 1.5
+            elif k == 0:
+                acts += act_of[i]
+            weights += w[ops[i]][mi[mbs[i]]][lg[tp[i]]][algo[i]]
         return weights, inputs, acts
-
-    def _saved_by_recompute(self, ops, recompute, mbs, tp, algo):
-        if len(ops) <= 1 or sum(recompute) == 0:
-            return 0
-        saved = 0
-        shared = self.opt.consider_shared_space
-        for i in range(len(ops) - 1):
-            if recompute[i] == 1 and recompute[i + 1] == 1:
-                op = ops[i]
-                if shared and op == "enc-attention-dropout":
-                    saved += self._act(op, mbs[i], tp[i], algo[i]) * 1.5
-                elif shared and _shares_buffer(op):
-                    saved += 0
-                elif ops[i + 1] in ("enc-1st-layernorm",) or "-conv1" in ops[i + 1]:
-                    saved += 0
-                else:
-                    saved += self._act(op, mbs[i], tp[i], algo[i])
-        return saved
-
-    def _peak_recompute(self, ops, recompute, mbs, tp, algo):
-        """Largest activation footprint of any single recomputed segment while it is being replayed."""
-        if len(ops) <= 1 or sum(recompute) == 0:
-            return 0
-        run = 0
-        peaks = [0]
-        shared = self.opt.consider_shared_space
-        last = len(ops) - 1
-        for i in range(last):
-            if recompute[i] == 1 and recompute[i + 1] == 1:
-                op = ops[i]
-                if shared and _shares_buffer(op):
-                    run += 0
-                elif shared and op == "enc-attention-dropout":
-                    run += self._act(op, mbs[i], tp[i], algo[i]) * 1.5
-                else:
-                    run += self._act(op, mbs[i], tp[i], algo[i])
-                    if ops[i + 1] in ("enc-1st-layernorm",) or "-conv1" in ops[i + 1] or i + 1 == last:
-                        peaks.append(run)
-                        run = 0
-            else:
-                if run > 0:
-                    peaks.append(run)
-                    run = 0
-        return max(peaks)
 
     def _reserved(self, ops, mbs, tp, dp, algo, weight_mb):
         rf = rb = 0
@@ -226,13 +262,24 @@ class CostModel:
         raise RuntimeError(f"unknown memory_pred_type {self.opt.memory_pred_type}")
 
     def stage_memory(self, ops, recompute, tp, dp, micro_bs, stages_behind, algo, breakdown=False):
+        key = (tuple(ops), tuple(recompute), tuple(tp), tuple(dp), micro_bs, stages_behind, tuple(algo), breakdown)
+        hit = self._exact_mem_cache.get(key)
+        if hit is None:
+            if len(self._exact_mem_cache) > 50000:
+                self._exact_mem_cache.clear()
+            hit = self._exact_mem_cache[key] = self._stage_memory(ops, recompute, tp, dp, micro_bs, stages_behind,
+                                                                  algo, breakdown)
+        return hit
+
+    def _stage_memory(self, ops, recompute, tp, dp, micro_bs, stages_behind, algo, breakdown=False):
         mbs = [micro_bs // dp[j] for j in range(len(ops))]
-        w, inputs, acts = self._memory_terms(ops, mbs, tp, algo)
+        arrays = self._act_arrays(ops, mbs, tp, algo)
+        w, inputs, acts = self._memory_terms(ops, mbs, tp, algo, arrays)
         grads = w
         main = w * self.opt.main_params_factor
         optim = w * self.opt.optimizer_factor
-        saved = self._saved_by_recompute(ops, recompute, mbs, tp, algo)
-        peak_rc = self._peak_recompute(ops, recompute, mbs, tp, algo)
+        saved = self._saved_fast(recompute, *arrays)
+        peak_rc = self._peak_fast(recompute, *arrays)
         reserved = self._reserved(ops, mbs, tp, dp, algo, w) if self.opt.consider_reserved_space else 0
         in_flight = (inputs + acts - saved) * stages_behind
         peak = inputs + acts - saved + peak_rc
@@ -262,21 +309,36 @@ class CostModel:
         n = len(ops)
         if not self.opt.flex_recompute:
             return [1] * n
+        # the search asks the same question again and again (the same candidate move from many trials): the answer
+        # depends on nothing but these arguments
+        key = (tuple(ops), micro_bs, tuple(tp), tuple(dp), stages_behind, tuple(algo))
+        hit = self._rc_cache.get(key)
+        if hit is not None:
+            return list(hit)
+        rc = self._choose_recompute(ops, micro_bs, tp, dp, stages_behind, algo)
+        if len(self._rc_cache) > 50000:
+            self._rc_cache.clear()
+        self._rc_cache[key] = tuple(rc)
+        return rc
+
+    def _choose_recompute(self, ops, micro_bs, tp, dp, stages_behind, algo) -> List[int]:
+        n = len(ops)
         rc = [0] * n
         mem = self.stage_memory_cached(ops, rc, tp, dp, micro_bs, stages_behind, algo) + self.opt.peak_mem_in_backward
         limit = self.opt.memory_limit
         if mem - limit <= 0:
             return rc
+        mbs = [micro_bs // dp[i] for i in range(len(dp))]
+        acts, kinds, ends = self._act_arrays(ops, mbs, tp, algo)
         groups: Dict[str, dict] = {}
         for i in range(n):
             g = groups.setdefault(ops[i], {"index": [], "size": [], "done": False, "sum": 0})
-            sz = self._act(ops[i], micro_bs // dp[i], tp[i], algo[i]) * (stages_behind + 1)
+            sz = acts[i] * (stages_behind + 1)
             g["index"].append(i)
             g["size"].append(sz)
             g["sum"] += sz
-        mbs = [micro_bs // dp[i] for i in range(len(dp))]
         saved0 = 0
-        peak0 = self._peak_recompute(ops, rc, mbs, tp, algo)
+        peak0 = self._peak_fast(rc, acts, kinds, ends)
         never = self.opt.never_recompute
         while mem - limit > 0:
             # pick the not-yet-recomputed op kind with the largest total activation
@@ -309,10 +371,10 @@ class CostModel:
                         rc[i + 1] = 1
                 else:
                     break
-            saved1 = self._saved_by_recompute(ops, rc, mbs, tp, algo)
+            saved1 = self._saved_fast(rc, acts, kinds, ends)
             mem -= (saved1 - saved0) * (stages_behind + 1)
             saved0 = saved1
-            peak1 = self._peak_recompute(ops, rc, mbs, tp, algo)
+            peak1 = self._peak_fast(rc, acts, kinds, ends)
             mem += peak1 - peak0
             peak0 = peak1
         return rc
