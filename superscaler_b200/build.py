@@ -24,6 +24,7 @@ OBJ = CSRC / "build"
 EXT_SUFFIX = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
 TARGET = PKG / f"_C{EXT_SUFFIX}"
 HOST_SRC = PKG / "csrc_host"                      # host-only helpers (no CUDA, no torch): loadable on CPU boxes
+HOST_MODULES = {"dataset_helpers.cpp": "_data_helpers", "search_native.cpp": "_search_native"}
 HOST_TARGET = PKG / f"_data_helpers{EXT_SUFFIX}"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
@@ -97,13 +98,17 @@ def build(verbose: bool = False, force: bool = False) -> Path:
 
 
 def build_host_helpers(force: bool = False) -> Path:
-    """Dataset index builders: one pybind11 module compiled with the host compiler only."""
+    """Host-only helpers, one pybind11 module per source file, compiled with the host compiler only: the dataset
+    index builders and the inner loops of the search's cost model.  Floating-point contraction is off so that the
+    native cost model rounds exactly like its Python definition."""
     import pybind11
-    srcs = sorted(HOST_SRC.glob("*.cpp"))
-    if force or _newer(srcs, HOST_TARGET):
-        py_inc = sysconfig.get_paths()["include"]
-        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", f"-I{py_inc}", f"-I{pybind11.get_include()}",
-              *map(str, srcs), "-o", str(HOST_TARGET)])
+    py_inc = sysconfig.get_paths()["include"]
+    for src_name, module in HOST_MODULES.items():
+        src = HOST_SRC / src_name
+        target = PKG / f"{module}{EXT_SUFFIX}"
+        if force or _newer([src], target):
+            _run(["g++", "-O2", "-std=c++17", "-ffp-contract=off", "-fPIC", "-shared", f"-I{py_inc}",
+                  f"-I{pybind11.get_include()}", str(src), "-o", str(target)])
     return HOST_TARGET
 
 

@@ -48,6 +48,12 @@ def _shares_buffer(op: str) -> bool:
     return op in _SHARED_ZERO or "-bn3" in op or ("-downsample" in op and "0-0" not in op)
 
 
+try:  # built by `python -m superscaler_b200.build`; the Python definitions below are the same arithmetic
+    from .. import _search_native as _native
+except ImportError:  # pragma: no cover
+    _native = None
+
+
 class CostModel:
     def __init__(self, db: ProfileDB, opt: CostOptions):
         self.db, self.opt = db, opt
@@ -61,11 +67,30 @@ class CostModel:
         self._overlap = opt.price_overlap and db.has_overlap_columns
         # per-name facts and the tp -> table index map, computed once (the search calls these millions of times)
         self._lg = {1 << k: int(math.log(1 << k, 2)) for k in range(16)}
+        self._name_ids: Dict[tuple, int] = {}
+        self._stage_time_cache: Dict[tuple, float] = {}
         self._rc_cache: Dict[tuple, tuple] = {}
+        self._arrays_cache: Dict[tuple, tuple] = {}
+        self._names_cache: Dict[tuple, tuple] = {}
         self._terms_cache: Dict[tuple, tuple] = {}
         self._exact_mem_cache: Dict[tuple, object] = {}
         self._kind: Dict[str, int] = {}          # 0 plain, 1 counted 1.5x (attention dropout), 2 aliases a neighbour
         self._starts_layer: Dict[str, bool] = {}
+
+    # ---- memo keys ---------------------------------------------------------------------------
+    def _nid(self, ops) -> int:
+        """Small integer standing for the exact sequence of op names (memo keys hash it instead of the names)."""
+        names = tuple(ops)
+        i = self._name_ids.get(names)
+        if i is None:
+            i = self._name_ids[names] = len(self._name_ids)
+        return i
+
+    @staticmethod
+    def _ck(seq):
+        """Per-op list as a memo key part: the value itself when all entries are equal (the usual case), else a tuple."""
+        v = seq[0]
+        return v if seq.count(v) == len(seq) else tuple(seq)
 
     # ---- time -------------------------------------------------------------------------------
     def stage_time_terms(self, ops, mbs, tp, algo, dp, in_cross_node, out_cross_node):
@@ -73,7 +98,8 @@ class CostModel:
         arguments: the search prices the same stage slice many times."""
         if len(ops) == 0:
             return 0, 0, 0, 0, 0
-        key = (tuple(ops), tuple(mbs), tuple(tp), tuple(algo), tuple(dp), in_cross_node, out_cross_node)
+        ck = self._ck
+        key = (self._nid(ops), ck(mbs), ck(tp), ck(algo), ck(dp), in_cross_node, out_cross_node)
         hit = self._terms_cache.get(key)
         if hit is None:
             if len(self._terms_cache) > 50000:
@@ -86,10 +112,10 @@ class CostModel:
         mi, db = self._mi, self.db
         fwd = bwd = 0
         tp_comm = 0
-        log2 = math.log
+        lg = self._lg
         for i in range(len(ops)):
             op = ops[i]
-            a, b, c = mi[mbs[i]], int(log2(tp[i], 2)), algo[i]
+            a, b, c = mi[mbs[i]], lg[tp[i]], algo[i]
             fwd += self._fwd[op][a][b][c]
             bwd += self._bwd[op][a][b][c]
             if self._overlap:
@@ -99,8 +125,8 @@ class CostModel:
                 for suffix in ("qkv", "dense", "GEMM", "conv", "downsample"):
                     if suffix in op:
                         tp_comm += db.collective_time("all_reduce", tp[i], self._out[op][a][b][c]) * 1000
-        in_size = self._in[ops[0]][mi[mbs[0]]][int(log2(tp[0], 2))][algo[0]]
-        out_size = self._out[ops[-1]][mi[mbs[-1]]][int(log2(tp[0], 2))][algo[-1]]
+        in_size = self._in[ops[0]][mi[mbs[0]]][lg[tp[0]]][algo[0]]
+        out_size = self._out[ops[-1]][mi[mbs[-1]]][lg[tp[0]]][algo[-1]]
         in_comm = in_size / (db.inter_bandwidth(in_size) if in_cross_node else db.intra_bandwidth(in_size))
         out_comm = out_size / (db.inter_bandwidth(out_size) if out_cross_node else db.intra_bandwidth(out_size))
         fwd_rs = bwd_rs = 0
@@ -113,7 +139,7 @@ class CostModel:
                 f, b, n = reshard_primitives(src, dst)
                 if f is None and b is None:
                     continue
-                size = self._in[ops[i]][mi[mbs[i]]][int(log2(tp[i], 2))][algo[i]]
+                size = self._in[ops[i]][mi[mbs[i]]][lg[tp[i]]][algo[i]]
                 if f is not None:
                     fwd_rs += db.collective_time(f, n, size)
                 if b is not None:
@@ -127,12 +153,25 @@ class CostModel:
         if len(ops) == 0 or sum(recompute) == 0:
             return 0
         total = 0
+        fwd, mi, lg = self._fwd, self._mi, self._lg
         for i in range(len(ops)):
             if recompute[i] == 1:
-                total += self._fwd[ops[i]][self._mi[mbs[i]]][int(math.log(tp[i], 2))][algo[i]]
+                total += fwd[ops[i]][mi[mbs[i]]][lg[tp[i]]][algo[i]]
         return total
 
     def stage_time(self, ops, recompute, tp, dp, micro_bs, algo) -> float:
+        if len(ops) == 0:
+            return self._stage_time(ops, recompute, tp, dp, micro_bs, algo)
+        ck = self._ck
+        key = (self._nid(ops), bytes(recompute), ck(tp), ck(dp), micro_bs, ck(algo))
+        hit = self._stage_time_cache.get(key)
+        if hit is None:
+            if len(self._stage_time_cache) > 100000:
+                self._stage_time_cache.clear()
+            hit = self._stage_time_cache[key] = self._stage_time(ops, recompute, tp, dp, micro_bs, algo)
+        return hit
+
+    def _stage_time(self, ops, recompute, tp, dp, micro_bs, algo) -> float:
         mbs = [micro_bs // dp[j] for j in range(len(ops))]
         fwd, bwd, cin, cout, _ = self.stage_time_terms(ops, mbs, tp, algo, dp, False, False)
         rc = self.recompute_time(ops, recompute, mbs, tp, algo)
@@ -155,31 +194,44 @@ class CostModel:
     def _act_arrays(self, ops, mbs, tp, algo):
         """Per op of a stage: its activation size, its accounting kind (see _kind) and whether the NEXT op starts a
         layer (recompute segments end there).  The three passes below walk these lists instead of the tables."""
-        kind_of, starts = self._kind, self._starts_layer
-        shared = self.opt.consider_shared_space
+        names = tuple(ops)
+        ck = self._ck
+        key = (self._nid(names), ck(mbs), ck(tp), ck(algo))
+        hit = self._arrays_cache.get(key)
+        if hit is not None:
+            return hit
+        by_name = self._names_cache.get(names)
+        if by_name is None:
+            kind_of, starts = self._kind, self._starts_layer
+            for op in set(names):
+                if op not in kind_of:
+                    kind_of[op] = 1 if op == "enc-attention-dropout" else (2 if _shares_buffer(op) else 0)
+                    starts[op] = op in ("enc-1st-layernorm",) or "-conv1" in op
+            kinds = [kind_of[op] for op in names] if self.opt.consider_shared_space else [0] * len(names)
+            ends = [starts[op] for op in names[1:]]
+            if len(self._names_cache) > 20000:
+                self._names_cache.clear()
+            by_name = self._names_cache[names] = (kinds, ends)
+        kinds, ends = by_name
         a, mi, lg = self._a, self._mi, self._lg
-        acts, kinds, ends = [], [], []
-        n = len(ops)
-        for i in range(n):
-            op = ops[i]
-            acts.append(a[op][mi[mbs[i]]][lg[tp[i]]][algo[i]])
-            k = kind_of.get(op)
-            if k is None:
-                k = kind_of[op] = 1 if op == "enc-attention-dropout" else (2 if _shares_buffer(op) else 0)
-            kinds.append(k if shared else 0)
-            if i + 1 < n:
-                nxt = ops[i + 1]
-                e = starts.get(nxt)
-                if e is None:
-                    e = starts[nxt] = nxt in ("enc-1st-layernorm",) or "-conv1" in nxt
-                ends.append(e)
-        return acts, kinds, ends
+        n = len(names)
+        if tp.count(tp[0]) == n and mbs.count(mbs[0]) == n and algo.count(algo[0]) == n:
+            i1, i2, i3 = mi[mbs[0]], lg[tp[0]], algo[0]
+            acts = [a[op][i1][i2][i3] for op in names]
+        else:
+            acts = [a[op][mi[m]][lg[t]][g] for op, m, t, g in zip(names, mbs, tp, algo)]
+        if len(self._arrays_cache) > 20000:
+            self._arrays_cache.clear()
+        out = self._arrays_cache[key] = (acts, kinds, ends)
+        return out
 
     @staticmethod
     def _saved_fast(recompute, acts, kinds, ends):
         n = len(acts)
         if n <= 1 or sum(recompute) == 0:
             return 0
+        if _native is not None:
+            return _native.saved_by_recompute(recompute, acts, kinds, ends)
         saved = 0
         for i in range(n - 1):
             if recompute[i] == 1 and recompute[i + 1] == 1:
@@ -195,6 +247,8 @@ class CostModel:
         n = len(acts)
         if n <= 1 or sum(recompute) == 0:
             return 0
+        if _native is not None:
+            return _native.peak_recompute(recompute, acts, kinds, ends)
         run = 0
         best = 0
         last = n - 1
@@ -236,7 +290,7 @@ class CostModel:
     def _reserved(self, ops, mbs, tp, dp, algo, weight_mb):
         rf = rb = 0
         for i in range(len(ops) - 1):
-            a, b, c = self._mi[mbs[i]], int(math.log(tp[i], 2)), algo[i]
+            a, b, c = self._mi[mbs[i]], self._lg[tp[i]], algo[i]
             v = self._rf[ops[i]][a][b][c]
             if v > rf:
                 rf = v
@@ -249,7 +303,7 @@ class CostModel:
                 src = op_spec(ops[i - 1], tp[i - 1], dp[i - 1], algo[i - 1], as_input=False)
                 dst = op_spec(ops[i], tp[i], dp[i], algo[i], as_input=True)
                 f, b, n = reshard_primitives(src, dst)
-                size = self._in[ops[i]][self._mi[mbs[i]]][int(math.log(tp[i], 2))][algo[i]]
+                size = self._in[ops[i]][self._mi[mbs[i]]][self._lg[tp[i]]][algo[i]]
                 for prim in (f, b):
                     if prim is not None:
                         m = size * n if prim in ("all_gather", "all_to_all") else size
@@ -262,7 +316,8 @@ class CostModel:
         raise RuntimeError(f"unknown memory_pred_type {self.opt.memory_pred_type}")
 
     def stage_memory(self, ops, recompute, tp, dp, micro_bs, stages_behind, algo, breakdown=False):
-        key = (tuple(ops), tuple(recompute), tuple(tp), tuple(dp), micro_bs, stages_behind, tuple(algo), breakdown)
+        ck = self._ck
+        key = (self._nid(ops), bytes(recompute), ck(tp), ck(dp), micro_bs, stages_behind, ck(algo), breakdown)
         hit = self._exact_mem_cache.get(key)
         if hit is None:
             if len(self._exact_mem_cache) > 50000:
@@ -311,7 +366,8 @@ class CostModel:
             return [1] * n
         # the search asks the same question again and again (the same candidate move from many trials): the answer
         # depends on nothing but these arguments
-        key = (tuple(ops), micro_bs, tuple(tp), tuple(dp), stages_behind, tuple(algo))
+        ck = self._ck
+        key = (self._nid(ops), micro_bs, ck(tp), ck(dp), stages_behind, ck(algo))
         hit = self._rc_cache.get(key)
         if hit is not None:
             return list(hit)
@@ -330,6 +386,13 @@ class CostModel:
             return rc
         mbs = [micro_bs // dp[i] for i in range(len(dp))]
         acts, kinds, ends = self._act_arrays(ops, mbs, tp, algo)
+        never = self.opt.never_recompute
+        if _native is not None:
+            ids: Dict[str, int] = {}
+            group_of = [ids.setdefault(op, len(ids)) for op in ops]
+            eligible = [int(name not in ("enc-1st-layernorm",) and "-conv1" not in name and "-relu" not in name
+                            and name not in never) for name in ids]
+            return _native.choose_recompute(acts, kinds, ends, group_of, eligible, mem, limit, stages_behind)
         groups: Dict[str, dict] = {}
         for i in range(n):
             g = groups.setdefault(ops[i], {"index": [], "size": [], "done": False, "sum": 0})
@@ -339,7 +402,6 @@ class CostModel:
             g["sum"] += sz
         saved0 = 0
         peak0 = self._peak_fast(rc, acts, kinds, ends)
-        never = self.opt.never_recompute
         while mem - limit > 0:
             # pick the not-yet-recomputed op kind with the largest total activation
             best, best_sz = None, 0
