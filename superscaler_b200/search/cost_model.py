@@ -68,6 +68,7 @@ class CostModel:
         # per-name facts and the tp -> table index map, computed once (the search calls these millions of times)
         self._lg = {1 << k: int(math.log(1 << k, 2)) for k in range(16)}
         self._name_ids: Dict[tuple, int] = {}
+        self._groups_cache: Dict[int, tuple] = {}
         self._stage_time_cache: Dict[tuple, float] = {}
         self._rc_cache: Dict[tuple, tuple] = {}
         self._arrays_cache: Dict[tuple, tuple] = {}
@@ -388,11 +389,15 @@ class CostModel:
         acts, kinds, ends = self._act_arrays(ops, mbs, tp, algo)
         never = self.opt.never_recompute
         if _native is not None:
-            ids: Dict[str, int] = {}
-            group_of = [ids.setdefault(op, len(ids)) for op in ops]
-            eligible = [int(name not in ("enc-1st-layernorm",) and "-conv1" not in name and "-relu" not in name
-                            and name not in never) for name in ids]
-            return _native.choose_recompute(acts, kinds, ends, group_of, eligible, mem, limit, stages_behind)
+            nid = self._nid(ops)
+            grouping = self._groups_cache.get(nid)
+            if grouping is None:
+                ids: Dict[str, int] = {}
+                group_of = [ids.setdefault(op, len(ids)) for op in ops]
+                eligible = [int(name not in ("enc-1st-layernorm",) and "-conv1" not in name and "-relu" not in name
+                                and name not in never) for name in ids]
+                grouping = self._groups_cache[nid] = (group_of, eligible)
+            return _native.choose_recompute(acts, kinds, ends, grouping[0], grouping[1], mem, limit, stages_behind)
         groups: Dict[str, dict] = {}
         for i in range(n):
             g = groups.setdefault(ops[i], {"index": [], "size": [], "done": False, "sum": 0})

@@ -41,6 +41,7 @@ def test_choose_recompute_equals_python():
         def __init__(self, acts, kinds, ends, mem):
             self.opt = cm.CostOptions(memory_limit=1000.0, never_recompute=("never-op",))
             self._arr, self._mem = (acts, kinds, ends), mem
+            self._name_ids, self._groups_cache = {}, {}
 
         def _act_arrays(self, ops, mbs, tp, algo):
             return self._arr
