@@ -82,3 +82,24 @@ def test_b200_shapes_in_plan_json():
     assert (b200["num_attention_heads"], b200["kv_channels"], b200["ffn_hidden_size"], b200["vocab_size"]) == \
         (16, 128, 8192, 51200)
     assert b200["num_ops_in_each_stage"] == ref["num_ops_in_each_stage"] == [len(names)]
+
+
+def test_search_on_the_b200_database_writes_a_trainable_plan(tmp_path):
+    """The committed B200 database drives a search; the plan passes the trainer's shape checks and its micro-batch
+    divides the global batch (candidates that do not are dropped with a message)."""
+    from superscaler_b200.runtime.trainer import _validate_plan
+    db = os.path.join(os.path.dirname(os.path.dirname(__file__)), "profiled-time-b200") + os.sep
+    out = str(tmp_path) + "/"
+    for sub in ("csv", "top_configs", "trends"):
+        os.makedirs(out + sub, exist_ok=True)
+    args = SearchArgs(model_name="gpt", model_size="1_3B", global_batch_size=512, micro_batch_size=[8, 16, 24, 32],
+                      num_nodes=1, num_gpus_per_node=2, memory_limit=170000, profiled_time_path=db,
+                      config_save_path=out, log_path=out, config_suffix="t", max_num_hops=7, time_budget_total=60,
+                      multi_process=False, explored_budget=200, shapes="b200").finalize()
+    assert args.micro_batch_size == [8, 16, 32]
+    Searcher(SearchContext(args, verbose=False)).run(1)
+    with open(f"{out}gpt_1_3B_1stages_t.json") as f:
+        plan = json.load(f)
+    _validate_plan(plan)
+    assert plan["global_batch_size"] % plan["micro_batch_size"] == 0 and plan["kv_channels"] == 128
+    assert sum(plan["num_gpus"]) == 2
