@@ -3,6 +3,8 @@ check.  Inputs exceed the L2 cache so that memory counters stay meaningful, but 
 
     python -m superscaler_b200.profiler.kernel_case gemm 16384 8192 2048 [--a-mn] [--b-mn] [--single]
     python -m superscaler_b200.profiler.kernel_case attention 2 16 2048 128 [--dropout 0.1]
+    python -m superscaler_b200.profiler.kernel_case layernorm 32768 2048
+    python -m superscaler_b200.profiler.kernel_case embedding 32768 2048 51200 [--dropout 0.1]
 
 Prints one line per kernel family: milliseconds per call (CUDA events, after warm-up) and TFLOP/s.
 """
@@ -70,6 +72,52 @@ def run_attention(a) -> None:
               f"{flops * mult / ms / 1e9:.0f} TFLOP/s status {int(ext.status().item())}")
 
 
+def run_layernorm(a) -> None:
+    """LayerNorm forward and backward (dx, and the gamma / beta gradients accumulated into fp32 buffers)."""
+    ext = native.ext()
+    torch.manual_seed(0)
+    x = torch.randn(a.rows, a.H, device="cuda").bfloat16()
+    dy = torch.randn_like(x)
+    gamma, beta = torch.ones(a.H, device="cuda"), torch.zeros(a.H, device="cuda")
+    dg, db = torch.zeros_like(gamma), torch.zeros_like(beta)
+    y, mean, rstd = ext.layernorm_fwd(x, None, gamma, beta, 1e-5)
+    nbytes = x.numel() * 2
+    for name, fn, moved in (("fwd", lambda: ext.layernorm_fwd(x, None, gamma, beta, 1e-5), 2 * nbytes),
+                            ("bwd", lambda: ext.layernorm_bwd(dy, x, gamma, mean, rstd, None, dg, db, True),
+                             3 * nbytes)):
+        ms = _time(fn, a.warmup, a.iters)
+        print(f"layernorm {name} {a.rows}x{a.H}: {ms:.4f} ms {moved / ms / 1e6:.0f} GB/s (algorithmic bytes) "
+              f"status {int(ext.status().item())}")
+
+
+def run_embedding(a) -> None:
+    """Embedding forward (word + position + dropout) and the two forms of its backward scatter."""
+    ext = native.ext()
+    torch.manual_seed(0)
+    T, H, V = a.tokens, a.H, a.V
+    seq = min(2048, T)
+    ids = torch.randint(0, V, (T,), device="cuda")
+    pos = torch.arange(T, device="cuda") % seq
+    W = torch.randn(V, H, device="cuda").bfloat16()
+    P = torch.randn(seq, H, device="cuda").bfloat16()
+    g = torch.randn(T, H, device="cuda").bfloat16()
+    dW, dP = torch.zeros(V, H, device="cuda"), torch.zeros(seq, H, device="cuda")
+
+    def sorted_bwd():
+        for keys_t, dst in ((ids, dW), (pos, dP)):
+            keys, order = torch.sort(keys_t, stable=True)
+            ext.embedding_bwd_sorted(keys, order, g, dst, 0, a.dropout, 5)
+
+    cases = (("fwd", lambda: ext.embedding_fwd(ids, pos, W, P, 0, a.dropout, 5), 3 * T * H * 2),
+             ("bwd sorted runs", sorted_bwd, T * H * 2 + 2 * T * H * 4),
+             ("bwd float atomics", lambda: ext.embedding_bwd(ids, pos, g, dW, dP, 0, a.dropout, 5),
+              T * H * 2 + 2 * T * H * 4))
+    for name, fn, moved in cases:
+        ms = _time(fn, a.warmup, a.iters)
+        print(f"embedding {name} tokens {T} H {H} V {V} dropout={a.dropout}: {ms:.4f} ms "
+              f"{moved / ms / 1e6:.0f} GB/s (algorithmic bytes) status {int(ext.status().item())}")
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="kind", required=True)
@@ -81,10 +129,15 @@ def main(argv=None) -> None:
     t = sub.add_parser("attention")
     t.add_argument("B", type=int), t.add_argument("NH", type=int), t.add_argument("S", type=int)
     t.add_argument("HD", type=int), t.add_argument("--dropout", type=float, default=0.0)
-    for p in (g, t):
+    ln = sub.add_parser("layernorm")
+    ln.add_argument("rows", type=int), ln.add_argument("H", type=int)
+    e = sub.add_parser("embedding")
+    e.add_argument("tokens", type=int), e.add_argument("H", type=int), e.add_argument("V", type=int)
+    e.add_argument("--dropout", type=float, default=0.0)
+    for p in (g, t, ln, e):
         p.add_argument("--warmup", type=int, default=3), p.add_argument("--iters", type=int, default=3)
     a = ap.parse_args(argv)
-    (run_gemm if a.kind == "gemm" else run_attention)(a)
+    {"gemm": run_gemm, "attention": run_attention, "layernorm": run_layernorm, "embedding": run_embedding}[a.kind](a)
 
 
 if __name__ == "__main__":
