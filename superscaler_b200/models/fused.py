@@ -68,6 +68,7 @@ class FusedAttention(FusedGroup):
         score = members[0]
         self.core = AttentionCoreOp(score.info, score.env, mode=score.mode)
         self.core.sq, self.core.sk = score.sq, score.sk
+        self.core._names = score._names        # the relative-position table, when the model has one
         self.reads = self.core.reads
         self.writes = ("x",)
 

@@ -46,6 +46,11 @@ class T5Config:
     activation: int = F.ACT_GELU
     make_vocab_divisible_by: int = 128
     max_tp: int = 8
+    # T5 relative-position buckets in the self-attentions (reference path only until the attention kernels take the
+    # distance table); off = learned absolute positions alone, as in the reference's T5
+    relative_position_bias: bool = False
+    relative_attention_num_buckets: int = 32
+    relative_attention_max_distance: int = 128
 
     @property
     def padded_vocab(self) -> int:

@@ -151,7 +151,37 @@ class _AttnDims:
         return nh, c.head_dim
 
 
-class AttentionCoreOp(Op, _AttnDims):
+class _RelativeBias:
+    """T5 relative-position bias of a self-attention op: one [heads, buckets] table per stack (encoder looks both
+    ways, decoder backwards only), declared by the score op and shared by all layers of the stack."""
+
+    def uses_relative_bias(self) -> bool:
+        return bool(getattr(self.env.cfg, "relative_position_bias", False)) and self.mode != "cross"
+
+    def declare_relative_bias(self) -> None:
+        if not self.uses_relative_bias():
+            return
+        c = self.env.cfg
+        stack = "dec" if self.mode == "causal" else "enc"
+        self.param_spec("relative_attention_bias.weight", (c.heads // self.pl.tp, c.relative_attention_num_buckets),
+                        "normal", full_shape=(c.heads, c.relative_attention_num_buckets), shard_dim=0, std=c.init_std,
+                        weight_decay=False, fp32=True, seed_key=f"{stack}_relative_attention_bias",
+                        shared_key=f"{stack}_relative_attention_bias")
+
+    def relative_bias(self, sq: int, sk: int) -> torch.Tensor:
+        """[local heads, sq, sk] fp32 (reference path; a kernel takes the distance table instead)."""
+        from .relative_position import bias_from_table, distance_table
+        c = self.env.cfg
+        w = self.p("relative_attention_bias.weight")
+        if w.is_cuda:
+            raise NotImplementedError("relative-position bias on the GPU needs attention kernels that take the "
+                                      "per-head distance table; they are not built yet")
+        table = distance_table(w.float(), sq, sk, self.mode != "causal", c.relative_attention_num_buckets,
+                               c.relative_attention_max_distance)
+        return bias_from_table(table, sq, sk)
+
+
+class AttentionCoreOp(Op, _AttnDims, _RelativeBias):
     """score + softmax + dropout + context as ONE flash-attention kernel (the fused form of the four
     reference ops flex_ops.py:711-1015).  mode: "causal" | "full" | "cross"."""
     reads = ("x",)
@@ -172,7 +202,11 @@ class AttentionCoreOp(Op, _AttnDims):
         x = st["x"]
         b = x.shape[0] // self.sq
         scale = 1.0 / math.sqrt(hd)
-        if self.mode == "cross":
+        if self.uses_relative_bias():
+            st["x"] = F.attention_with_bias(x, b, nh, self.sq, hd, scale, self.mode == "causal",
+                                            st.get("enc_lens") if self.mode == "full" else None,
+                                            self.relative_bias(self.sq, self.sq), p_drop)
+        elif self.mode == "cross":
             kv = st["kv"]
             st["x"] = F.flash_attention(x, kv, kv, b, nh, self.sq, self.sk, hd, cols=(0, 0, w), scale=scale,
                                         causal=False, kv_lens=st.get("enc_lens"), dropout_p=p_drop,
@@ -294,7 +328,7 @@ class LMHeadLossOp(Op):
 # ------------------------------------------------------------------------------------------------
 # Unfused attention pieces (only used when a plan separates them; slow path, one GEMM per head)
 # ------------------------------------------------------------------------------------------------
-class ScoreOp(Op, _AttnDims):
+class ScoreOp(Op, _AttnDims, _RelativeBias):
     """scores[b, h] = Q K^T (unscaled; the softmax op applies the scale); keeps V as "value"."""
     reads = ("x",)
     writes = ("x", "value")
@@ -305,6 +339,9 @@ class ScoreOp(Op, _AttnDims):
         self.sq, self.sk = getattr(env.cfg, sq_attr), getattr(env.cfg, sk_attr)
         if mode == "cross":
             self.reads = ("x", "kv")
+
+    def declare(self):
+        self.declare_relative_bias()
 
     def forward(self, st):
         nh, hd = self.dims(st)
@@ -322,6 +359,9 @@ class ScoreOp(Op, _AttnDims):
                 kk = k[bi * self.sk:(bi + 1) * self.sk, hi * hd:(hi + 1) * hd]
                 scores.append(F.linear(qq, kk))
         st["x"] = torch.stack(scores).view(b, nh, self.sq, self.sk)
+        if self.uses_relative_bias():
+            # the softmax op multiplies by 1 / sqrt(head_dim): the bias is added pre-divided so that it arrives whole
+            st["x"] = st["x"] + (self.relative_bias(self.sq, self.sk) * math.sqrt(hd)).to(st["x"].dtype)
         st["value"] = v
 
 

@@ -536,6 +536,24 @@ def flash_attention(q, k, v, B, NH, SQ, SK, HD, cols=(0, 0, 0), scale=None, caus
                              float(dropout_p), int(seed))
 
 
+def attention_with_bias(qkv, B, NH, S, HD, scale, causal, kv_lens, bias, dropout_p=0.0):
+    """Self-attention on a fused QKV matrix with an additive [NH, S, S] bias on the scores: plain differentiable
+    PyTorch (fp32), the reference for kernels that take the bias as a per-head distance table."""
+    assert dropout_p == 0.0, "dropout > 0 needs the GPU path"
+    w = NH * HD
+    q = qkv[:, :w].float().view(B, S, NH, HD).transpose(1, 2)
+    k = qkv[:, w:2 * w].float().view(B, S, NH, HD).transpose(1, 2)
+    v = qkv[:, 2 * w:3 * w].float().view(B, S, NH, HD).transpose(1, 2)
+    s = torch.matmul(q, k.transpose(-1, -2)) * scale + bias[None].float()
+    if causal:
+        s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool, device=qkv.device).tril(), float("-inf"))
+    if kv_lens is not None:
+        idx = torch.arange(S, device=qkv.device)[None, None, None, :]
+        s = s.masked_fill(idx >= kv_lens.view(B, 1, 1, 1), float("-inf"))
+    o = torch.matmul(torch.softmax(s, dim=-1), v)
+    return o.transpose(1, 2).reshape(B * S, w).to(qkv.dtype)
+
+
 def fused_qkv_attention(qkv, B, NH, S, HD, causal=True, dropout_p=0.0, seed=0, scale=None):
     """Self-attention on a fused QKV matrix [B*S, 3*NH*HD] laid out as [Q heads | K heads | V heads]."""
     h = NH * HD

@@ -18,8 +18,12 @@ from ..parallel.relayout import Layout, Side, Transfer
 DECLARING_OPS = {
     "word_embeddings": ("encoder-embedding", "decoder-embedding", "gpt-post-process", "t5-post-process"),
     "position_embeddings": ("encoder-embedding", "decoder-embedding"),
+    # T5 relative-position tables [heads / tp, buckets]: one per stack, used by every layer of the stack
+    "enc_relative_attention_bias": ("enc-attention-score",),
+    "dec_relative_attention_bias": ("dec-attention-score-1",),
 }
-LAYOUT = {"word_embeddings": Layout("rep", "split"), "position_embeddings": Layout("rep", "rep")}
+LAYOUT = {"word_embeddings": Layout("rep", "split"), "position_embeddings": Layout("rep", "rep"),
+          "enc_relative_attention_bias": Layout("rep", "split"), "dec_relative_attention_bias": Layout("rep", "split")}
 
 
 class TiedWeights:
@@ -28,6 +32,8 @@ class TiedWeights:
         plan, ps = trainer.plan, trainer.pstate
         self.links: List[Tuple[str, Side, Side]] = []   # (shared key, root side, other side)
         for key, op_names in DECLARING_OPS.items():
+            if key.endswith("relative_attention_bias") and not getattr(trainer.cfg, "relative_position_bias", False):
+                continue
             holders: List[Side] = []
             seen = set()   # physical stages that already hold a copy (one copy per stage, shared by its chunks)
             for s, (lo, hi) in enumerate(trainer.stage_bounds):
