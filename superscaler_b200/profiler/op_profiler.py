@@ -54,12 +54,15 @@ def _tensor_mb(t) -> float:
 
 
 _L2_FLUSH = None
+_FLUSH_ENABLED = True     # --no-l2-flush times the calls back to back without evicting their operands
 
 
 def _flush_l2() -> None:
     """Overwrites a buffer twice the size of the L2 cache, so that the next call finds its inputs and weights in
     HBM as it does inside a training step (where thousands of other kernels ran since they were produced)."""
     global _L2_FLUSH
+    if not _FLUSH_ENABLED:
+        return
     if _L2_FLUSH is None:
         _L2_FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     _L2_FLUSH.zero_()
@@ -219,7 +222,12 @@ def main(argv=None) -> None:
     ap.add_argument("--prof-path", required=True)
     ap.add_argument("--prof-repeat-times", type=int, default=10)
     ap.add_argument("--prof-warmup-times", type=int, default=3)
+    ap.add_argument("--no-l2-flush", action="store_true",
+                    help="do not evict the L2 cache before every timed call (operands of small ops then stay "
+                         "cached between the repeats)")
     args = ap.parse_args(argv)
+    global _FLUSH_ENABLED
+    _FLUSH_ENABLED = not args.no_l2_flush
     rank, world, _ = init_distributed()
     tp = args.prof_tp_size or world
     assert tp == world, "launch exactly tp ranks"
