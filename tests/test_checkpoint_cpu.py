@@ -47,3 +47,36 @@ def test_reassemble_under_plan(tmp_path):
     b = _trainer()
     ck.load_under_plan(b, str(tmp_path))
     assert torch.equal(a.store.master, b.store.master)
+
+
+def test_export_to_upstream_megatron_names_and_back(tmp_path):
+    """A checkpoint merged from its shards converts to the upstream GPT parameter names (QKV rows interleaved per
+    head) and back without loss; the converted QKV projects like the original."""
+    import torch
+    from superscaler_b200.runtime import checkpointing
+    from superscaler_b200.runtime.megatron_names import export_megatron_gpt, import_megatron_gpt
+    from superscaler_b200.runtime.trainer import Trainer
+    from helpers import tiny_gpt_plan
+    t = Trainer(tiny_gpt_plan(layers=2), device="cpu")
+    checkpointing.save_checkpoint(t, str(tmp_path))
+    full = checkpointing.merge_tp_shards(str(tmp_path), 0)
+    heads = t.cfg.heads
+    up = export_megatron_gpt(full, t.op_names, heads)
+    assert "language_model.embedding.word_embeddings.weight" in up
+    assert "language_model.encoder.layers.1.self_attention.query_key_value.weight" in up
+    assert "language_model.encoder.layers.0.mlp.dense_4h_to_h.bias" in up
+    assert "language_model.encoder.final_layernorm.weight" in up
+    assert len(up) == 2 + 12 * 2 + 2
+    legacy = export_megatron_gpt(full, t.op_names, heads, legacy=True)
+    assert "language_model.transformer.layers.0.attention.dense.weight" in legacy
+    back = import_megatron_gpt(up, t.op_names, heads)
+    assert all(torch.equal(back[k], full[k]) for k in back) and set(back) == {k for k in full if k in back}
+    # per-head interleaving: head 1's K rows of ours are rows [1 * 3 * hd + hd, ... + 2 * hd) upstream
+    ours = next(v for k, v in full.items() if k.endswith("query_key_value.weight"))
+    theirs = up["language_model.encoder.layers.0.self_attention.query_key_value.weight"]
+    hd = ours.shape[1] // heads
+    assert torch.equal(theirs[1 * 3 * hd + hd: 1 * 3 * hd + 2 * hd], ours[1, hd:2 * hd])
+    x = torch.randn(5, ours.shape[2])
+    q_ours = (x @ ours[0].float().t()).view(5, heads, hd)
+    q_theirs = (x @ theirs.float().t()).view(5, heads, 3, hd)[:, :, 0]
+    assert torch.allclose(q_ours, q_theirs)
