@@ -80,3 +80,34 @@ def test_export_to_upstream_megatron_names_and_back(tmp_path):
     q_ours = (x @ ours[0].float().t()).view(5, heads, hd)
     q_theirs = (x @ theirs.float().t()).view(5, heads, 3, hd)[:, :, 0]
     assert torch.allclose(q_ours, q_theirs)
+
+
+def test_gpt_logits_match_huggingface_gpt2(tmp_path):
+    """An independent implementation as oracle: the exported weights loaded into transformers' GPT2LMHeadModel
+    give the same logits as this framework's op-list GPT (up to the bf16 rounding its CPU path emulates)."""
+    import pytest
+    import torch
+    transformers = pytest.importorskip("transformers")
+    from superscaler_b200.data.synthetic import gpt_batch
+    from superscaler_b200.runtime import checkpointing
+    from superscaler_b200.runtime.hf_export import hf_gpt2_config, to_hf_gpt2
+    from superscaler_b200.runtime.trainer import Trainer
+    from helpers import tiny_gpt_plan
+    plan = tiny_gpt_plan(layers=2, seq=64, hidden=128, heads=2, head_dim=64, vocab=512, global_bs=4, micro_bs=4)
+    t = Trainer(plan, device="cpu", model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0),
+                lr_warmup_steps=0, lr=1e-3)
+    batch = gpt_batch(4, 64, 512, seed=3)
+    for _ in range(2):                       # a trained model: biases and LayerNorm parameters are no longer trivial
+        t.train_step(batch)
+    checkpointing.save_checkpoint(t, str(tmp_path))
+    full = checkpointing.merge_tp_shards(str(tmp_path), t.iteration)
+    hf = transformers.GPT2LMHeadModel(hf_gpt2_config(t.cfg)).eval()
+    missing, unexpected = hf.load_state_dict(to_hf_gpt2(full, t.op_names), strict=False)
+    assert not unexpected and all(k.endswith(("attn.bias", "attn.masked_bias")) for k in missing)
+    with torch.no_grad():
+        want = hf(batch["ids"]).logits.float()
+    got = t.logits(batch["ids"]).float()
+    rel = float((got - want).norm() / want.norm())
+    assert rel < 2e-2, rel
+    agree = float((got.argmax(-1) == want.argmax(-1)).float().mean())
+    assert agree > 0.9, agree
