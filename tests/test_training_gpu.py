@@ -60,6 +60,29 @@ def test_replays_from_one_seed_are_bitwise_equal():
         assert torch.equal(master, runs[0][1])
 
 
+def test_gpu_logits_match_huggingface_gpt2(tmp_path):
+    """The whole GPT through the native kernels against an independent fp32 implementation: the weights of a
+    briefly trained model are exported to transformers' GPT2LMHeadModel (CPU, fp32) and the logits compared."""
+    transformers = pytest.importorskip("transformers")
+    from superscaler_b200.runtime import checkpointing
+    from superscaler_b200.runtime.hf_export import hf_gpt2_config, to_hf_gpt2
+    plan = _plan()
+    losses, t = _run(plan, steps=2, overrides=dict(hidden_dropout=0.0, attention_dropout=0.0))
+    checkpointing.save_checkpoint(t, str(tmp_path))
+    full = checkpointing.merge_tp_shards(str(tmp_path), t.iteration)
+    hf = transformers.GPT2LMHeadModel(hf_gpt2_config(t.cfg)).eval()
+    missing, unexpected = hf.load_state_dict(to_hf_gpt2(full, t.op_names), strict=False)
+    assert not unexpected and all(k.endswith(("attn.bias", "attn.masked_bias")) for k in missing)
+    ids = gpt_batch(plan["micro_batch_size"], plan["seq_length"], 2048, seed=5)["ids"]
+    with torch.no_grad():
+        want = hf(ids).logits.float()
+    got = t.logits(ids).float().cpu()
+    assert native.check_status() == 0
+    rel = float((got - want).norm() / want.norm())
+    assert rel < 3e-2, rel
+    assert float((got.argmax(-1) == want.argmax(-1)).float().mean()) > 0.9
+
+
 def test_t5_and_resnet_train_on_gpu():
     from superscaler_b200.data.synthetic import resnet_batch, t5_batch
     from helpers import tiny_resnet_plan, tiny_t5_plan
