@@ -101,6 +101,19 @@ class HealthMonitor:
                 raise
 
 
+def store_from_env(rank: int, world: int, port_offset: int = 7, timeout_s: float = 60.0):
+    """A TCPStore of its own for the heartbeats, on MASTER_ADDR : MASTER_PORT + port_offset (rank 0 hosts it), so
+    that the monitor does not share a connection with the process group it watches over."""
+    import datetime
+    import os
+
+    import torch.distributed as dist
+    host = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    port = int(os.environ.get("MASTER_PORT", "29500")) + port_offset
+    return dist.TCPStore(host, port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=timeout_s),
+                         wait_for_workers=False)
+
+
 def device_status_message(code: int) -> str:
     return {0: "ok", 1: "a kernel gave up waiting on one of its own barriers (mbarrier time limit)",
             2: "a kernel gave up waiting for a peer GPU (peer time limit): a rank is late or gone"}.get(

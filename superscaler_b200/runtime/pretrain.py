@@ -11,8 +11,10 @@ from __future__ import annotations
 
 import argparse
 import csv
+import contextlib
 import json
 import os
+import sys
 import time
 
 import torch
@@ -64,6 +66,12 @@ def main(argv=None) -> None:
     ap.add_argument("--eval-interval", type=int, default=None, help="evaluate every this many iterations")
     ap.add_argument("--eval-iters", type=int, default=2, help="batches per evaluation")
     ap.add_argument("--tensorboard-dir", default=None, help="scalar logs (written by the last rank)")
+    ap.add_argument("--health-check", action="store_true",
+                    help="publish a heartbeat every iteration and stop with exit code 3 when a peer failed or went "
+                         "silent, instead of waiting in the next collective")
+    ap.add_argument("--health-stale-after-s", type=float, default=600.0)
+    ap.add_argument("--inject-failure", default=None, metavar="RANK:ITERATION",
+                    help="host-side fault injection for tests: that rank raises at the start of that iteration")
     ap.add_argument("--no-fused-comm", action="store_true")
     ap.add_argument("--interleave-factor", type=int, default=1,
                     help="model chunks per pipeline stage (interleaved 1F1B); re-cuts the plan's stages evenly")
@@ -89,6 +97,11 @@ def main(argv=None) -> None:
     if args.load:
         checkpointing.load_checkpoint(trainer, args.load, load_optim=not args.no_load_optim,
                                       load_rng=not args.no_load_rng, finetune=args.finetune)
+    monitor = None
+    if args.health_check and world > 1:
+        from .health import HealthMonitor, store_from_env
+        monitor = HealthMonitor(store_from_env(rank, world), rank, world, stale_after_s=args.health_stale_after_s)
+    fail_rank, fail_iter = (int(x) for x in args.inject_failure.split(":")) if args.inject_failure else (-1, -1)
     writer = None
     if args.tensorboard_dir and rank == world - 1:
         from torch.utils.tensorboard import SummaryWriter
@@ -102,7 +115,7 @@ def main(argv=None) -> None:
     config_name = os.path.splitext(os.path.basename(args.flexpipe_config))[0]
     regions = ["iteration", "forward-backward", "backward-params-all-reduce", "optimizer"]
     pool_start = trainer.iteration
-    for it in range(trainer.iteration, args.train_iters):
+    def one_step(it):
         timers("iteration").start()
         batch = trainer.to_device(pool[(it - pool_start) % len(pool)])
         timers("forward-backward").start()
@@ -120,6 +133,21 @@ def main(argv=None) -> None:
         trainer.iteration += 1
         timers("optimizer").stop()
         timers("iteration").stop()
+        return loss, lr
+
+    for it in range(trainer.iteration, args.train_iters):
+        if monitor is not None:
+            from .health import PeerFailure
+            try:
+                monitor.beat(it)            # a failed or silent peer ends the run HERE, before the next collective
+            except PeerFailure as e:
+                print(f"rank {rank}: stopping before iteration {it + 1}: {e}", flush=True)
+                sys.stdout.flush()
+                os._exit(3)                 # no collective clean-up: the peer it would wait for is gone
+        with (monitor.guard() if monitor is not None else contextlib.nullcontext()):
+            if rank == fail_rank and it == fail_iter:
+                raise RuntimeError(f"injected failure at iteration {it}")
+            loss, lr = one_step(it)
         if (it + 1) % args.log_interval == 0:
             row = timers.row(regions)
             lv = trainer.loss_value({"loss_tensor": loss})

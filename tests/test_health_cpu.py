@@ -93,3 +93,38 @@ def test_corrupted_checkpoint_shard_is_reported(tmp_path):
         f.truncate(os.path.getsize(path) // 2)
     with pytest.raises(checkpointing.CheckpointError, match="model_optim_rng.pt"):
         checkpointing.load_checkpoint(t, str(tmp_path))
+
+
+def _cli_rank(rank, world, port, plan_path, inject):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    import torch
+    torch.set_num_threads(1)
+    from superscaler_b200.runtime import pretrain
+    pretrain.main(["--flexpipe-config", plan_path, "--train-iters", "6", "--lr-decay-iters", "10", "--hidden-dropout",
+                   "0", "--attention-dropout", "0", "--distributed-backend", "gloo", "--health-check",
+                   "--inject-failure", inject])
+
+
+def test_training_cli_stops_instead_of_hanging_when_a_rank_fails(tmp_path):
+    """Host-side fault injection through the training entry point: rank 1 raises at iteration 2 of a dp-2 run.
+    Neither process may hang: the failing rank exits with its exception, the survivor leaves either at its next
+    heartbeat check (exit code 3) or with the error of the collective that lost its peer."""
+    import json
+    import torch.multiprocessing as mp
+    from dist_utils import _free_port
+    plan_path = tmp_path / "gpt_tiny_dp2.json"
+    plan_path.write_text(json.dumps(tiny_gpt_plan(num_gpus=(2,), tp=[1])))
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_cli_rank, args=(r, 2, port, str(plan_path), "1:2")) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.terminate()
+    assert not alive, "a rank hung after its peer failed"
+    assert procs[1].exitcode not in (0, None)
+    assert procs[0].exitcode not in (0, None)
