@@ -107,14 +107,17 @@ class QKVOp(Op):
             if self.kind == "self":
                 self.param_spec("query_key_value.weight", (3, proj // tp, h), "normal", full_shape=(3, proj, h),
                                 shard_dim=1, std=c.init_std)
-                self.param_spec("query_key_value.bias", (3, proj // tp), "zeros", weight_decay=False)
+                self.param_spec("query_key_value.bias", (3, proj // tp), "zeros", weight_decay=False,
+                                full_shape=(3, proj), shard_dim=1)
             else:
                 self.param_spec("query.weight", (proj // tp, h), "normal", full_shape=(proj, h), shard_dim=0,
                                 std=c.init_std)
-                self.param_spec("query.bias", (proj // tp,), "zeros", weight_decay=False)
+                self.param_spec("query.bias", (proj // tp,), "zeros", weight_decay=False, full_shape=(proj,),
+                                shard_dim=0)
                 self.param_spec("key_value.weight", (2, proj // tp, h), "normal", full_shape=(2, proj, h),
                                 shard_dim=1, std=c.init_std)
-                self.param_spec("key_value.bias", (2, proj // tp), "zeros", weight_decay=False)
+                self.param_spec("key_value.bias", (2, proj // tp), "zeros", weight_decay=False,
+                                full_shape=(2, proj), shard_dim=1)
         else:
             assert self.kind == "self", "algo 1 exists for self-attention QKV only"
             self.param_spec("query_key_value.weight", (3 * proj, h // tp), "normal", full_shape=(3 * proj, h),

@@ -61,6 +61,10 @@ def main(argv=None) -> None:
     ap.add_argument("--exit-duration-in-mins", type=float, default=None,
                     help="save a checkpoint and stop once the run has lasted this long")
     ap.add_argument("--finetune", action="store_true", help="load the weights only and restart at iteration 0")
+    ap.add_argument("--load-resharded", action="store_true",
+                    help="the checkpoint under --load was written under ANOTHER plan (other GPU count, tensor-parallel "
+                         "degrees or stage split): merge its shards and re-slice the weights for this plan; optimizer "
+                         "state is not carried over")
     ap.add_argument("--no-load-optim", action="store_true")
     ap.add_argument("--no-load-rng", action="store_true")
     ap.add_argument("--eval-interval", type=int, default=None, help="evaluate every this many iterations")
@@ -94,7 +98,10 @@ def main(argv=None) -> None:
                       weight_decay=args.weight_decay, clip_grad=args.clip_grad, lr_decay_steps=args.lr_decay_iters,
                       lr_warmup_steps=int(args.lr_warmup_fraction * args.lr_decay_iters), lr_style=args.lr_decay_style,
                       optimizer=args.optimizer, fused_comm=not args.no_fused_comm)
-    if args.load:
+    if args.load and args.load_resharded:
+        trainer.iteration = 0 if args.finetune else checkpointing.load_under_plan(trainer, args.load)
+        trainer.lr_schedule.step(trainer.iteration)      # the schedule continues where the old run stopped
+    elif args.load:
         checkpointing.load_checkpoint(trainer, args.load, load_optim=not args.no_load_optim,
                                       load_rng=not args.no_load_rng, finetune=args.finetune)
     monitor = None
