@@ -1,6 +1,7 @@
 """Checkpoint layout and resume (CPU)."""
 import os
 
+import pytest
 import torch
 
 from superscaler_b200.data.synthetic import gpt_batch
@@ -111,3 +112,40 @@ def test_gpt_logits_match_huggingface_gpt2(tmp_path):
     assert rel < 2e-2, rel
     agree = float((got.argmax(-1) == want.argmax(-1)).float().mean())
     assert agree > 0.9, agree
+
+
+def _save_worker(rank, world, plan, root):
+    from superscaler_b200.data.synthetic import gpt_batch
+    from superscaler_b200.runtime.trainer import Trainer
+    t = Trainer(plan, rank=rank, world_size=world, device="cpu", lr_warmup_steps=0, lr=1e-3,
+                model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2))
+    for i in range(2):
+        t.train_step(gpt_batch(4, 128, 512, seed=i))
+    ck.save_checkpoint(t, root)
+
+
+@pytest.mark.parametrize("name,kw,world", [("pp2", dict(num_gpus=(1, 1)), 2), ("tp2", dict(num_gpus=(2,), tp=[2]), 2),
+                                           ("pp2_tp2", dict(num_gpus=(2, 2), tp=[2, 2]), 4)])
+def test_checkpoints_of_parallel_plans_reload_on_one_rank(tmp_path, name, kw, world):
+    """Shards written by pipeline / tensor parallel runs merge into the weights the single-process run has after
+    the same two steps (the tied embedding copy of the last stage included)."""
+    from dist_utils import run_ranks
+    from superscaler_b200.data.synthetic import gpt_batch
+    from superscaler_b200.runtime.trainer import Trainer
+    from helpers import tiny_gpt_plan
+    root = str(tmp_path / name)
+    run_ranks(_save_worker, world, tiny_gpt_plan(**kw), root)
+    ov = dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2)
+    ref = Trainer(tiny_gpt_plan(), device="cpu", lr_warmup_steps=0, lr=1e-3, model_overrides=ov)
+    for i in range(2):
+        ref.train_step(gpt_batch(4, 128, 512, seed=i))
+    got = Trainer(tiny_gpt_plan(), device="cpu", lr_warmup_steps=0, lr=1e-3, model_overrides=ov, seed=77)
+    assert ck.load_under_plan(got, root) == 2
+    for n in ref.store.params:
+        a, b = ref.store.state_dict()[n], got.store.state_dict()[n]
+        # two Adam steps of 1e-3 move every weight by up to 2e-3 whatever the size of its gradient, so runs whose
+        # tiny gradients differ in rounding may end 4e-3 apart; a wrongly placed shard would differ by ~0.03
+        assert torch.allclose(a, b, atol=5e-3), (n, float((a - b).abs().max()))
+    batch = gpt_batch(4, 128, 512, seed=9)
+    la, lb = ref.loss_value(ref.train_step(batch)), got.loss_value(got.train_step(batch))
+    assert abs(la - lb) < 2e-2
