@@ -149,3 +149,43 @@ def test_checkpoints_of_parallel_plans_reload_on_one_rank(tmp_path, name, kw, wo
     batch = gpt_batch(4, 128, 512, seed=9)
     la, lb = ref.loss_value(ref.train_step(batch)), got.loss_value(got.train_step(batch))
     assert abs(la - lb) < 2e-2
+
+
+def _model_bits(model):
+    from superscaler_b200.data import synthetic as syn
+    from helpers import tiny_resnet_plan, tiny_t5_plan
+    if model == "gpt":
+        return tiny_gpt_plan, dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2), \
+            (lambda seed: syn.gpt_batch(4, 128, 512, seed=seed))
+    if model == "t5":
+        return tiny_t5_plan, dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2), \
+            (lambda seed: syn.t5_batch(4, 64, 32, 256, seed=seed))
+    return tiny_resnet_plan, dict(image_size=32, num_classes=16), \
+        (lambda seed: syn.resnet_batch(4, 32, 16, seed=seed, dtype=torch.float32))
+
+
+def _load_worker(rank, world, model, kw, root, want):
+    plan_fn, ov, batch_fn = _model_bits(model)
+    t = Trainer(plan_fn(**kw), rank=rank, world_size=world, device="cpu", lr_warmup_steps=0, lr=1e-3,
+                model_overrides=ov, seed=55)
+    assert ck.load_under_plan(t, root) == 2
+    got = t.loss_value(t.train_step(batch_fn(9)))
+    assert abs(got - want) < 2e-2 * max(1.0, abs(want)), (rank, got, want)
+
+
+@pytest.mark.parametrize("model,kw,world", [("gpt", dict(num_gpus=(2,), tp=[2]), 2), ("gpt", dict(num_gpus=(1, 1)), 2),
+                                            ("t5", dict(num_gpus=(2,), tp=[2]), 2), ("t5", dict(num_gpus=(1, 1)), 2),
+                                            ("resnet", dict(num_gpus=(2,), tp=[2]), 2),
+                                            ("resnet", dict(num_gpus=(1, 1)), 2)])
+def test_one_rank_checkpoint_loads_under_parallel_plans(tmp_path, model, kw, world):
+    """The other direction: a checkpoint written by one rank is re-sliced for tensor / pipeline parallel plans of
+    all three models; the next step's loss equals the single-process continuation."""
+    from dist_utils import run_ranks
+    plan_fn, ov, batch_fn = _model_bits(model)
+    root = str(tmp_path / "ckpt")
+    ref = Trainer(plan_fn(), device="cpu", lr_warmup_steps=0, lr=1e-3, model_overrides=ov)
+    for i in range(2):
+        ref.train_step(batch_fn(i))
+    ck.save_checkpoint(ref, root)
+    want = ref.loss_value(ref.train_step(batch_fn(9)))
+    run_ranks(_load_worker, world, model, kw, root, want)
