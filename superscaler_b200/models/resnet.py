@@ -251,6 +251,10 @@ def build_resnet_op(info: OpInfo, env: Env) -> Op:
     c: ResNetConfig = env.cfg
     n = info.name
     if n == "conv1":
+        # the stem reads 3 input channels, which cannot be split over a tensor-parallel group: it always splits its
+        # output channels, whatever the plan says (the reference's ParallelConvOp, flex_ops.py:1461-1494, would
+        # divide 3 by the group size)
+        info.algo = 0
         return ConvOp(info, env, 3, c.in_channels, 7, 2, 3)
     if n == "bn1":
         return BNOp(info, env, c.in_channels)

@@ -91,3 +91,29 @@ def test_t5_and_resnet_parallel_plans_match_single_process(model, plan_kw, world
     plan_fn = tiny_t5_plan if model == "t5" else (lambda **kw: tiny_resnet_plan(global_bs=16, micro_bs=8, **kw))
     base = _other_model_losses(model, plan_fn())
     run_ranks(_other_model_worker, world, model, plan_fn(**plan_kw), base)
+
+
+def test_gpt_alternative_partitioning_matches_single_process():
+    """algo 1 of every tensor-parallel op (row-parallel QKV and MLP up-projection, column-parallel output
+    projections) on two ranks, alone and mixed with algo 0 from layer to layer."""
+    plan = tiny_gpt_plan(**KW, num_gpus=(2,), tp=[2])
+    n = plan["num_ops_in_each_stage"][0]
+    plan["algo_of_each_op"] = [[1] * n]
+    plan["resharding_stages"] = [True]
+    run_ranks(_worker, 2, plan, _base())
+    mixed = tiny_gpt_plan(**KW, num_gpus=(2,), tp=[2])
+    mixed["algo_of_each_op"] = [[(i // 13) % 2 for i in range(n)]]
+    mixed["resharding_stages"] = [True]
+    run_ranks(_worker, 2, mixed, _base())
+
+
+def test_resnet_input_channel_partitioning_matches_single_process():
+    """algo 1 of the convolutions (input channels split, partial outputs summed) on two ranks."""
+    from helpers import tiny_resnet_plan
+    plan_fn = lambda **kw: tiny_resnet_plan(global_bs=16, micro_bs=8, **kw)
+    base = _other_model_losses("resnet", plan_fn())
+    plan = plan_fn(num_gpus=(2,), tp=[2])
+    n = plan["num_ops_in_each_stage"][0]
+    plan["algo_of_each_op"] = [[1] * n]
+    plan["resharding_stages"] = [True]
+    run_ranks(_other_model_worker, 2, "resnet", plan, base)
