@@ -117,3 +117,10 @@ def test_resnet_input_channel_partitioning_matches_single_process():
     plan["algo_of_each_op"] = [[1] * n]
     plan["resharding_stages"] = [True]
     run_ranks(_other_model_worker, 2, "resnet", plan, base)
+
+
+@pytest.mark.parametrize("plan_kw,world", [(dict(num_gpus=(2,), tp=[2]), 2), (dict(num_gpus=(1, 1)), 2),
+                                           (dict(num_gpus=(2,), tp=[1]), 2)])
+def test_recompute_under_parallel_plans_matches_single_process(plan_kw, world):
+    """Per-op recompute (every layer checkpointed) combined with tensor, pipeline and data parallelism."""
+    run_ranks(_worker, world, tiny_gpt_plan(**KW, recompute=1, **plan_kw), _base())
