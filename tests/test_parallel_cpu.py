@@ -124,3 +124,50 @@ def test_resnet_input_channel_partitioning_matches_single_process():
 def test_recompute_under_parallel_plans_matches_single_process(plan_kw, world):
     """Per-op recompute (every layer checkpointed) combined with tensor, pipeline and data parallelism."""
     run_ranks(_worker, world, tiny_gpt_plan(**KW, recompute=1, **plan_kw), _base())
+
+
+def _searched_resnet_worker(rank, world, plan):
+    from superscaler_b200.data import synthetic as syn
+    t = Trainer(plan, rank=rank, world_size=world, lr_warmup_steps=0, device="cpu", lr=1e-3,
+                model_overrides=dict(image_size=64, num_classes=16, in_channels=8))
+    batch = syn.resnet_batch(16, 64, 16, seed=1, dtype=torch.float32)
+    losses = [t.loss_value(t.train_step(batch)) for _ in range(3)]
+    assert all(l == l for l in losses) and losses[-1] < losses[0], losses
+
+
+def test_runtime_executes_the_plan_the_search_wrote_for_wide_resnet():
+    """The 2-stage plan of the reference search for Wide-ResNet 1B on 4 GPUs (stage 1 switches from dp 2 to tp 2
+    in the middle, both partitioning algorithms, partial recompute), run with narrow channels on four gloo ranks."""
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(__file__), "golden", "reference_search", "resnet_1B_2stages.json")) as f:
+        plan = json.load(f)
+    plan.update(global_batch_size=16, micro_batch_size=8, in_channels=8)
+    run_ranks(_searched_resnet_worker, 4, plan)
+
+
+def _searched_gpt_losses(plan, rank=0, world=1):
+    t = Trainer(plan, rank=rank, world_size=world, model_overrides=NODROP, lr_warmup_steps=0, device="cpu", lr=1e-3)
+    return [t.loss_value(t.train_step(gpt_batch(8, 32, 256, seed=1))) for _ in range(2)]
+
+
+def _searched_gpt_worker(rank, world, plan, want):
+    got = _searched_gpt_losses(plan, rank, world)
+    assert max(abs(a - b) for a, b in zip(got, want)) < 5e-3, (rank, got, want)
+
+
+@pytest.mark.parametrize("stages", [2, 4])
+def test_runtime_executes_the_plans_the_search_wrote_for_gpt(stages):
+    """The reference search's GPT-3 1.3B plans for 4 GPUs (uneven op counts per stage, partial recompute chosen
+    per op; the 2-stage plan with two GPUs per stage), shrunk to a narrow 24-layer model, against one process."""
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(__file__), "golden", "reference_search", f"gpt_1_3B_{stages}stages.json")) as f:
+        plan = json.load(f)
+    plan.update(global_batch_size=8, micro_batch_size=2, seq_length=32, max_position_embeddings=32, hidden_size=64,
+                num_attention_heads=2, kv_channels=32, vocab_size=256)
+    if max(max(d) for d in plan["data_parallel_size_of_each_op"]) > 2:
+        plan["micro_batch_size"] = 4
+    single = tiny_gpt_plan(layers=24, seq=32, hidden=64, heads=2, head_dim=32, vocab=256, global_bs=8,
+                           micro_bs=plan["micro_batch_size"])
+    run_ranks(_searched_gpt_worker, 4, plan, _searched_gpt_losses(single))
