@@ -171,3 +171,31 @@ def test_runtime_executes_the_plans_the_search_wrote_for_gpt(stages):
     single = tiny_gpt_plan(layers=24, seq=32, hidden=64, heads=2, head_dim=32, vocab=256, global_bs=8,
                            micro_bs=plan["micro_batch_size"])
     run_ranks(_searched_gpt_worker, 4, plan, _searched_gpt_losses(single))
+
+
+def _searched_t5_losses(plan, rank=0, world=1):
+    from superscaler_b200.data import synthetic as syn
+    t = Trainer(plan, rank=rank, world_size=world, model_overrides=NODROP, lr_warmup_steps=0, device="cpu", lr=1e-3)
+    return [t.loss_value(t.train_step(syn.t5_batch(8, 32, 16, 256, seed=1))) for _ in range(2)]
+
+
+def _searched_t5_worker(rank, world, plan, want):
+    got = _searched_t5_losses(plan, rank, world)
+    assert max(abs(a - b) for a, b in zip(got, want)) < 5e-3, (rank, got, want)
+
+
+def test_runtime_executes_the_plan_the_search_wrote_for_t5():
+    """The reference search's 4-stage T5 770M plan (ops per stage 113 / 118 / 195 / 395: the encoder output crosses
+    three boundaries as an extra tensor), shrunk to a narrow 24 + 24 layer model."""
+    import json
+    import os
+    from helpers import tiny_t5_plan
+    with open(os.path.join(os.path.dirname(__file__), "golden", "reference_search", "t5_770M_4stages.json")) as f:
+        plan = json.load(f)
+    small = dict(global_batch_size=8, micro_batch_size=2, encoder_seq_length=32, decoder_seq_length=16,
+                 max_position_embeddings=32, hidden_size=64, num_attention_heads=2, kv_channels=32, ffn_hidden_size=128,
+                 vocab_size=256)
+    plan.update(small)
+    single = tiny_t5_plan(layers=24, enc_seq=32, dec_seq=16, hidden=64, heads=2, head_dim=32, ffn=128, vocab=256,
+                          global_bs=8, micro_bs=2)
+    run_ranks(_searched_t5_worker, 4, plan, _searched_t5_losses(single), timeout=600)
