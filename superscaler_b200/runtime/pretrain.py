@@ -27,6 +27,29 @@ from .timers import Timers
 from .trainer import Trainer
 
 
+def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int):
+    """Batches of a GPT token corpus: `prefix`.bin holds the token ids (uint16, or uint32 with `prefix`.u32 present
+    instead), `prefix`.npy the document lengths.  Batch i is global samples [i * gbs, (i + 1) * gbs) of the
+    shuffled sample order (a function of the seed and of --train-iters), so a run resumed with the same
+    --train-iters continues where the data stopped."""
+    import numpy as np
+    from ..data.indexed import GPTSampleDataset, TokenCorpus
+    assert trainer.model_name == "gpt", "--data-path feeds the GPT entry point"
+    wide = os.path.exists(prefix + ".u32")
+    corpus = TokenCorpus.from_files(prefix + (".u32" if wide else ".bin"), prefix + ".npy",
+                                    dtype=np.uint32 if wide else np.uint16)
+    gbs, seq = trainer.plan["global_batch_size"], trainer.cfg.seq_length
+    data = GPTSampleDataset(corpus, seq, num_samples=train_iters * gbs, seed=seed)
+
+    def batch(i):
+        rows = np.stack([data[(i * gbs + j) % len(data)] for j in range(gbs)])
+        t = torch.from_numpy(rows)
+        out = {"ids": t[:, :-1].contiguous(), "labels": t[:, 1:].contiguous()}
+        return {k: v.pin_memory() for k, v in out.items()} if torch.cuda.is_available() else out
+
+    return batch
+
+
 def make_batch_fn(trainer: Trainer):
     plan, cfg = trainer.plan, trainer.cfg
     gbs = plan["global_batch_size"]
@@ -77,6 +100,9 @@ def main(argv=None) -> None:
     ap.add_argument("--inject-failure", default=None, metavar="RANK:ITERATION",
                     help="host-side fault injection for tests: that rank raises at the start of that iteration")
     ap.add_argument("--no-fused-comm", action="store_true")
+    ap.add_argument("--data-path", default=None,
+                    help="GPT token corpus prefix (<prefix>.bin uint16 token ids + <prefix>.npy document lengths); "
+                         "default: synthetic batches")
     ap.add_argument("--interleave-factor", type=int, default=1,
                     help="model chunks per pipeline stage (interleaved 1F1B); re-cuts the plan's stages evenly")
     ap.add_argument("--interleave-ops", type=int, nargs="+", default=None,
@@ -114,17 +140,19 @@ def main(argv=None) -> None:
         from torch.utils.tensorboard import SummaryWriter
         writer = SummaryWriter(log_dir=args.tensorboard_dir)
     t_start = time.time()
-    batch_fn = make_batch_fn(trainer)
+    batch_fn = (make_dataset_batch_fn(trainer, args.data_path, args.train_iters, args.seed) if args.data_path
+                else make_batch_fn(trainer))
     # synthetic batches are generated on the host before the loop (a pool of up to 4, reused in turn): building
     # a 768-image batch takes longer than a training step and is not part of what an iteration measures
-    pool = [batch_fn(i) for i in range(trainer.iteration, min(args.train_iters, trainer.iteration + 4))]
+    pool = [] if args.data_path else \
+        [batch_fn(i) for i in range(trainer.iteration, min(args.train_iters, trainer.iteration + 4))]
     timers = Timers(trainer.device.type == "cuda")
     config_name = os.path.splitext(os.path.basename(args.flexpipe_config))[0]
     regions = ["iteration", "forward-backward", "backward-params-all-reduce", "optimizer"]
     pool_start = trainer.iteration
     def one_step(it):
         timers("iteration").start()
-        batch = trainer.to_device(pool[(it - pool_start) % len(pool)])
+        batch = trainer.to_device(batch_fn(it) if args.data_path else pool[(it - pool_start) % len(pool)])
         timers("forward-backward").start()
         loss = trainer.forward_backward(batch)
         trainer._fold_autograd_grads()
