@@ -71,3 +71,22 @@ def test_wordpiece_longest_match_and_specials(tmp_path):
 def test_unknown_tokenizer_kind():
     with pytest.raises(NotImplementedError):
         build_tokenizer("SentencePiece", "x")
+
+
+def test_preprocess_writes_a_corpus_the_dataset_reads(tmp_path, capsys):
+    import numpy as np
+    from superscaler_b200.data import preprocess
+    from superscaler_b200.data.indexed import GPTSampleDataset, TokenCorpus
+    vf, mf, vocab, space = _bpe_files(tmp_path)
+    src = tmp_path / "docs.jsonl"
+    src.write_text('{"text": "low lower newer"}\n\nnewer low\n{"text": "lower"}\n', encoding="utf-8")
+    preprocess.main(["--input", str(src), "--output", str(tmp_path / "c"), "--vocab-file", vf, "--merge-file", mf])
+    assert "tokens" in capsys.readouterr().out
+    tok = build_tokenizer("GPT2BPETokenizer", vf, mf)
+    lengths = np.load(tmp_path / "c.npy")
+    tokens = np.fromfile(tmp_path / "c.bin", dtype=np.uint16)
+    want = [tok.tokenize(t) + [tok.eod] for t in ("low lower newer", "newer low", "lower")]
+    assert lengths.tolist() == [len(w) for w in want] and tokens.tolist() == sum(want, [])
+    corpus = TokenCorpus.from_files(str(tmp_path / "c.bin"), str(tmp_path / "c.npy"))
+    ds = GPTSampleDataset(corpus, seq_length=4, num_samples=3, seed=1)
+    assert all(len(ds[i]) == 5 for i in range(len(ds)))
