@@ -45,6 +45,21 @@ def best_throughput(log_path: str) -> Tuple[Optional[str], float]:
     return best, best_t
 
 
+def throughput_table(log_path: str) -> str:
+    """Markdown table of every run under log_path/csv: iteration time (slowest rank), samples / s, peak memory over
+    the stages (the text counterpart of the reference's result CSVs and plots, scripts/get_e2e_performance.py and
+    scripts/plot_fig*.py; no plotting library is assumed here)."""
+    names = sorted({os.path.basename(f).rsplit("_stage", 1)[0]
+                    for f in glob.glob(os.path.join(log_path, "csv", "*_stage*_rank*.csv"))})
+    lines = ["| run | ranks | iteration (ms) | samples / s | peak memory (MB) |", "|---|---|---|---|---|"]
+    for n in names:
+        ranks = len(glob.glob(os.path.join(log_path, "csv", f"{n}_stage*_rank*.csv")))
+        mem = stage_memory_mb(log_path, n)
+        lines.append(f"| {n} | {ranks} | {run_iteration_time_ms(log_path, n):.1f} | {throughput(log_path, n):.2f} | "
+                     f"{max(mem.values()) if mem else 0:.0f} |")
+    return "\n".join(lines)
+
+
 def search_cost(log_path: str, model: str, size: str) -> Optional[float]:
     files = sorted(glob.glob(os.path.join(log_path, f"{model}_{size}_summary_*.csv")))
     if not files:
@@ -88,7 +103,11 @@ def main(argv=None) -> None:
     ap.add_argument("--log-path", required=True)
     ap.add_argument("--config", default=None)
     ap.add_argument("--pred-csv", default=None)
+    ap.add_argument("--table", action="store_true", help="markdown table of all runs under the log path")
     a = ap.parse_args(argv)
+    if a.table:
+        print(throughput_table(a.log_path))
+        return
     if a.config is None:
         name, t = best_throughput(a.log_path)
         print(json.dumps({"best_config": name, "samples_per_s": t}))

@@ -87,3 +87,17 @@ def test_pretrain_on_a_token_corpus(tmp_path, capsys):
     pretrain.main(common + ["--train-iters", "50", "--load", str(tmp_path / "ckpt")])
     more = [float(x) for x in re.findall(r"lm loss: ([0-9.E+-]+)", capsys.readouterr().out)]
     assert len(more) == 1 and more[0] < losses[0]
+
+
+def test_throughput_table(tmp_path, capsys):
+    log = tmp_path / "logs"
+    os.makedirs(log / "csv")
+    for name, times in (("a_2stages_x", [100.0, 110.0]), ("b_1stages_x", [50.0])):
+        for r, t in enumerate(times):
+            (log / "csv" / f"{name}_stage{r}_rank{r}.csv").write_text(
+                "global_batch_size,time,forward-backward,backward-params-all-reduce,optimizer,max_allocated_memory(MB)\n"
+                f"8,{t},90,5,5,{1000 + r}\n")
+    results.main(["--log-path", str(log), "--table"])
+    out = capsys.readouterr().out.splitlines()
+    assert out[2].startswith("| a_2stages_x | 2 | 110.0 | 72.73 | 1001 |")
+    assert out[3].startswith("| b_1stages_x | 1 | 50.0 | 160.00 | 1000 |")
