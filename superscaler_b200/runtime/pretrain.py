@@ -108,8 +108,12 @@ def main(argv=None) -> None:
     ap.add_argument("--interleave-ops", type=int, nargs="+", default=None,
                     help="ops of every virtual stage (stages x interleave-factor numbers) instead of the even cut")
     ap.add_argument("--distributed-backend", default=None, choices=[None, "nccl", "gloo"])
-    args = ap.parse_args(argv)
+    # launch scripts written for the reference pass many Megatron flags the plan JSON already determines (--fp16,
+    # --num-layers, --micro-batch-size ...): they are accepted and reported, not refused
+    args, ignored = ap.parse_known_args(argv)
     rank, world, _ = init_distributed(args.distributed_backend)
+    if ignored and rank == 0:
+        print("flags without effect here (the plan and the defaults decide): " + " ".join(ignored), flush=True)
     with open(args.flexpipe_config) as f:
         plan = json.load(f)
     if args.interleave_factor > 1:
