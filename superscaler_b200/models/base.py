@@ -11,7 +11,7 @@ send/recv offsets (runtime/megatron/model/flex_model.py:180-209).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Sequence, Tuple
 
 import torch
 

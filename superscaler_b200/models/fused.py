@@ -14,9 +14,8 @@ dropout-add, so those two stay separate kernels on the NCCL path.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Sequence
+from typing import List, Sequence
 
-import torch
 
 from ..ops import functional as F
 from ..parallel import mappings as M

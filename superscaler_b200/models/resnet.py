@@ -11,7 +11,7 @@ ops are replicated over the TP group.  BatchNorm statistics are local to a data-
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Sequence
 
 import torch

@@ -12,7 +12,6 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List
 
-import torch
 
 from ..ops import functional as F
 from .base import Env, Op, OpInfo

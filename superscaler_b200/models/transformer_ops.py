@@ -12,13 +12,12 @@ dense / MLP-2 row-parallel); algo 1 swaps the roles (flex_ops.py:483-538,1027-10
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional, Sequence
 
 import torch
 
 from ..ops import functional as F
 from ..parallel import mappings as M
-from .base import Env, Op, OpInfo
+from .base import Op
 
 
 def _prefix(name: str) -> str:

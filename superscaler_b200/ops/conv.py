@@ -12,7 +12,7 @@ import torch
 import torch.nn.functional as TF
 
 from . import native
-from .functional import _bgrad, _vec_grad, _wgrad, gemm
+from .functional import _vec_grad, _wgrad, gemm
 
 
 def _pad8(n: int) -> int:

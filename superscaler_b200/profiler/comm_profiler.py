@@ -15,7 +15,6 @@ from __future__ import annotations
 import argparse
 import csv
 import glob
-import os
 import statistics
 
 import torch

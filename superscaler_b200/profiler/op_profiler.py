@@ -29,7 +29,6 @@ from typing import Dict, List
 import torch
 import torch.distributed as dist
 
-from ..models.base import OpInfo
 from ..parallel.state import init_distributed
 from ..runtime.stage import run_op
 from ..runtime.trainer import Trainer

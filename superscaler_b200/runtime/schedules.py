@@ -21,8 +21,8 @@ from typing import Any, Dict, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-from ..models.static_info import live_keys_before, op_io, produced_layouts
-from ..parallel.relayout import Layout, Side, Transfer, global_shape, local_shape
+from ..models.static_info import live_keys_before
+from ..parallel.relayout import Layout, Side, Transfer, global_shape
 
 _DTYPES = [torch.bfloat16, torch.float32, torch.int64, torch.float16, torch.uint8, torch.int32]
 _META_WORDS = 12  # per key: ndim, dtype, row, col, groups, requires_grad, then up to 6 dims

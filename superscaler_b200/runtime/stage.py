@@ -8,7 +8,7 @@ tensors and the dropout seed counter; backward replays it with gradients enabled
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Sequence
 
 import torch
 

@@ -9,9 +9,8 @@ runtime/megatron/training.py:227-496).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Tuple
+from typing import List, Tuple
 
-import torch
 
 from ..parallel.relayout import Layout, Side, Transfer
 

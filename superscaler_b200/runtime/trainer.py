@@ -13,9 +13,7 @@ clipping and the inf/nan skip run on the device without a host sync; timing uses
 from __future__ import annotations
 
 import json
-import os
-import time
-from typing import Any, Callable, Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Optional
 
 import torch
 import torch.distributed as dist

@@ -12,8 +12,8 @@ import json
 import os
 import random
 import time
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from dataclasses import dataclass
+from typing import Dict, List, Optional
 
 from .config import GPT_SIZES, RESNET_SIZES, STATE_MULTIPLIERS, T5_SIZES
 from .cost_model import CostModel, CostOptions

@@ -14,10 +14,10 @@ max(compute, comm) instead of compute + comm).  Databases without those columns 
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
 
-from .config import Plan, StagePlan
+from .config import Plan
 from .database import ProfileDB
 from .opinfo import op_spec, reshard_primitives
 

@@ -13,8 +13,7 @@ from __future__ import annotations
 
 import csv
 import math
-import os
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence
 
 MISSING = 1000000  # value of a table cell that no file filled in
 

@@ -10,10 +10,10 @@ recomputed.  For T5 every split point between encoder stages and decoder stages 
 from __future__ import annotations
 
 import argparse
-from typing import List, Optional
+from typing import List
 
 from .config import Plan, build_plan, save_plan
-from .context import SearchArgs, SearchContext, add_cli_arguments, args_from_namespace
+from .context import SearchContext, add_cli_arguments, args_from_namespace
 
 
 def uniform_plans(ctx: SearchContext, pp: int, tp: int, dp: int, micro_bs: int, recompute: bool) -> List[Plan]:

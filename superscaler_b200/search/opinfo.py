@@ -8,7 +8,7 @@ logical activation (``[s, b, h]`` for transformers, ``[b, c, h*w]`` for ResNet),
 from __future__ import annotations
 
 import csv
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 GPT_TUNABLE = ["encoder-embedding", "enc-attention-qkv", "enc-attention-dense", "enc-MLP-GEMM-1", "enc-MLP-GEMM-2"]
 T5_TUNABLE = GPT_TUNABLE + ["dec-attention-qkv-1", "dec-attention-dense-1", "dec-attention-qkv-2",

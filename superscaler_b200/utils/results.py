@@ -10,7 +10,7 @@ from __future__ import annotations
 import csv
 import glob
 import os
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, Optional, Tuple
 
 
 def read_runtime_csv(path: str) -> Dict[str, float]:
