@@ -29,8 +29,22 @@ def _entry(rank, world, port, fn, args, errq):
             dist.destroy_process_group()
 
 
+_CTX = None
+
+
+def _context():
+    """Ranks are forked from a server process that has already imported torch (a fresh interpreter per rank spends
+    seconds on that import); the server itself never initialises a process group or starts threads."""
+    global _CTX
+    if _CTX is None:
+        _CTX = mp.get_context("forkserver")
+        _CTX.set_forkserver_preload(["torch", "torch.distributed", "numpy", "superscaler_b200.runtime.trainer",
+                                     "superscaler_b200.data.synthetic", "superscaler_b200.runtime.checkpointing"])
+    return _CTX
+
+
 def run_ranks(fn, world: int, *args, timeout: float = 240.0):
-    ctx = mp.get_context("spawn")
+    ctx = _context()
     errq = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq)) for r in range(world)]
