@@ -27,7 +27,7 @@ from .timers import Timers
 from .trainer import Trainer
 
 
-def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int):
+def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, eod_token=None):
     """Batches of a GPT token corpus: `prefix`.bin holds the token ids (uint16, or uint32 with `prefix`.u32 present
     instead), `prefix`.npy the document lengths.  Batch i is global samples [i * gbs, (i + 1) * gbs) of the
     shuffled sample order (a function of the seed and of --train-iters), so a run resumed with the same
@@ -45,6 +45,11 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
         rows = np.stack([data[(i * gbs + j) % len(data)] for j in range(gbs)])
         t = torch.from_numpy(rows)
         out = {"ids": t[:, :-1].contiguous(), "labels": t[:, 1:].contiguous()}
+        if eod_token is not None:
+            # positions whose INPUT is the end-of-document token would have to predict the first token of an
+            # unrelated document: they do not count (reference: eod_mask_loss of get_ltor_masks_and_position_ids,
+            # runtime/megatron/utils.py)
+            out["loss_mask"] = (out["ids"] != eod_token).to(torch.float32)
         return {k: v.pin_memory() for k, v in out.items()} if torch.cuda.is_available() else out
 
     return batch
@@ -103,6 +108,8 @@ def main(argv=None) -> None:
     ap.add_argument("--data-path", default=None,
                     help="GPT token corpus prefix (<prefix>.bin uint16 token ids + <prefix>.npy document lengths); "
                          "default: synthetic batches")
+    ap.add_argument("--eod-mask-loss", type=int, default=None, metavar="EOD_TOKEN_ID",
+                    help="with --data-path: positions whose input is this end-of-document token do not count in the loss")
     ap.add_argument("--interleave-factor", type=int, default=1,
                     help="model chunks per pipeline stage (interleaved 1F1B); re-cuts the plan's stages evenly")
     ap.add_argument("--interleave-ops", type=int, nargs="+", default=None,
@@ -144,7 +151,8 @@ def main(argv=None) -> None:
         from torch.utils.tensorboard import SummaryWriter
         writer = SummaryWriter(log_dir=args.tensorboard_dir)
     t_start = time.time()
-    batch_fn = (make_dataset_batch_fn(trainer, args.data_path, args.train_iters, args.seed) if args.data_path
+    batch_fn = (make_dataset_batch_fn(trainer, args.data_path, args.train_iters, args.seed, args.eod_mask_loss)
+                if args.data_path
                 else make_batch_fn(trainer))
     # synthetic batches are generated on the host before the loop (a pool of up to 4, reused in turn): building
     # a 768-image batch takes longer than a training step and is not part of what an iteration measures

@@ -84,7 +84,7 @@ def test_pretrain_on_a_token_corpus(tmp_path, capsys):
     pretrain.main(common + ["--train-iters", "40", "--save", str(tmp_path / "ckpt")])
     losses = [float(x) for x in re.findall(r"lm loss: ([0-9.E+-]+)", capsys.readouterr().out)]
     assert len(losses) == 4 and losses[-1] < 0.5 * losses[0]
-    pretrain.main(common + ["--train-iters", "50", "--load", str(tmp_path / "ckpt")])
+    pretrain.main(common + ["--train-iters", "50", "--load", str(tmp_path / "ckpt"), "--eod-mask-loss", "21"])
     more = [float(x) for x in re.findall(r"lm loss: ([0-9.E+-]+)", capsys.readouterr().out)]
     assert len(more) == 1 and more[0] < losses[0]
 
