@@ -199,3 +199,18 @@ def test_runtime_executes_the_plan_the_search_wrote_for_t5():
     single = tiny_t5_plan(layers=24, enc_seq=32, dec_seq=16, hidden=64, heads=2, head_dim=32, ffn=128, vocab=256,
                           global_bs=8, micro_bs=2)
     run_ranks(_searched_t5_worker, 4, plan, _searched_t5_losses(single), timeout=600)
+
+
+def test_runtime_executes_the_estimated_13b_plan_shape():
+    """plans/gpt_13B_8gpu_b200_extrapolated.json (two pipeline stages of four data-parallel GPUs, searched against
+    scaled tables) with narrow layers on eight gloo ranks, against one process."""
+    import json
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(__file__)), "plans", "gpt_13B_8gpu_b200_extrapolated.json")
+    with open(path) as f:
+        plan = json.load(f)
+    assert sum(plan["num_gpus"]) == 8 and plan["num_layers"] == 40
+    plan.update(global_batch_size=8, micro_batch_size=4, seq_length=32, max_position_embeddings=32, hidden_size=64,
+                num_attention_heads=2, kv_channels=32, vocab_size=256)
+    single = tiny_gpt_plan(layers=40, seq=32, hidden=64, heads=2, head_dim=32, vocab=256, global_bs=8, micro_bs=4)
+    run_ranks(_searched_gpt_worker, 8, plan, _searched_gpt_losses(single), timeout=600)

@@ -124,3 +124,37 @@ def test_uniform_grid_baseline_and_predictor_on_the_reference_database(tmp_path)
     _, plan, report = predict(args)
     assert abs(max(plan.time_list) - 58760.92) < 0.01 and len(report) == 4
     assert 512 / (best / 1000) < 512 / 58.76092 / 1.2          # the searched plan is more than 1.2x faster
+
+
+def test_extrapolated_tables_scale_by_the_hidden_size_and_drive_a_search(tmp_path):
+    """Tables for an unprofiled GPT size: linear-layer times and weights grow with the square of the hidden-size
+    ratio, everything else linearly; the collective tables are re-keyed for the new tensor sizes, and a search
+    against the result writes a plan the trainer's checks accept."""
+    from superscaler_b200.profiler.extrapolate import extrapolate
+    from superscaler_b200.runtime.trainer import _validate_plan
+    src = os.path.join(os.path.dirname(os.path.dirname(__file__)), "profiled-time-b200") + os.sep
+    dst = str(tmp_path / "db") + os.sep
+    files = extrapolate(src, dst, "1_3B", "6_7B")
+    assert os.path.isfile(dst + "EXTRAPOLATED.md") and any("prim_gpt_6_7B_all_reduce_8gpus" in f for f in files)
+
+    def table(path):
+        with open(path) as f:
+            return {r[0]: [float(x) for x in r[1:]] for r in list(csv.reader(f))[1:]}
+    a, b = table(src + "gpt_1_3B_mbs8_tp1_algo0.csv"), table(dst + "gpt_6_7B_mbs8_tp1_algo0.csv")
+    r = 4096 / 2048
+    assert abs(b["enc-MLP-GEMM-1"][0] - a["enc-MLP-GEMM-1"][0] * r * r) < 0.01      # forward time
+    assert abs(b["enc-MLP-GEMM-1"][4] - a["enc-MLP-GEMM-1"][4] * r * r) < 0.01      # weights
+    assert abs(b["enc-attention-score"][0] - a["enc-attention-score"][0] * r) < 0.01
+    assert abs(b["enc-1st-layernorm"][5] - a["enc-1st-layernorm"][5] * r) < 0.01    # activations
+    out = str(tmp_path / "out") + os.sep
+    for sub in ("csv", "top_configs", "trends"):
+        os.makedirs(out + sub, exist_ok=True)
+    args = SearchArgs(model_name="gpt", model_size="6_7B", global_batch_size=512, micro_batch_size=[4, 8, 16, 32, 64],
+                      num_nodes=1, num_gpus_per_node=8, memory_limit=170000, profiled_time_path=dst,
+                      config_save_path=out, log_path=out, config_suffix="t", max_num_hops=7, time_budget_total=60,
+                      multi_process=False, explored_budget=150).finalize()
+    res = Searcher(SearchContext(args, verbose=False)).run(2)
+    with open(f"{out}gpt_6_7B_2stages_t.json") as f:
+        plan = json.load(f)
+    _validate_plan(plan)
+    assert sum(plan["num_gpus"]) == 8 and res[0] < 100000             # no missing-table penalty in the price
