@@ -4,7 +4,10 @@ Public API (what a user calls):
 
     trainer = Trainer.from_plan("plan.json", model_overrides={...})
     for batch in loader:                      # pinned host tensors, one global batch
-        stats = trainer.train_step(batch)     # -> {"loss": float, ...}
+        stats = trainer.train_step(batch)     # -> {"loss_tensor": device scalar, "lr": ..., "iteration": ...}
+        loss = trainer.loss_value(stats)      # host float (synchronises; averaged over the data-parallel ranks)
+    trainer.evaluate(batches)                 # mean loss / perplexity without touching gradients
+    trainer.logits(ids)                       # inference forward of a single-stage GPT plan
 
 Counterpart of the reference's pretrain / train_step (runtime/megatron/training.py:83-168,656-752) with
 these differences: gradients accumulate in fp32 directly from the wgrad kernels; the optimizer step,
