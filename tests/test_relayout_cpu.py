@@ -120,3 +120,34 @@ def _bcast_worker(rank, world):
 def test_broadcast_batch_inside_sub_groups():
     from dist_utils import run_ranks
     run_ranks(_bcast_worker, 4)
+
+
+def test_pack_and_unpack_move_the_right_elements_for_every_layout_pair():
+    """The whole forward data path (plan, packing on the owners, unpacking on the requesters) in one process, for
+    every pair of sides with tp, dp in {1, 2, 4, 8} (same ranks or disjoint), every pair of layouts, 2-D and 3-D
+    tensors: each destination rank must end up with exactly its region of the global tensor."""
+    from superscaler_b200.parallel.relayout import _msg_numel, _pack, _unpack
+    torch.manual_seed(0)
+    shapes = [(16, 48), (16, 48, 3)]
+    degrees = [(1, 1), (2, 1), (1, 2), (2, 2), (4, 1), (1, 4), (4, 2), (2, 4), (8, 1), (1, 8)]
+    checked = 0
+    for gshape in shapes:
+        G = torch.randn(gshape)
+        for (stp, sdp), (dtp, ddp) in itertools.product(degrees, repeat=2):
+            for same in (True, False):
+                src = Side(0, stp, sdp)
+                dst = Side(0 if same else src.size, dtp, ddp)
+                for sl, dl in itertools.product(LAYOUTS, repeat=2):
+                    if sl.groups != dl.groups:
+                        continue
+                    held = {r: _local(G, src, sl, r) for r in range(src.first_rank, src.first_rank + src.size)}
+                    outs = {r: torch.full(local_shape(dst, dl, gshape), float("nan"))
+                            for r in range(dst.first_rank, dst.first_rank + dst.size)}
+                    for m in plan_transfer(src, sl, dst, dl, gshape):
+                        buf = _pack(held[m.src], src, sl, m.src, m, gshape)
+                        assert buf.numel() == _msg_numel(m, gshape)
+                        _unpack(buf, outs[m.dst], dst, dl, m.dst, m, gshape, False)
+                    for r, out in outs.items():
+                        assert torch.equal(out, _local(G, dst, dl, r)), (gshape, src, sl, dst, dl, r)
+                        checked += 1
+    assert checked > 10000
