@@ -51,16 +51,19 @@ class ParamStore:
         self.master = self.grad = self.exp_avg = self.exp_avg_sq = self.model16 = None
         self.wd_end = 0
         self.total = 0
-        self._shared: Dict[str, str] = {}
+        self._shared: Dict[Tuple[str, int], str] = {}   # (shared key, tensor-parallel degree) -> parameter name
         self.grad_allocator = None      # optional: numel -> (tensor, owner) for a peer-mapped gradient buffer
         self.symm_grad = None
 
     def declare(self, spec: ParamSpec) -> str:
-        """Registers a parameter; tied parameters (same shared_key) resolve to the first declaration."""
+        """Registers a parameter; tied parameters (same shared_key AND the same tensor-parallel degree, hence the
+        same shard) resolve to the first declaration.  Ops of one stage that share a weight under different
+        degrees keep a copy each; runtime/tied.py keeps such copies equal, as it does across stages."""
         if spec.shared_key is not None:
-            if spec.shared_key in self._shared:
-                return self._shared[spec.shared_key]
-            self._shared[spec.shared_key] = spec.name
+            k = (spec.shared_key, spec.tp)
+            if k in self._shared:
+                return self._shared[k]
+            self._shared[k] = spec.name
         self.specs.append(spec)
         return spec.name
 
@@ -124,6 +127,9 @@ class ParamStore:
             p.main_grad = self.grad[off:off + n].view(s.shape)
             p.spec = s
             self.params[s.name] = p
+
+    def shared_name(self, key: str, tp: int) -> Optional[str]:
+        return self._shared.get((key, tp))
 
     def __getitem__(self, name: str) -> torch.nn.Parameter:
         return self.params[name]

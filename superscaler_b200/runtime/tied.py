@@ -34,17 +34,16 @@ class TiedWeights:
             if key.endswith("relative_attention_bias") and not getattr(trainer.cfg, "relative_position_bias", False):
                 continue
             holders: List[Side] = []
-            seen = set()   # physical stages that already hold a copy (one copy per stage, shared by its chunks)
+            seen = set()   # (physical stage, tp): one copy per stage and tensor-parallel degree, shared by its ops
             for s, (lo, hi) in enumerate(trainer.stage_bounds):
                 phys = s % ps.num_stages
-                if phys in seen:
-                    continue
                 for i in range(lo, hi):
                     if trainer.op_names[i] in op_names:
-                        holders.append(Side(ps.stage_start[phys], plan["model_parallel_size_of_each_op"][s][i - lo],
-                                            plan["data_parallel_size_of_each_op"][s][i - lo]))
-                        seen.add(phys)
-                        break
+                        tp = plan["model_parallel_size_of_each_op"][s][i - lo]
+                        if (phys, tp) in seen:
+                            continue
+                        seen.add((phys, tp))
+                        holders.append(Side(ps.stage_start[phys], tp, plan["data_parallel_size_of_each_op"][s][i - lo]))
             for other in holders[1:]:
                 self.links.append((key, holders[0], other))
 
@@ -54,31 +53,33 @@ class TiedWeights:
         out = []
         for key, root, other in self.links:
             if other.contains(self.t.rank):
-                name = self.t.store._shared.get(key)
+                name = self.t.store.shared_name(key, other.tp)
                 if name is not None:
                     out.append(name)
         return out
 
-    def _grad(self, key: str):
-        name = self.t.store._shared.get(key)
+    def _grad(self, key: str, tp: int):
+        name = self.t.store.shared_name(key, tp)
         return None if name is None else self.t.store.params[name].main_grad
 
     def sync_grads(self) -> None:
         rank, dev = self.t.rank, self.t.device
         for key, root, other in self.links:
-            if not (root.contains(rank) or other.contains(rank)):
+            in_root, in_other = root.contains(rank), other.contains(rank)
+            if not (in_root or in_other):
                 continue
-            g = self._grad(key)
+            g_root = self._grad(key, root.tp) if in_root else None
+            g_other = self._grad(key, other.tp) if in_other else None
             lay = LAYOUT[key]
-            mine = root if root.contains(rank) else other
-            # global shape of [1, rows, cols] with dim 1 (vocabulary) split over tp
-            local = (1,) + tuple(g.shape)
-            gshape = (1, local[1] * (mine.tp if lay.col == "split" else 1)) + tuple(local[2:])
-            up = Transfer(rank, other, lay, root, lay, gshape, g.dtype, dev)
-            got = up.post(g.unsqueeze(0).contiguous() if other.contains(rank) else None)()
-            if root.contains(rank):
-                g.add_(got.squeeze(0))
-            down = Transfer(rank, root, lay, other, lay, gshape, g.dtype, dev)
-            got = down.post(g.unsqueeze(0).contiguous() if root.contains(rank) else None)()
-            if other.contains(rank):
-                g.copy_(got.squeeze(0))
+            ref, side = (g_other, other) if in_other else (g_root, root)
+            # global shape of [1, rows, cols] with dim 1 (vocabulary / heads) split over tp
+            local = (1,) + tuple(ref.shape)
+            gshape = (1, local[1] * (side.tp if lay.col == "split" else 1)) + tuple(local[2:])
+            up = Transfer(rank, other, lay, root, lay, gshape, ref.dtype, dev)
+            got = up.post(g_other.unsqueeze(0).contiguous() if in_other else None)()
+            if in_root:
+                g_root.add_(got.squeeze(0))
+            down = Transfer(rank, root, lay, other, lay, gshape, ref.dtype, dev)
+            got = down.post(g_root.unsqueeze(0).contiguous() if in_root else None)()
+            if in_other:
+                g_other.copy_(got.squeeze(0))

@@ -136,9 +136,12 @@ class Trainer:
         self.env.training = training
         self.stage = Stage(chunks, self.env, build_fn, fuse_fn if fuse else None)
         self._tied = None
-        if self.pstate.num_stages > 1:
+        if world_size > 1:
+            # copies of a tied weight in other pipeline stages, or in ops of this stage with another tensor-parallel
+            # degree, are kept equal by summing their gradients every step
             from .tied import TiedWeights
-            self._tied = TiedWeights(self)
+            tied = TiedWeights(self)
+            self._tied = tied if tied.links else None
         self.optimizer = StageOptimizer(self.store, self.pstate, lr=lr, weight_decay=weight_decay, clip_grad=clip_grad,
                                         kind=optimizer,
                                         norm_exclude=self._tied.duplicate_param_names() if self._tied else ())

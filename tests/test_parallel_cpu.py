@@ -214,3 +214,34 @@ def test_runtime_executes_the_estimated_13b_plan_shape():
                 num_attention_heads=2, kv_channels=32, vocab_size=256)
     single = tiny_gpt_plan(layers=40, seq=32, hidden=64, heads=2, head_dim=32, vocab=256, global_bs=8, micro_bs=4)
     run_ranks(_searched_gpt_worker, 8, plan, _searched_gpt_losses(single), timeout=600)
+
+
+def _fuzz_worker(rank, world, plans, want):
+    for i, plan in enumerate(plans):
+        got = _losses(plan, rank, world)
+        assert max(abs(a - b) for a, b in zip(got, want)) < 3e-3, (rank, i, got, want,
+                                                                    plan["model_parallel_size_of_each_op"],
+                                                                    plan["algo_of_each_op"])
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_random_per_op_layouts_match_single_process(seed):
+    """In-stage resharding fuzz: every op of a two-rank stage draws its own (tp, dp) in {(1, 2), (2, 1)} in runs of
+    random length and its own partitioning algorithm; forward AND gradients (the later losses) must not change."""
+    import random
+    rng = random.Random(seed)
+    plans = []
+    for _ in range(4):
+        plan = tiny_gpt_plan(**KW, num_gpus=(2,), tp=[2])
+        n = plan["num_ops_in_each_stage"][0]
+        tp, cur = [], rng.choice([1, 2])
+        while len(tp) < n:
+            tp += [cur] * rng.randint(1, 9)
+            cur = 3 - cur
+        tp = tp[:n]
+        plan["model_parallel_size_of_each_op"] = [tp]
+        plan["data_parallel_size_of_each_op"] = [[2 // t for t in tp]]
+        plan["algo_of_each_op"] = [[rng.randint(0, 1) for _ in range(n)]]
+        plan["resharding_stages"] = [True]
+        plans.append(plan)
+    run_ranks(_fuzz_worker, 2, plans, _base(), timeout=600)
