@@ -245,3 +245,69 @@ def test_random_per_op_layouts_match_single_process(seed):
         plan["resharding_stages"] = [True]
         plans.append(plan)
     run_ranks(_fuzz_worker, 2, plans, _base(), timeout=600)
+
+
+def _fuzz4_losses(plan, rank=0, world=1):
+    ov = dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=4)
+    t = Trainer(plan, rank=rank, world_size=world, model_overrides=ov, lr_warmup_steps=0, device="cpu", lr=1e-3)
+    return [t.loss_value(t.train_step(gpt_batch(8, 64, 256, seed=1))) for _ in range(2)]
+
+
+def _fuzz4_worker(rank, world, plans, want):
+    for i, plan in enumerate(plans):
+        got = _fuzz4_losses(plan, rank, world)
+        assert max(abs(a - b) for a, b in zip(got, want)) < 3e-3, (rank, i, got, want,
+                                                                    plan["model_parallel_size_of_each_op"],
+                                                                    plan["algo_of_each_op"])
+
+
+def test_random_per_op_layouts_on_four_ranks_match_single_process():
+    """The same fuzz with tp in {1, 2, 4} on a four-rank stage (dp = 4 / tp), four heads."""
+    import random
+    rng = random.Random(7)
+    kw = dict(layers=2, seq=64, hidden=64, heads=4, head_dim=16, vocab=256, global_bs=8, micro_bs=4)
+    plans = []
+    for _ in range(3):
+        plan = tiny_gpt_plan(**kw, num_gpus=(4,), tp=[4])
+        n = plan["num_ops_in_each_stage"][0]
+        tp = []
+        while len(tp) < n:
+            tp += [rng.choice([1, 2, 4])] * rng.randint(1, 9)
+        tp = tp[:n]
+        plan["model_parallel_size_of_each_op"] = [tp]
+        plan["data_parallel_size_of_each_op"] = [[4 // t for t in tp]]
+        plan["algo_of_each_op"] = [[rng.randint(0, 1) for _ in range(n)]]
+        plan["resharding_stages"] = [True]
+        plans.append(plan)
+    run_ranks(_fuzz4_worker, 4, plans, _fuzz4_losses(tiny_gpt_plan(**kw)), timeout=600)
+
+
+def _resnet_fuzz_worker(rank, world, plans, want):
+    for i, plan in enumerate(plans):
+        got = _other_model_losses("resnet", plan, rank, world, steps=2)
+        assert max(abs(a - b) for a, b in zip(got, want)) < 2e-2 * max(1.0, abs(want[0])), \
+            (rank, i, got, want, plan["model_parallel_size_of_each_op"], plan["algo_of_each_op"])
+
+
+def test_random_per_op_layouts_of_wide_resnet_match_single_process():
+    """Convolutions, ReLU and pooling ops draw (tp, dp) and the partitioning algorithm at random on two ranks;
+    the ops that normalise over the batch (BatchNorm, and the downsample path that contains one) stay on dp = 1 so
+    that their statistics see the whole micro-batch, as in the single-process run."""
+    import random
+    from helpers import tiny_resnet_plan
+    from superscaler_b200.models.resnet import ResNetConfig, resnet_op_names
+    rng = random.Random(3)
+    plan_fn = lambda **kw: tiny_resnet_plan(global_bs=16, micro_bs=8, **kw)
+    names = resnet_op_names(ResNetConfig(blocks=(1, 1, 1, 1)))
+    plans = []
+    for _ in range(3):
+        plan = plan_fn(num_gpus=(2,), tp=[2])
+        assert plan["num_ops_in_each_stage"][0] == len(names)
+        tp = [2 if ("bn" in n or "downsample" in n) else rng.choice([1, 2]) for n in names]
+        plan["model_parallel_size_of_each_op"] = [tp]
+        plan["data_parallel_size_of_each_op"] = [[2 // t for t in tp]]
+        plan["algo_of_each_op"] = [[rng.randint(0, 1) for _ in names]]
+        plan["resharding_stages"] = [True]
+        plans.append(plan)
+    base = _other_model_losses("resnet", plan_fn(), steps=2)
+    run_ranks(_resnet_fuzz_worker, 2, plans, base, timeout=600)
