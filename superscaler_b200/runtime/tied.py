@@ -63,23 +63,29 @@ class TiedWeights:
         return None if name is None else self.t.store.params[name].main_grad
 
     def sync_grads(self) -> None:
+        """Two passes over the links: first every copy's gradient is added at the root, then the total goes back to
+        every copy (with three holders -- T5's encoder embedding, decoder embedding and LM head -- a copy must not
+        be overwritten before the last contribution has arrived at the root)."""
         rank, dev = self.t.rank, self.t.device
-        for key, root, other in self.links:
-            in_root, in_other = root.contains(rank), other.contains(rank)
-            if not (in_root or in_other):
-                continue
-            g_root = self._grad(key, root.tp) if in_root else None
-            g_other = self._grad(key, other.tp) if in_other else None
-            lay = LAYOUT[key]
-            ref, side = (g_other, other) if in_other else (g_root, root)
-            # global shape of [1, rows, cols] with dim 1 (vocabulary / heads) split over tp
-            local = (1,) + tuple(ref.shape)
-            gshape = (1, local[1] * (side.tp if lay.col == "split" else 1)) + tuple(local[2:])
-            up = Transfer(rank, other, lay, root, lay, gshape, ref.dtype, dev)
-            got = up.post(g_other.unsqueeze(0).contiguous() if in_other else None)()
-            if in_root:
-                g_root.add_(got.squeeze(0))
-            down = Transfer(rank, root, lay, other, lay, gshape, ref.dtype, dev)
-            got = down.post(g_root.unsqueeze(0).contiguous() if in_root else None)()
-            if in_other:
-                g_other.copy_(got.squeeze(0))
+        for phase in ("up", "down"):
+            for key, root, other in self.links:
+                in_root, in_other = root.contains(rank), other.contains(rank)
+                if not (in_root or in_other):
+                    continue
+                g_root = self._grad(key, root.tp) if in_root else None
+                g_other = self._grad(key, other.tp) if in_other else None
+                lay = LAYOUT[key]
+                ref, side = (g_other, other) if in_other else (g_root, root)
+                # global shape of [1, rows, cols] with dim 1 (vocabulary / heads) split over tp
+                local = (1,) + tuple(ref.shape)
+                gshape = (1, local[1] * (side.tp if lay.col == "split" else 1)) + tuple(local[2:])
+                if phase == "up":
+                    up = Transfer(rank, other, lay, root, lay, gshape, ref.dtype, dev)
+                    got = up.post(g_other.unsqueeze(0).contiguous() if in_other else None)()
+                    if in_root:
+                        g_root.add_(got.squeeze(0))
+                else:
+                    down = Transfer(rank, root, lay, other, lay, gshape, ref.dtype, dev)
+                    got = down.post(g_root.unsqueeze(0).contiguous() if in_root else None)()
+                    if in_other:
+                        g_other.copy_(got.squeeze(0))

@@ -75,7 +75,8 @@ def _other_model_losses(model, plan, rank=0, world=1, steps=3):
 def _other_model_worker(rank, world, model, plan, want):
     got = _other_model_losses(model, plan, rank, world)
     # the ResNet bound covers what threaded fp32 reductions plus Adam do to two runs of the SAME plan (3e-3)
-    assert max(abs(a - b) for a, b in zip(got, want)) < 2e-2 * max(1.0, abs(want[0])), (rank, got, want)
+    bound = 5e-3 if model == "t5" else 2e-2 * max(1.0, abs(want[0]))
+    assert max(abs(a - b) for a, b in zip(got, want)) < bound, (rank, got, want)
 
 
 # Data-parallel Wide-ResNet plans are left out on purpose: BatchNorm normalises with the statistics of the samples a
@@ -311,3 +312,48 @@ def test_random_per_op_layouts_of_wide_resnet_match_single_process():
         plans.append(plan)
     base = _other_model_losses("resnet", plan_fn(), steps=2)
     run_ranks(_resnet_fuzz_worker, 2, plans, base, timeout=600)
+
+
+def test_random_stage_cuts_match_single_process():
+    """Pipeline fuzz on four ranks: 2 to 4 stages cut at random ops (also in the middle of a layer, where the
+    residual, the deferred bias or the value tensor cross the boundary), random GPU counts and tp per stage,
+    recompute on or off per stage."""
+    import random
+    rng = random.Random(5)
+    kw = dict(layers=2, seq=64, hidden=64, heads=4, head_dim=16, vocab=256, global_bs=8, micro_bs=4)
+    n = len(tiny_gpt_plan(**kw)["algo_of_each_op"][0])
+    plans = []
+    for _ in range(4):
+        stages = rng.randint(2, 4)
+        gpus = {2: [(2, 2), (1, 3), (3, 1)], 3: [(1, 1, 2), (2, 1, 1), (1, 2, 1)], 4: [(1, 1, 1, 1)]}[stages]
+        gpus = [g for g in gpus if all(x in (1, 2, 4) for x in g)] or [(2, 2)]
+        num_gpus = rng.choice(gpus)
+        cuts = sorted(rng.sample(range(1, n), stages - 1))
+        counts = [b - a for a, b in zip([0] + cuts, cuts + [n])]
+        tp = [rng.choice([t for t in (1, 2, 4) if t <= g]) for g in num_gpus]
+        plan = tiny_gpt_plan(**kw, num_gpus=num_gpus, tp=tp, ops_per_stage=counts, recompute=rng.randint(0, 1))
+        plans.append(plan)
+    run_ranks(_fuzz4_worker, 4, plans, _fuzz4_losses(tiny_gpt_plan(**kw)), timeout=600)
+
+
+def _t5_fuzz_worker(rank, world, plans, want):
+    for i, plan in enumerate(plans):
+        got = _other_model_losses("t5", plan, rank, world, steps=2)
+        assert max(abs(a - b) for a, b in zip(got, want)) < 5e-3, (rank, i, got, want, plan["num_ops_in_each_stage"])
+
+
+def test_random_stage_cuts_of_t5_match_single_process():
+    """T5 on four ranks with cuts at random ops: the encoder output travels as an extra tensor through every stage
+    between its producer and the last cross-attention that reads it."""
+    import random
+    from helpers import tiny_t5_plan
+    rng = random.Random(11)
+    n = len(tiny_t5_plan()["algo_of_each_op"][0])
+    plans = []
+    for num_gpus in ((1, 1, 1, 1), (2, 1, 1), (1, 1, 2)):
+        stages = len(num_gpus)
+        cuts = sorted(rng.sample(range(1, n), stages - 1))
+        counts = [b - a for a, b in zip([0] + cuts, cuts + [n])]
+        tp = [rng.choice([t for t in (1, 2) if t <= g]) for g in num_gpus]
+        plans.append(tiny_t5_plan(num_gpus=num_gpus, tp=tp, ops_per_stage=counts, recompute=rng.randint(0, 1)))
+    run_ranks(_t5_fuzz_worker, 4, plans, _other_model_losses("t5", tiny_t5_plan(), steps=2), timeout=600)
