@@ -35,9 +35,13 @@ class _CheckpointFn(torch.autograd.Function):
         holder["out_keys"] = out_keys
         ctx.out_keys = out_keys
         outs = tuple(st[k] for k in out_keys)
-        # inputs passed through unchanged must not be returned as the same tensor object
+        # Inputs passed through unchanged must not be returned as the same tensor object, and neither may a
+        # parameter an op hands on (the deferred bias of a projection whose dropout + add lies behind the segment's
+        # end): autograd would make the returned object an output of this node, so the PARAMETER itself would get
+        # this node as its grad_fn and the replay in backward would recurse into it.  Under no_grad only such
+        # leaves can require grad; they are returned as views.
         ids_in = {id(t) for t in tensors}
-        return tuple(o.view_as(o) if id(o) in ids_in else o for o in outs)
+        return tuple(o.view_as(o) if (id(o) in ids_in or o.requires_grad) else o for o in outs)
 
     @staticmethod
     def backward(ctx, *grads):

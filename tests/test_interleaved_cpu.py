@@ -108,3 +108,34 @@ def test_pipeline_evaluation_matches_single_process(v):
     assert base[3] < base[1]           # evaluating after two steps sees the trained weights
     plan = interleave_plan(tiny_gpt_plan(**KW, num_gpus=(1, 1), tp=[1, 1]), v)
     run_ranks(_eval_worker, 2, plan, base)
+
+
+def _fuzz_worker(rank, world, plans, want):
+    for i, plan in enumerate(plans):
+        got = _losses(plan, rank, world)
+        assert max(abs(a - b) for a, b in zip(got, want)) < 3e-3, (rank, i, got, want, plan["num_ops_in_each_stage"])
+
+
+def test_interleaved_plans_with_random_cuts_match_single_process():
+    """Interleaving fuzz on four ranks: two or four physical stages, 2 or 3 chunks each, virtual-stage cuts at random
+    ops, one or two (tensor-parallel) GPUs per stage, recompute on or off."""
+    import random
+    rng = random.Random(17)
+    plans = []
+    for gpus, tp in (((2, 2), [2, 2]), ((1, 1, 1, 1), [1, 1, 1, 1]), ((2, 2), [1, 1])):
+        v = rng.choice([2, 3]) if len(gpus) == 2 else 2
+        base = tiny_gpt_plan(**KW, num_gpus=gpus, tp=tp, recompute=rng.randint(0, 1))
+        n = sum(base["num_ops_in_each_stage"])
+        total = len(gpus) * v
+        cuts = sorted(rng.sample(range(1, n), total - 1))
+        counts = [b - a for a, b in zip([0] + cuts, cuts + [n])]
+        plans.append(interleave_plan(base, v, counts))
+    # 12 / 2 = 6 micro-batches: a multiple of 2 stages; the 4-stage plan needs a multiple of 4 -> micro batch 3
+    for p in plans:
+        if len(p["num_gpus"]) // p["interleave_factor"] == 4:
+            p["micro_batch_size"] = 3
+    single = tiny_gpt_plan(**KW)
+    want = _losses(single)
+    run_ranks(_fuzz_worker, 4, [p for p in plans if p["micro_batch_size"] == 2], want, timeout=600)
+    single3 = tiny_gpt_plan(**{**KW, "micro_bs": 3})
+    run_ranks(_fuzz_worker, 4, [p for p in plans if p["micro_batch_size"] == 3], _losses(single3), timeout=600)

@@ -357,3 +357,24 @@ def test_random_stage_cuts_of_t5_match_single_process():
         tp = [rng.choice([t for t in (1, 2) if t <= g]) for g in num_gpus]
         plans.append(tiny_t5_plan(num_gpus=num_gpus, tp=tp, ops_per_stage=counts, recompute=rng.randint(0, 1)))
     run_ranks(_t5_fuzz_worker, 4, plans, _other_model_losses("t5", tiny_t5_plan(), steps=2), timeout=600)
+
+
+def test_random_stage_cuts_of_wide_resnet_match_single_process():
+    """Wide-ResNet on four ranks, cuts at random ops (inside bottleneck blocks too, where the block input travels on
+    as the residual), stages of one GPU or of two tensor-parallel GPUs."""
+    import random
+    from helpers import tiny_resnet_plan
+    rng = random.Random(13)
+    plan_fn = lambda **kw: tiny_resnet_plan(global_bs=16, micro_bs=8, **kw)
+    n = len(plan_fn()["algo_of_each_op"][0])
+    plans = []
+    for num_gpus in ((1, 1, 1, 1), (2, 1, 1), (1, 2, 1), (2, 2)):
+        stages = len(num_gpus)
+        cuts = sorted(rng.sample(range(1, n), stages - 1))
+        counts = [b - a for a, b in zip([0] + cuts, cuts + [n])]
+        plan = plan_fn(num_gpus=num_gpus, tp=list(num_gpus), ops_per_stage=counts, recompute=rng.randint(0, 1))
+        plan["algo_of_each_op"] = [[rng.randint(0, 1) for _ in range(c)] for c in counts]
+        plan["resharding_stages"] = [True] * stages
+        plans.append(plan)
+    base = _other_model_losses("resnet", plan_fn(), steps=2)
+    run_ranks(_resnet_fuzz_worker, 4, plans, base, timeout=600)

@@ -104,3 +104,28 @@ def test_plan_validation_messages():
     bad["recompute_ops"][0].pop()
     with pytest.raises(ValueError, match="recompute_ops has"):
         Trainer(bad, device="cpu")
+
+
+def test_recompute_segment_may_end_right_after_a_projection():
+    """The deferred bias of the attention output / MLP down projection (a parameter handed to the following
+    dropout + add op) can be an OUTPUT of a checkpointed segment: per-op recompute flags that stop between the two
+    ops must train like the plan without recompute (the parameter used to become an output node of the
+    checkpoint function, and the replay recursed without end)."""
+    import torch
+    from superscaler_b200.data.synthetic import gpt_batch
+    from superscaler_b200.runtime.trainer import Trainer
+    from helpers import tiny_gpt_plan
+    ov = dict(hidden_dropout=0.0, attention_dropout=0.0)
+
+    def losses(plan):
+        t = Trainer(plan, model_overrides=ov, lr_warmup_steps=0, device="cpu", lr=1e-3)
+        return [t.loss_value(t.train_step(gpt_batch(4, 128, 512, seed=1))) for _ in range(3)]
+
+    base = losses(tiny_gpt_plan())
+    plan = tiny_gpt_plan()
+    rc = [0] * len(plan["recompute_ops"][0])
+    for i in (2, 3, 4, 5, 6, 7, 10, 11, 12, 15, 16, 17, 18, 19, 20):     # ..., dense (7) | dropout-add (8) not
+        rc[i] = 1
+    plan["recompute_ops"] = [rc]
+    got = losses(plan)
+    assert max(abs(a - b) for a, b in zip(got, base)) < 1e-4, (got, base)
