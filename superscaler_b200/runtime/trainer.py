@@ -48,6 +48,11 @@ def _model_factory(model_name: str):
     raise ValueError(f"unknown model {model_name}")
 
 
+# ops that keep their activations whatever the plan says: the embeddings and the loss ops (the search never marks
+# them either, reference: search/model_ops_info.py:76-90)
+_NEVER_RECOMPUTED = ("encoder-embedding", "decoder-embedding", "gpt-post-process", "t5-post-process", "fc")
+
+
 def _validate_plan(plan: dict) -> None:
     """Shape checks of a plan JSON with messages that name the offending stage (a wrong plan otherwise fails deep
     inside group creation or a kernel launch)."""
@@ -121,7 +126,8 @@ class Trainer:
                                   tp=plan["model_parallel_size_of_each_op"][s][i - lo],
                                   dp=plan["data_parallel_size_of_each_op"][s][i - lo],
                                   algo=plan["algo_of_each_op"][s][i - lo],
-                                  recompute=plan["recompute_ops"][s][i - lo]) for i in range(lo, hi)])
+                                  recompute=0 if names[i] in _NEVER_RECOMPUTED else plan["recompute_ops"][s][i - lo])
+                           for i in range(lo, hi)])
         self.infos = [i for c in chunks for i in c]
         F.manual_seed(seed + 100 * self.pstate.stage)
         self.store = ParamStore(self.device, base_seed=seed)

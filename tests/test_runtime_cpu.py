@@ -129,3 +129,44 @@ def test_recompute_segment_may_end_right_after_a_projection():
     plan["recompute_ops"] = [rc]
     got = losses(plan)
     assert max(abs(a - b) for a, b in zip(got, base)) < 1e-4, (got, base)
+
+
+def test_random_per_op_recompute_flags_do_not_change_training():
+    """Per-op recompute fuzz (single process): any 0/1 pattern over the ops, with segments starting and ending
+    anywhere, trains like the plan that keeps everything (the search sets these flags op by op)."""
+    import random
+    import torch
+    from superscaler_b200.data import synthetic as syn
+    from superscaler_b200.runtime.trainer import Trainer
+    from helpers import tiny_gpt_plan, tiny_resnet_plan, tiny_t5_plan
+    rng = random.Random(23)
+    cases = [
+        ("gpt", tiny_gpt_plan, dict(hidden_dropout=0.0, attention_dropout=0.0),
+         lambda: syn.gpt_batch(4, 128, 512, seed=1), 3e-3),     # segment ends split fused op groups: rounding
+        ("t5", tiny_t5_plan, dict(hidden_dropout=0.0, attention_dropout=0.0),
+         lambda: syn.t5_batch(4, 64, 32, 256, seed=1), 3e-3),
+        ("resnet", lambda: tiny_resnet_plan(global_bs=16, micro_bs=8), dict(image_size=64, num_classes=16),
+         lambda: syn.resnet_batch(16, 64, 16, seed=1, dtype=torch.float32), 2e-2),
+    ]
+    for name, plan_fn, ov, batch_fn, tol in cases:
+        def losses(plan):
+            t = Trainer(plan, model_overrides=ov, lr_warmup_steps=0, device="cpu", lr=1e-3)
+            b = batch_fn()
+            return [t.loss_value(t.train_step(b)) for _ in range(2)]
+        base = losses(plan_fn())
+        for trial in range(4):
+            plan = plan_fn()
+            n = len(plan["recompute_ops"][0])
+            rc, cur = [], rng.randint(0, 1)
+            while len(rc) < n:
+                rc += [cur] * rng.randint(1, 6)
+                cur = 1 - cur
+            rc = rc[:n]
+            # the ops the search never recomputes (embeddings, the loss op; reference: search/model_ops_info.py:76-90)
+            never = {"encoder-embedding", "decoder-embedding", "gpt-post-process", "t5-post-process", "final-layernorm",
+                     "fc", "conv1"}
+            names = Trainer(plan_fn(), model_overrides=ov, device="cpu").op_names
+            rc = [0 if names[i] in never else rc[i] for i in range(n)]
+            plan["recompute_ops"] = [rc]
+            got = losses(plan)
+            assert max(abs(a - b) for a, b in zip(got, base)) < tol, (name, trial, got, base, rc)
