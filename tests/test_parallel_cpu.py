@@ -244,6 +244,11 @@ def test_random_per_op_layouts_match_single_process(seed):
         plan["data_parallel_size_of_each_op"] = [[2 // t for t in tp]]
         plan["algo_of_each_op"] = [[rng.randint(0, 1) for _ in range(n)]]
         plan["resharding_stages"] = [True]
+        rc, cur = [], rng.randint(0, 1)          # and its own recompute flag, in runs of random length
+        while len(rc) < n:
+            rc += [cur] * rng.randint(1, 7)
+            cur = 1 - cur
+        plan["recompute_ops"] = [rc[:n]]
         plans.append(plan)
     run_ranks(_fuzz_worker, 2, plans, _base(), timeout=600)
 
