@@ -47,3 +47,25 @@ def test_generation_on_a_tiny_gpt_learns_a_repeating_pattern():
     # sampling with a tiny nucleus equals greedy decoding
     same = generate(t, [[5, 6, 7]], max_new_tokens=4, top_p=1e-4, vocab_size=64)
     assert same[0] == out[0][:7]
+
+
+def _tp_logits_worker(rank, world, plan, want):
+    t = Trainer(plan, rank=rank, world_size=world, model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0,
+                                                                        max_tp=2), device="cpu")
+    ids = gpt_batch(4, 32, 64, seed=3)["ids"]
+    got = t.logits(ids)
+    assert got.shape == want.shape and float((got.float() - want.float()).abs().max()) < 2e-2
+    out = generate(t, [[5, 6, 7]], max_new_tokens=3, greedy=True, vocab_size=64)
+    assert len(out[0]) == 6
+
+
+def test_logits_and_generation_under_tensor_parallelism():
+    """The vocabulary-parallel LM head gathers its logit shards: two ranks give the single-process logits."""
+    import sys, os
+    sys.path.insert(0, os.path.dirname(__file__))
+    from dist_utils import run_ranks
+    kw = dict(layers=2, seq=32, hidden=64, heads=2, head_dim=32, vocab=64, global_bs=4, micro_bs=4)
+    single = Trainer(tiny_gpt_plan(**kw), model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2),
+                     device="cpu")
+    want = single.logits(gpt_batch(4, 32, 64, seed=3)["ids"])
+    run_ranks(_tp_logits_worker, 2, tiny_gpt_plan(**kw, num_gpus=(2,), tp=[2]), want)
