@@ -139,3 +139,25 @@ def test_interleaved_plans_with_random_cuts_match_single_process():
     run_ranks(_fuzz_worker, 4, [p for p in plans if p["micro_batch_size"] == 2], want, timeout=600)
     single3 = tiny_gpt_plan(**{**KW, "micro_bs": 3})
     run_ranks(_fuzz_worker, 4, [p for p in plans if p["micro_batch_size"] == 3], _losses(single3), timeout=600)
+
+
+def _t5_losses(plan, rank=0, world=1):
+    from superscaler_b200.data import synthetic as syn
+    t = Trainer(plan, rank=rank, world_size=world, model_overrides=NODROP, lr_warmup_steps=0, device="cpu", lr=1e-3)
+    b = syn.t5_batch(8, 64, 32, 256, seed=1)
+    return [t.loss_value(t.train_step(b)) for _ in range(2)]
+
+
+def _t5_worker(rank, world, plan, want):
+    got = _t5_losses(plan, rank, world)
+    assert max(abs(a - b) for a, b in zip(got, want)) < 5e-3, (rank, got, want, plan["num_ops_in_each_stage"])
+
+
+def test_interleaved_t5_matches_single_process():
+    """T5 with two chunks per stage and uneven cuts on 2 x 2 tensor-parallel ranks: the encoder output rides through
+    the virtual stages, also across the wrap-around from the last physical stage back to the first."""
+    from helpers import tiny_t5_plan
+    base = tiny_t5_plan(num_gpus=(2, 2), tp=[2, 2], recompute=1, global_bs=8, micro_bs=2)
+    n = sum(base["num_ops_in_each_stage"])
+    plan = interleave_plan(base, 2, [9, 14, 17, n - 40])
+    run_ranks(_t5_worker, 4, plan, _t5_losses(tiny_t5_plan(global_bs=8, micro_bs=2)))
