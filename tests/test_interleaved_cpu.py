@@ -159,5 +159,5 @@ def test_interleaved_t5_matches_single_process():
     from helpers import tiny_t5_plan
     base = tiny_t5_plan(num_gpus=(2, 2), tp=[2, 2], recompute=1, global_bs=8, micro_bs=2)
     n = sum(base["num_ops_in_each_stage"])
-    plan = interleave_plan(base, 2, [9, 14, 17, n - 40])
+    plan = interleave_plan(base, 2, [9, 14, 6, n - 29])
     run_ranks(_t5_worker, 4, plan, _t5_losses(tiny_t5_plan(global_bs=8, micro_bs=2)))
