@@ -55,14 +55,26 @@ def _local_names(trainer) -> Dict[str, str]:
     return out
 
 
-def save_checkpoint(trainer, root: str, iteration: Optional[int] = None) -> Optional[str]:
-    it = trainer.iteration if iteration is None else iteration
+def _shard_of(trainer):
+    """(does this rank write, shard number in the directory name).  A stage whose ops all use one tensor-parallel
+    degree is written by the data-parallel rank 0 of every tensor-parallel rank, as in the reference
+    (runtime/megatron/checkpointing.py:121).  In a stage that mixes degrees a rank can hold the only copy of one
+    op's shard while being a replica for another op, so every rank writes, numbered by its position in the stage."""
     ps = trainer.pstate
     first = trainer.infos[0]
     pl = ps.placement(first.tp, first.dp)
+    if len({i.tp for i in trainer.infos}) == 1:
+        return pl.dp_rank == 0, pl.tp_rank
+    return True, ps.local_rank_in_stage
+
+
+def save_checkpoint(trainer, root: str, iteration: Optional[int] = None) -> Optional[str]:
+    it = trainer.iteration if iteration is None else iteration
+    ps = trainer.pstate
+    writes, shard = _shard_of(trainer)
     path = None
-    if pl.dp_rank == 0:
-        d = checkpoint_dir(root, it, pl.tp_rank, ps.stage, ps.num_stages)
+    if writes:
+        d = checkpoint_dir(root, it, shard, ps.stage, ps.num_stages)
         os.makedirs(d, exist_ok=True)
         names = _local_names(trainer)
         model = {names[k]: v.cpu() for k, v in trainer.store.state_dict().items()}
@@ -107,9 +119,8 @@ def load_checkpoint(trainer, root: str, load_optim: bool = True, load_rng: bool 
     if it is None:
         return 0
     ps = trainer.pstate
-    first = trainer.infos[0]
-    pl = ps.placement(first.tp, first.dp)
-    path = os.path.join(checkpoint_dir(root, it, pl.tp_rank, ps.stage, ps.num_stages), "model_optim_rng.pt")
+    _, shard = _shard_of(trainer)
+    path = os.path.join(checkpoint_dir(root, it, shard, ps.stage, ps.num_stages), "model_optim_rng.pt")
     sd = _load_file(path)
     if sd.get("plan") is not None and sd["plan"]["num_ops_in_each_stage"] != trainer.plan["num_ops_in_each_stage"]:
         raise RuntimeError("checkpoint was written under a different stage split; use load_under_plan()")

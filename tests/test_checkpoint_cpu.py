@@ -189,3 +189,44 @@ def test_one_rank_checkpoint_loads_under_parallel_plans(tmp_path, model, kw, wor
     ck.save_checkpoint(ref, root)
     want = ref.loss_value(ref.train_step(batch_fn(9)))
     run_ranks(_load_worker, world, model, kw, root, want)
+
+
+def _mixed_plan(first_tp):
+    plan = tiny_gpt_plan(num_gpus=(2,), tp=[2])
+    n = plan["num_ops_in_each_stage"][0]
+    tp = [first_tp] * 10 + [3 - first_tp] * (n - 10)
+    plan["model_parallel_size_of_each_op"] = [tp]
+    plan["data_parallel_size_of_each_op"] = [[2 // t for t in tp]]
+    plan["resharding_stages"] = [True]
+    return plan
+
+
+def _resume_worker(rank, world, plan, root):
+    ov = dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2)
+    a = Trainer(plan, rank=rank, world_size=world, device="cpu", lr_warmup_steps=0, lr=1e-3, model_overrides=ov)
+    for i in range(2):
+        a.train_step(gpt_batch(4, 128, 512, seed=i))
+    ck.save_checkpoint(a, root)
+    b = Trainer(plan, rank=rank, world_size=world, device="cpu", lr_warmup_steps=0, lr=1e-3, model_overrides=ov, seed=9)
+    assert ck.load_checkpoint(b, root) == 2
+    assert torch.equal(a.store.master, b.store.master)
+    la = a.loss_value(a.train_step(gpt_batch(4, 128, 512, seed=5)))
+    lb = b.loss_value(b.train_step(gpt_batch(4, 128, 512, seed=5)))
+    assert abs(la - lb) < 1e-6
+
+
+@pytest.mark.parametrize("first_tp", [1, 2])
+def test_checkpoint_of_a_stage_that_mixes_tensor_parallel_degrees(tmp_path, first_tp):
+    """Ops 0..9 on (tp, dp) = (1, 2) and the rest on (2, 1), or the other way round: every rank holds the only copy
+    of some shard, so every rank writes; the same plan resumes exactly and one rank reloads the merged weights."""
+    from dist_utils import run_ranks
+    root = str(tmp_path / "ckpt")
+    run_ranks(_resume_worker, 2, _mixed_plan(first_tp), root)
+    ov = dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2)
+    ref = Trainer(tiny_gpt_plan(), device="cpu", lr_warmup_steps=0, lr=1e-3, model_overrides=ov)
+    for i in range(2):
+        ref.train_step(gpt_batch(4, 128, 512, seed=i))
+    got = Trainer(tiny_gpt_plan(), device="cpu", lr_warmup_steps=0, lr=1e-3, model_overrides=ov, seed=77)
+    assert ck.load_under_plan(got, root) == 2
+    batch = gpt_batch(4, 128, 512, seed=9)
+    assert abs(ref.loss_value(ref.train_step(batch)) - got.loss_value(got.train_step(batch))) < 2e-2
