@@ -88,6 +88,11 @@ class BatchNormFn(torch.autograd.Function):
             mean = xf.mean(0)
             var = xf.var(0, unbiased=False)
             rstd = torch.rsqrt(var + eps)
+            if run_mean is not None:
+                # same update as the kernel (and torch.nn.BatchNorm2d): unbiased variance into the running estimate
+                n = xf.shape[0]
+                run_mean.mul_(1.0 - momentum).add_(mean, alpha=momentum)
+                run_var.mul_(1.0 - momentum).add_(var * (n / max(n - 1, 1)), alpha=momentum)
             y = (xf - mean) * rstd * gamma.float() + beta.float()
             if r2 is not None:
                 y = y + r2.float()

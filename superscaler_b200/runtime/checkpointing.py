@@ -55,6 +55,18 @@ def _local_names(trainer) -> Dict[str, str]:
     return out
 
 
+def _buffers(trainer) -> Dict[str, torch.Tensor]:
+    """Non-parameter state of the ops (BatchNorm running statistics), keyed like the parameters of their op."""
+    lo = trainer.stage_bounds[trainer.pstate.stage][0]
+    out = {}
+    for op in trainer.stage.raw_ops:
+        for owner in (op, getattr(op, "bn_op", None)):
+            if owner is not None and getattr(owner, "run_mean", None) is not None:
+                base = f"language_model.ops.{owner.info.index - lo}.{owner.key}"
+                out[base + ".running_mean"], out[base + ".running_var"] = owner.run_mean, owner.run_var
+    return out
+
+
 def _shard_of(trainer):
     """(does this rank write, shard number in the directory name).  A stage whose ops all use one tensor-parallel
     degree is written by the data-parallel rank 0 of every tensor-parallel rank, as in the reference
@@ -90,6 +102,7 @@ def save_checkpoint(trainer, root: str, iteration: Optional[int] = None) -> Opti
             "np_rng_state": np.random.get_state(),
             "torch_rng_state": torch.get_rng_state(),
             "rng_tracker_states": {"dropout_seed_state": F.seed_state().get_state()},
+            "buffers": {k: v.cpu().clone() for k, v in _buffers(trainer).items()},
             "plan": trainer.plan,
             "op_names": {i: trainer.op_names[i] for i in trainer.owned_op_indices()},
             "param_specs": {names[s.name]: {"full_shape": s.full_shape, "shard_dim": s.shard_dim, "tp": s.tp,
@@ -126,6 +139,16 @@ def load_checkpoint(trainer, root: str, load_optim: bool = True, load_rng: bool 
         raise RuntimeError("checkpoint was written under a different stage split; use load_under_plan()")
     names = _local_names(trainer)
     trainer.store.load_state_dict({k: sd["model"][names[k]] for k in trainer.store.params})
+    saved = sd.get("buffers", {})
+    if saved:
+        # running statistics exist once an op has run: one forward under no_grad creates them, then they are filled
+        for op in trainer.stage.raw_ops:
+            for owner in (op, getattr(op, "bn_op", None)):
+                if owner is not None and hasattr(owner, "_buffers"):
+                    owner._buffers(trainer.device)
+        for k, v in _buffers(trainer).items():
+            if k in saved:
+                v.copy_(saved[k].to(v.device))
     if finetune or it == "release":
         trainer.iteration = 0
         return 0

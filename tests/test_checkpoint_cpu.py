@@ -230,3 +230,21 @@ def test_checkpoint_of_a_stage_that_mixes_tensor_parallel_degrees(tmp_path, firs
     assert ck.load_under_plan(got, root) == 2
     batch = gpt_batch(4, 128, 512, seed=9)
     assert abs(ref.loss_value(ref.train_step(batch)) - got.loss_value(got.train_step(batch))) < 2e-2
+
+
+def test_batchnorm_running_statistics_travel_with_the_checkpoint(tmp_path):
+    from superscaler_b200.data.synthetic import resnet_batch
+    from helpers import tiny_resnet_plan
+    ov = dict(image_size=64, num_classes=16)
+    a = Trainer(tiny_resnet_plan(global_bs=8, micro_bs=4), device="cpu", lr_warmup_steps=0, model_overrides=ov)
+    for i in range(2):
+        a.train_step(resnet_batch(8, 64, 16, seed=i, dtype=torch.float32))
+    ck.save_checkpoint(a, str(tmp_path))
+    b = Trainer(tiny_resnet_plan(global_bs=8, micro_bs=4), device="cpu", lr_warmup_steps=0, model_overrides=ov, seed=3)
+    assert ck.load_checkpoint(b, str(tmp_path)) == 2
+    stats_a, stats_b = ck._buffers(a), ck._buffers(b)
+    assert len(stats_a) >= 2 * 13 and stats_a.keys() == stats_b.keys()       # 12 block BNs + stem (+ downsample BNs)
+    assert any("downsample.bn.running_mean" in k for k in stats_a)
+    for k in stats_a:
+        assert torch.equal(stats_a[k], stats_b[k]), k
+    assert any(float(v.abs().sum()) > 0 for k, v in stats_a.items() if k.endswith("running_mean"))
