@@ -158,3 +158,15 @@ def test_extrapolated_tables_scale_by_the_hidden_size_and_drive_a_search(tmp_pat
         plan = json.load(f)
     _validate_plan(plan)
     assert sum(plan["num_gpus"]) == 8 and res[0] < 100000             # no missing-table penalty in the price
+
+
+def test_every_golden_plan_passes_the_trainers_shape_checks():
+    from superscaler_b200.runtime.trainer import _validate_plan
+    import glob
+    files = sorted(glob.glob(f"{GOLD}/*stages.json"))
+    assert len(files) == 12
+    for f in files:
+        with open(f) as fh:
+            plan = json.load(fh)
+        _validate_plan(plan)
+        assert plan["global_batch_size"] % plan["micro_batch_size"] == 0, f
