@@ -161,3 +161,15 @@ def test_interleaved_t5_matches_single_process():
     n = sum(base["num_ops_in_each_stage"])
     plan = interleave_plan(base, 2, [9, 14, 6, n - 29])
     run_ranks(_t5_worker, 4, plan, _t5_losses(tiny_t5_plan(global_bs=8, micro_bs=2)))
+
+
+def test_interleaved_wide_resnet_matches_single_process():
+    """Wide-ResNet with three chunks per stage and uneven cuts (inside bottleneck blocks, so the residual rides over
+    the boundaries) on two pipeline ranks, every block recomputed."""
+    import test_parallel_cpu as PP
+    from helpers import tiny_resnet_plan
+    plan_fn = lambda **kw: tiny_resnet_plan(global_bs=16, micro_bs=4, **kw)
+    base = plan_fn(num_gpus=(1, 1), recompute=1)
+    n = sum(base["num_ops_in_each_stage"])
+    plan = interleave_plan(base, 3, [3, 6, 9, 5, 8, n - 31])
+    run_ranks(PP._resnet_fuzz_worker, 2, [plan], PP._other_model_losses("resnet", plan_fn(), steps=2), timeout=600)
