@@ -44,9 +44,12 @@ class Env:
 
     def tp_context(self, pl: OpPlacement, local_bs: int):
         """Symmetric scratch for the fused GEMM + all-reduce kernel of this op's tensor-parallel group, or None
-        when the NCCL path is to be used (tp == 1, CPU tensors, or fused communication switched off).  Created
+        when the NCCL path is to be used (tp == 1, CPU tensors, a group that spans nodes and so cannot map peer
+        memory, or fused communication switched off).  Created
         on first use; all ranks of the group reach that point together because they execute the same plan."""
         if not self.fused_comm or pl.tp == 1 or self.store.device.type != "cuda":
+            return None
+        if not self.pstate.same_node(pl.tp_ranks):
             return None
         key = tuple(pl.tp_ranks)
         ctx = self.tp_contexts.get(key)

@@ -44,6 +44,13 @@ class ParallelState:
         s = self.stage_start[stage]
         return list(range(s, s + self.num_gpus[stage]))
 
+    def same_node(self, ranks: Sequence[int]) -> bool:
+        """True when `ranks` all run on one node, i.e. can map each other's memory over NVLink.  The launcher places
+        LOCAL_WORLD_SIZE consecutive ranks on every node (torchrun's contract); without it the job is one node."""
+        import os
+        per_node = int(os.environ.get("LOCAL_WORLD_SIZE", "0")) or self.world_size
+        return len({r // per_node for r in ranks}) <= 1
+
     def is_first_stage(self) -> bool:
         return self.stage == 0
 

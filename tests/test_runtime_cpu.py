@@ -170,3 +170,17 @@ def test_random_per_op_recompute_flags_do_not_change_training():
             plan["recompute_ops"] = [rc]
             got = losses(plan)
             assert max(abs(a - b) for a, b in zip(got, base)) < tol, (name, trial, got, base, rc)
+
+
+def test_peer_memory_groups_must_sit_on_one_node(monkeypatch):
+    """Rank sets that cross a node boundary (LOCAL_WORLD_SIZE consecutive ranks per node) cannot use the peer-memory
+    kernels; without the launcher's variable the whole job counts as one node."""
+    from superscaler_b200.parallel.state import ParallelState
+    ps = ParallelState([8, 8], rank=5, world_size=16)
+    monkeypatch.delenv("LOCAL_WORLD_SIZE", raising=False)
+    assert ps.same_node(range(16))
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")
+    assert ps.same_node((0, 1, 2, 3)) and ps.same_node(range(8, 16)) and ps.same_node((12,))
+    assert not ps.same_node((6, 7, 8, 9)) and not ps.same_node((0, 8))
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "4")
+    assert not ps.same_node(range(8)) and ps.same_node((4, 5, 6, 7))
