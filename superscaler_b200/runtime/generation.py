@@ -4,8 +4,8 @@ Counterpart of the reference's sampling utilities (runtime/megatron/text_generat
 sample_sequence_batch, generate_samples_*).  The op-list model has no key / value cache (neither have the
 reference's flex ops), so every new token re-runs the causal forward over the whole window of `seq_length`
 positions: prompts are right-padded, and because attention is causal the padding cannot influence the position
-that is read.  Runs single-stage plans (one GPU, or a tensor-parallel group in which every rank calls generate
-with the same arguments and seed).
+that is read.  Runs every plan `Trainer.logits` runs (one GPU, tensor / data parallel groups, pipelines); every rank
+calls generate with the same arguments and seed and returns the same sequences.
 """
 from __future__ import annotations
 

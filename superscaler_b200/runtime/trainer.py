@@ -243,20 +243,59 @@ class Trainer:
 
     @torch.no_grad()
     def logits(self, ids: torch.Tensor) -> torch.Tensor:
-        """Inference forward of a single-stage GPT plan: token ids [b, seq_length] -> logits [b, seq_length,
-        padded vocabulary].  Dropout is off; nothing is kept for a backward pass."""
-        assert self.pstate.num_stages == 1, "logits() runs single-stage plans (tensor / data parallel or 1 GPU)"
+        """Inference forward of a GPT plan (one stage or a pipeline, any per-op tensor / data parallel layout; not
+        interleaved): token ids [b, seq_length] -> logits [b, seq_length, padded vocabulary] on every rank.  Every
+        rank passes the same ids.  Rows are split over the data-parallel ranks like a micro-batch (b is padded to a
+        multiple of the data-parallel degrees and cut again), the stages hand the activations on once, and the last
+        stage shares the logits with the others.  Dropout is off; nothing is kept for a backward pass."""
+        import math
+        from ..parallel import mappings as M
+        from .schedules import Boundary, _run_batch
+        assert self.interleave == 1, "logits() does not run interleaved plans; reload the checkpoint under a plain one"
+        ps = self.pstate
+        b, s = ids.shape
+        mult = math.lcm(*(d for stage in self.plan["data_parallel_size_of_each_op"] for d in stage))
+        total = -(-b // mult) * mult
+        if total != b:
+            ids = torch.cat([ids, ids.new_zeros(total - b, s)])
+        prev = Boundary(self, ps.stage - 1) if ps.stage > 0 else None
+        nxt = Boundary(self, ps.stage) if ps.stage < ps.num_stages - 1 else None
         was = self.env.training
         self.env.training = False
+        out = None
         try:
-            st: Dict[str, Any] = {"ids": ids.to(self.device)}
+            st: Dict[str, Any] = {}
             if self.world_size > 1:
                 st["_meta"] = {}
+            if prev is None:
+                st["ids"] = ids[self.local_rows(self.infos[0], total)].to(self.device)
+            else:
+                prev.handshake_recv()
+                ops, assemble = prev.forward_ops(None, None)
+                _run_batch(ops)
+                tensors, sides = assemble()
+                st.update(tensors)
+                st["_meta"].update(sides)
             self.stage.forward(st)
+            if nxt is not None:
+                sent = {k: st[k] for k in nxt.keys}
+                sides = {k: st["_meta"][k] for k in nxt.keys}
+                nxt.handshake_send(sent, sides)
+                _run_batch(nxt.forward_ops(sent, sides)[0])
+            else:
+                last = self.infos[-1]
+                pl = ps.placement(last.tp, last.dp)
+                out = M.gather_from_group(st["logits"], 0, ps.group(pl.dp_ranks)).contiguous()
         finally:
             self.env.training = was
-        b, s = ids.shape
-        return st["logits"].view(b, s, -1)
+        if ps.num_stages > 1:
+            src = ps.stage_start[-1]
+            head = [(tuple(out.shape), out.dtype) if ps.rank == src else None]
+            dist.broadcast_object_list(head, src)
+            if out is None:
+                out = torch.empty(head[0][0], dtype=head[0][1], device=self.device)
+            dist.broadcast(out, src)
+        return out.view(total, s, -1)[:b]
 
     @torch.no_grad()
     def evaluate(self, batches) -> Dict[str, float]:

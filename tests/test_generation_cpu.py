@@ -69,3 +69,35 @@ def test_logits_and_generation_under_tensor_parallelism():
                      device="cpu")
     want = single.logits(gpt_batch(4, 32, 64, seed=3)["ids"])
     run_ranks(_tp_logits_worker, 2, tiny_gpt_plan(**kw, num_gpus=(2,), tp=[2]), want)
+
+
+def _plans_logits_worker(rank, world, plans, want, want_gen):
+    for plan in plans:
+        t = Trainer(plan, rank=rank, world_size=world, model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0,
+                                                                            max_tp=2), device="cpu")
+        got = t.logits(gpt_batch(4, 32, 64, seed=3)["ids"])
+        assert got.shape == want.shape and float((got.float() - want.float()).abs().max()) < 2e-2, (rank, plan)
+        # one prompt: fewer rows than data-parallel ranks, padded inside logits()
+        assert generate(t, [[5, 6, 7]], max_new_tokens=3, greedy=True, vocab_size=64) == want_gen, (rank, plan)
+
+
+def test_logits_and_generation_under_pipeline_and_data_parallel_plans():
+    """Every rank of a pipeline / data-parallel / mixed-layout plan gets the single-process logits and continues a
+    prompt with the same tokens."""
+    import sys, os
+    sys.path.insert(0, os.path.dirname(__file__))
+    from dist_utils import run_ranks
+    kw = dict(layers=2, seq=32, hidden=64, heads=2, head_dim=32, vocab=64, global_bs=4, micro_bs=4)
+    single = Trainer(tiny_gpt_plan(**kw), model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2),
+                     device="cpu")
+    want = single.logits(gpt_batch(4, 32, 64, seed=3)["ids"])
+    want_gen = generate(single, [[5, 6, 7]], max_new_tokens=3, greedy=True, vocab_size=64)
+    mixed = tiny_gpt_plan(**kw, num_gpus=(2,), tp=[2])
+    n = mixed["num_ops_in_each_stage"][0]
+    tp = [1] * 12 + [2] * (n - 12)          # data parallel first, tensor parallel (and a sharded LM head) after
+    mixed.update(model_parallel_size_of_each_op=[tp], data_parallel_size_of_each_op=[[2 // t for t in tp]],
+                 resharding_stages=[True])
+    run_ranks(_plans_logits_worker, 2, [tiny_gpt_plan(**kw, num_gpus=(2,), tp=[1]), tiny_gpt_plan(**kw, num_gpus=(1, 1)),
+                                        mixed], want, want_gen)
+    run_ranks(_plans_logits_worker, 4, [tiny_gpt_plan(**kw, num_gpus=(2, 2), tp=[1, 2]),
+                                        tiny_gpt_plan(**kw, num_gpus=(1, 2, 1), tp=[1, 1, 1])], want, want_gen)
