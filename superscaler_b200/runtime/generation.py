@@ -77,3 +77,74 @@ def generate_text(trainer, tokenizer, texts: Sequence[str], max_new_tokens: int,
     out = generate(trainer, [tokenizer.tokenize(t) for t in texts], max_new_tokens, eod=eod,
                    vocab_size=tokenizer.vocab_size, **kw)
     return [tokenizer.detokenize([i for i in s if i != eod]) for s in out]
+
+
+def main(argv=None) -> None:
+    """Command line (counterpart of the reference's tools/generate_samples_gpt.py + runtime/megatron/
+    text_generation_utils.py: generate_samples_input_from_file / generate_and_write_samples_unconditional):
+
+        python [-m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1] \\
+            -m superscaler_b200.runtime.generation --flexpipe-config plan.json --load ckpt/ \\
+            --vocab-file vocab.json --merge-file merges.txt --prompt "The capital of France is" \\
+            [--sample-input-file prompts.txt] [--sample-output-file out.txt] [--num-samples 4] \\
+            --out-seq-length 64 [--greedy | --temperature 0.9 --top_k 40 --top_p 0.9]
+
+    Prompts come from --prompt (repeatable), from the lines of --sample-input-file, or -- with --num-samples alone
+    -- are the end-of-document token (unconditional samples).  The checkpoint may have been written under another
+    plan of the same model.  Rank 0 prints (and writes) the texts."""
+    import argparse
+    import json
+
+    from ..parallel.state import init_distributed
+    from ..tokenizer import build_tokenizer
+    from . import checkpointing
+    from .trainer import Trainer
+    ap = argparse.ArgumentParser(description=main.__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--flexpipe-config", required=True)
+    ap.add_argument("--load", default=None, help="checkpoint directory (default: random weights)")
+    ap.add_argument("--tokenizer-type", default="GPT2BPETokenizer")
+    ap.add_argument("--vocab-file", required=True)
+    ap.add_argument("--merge-file", default=None)
+    ap.add_argument("--prompt", action="append", default=[])
+    ap.add_argument("--sample-input-file", default=None)
+    ap.add_argument("--sample-output-file", default=None)
+    ap.add_argument("--num-samples", type=int, default=0, help="unconditional samples when no prompt is given")
+    ap.add_argument("--out-seq-length", type=int, default=64, help="new tokens per sample")
+    ap.add_argument("--temperature", type=float, default=1.0)
+    ap.add_argument("--top_k", "--top-k", type=int, default=0)
+    ap.add_argument("--top_p", "--top-p", type=float, default=0.0)
+    ap.add_argument("--greedy", action="store_true")
+    ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--distributed-backend", default=None, choices=[None, "nccl", "gloo"])
+    args, _ = ap.parse_known_args(argv)
+    rank, world, _ = init_distributed(args.distributed_backend)
+    with open(args.flexpipe_config) as f:
+        plan = json.load(f)
+    trainer = Trainer(plan, rank=rank, world_size=world, seed=args.seed,
+                      model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0))
+    if args.load:
+        checkpointing.load_under_plan(trainer, args.load)
+    tok = build_tokenizer(args.tokenizer_type, args.vocab_file, args.merge_file)
+    assert tok.vocab_size <= trainer.cfg.padded_vocab, "the tokenizer has more entries than the model's embedding table"
+    texts = list(args.prompt)
+    if args.sample_input_file:
+        with open(args.sample_input_file) as f:
+            texts += [line.rstrip("\n") for line in f if line.strip()]
+    kw = dict(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, greedy=args.greedy, seed=args.seed)
+    if texts:
+        outs = generate_text(trainer, tok, texts, args.out_seq_length, **kw)
+    else:
+        assert args.num_samples > 0, "give --prompt, --sample-input-file or --num-samples"
+        seqs = generate(trainer, [[tok.eod]] * args.num_samples, args.out_seq_length, eod=None,
+                        vocab_size=tok.vocab_size, **kw)
+        outs = [tok.detokenize([i for i in s[1:] if i != tok.eod]) for s in seqs]
+    if rank == 0:
+        for i, o in enumerate(outs):
+            print(f"--- sample {i} ---\n{o}", flush=True)
+        if args.sample_output_file:
+            with open(args.sample_output_file, "w") as f:
+                f.write(json.dumps(outs, indent=1))
+
+
+if __name__ == "__main__":
+    main()

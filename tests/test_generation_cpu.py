@@ -101,3 +101,28 @@ def test_logits_and_generation_under_pipeline_and_data_parallel_plans():
                                         mixed], want, want_gen)
     run_ranks(_plans_logits_worker, 4, [tiny_gpt_plan(**kw, num_gpus=(2, 2), tp=[1, 2]),
                                         tiny_gpt_plan(**kw, num_gpus=(1, 2, 1), tp=[1, 1, 1])], want, want_gen)
+
+
+def test_generation_command_line(tmp_path, capsys):
+    """Prompts from flags and from a file, then unconditional samples, through the tiny byte-level BPE vocabulary."""
+    import json
+    import sys, os
+    sys.path.insert(0, os.path.dirname(__file__))
+    from test_tokenizer_cpu import _bpe_files
+    from superscaler_b200.runtime import generation
+    vf, mf, vocab, _ = _bpe_files(tmp_path)
+    plan = tmp_path / "plan.json"
+    plan.write_text(json.dumps(tiny_gpt_plan(layers=1, seq=32, hidden=64, heads=2, head_dim=32, vocab=384,
+                                             global_bs=2, micro_bs=2)))
+    (tmp_path / "prompts.txt").write_text("newer\n\nlow low\n")
+    out = tmp_path / "out.json"
+    generation.main(["--flexpipe-config", str(plan), "--vocab-file", vf, "--merge-file", mf, "--prompt", "lower new",
+                     "--sample-input-file", str(tmp_path / "prompts.txt"), "--sample-output-file", str(out),
+                     "--out-seq-length", "4", "--top_k", "5", "--temperature", "0.8"])
+    texts = json.loads(out.read_text())
+    assert len(texts) == 3 and texts[0].startswith("lower new") and texts[1].startswith("newer")
+    assert texts[2].startswith("low low") and "--- sample 2 ---" in capsys.readouterr().out
+    generation.main(["--flexpipe-config", str(plan), "--vocab-file", vf, "--merge-file", mf, "--num-samples", "2",
+                     "--out-seq-length", "3", "--greedy", "--sample-output-file", str(out)])
+    texts = json.loads(out.read_text())
+    assert len(texts) == 2 and texts[0] == texts[1]
