@@ -173,3 +173,43 @@ def test_restart_on_fewer_ranks_from_a_checkpoint_of_another_plan(tmp_path, caps
     # weights carried over: the resumed run is where the uninterrupted one was, not back at the initial loss
     # (optimizer moments restart, so the match is close, not exact)
     assert abs(resumed[0] - scratch[4]) < 0.05 * scratch[4] and resumed[0] < scratch[0] - 0.1
+
+
+def _cli_train_logged(rank, world, port, argv, log):
+    import contextlib
+    with open(f"{log}.{rank}", "w") as f, contextlib.redirect_stdout(f):
+        _cli_train(rank, world, port, argv)
+
+
+def test_interleaved_cli_run_resumes_exactly(tmp_path):
+    """`--interleave-factor 2` on two pipeline ranks: a run stopped after 2 of 4 iterations and resumed from its
+    checkpoint (weights of both chunks, optimizer state, schedule) prints the losses of the uninterrupted run."""
+    import json
+    import re
+    import torch.multiprocessing as mp
+    from dist_utils import _free_port
+    plan = tmp_path / "gpt_tiny_pp2.json"
+    plan.write_text(json.dumps(tiny_gpt_plan(num_gpus=(1, 1), micro_bs=1)))
+    common = ["--flexpipe-config", str(plan), "--distributed-backend", "gloo", "--interleave-factor", "2",
+              "--lr-decay-iters", "100", "--lr", "1e-3", "--lr-warmup-fraction", "0", "--hidden-dropout", "0",
+              "--attention-dropout", "0"]
+    ctx = mp.get_context("spawn")
+
+    def launch(name, extra):
+        port = _free_port()
+        log = str(tmp_path / name)
+        procs = [ctx.Process(target=_cli_train_logged, args=(r, 2, port, common + extra, log)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(180)
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+        text = open(log + ".0").read() + open(log + ".1").read()
+        return [float(x) for x in re.findall(r"lm loss: ([0-9.E+-]+)", text)]
+
+    whole = launch("whole", ["--train-iters", "4"])
+    ckpt = str(tmp_path / "ckpt")
+    first = launch("first", ["--train-iters", "2", "--save", ckpt])
+    second = launch("second", ["--train-iters", "4", "--load", ckpt])
+    assert len(whole) == 4 and first == whole[:2] and len(second) == 2
+    assert max(abs(a - b) for a, b in zip(second, whole[2:])) < 1e-4, (second, whole)
