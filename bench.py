@@ -124,8 +124,19 @@ def describe_parallelism(plan: dict) -> str:
 
 
 def run_reference(args):
+    """The unmodified reference on the same metric and config; rank 0 prints the one JSON line."""
     from baseline import reference_arm
-    print(json.dumps(reference_arm.run(args)), flush=True)
+    rank = int(os.environ.get("RANK", "0"))
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    out = reference_arm.run(args)
+    if sampler:
+        clocks = sampler.stop()
+        if "unavailable" not in out:
+            out["clocks"] = clocks
+    if rank == 0:
+        print(json.dumps(out), flush=True)
 
 
 def main():

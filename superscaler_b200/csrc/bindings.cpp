@@ -74,6 +74,8 @@ int bn_fwd_launch(const void* x, const void* residual, const float* gamma, const
 int bn_bwd_launch(const void* dy, const void* x, const void* y, const float* mean, const float* rstd,
                   const float* gamma, void* dx, void* dres, float* dgamma, float* dbeta, float* part, float* sums,
                   int accumulate, long long rows, int C, int relu, int num_sms, cudaStream_t stream);
+int bn_apply_launch(const void* x, const void* residual, const float* mean, const float* rstd, const float* gamma,
+                    const float* beta, void* y, long long rows, int C, int relu, int num_sms, cudaStream_t stream);
 int maxpool_fwd_launch(const void* x, void* y, void* idx, int N, int H, int W, int C, int num_sms, cudaStream_t stream);
 int maxpool_bwd_launch(const void* dy, const void* idx, void* dx, int N, int H, int W, int C, int num_sms,
                        cudaStream_t stream);
@@ -494,6 +496,21 @@ std::vector<Tensor> bn_fwd(const Tensor& x, const OptTensor& residual, const Ten
   return {y, mean, rstd};
 }
 
+// Inference BatchNorm: normalises with the given per-channel mean / rstd (fp32 [C]); returns y.
+Tensor bn_apply(const Tensor& x, const OptTensor& residual, const Tensor& mean, const Tensor& rstd, const Tensor& gamma,
+                const Tensor& beta, bool relu) {
+  check_bf16_2d(x, "x");
+  TORCH_CHECK(x.is_contiguous() && gamma.scalar_type() == torch::kFloat32 && beta.scalar_type() == torch::kFloat32 &&
+              mean.scalar_type() == torch::kFloat32 && rstd.scalar_type() == torch::kFloat32 &&
+              mean.numel() == x.size(1) && rstd.numel() == x.size(1));
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  check_launch(ssb::bn_apply_launch(x.data_ptr(), opt_ptr(residual), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                                    gamma.data_ptr<float>(), beta.data_ptr<float>(), y.data_ptr(), x.size(0),
+                                    static_cast<int>(x.size(1)), relu, num_sms(), cur_stream()), "bn_apply");
+  return y;
+}
+
 // Returns (dx, dresidual or undefined); dgamma / dbeta are written (or accumulated) in place.
 std::vector<Tensor> bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, const Tensor& mean, const Tensor& rstd,
                            const Tensor& gamma, Tensor& dgamma, Tensor& dbeta, bool accumulate, bool relu,
@@ -686,6 +703,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("subsample", &subsample);
   m.def("bn_fwd", &bn_fwd);
   m.def("bn_bwd", &bn_bwd);
+  m.def("bn_apply", &bn_apply);
   m.def("maxpool_fwd", &maxpool_fwd);
   m.def("maxpool_bwd", &maxpool_bwd);
   m.def("avgpool", &avgpool);

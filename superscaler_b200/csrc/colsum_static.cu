@@ -5,6 +5,8 @@
 #include <mutex>
 
 #include "colsum_static.h"
+
+#include <cstdint>
 #include "common.cuh"
 
 namespace ssb {
@@ -83,6 +85,10 @@ extern "C" int ssb_colsum_bf16_static(const void* a, long long lda, float* out, 
                                       void* stream) {
   if (a == nullptr || out == nullptr || rows < 1 || n < 2 || (n & 1) || (lda & 1) || lda < n)
     return SSB_COLSUM_STATIC_E_BAD_ARG;
+  // the partial kernel reads `a` two bf16 values at a time and both kernels access `out` / the scratch as floats:
+  // a pointer off a 4-byte boundary would be a misaligned-address fault on the device, so it is refused here
+  if ((reinterpret_cast<uintptr_t>(a) & 3u) || (reinterpret_cast<uintptr_t>(out) & 3u))
+    return SSB_COLSUM_STATIC_E_BAD_ARG;
   if (n > SSB_COLSUM_STATIC_MAX_N) return SSB_COLSUM_STATIC_E_TOO_LARGE;
   const int slices = ssb::ln_bwd_slices(rows);
   if (slices > SSB_COLSUM_STATIC_MAX_SLICES) return SSB_COLSUM_STATIC_E_TOO_LARGE;
@@ -99,8 +105,8 @@ extern "C" int ssb_colsum_bf16_static(const void* a, long long lda, float* out, 
 extern "C" const char* ssb_colsum_static_strerror(int code) {
   switch (code) {
     case SSB_COLSUM_STATIC_OK: return "ok";
-    case SSB_COLSUM_STATIC_E_BAD_ARG: return "bad argument: null pointer, rows < 1, n < 2, odd n or lda, or lda < n";
-    case SSB_COLSUM_STATIC_E_TOO_LARGE: return "n exceeds SSB_COLSUM_STATIC_MAX_N (8192): the fixed scratch array is too small";
+    case SSB_COLSUM_STATIC_E_BAD_ARG: return "bad argument: null pointer, `a` or `out` not 4-byte aligned, rows < 1, n < 2, odd n or lda, or lda < n";
+    case SSB_COLSUM_STATIC_E_TOO_LARGE: return "n exceeds SSB_COLSUM_STATIC_MAX_N (8192) or the row slices exceed SSB_COLSUM_STATIC_MAX_SLICES (128): the fixed scratch array is too small";
     case SSB_COLSUM_STATIC_E_SETUP: return "could not look up the scratch array on the current device";
     case SSB_COLSUM_STATIC_E_LAUNCH: return "kernel launch rejected";
     default: return "unknown code";

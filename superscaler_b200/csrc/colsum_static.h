@@ -12,6 +12,8 @@
 //   out[j] (+)= sum over r < rows of a[r * lda + j],   j < n,  `a` bf16 on the device, `out` fp32 on the device.
 //
 // Limits and rules:
+//   * `a` and `out` must be 4-byte aligned (`a` is read two bf16 values at a time): a bf16 view that starts on an odd
+//     element is refused with SSB_COLSUM_STATIC_E_BAD_ARG and nothing is launched.
 //   * n must be even, at most SSB_COLSUM_STATIC_MAX_N (8192); lda must be even and >= n; rows >= 1.  Larger sizes
 //     are refused with SSB_COLSUM_STATIC_E_TOO_LARGE and nothing is launched.  The array holds
 //     128 x 8192 floats = 4 MiB per device.
@@ -34,7 +36,7 @@ extern "C" {
 #define SSB_COLSUM_STATIC_MAX_SLICES 128
 
 #define SSB_COLSUM_STATIC_OK 0
-#define SSB_COLSUM_STATIC_E_BAD_ARG 1     /* null pointer, rows < 1, n < 2, odd n or lda, lda < n */
+#define SSB_COLSUM_STATIC_E_BAD_ARG 1     /* null or misaligned pointer, rows < 1, n < 2, odd n or lda, lda < n */
 #define SSB_COLSUM_STATIC_E_TOO_LARGE 2   /* n > SSB_COLSUM_STATIC_MAX_N */
 #define SSB_COLSUM_STATIC_E_SETUP 3       /* the address lookup of the scratch array failed on this device */
 #define SSB_COLSUM_STATIC_E_LAUNCH 4      /* a kernel launch was rejected */

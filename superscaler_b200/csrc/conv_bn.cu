@@ -459,6 +459,17 @@ int bn_fwd_launch(const void* x, const void* residual, const float* gamma, const
   return static_cast<int>(cudaGetLastError());
 }
 
+// y = [relu](gamma * (x - mean) * rstd + beta [+ residual]) with GIVEN per-channel statistics (inference: the running
+// estimates); no statistics pass, nothing updated.
+int bn_apply_launch(const void* x, const void* residual, const float* mean, const float* rstd, const float* gamma,
+                    const float* beta, void* y, long long rows, int C, int relu, int num_sms, cudaStream_t stream) {
+  if (C % 8) return -3;
+  bn_apply_kernel<<<grid_for(rows * (C / 8), num_sms), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(residual), mean, rstd, gamma,
+      beta, reinterpret_cast<__nv_bfloat16*>(y), rows, C, relu);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // sums: scratch of 2 * C floats; part as above.
 int bn_bwd_launch(const void* dy, const void* x, const void* y, const float* mean, const float* rstd,
                   const float* gamma, void* dx, void* dres, float* dgamma, float* dbeta, float* part, float* sums,

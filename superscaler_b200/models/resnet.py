@@ -119,6 +119,10 @@ class BNOp(Op):
     def apply(self, x, residual=None, relu=None):
         c = self.env.cfg
         rm, rv = self._buffers(x.device)
+        if not self.env.training:
+            # evaluation: running statistics, buffers untouched (torch.nn.BatchNorm2d.eval() in the reference)
+            return C.batch_norm_inference(x, self.p(f"{self.key}.weight"), self.p(f"{self.key}.bias"), rm, rv,
+                                          residual, c.bn_eps, self.relu if relu is None else relu)
         return C.batch_norm(x, self.p(f"{self.key}.weight"), self.p(f"{self.key}.bias"), residual, rm, rv, c.bn_eps,
                             c.bn_momentum, self.relu if relu is None else relu)
 

@@ -320,10 +320,16 @@ class LMHeadLossOp(Op):
             return
         labels = st["labels"]
         mask = st.get("loss_mask")
-        ntok = labels.numel()
-        scale = st.get("loss_scale", 1.0) / ntok
-        st["loss"] = F.lm_head_cross_entropy(x, self.p("word_embeddings.weight"), labels,
-                                             mask.reshape(-1).float() if mask is not None else None,
+        scale = st.get("loss_scale", 1.0)
+        if mask is None:
+            weights, scale = None, scale / labels.numel()
+        else:
+            # masked mean as the reference's loss_func (runtime/pretrain_gpt.py:64-72, pretrain_t5.py:88-99):
+            # sum(loss * mask) / mask.sum() over this rank's rows; the division rides in the per-row weights so
+            # that no count has to be read back to the host
+            m = mask.reshape(-1).float()
+            weights = m / m.sum().clamp(min=1.0)
+        st["loss"] = F.lm_head_cross_entropy(x, self.p("word_embeddings.weight"), labels, weights,
                                              self.pl.tp_rank * self.v_local, scale, self.tp_group)
 
 

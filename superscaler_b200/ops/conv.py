@@ -134,6 +134,26 @@ def batch_norm(x, gamma, beta, residual=None, run_mean=None, run_var=None, eps=1
     return BatchNormFn.apply(x, residual, gamma, beta, run_mean, run_var, eps, momentum, relu)
 
 
+@torch.no_grad()
+def batch_norm_inference(x, gamma, beta, run_mean, run_var, residual=None, eps=1e-5, relu=False):
+    """Evaluation-mode BatchNorm as torch.nn.BatchNorm2d.eval(): normalises with the running estimates and leaves
+    them untouched (the reference evaluates with torch's module, runtime/megatron/model/flex_ops.py:1561-1600)."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    r2 = residual.reshape(-1, shape[-1]).contiguous() if residual is not None else None
+    rstd = torch.rsqrt(run_var.float() + eps)
+    if x.is_cuda:
+        y = native.ext().bn_apply(x2.contiguous(), r2, run_mean, rstd, gamma, beta, relu)
+    else:
+        y = (x2.float() - run_mean) * rstd * gamma.float() + beta.float()
+        if r2 is not None:
+            y = y + r2.float()
+        if relu:
+            y = torch.relu(y)
+        y = y.to(x.dtype)
+    return y.view(shape)
+
+
 class MaxPool3x3s2Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x):

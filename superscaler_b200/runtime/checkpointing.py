@@ -83,6 +83,8 @@ def _shard_of(trainer):
 def save_checkpoint(trainer, root: str, iteration: Optional[int] = None) -> Optional[str]:
     it = trainer.iteration if iteration is None else iteration
     ps = trainer.pstate
+    if hasattr(trainer, "check_device_status"):
+        trainer.check_device_status()        # never write weights that a timed-out kernel may have corrupted
     writes, shard = _shard_of(trainer)
     path = None
     if writes:

@@ -13,7 +13,9 @@ failure turns into a `PeerFailure` exception on the survivors instead of a hang.
             trainer.train_step(batch)
 
 The device side has the matching property: every kernel that waits on another GPU gives up after a bounded time and
-reports `kStatusPeerTimeout` in the status word (`ops/native.py::check_status`), see csrc/comm_sm100.cu.
+reports `kStatusPeerTimeout` in the status word (`ops/native.py::check_status`), see csrc/comm_sm100.cu.  The trainer
+reads that word wherever the host synchronises anyway (`Trainer.loss_value`, `save_checkpoint`) and raises
+`DeviceStatusError`, publishing the failure through the attached monitor (`trainer.health_monitor`).
 """
 from __future__ import annotations
 
@@ -26,6 +28,14 @@ class PeerFailure(RuntimeError):
     def __init__(self, rank: int, reason: str):
         super().__init__(f"rank {rank}: {reason}")
         self.rank, self.reason = rank, reason
+
+
+class DeviceStatusError(RuntimeError):
+    """A kernel of this rank returned from a bounded wait without its data (status word != 0)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"device status {code}: {message}")
+        self.code = code
 
 
 class DictStore:

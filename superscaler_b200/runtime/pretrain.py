@@ -145,6 +145,7 @@ def main(argv=None) -> None:
     if args.health_check and world > 1:
         from .health import HealthMonitor, store_from_env
         monitor = HealthMonitor(store_from_env(rank, world), rank, world, stale_after_s=args.health_stale_after_s)
+        trainer.health_monitor = monitor     # a device status error is published to the peers before it is raised
     fail_rank, fail_iter = (int(x) for x in args.inject_failure.split(":")) if args.inject_failure else (-1, -1)
     writer = None
     if args.tensorboard_dir and rank == world - 1:
@@ -156,15 +157,16 @@ def main(argv=None) -> None:
                 else make_batch_fn(trainer))
     # synthetic batches are generated on the host before the loop (a pool of up to 4, reused in turn): building
     # a 768-image batch takes longer than a training step and is not part of what an iteration measures
-    pool = [] if args.data_path else \
-        [batch_fn(i) for i in range(trainer.iteration, min(args.train_iters, trainer.iteration + 4))]
+    # batch of iteration `it` is batch_fn(it % 4) whether the run is fresh or resumed, so a resumed run sees the
+    # batches the uninterrupted run would have seen
+    pool = {} if args.data_path else \
+        {i % 4: batch_fn(i % 4) for i in range(trainer.iteration, min(args.train_iters, trainer.iteration + 4))}
     timers = Timers(trainer.device.type == "cuda")
     config_name = os.path.splitext(os.path.basename(args.flexpipe_config))[0]
     regions = ["iteration", "forward-backward", "backward-params-all-reduce", "optimizer"]
-    pool_start = trainer.iteration
     def one_step(it):
         timers("iteration").start()
-        batch = trainer.to_device(batch_fn(it) if args.data_path else pool[(it - pool_start) % len(pool)])
+        batch = trainer.to_device(batch_fn(it) if args.data_path else pool[it % 4])
         timers("forward-backward").start()
         loss = trainer.forward_backward(batch)
         trainer._fold_autograd_grads()
@@ -175,8 +177,9 @@ def main(argv=None) -> None:
             trainer._tied.sync_grads()
         timers("backward-params-all-reduce").stop()
         timers("optimizer").start()
-        lr = trainer.lr_schedule.step()
+        lr = trainer.lr_schedule.get_lr()
         trainer.optimizer.step(lr=lr)
+        trainer.lr_schedule.step()
         trainer.iteration += 1
         timers("optimizer").stop()
         timers("iteration").stop()

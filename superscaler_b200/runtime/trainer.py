@@ -223,13 +223,42 @@ class Trainer:
         self.optimizer.reduce_gradients()
         if self._tied is not None:
             self._tied.sync_grads()
-        lr = self.lr_schedule.step()
-        self.optimizer.step(lr=lr)
+        lr = self.lr_schedule.get_lr()          # the reference steps its scheduler after the update
+        self.optimizer.step(lr=lr)              # (runtime/megatron/training.py:735-742): update k uses lr(k)
+        self.lr_schedule.step()
         self.iteration += 1
         return {"loss_tensor": loss, "lr": lr, "iteration": self.iteration}
 
+    def _read_device_status(self) -> int:
+        """The kernels' status word of this device (0 = every bounded wait completed).  Synchronises."""
+        from ..ops import native
+        if self.device.type != "cuda" or not native.available():
+            return 0
+        code = native.check_status()
+        if code:
+            native.ext().status().zero_()
+        return code
+
+    def check_device_status(self) -> None:
+        """Raises DeviceStatusError when a kernel of this rank gave up a bounded wait since the last check: the data
+        of that call (reduced gradients, a fused GEMM's output) is undefined, so the weights must not be trusted or
+        saved.  Called where the host synchronises anyway: `loss_value` and `save_checkpoint`.  With a
+        `health_monitor` attached the failure is published to the other ranks before the exception leaves."""
+        code = self._read_device_status()
+        if code == 0:
+            return
+        from .health import DeviceStatusError, device_status_message
+        err = DeviceStatusError(code, f"iteration {self.iteration}: {device_status_message(code)}; the results of "
+                                      "that kernel are undefined, later weights are not to be saved")
+        monitor = getattr(self, "health_monitor", None)
+        if monitor is not None:
+            monitor.publish_failure(f"DeviceStatusError: {err}")
+        raise err
+
     def loss_value(self, stats: Dict[str, Any]) -> float:
-        """Host read of the iteration loss (synchronises); averaged over the last stage's DP group."""
+        """Host read of the iteration loss (synchronises); averaged over the last stage's DP group.  Also reads
+        the kernels' status word and raises if a bounded wait ran out."""
+        self.check_device_status()
         t = stats["loss_tensor"].clone()
         if self.world_size > 1:
             last = len(self.stage_bounds) - 1

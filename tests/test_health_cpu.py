@@ -213,3 +213,33 @@ def test_interleaved_cli_run_resumes_exactly(tmp_path):
     second = launch("second", ["--train-iters", "4", "--load", ckpt])
     assert len(whole) == 4 and first == whole[:2] and len(second) == 2
     assert max(abs(a - b) for a, b in zip(second, whole[2:])) < 1e-4, (second, whole)
+
+
+def test_device_status_word_stops_training_and_saving(tmp_path):
+    """A kernel that gave up a bounded wait leaves a status word behind; the trainer reads it where the host
+    synchronises anyway (loss read-back, checkpoint save), raises, and tells the other ranks through the monitor."""
+    import pytest
+    from helpers import tiny_gpt_plan
+    from superscaler_b200.data.synthetic import gpt_batch
+    from superscaler_b200.runtime import checkpointing
+    from superscaler_b200.runtime.health import DeviceStatusError, DictStore, HealthMonitor, PeerFailure
+    from superscaler_b200.runtime.trainer import Trainer
+    plan = tiny_gpt_plan()
+    t = Trainer(plan, lr_warmup_steps=0, device="cpu",
+                model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=1))
+    stats = t.train_step(gpt_batch(plan["global_batch_size"], plan["seq_length"], 512, seed=1))
+    assert t.loss_value(stats) > 0                       # status 0: nothing happens
+    store = DictStore()
+    t.health_monitor = HealthMonitor(store, rank=0, world=2)
+    codes = iter([2, 2])
+    t._read_device_status = lambda: next(codes, 0)       # what a timed-out peer wait would leave in the status word
+    with pytest.raises(DeviceStatusError) as e:
+        t.loss_value(stats)
+    assert e.value.code == 2 and "peer" in str(e.value)
+    with pytest.raises(DeviceStatusError):
+        checkpointing.save_checkpoint(t, str(tmp_path))
+    assert not any(tmp_path.iterdir())                   # nothing was written
+    with pytest.raises(PeerFailure):                     # the other rank learns of it before its next collective
+        HealthMonitor(store, rank=1, world=2).check_peers()
+    checkpointing.save_checkpoint(t, str(tmp_path))      # status read and cleared: saving works again
+    assert any(tmp_path.iterdir())

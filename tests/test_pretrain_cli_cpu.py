@@ -101,3 +101,20 @@ def test_throughput_table(tmp_path, capsys):
     out = capsys.readouterr().out.splitlines()
     assert out[2].startswith("| a_2stages_x | 2 | 110.0 | 72.73 | 1001 |")
     assert out[3].startswith("| b_1stages_x | 1 | 50.0 | 160.00 | 1000 |")
+
+
+def test_synthetic_run_resumed_past_iteration_four_sees_the_same_batches(tmp_path, capsys):
+    """The synthetic batch of iteration k is the same in a fresh run and in one resumed at any iteration: seven
+    iterations in one go print the losses of five iterations plus two after a restart."""
+    import re
+    plan_path = tmp_path / "gpt_tiny_1stages_resume.json"
+    plan_path.write_text(json.dumps(tiny_gpt_plan()))
+    common = ["--flexpipe-config", str(plan_path), "--lr-decay-iters", "20", "--hidden-dropout", "0",
+              "--attention-dropout", "0", "--lr", "1e-3"]
+    pretrain.main(common + ["--train-iters", "7"])
+    whole = re.findall(r"lm loss: ([0-9.E+-]+)", capsys.readouterr().out)
+    pretrain.main(common + ["--train-iters", "5", "--save", str(tmp_path / "ckpt")])
+    first = re.findall(r"lm loss: ([0-9.E+-]+)", capsys.readouterr().out)
+    pretrain.main(common + ["--train-iters", "7", "--load", str(tmp_path / "ckpt")])
+    second = re.findall(r"lm loss: ([0-9.E+-]+)", capsys.readouterr().out)
+    assert len(whole) == 7 and first + second == whole

@@ -184,3 +184,40 @@ def test_peer_memory_groups_must_sit_on_one_node(monkeypatch):
     assert not ps.same_node((6, 7, 8, 9)) and not ps.same_node((0, 8))
     monkeypatch.setenv("LOCAL_WORLD_SIZE", "4")
     assert not ps.same_node(range(8)) and ps.same_node((4, 5, 6, 7))
+
+
+def test_masked_lm_loss_is_mean_over_unmasked_tokens():
+    """The loss of a batch with a loss mask is the mean cross entropy of the unmasked tokens only, and so are its
+    gradients (reference: runtime/pretrain_gpt.py:64-72)."""
+    from superscaler_b200.ops import functional as F
+    torch.manual_seed(3)
+    tokens, hidden, vocab = 24, 16, 40
+    x = torch.randn(tokens, hidden, requires_grad=True)
+    w = torch.randn(vocab, hidden, requires_grad=True)
+    labels = torch.randint(0, vocab, (tokens,))
+    mask = (torch.rand(tokens) < 0.4).float()
+    mask[0] = 1.0
+    weights = mask / mask.sum().clamp(min=1.0)
+    loss = F.lm_head_cross_entropy(x, w, labels, weights, 0, 1.0, None)
+    loss.backward()
+    x2, w2 = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    keep = mask.bool()
+    ref = torch.nn.functional.cross_entropy((x2 @ w2.t())[keep], labels[keep])
+    ref.backward()
+    # the CPU restatement of the GEMM rounds its result like the bf16 kernel does
+    assert abs(loss.item() - ref.item()) < 2e-2
+    assert torch.allclose(x.grad, x2.grad, atol=2e-2) and torch.allclose(w.grad, w2.grad, atol=2e-2)
+    unmasked = torch.nn.functional.cross_entropy(x2 @ w2.t(), labels)
+    assert abs(loss.item() - unmasked.item()) > 5e-2          # and it is not the mean over all tokens
+
+    # through the trainer: a half-masked batch reports the mean over its unmasked half, not half of it
+    plan = tiny_gpt_plan(global_bs=2, micro_bs=2)
+    t = Trainer(plan, model_overrides=NODROP, lr_warmup_steps=0, device="cpu")
+    batch = gpt_batch(2, plan["seq_length"], 512, seed=1)
+    full = t.evaluate([dict(batch)])["lm loss"]
+    batch["loss_mask"] = torch.ones_like(batch["labels"], dtype=torch.float32)
+    ones = t.evaluate([dict(batch)])["lm loss"]
+    batch["loss_mask"][:, ::2] = 0.0
+    half = t.evaluate([dict(batch)])["lm loss"]
+    assert abs(full - ones) < 1e-4
+    assert abs(half - ones) < 0.5 and half > 0.7 * ones

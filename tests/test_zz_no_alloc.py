@@ -54,4 +54,11 @@ def test_static_colsum_rejects_oversize_and_bad_arguments():
     assert b"8192" in lib.ssb_colsum_static_strerror(2)
     assert fn(a.data_ptr(), 16, out.data_ptr(), 0, 8, 15, None) == 1           # odd n
     assert fn(None, 16, out.data_ptr(), 0, 8, 16, None) == 1
+    # a view that starts on an odd bf16 element (2-byte aligned) or an `out` off a 4-byte boundary: refused on the
+    # host, nothing launched, `out` untouched
+    out.fill_(5.0)
+    assert fn(a.data_ptr() + 2, 16, out.data_ptr(), 0, 7, 14, None) == 1
+    assert fn(a.data_ptr(), 16, out.data_ptr() + 2, 0, 8, 14, None) == 1
+    assert b"aligned" in lib.ssb_colsum_static_strerror(1)
     torch.cuda.synchronize()
+    assert bool((out == 5.0).all())
