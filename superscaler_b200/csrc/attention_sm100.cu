@@ -17,8 +17,7 @@
 //   dK/dV   : CTA = 128 keys; query blocks of 64; S^T = K.Q^T and dP^T = V.dO^T double-buffered,
 //             dV += P^T.dO and dK += dS^T.Q accumulate in TMEM.
 //   dQ      : CTA = 128 queries; key blocks of 64; dQ += dS.K accumulates in TMEM.
-#include "attention_sm100.cuh"
-#include "common.cuh"
+#include "attention_device.cuh"
 
 namespace ssb {
 
@@ -27,73 +26,7 @@ int make_tma_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
 
 namespace {
 
-constexpr int kMathThreads = 512;               // 4 column groups x 4 warps
-constexpr int kAttnThreads = 64 + kMathThreads;  // + TMA warp + MMA warp
-constexpr float kLog2e = 1.4426950408889634f;
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t fmix32(uint32_t x) {
-  x ^= x >> 16;
-  x *= 0x85EBCA6Bu;
-  x ^= x >> 13;
-  x *= 0xC2B2AE35u;
-  x ^= x >> 16;
-  return x;
-}
-// Dropout mask: one 32-bit hash decides the four keys 4g .. 4g+3 of query q; key 4g+i is kept when byte i of the
-// hash is below keep8 = round(256 (1 - p)).  The dropout probability is therefore quantised to 1/256 (the scale
-// applied to the kept values is the exact 256 / keep8), which makes the mask four times cheaper to generate than
-// one 16-bit lane per element.
-__device__ __forceinline__ uint32_t attn_quad_hash(uint32_t bh_seed, uint32_t q, uint32_t quads_per_row, uint32_t quad) {
-  return fmix32((q * quads_per_row + quad) * 0x9E3779B1u + bh_seed);
-}
-__device__ __forceinline__ bool keep_byte(uint32_t h, int i, uint32_t keep8) { return ((h >> (8 * i)) & 0xFFu) < keep8; }
-__host__ __device__ __forceinline__ uint32_t dropout_keep8(float p) {
-  const int k = static_cast<int>((1.0f - p) * 256.0f + 0.5f);
-  return static_cast<uint32_t>(k < 1 ? 1 : (k > 256 ? 256 : k));
-}
-
-// Writes 32 consecutive bf16 columns (16 packed words) of row r into a [rows][128 B] swizzled chunk.
-// piece0 = index of the first 16-byte piece inside the 128-byte row (0 or 4).
-__device__ __forceinline__ void store_row32_sw128(uint8_t* chunk, int r, int piece0, const uint32_t (&w)[16]) {
-  uint8_t* row = chunk + r * 128;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int piece = (piece0 + i) ^ (r & 7);
-    *reinterpret_cast<uint4*>(row + piece * 16) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-  }
-}
-
-// Writes 16 consecutive bf16 columns (8 packed words) of row r; piece0 = first 16-byte piece (even).
-__device__ __forceinline__ void store_row16_sw128(uint8_t* chunk, int r, int piece0, const uint32_t (&w)[8]) {
-  uint8_t* row = chunk + r * 128;
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int piece = (piece0 + i) ^ (r & 7);
-    *reinterpret_cast<uint4*>(row + piece * 16) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-  }
-}
-
-// Bounded wait whose outcome is the same for every lane of the warp, so that the warp-collective
-// tcgen05.ld that follows is never executed by a part of the warp only.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
-}
-
-struct Pipe {
-  int stage = 0;
-  uint32_t phase = 0;
-  __device__ __forceinline__ void advance(int n) {
-    if (++stage == n) {
-      stage = 0;
-      phase ^= 1;
-    }
-  }
-};
+using namespace attn;
 
 // =============================================================================================
 //                                         FORWARD
@@ -114,12 +47,6 @@ struct FwdCfg {
   static constexpr int kSmem = kTile * 5 + kPBytes + kXBytes + 1024 + 256;
   static constexpr int kTmemCols = 512;  // S0 [0,128) S1 [128,256) O0 [256,256+HD) O1 [384,384+HD)
 };
-
-template <int N>
-__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
-  if constexpr (N == 32) tmem_ld_32x32(taddr, r);
-  else tmem_ld_32x16(taddr, r);
-}
 
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -278,7 +205,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t keep8 = dropout_keep8(p.dropout_p);
     const float inv_keep = p.dropout_p > 0.f ? 256.0f / static_cast<float>(keep8) : 1.0f;  // applied once, to O
     const uint32_t bh_seed = static_cast<uint32_t>(hash64(p.dropout_seed, static_cast<uint64_t>(b) * p.NH + head));
-    const uint32_t quads_per_row = (p.SK + 3) >> 2;
+    const uint32_t qquads = (p.SQ + 3) >> 2;
+    const int sub = lane & 3;  // position of this query in its quad: lanes 4t .. 4t+3 share the hashes of a key
     float m = -INFINITY, l = 0.f, alpha_pending = 1.f;
     float o[OC];
 #pragma unroll
@@ -331,6 +259,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const float mc = m_use * c;
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t w[16];
+      // each lane of a query quad hashes 8 of the 32 keys of this step (key = kv0 + 4 jj + sub); the quad exchanges them
+      uint32_t hq[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+      if (p.dropout_p > 0.f) {
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) hq[jj] = attn_col_hash(bh_seed, kv0 + 4 * jj + sub, qquads, q >> 2);
+      }
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
         float pe[4];
@@ -340,9 +274,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           rs4[e] += pe[e];                                   // four partial sums: no 32-long dependent chain
         }
         if (p.dropout_p > 0.f) {
-          const uint32_t h = attn_quad_hash(bh_seed, q, quads_per_row, (kv0 + i) >> 2);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) pe[e] = keep_byte(h, e, keep8) ? pe[e] : 0.f;
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t h = __shfl_sync(0xffffffffu, hq[i >> 2], (lane & ~3) | e);  // hash of key kv0 + i + e
+            pe[e] = keep_byte(h, sub, keep8) ? pe[e] : 0.f;
+          }
         }
         w[i >> 1] = pack_bf16x2(pe[0], pe[1]);
         w[(i >> 1) + 1] = pack_bf16x2(pe[2], pe[3]);
@@ -583,11 +519,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t keep8 = dropout_keep8(p.dropout_p);
     const float inv_keep = p.dropout_p > 0.f ? 256.0f / static_cast<float>(keep8) : 1.0f;
     const uint32_t bh_seed = static_cast<uint32_t>(hash64(p.dropout_seed, static_cast<uint64_t>(b) * p.NH + head));
-    const uint32_t quads_per_row = (p.SK + 3) >> 2;
+    const uint32_t qquads = (p.SQ + 3) >> 2;
     const float* lse_row = p.LSE + (static_cast<size_t>(b) * p.NH + head) * p.SQ;
     const float* delta_row = p.delta + (static_cast<size_t>(b) * p.NH + head) * p.SQ;
     const bool kv_ok = kv < kv_len;
-    const int sub = lane & 3;  // position of this key in its quad: lanes 4t .. 4t+3 share the hash of (query, quad)
     const bool stats_vec = (p.SQ & 3) == 0;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
@@ -622,11 +557,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tmem_ld_32x16(tmem_base + lane_addr + 128 + st * 64 + g * 16, rp);
       tmem_ld_wait();
       uint32_t wp[8], wd[8];
-      // dropout: each lane of a quad hashes 4 of the 16 queries (query index = 4 j + sub), the quad exchanges them
+      // dropout: this key's hashes of the four query quads of the step
       uint32_t hq[4] = {0u, 0u, 0u, 0u};
       if (p.dropout_p > 0.f) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) hq[j] = attn_quad_hash(bh_seed, qbase + 4 * j + sub, quads_per_row, kv >> 2);
+        for (int j = 0; j < 4; ++j) hq[j] = attn_col_hash(bh_seed, kv, qquads, (qbase >> 2) + j);
       }
 #pragma unroll
       for (int i = 0; i < 16; i += 2) {
@@ -637,9 +572,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           float dp = __uint_as_float(rp[i + e]);
           float pd = pr;
           if (p.dropout_p > 0.f) {
-            // hash of query i + e: held by the lane of this quad whose sub equals (i + e) & 3
-            const uint32_t h = __shfl_sync(0xffffffffu, hq[(i + e) >> 2], (lane & ~3) | ((i + e) & 3));
-            const bool keep = keep_byte(h, sub, keep8);
+            const bool keep = keep_byte(hq[(i + e) >> 2], (i + e) & 3, keep8);
             pd = keep ? pr : 0.f;                  // unscaled: dV is multiplied by 256 / keep8 once, at the end
             dp = keep ? dp * inv_keep : 0.f;
           }
@@ -885,7 +818,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t keep8 = dropout_keep8(p.dropout_p);
     const float inv_keep = p.dropout_p > 0.f ? 256.0f / static_cast<float>(keep8) : 1.0f;
     const uint32_t bh_seed = static_cast<uint32_t>(hash64(p.dropout_seed, static_cast<uint64_t>(b) * p.NH + head));
-    const uint32_t quads_per_row = (p.SK + 3) >> 2;
+    const uint32_t qquads = (p.SQ + 3) >> 2;
+    const int sub = lane & 3;  // position of this query in its quad
     const bool q_ok = q < p.SQ;
     const size_t stat_idx = (static_cast<size_t>(b) * p.NH + head) * p.SQ + (q_ok ? q : 0);
     const float lse2 = p.LSE[stat_idx] * kLog2e;
@@ -903,17 +837,24 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tmem_ld_32x16(tmem_base + lane_addr + 128 + st * 64 + g * 16, rp);
       tmem_ld_wait();
       uint32_t wd[8];
+      // each lane of a query quad hashes 4 of the 16 keys of this step (key = kvb + 4 j + sub); the quad exchanges them
+      uint32_t hq[4] = {0u, 0u, 0u, 0u};
+      if (p.dropout_p > 0.f) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) hq[j] = attn_col_hash(bh_seed, kvb + 4 * j + sub, qquads, q >> 2);
+      }
 #pragma unroll
       for (int i = 0; i < 16; i += 4) {
         const int kv = kvb + i;
-        uint32_t h = 0;
-        if (p.dropout_p > 0.f) h = attn_quad_hash(bh_seed, q, quads_per_row, kv >> 2);
         float dsv[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float pr = ex2(__uint_as_float(rs[i + e]) * c - lse2);
           float dp = __uint_as_float(rp[i + e]);
-          if (p.dropout_p > 0.f) dp = keep_byte(h, e, keep8) ? dp * inv_keep : 0.f;
+          if (p.dropout_p > 0.f) {
+            const uint32_t h = __shfl_sync(0xffffffffu, hq[i >> 2], (lane & ~3) | e);  // hash of key kv + e
+            dp = keep_byte(h, sub, keep8) ? dp * inv_keep : 0.f;
+          }
           dsv[e] = pr * (dp - delta) * p.scale;
         }
         if (need_mask) {
@@ -997,6 +938,15 @@ int set_smem(K kernel, int bytes) {
 
 }  // namespace
 
+// delta[b, h, q] = rowsum(dO * O), the first step of both backward paths.
+int attn_delta_launch(const AttnParams& p, const void* dout, int lddo, float* delta, cudaStream_t stream) {
+  const long long warps = static_cast<long long>(p.B) * p.SQ * p.NH;
+  attn_delta_kernel<<<static_cast<unsigned>((warps + 3) / 4), 128, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(p.O), p.ldo, p.o_col0, reinterpret_cast<const __nv_bfloat16*>(dout), lddo,
+      p.o_col0, delta, p.B, p.NH, p.SQ, p.HD);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // q/k/v: base pointers of the 2-D matrices that hold the heads (see AttnParams); ld in elements.
 int attn_fwd_launch(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const AttnParams& p,
                     cudaStream_t stream) {
@@ -1030,12 +980,7 @@ int attn_bwd_launch(const void* q, int ldq, const void* k, int ldk, const void* 
   if (p.causal && p.SQ != p.SK) return -2;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (lddo % 8) || (p.lddq % 8) || (p.lddk % 8) || (p.lddv % 8)) return -3;
   int rc;
-  {
-    const long long warps = static_cast<long long>(p.B) * p.SQ * p.NH;
-    attn_delta_kernel<<<static_cast<unsigned>((warps + 3) / 4), 128, 0, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(p.O), p.ldo, p.o_col0, reinterpret_cast<const __nv_bfloat16*>(dout),
-        lddo, p.o_col0, delta_scratch, p.B, p.NH, p.SQ, p.HD);
-  }
+  if ((rc = attn_delta_launch(p, dout, lddo, delta_scratch, stream))) return rc;
   AttnParams pp = p;
   pp.delta = delta_scratch;
   CUtensorMap tq64, tk128, tv128, tdo64, tq128, tk64, tv64, tdo128;

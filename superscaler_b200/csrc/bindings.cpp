@@ -57,6 +57,9 @@ int attn_fwd_launch(const void* q, int ldq, const void* k, int ldk, const void* 
                     cudaStream_t stream);
 int attn_bwd_launch(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const void* dout,
                     int lddo, const AttnParams& p, float* delta_scratch, cudaStream_t stream);
+long long attn_bwd_fused_scratch_floats(int B, int NH, int SQ, int HD);
+int attn_bwd_fused_launch(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const void* dout,
+                          int lddo, const AttnParams& p, float* scratch, cudaStream_t stream);
 int comm_max_blocks();
 void comm_set_peer_timeout_ns(unsigned long long ns);
 int allreduce_scale_f32_launch(void* const* peer_ptrs, void* mc_ptr, void* const* flag_ptrs, int rank, int world,
@@ -417,6 +420,10 @@ std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, 
   return {o, lse};
 }
 
+// false (default): the fused backward kernel, whose dQ is accumulated with floating-point reductions in arrival
+// order; true: the dK/dV + dQ kernel pair, bitwise reproducible.
+bool g_attn_bwd_deterministic = false;
+
 // dq, dk, dv are written into caller-provided 2-D matrices (same conventions as q, k, v).
 void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& lse, const Tensor& dout,
               Tensor& dq, Tensor& dk, Tensor& dv, int64_t B, int64_t NH, int64_t SQ, int64_t SK, int64_t HD,
@@ -433,6 +440,17 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   p.dQ = dq.data_ptr(); p.lddq = static_cast<int>(dq.stride(0)); p.dq_col0 = static_cast<int>(dq_col0);
   p.dK = dk.data_ptr(); p.lddk = static_cast<int>(dk.stride(0)); p.dk_col0 = static_cast<int>(dk_col0);
   p.dV = dv.data_ptr(); p.lddv = static_cast<int>(dv.stride(0)); p.dv_col0 = static_cast<int>(dv_col0);
+  if (!g_attn_bwd_deterministic) {
+    // one kernel, five tile products; dQ is summed over the key blocks in an fp32 scratch in arrival order
+    Tensor scratch = torch::empty({ssb::attn_bwd_fused_scratch_floats(B, NH, SQ, HD)},
+                                  torch::dtype(torch::kFloat32).device(q.device()));
+    check_launch(ssb::attn_bwd_fused_launch(q.data_ptr(), static_cast<int>(q.stride(0)), k.data_ptr(),
+                                            static_cast<int>(k.stride(0)), v.data_ptr(), static_cast<int>(v.stride(0)),
+                                            dout.data_ptr(), static_cast<int>(dout.stride(0)), p,
+                                            scratch.data_ptr<float>(), cur_stream()),
+                 "attn_bwd_fused");
+    return;
+  }
   Tensor delta = torch::empty({B, NH, SQ}, torch::dtype(torch::kFloat32).device(q.device()));
   check_launch(ssb::attn_bwd_launch(q.data_ptr(), static_cast<int>(q.stride(0)), k.data_ptr(), static_cast<int>(k.stride(0)),
                                     v.data_ptr(), static_cast<int>(v.stride(0)), dout.data_ptr(),
@@ -698,6 +716,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_finalize", &ce_finalize);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
+  m.def("set_attn_bwd_deterministic", [](bool on) { g_attn_bwd_deterministic = on; });
+  m.def("attn_bwd_deterministic", []() { return g_attn_bwd_deterministic; });
   m.def("im2col", &im2col);
   m.def("col2im", &col2im);
   m.def("subsample", &subsample);

@@ -114,10 +114,101 @@ allreduce_scale_f32_kernel(AllReduceArgs a) {
   block_barrier(a.flag_ptrs, a.rank, a.world, a.epoch + 1, a.status, a.limit_ns);
 }
 
+// Slice of rank r when n4 vectors of four floats are dealt out to `world` ranks: equal runs of an even number of
+// vectors (so that a slice of the matching bf16 buffer starts on a 16-byte boundary), the last one shorter.
+__host__ __device__ inline void slice_of(long long n4, int world, int rank, long long* lo, long long* hi) {
+  long long per = (n4 + world - 1) / world;
+  per += per & 1;
+  const long long a = rank * per, b = a + per;
+  *lo = a < n4 ? a : n4;
+  *hi = b < n4 ? b : n4;
+}
+
+// Reduce-scatter fused with the 1/dp scaling and with the sum of squares of the result: rank r sums slice r of
+// every peer's buffer (in the switch with a multicast mapping), writes it to its OWN buffer only, and leaves one
+// partial sum of squares per block in `partials` (folded by a second tiny kernel, so the norm does not depend on
+// the order of arrival).  After every rank has read what it needs (second barrier), the rest of the local buffer
+// is cleared: it is the gradient accumulator of the next iteration and its other slices are never looked at again.
+__global__ void __launch_bounds__(512)
+reduce_scatter_scale_sumsq_f32_kernel(AllReduceArgs a, float* __restrict__ partials) {
+  __shared__ float sm[16];
+  const bool ok = block_barrier(a.flag_ptrs, a.rank, a.world, a.epoch, a.status, a.limit_ns);
+  const long long n4 = a.n / 4;
+  long long lo, hi;
+  slice_of(n4, a.world, a.rank, &lo, &hi);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long first = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  float4* mine = reinterpret_cast<float4*>(a.peer_ptrs[a.rank]);
+  float acc = 0.f;
+  if (ok) {
+    if (a.mc_ptr != nullptr) {
+      for (long long i = lo + first; i < hi; i += stride) {
+        float4 v = multimem_ld_reduce_f32x4(a.mc_ptr + i * 4);
+        v.x *= a.scale; v.y *= a.scale; v.z *= a.scale; v.w *= a.scale;
+        mine[i] = v;
+        acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+    } else {
+      for (long long i = lo + first; i < hi; i += stride) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int p = 0; p < a.world; ++p) {
+          const float4 v = reinterpret_cast<const float4*>(a.peer_ptrs[p])[i];
+          s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        s.x *= a.scale; s.y *= a.scale; s.z *= a.scale; s.w *= a.scale;
+        mine[i] = s;
+        acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+      }
+    }
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? sm[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) partials[blockIdx.x] = t;
+  }
+  if (!ok) return;
+  // nobody reads this rank's buffer after the second barrier
+  if (!block_barrier(a.flag_ptrs, a.rank, a.world, a.epoch + 1, a.status, a.limit_ns)) return;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (long long i = first; i < lo; i += stride) mine[i] = zero;
+  for (long long i = hi + first; i < n4; i += stride) mine[i] = zero;
+}
+
+// All-gather of a buffer of 16-bit elements whose slice r (same split as above, in units of 8 elements) is final on
+// rank r: every rank writes its slice into every peer (one multicast store per 16 bytes with a multicast mapping).
+// The closing barrier tells every rank that all slices have landed.  No opening barrier: the callers' streams have
+// passed a barrier of the same group since anyone last read the destination.
+__global__ void __launch_bounds__(512)
+allgather_b16_kernel(AllReduceArgs a) {
+  const long long n8 = a.n / 8;  // a.n counts 16-bit elements here
+  long long lo, hi;
+  slice_of(n8, a.world, a.rank, &lo, &hi);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long first = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const float4* mine = reinterpret_cast<const float4*>(a.peer_ptrs[a.rank]);
+  if (a.mc_ptr != nullptr) {
+    for (long long i = lo + first; i < hi; i += stride) multimem_st_f32x4(a.mc_ptr + i * 4, mine[i]);
+  } else {
+    for (long long i = lo + first; i < hi; i += stride) {
+      const float4 v = mine[i];
+      for (int p = 0; p < a.world; ++p)
+        if (p != a.rank) reinterpret_cast<float4*>(a.peer_ptrs[p])[i] = v;
+    }
+  }
+  block_barrier(a.flag_ptrs, a.rank, a.world, a.epoch, a.status, a.limit_ns);
+}
+
 }  // namespace
 
 constexpr int kCommBlocks = 64;
 int comm_max_blocks() { return kCommBlocks; }
+
+void comm_slice_of(long long n_units, int world, int rank, long long* lo, long long* hi) {
+  slice_of(n_units, world, rank, lo, hi);
+}
 
 // Time a kernel waits for a peer before it records kStatusPeerTimeout and returns (process-wide; default 20 s).
 static uint64_t g_peer_limit_ns = kPeerTimeLimitNs;
@@ -135,6 +226,36 @@ int allreduce_scale_f32_launch(void* const* peer_ptrs, void* mc_ptr, void* const
   a.rank = rank; a.world = world; a.n = n; a.scale = scale; a.epoch = epoch; a.status = status;
   a.limit_ns = g_peer_limit_ns;
   allreduce_scale_f32_kernel<<<kCommBlocks, 512, 0, stream>>>(a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Reduce-scatter of a symmetric fp32 buffer (see the kernel); `partials` holds comm_max_blocks() floats.  Uses
+// epoch and epoch + 1.  n must be a multiple of 4.
+int reduce_scatter_scale_sumsq_f32_launch(void* const* peer_ptrs, void* mc_ptr, void* const* flag_ptrs, int rank,
+                                          int world, long long n, float scale, unsigned epoch, float* partials,
+                                          int* status, cudaStream_t stream) {
+  if (n % 4 || world < 1 || world > 32) return -2;
+  AllReduceArgs a;
+  a.peer_ptrs = reinterpret_cast<float* const*>(peer_ptrs);
+  a.mc_ptr = reinterpret_cast<float*>(mc_ptr);
+  a.flag_ptrs = reinterpret_cast<uint32_t* const*>(flag_ptrs);
+  a.rank = rank; a.world = world; a.n = n; a.scale = scale; a.epoch = epoch; a.status = status;
+  a.limit_ns = g_peer_limit_ns;
+  reduce_scatter_scale_sumsq_f32_kernel<<<kCommBlocks, 512, 0, stream>>>(a, partials);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// All-gather of a symmetric buffer of n 16-bit elements (n a multiple of 8).  Uses one epoch.
+int allgather_b16_launch(void* const* peer_ptrs, void* mc_ptr, void* const* flag_ptrs, int rank, int world,
+                         long long n, unsigned epoch, int* status, cudaStream_t stream) {
+  if (n % 8 || world < 1 || world > 32) return -2;
+  AllReduceArgs a;
+  a.peer_ptrs = reinterpret_cast<float* const*>(peer_ptrs);
+  a.mc_ptr = reinterpret_cast<float*>(mc_ptr);
+  a.flag_ptrs = reinterpret_cast<uint32_t* const*>(flag_ptrs);
+  a.rank = rank; a.world = world; a.n = n; a.scale = 1.f; a.epoch = epoch; a.status = status;
+  a.limit_ns = g_peer_limit_ns;
+  allgather_b16_kernel<<<kCommBlocks, 512, 0, stream>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
 
