@@ -64,6 +64,12 @@ int comm_max_blocks();
 void comm_set_peer_timeout_ns(unsigned long long ns);
 int allreduce_scale_f32_launch(void* const* peer_ptrs, void* mc_ptr, void* const* flag_ptrs, int rank, int world,
                                long long n, float scale, unsigned epoch, int* status, cudaStream_t stream);
+int reduce_scatter_scale_sumsq_f32_launch(void* const* peer_ptrs, void* mc_ptr, void* const* flag_ptrs, int rank,
+                                          int world, long long n, float scale, unsigned epoch, float* partials,
+                                          int* status, cudaStream_t stream);
+int allgather_b16_launch(void* const* peer_ptrs, void* mc_ptr, void* const* flag_ptrs, int rank, int world,
+                         long long n, unsigned epoch, int* status, cudaStream_t stream);
+void comm_slice_of(long long n_units, int world, int rank, long long* lo, long long* hi);
 int bn_slices(long long rows);
 int im2col_launch(const void* x, void* cols, int N, int H, int W, int C, int KH, int KW, int stride, int pad, int Kpad,
                   int num_sms, cudaStream_t stream);
@@ -598,6 +604,44 @@ void allreduce_scale_f32(const Tensor& peer_ptrs, int64_t mc_ptr, const Tensor& 
                "allreduce_scale_f32");
 }
 
+// Reduce-scatter of the first n elements of a symmetric fp32 buffer (sum over the ranks, times `scale`): rank r ends
+// up with slice r in its own buffer and the rest of its buffer cleared; `partials` [comm_max_blocks] receives per-block
+// sums of squares of the reduced slice.  `epoch` must advance by 2 per call on every rank.
+void reduce_scatter_scale_sumsq_f32(const Tensor& peer_ptrs, int64_t mc_ptr, const Tensor& flag_ptrs, int64_t rank,
+                                    int64_t world, int64_t n, double scale, int64_t epoch, Tensor& partials) {
+  TORCH_CHECK(peer_ptrs.is_cuda() && peer_ptrs.scalar_type() == torch::kInt64 && peer_ptrs.numel() == world);
+  TORCH_CHECK(flag_ptrs.is_cuda() && flag_ptrs.scalar_type() == torch::kInt64 && flag_ptrs.numel() == world);
+  TORCH_CHECK(partials.is_cuda() && partials.scalar_type() == torch::kFloat32 &&
+              partials.numel() >= ssb::comm_max_blocks());
+  c10::cuda::CUDAGuard guard(peer_ptrs.device());
+  check_launch(ssb::reduce_scatter_scale_sumsq_f32_launch(
+                   reinterpret_cast<void* const*>(peer_ptrs.data_ptr<int64_t>()), reinterpret_cast<void*>(mc_ptr),
+                   reinterpret_cast<void* const*>(flag_ptrs.data_ptr<int64_t>()), rank, world, n,
+                   static_cast<float>(scale), static_cast<unsigned>(epoch), partials.data_ptr<float>(),
+                   status_tensor().data_ptr<int>(), cur_stream()),
+               "reduce_scatter_scale_sumsq_f32");
+}
+
+// All-gather of the first n 16-bit elements of a symmetric buffer whose slice r is final on rank r.  One epoch per call.
+void allgather_b16(const Tensor& peer_ptrs, int64_t mc_ptr, const Tensor& flag_ptrs, int64_t rank, int64_t world,
+                   int64_t n, int64_t epoch) {
+  TORCH_CHECK(peer_ptrs.is_cuda() && peer_ptrs.scalar_type() == torch::kInt64 && peer_ptrs.numel() == world);
+  TORCH_CHECK(flag_ptrs.is_cuda() && flag_ptrs.scalar_type() == torch::kInt64 && flag_ptrs.numel() == world);
+  c10::cuda::CUDAGuard guard(peer_ptrs.device());
+  check_launch(ssb::allgather_b16_launch(reinterpret_cast<void* const*>(peer_ptrs.data_ptr<int64_t>()),
+                                         reinterpret_cast<void*>(mc_ptr),
+                                         reinterpret_cast<void* const*>(flag_ptrs.data_ptr<int64_t>()), rank, world, n,
+                                         static_cast<unsigned>(epoch), status_tensor().data_ptr<int>(), cur_stream()),
+               "allgather_b16");
+}
+
+// [lo, hi) in elements of rank `rank`'s slice of the first n elements (n a multiple of 8), as the two kernels split it.
+std::vector<int64_t> comm_slice(int64_t n, int64_t world, int64_t rank) {
+  long long lo = 0, hi = 0;
+  ssb::comm_slice_of(n / 8, static_cast<int>(world), static_cast<int>(rank), &lo, &hi);
+  return {lo * 8, hi * 8};
+}
+
 // out = bias / dropout / residual epilogue of the SUM over the tp ranks of (a . b^T), on every rank, in one kernel
 // (csrc/gemm_ar_sm100.cu).  partial_ptrs / result_ptrs / flag_ptrs: int64 device tensors [tp] with every rank's
 // address of the symmetric partial scratch, of this call's result buffer and of the flag table.
@@ -728,6 +772,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("maxpool_bwd", &maxpool_bwd);
   m.def("avgpool", &avgpool);
   m.def("allreduce_scale_f32", &allreduce_scale_f32);
+  m.def("reduce_scatter_scale_sumsq_f32", &reduce_scatter_scale_sumsq_f32);
+  m.def("allgather_b16", &allgather_b16);
+  m.def("comm_slice", &comm_slice);
   m.def("comm_max_blocks", &comm_max_blocks);
   m.def("status", &status);
   m.def("comm_set_peer_timeout_ms", [](double ms) { ssb::comm_set_peer_timeout_ns(static_cast<unsigned long long>(ms * 1e6)); });

@@ -114,14 +114,14 @@ allreduce_scale_f32_kernel(AllReduceArgs a) {
   block_barrier(a.flag_ptrs, a.rank, a.world, a.epoch + 1, a.status, a.limit_ns);
 }
 
-// Slice of rank r when n4 vectors of four floats are dealt out to `world` ranks: equal runs of an even number of
-// vectors (so that a slice of the matching bf16 buffer starts on a 16-byte boundary), the last one shorter.
-__host__ __device__ inline void slice_of(long long n4, int world, int rank, long long* lo, long long* hi) {
-  long long per = (n4 + world - 1) / world;
-  per += per & 1;
+// Slice of rank r when n_units units (of 8 elements each: two float4 of an fp32 buffer, one 16-byte vector of a
+// 16-bit buffer, so that both buffers split at the same elements) are dealt out to `world` ranks: equal runs, the
+// last one shorter.
+__host__ __device__ inline void slice_of(long long n_units, int world, int rank, long long* lo, long long* hi) {
+  const long long per = (n_units + world - 1) / world;
   const long long a = rank * per, b = a + per;
-  *lo = a < n4 ? a : n4;
-  *hi = b < n4 ? b : n4;
+  *lo = a < n_units ? a : n_units;
+  *hi = b < n_units ? b : n_units;
 }
 
 // Reduce-scatter fused with the 1/dp scaling and with the sum of squares of the result: rank r sums slice r of
@@ -135,7 +135,9 @@ reduce_scatter_scale_sumsq_f32_kernel(AllReduceArgs a, float* __restrict__ parti
   const bool ok = block_barrier(a.flag_ptrs, a.rank, a.world, a.epoch, a.status, a.limit_ns);
   const long long n4 = a.n / 4;
   long long lo, hi;
-  slice_of(n4, a.world, a.rank, &lo, &hi);
+  slice_of(a.n / 8, a.world, a.rank, &lo, &hi);
+  lo *= 2;  // units of 8 floats -> float4 indices
+  hi *= 2;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long first = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   float4* mine = reinterpret_cast<float4*>(a.peer_ptrs[a.rank]);
@@ -230,11 +232,11 @@ int allreduce_scale_f32_launch(void* const* peer_ptrs, void* mc_ptr, void* const
 }
 
 // Reduce-scatter of a symmetric fp32 buffer (see the kernel); `partials` holds comm_max_blocks() floats.  Uses
-// epoch and epoch + 1.  n must be a multiple of 4.
+// epoch and epoch + 1.  n must be a multiple of 8.
 int reduce_scatter_scale_sumsq_f32_launch(void* const* peer_ptrs, void* mc_ptr, void* const* flag_ptrs, int rank,
                                           int world, long long n, float scale, unsigned epoch, float* partials,
                                           int* status, cudaStream_t stream) {
-  if (n % 4 || world < 1 || world > 32) return -2;
+  if (n % 8 || world < 1 || world > 32) return -2;
   AllReduceArgs a;
   a.peer_ptrs = reinterpret_cast<float* const*>(peer_ptrs);
   a.mc_ptr = reinterpret_cast<float*>(mc_ptr);

@@ -666,6 +666,16 @@ def set_deterministic_embedding_grad(on: bool) -> None:
     _DETERMINISTIC_EMBEDDING_GRAD[0] = bool(on)
 
 
+def set_deterministic(on: bool) -> None:
+    """Bitwise-reproducible training steps on the GPU.  On: the embedding gradient is summed in sorted runs (the
+    default anyway) and the attention backward runs as the dK/dV + dQ kernel pair.  Off (the default for attention):
+    the fused attention backward kernel, which sums the key blocks' shares of dQ in an fp32 buffer in the order
+    they arrive, so dQ may differ in the last bit between two runs of the same step."""
+    set_deterministic_embedding_grad(on)
+    if native.available():
+        native.ext().set_attn_bwd_deterministic(bool(on))
+
+
 def embedding(ids, pos, W, P=None, v0=0, dropout_p=0.0, seed=0):
     return EmbeddingFn.apply(ids, pos, W, P, v0, dropout_p, seed)
 

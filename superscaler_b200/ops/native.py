@@ -47,7 +47,8 @@ KERNELS_PER_CALL = {"gemm": 1, "layernorm_fwd": 1, "layernorm_bwd": 4, "colsum":
                     "cast_f32_to_bf16": 1, "softmax_fwd": 1, "softmax_bwd": 1, "sumsq": 2, "adam_step": 1,
                     "sgd_step": 1, "embedding_fwd": 1, "embedding_bwd": 1, "ce_stats": 1, "ce_finalize": 1,
                     "attn_fwd": 1, "attn_bwd": 3, "im2col": 1, "col2im": 1, "subsample": 1, "bn_fwd": 3, "bn_bwd": 3, "bn_apply": 1,
-                    "maxpool_fwd": 1, "maxpool_bwd": 1, "avgpool": 1, "allreduce_scale_f32": 1}
+                    "maxpool_fwd": 1, "maxpool_bwd": 1, "avgpool": 1, "allreduce_scale_f32": 1,
+                    "reduce_scatter_scale_sumsq_f32": 1, "allgather_b16": 1}
 launch_counter = {"kernels": 0, "calls": 0}
 
 

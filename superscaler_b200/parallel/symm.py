@@ -48,13 +48,44 @@ class SymmetricBuffer:
         self._epoch += 2
         return e
 
-    def allreduce_scale_(self, numel: Optional[int] = None, scale: float = 1.0) -> None:
-        """In place on `self.tensor[:numel]` (fp32): sum over the group's ranks, times `scale`."""
+    def _tables_at(self, offset: int):
+        """Pointer tables (peer addresses, multicast address) of the sub-buffer that starts `offset` elements in."""
+        if offset == 0:
+            return self.peer_ptrs, self.multicast_ptr
+        cache = self.__dict__.setdefault("_offset_tables", {})
+        if offset not in cache:
+            nbytes = offset * self.tensor.element_size()
+            cache[offset] = (self.peer_ptrs + nbytes, self.multicast_ptr + nbytes if self.multicast_ptr else 0)
+        return cache[offset]
+
+    def allreduce_scale_(self, numel: Optional[int] = None, scale: float = 1.0, offset: int = 0) -> None:
+        """In place on `self.tensor[offset:offset + numel]` (fp32): sum over the group's ranks, times `scale`."""
         from ..ops import native
-        n = self.tensor.numel() if numel is None else numel
-        assert self.tensor.dtype == torch.float32 and n % 4 == 0
-        native.ext().allreduce_scale_f32(self.peer_ptrs, self.multicast_ptr, self.flag_ptrs, self.rank, self.world, n,
-                                         scale, self.next_epoch())
+        n = self.tensor.numel() - offset if numel is None else numel
+        assert self.tensor.dtype == torch.float32 and n % 4 == 0 and offset % 4 == 0
+        ptrs, mc = self._tables_at(offset)
+        native.ext().allreduce_scale_f32(ptrs, mc, self.flag_ptrs, self.rank, self.world, n, scale, self.next_epoch())
+
+    def slice_of(self, numel: int):
+        """[lo, hi) of this rank's slice of the first `numel` elements, as the two kernels below deal them out."""
+        from ..ops import native
+        lo, hi = native.ext().comm_slice(numel, self.world, self.rank)
+        return int(lo), int(hi)
+
+    def reduce_scatter_scale_sumsq_(self, numel: int, scale: float, partials: torch.Tensor) -> None:
+        """fp32: this rank's slice of `self.tensor[:numel]` becomes the sum over the ranks times `scale`, the rest of
+        `self.tensor[:numel]` is cleared, `partials` receives per-block sums of squares of the reduced slice."""
+        from ..ops import native
+        assert self.tensor.dtype == torch.float32 and numel % 8 == 0
+        native.ext().reduce_scatter_scale_sumsq_f32(self.peer_ptrs, self.multicast_ptr, self.flag_ptrs, self.rank,
+                                                    self.world, numel, scale, self.next_epoch(), partials)
+
+    def allgather_(self, numel: int) -> None:
+        """16-bit buffer: every rank's slice of `self.tensor[:numel]` is copied into every other rank's buffer."""
+        from ..ops import native
+        assert self.tensor.element_size() == 2 and numel % 8 == 0
+        native.ext().allgather_b16(self.peer_ptrs, self.multicast_ptr, self.flag_ptrs, self.rank, self.world, numel,
+                                   self.next_epoch())
 
 
 class FusedTPContext:

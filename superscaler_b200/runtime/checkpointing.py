@@ -85,6 +85,8 @@ def save_checkpoint(trainer, root: str, iteration: Optional[int] = None) -> Opti
     ps = trainer.pstate
     if hasattr(trainer, "check_device_status"):
         trainer.check_device_status()        # never write weights that a timed-out kernel may have corrupted
+    if hasattr(trainer.optimizer, "sync_replicas"):
+        trainer.optimizer.sync_replicas()    # collective: the slices other ranks own after sharded optimizer steps
     writes, shard = _shard_of(trainer)
     path = None
     if writes:

@@ -54,12 +54,32 @@ class StageOptimizer:
             groups.setdefault(copies, []).append((off, (n + 127) // 128 * 128))
         self.norm_groups = {c: _merge(r) for c, r in groups.items()}
         self.dp_buckets = store.buckets_by_dp()
+        # Sharded update (pure data-parallel stage with peer-mapped gradient AND model buffers): the weight-decay
+        # part [0, wd_end) of the flat buffers, which holds all the large matrices, is reduce-SCATTERED; every rank
+        # runs Adam on its slice only and writes the new bf16 weights into every rank's model buffer.  Half the
+        # NVLink bytes of an all-reduce and 1 / dp of the optimizer work.  The small tail [wd_end, total) (biases,
+        # LayerNorm / BatchNorm parameters, some of which the model reads from the fp32 master buffer) stays
+        # replicated: all-reduced and updated on every rank.  Master weights and moments outside a rank's slice
+        # go stale; `sync_replicas()` refreshes them before a checkpoint is written.
+        self.sharded = store.symm_grad is not None and store.symm_model16 is not None and store.wd_end >= 8 * 128
+        if self.sharded:
+            self.shard_lo, self.shard_hi = store.symm_grad.slice_of(store.wd_end)
+            self._partials = torch.zeros(native.ext().comm_max_blocks(), dtype=torch.float32, device=dev)
+            self._tail_sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+            self._skipped_tail = torch.zeros(1, dtype=torch.int32, device=dev)   # the slice's launch does the counting
+        self._replicas_stale = False
 
     # ---- data-parallel gradient reduction (NCCL path) -----------------------------------------
     def reduce_gradients(self) -> None:
         """Average gradients over each op's DP group.  With a peer-mapped gradient buffer (pure data-parallel
         stage) ONE fused kernel sums over the ranks and applies 1/dp through NVSwitch; otherwise one NCCL
         all-reduce per contiguous (tp, dp) range."""
+        if self.sharded:
+            sg, st = self.store.symm_grad, self.store
+            sg.reduce_scatter_scale_sumsq_(st.wd_end, 1.0 / sg.world, self._partials)
+            if st.total > st.wd_end:
+                sg.allreduce_scale_(st.total - st.wd_end, 1.0 / sg.world, offset=st.wd_end)
+            return
         if self.store.symm_grad is not None:
             self.store.symm_grad.allreduce_scale_(self.store.total, 1.0 / self.store.symm_grad.world)
             return
@@ -76,6 +96,17 @@ class StageOptimizer:
     # ---- norm + update ----------------------------------------------------------------------
     def _global_sumsq(self) -> torch.Tensor:
         g = self.store.grad
+        if self.sharded:
+            # this rank's slice counts once (the slices partition the buffer), the replicated tail 1 / dp times
+            st = self.store
+            world = st.symm_grad.world
+            if st.total > st.wd_end:
+                native.ext().sumsq(g[st.wd_end:st.total], self._tail_sumsq, False)
+                torch.add(self._partials.sum(), self._tail_sumsq[0], alpha=1.0 / world, out=self.sumsq[0])
+            else:
+                self.sumsq[0] = self._partials.sum()
+            dist.all_reduce(self.sumsq)
+            return self.sumsq
         first = True
         if g.is_cuda:
             ext = native.ext()
@@ -106,6 +137,23 @@ class StageOptimizer:
         self.step_count += 1
         st = self.store
         sumsq = self._global_sumsq()
+        if self.sharded:
+            ext = native.ext()
+            lo, hi = self.shard_lo, self.shard_hi
+            for a, b, wd_end, skipped in ((lo, hi, hi - lo, self.skipped), (st.wd_end, st.total, 0, self._skipped_tail)):
+                if b <= a:
+                    continue
+                if self.kind == "adam":
+                    ext.adam_step(st.master[a:b], st.exp_avg[a:b], st.exp_avg_sq[a:b], st.grad[a:b], st.model16[a:b],
+                                  sumsq, skipped, lr, self.betas[0], self.betas[1], self.eps, self.wd,
+                                  self.step_count, grad_scale, self.clip_grad, wd_end, zero_grad)
+                else:
+                    ext.sgd_step(st.master[a:b], st.exp_avg[a:b], st.grad[a:b], st.model16[a:b], sumsq, skipped,
+                                 lr, self.momentum, self.wd, grad_scale, self.clip_grad, wd_end, zero_grad,
+                                 self.step_count == 1)
+            st.symm_model16.allgather_(st.wd_end)
+            self._replicas_stale = True
+            return
         if st.grad.is_cuda:
             ext = native.ext()
             if self.kind == "adam":
@@ -144,7 +192,23 @@ class StageOptimizer:
         """Host read of the last global gradient norm (synchronises)."""
         return float(self.sumsq.sqrt())
 
+    def sync_replicas(self) -> None:
+        """After sharded steps: every rank fetches the other ranks' slices of the fp32 master weights and of the
+        moments (NCCL broadcasts, collective), so that any rank can write a complete checkpoint."""
+        if not self.sharded or not self._replicas_stale:
+            return
+        sg, st = self.store.symm_grad, self.store
+        for r in range(sg.world):
+            lo, hi = (int(x) for x in native.ext().comm_slice(st.wd_end, sg.world, r))
+            if hi <= lo:
+                continue
+            bufs = [st.master, st.exp_avg] + ([st.exp_avg_sq] if self.kind == "adam" else [])
+            for buf in bufs:
+                dist.broadcast(buf[lo:hi], src=dist.get_global_rank(sg.group, r), group=sg.group)
+        self._replicas_stale = False
+
     def state_dict(self) -> dict:
+        self.sync_replicas()
         return {"step": self.step_count, "exp_avg": self.store.exp_avg.clone(), "exp_avg_sq": self.store.exp_avg_sq.clone(),
                 "master": self.store.master.clone()}
 

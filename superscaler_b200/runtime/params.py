@@ -54,6 +54,8 @@ class ParamStore:
         self._shared: Dict[Tuple[str, int], str] = {}   # (shared key, tensor-parallel degree) -> parameter name
         self.grad_allocator = None      # optional: numel -> (tensor, owner) for a peer-mapped gradient buffer
         self.symm_grad = None
+        self.model16_allocator = None   # optional: numel -> peer-mapped bf16 model buffer (sharded optimizer step)
+        self.symm_model16 = None
 
     def declare(self, spec: ParamSpec) -> str:
         """Registers a parameter; tied parameters (same shared_key AND the same tensor-parallel degree, hence the
@@ -108,7 +110,11 @@ class ParamStore:
             self.grad = torch.zeros(self.total, **f32)
         self.exp_avg = torch.zeros(self.total, **f32)
         self.exp_avg_sq = torch.zeros(self.total, **f32)
-        self.model16 = torch.zeros(self.total, dtype=torch.bfloat16, device=self.device)
+        if self.model16_allocator is not None:
+            self.symm_model16 = self.model16_allocator(self.total)
+            self.model16 = self.symm_model16.tensor
+        else:
+            self.model16 = torch.zeros(self.total, dtype=torch.bfloat16, device=self.device)
         for s in ordered:
             off, n = self.offsets[s.name]
             full = self._init_full(s)

@@ -105,6 +105,9 @@ def main(argv=None) -> None:
     ap.add_argument("--inject-failure", default=None, metavar="RANK:ITERATION",
                     help="host-side fault injection for tests: that rank raises at the start of that iteration")
     ap.add_argument("--no-fused-comm", action="store_true")
+    ap.add_argument("--deterministic", action="store_true",
+                    help="bitwise-reproducible steps: attention backward as the dK/dV + dQ kernel pair instead of the "
+                         "fused kernel that sums dQ in arrival order")
     ap.add_argument("--data-path", default=None,
                     help="GPT token corpus prefix (<prefix>.bin uint16 token ids + <prefix>.npy document lengths); "
                          "default: synthetic batches")
@@ -126,6 +129,9 @@ def main(argv=None) -> None:
     if args.interleave_factor > 1:
         from .schedules import interleave_plan
         plan = interleave_plan(plan, args.interleave_factor, args.interleave_ops)
+    if args.deterministic:
+        from ..ops import functional as F
+        F.set_deterministic(True)
     overrides = {}
     if args.hidden_dropout is not None:
         overrides["hidden_dropout"] = args.hidden_dropout

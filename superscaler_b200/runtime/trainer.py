@@ -81,7 +81,7 @@ class Trainer:
                  model_overrides: Optional[dict] = None, lr: float = 1.5e-4, min_lr: float = 1e-5,
                  weight_decay: float = 0.01, clip_grad: float = 1.0, lr_decay_steps: int = 320000,
                  lr_warmup_steps: int = 3200, lr_style: str = "cosine", optimizer: str = "adam",
-                 fuse: bool = True, fused_comm: bool = False, training: bool = True):
+                 fuse: bool = True, fused_comm: bool = True, training: bool = True, shard_optimizer: bool = True):
         self.plan = plan
         self.rank, self.world_size = rank, world_size
         if device is None:
@@ -137,6 +137,10 @@ class Trainer:
         if fused_comm and pure_dp:
             from ..parallel.symm import SymmetricBuffer
             self.store.grad_allocator = lambda n: SymmetricBuffer(n, torch.float32, None, self.device)
+            if shard_optimizer:
+                # the bf16 model copy is peer-mapped too: each rank updates one slice of the weights and writes the
+                # result into every rank's copy
+                self.store.model16_allocator = lambda n: SymmetricBuffer(n, torch.bfloat16, None, self.device)
         self.env = Env(cfg=self.cfg, pstate=self.pstate, store=self.store, micro_bs=self.micro_bs,
                        fused_comm=fused_comm)
         self.env.training = training

@@ -45,15 +45,31 @@ def main():
         if (kw["global_bs"] // kw["micro_bs"]) % world == 0:
             from superscaler_b200.runtime.schedules import interleave_plan
             plans["pp_interleaved"] = interleave_plan(plans["pp"], 2)
-        out = {}
+        out, masters = {}, {}
         for name, plan in plans.items():
             for fused in ((True, False) if name in ("dp", "tp") else (False,)):
-                t = Trainer(plan, rank=rank, world_size=world, model_overrides=nd, lr_warmup_steps=0, fused_comm=fused)
-                ls = [t.loss_value(t.train_step(gpt_batch(8, 256, 2048, seed=1))) for _ in range(3)]
-                out[f"{name}{'_fused' if fused else ''}"] = ls
-                del t
+                for shard in ((True, False) if (name == "dp" and fused) else (False,)):
+                    t = Trainer(plan, rank=rank, world_size=world, model_overrides=nd, lr_warmup_steps=0,
+                                fused_comm=fused, shard_optimizer=shard)
+                    ls = [t.loss_value(t.train_step(gpt_batch(8, 256, 2048, seed=1))) for _ in range(3)]
+                    key = f"{name}{'_fused' if fused else ''}{'_sharded' if shard else ''}"
+                    out[key] = ls
+                    if name == "dp":
+                        assert t.optimizer.sharded == (fused and shard), key
+                        sd = t.optimizer.state_dict()             # collective: gathers the slices of a sharded run
+                        masters[key] = (sd["master"].clone(), sd["exp_avg_sq"].clone(), t.store.model16.clone())
+                    del t
         torch.cuda.synchronize()
         assert native.check_status() == 0
+        # reduce-scatter + sharded Adam + all-gather of the bf16 weights against all-reduce + replicated Adam: the same
+        # update up to the rounding of the gradient norm (summed in another order)
+        assert max(abs(a - b) for a, b in zip(out["dp_fused_sharded"], out["dp_fused"])) < 1e-4, out
+        for a, b in zip(masters["dp_fused_sharded"], masters["dp_fused"]):
+            assert (a.float() - b.float()).abs().max().item() < 1e-4
+        mine = masters["dp_fused_sharded"][2].float()
+        other = mine.clone()
+        dist.broadcast(other, src=0)
+        assert torch.equal(mine, other), "bf16 weights differ between ranks after the sharded update"
         base = out["dp"]
         for k, v in out.items():
             assert all(x == x for x in v) and v[-1] < v[0], (k, v)
