@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BS)
     ap.add_argument("--layers", type=int, default=None, help="debug only; a non-default value is reported")
     ap.add_argument("--fused-comm", type=int, default=1)
+    ap.add_argument("--deterministic", type=int, default=0,
+                    help="1: bitwise-reproducible kernels (attention backward as the dK/dV + dQ kernel pair)")
     return ap.parse_args()
 
 
@@ -160,6 +162,9 @@ def main():
             plan = json.load(f)
     else:
         plan = default_plan(world, args.mbs_per_gpu, args.global_batch, layers)
+    if args.deterministic:
+        from superscaler_b200.ops import functional as F
+        F.set_deterministic(True)
     trainer = Trainer(plan, rank=rank, world_size=world, fused_comm=bool(args.fused_comm),
                       model_overrides=dict(vocab=GPT13B["vocab_size"]))
     gbs, seq, vocab = plan["global_batch_size"], plan["seq_length"], GPT13B["vocab_size"]
