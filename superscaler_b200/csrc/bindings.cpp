@@ -20,6 +20,7 @@ int layernorm_fwd_launch(const void* x, const void* residual, const float* gamma
                          void* sum_out, float* mean, float* rstd, int rows, int H, float eps, int num_sms,
                          cudaStream_t stream);
 int ln_bwd_slices(int rows);
+int ln_bwd_part_rows(int rows, int H, int num_sms);
 int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
                          const void* dres, void* dx, float* dgamma, float* dbeta, float* part_g, float* part_b,
                          int accumulate_wgrad, int rows, int H, int num_sms, cudaStream_t stream);
@@ -197,7 +198,8 @@ Tensor layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, con
   c10::cuda::CUDAGuard guard(x.device());
   const int rows = static_cast<int>(x.size(0)), H = static_cast<int>(x.size(1));
   Tensor dx = torch::empty_like(x);
-  Tensor part = torch::empty({2, ssb::ln_bwd_slices(rows), H}, torch::dtype(torch::kFloat32).device(x.device()));
+  Tensor part = torch::empty({2, ssb::ln_bwd_part_rows(rows, H, num_sms()), H},
+                             torch::dtype(torch::kFloat32).device(x.device()));
   check_launch(ssb::layernorm_bwd_launch(dy.data_ptr(), x.data_ptr(), gamma.data_ptr<float>(), mean.data_ptr<float>(),
                                          rstd.data_ptr<float>(), opt_ptr(dres), dx.data_ptr(), dgamma.data_ptr<float>(),
                                          dbeta.data_ptr<float>(), part[0].data_ptr<float>(), part[1].data_ptr<float>(),
@@ -648,15 +650,18 @@ std::vector<int64_t> comm_slice(int64_t n, int64_t world, int64_t rank) {
 void gemm_allreduce(const Tensor& a, const Tensor& b, bool b_mn, Tensor& d, const OptTensor& bias,
                     const OptTensor& residual, double alpha, double dropout_p, int64_t seed, const Tensor& partial_ptrs,
                     const Tensor& result_ptrs, const Tensor& flag_ptrs, int64_t rank, int64_t tp,
-                    int64_t epoch, int64_t max_tiles, int64_t capacity_elems) {
+                    int64_t epoch, int64_t max_tiles, int64_t capacity_elems, bool scatter,
+                    int64_t wait_consumed_epoch) {
   check_bf16_2d(a, "a");
   check_bf16_2d(b, "b");
   check_bf16_2d(d, "d");
   c10::cuda::CUDAGuard guard(a.device());
   const int64_t M = a.size(0), K = a.size(1);
   const int64_t N = b_mn ? b.size(1) : b.size(0);
+  const int64_t out_rows = scatter ? M / tp : M;   // reduce-scatter form: this rank keeps M / tp rows
   TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K, "gemm_allreduce: reduction sizes differ");
-  TORCH_CHECK(d.size(0) == M && d.size(1) == N, "gemm_allreduce: output must be [", M, ", ", N, "]");
+  TORCH_CHECK(!scatter || M % (tp * 128) == 0, "reduce-scatter form: rows per rank must be a multiple of 128");
+  TORCH_CHECK(d.size(0) == out_rows && d.size(1) == N, "gemm_allreduce: output must be [", out_rows, ", ", N, "]");
   for (const Tensor* t : {&partial_ptrs, &result_ptrs, &flag_ptrs})
     TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kInt64 && t->numel() == tp, "pointer tables must be int64 [tp]");
   ssb::GemmParams p{};
@@ -670,13 +675,15 @@ void gemm_allreduce(const Tensor& a, const Tensor& b, bool b_mn, Tensor& d, cons
   }
   if (residual.has_value()) {
     check_bf16_2d(*residual, "residual");
-    TORCH_CHECK(residual->size(0) == M && residual->size(1) == N && residual->stride(0) % 8 == 0, "residual shape");
+    TORCH_CHECK(residual->size(0) == out_rows && residual->size(1) == N && residual->stride(0) % 8 == 0, "residual shape");
     p.residual = residual->data_ptr(); p.ldres = static_cast<int>(residual->stride(0));
   }
   p.dropout_p = static_cast<float>(dropout_p);
   p.dropout_seed = static_cast<unsigned long long>(seed);
   p.status = status_tensor().data_ptr<int>();
   ssb::GemmArComm cm{};
+  cm.scatter = scatter ? 1 : 0;
+  cm.wait_consumed_epoch = static_cast<uint32_t>(wait_consumed_epoch);
   cm.partial_ptrs = reinterpret_cast<const void* const*>(partial_ptrs.data_ptr<int64_t>());
   cm.result_ptrs = reinterpret_cast<const void* const*>(result_ptrs.data_ptr<int64_t>());
   cm.flag_ptrs = reinterpret_cast<uint32_t* const*>(flag_ptrs.data_ptr<int64_t>());

@@ -32,8 +32,11 @@
 // monotonically growing epoch, so they are never reset.  Every wait is bounded: on a timeout the kernel records
 // kStatusPeerTimeout and returns.  The signalling store is a plain st.release.sys after cp.async.bulk.wait_group 0:
 // an extra __threadfence_system() in front of it cost 10-25 us per tile while TMA loads were in flight.
-// Built with -DSSB_AR_TRACE the kernel records %globaltimer at its hand-over points for the first 16 tiles of every CTA
-// into a buffer set with ssb_ar_set_trace() (a development aid; off in normal builds).
+//
+// Reduce-scatter form (GemmArComm::scatter): the owner of a tile is the rank that keeps its ROWS, the owner warps
+// write the reduced rows to the local [M / tp][N] output and push nothing, the receiver warps have no work.  Used for
+// the backward of an all-gather -> GEMM (the gradient of the gathered input is needed only on the rank the rows came
+// from): half the NVLink bytes of the all-reduce form.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -107,12 +110,6 @@ __device__ __forceinline__ void bulk_copy_s2g(void* gdst, const void* ssrc, uint
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(ssrc)), "r"(bytes)
                : "memory");
 }
-#ifdef SSB_AR_TRACE
-__device__ unsigned long long* g_trace = nullptr;  // [cta][tile iter][16 events]
-#define TRACE(ev) do { if (g_trace && lane == 0 && (warp == 2 || warp == 8 || warp == 12) && titer < 16) g_trace[(blockIdx.x * 16 + titer) * 16 + (ev)] = global_timer_ns(); } while (0)
-#else
-#define TRACE(ev) do {} while (0)
-#endif
 
 struct TileCoord {
   int m_blk, n_blk;
@@ -130,8 +127,10 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) 
 }
 
 // Final epilogue on 8 consecutive columns [n0, n0+8) of row `row`: bias, dropout, residual (see GemmParams).
-__device__ __forceinline__ uint4 final_epilogue8(const GemmParams& p, int row, int n0, float (&v)[8], uint32_t keep16,
-                                                 float drop_scale) {
+// `row` is the row of the full [M][N] product (it enters the dropout counter, so the mask does not depend on how
+// the rows are dealt out), `mem_row` the row of p.residual that holds it (differs in the reduce-scatter form).
+__device__ __forceinline__ uint4 final_epilogue8(const GemmParams& p, int row, int mem_row, int n0, float (&v)[8],
+                                                 uint32_t keep16, float drop_scale) {
   if (p.bias != nullptr) {
     if (p.bias_fp32) {
       const float4 b0 = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + n0));
@@ -158,7 +157,7 @@ __device__ __forceinline__ uint4 final_epilogue8(const GemmParams& p, int row, i
   }
   if (p.residual != nullptr) {
     const uint4 q = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.residual) +
-                                                         static_cast<size_t>(row) * p.ldres + n0));
+                                                         static_cast<size_t>(mem_row) * p.ldres + n0));
     float2 f;
     f = unpack_bf16x2(q.x); v[0] += f.x; v[1] += f.y;
     f = unpack_bf16x2(q.y); v[2] += f.x; v[3] += f.y;
@@ -205,7 +204,20 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   // tile / tp is unique per owner), and the rotation advances once per sweep of the grid, so a CTA alternates
   // between owned and foreign tiles instead of owning all of its tiles.
   const int rot_div = max(1, cm.grid / cm.tp);
-  auto owner_of = [&](int tile) { return (tile % cm.tp + (tile / cm.tp) / rot_div) % cm.tp; };
+  // reduce-scatter form: the owner is the rank that keeps the tile's rows; its slot is the tile's index among them
+  const int mb_per_rank = cm.scatter ? (p.M / cm.tp) / BM : 1;
+  auto owner_of = [&](int tile) {
+    if (cm.scatter) return tile_coord(tile, num_m, num_n).m_blk / mb_per_rank;
+    return (tile % cm.tp + (tile / cm.tp) / rot_div) % cm.tp;
+  };
+  auto slot_of = [&](int tile) {
+    if (cm.scatter) {
+      const TileCoord c = tile_coord(tile, num_m, num_n);
+      return (c.m_blk % mb_per_rank) * num_n + c.n_blk;
+    }
+    return tile / cm.tp;
+  };
+  uint32_t* const consumed_flags_mine = cm.flag_ptrs[cm.rank] + final_base + static_cast<size_t>(cm.max_tiles) * 4;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -299,16 +311,17 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     uint8_t* stage = stage_e + (warp - 2) * (2 * kChunkBytes);  // two 2 KB buffers per warp
     int iter = 0;
     bool ok = true;
+    // every owner has finished reading what the last reduce-scatter call left in its scratch
+    if (cm.wait_consumed_epoch != 0)
+      ok = wait_flag_warp(consumed_flags_mine + lane, lane < cm.tp, cm.wait_consumed_epoch, abort_flag, p.status);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
       const int acc = iter & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], (iter >> 1) & 1, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
-      const int titer = iter;
-      TRACE(0);
       const int owner = owner_of(tile);
       // slot of this (source rank, tile) in the owner's scratch; inside a slot: [quarter][32-column chunk][32 rows][64 B]
       uint8_t* dst = reinterpret_cast<uint8_t*>(const_cast<void*>(cm.partial_ptrs[owner])) +
-                     ((static_cast<size_t>(cm.rank) * slots + tile / cm.tp) * kTileElems) * 2 +
+                     ((static_cast<size_t>(cm.rank) * slots + slot_of(tile)) * kTileElems) * 2 +
                      static_cast<size_t>(quarter) * (32 * BN * 2);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
@@ -340,13 +353,10 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           tma_store_commit();
         }
       }
-      TRACE(8);
       if (lane == 0) {
         tma_store_wait<0>();       // every chunk of this quarter has been written to the owner's memory
-        TRACE(9);
         st_release_sys_u32(cm.flag_ptrs[owner] + static_cast<size_t>(tile) * part_flags_per_tile + cm.rank * 4 + quarter,
                            cm.epoch);
-        TRACE(1);
       }
       __syncwarp();
     }
@@ -362,10 +372,7 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const bool owner_role = warp < 10;  // warps 6..9 reduce and publish owned tiles, warps 10..13 receive foreign ones
     uint8_t* stage = stage_c + (quarter) * (R * BN * 2);  // 4 KB per owner-role warp
     bool ok = true;
-    int titer = -1;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      ++titer;
-      TRACE(2);
       const TileCoord tc = tile_coord(tile, num_m, num_n);
       const int owner = owner_of(tile);
       const int row0 = tc.m_blk * BM + quarter * 32;
@@ -373,13 +380,14 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const bool col_ok = col < p.N;             // N is a multiple of 8
       const int rows = min(32, p.M - row0);      // may be <= 0 on the ragged edge
       if ((owner == cm.rank) != owner_role) continue;
+      if (cm.scatter && !owner_role) continue;  // reduce-scatter: nothing comes back
+      const int mem_row0 = cm.scatter ? row0 - cm.rank * (p.M / cm.tp) : row0;  // row of the local output
       if (owner_role) {
         ok = wait_flag_warp(my_flags + static_cast<size_t>(tile) * part_flags_per_tile + lane * 4 + quarter,
                             lane < cm.tp, cm.epoch, abort_flag, p.status);
         if (!ok) break;
-        TRACE(3);
         // partial slots are stored [quarter][chunk][row][64 B]: this lane's 8 columns sit in chunk lane / 4
-        const size_t slot_off = static_cast<size_t>(tile / cm.tp) * kTileElems + static_cast<size_t>(quarter) * (32 * BN) +
+        const size_t slot_off = static_cast<size_t>(slot_of(tile)) * kTileElems + static_cast<size_t>(quarter) * (32 * BN) +
                                 (lane >> 2) * (32 * 32) + (lane & 3) * 8;
         const size_t res_off = static_cast<size_t>(tile) * kTileElems + static_cast<size_t>(quarter) * (32 * BN);
 #pragma unroll 1
@@ -404,16 +412,25 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               f = unpack_bf16x2(q[i].w); v[i][6] += f.x; v[i][7] += f.y;
             }
           }
-          if (rb == 0) TRACE(5);
+          if (cm.scatter) {
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+              if (col_ok && rb + i < rows) {
+                const uint4 o = final_epilogue8(p, row0 + rb + i, mem_row0 + rb + i, col, v[i], keep16, drop_scale);
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) +
+                                          static_cast<size_t>(mem_row0 + rb + i) * p.ldd + col) = o;
+              }
+            }
+            continue;
+          }
           if (lane == 0) tma_store_wait_read<0>();  // the previous batch has left the staging buffer
           __syncwarp();
-          if (rb == 8) TRACE(6);
 #pragma unroll
           for (int i = 0; i < R; ++i) {
             const int row = row0 + rb + i;
             uint4 o = make_uint4(0u, 0u, 0u, 0u);
             if (col_ok && rb + i < rows) {
-              o = final_epilogue8(p, row, col, v[i], keep16, drop_scale);
+              o = final_epilogue8(p, row, row, col, v[i], keep16, drop_scale);
               *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.ldd + col) = o;
             }
             *reinterpret_cast<uint4*>(stage + i * (BN * 2) + lane * 16) = o;
@@ -430,21 +447,17 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             tma_store_commit();
           }
         }
-        TRACE(7);
-        if (lane == 0) {
+        if (lane == 0 && !cm.scatter) {
           tma_store_wait<0>();
-          TRACE(11);
           for (int pr = 0; pr < cm.tp; ++pr)
             if (pr != cm.rank)
               st_release_sys_u32(cm.flag_ptrs[pr] + final_base + static_cast<size_t>(tile) * 4 + quarter, cm.epoch);
-          TRACE(4);
         }
         __syncwarp();
       } else {
         ok = wait_flag_warp(my_flags + final_base + static_cast<size_t>(tile) * 4 + quarter, lane == 0, cm.epoch,
                             abort_flag, p.status);
         if (!ok) break;
-        TRACE(5);
         const __nv_bfloat16* src = my_result + static_cast<size_t>(tile) * kTileElems +
                                    static_cast<size_t>(quarter * 32) * BN + lane * 8;
 #pragma unroll 1
@@ -459,10 +472,25 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) +
                                         static_cast<size_t>(row0 + rb + i) * p.ldd + col) = q[i];
         }
-        TRACE(6);
       }
     }
     if (lane == 0) tma_store_wait<0>();
+    if (cm.scatter && owner_role && ok) {
+      // Publish "consumed": the four owner warps of every CTA count themselves; the last one of the grid resets the
+      // counter for the next call and tells every peer that this rank has read all the partials of this epoch.
+      __syncwarp();
+      if (lane == 0) {
+        uint32_t* counter = consumed_flags_mine + cm.tp;
+        __threadfence();
+        const uint32_t seen = atomicAdd(counter, 1u);
+        if (seen == 4u * gridDim.x - 1u) {
+          *counter = 0u;
+          __threadfence_system();
+          for (int pr = 0; pr < cm.tp; ++pr)
+            st_release_sys_u32(cm.flag_ptrs[pr] + final_base + static_cast<size_t>(cm.max_tiles) * 4 + cm.rank, cm.epoch);
+        }
+      }
+    }
   }
 
   // ------------------------------- teardown ----------------------------------
@@ -477,11 +505,6 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 
 }  // namespace
 
-#ifdef SSB_AR_TRACE
-extern "C" int ssb_ar_set_trace(unsigned long long* buf) {
-  return (int)cudaMemcpyToSymbol(g_trace, &buf, sizeof(buf));
-}
-#endif
 
 // A [M][K] bf16 (K contiguous); B [N][K] (b_mn_major = 0) or [K][N] (1).  p describes the FINAL epilogue
 // (alpha, bias, dropout, residual) and the local bf16 output; activation / pre-activation / accumulate / fp32
@@ -493,6 +516,7 @@ int gemm_ar_launch(const void* A, int lda, const void* B, int ldb, int b_mn_majo
   if ((lda % 8) || (ldb % 8) || (p.ldd % 8)) return -3;
   const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   if (num_tiles > cm.max_tiles || cm.tp < 1 || cm.tp > 32) return -6;
+  if (cm.scatter && (p.M % (cm.tp * BM))) return -2;  // every rank keeps whole 128-row blocks
   if (static_cast<long long>(num_tiles + cm.tp) * kTileElems > cm.capacity_elems) return -6;
   CUtensorMap ta, tb;
   int rc = make_tma_2d_bf16(&ta, A, p.M, p.K, lda, BM, BK);

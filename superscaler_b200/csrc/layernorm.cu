@@ -198,30 +198,45 @@ ln_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
   }
 }
 
-// Same as ln_bwd_dx_kernel for H = VPL * 256: the packed dy and x rows stay in registers between the two passes
-// (one read of each from memory) and gamma is read in 16-byte pieces.
-template <int VPL>
+// One pass over dy and x for H = VPL * 256 * WPR: dx, and in the same sweep every lane keeps running sums of
+// dy * xhat and dy for its 8 * VPL columns over all rows its warp visits.  WPR warps share a row (each owns a
+// contiguous part of the columns, so that the running sums fit in registers) and exchange their two row sums through
+// shared memory.  The warps of a block fold their column sums through shared memory in a fixed order and the block
+// writes ONE row of partials (part_g[block][h], part_b[block][h]); fold_partials_kernel adds the blocks.  dy and x
+// are read once instead of twice, and the result does not depend on the order of execution.
+template <int VPL, int WPR>
 __global__ void __launch_bounds__(kLnWarpsPerBlock * 32)
-ln_bwd_dx_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-                     const float* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ rstd,
-                     const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, int rows, int H) {
-  const int lane = threadIdx.x & 31;
-  const int warp_global = blockIdx.x * kLnWarpsPerBlock + (threadIdx.x >> 5);
-  const int warps_total = gridDim.x * kLnWarpsPerBlock;
-  for (int row = warp_global; row < rows; row += warps_total) {
+ln_bwd_onepass_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const float* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ rstd,
+                      const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                      float* __restrict__ part_g, float* __restrict__ part_b, int rows, int H) {
+  constexpr int RPB = kLnWarpsPerBlock / WPR;        // rows a block works on at a time
+  __shared__ float fold_g[VPL * 256 * WPR], fold_b[VPL * 256 * WPR];
+  __shared__ float xch[2][RPB][WPR][2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rslot = warp / WPR, part = warp % WPR;
+  const int v0 = part * VPL * 32;                    // first 16-byte vector of this warp's columns
+  float ag[VPL][8], ab[VPL][8];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ag[i][j] = ab[i][j] = 0.f;
+  int it = 0;
+  // every warp of a row slot runs the same number of iterations: the named barrier below is reached by all of them
+  for (int row = blockIdx.x * RPB + rslot; row < rows; row += gridDim.x * RPB, ++it) {
     const uint4* dyr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * H);
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
     const float mu = mean[row], rs = rstd[row];
     uint4 qd[VPL], qx[VPL];
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      qd[i] = dyr[i * 32 + lane];
-      qx[i] = xr[i * 32 + lane];
+      qd[i] = dyr[v0 + i * 32 + lane];
+      qx[i] = xr[v0 + i * 32 + lane];
     }
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      const int v = i * 32 + lane;
+      const int v = v0 + i * 32 + lane;
       const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * v);
       const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * v + 1);
       const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
@@ -231,18 +246,38 @@ ln_bwd_dx_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
       const float xv[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
+        const float xhat = (xv[j] - mu) * rs;
         const float dg = d[j] * g[j];
         s1 += dg;
-        s2 += dg * (xv[j] - mu) * rs;
+        s2 += dg * xhat;
+        ag[i][j] += d[j] * xhat;
+        ab[i][j] += d[j];
       }
     }
-    s1 = warp_sum(s1) / static_cast<float>(H);
-    s2 = warp_sum(s2) / static_cast<float>(H);
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if constexpr (WPR > 1) {
+      float* slot = &xch[it & 1][rslot][0][0];
+      if (lane == 0) {
+        slot[part * 2] = s1;
+        slot[part * 2 + 1] = s2;
+      }
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + rslot), "r"(32 * WPR) : "memory");
+      s1 = 0.f;
+      s2 = 0.f;
+#pragma unroll
+      for (int w = 0; w < WPR; ++w) {
+        s1 += slot[w * 2];
+        s2 += slot[w * 2 + 1];
+      }
+    }
+    s1 /= static_cast<float>(H);
+    s2 /= static_cast<float>(H);
     uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * H);
     const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * H) : nullptr;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      const int v = i * 32 + lane;
+      const int v = v0 + i * 32 + lane;
       const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * v);
       const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * v + 1);
       const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
@@ -266,6 +301,25 @@ ln_bwd_dx_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
       w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
       dxr[v] = w;
     }
+  }
+  // fold the row slots of the block in the order 0, 1, ...: slot s adds its warps' sums to the columns they own
+  for (int sl = 0; sl < RPB; ++sl) {
+    if (rslot == sl) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int c = (v0 + i * 32 + lane) * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          fold_g[c + j] = (sl == 0 ? 0.f : fold_g[c + j]) + ag[i][j];
+          fold_b[c + j] = (sl == 0 ? 0.f : fold_b[c + j]) + ab[i][j];
+        }
+      }
+    }
+    __syncthreads();
+  }
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    part_g[static_cast<size_t>(blockIdx.x) * H + c] = fold_g[c];
+    part_b[static_cast<size_t>(blockIdx.x) * H + c] = fold_b[c];
   }
 }
 
@@ -383,21 +437,40 @@ int ln_bwd_slices(int rows) {
   return s < 1 ? 1 : (s > 128 ? 128 : s);
 }
 
+// Rows of partial sums the backward needs in each of part_g / part_b (then H floats per row).
+int ln_bwd_part_rows(int rows, int H, int num_sms) {
+  if (H == 1024 || H == 2048) {  // one-pass kernel: one row of partials per block
+    const int rpb = H == 1024 ? kLnWarpsPerBlock : kLnWarpsPerBlock / 2;   // rows a block works on at a time
+    const int want = (rows + rpb - 1) / rpb;
+    const int cap = num_sms * (H == 1024 ? 2 : 3);   // resident blocks per SM at the kernels' register counts
+    return want < cap ? want : cap;
+  }
+  return ln_bwd_slices(rows);
+}
+
 int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
                          const void* dres, void* dx, float* dgamma, float* dbeta, float* part_g, float* part_b,
                          int accumulate_wgrad, int rows, int H, int num_sms, cudaStream_t stream) {
   if (H % 8) return -3;
-  const int blocks = min((rows + kLnWarpsPerBlock - 1) / kLnWarpsPerBlock, num_sms * 16);
   const auto* dyb = reinterpret_cast<const __nv_bfloat16*>(dy);
   const auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
   const auto* drb = reinterpret_cast<const __nv_bfloat16*>(dres);
   auto* dxb = reinterpret_cast<__nv_bfloat16*>(dx);
-  const dim3 g(blocks), b(kLnWarpsPerBlock * 32);
-  switch (H) {  // rows that fit in registers are read once
-    case 1024: ln_bwd_dx_reg_kernel<4><<<g, b, 0, stream>>>(dyb, xb, gamma, mean, rstd, drb, dxb, rows, H); break;
-    case 2048: ln_bwd_dx_reg_kernel<8><<<g, b, 0, stream>>>(dyb, xb, gamma, mean, rstd, drb, dxb, rows, H); break;
-    default: ln_bwd_dx_kernel<<<g, b, 0, stream>>>(dyb, xb, gamma, mean, rstd, drb, dxb, rows, H);
+  if (H == 1024 || H == 2048) {
+    // dy and x are read once: dx and the per-column sums come out of the same sweep
+    const int nb = ln_bwd_part_rows(rows, H, num_sms);
+    const dim3 g(nb), b(kLnWarpsPerBlock * 32);
+    if (H == 1024)
+      ln_bwd_onepass_kernel<4, 1><<<g, b, 0, stream>>>(dyb, xb, gamma, mean, rstd, drb, dxb, part_g, part_b, rows, H);
+    else
+      ln_bwd_onepass_kernel<4, 2><<<g, b, 0, stream>>>(dyb, xb, gamma, mean, rstd, drb, dxb, part_g, part_b, rows, H);
+    fold_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(part_g, dgamma, nb, H, accumulate_wgrad);
+    fold_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(part_b, dbeta, nb, H, accumulate_wgrad);
+    return static_cast<int>(cudaGetLastError());
   }
+  const int blocks = min((rows + kLnWarpsPerBlock - 1) / kLnWarpsPerBlock, num_sms * 16);
+  const dim3 g(blocks), b(kLnWarpsPerBlock * 32);
+  ln_bwd_dx_kernel<<<g, b, 0, stream>>>(dyb, xb, gamma, mean, rstd, drb, dxb, rows, H);
   const int slices = ln_bwd_slices(rows);
   const int rps = (rows + slices - 1) / slices;
   dim3 grid((H / 2 + 31) / 32, slices);

@@ -114,13 +114,14 @@ class FusedTPContext:
 
         self.partial = symm.empty(self.capacity, dtype=torch.bfloat16, device=device)
         self.results = [symm.empty(self.capacity, dtype=torch.bfloat16, device=device) for _ in range(2)]
-        self.flags = symm.empty(self.max_tiles * (self.tp * 4 + 4), dtype=torch.int32, device=device)
+        self.flags = symm.empty(self.max_tiles * (self.tp * 4 + 4) + self.tp + 1, dtype=torch.int32, device=device)
         self.flags.zero_()
         _, self.partial_ptrs = table(self.partial)
         handles = [table(r) for r in self.results]
         self.result_ptrs = [h[1] for h in handles]
         _, self.flag_ptrs = table(self.flags)
         self.epoch = 0
+        self.last_scatter_epoch = 0     # epoch of the last reduce-scatter call: later calls wait for its "consumed" flags
         torch.cuda.synchronize(device)
         dist.barrier(self.group)
 
@@ -140,7 +141,27 @@ class FusedTPContext:
         par = self.epoch & 1
         native.ext().gemm_allreduce(x, w, b_mn, out, bias, residual, alpha, dropout_p, seed, self.partial_ptrs,
                                     self.result_ptrs[par], self.flag_ptrs, self.rank, self.tp, self.epoch,
-                                    self.max_tiles, self.capacity)
+                                    self.max_tiles, self.capacity, False, self.last_scatter_epoch)
+        return out
+
+    def linear_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, bias=None, residual=None,
+                              alpha: float = 1.0, dropout_p: float = 0.0, seed: int = 0, out=None) -> torch.Tensor:
+        """Rows [r M / tp, (r + 1) M / tp) of sum over the group of (x_r . w_r^T) [+ bias, dropout, + residual] on rank
+        r: the GEMM -> reduce-scatter form of the same kernel (nothing travels back to the peers).  M / tp must be a
+        multiple of 128.  `residual` and the result are this rank's [M / tp, N] rows."""
+        from ..ops import native
+        M = x.shape[0]
+        N = w.shape[1] if b_mn else w.shape[0]
+        assert self.fits(M, N), f"fused TP scratch too small for {M}x{N}"
+        assert M % (self.tp * self.TILE_M) == 0, "rows per rank must be a multiple of 128"
+        if out is None:
+            out = torch.empty((M // self.tp, N), dtype=torch.bfloat16, device=x.device)
+        self.epoch += 1
+        par = self.epoch & 1
+        native.ext().gemm_allreduce(x, w, b_mn, out, bias, residual, alpha, dropout_p, seed, self.partial_ptrs,
+                                    self.result_ptrs[par], self.flag_ptrs, self.rank, self.tp, self.epoch,
+                                    self.max_tiles, self.capacity, True, self.last_scatter_epoch)
+        self.last_scatter_epoch = self.epoch
         return out
 
     # ---- all-gather fused into the consuming GEMM (csrc/gemm_ag_sm100.cu) -------------------------------------
