@@ -97,11 +97,16 @@ class FusedDenseDropAdd(FusedGroup):
 
 
 class FusedUpAct(FusedGroup):
+    def accepts_dealt_out_rows(self) -> bool:
+        return self.members[0].info.algo == 0
+
     def forward(self, st):
         up: MLPUpOp = self.members[0]
         w, b = up.p("dense_h_to_4h.weight"), up.p("dense_h_to_4h.bias")
         x = st["x"]
-        if up.info.algo == 0 and self.tpctx() is not None:
+        if st.pop("_x_rows_dealt_out", False):
+            st["x"] = F.gathered_column_linear_fused(x, w, b, self.env.cfg.activation, self.tpctx())
+        elif up.info.algo == 0 and self.tpctx() is not None:
             st["x"] = F.column_parallel_linear_fused(x, w, b, self.env.cfg.activation, self.tpctx())
         elif up.info.algo == 0:
             st["x"] = F.linear(M.copy_to_group(x, self.tp_group), w, b, act=self.env.cfg.activation)
@@ -113,6 +118,9 @@ class FusedUpAct(FusedGroup):
 class FusedMLP(FusedGroup):
     """GEMM-1 + activation + GEMM-2 + dropout + residual (tp == 1: two forward kernels)."""
 
+    def accepts_dealt_out_rows(self) -> bool:
+        return self.members[0].info.algo == 0 and self.members[2].info.algo == 0
+
     def forward(self, st):
         up: MLPUpOp = self.members[0]
         down: DenseOp = self.members[2]
@@ -121,7 +129,10 @@ class FusedMLP(FusedGroup):
         w1, b1 = up.p("dense_h_to_4h.weight"), up.p("dense_h_to_4h.bias")
         w2, b2 = down.p(f"{down.key}.weight"), down.p(f"{down.key}.bias")
         x, res = st["x"], st.pop("residual")
-        if self.pl.tp == 1:
+        if st.pop("_x_rows_dealt_out", False):
+            h = F.gathered_column_linear_fused(x, w1, b1, c.activation, self.tpctx())
+            st["x"] = F.row_parallel_linear_fused(h, w2, b2, res, p_drop, self.seed(), self.tpctx())
+        elif self.pl.tp == 1:
             st["x"] = F.mlp(x, w1, b1, w2, b2, residual=res, act=c.activation, dropout_p=p_drop, seed=self.seed())
         elif self.tpctx() is not None:
             h = F.column_parallel_linear_fused(x, w1, b1, c.activation, self.tpctx())

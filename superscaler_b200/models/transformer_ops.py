@@ -123,9 +123,16 @@ class QKVOp(Op):
                             shard_dim=1, std=c.init_std)
             self.param_spec("query_key_value.bias", (3 * proj,), "zeros", weight_decay=False)
 
+    def accepts_dealt_out_rows(self) -> bool:
+        return self.info.algo == 0 and self.kind == "self"
+
     def forward(self, st):
         x = st["x"]
-        if self.info.algo == 0 and self.kind == "self" and self.tpctx() is not None:
+        if st.pop("_x_rows_dealt_out", False):
+            w = self.p("query_key_value.weight")
+            st["x"] = F.gathered_column_linear_fused(x, w.view(-1, w.shape[-1]), self.p("query_key_value.bias").view(-1),
+                                                     F.ACT_NONE, self.tpctx())
+        elif self.info.algo == 0 and self.kind == "self" and self.tpctx() is not None:
             w = self.p("query_key_value.weight")
             st["x"] = F.column_parallel_linear_fused(x, w.view(-1, w.shape[-1]), self.p("query_key_value.bias").view(-1),
                                                      F.ACT_NONE, self.tpctx())

@@ -269,6 +269,60 @@ def column_parallel_linear_fused(x, weight, bias, act, tpctx):
     return ColumnParallelLinearFusedFn.apply(x, weight, bias, act, tpctx)
 
 
+class GatheredColumnLinearFn(torch.autograd.Function):
+    """y_r = act(concat over the tp ranks of x_s . W_r^T + b_r) for an input whose ROWS are dealt out over the ranks of
+    the tensor-parallel group (the previous op ran data parallel over the same GPUs): the gather of the rows runs
+    inside the GEMM kernel (csrc/gemm_ag_sm100.cu, csrc/gemm2_sm100.cu), and the backward is the GEMM -> reduce-scatter
+    form of the fused GEMM + collective kernel, which leaves on every rank the input gradient of its own rows.
+
+    Reference counterpart: the dp -> tp case of tensor_adapter (all-gather of the rows, backward reduce-scatter;
+    runtime/megatron/mpu/mappings.py:382-468, 212-303) followed by ColumnParallelLinear
+    (runtime/megatron/mpu/layers.py:459-470)."""
+
+    @staticmethod
+    def forward(ctx, x_local, weight, bias, act, tpctx):
+        rows, K = x_local.shape
+        M = rows * tpctx.tp
+        need_pre = act in (ACT_GELU, ACT_RELU)
+        preact = torch.empty((M, weight.shape[0]), dtype=x_local.dtype, device=x_local.device) if need_pre else None
+        tpctx.ensure_allgather(M, K)
+        xl = x_local.contiguous()
+        y = tpctx.allgather_linear(xl, weight, bias=bias, act=act, preact_out=preact)
+        ctx.save_for_backward(tpctx.gathered_input(xl), weight, preact)
+        ctx.bias_ref, ctx.act, ctx.tpctx = bias, act, tpctx
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_full, weight, preact = ctx.saved_tensors
+        g = dy.contiguous()
+        if ctx.act in (ACT_GELU, ACT_RELU):
+            op = EW_BIAS_GELU_BWD if ctx.act == ACT_GELU else EW_RELU_BWD
+            g = native.ext().elementwise(op, preact, g, None, 0.0, 0)
+        # Every rank differentiates the mean loss of ITS rows: going back from the tensor-parallel region (one copy of
+        # the rows, data-parallel degree 1) to the ranks that hold tp disjoint row shares, the gradient is scaled by
+        # tp, so that the 1 / dp averaging of the parameter gradients upstream still yields the global mean (the
+        # relayout engine applies the same factor, parallel/relayout.py::plan_transfer)
+        dx = (ctx.tpctx.linear_reduce_scatter(g, weight, b_mn=True, alpha=float(ctx.tpctx.tp))
+              if ctx.needs_input_grad[0] else None)
+        dw = _wgrad(weight, g, x_full) if ctx.needs_input_grad[1] else None
+        db = _bgrad(ctx.bias_ref, g) if (ctx.bias_ref is not None and ctx.needs_input_grad[2]) else None
+        return dx, dw, db, None, None
+
+
+def gathered_column_linear_fused(x_local, weight, bias, act, tpctx):
+    return GatheredColumnLinearFn.apply(x_local, weight, bias, act, tpctx)
+
+
+def can_gather_in_gemm(x_local, tpctx) -> bool:
+    """Shapes the fused all-gather -> GEMM and GEMM -> reduce-scatter kernels take: whole 128-row blocks per rank, a
+    reduction length in whole 64-column tiles, and a fused scratch that holds the gathered product."""
+    if tpctx is None or x_local.dim() != 2 or not x_local.is_cuda:
+        return False
+    rows, K = x_local.shape
+    return rows % 128 == 0 and K % 64 == 0 and tpctx.fits(rows * tpctx.tp, K)
+
+
 class MLPFn(torch.autograd.Function):
     """y = residual + dropout(act(x W1^T + b1) W2^T + b2) with the activation derivative folded into the
     dgrad GEMM epilogue of the second layer (4 ops of the reference op list in 2 forward / 4 backward GEMMs:

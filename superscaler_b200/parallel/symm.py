@@ -185,6 +185,22 @@ class FusedTPContext:
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
 
+    def ensure_allgather(self, rows_total: int, k: int) -> None:
+        """Collective on first use (every rank of the group reaches it with the same arguments): makes the gather
+        scratch large enough for [rows_total, k]."""
+        if getattr(self, "ag_capacity", 0) < rows_total * k or getattr(self, "ag_max_blocks", 0) < -(-rows_total // self.TILE_M):
+            self.enable_allgather(rows_total, k)
+
+    def gathered_input(self, x_local: torch.Tensor) -> torch.Tensor:
+        """The full [rows * tp, K] input of the LAST allgather_linear call, as a tensor of its own: the peers' rows out
+        of this rank's gather scratch (every one of them has arrived when that kernel ends), this rank's rows from
+        `x_local` (the kernel reads them in place and never copies them)."""
+        rows, K = x_local.shape
+        M = rows * self.tp
+        full = self.ag_bufs[self.ag_epoch & 1][:M * K].view(M, K).clone()
+        full[self.rank * rows:(self.rank + 1) * rows] = x_local
+        return full
+
     def allgather_linear(self, x_local: torch.Tensor, w: torch.Tensor, *, bias=None, act: int = 0, preact_out=None,
                          out=None) -> torch.Tensor:
         """act(concat over the group of x_r . w^T + bias): rows of rank r land at [r * rows, (r + 1) * rows)."""

@@ -79,6 +79,19 @@ def _same_layout(side_a: Side, lay_a: Layout, side_b: Side, lay_b: Layout) -> bo
     return True
 
 
+def _rows_gather_in_gemm(op: Op, t: torch.Tensor, cur_side: Side, cur_lay: Layout, side: Side) -> bool:
+    """True when `t` holds this rank's share of rows dealt out over exactly the ranks of the op's tensor-parallel
+    group (previous op: tp 1, dp = this op's tp; this op: dp 1) and the op can take them as they are: the K4 / K5
+    path.  SSB_FUSED_GATHER=0 keeps the relayout engine (NCCL) for comparison."""
+    import os
+    if os.environ.get("SSB_FUSED_GATHER", "1") == "0" or not getattr(op, "accepts_dealt_out_rows", lambda: False)():
+        return False
+    if not (cur_side.first_rank == side.first_rank and cur_side.tp == 1 and side.dp == 1 and cur_side.dp == side.tp
+            and side.tp > 1 and cur_lay.row == "split"):
+        return False
+    return F.can_gather_in_gemm(t, op.tpctx())
+
+
 def run_op(op: Op, st: Dict[str, torch.Tensor]) -> None:
     """Brings every tensor the op reads to the layout it requires under the op's own (tp, dp) -- the in-stage
     resharding of the reference's pre_forward_tensor_adapter_hook (flex_model.py:250-300) -- then runs it."""
@@ -98,6 +111,12 @@ def run_op(op: Op, st: Dict[str, torch.Tensor]) -> None:
                 if cur_lay.groups != want.groups:
                     want = Layout(want.row, want.col, cur_lay.groups)
                 if not _same_layout(cur_side, cur_lay, side, want):
+                    if k == "x" and _rows_gather_in_gemm(op, t, cur_side, cur_lay, side):
+                        # dp -> tp: the consumer is a column-parallel GEMM that gathers the rows itself, inside its
+                        # kernel (and reduce-scatters the input gradient in its backward); nothing moves here
+                        st["_x_rows_dealt_out"] = True
+                        meta[k] = (side, want)
+                        continue
                     one_d = t.dim() == 1
                     moved = relayout(t.unsqueeze(0) if one_d else t, ps.rank, cur_side, cur_lay, side, want)
                     st[k] = moved.squeeze(0) if one_d else moved

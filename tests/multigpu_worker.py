@@ -80,6 +80,30 @@ def main():
         other = mine.clone()
         dist.broadcast(other, src=0)
         assert torch.equal(mine, other), "bf16 weights differ between ranks after the sharded update"
+        # dp -> tp inside a stage, right at the column-parallel GEMMs: LayerNorms, embedding and the head run data
+        # parallel, the attention block and the MLP tensor parallel.  The rows are then gathered INSIDE the QKV and MLP
+        # up-projection kernels and their input gradients reduce-scattered by the dgrad kernel; with SSB_FUSED_GATHER=0
+        # the relayout engine moves them with NCCL instead.  Both must train like the data-parallel run.
+        from superscaler_b200.models.gpt import gpt_op_names
+        names = gpt_op_names(kw["layers"])
+        mixed = tiny_gpt_plan(**kw, num_gpus=(world,), tp=[1])
+        mixed["model_parallel_size_of_each_op"] = [[world if (("attention" in n and "post" not in n) or "MLP-GEMM" in n
+                                                                or "MLP-gelu" in n) else 1 for n in names]]
+        mixed["data_parallel_size_of_each_op"] = [[world // t for t in mixed["model_parallel_size_of_each_op"][0]]]
+        mixed["resharding_stages"] = [True]
+        import os
+        for fused_gather in ("1", "0"):
+            os.environ["SSB_FUSED_GATHER"] = fused_gather
+            t = Trainer(mixed, rank=rank, world_size=world, model_overrides=nd, lr_warmup_steps=0, fused_comm=True)
+            out[f"mixed_gather{fused_gather}"] = [t.loss_value(t.train_step(gpt_batch(8, 256, 2048, seed=1))) for _ in range(3)]
+            if fused_gather == "1":
+                used = [type(o).__name__ for o in t.stage.ops if getattr(o, "accepts_dealt_out_rows", lambda: False)()]
+                assert used, "no op of the mixed plan takes dealt-out rows"
+            del t
+        os.environ.pop("SSB_FUSED_GATHER")
+        torch.cuda.synchronize()
+        assert native.check_status() == 0
+        assert max(abs(a - b) for a, b in zip(out["mixed_gather1"], out["mixed_gather0"])) < 2e-3, out
         base = out["dp"]
         for k, v in out.items():
             assert all(x == x for x in v) and v[-1] < v[0], (k, v)
@@ -124,6 +148,34 @@ def main():
         assert all(abs(v - gathered[0]) < 1e-3 * max(1.0, abs(gathered[0])) for v in gathered), gathered
         if rank == 0:
             print("GEMM_AR_OK worst rel err", round(worst, 5), flush=True)
+    elif mode == "gemm_rs":
+        # GEMM -> reduce-scatter form of the fused kernel against GEMM + NCCL reduce_scatter, interleaved with the
+        # all-reduce form on the same scratch (the "consumed" hand-shake keeps a fast rank from overwriting partials
+        # an owner still reads)
+        from superscaler_b200.ops import functional as F
+        from superscaler_b200.parallel.symm import FusedTPContext
+        ctx = FusedTPContext(None, 4096, 2048, dev)
+        worst = 0.0
+        for rep in range(3):
+            for (M, N, K, b_mn) in [(256 * world, 512, 256, False), (4096, 2048, 1024, True), (1024, 1024, 512, False)]:
+                g = torch.Generator(device=dev).manual_seed(31 * rank + M + N + rep)
+                x = (torch.randn(M, K, device=dev, generator=g) * 0.5).bfloat16()
+                w = (torch.randn((K, N) if b_mn else (N, K), device=dev, generator=g) * 0.1).bfloat16()
+                out = ctx.linear_reduce_scatter(x, w, b_mn=b_mn)
+                y = F.gemm(x, w, b_mn=b_mn, out_dtype=torch.float32)
+                ref = torch.empty(M // world, N, device=dev, dtype=torch.float32)
+                dist.reduce_scatter_tensor(ref, y)
+                full = ctx.linear_allreduce(x, w, b_mn=b_mn)          # the other form right behind it, same scratch
+                dist.all_reduce(y)
+                torch.cuda.synchronize()
+                scale = ref.abs().max().item()
+                err = (out.float() - ref).abs().max().item() / scale
+                err2 = (full.float() - y).abs().max().item() / y.abs().max().item()
+                worst = max(worst, err, err2)
+                assert err < 2e-2 and err2 < 2e-2, f"rank {rank} case {(M, N, K, b_mn)} rep {rep}: {err} {err2}"
+        assert native.check_status() == 0
+        if rank == 0:
+            print("GEMM_RS_OK worst rel err", round(worst, 5), flush=True)
     elif mode == "ag_gemm":
         from superscaler_b200.ops import functional as F
         from superscaler_b200.parallel.symm import FusedTPContext

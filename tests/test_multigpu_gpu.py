@@ -38,3 +38,8 @@ def test_fused_gemm_allreduce_matches_gemm_plus_nccl():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_allgather_gemm_matches_allgather_plus_gemm():
     assert "AG_GEMM_OK" in _launch("ag_gemm")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_gemm_reduce_scatter_matches_gemm_plus_nccl():
+    assert "GEMM_RS_OK" in _launch("gemm_rs")
