@@ -48,6 +48,9 @@ def parse():
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BS)
     ap.add_argument("--layers", type=int, default=None, help="debug only; a non-default value is reported")
     ap.add_argument("--fused-comm", type=int, default=1)
+    ap.add_argument("--fused-check", type=int, default=1,
+                    help="on 2 or more GPUs: check and time the fused GEMM + collective kernels against the NCCL path "
+                         "before the timed regions (reported under 'fused_collectives')")
     ap.add_argument("--deterministic", type=int, default=0,
                     help="1: bitwise-reproducible kernels (attention backward as the dK/dV + dQ kernel pair)")
     return ap.parse_args()
@@ -201,6 +204,16 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms[0].item() / n_steps, ms[1].item() / n_steps, clocks, native.launch_counter["kernels"]
 
+    # ---- 2 or more GPUs: the fused compute + collective kernels against the NCCL path (untimed) --------------
+    fused = None
+    if world > 1 and args.fused_check:
+        try:
+            from superscaler_b200.profiler import fused_bench
+            fused = fused_bench.run_in_bench(torch.device("cuda", local), rank, world)
+        except Exception as e:  # noqa: BLE001 - reported in the JSON line, the training benchmark goes on
+            fused = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+        barrier()
+
     # ---- device-timed region: batches resident on the device ----------------------------------
     resident = [trainer.to_device(gpt_batch(gbs, seq, vocab, seed=1000 + i)) for i in range(2)]
 
@@ -242,6 +255,8 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "clocks": clocks_e2e},
             "gpu_launches": launches,
         }
+        if fused is not None:
+            out["fused_collectives"] = fused
         if layers != GPT13B["num_layers"] or gbs != GLOBAL_BS:
             out["invalid_reduced_config"] = True
         print(json.dumps(out), flush=True)
