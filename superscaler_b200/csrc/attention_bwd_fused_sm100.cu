@@ -56,7 +56,7 @@ struct FusedCfg {
   static constexpr int kColS = 0, kColDP = 64, kColDQ = 128, kColDV = 256, kColDK = 384;
 };
 
-template <int HD, bool DROPOUT>
+template <int HD, bool DROPOUT, bool BIAS>
 __global__ void __launch_bounds__(kFusedThreads, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -295,6 +295,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const bool stats_vec = (p.SQ & 3) == 0;
     // shared-memory offsets of this thread's two 16-byte pieces of a [128][128 B] swizzled tile row: fixed for the
     // whole kernel (row r, pieces 2 g and 2 g + 1)
+    // score bias: bias2[q] = bias_table[head][kv - q + SQ - 1] log2(e); its gradient is dS summed along the diagonals
+    const int n_dist = p.SQ + p.SK - 1;
+    const float* bias_head = BIAS ? p.bias_table + static_cast<size_t>(head) * n_dist : nullptr;
+    float* dbias_head = BIAS ? p.dbias_table + static_cast<size_t>(head) * n_dist : nullptr;
     const uint32_t piece_a = static_cast<uint32_t>(r * 128 + (((2 * g) ^ (r & 7)) << 4));
     const uint32_t piece_b = static_cast<uint32_t>(r * 128 + (((2 * g + 1) ^ (r & 7)) << 4));
 
@@ -337,12 +341,18 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tc_fence_before_sync();
       warp_arrive(sdp_free, lane);  // the products of the next query block may overwrite S^T / dP^T now
       uint32_t wp[8], wd[8];
+      float dsv[BIAS ? 16 : 1];
 #pragma unroll
       for (int i = 0; i < 16; i += 2) {
         float pv[2], dv[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const float pr = ex2(fmaf(__uint_as_float(rs[i + e]), c, -lse2[i + e]));
+          float shift = -lse2[i + e];
+          if constexpr (BIAS) {
+            const int d = min(max(kv - (qbase + i + e) + p.SQ - 1, 0), n_dist - 1);
+            shift = fmaf(__ldg(bias_head + d), kLog2e, shift);
+          }
+          const float pr = ex2(fmaf(__uint_as_float(rs[i + e]), c, shift));
           const float dp = __uint_as_float(rp[i + e]);
           if constexpr (DROPOUT) {
             const float mk = keep_byte(hq[(i + e) >> 2], (i + e) & 3, keep8) ? inv_keep : 0.f;
@@ -362,6 +372,28 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
         wp[i >> 1] = pack_bf16x2(pv[0], pv[1]);
         wd[i >> 1] = pack_bf16x2(dv[0], dv[1]);
+        if constexpr (BIAS) {
+          dsv[i] = dv[0];
+          dsv[i + 1] = dv[1];
+        }
+      }
+      if constexpr (BIAS) {
+        // Gradient of the bias table: dS (before the softmax scale) summed along the diagonals key - query.  Lane l
+        // holds key kv and queries qbase .. qbase + 15; the diagonal through (l, i) continues at (l + 1, i + 1), so a
+        // running sum handed from lane l + 1 to lane l while i walks down collects a warp's share of every diagonal:
+        // at the end lane l holds the diagonal through (l, 0), and the diagonals that leave the warp at lane 0 are
+        // flushed as they complete.  47 reductions per warp and step instead of 512.
+        float run = 0.f;
+#pragma unroll
+        for (int i = 15; i >= 0; --i) {
+          run = dsv[i] + __shfl_down_sync(0xffffffffu, run, 1) * (lane < 31 ? 1.f : 0.f);
+          if (i > 0 && lane == 0) {
+            const int d = kv - (qbase + i) + p.SQ - 1;
+            if (d >= 0 && d < n_dist) atomicAdd(dbias_head + d, run);
+          }
+        }
+        const int d = kv - qbase + p.SQ - 1;
+        if (d >= 0 && d < n_dist) atomicAdd(dbias_head + d, run);
       }
       // P^T: read by dV of the previous block (queued at the start of this block).  This parity's dS^T chunk: read by
       // dK of block it - 2 and by dQ of the previous pair, which reads both chunks and was queued during this block
@@ -483,18 +515,18 @@ int set_smem(K kernel, int bytes) {
   return static_cast<int>(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
 }
 
-template <int HD, bool DROPOUT>
+template <int HD, bool DROPOUT, bool BIAS>
 int launch_fused(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                  const CUtensorMap& tacc, const AttnParams& p, const float* dq_acc, cudaStream_t stream) {
   static bool done = false;
   int rc;
   if (!done) {
-    if ((rc = set_smem(attn_bwd_fused_kernel<HD, DROPOUT>, FusedCfg<HD>::kSmem))) return rc;
+    if ((rc = set_smem(attn_bwd_fused_kernel<HD, DROPOUT, BIAS>, FusedCfg<HD>::kSmem))) return rc;
     done = true;
   }
   const int n_tiles = (p.SQ + 127) / 128;
   dim3 grid_kv((p.SK + 127) / 128, p.NH, p.B);
-  attn_bwd_fused_kernel<HD, DROPOUT><<<grid_kv, kFusedThreads, FusedCfg<HD>::kSmem, stream>>>(tq, tk, tv, tdo, tacc, p);
+  attn_bwd_fused_kernel<HD, DROPOUT, BIAS><<<grid_kv, kFusedThreads, FusedCfg<HD>::kSmem, stream>>>(tq, tk, tv, tdo, tacc, p);
   dim3 grid_cv((p.SQ * (HD / 8) + 255) / 256, p.NH, p.B);
   attn_dq_convert_kernel<HD><<<grid_cv, 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(p.dQ), p.lddq,
                                                           p.dq_col0, p.NH, p.SQ, n_tiles, p.scale);
@@ -543,11 +575,19 @@ int attn_bwd_fused_launch(const void* q, int ldq, const void* k, int ldk, const 
   if ((rc = make_tma_2d_bf16(&tv128, v, rk, ldv, ldv, 128, 64))) return rc;
   if ((rc = make_tma_2d_f32(&tacc, dq_acc, static_cast<uint64_t>(acc_rows), static_cast<uint64_t>(p.HD), 32))) return rc;
   const bool drop = p.dropout_p > 0.f;
+  if (p.bias_table != nullptr) {
+    if (p.dbias_table == nullptr) return -2;
+    if (p.HD == 128)
+      return drop ? launch_fused<128, true, true>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream)
+                  : launch_fused<128, false, true>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream);
+    return drop ? launch_fused<64, true, true>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream)
+                : launch_fused<64, false, true>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream);
+  }
   if (p.HD == 128)
-    return drop ? launch_fused<128, true>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream)
-                : launch_fused<128, false>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream);
-  return drop ? launch_fused<64, true>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream)
-              : launch_fused<64, false>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream);
+    return drop ? launch_fused<128, true, false>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream)
+                : launch_fused<128, false, false>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream);
+  return drop ? launch_fused<64, true, false>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream)
+              : launch_fused<64, false, false>(tq64, tk128, tv128, tdo64, tacc, pp, dq_acc, stream);
 }
 
 }  // namespace ssb

@@ -48,7 +48,7 @@ struct FwdCfg {
   static constexpr int kTmemCols = 512;  // S0 [0,128) S1 [128,256) O0 [256,256+HD) O1 [384,384+HD)
 };
 
-template <int HD>
+template <int HD, bool BIAS>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -207,6 +207,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t bh_seed = static_cast<uint32_t>(hash64(p.dropout_seed, static_cast<uint64_t>(b) * p.NH + head));
     const uint32_t qquads = (p.SQ + 3) >> 2;
     const int sub = lane & 3;  // position of this query in its quad: lanes 4t .. 4t+3 share the hashes of a key
+    // With a bias the logits are brought into the log2 domain first (x c + bias log2 e) and everything below works
+    // on them with a factor of one; without it the raw accumulator is used and the factor is c.
+    const float cc = BIAS ? 1.0f : c;
+    const float* bias_row = BIAS ? p.bias_table + static_cast<size_t>(head) * (p.SQ + p.SK - 1) + (p.SQ - 1) - min(q, p.SQ - 1)
+                                 : nullptr;
     float m = -INFINITY, l = 0.f, alpha_pending = 1.f;
     float o[OC];
 #pragma unroll
@@ -229,6 +234,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_32x32(tmem_base + lane_addr + st * 128 + g * 32, rr);
       tmem_ld_wait();
       float mx = -INFINITY;
+      if constexpr (BIAS) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float bv = __ldg(bias_row + min(kv0 + i, p.SK - 1));
+          rr[i] = __float_as_uint(fmaf(__uint_as_float(rr[i]), c, bv * kLog2e));
+        }
+      }
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -255,8 +267,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mx = fmaxf(fmaxf(xm[r], xm[128 + r]), fmaxf(xm[256 + r], xm[384 + r]));
       mx = fmaxf(mx, m);
       const float m_use = (mx == -INFINITY) ? 0.f : mx;  // fully masked so far: keep exponents finite
-      const float alpha = ex2((m - m_use) * c);         // m = -inf -> 0
-      const float mc = m_use * c;
+      const float alpha = ex2((m - m_use) * cc);        // m = -inf -> 0
+      const float mc = m_use * cc;
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t w[16];
       // each lane of a query quad hashes 8 of the 32 keys of this step (key = kv0 + 4 jj + sub); the quad exchanges them
@@ -270,7 +282,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         float pe[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          pe[e] = ex2(__uint_as_float(rr[i + e]) * c - mc);  // masked entries: ex2(-inf) = 0
+          pe[e] = ex2(__uint_as_float(rr[i + e]) * cc - mc);  // masked entries: ex2(-inf) = 0
           rs4[e] += pe[e];                                   // four partial sums: no 32-long dependent chain
         }
         if (p.dropout_p > 0.f) {
@@ -329,7 +341,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       // rows with no visible key get +inf so that the backward probabilities exp(s - lse) vanish
       if (g == 0)
-        p.LSE[(static_cast<size_t>(b) * p.NH + head) * p.SQ + q] = l > 0.f ? m * p.scale + logf(l) : INFINITY;
+        p.LSE[(static_cast<size_t>(b) * p.NH + head) * p.SQ + q] =
+            l > 0.f ? m * (BIAS ? 1.0f / kLog2e : p.scale) + logf(l) : INFINITY;
     }
   }
 
@@ -961,16 +974,16 @@ int attn_fwd_launch(const void* q, int ldq, const void* k, int ldk, const void* 
   if ((rc = make_tma_2d_bf16(&tk, k, static_cast<uint64_t>(p.B) * p.SK, ldk, ldk, 128, 64))) return rc;
   if ((rc = make_tma_2d_bf16(&tv, v, static_cast<uint64_t>(p.B) * p.SK, ldv, ldv, 128, 64))) return rc;
   dim3 grid((p.SQ + 127) / 128, p.NH, p.B);
-  if (p.HD == 128) {
-    static bool done = false;
-    if (!done) { if ((rc = set_smem(attn_fwd_kernel<128>, FwdCfg<128>::kSmem))) return rc; done = true; }
-    attn_fwd_kernel<128><<<grid, kAttnThreads, FwdCfg<128>::kSmem, stream>>>(tq, tk, tv, p);
-  } else {
-    static bool done = false;
-    if (!done) { if ((rc = set_smem(attn_fwd_kernel<64>, FwdCfg<64>::kSmem))) return rc; done = true; }
-    attn_fwd_kernel<64><<<grid, kAttnThreads, FwdCfg<64>::kSmem, stream>>>(tq, tk, tv, p);
-  }
-  return static_cast<int>(cudaGetLastError());
+  auto launch = [&](auto kernel, int smem) -> int {
+    int r = set_smem(kernel, smem);   // idempotent and cheap; set on every call so each instantiation is covered
+    if (r) return r;
+    kernel<<<grid, kAttnThreads, smem, stream>>>(tq, tk, tv, p);
+    return static_cast<int>(cudaGetLastError());
+  };
+  const bool bias = p.bias_table != nullptr;
+  if (p.HD == 128)
+    return bias ? launch(attn_fwd_kernel<128, true>, FwdCfg<128>::kSmem) : launch(attn_fwd_kernel<128, false>, FwdCfg<128>::kSmem);
+  return bias ? launch(attn_fwd_kernel<64, true>, FwdCfg<64>::kSmem) : launch(attn_fwd_kernel<64, false>, FwdCfg<64>::kSmem);
 }
 
 // dout shares the layout of O (p.ldo / p.o_col0 describe both).
@@ -978,6 +991,7 @@ int attn_bwd_launch(const void* q, int ldq, const void* k, int ldk, const void* 
                     int lddo, const AttnParams& p, float* delta_scratch, cudaStream_t stream) {
   if (p.HD != 64 && p.HD != 128) return -2;
   if (p.causal && p.SQ != p.SK) return -2;
+  if (p.bias_table != nullptr) return -2;  // the score bias exists in the forward and the fused backward kernel only
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (lddo % 8) || (p.lddq % 8) || (p.lddk % 8) || (p.lddv % 8)) return -3;
   int rc;
   if ((rc = attn_delta_launch(p, dout, lddo, delta_scratch, stream))) return rc;

@@ -26,6 +26,11 @@ struct AttnParams {
   void* dK; int lddk; int dk_col0;
   void* dV; int lddv; int dv_col0;
   int* status;
+  // Optional additive bias on the scores that depends on (head, key - query) only (relative-position bias):
+  // logits are scale * q.k + bias_table[head][key - query + SQ - 1]; fp32 [NH][SQ + SK - 1].  dbias_table, same
+  // shape, receives (accumulates) its gradient in the fused backward kernel.  Null: no bias.
+  const float* bias_table;
+  float* dbias_table;
 };
 
 }  // namespace ssb

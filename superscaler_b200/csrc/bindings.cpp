@@ -412,9 +412,11 @@ ssb::AttnParams attn_params(int64_t B, int64_t NH, int64_t SQ, int64_t SK, int64
 
 // q, k, v: 2-D bf16 matrices [B*S, ld] holding the heads at columns col0 + head*HD.
 // Returns (O [B*SQ, NH*HD], LSE [B, NH, SQ]).
+// bias_table (optional): fp32 [NH, SQ + SK - 1], added to the scaled scores as bias[head][key - query + SQ - 1].
 std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, int64_t B, int64_t NH, int64_t SQ,
                              int64_t SK, int64_t HD, int64_t q_col0, int64_t k_col0, int64_t v_col0, double scale,
-                             bool causal, const OptTensor& kv_lens, double dropout_p, int64_t seed) {
+                             bool causal, const OptTensor& kv_lens, double dropout_p, int64_t seed,
+                             const OptTensor& bias_table) {
   check_bf16_2d(q, "q"); check_bf16_2d(k, "k"); check_bf16_2d(v, "v");
   TORCH_CHECK(q.size(0) == B * SQ && k.size(0) == B * SK && v.size(0) == B * SK, "attention: row counts");
   c10::cuda::CUDAGuard guard(q.device());
@@ -422,6 +424,11 @@ std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, 
   Tensor o = torch::empty({B * SQ, NH * HD}, q.options());
   Tensor lse = torch::empty({B, NH, SQ}, torch::dtype(torch::kFloat32).device(q.device()));
   p.O = o.data_ptr(); p.ldo = static_cast<int>(o.stride(0)); p.o_col0 = 0; p.LSE = lse.data_ptr<float>();
+  if (bias_table.has_value()) {
+    TORCH_CHECK(bias_table->is_cuda() && bias_table->scalar_type() == torch::kFloat32 && bias_table->is_contiguous() &&
+                bias_table->numel() == NH * (SQ + SK - 1), "bias_table must be fp32 [NH, SQ + SK - 1]");
+    p.bias_table = bias_table->data_ptr<float>();
+  }
   check_launch(ssb::attn_fwd_launch(q.data_ptr(), static_cast<int>(q.stride(0)), k.data_ptr(), static_cast<int>(k.stride(0)),
                                     v.data_ptr(), static_cast<int>(v.stride(0)), p, cur_stream()),
                "attn_fwd");
@@ -436,7 +443,8 @@ bool g_attn_bwd_deterministic = false;
 void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& lse, const Tensor& dout,
               Tensor& dq, Tensor& dk, Tensor& dv, int64_t B, int64_t NH, int64_t SQ, int64_t SK, int64_t HD,
               int64_t q_col0, int64_t k_col0, int64_t v_col0, int64_t dq_col0, int64_t dk_col0, int64_t dv_col0,
-              double scale, bool causal, const OptTensor& kv_lens, double dropout_p, int64_t seed) {
+              double scale, bool causal, const OptTensor& kv_lens, double dropout_p, int64_t seed,
+              const OptTensor& bias_table, const OptTensor& dbias_table) {
   check_bf16_2d(q, "q"); check_bf16_2d(k, "k"); check_bf16_2d(v, "v"); check_bf16_2d(o, "o"); check_bf16_2d(dout, "dout");
   check_bf16_2d(dq, "dq"); check_bf16_2d(dk, "dk"); check_bf16_2d(dv, "dv");
   TORCH_CHECK(o.stride(0) == dout.stride(0), "o and dout must share a layout");
@@ -448,7 +456,15 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   p.dQ = dq.data_ptr(); p.lddq = static_cast<int>(dq.stride(0)); p.dq_col0 = static_cast<int>(dq_col0);
   p.dK = dk.data_ptr(); p.lddk = static_cast<int>(dk.stride(0)); p.dk_col0 = static_cast<int>(dk_col0);
   p.dV = dv.data_ptr(); p.lddv = static_cast<int>(dv.stride(0)); p.dv_col0 = static_cast<int>(dv_col0);
-  if (!g_attn_bwd_deterministic) {
+  if (bias_table.has_value()) {
+    TORCH_CHECK(dbias_table.has_value() && bias_table->scalar_type() == torch::kFloat32 && bias_table->is_contiguous() &&
+                dbias_table->scalar_type() == torch::kFloat32 && dbias_table->is_contiguous() &&
+                bias_table->numel() == NH * (SQ + SK - 1) && dbias_table->numel() == bias_table->numel(),
+                "bias_table / dbias_table must be fp32 [NH, SQ + SK - 1]");
+    p.bias_table = bias_table->data_ptr<float>();
+    p.dbias_table = dbias_table->data_ptr<float>();
+  }
+  if (!g_attn_bwd_deterministic || bias_table.has_value()) {
     // one kernel, five tile products; dQ is summed over the key blocks in an fp32 scratch in arrival order
     Tensor scratch = torch::empty({ssb::attn_bwd_fused_scratch_floats(B, NH, SQ, HD)},
                                   torch::dtype(torch::kFloat32).device(q.device()));

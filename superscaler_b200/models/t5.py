@@ -45,8 +45,10 @@ class T5Config:
     activation: int = F.ACT_GELU
     make_vocab_divisible_by: int = 128
     max_tp: int = 8
-    # T5 relative-position buckets in the self-attentions (reference path only until the attention kernels take the
-    # distance table); off = learned absolute positions alone, as in the reference's T5
+    # T5 relative-position buckets in the self-attentions: one learned [heads, buckets] table per stack, added to the
+    # scores through a per-head table over the distance key - query (the flash-attention kernels take that table);
+    # off = learned absolute positions alone, as in the reference's T5.  A plan turns it on with
+    # "relative_position_bias": true (the B200 definition of T5 770M does).
     relative_position_bias: bool = False
     relative_attention_num_buckets: int = 32
     relative_attention_max_distance: int = 128
@@ -140,6 +142,12 @@ def t5_config_from_plan(d: dict, **overrides) -> T5Config:
                    head_dim=d["kv_channels"], ffn=d["ffn_hidden_size"], seq_length=d["encoder_seq_length"],
                    dec_seq_length=d["decoder_seq_length"], max_positions=d["max_position_embeddings"],
                    vocab=d.get("vocab_size", 30592))
+    # optional keys of the B200 model definition (absent in plans of the reference's T5)
+    if d.get("relative_position_bias"):
+        cfg.relative_position_bias = True
+        cfg.relative_attention_num_buckets = int(d.get("relative_attention_num_buckets", 32))
+    if d.get("activation") in ("relu", "gelu"):
+        cfg.activation = F.ACT_RELU if d["activation"] == "relu" else F.ACT_GELU
     for k, v in overrides.items():
         setattr(cfg, k, v)
     return cfg

@@ -181,13 +181,16 @@ class _RelativeBias:
         """[local heads, sq, sk] fp32 (reference path; a kernel takes the distance table instead)."""
         from .relative_position import bias_from_table, distance_table
         c = self.env.cfg
+        return bias_from_table(self.relative_bias_table(sq, sk), sq, sk)
+
+    def relative_bias_table(self, sq: int, sk: int) -> torch.Tensor:
+        """[local heads, sq + sk - 1] fp32, differentiable: entry d - (sq - 1) ... the bias of distance key - query = d.
+        This is what the flash-attention kernels take (the bias depends on the distance alone)."""
+        from .relative_position import distance_table
+        c = self.env.cfg
         w = self.p("relative_attention_bias.weight")
-        if w.is_cuda:
-            raise NotImplementedError("relative-position bias on the GPU needs attention kernels that take the "
-                                      "per-head distance table; they are not built yet")
-        table = distance_table(w.float(), sq, sk, self.mode != "causal", c.relative_attention_num_buckets,
-                               c.relative_attention_max_distance)
-        return bias_from_table(table, sq, sk)
+        return distance_table(w.float(), sq, sk, self.mode != "causal", c.relative_attention_num_buckets,
+                              c.relative_attention_max_distance)
 
 
 class AttentionCoreOp(Op, _AttnDims, _RelativeBias):
@@ -211,7 +214,13 @@ class AttentionCoreOp(Op, _AttnDims, _RelativeBias):
         x = st["x"]
         b = x.shape[0] // self.sq
         scale = 1.0 / math.sqrt(hd)
-        if self.uses_relative_bias():
+        if self.uses_relative_bias() and x.is_cuda:
+            st["x"] = F.flash_attention(x, x, x, b, nh, self.sq, self.sq, hd, cols=(0, w, 2 * w), scale=scale,
+                                        causal=self.mode == "causal",
+                                        kv_lens=st.get("enc_lens") if self.mode == "full" else None,
+                                        dropout_p=p_drop, seed=self.seed(sharded=True),
+                                        bias_table=self.relative_bias_table(self.sq, self.sq))
+        elif self.uses_relative_bias():
             st["x"] = F.attention_with_bias(x, b, nh, self.sq, hd, scale, self.mode == "causal",
                                             st.get("enc_lens") if self.mode == "full" else None,
                                             self.relative_bias(self.sq, self.sq), p_drop)

@@ -508,18 +508,23 @@ class FlashAttnFn(torch.autograd.Function):
     (runtime/megatron/model/flex_ops.py:711-1015)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, B, NH, SQ, SK, HD, cols, scale, causal, kv_lens, dropout_p, seed):
+    def forward(ctx, q, k, v, B, NH, SQ, SK, HD, cols, scale, causal, kv_lens, dropout_p, seed, bias_table=None):
         qc, kc, vc = cols
+        ctx.has_bias = bias_table is not None
         if q.is_cuda:
+            bt = bias_table.float().contiguous() if bias_table is not None else None
             o, lse = native.ext().attn_fwd(q, k, v, B, NH, SQ, SK, HD, qc, kc, vc, scale, causal, kv_lens, dropout_p,
-                                           seed)
-            ctx.save_for_backward(q, k, v, o, lse, kv_lens if kv_lens is not None else torch.empty(0))
+                                           seed, bt)
+            ctx.save_for_backward(q, k, v, o, lse, kv_lens if kv_lens is not None else torch.empty(0),
+                                  bt if bt is not None else torch.empty(0))
         else:
+            assert bias_table is None, "the score bias exists on the GPU path and in attention_with_bias"
             assert dropout_p == 0.0, "dropout > 0 needs the GPU path"
             w = NH * HD
             o = _attn_reference(q[:, qc:qc + w], k[:, kc:kc + w], v[:, vc:vc + w], B, NH, SQ, SK, HD, scale, causal,
                                 kv_lens).to(q.dtype)
-            ctx.save_for_backward(q, k, v, o, torch.empty(0), kv_lens if kv_lens is not None else torch.empty(0))
+            ctx.save_for_backward(q, k, v, o, torch.empty(0), kv_lens if kv_lens is not None else torch.empty(0),
+                                  torch.empty(0))
         ctx.dims = (B, NH, SQ, SK, HD)
         ctx.cols, ctx.scale, ctx.causal, ctx.dropout_p, ctx.seed = cols, scale, causal, dropout_p, seed
         ctx.has_lens = kv_lens is not None
@@ -529,8 +534,10 @@ class FlashAttnFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, o, lse, kv_lens = ctx.saved_tensors
+        q, k, v, o, lse, kv_lens, bias_table = ctx.saved_tensors
         kv_lens = kv_lens if ctx.has_lens else None
+        bias_table = bias_table if ctx.has_bias else None
+        dbias = torch.zeros_like(bias_table) if bias_table is not None else None
         B, NH, SQ, SK, HD = ctx.dims
         qc, kc, vc = ctx.cols
         do = do.contiguous()
@@ -552,12 +559,12 @@ class FlashAttnFn(torch.autograd.Function):
             else:
                 dq, dk, dv = _grad_like(q, w), _grad_like(k, w), _grad_like(v, w)
             native.ext().attn_bwd(q, k, v, o, lse, do, dq, dk, dv, B, NH, SQ, SK, HD, qc, kc, vc, qc, kc, vc,
-                                  ctx.scale, ctx.causal, kv_lens, ctx.dropout_p, ctx.seed)
+                                  ctx.scale, ctx.causal, kv_lens, ctx.dropout_p, ctx.seed, bias_table, dbias)
             if ctx.same_qkv:
-                return (dq, None, None) + (None,) * 11
+                return (dq, None, None) + (None,) * 11 + (dbias,)
             if ctx.same_kv:
-                return (dq, dk, None) + (None,) * 11
-            return (dq, dk, dv) + (None,) * 11
+                return (dq, dk, None) + (None,) * 11 + (dbias,)
+            return (dq, dk, dv) + (None,) * 11 + (dbias,)
         w = NH * HD
         with torch.enable_grad():
             qq = q[:, qc:qc + w].detach().float().requires_grad_(True)
@@ -570,23 +577,25 @@ class FlashAttnFn(torch.autograd.Function):
         if ctx.same_qkv:
             dq[:, kc:kc + w] = gk.to(q.dtype)
             dq[:, vc:vc + w] = gv.to(q.dtype)
-            return (dq, None, None) + (None,) * 11
+            return (dq, None, None) + (None,) * 12
         dk = torch.zeros_like(k)
         dk[:, kc:kc + w] = gk.to(k.dtype)
         if ctx.same_kv:
             dk[:, vc:vc + w] = gv.to(k.dtype)
-            return (dq, dk, None) + (None,) * 11
+            return (dq, dk, None) + (None,) * 12
         dv = torch.zeros_like(v)
         dv[:, vc:vc + w] = gv.to(v.dtype)
-        return (dq, dk, dv) + (None,) * 11
+        return (dq, dk, dv) + (None,) * 12
 
 
 def flash_attention(q, k, v, B, NH, SQ, SK, HD, cols=(0, 0, 0), scale=None, causal=False, kv_lens=None,
-                    dropout_p=0.0, seed=0):
+                    dropout_p=0.0, seed=0, bias_table=None):
+    """bias_table (GPU path): fp32 [NH, SQ + SK - 1], differentiable; the scores of head h get
+    bias_table[h, key - query + SQ - 1] added after the scale (a relative-position bias as a table over the distance)."""
     if scale is None:
         scale = 1.0 / math.sqrt(HD)
     return FlashAttnFn.apply(q, k, v, B, NH, SQ, SK, HD, tuple(cols), float(scale), bool(causal), kv_lens,
-                             float(dropout_p), int(seed))
+                             float(dropout_p), int(seed), bias_table)
 
 
 def attention_with_bias(qkv, B, NH, S, HD, scale, causal, kv_lens, bias, dropout_p=0.0):

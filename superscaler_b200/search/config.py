@@ -160,6 +160,10 @@ def plan_to_dict(plan: Plan, model_name: str, model_size: str, num_layers: int, 
         d["ffn_hidden_size"] = ffn
         if shapes == "b200":
             d["vocab_size"] = _vocab
+            # the benchmark's T5: ReLU feed-forward, relative-position buckets instead of nothing but absolute positions
+            d["activation"] = "relu"
+            d["relative_position_bias"] = True
+            d["relative_attention_num_buckets"] = 32
     else:
         raise ValueError(f"unsupported model {model_name}")
     d["global_batch_size"] = plan.global_bs

@@ -420,3 +420,32 @@ def test_peer_wait_times_out_with_status_when_signal_is_withheld():
     a = torch.randn(256, 128, device=DEV).bfloat16()
     assert torch.isfinite(F.gemm(a, a).float()).all()
     assert native.check_status() == 0
+
+
+@pytest.mark.parametrize("cfg", [(2, 4, 256, 64, False, 0.0), (1, 2, 384, 64, True, 0.0), (2, 2, 256, 128, False, 0.0)])
+def test_flash_attention_relative_position_bias(cfg):
+    """Scores with a per-head bias that depends on key - query (T5 relative-position buckets): forward, dQ / dK / dV and
+    the gradient of the distance table against plain fp32 attention with the materialised [heads, S, S] bias."""
+    from superscaler_b200.models.relative_position import bias_from_table
+    B, NH, S, HD, causal, _ = cfg
+    torch.manual_seed(31)
+    h = NH * HD
+    qkv = (torch.randn(B * S, 3 * h, device=DEV) * 0.5).bfloat16()
+    table = (torch.randn(NH, 2 * S - 1, device=DEV) * 0.5)
+    lens = None if causal else torch.tensor([S, S - 37][:B] + [S] * (B - 2), device=DEV, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(HD)
+    do = torch.randn(B * S, h, device=DEV).bfloat16()
+    x = qkv.clone().requires_grad_(True)
+    t = table.clone().requires_grad_(True)
+    o = F.flash_attention(x, x, x, B, NH, S, S, HD, cols=(0, h, 2 * h), scale=scale, causal=causal, kv_lens=lens,
+                          bias_table=t)
+    o.backward(do)
+    xr = qkv.float().clone().requires_grad_(True)
+    tr = table.clone().requires_grad_(True)
+    ref = F.attention_with_bias(xr, B, NH, S, HD, scale, causal, lens, bias_from_table(tr, S, S))
+    ref.backward(do.float())
+    assert rel(o, ref) < 1e-2
+    for lo in (0, h, 2 * h):
+        assert rel(x.grad[:, lo:lo + h], xr.grad[:, lo:lo + h]) < 2e-2
+    assert rel(t.grad, tr.grad) < 2e-2
+    assert native.check_status() == 0

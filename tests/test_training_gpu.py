@@ -108,6 +108,19 @@ def test_t5_and_resnet_train_on_gpu():
                              global_bs=4, micro_bs=2), lr_warmup_steps=0)
     l = [t.loss_value(t.train_step(t5_batch(4, 256, 128, 2048, seed=1))) for _ in range(4)]
     assert all(x == x for x in l) and l[-1] < l[0]
+    # the benchmark's T5 definition: relative-position buckets (the kernels take them as a per-head distance table)
+    # and a ReLU feed-forward, switched on by optional keys of the plan
+    plan = tiny_t5_plan(layers=1, enc_seq=256, dec_seq=128, hidden=256, heads=4, head_dim=64, ffn=512, vocab=2048,
+                        global_bs=4, micro_bs=2)
+    plan.update(relative_position_bias=True, relative_attention_num_buckets=32, activation="relu")
+    tb = Trainer(plan, lr_warmup_steps=0, lr=1e-3)
+    assert tb.cfg.relative_position_bias
+    w0 = {k: v.clone() for k, v in tb.store.state_dict().items() if "relative_attention_bias" in k}
+    assert len(w0) == 2                                      # one table per stack
+    l = [tb.loss_value(tb.train_step(t5_batch(4, 256, 128, 2048, seed=1))) for _ in range(4)]
+    assert all(x == x for x in l) and l[-1] < l[0]
+    w1 = tb.store.state_dict()
+    assert all(not torch.equal(w0[k], w1[k]) for k in w0), "the relative-position tables received no gradient"
     r = Trainer(tiny_resnet_plan(in_channels=32, global_bs=16, micro_bs=8), model_overrides=dict(image_size=64, num_classes=16),
                 lr_warmup_steps=0, lr=1e-3)
     l = [r.loss_value(r.train_step(resnet_batch(16, 64, 16, seed=1))) for _ in range(4)]
