@@ -10,6 +10,8 @@ For N > 1 launch one rank per GPU:
 Model / config (fixed): 24 layers, hidden 2048, 16 heads x 128, FFN 8192 GeLU, pre-LayerNorm, seq 2048,
 vocab 51200, bf16 weights N(0, 0.02), dropout 0.1 (hidden and attention), Adam + clip 1.0, global batch 512;
 token ids uniform over [0, 51200) from a seed (synthetic).  Strong scaling: the global batch stays 512.
+`--model t5` / `--model resnet` run the other two model families of the reference's evaluation (T5 770M at global
+batch 512, Wide-ResNet 1B at global batch 768) through the same two timed regions with their committed plans.
 
 Two timed regions, W warm-up steps before each, K steps inside, CUDA events bracketed by barrier +
 synchronize, max over ranks:
@@ -42,6 +44,10 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="gpt", choices=["gpt", "t5", "resnet"],
+                    help="gpt (default, the headline): GPT-3 1.3B, global batch 512; t5: T5 770M (encoder 512 / decoder "
+                         "128 tokens, ReLU, relative-position buckets), global batch 512; resnet: Wide-ResNet 1B, global "
+                         "batch 768 -- each with the committed searched plan for N GPUs")
     ap.add_argument("--mbs-per-gpu", type=int, default=8)
     ap.add_argument("--plan", default=None, help="plan JSON (default: the committed searched plan for N GPUs, "
                                                  "else pure data parallel)")
@@ -160,17 +166,49 @@ def main():
     rank, world, local = init_distributed()
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     layers = args.layers or GPT13B["num_layers"]
+    here = os.path.dirname(os.path.abspath(__file__))
     if args.plan:
         with open(args.plan) as f:
             plan = json.load(f)
-    else:
+    elif args.model == "gpt":
         plan = default_plan(world, args.mbs_per_gpu, args.global_batch, layers)
+    else:
+        name = {"t5": "t5_770M", "resnet": "resnet_1B"}[args.model]
+        with open(os.path.join(here, "plans", f"{name}_{world}gpu_b200.json")) as f:
+            plan = json.load(f)
     if args.deterministic:
         from superscaler_b200.ops import functional as F
         F.set_deterministic(True)
-    trainer = Trainer(plan, rank=rank, world_size=world, fused_comm=bool(args.fused_comm),
-                      model_overrides=dict(vocab=GPT13B["vocab_size"]))
-    gbs, seq, vocab = plan["global_batch_size"], plan["seq_length"], GPT13B["vocab_size"]
+    overrides = dict(vocab=GPT13B["vocab_size"]) if args.model == "gpt" else {}
+    trainer = Trainer(plan, rank=rank, world_size=world, fused_comm=bool(args.fused_comm), model_overrides=overrides)
+    gbs = plan["global_batch_size"]
+    cfg = trainer.cfg
+    if args.model == "gpt":
+        seq, vocab = plan["seq_length"], GPT13B["vocab_size"]
+        make_batch = lambda seed: gpt_batch(gbs, seq, vocab, seed=seed)
+        metric = "samples/s (GPT-3 1.3B, GBS 512, searched plan)"
+        model_desc = "GPT-3 1.3B (24L, h2048, 16x128 heads, ffn 8192, seq 2048, vocab 51200, dropout 0.1)"
+        data_desc = "synthetic (token ids uniform over [0, 51200) from a seed; random-init weights)"
+        published = PUBLISHED_BASELINE
+    elif args.model == "t5":
+        from superscaler_b200.data.synthetic import t5_batch
+        seq = cfg.seq_length
+        make_batch = lambda seed: t5_batch(gbs, cfg.seq_length, cfg.dec_seq_length, cfg.vocab, seed=seed)
+        metric = "samples/s (T5 770M, GBS 512, searched plan)"
+        model_desc = (f"T5 770M ({cfg.num_layers}+{cfg.num_layers}L, d_model {cfg.hidden}, {cfg.heads}x{cfg.head_dim} heads, "
+                      f"d_ff {cfg.ffn} ReLU, relative-position buckets {cfg.relative_attention_num_buckets if cfg.relative_position_bias else 0}, "
+                      f"vocab {cfg.vocab}, encoder {cfg.seq_length} / decoder {cfg.dec_seq_length} tokens)")
+        data_desc = "synthetic (token ids uniform from a seed; random-init weights)"
+        published = 15.14      # reference README.md:132, 4 unnamed GPUs
+    else:
+        from superscaler_b200.data.synthetic import resnet_batch
+        seq = cfg.image_size
+        make_batch = lambda seed: resnet_batch(gbs, cfg.image_size, cfg.num_classes, seed=seed)
+        metric = "samples/s (Wide-ResNet 1B, GBS 768, searched plan)"
+        model_desc = (f"Wide-ResNet 1B (bottleneck ResNet-50 layout, base channels {plan['in_channels']}, width factor "
+                      f"{plan['width_factor']}, {cfg.num_classes} classes, {cfg.image_size}x{cfg.image_size}x3 images)")
+        data_desc = "synthetic (images N(0,1), labels uniform, from a seed; Kaiming random-init weights)"
+        published = 41.52      # reference README.md:135, 4 unnamed GPUs
 
     def barrier():
         if world > 1:
@@ -215,7 +253,7 @@ def main():
         barrier()
 
     # ---- device-timed region: batches resident on the device ----------------------------------
-    resident = [trainer.to_device(gpt_batch(gbs, seq, vocab, seed=1000 + i)) for i in range(2)]
+    resident = [trainer.to_device(make_batch(1000 + i)) for i in range(2)]
 
     def step_resident(i):
         trainer.train_step(resident[i % 2])
@@ -224,7 +262,7 @@ def main():
     del resident
 
     # ---- end-to-end region: pinned host batch -> device every step, loss read back every step ---
-    host = [gpt_batch(gbs, seq, vocab, seed=2000 + i) for i in range(2)]
+    host = [make_batch(2000 + i) for i in range(2)]
     last_loss = [0.0]
 
     def step_e2e(i):
@@ -239,15 +277,15 @@ def main():
         value = gbs / (ms_dev / 1000.0)
         e2e_value = gbs / (max(ms_e2e, wall_e2e) / 1000.0)
         out = {
-            "metric": "samples/s (GPT-3 1.3B, GBS 512, searched plan)", "value": round(value, 3), "unit": "samples/s",
+            "metric": metric, "value": round(value, 3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_dev, 2),
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": round(value / PUBLISHED_BASELINE, 3),
-            "dtype": "bf16", "data": "synthetic (token ids uniform over [0, 51200) from a seed; random-init weights)",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": round(value / published, 3),
+            "dtype": "bf16", "data": data_desc,
             "impl": "ours",
-            "config": {"model": "GPT-3 1.3B (24L, h2048, 16x128 heads, ffn 8192, seq 2048, vocab 51200, dropout 0.1)",
+            "config": {"model": model_desc,
                        "global_batch": gbs, "seq_len": seq, "parallelism": describe_parallelism(plan),
                        "num_microbatches": trainer.num_microbatches, "l2": "inputs_exceed_l2 (2.6 GB of weights + "
-                       "activations stream through every step)", "layers": layers,
+                       "activations stream through every step)", "layers": layers if args.model == "gpt" else plan["num_layers"],
                        "params": trainer.num_parameters(), "kernel_status": status, "last_loss": round(last_loss[0], 4),
                        "max_allocated_mb": round(torch.cuda.max_memory_allocated() / 2 ** 20)},
             "clocks": clocks,
@@ -257,7 +295,7 @@ def main():
         }
         if fused is not None:
             out["fused_collectives"] = fused
-        if layers != GPT13B["num_layers"] or gbs != GLOBAL_BS:
+        if args.model == "gpt" and (layers != GPT13B["num_layers"] or gbs != GLOBAL_BS):
             out["invalid_reduced_config"] = True
         print(json.dumps(out), flush=True)
     if world > 1:

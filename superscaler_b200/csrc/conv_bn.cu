@@ -146,33 +146,57 @@ subsample_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict
 }
 
 // ------------------------------------ BatchNorm ---------------------------------------------
+// Layout of the partial-sum kernels: eight threads cover 128 contiguous bytes of a row (eight channels each), the
+// 32 thread groups of a block take every 32nd row of the slice, and the 32 partial sums of a channel meet in shared
+// memory at the end.
+__device__ __forceinline__ void bn_fold_and_store(float (&acc1)[8], float (&acc2)[8], float* __restrict__ part, int C,
+                                                  int c_block0) {
+  __shared__ float red[2][32][64];
+  const int lane8 = threadIdx.x & 7, rowlane = threadIdx.x >> 3;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    red[0][rowlane][lane8 * 8 + j] = acc1[j];
+    red[1][rowlane][lane8 * 8 + j] = acc2[j];
+  }
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const int which = threadIdx.x >> 6, ch = threadIdx.x & 63;
+    float t = 0.f;
+#pragma unroll 8
+    for (int k = 0; k < 32; ++k) t += red[which][k][ch];
+    if (c_block0 + ch < C) part[(static_cast<long long>(blockIdx.y) * 2 + which) * C + c_block0 + ch] = t;
+  }
+}
+
 // part[slice][0][c] = sum x, part[slice][1][c] = sum x^2 over the slice's rows; x is [rows, C].
 __global__ void __launch_bounds__(256)
 bn_stats_partial_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ part, long long rows, int C,
                         int rows_per_slice) {
-  __shared__ float s1[8][64], s2[8][64];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int col = (blockIdx.x * 32 + tx) * 2;
+  const int c0 = (blockIdx.x * 8 + (threadIdx.x & 7)) * 8;
   const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_slice;
   const long long r1 = min(rows, r0 + rows_per_slice);
-  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
-  if (col < C) {
-    for (long long r = r0 + ty; r < r1; r += 8) {
-      const float2 v = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + r * C + col));
-      a0 += v.x; a1 += v.y; b0 += v.x * v.x; b1 += v.y * v.y;
-    }
-  }
-  s1[ty][tx * 2] = a0; s1[ty][tx * 2 + 1] = a1; s2[ty][tx * 2] = b0; s2[ty][tx * 2 + 1] = b1;
-  __syncthreads();
-  if (ty == 0 && col < C) {
-    float c0 = 0.f, c1 = 0.f, d0 = 0.f, d1 = 0.f;
+  float a[8], b[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      c0 += s1[k][tx * 2]; c1 += s1[k][tx * 2 + 1]; d0 += s2[k][tx * 2]; d1 += s2[k][tx * 2 + 1];
+  for (int j = 0; j < 8; ++j) a[j] = b[j] = 0.f;
+  if (c0 < C) {
+    long long r = r0 + (threadIdx.x >> 3);
+    for (; r + 96 < r1; r += 128) {                 // four independent rows in flight per thread
+      float v[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) ld8(x + (r + 32 * u) * C + c0, v[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { a[j] += v[u][j]; b[j] += v[u][j] * v[u][j]; }
     }
-    float* p = part + static_cast<long long>(blockIdx.y) * 2 * C;
-    p[col] = c0; p[col + 1] = c1; p[C + col] = d0; p[C + col + 1] = d1;
+    for (; r < r1; r += 32) {
+      float v[8];
+      ld8(x + r * C + c0, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { a[j] += v[j]; b[j] += v[j] * v[j]; }
+    }
   }
+  bn_fold_and_store(a, b, part, C, blockIdx.x * 64);
 }
 
 // mean / rstd per channel from the partials; also updates the running statistics.
@@ -198,31 +222,72 @@ __global__ void bn_stats_final_kernel(const float* __restrict__ part, int slices
   }
 }
 
+// Thread layout of the two element-wise BatchNorm passes: eight consecutive threads cover 128 contiguous bytes of a
+// row (eight channels each), a block of 256 threads covers 32 rows of one 64-channel column block and walks down
+// the rows.  A thread's channels never change, so the per-channel constants are loaded once into registers; an
+// earlier form that recomputed the channel from a flat index read them again for every 16 bytes of data, and those
+// reads (a kilobyte per warp and array) kept the L1 busy while DRAM ran at 11 % of its peak.
+constexpr int kBnRowsPerBlock = 32;
+inline dim3 bn_grid(long long rows, int C, int num_sms) {
+  const int gx = (C / 8 + 7) / 8;
+  long long gy = (rows + kBnRowsPerBlock - 1) / kBnRowsPerBlock;
+  const long long cap = (static_cast<long long>(num_sms) * 16 + gx - 1) / gx;
+  if (gy > cap) gy = cap;
+  if (gy < 1) gy = 1;
+  if (gy > 65535) gy = 65535;
+  return dim3(gx, static_cast<unsigned>(gy));
+}
+
 // y = [relu]((x - mean) * rstd * gamma + beta [+ residual])
 __global__ void __launch_bounds__(256)
 bn_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
                 const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ gamma,
                 const float* __restrict__ beta, __nv_bfloat16* __restrict__ y, long long rows, int C, int relu) {
-  const int cvec = C / 8;
-  const long long total = rows * cvec;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int c0 = static_cast<int>(i % cvec) * 8;
-    float f[8], o[8];
-    ld8(x + i * 8, f);
+  const int cv = blockIdx.x * 8 + (threadIdx.x & 7);
+  if (cv >= C / 8) return;
+  const int c0 = cv * 8;
+  float a[8], b[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = (f[j] - mean[c0 + j]) * rstd[c0 + j] * gamma[c0 + j] + beta[c0 + j];
+  for (int j = 0; j < 8; ++j) {
+    a[j] = rstd[c0 + j] * gamma[c0 + j];
+    b[j] = beta[c0 + j] - mean[c0 + j] * a[j];
+  }
+  const long long stride = static_cast<long long>(gridDim.y) * kBnRowsPerBlock;
+  long long r = static_cast<long long>(blockIdx.y) * kBnRowsPerBlock + (threadIdx.x >> 3);
+  auto finish = [&](long long row, float (&f)[8], const float (&res)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      f[j] = f[j] * a[j] + b[j] + res[j];
+      if (relu) f[j] = fmaxf(f[j], 0.f);
+    }
+    st8(y + row * C + c0, f);
+  };
+  for (; r + 3 * stride < rows; r += 4 * stride) {   // four independent rows in flight per thread
+    float f[4][8], q[4][8];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) ld8(x + (r + u * stride) * C + c0, f[u]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (residual != nullptr) {
+        ld8(residual + (r + u * stride) * C + c0, q[u]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[u][j] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) finish(r + u * stride, f[u], q[u]);
+  }
+  for (; r < rows; r += stride) {
+    float f[8], q[8];
+    ld8(x + r * C + c0, f);
     if (residual != nullptr) {
-      float r[8];
-      ld8(residual + i * 8, r);
+      ld8(residual + r * C + c0, q);
+    } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] += r[j];
+      for (int j = 0; j < 8; ++j) q[j] = 0.f;
     }
-    if (relu) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = fmaxf(o[j], 0.f);
-    }
-    st8(y + i * 8, o);
+    finish(r, f, q);
   }
 }
 
@@ -232,37 +297,55 @@ bn_bwd_partial_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
                       const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
                       const float* __restrict__ rstd, float* __restrict__ part, long long rows, int C,
                       int rows_per_slice, int relu) {
-  __shared__ float s1[8][64], s2[8][64];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int col = (blockIdx.x * 32 + tx) * 2;
+  const int c0 = (blockIdx.x * 8 + (threadIdx.x & 7)) * 8;
   const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_slice;
   const long long r1 = min(rows, r0 + rows_per_slice);
-  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
-  if (col < C) {
-    const float m0 = mean[col], m1 = mean[col + 1], q0 = rstd[col], q1 = rstd[col + 1];
-    for (long long r = r0 + ty; r < r1; r += 8) {
-      float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dy + r * C + col));
-      const float2 v = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + r * C + col));
-      if (relu) {
-        const float2 o = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(y + r * C + col));
-        if (!(o.x > 0.f)) g.x = 0.f;
-        if (!(o.y > 0.f)) g.y = 0.f;
-      }
-      a0 += g.x; a1 += g.y;
-      b0 += g.x * (v.x - m0) * q0; b1 += g.y * (v.y - m1) * q1;
-    }
-  }
-  s1[ty][tx * 2] = a0; s1[ty][tx * 2 + 1] = a1; s2[ty][tx * 2] = b0; s2[ty][tx * 2 + 1] = b1;
-  __syncthreads();
-  if (ty == 0 && col < C) {
-    float c0 = 0.f, c1 = 0.f, d0 = 0.f, d1 = 0.f;
+  float a[8], b[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      c0 += s1[k][tx * 2]; c1 += s1[k][tx * 2 + 1]; d0 += s2[k][tx * 2]; d1 += s2[k][tx * 2 + 1];
+  for (int j = 0; j < 8; ++j) a[j] = b[j] = 0.f;
+  if (c0 < C) {
+    float m[8], q[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { m[j] = mean[c0 + j]; q[j] = rstd[c0 + j]; }
+    auto add = [&](float (&g)[8], const float (&v)[8], const float (&o)[8]) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (relu && !(o[j] > 0.f)) g[j] = 0.f;
+        a[j] += g[j];
+        b[j] += g[j] * (v[j] - m[j]) * q[j];
+      }
+    };
+    long long r = r0 + (threadIdx.x >> 3);
+    for (; r + 32 < r1; r += 64) {                  // two independent rows (up to six loads) in flight per thread
+      float g[2][8], v[2][8], o[2][8];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        ld8(dy + (r + 32 * u) * C + c0, g[u]);
+        ld8(x + (r + 32 * u) * C + c0, v[u]);
+        if (relu) {
+          ld8(y + (r + 32 * u) * C + c0, o[u]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[u][j] = 1.f;
+        }
+      }
+      add(g[0], v[0], o[0]);
+      add(g[1], v[1], o[1]);
     }
-    float* p = part + static_cast<long long>(blockIdx.y) * 2 * C;
-    p[col] = c0; p[col + 1] = c1; p[C + col] = d0; p[C + col + 1] = d1;
+    for (; r < r1; r += 32) {
+      float g[8], v[8], o[8];
+      ld8(dy + r * C + c0, g);
+      ld8(x + r * C + c0, v);
+      if (relu) {
+        ld8(y + r * C + c0, o);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = 1.f;
+      }
+      add(g, v, o);
+    }
   }
+  bn_fold_and_store(a, b, part, C, blockIdx.x * 64);
 }
 
 // sums[0][c] = sum g, sums[1][c] = sum g*xhat; dgamma (+)= sums[1], dbeta (+)= sums[0]
@@ -281,36 +364,64 @@ __global__ void bn_bwd_final_kernel(const float* __restrict__ part, int slices, 
   dgamma[c] = accumulate ? dgamma[c] + q : q;
 }
 
-// dx = gamma * rstd * (g - mean(g) - xhat * mean(g * xhat)); dres = g (when a residual was added)
+// dx = gamma * rstd * (g - mean(g) - xhat * mean(g * xhat)); dres = g (when a residual was added).
+// Per channel this is dx = A g + B x + D with A = gamma rstd, B = -A rstd mean(g xhat), D = -A mean(g) - B mean.
 __global__ void __launch_bounds__(256)
 bn_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                  const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean, const float* __restrict__ rstd,
                  const float* __restrict__ gamma, const float* __restrict__ sums, __nv_bfloat16* __restrict__ dx,
                  __nv_bfloat16* __restrict__ dres, long long rows, int C, int relu) {
-  const int cvec = C / 8;
-  const long long total = rows * cvec;
+  const int cv = blockIdx.x * 8 + (threadIdx.x & 7);
+  if (cv >= C / 8) return;
+  const int c0 = cv * 8;
   const float inv_n = 1.0f / static_cast<float>(rows);
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int c0 = static_cast<int>(i % cvec) * 8;
-    float g[8], v[8], o[8];
-    ld8(dy + i * 8, g);
-    ld8(x + i * 8, v);
-    if (relu) {
-      float yy[8];
-      ld8(y + i * 8, yy);
+  float A[8], Bc[8], D[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (!(yy[j] > 0.f)) g[j] = 0.f;
-    }
+  for (int j = 0; j < 8; ++j) {
+    const int c = c0 + j;
+    A[j] = gamma[c] * rstd[c];
+    Bc[j] = -A[j] * rstd[c] * sums[C + c] * inv_n;
+    D[j] = -A[j] * sums[c] * inv_n - Bc[j] * mean[c];
+  }
+  const long long stride = static_cast<long long>(gridDim.y) * kBnRowsPerBlock;
+  long long r = static_cast<long long>(blockIdx.y) * kBnRowsPerBlock + (threadIdx.x >> 3);
+  auto finish = [&](long long row, float (&g)[8], const float (&v)[8], const float (&yy)[8]) {
+    float o[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int c = c0 + j;
-      const float xhat = (v[j] - mean[c]) * rstd[c];
-      o[j] = gamma[c] * rstd[c] * (g[j] - sums[c] * inv_n - xhat * sums[C + c] * inv_n);
+      if (relu && !(yy[j] > 0.f)) g[j] = 0.f;
+      o[j] = A[j] * g[j] + Bc[j] * v[j] + D[j];
     }
-    st8(dx + i * 8, o);
-    if (dres != nullptr) st8(dres + i * 8, g);
+    st8(dx + row * C + c0, o);
+    if (dres != nullptr) st8(dres + row * C + c0, g);
+  };
+  for (; r + stride < rows; r += 2 * stride) {       // two independent rows (up to six loads) in flight per thread
+    float g[2][8], v[2][8], yy[2][8];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      ld8(dy + (r + u * stride) * C + c0, g[u]);
+      ld8(x + (r + u * stride) * C + c0, v[u]);
+      if (relu) {
+        ld8(y + (r + u * stride) * C + c0, yy[u]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) yy[u][j] = 1.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) finish(r + u * stride, g[u], v[u], yy[u]);
+  }
+  for (; r < rows; r += stride) {
+    float g[8], v[8], yy[8];
+    ld8(dy + r * C + c0, g);
+    ld8(x + r * C + c0, v);
+    if (relu) {
+      ld8(y + r * C + c0, yy);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) yy[j] = 1.f;
+    }
+    finish(r, g, v, yy);
   }
 }
 
@@ -319,54 +430,72 @@ bn_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
 __global__ void __launch_bounds__(256)
 maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ idx,
                    int N, int H, int W, int C) {
-  const int Ho = (H + 1) / 2, Wo = (W + 1) / 2;
-  const long long total = static_cast<long long>(N) * Ho * Wo * C;
+  // eight channels per thread: 16-byte loads of up to nine taps, one 16-byte store of y and one 8-byte store of idx
+  const int Ho = (H + 1) / 2, Wo = (W + 1) / 2, cvec = C / 8;
+  const long long total = static_cast<long long>(N) * Ho * Wo * cvec;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int c = static_cast<int>(i % C);
-    long long pix = i / C;
+    const int c0 = static_cast<int>(i % cvec) * 8;
+    const long long pix = i / cvec;
     const int wo = static_cast<int>(pix % Wo), ho = static_cast<int>((pix / Wo) % Ho);
     const long long n = pix / (static_cast<long long>(Wo) * Ho);
-    float best = -INFINITY;
-    int arg = 4;
+    float best[8];
+    uint32_t arg[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { best[j] = -INFINITY; arg[j] = 4; }
+#pragma unroll
     for (int r = 0; r < 3; ++r)
-      for (int s = 0; s < 3; ++s) {
-        const int h = ho * 2 + r - 1, w = wo * 2 + s - 1;
+#pragma unroll
+      for (int t = 0; t < 3; ++t) {
+        const int h = ho * 2 + r - 1, w = wo * 2 + t - 1;
         if (h < 0 || h >= H || w < 0 || w >= W) continue;
-        const float v = __bfloat162float(x[((n * H + h) * W + w) * C + c]);
-        if (v > best) { best = v; arg = r * 3 + s; }
+        float v[8];
+        ld8(x + ((n * H + h) * W + w) * C + c0, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (v[j] > best[j]) { best[j] = v[j]; arg[j] = r * 3 + t; }
       }
-    y[i] = __float2bfloat16(best);
-    idx[i] = static_cast<uint8_t>(arg);
+    st8(y + pix * C + c0, best);
+    uint2 packed;
+    packed.x = arg[0] | (arg[1] << 8) | (arg[2] << 16) | (arg[3] << 24);
+    packed.y = arg[4] | (arg[5] << 8) | (arg[6] << 16) | (arg[7] << 24);
+    *reinterpret_cast<uint2*>(idx + pix * C + c0) = packed;
   }
 }
 
 __global__ void __launch_bounds__(256)
 maxpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const uint8_t* __restrict__ idx,
                    __nv_bfloat16* __restrict__ dx, int N, int H, int W, int C) {
-  const int Ho = (H + 1) / 2, Wo = (W + 1) / 2;
-  const long long total = static_cast<long long>(N) * H * W * C;
+  const int Ho = (H + 1) / 2, Wo = (W + 1) / 2, cvec = C / 8;
+  const long long total = static_cast<long long>(N) * H * W * cvec;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int c = static_cast<int>(i % C);
-    long long pix = i / C;
+    const int c0 = static_cast<int>(i % cvec) * 8;
+    const long long pix = i / cvec;
     const int w = static_cast<int>(pix % W), h = static_cast<int>((pix / W) % H);
     const long long n = pix / (static_cast<long long>(W) * H);
-    float acc = 0.f;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     // output windows (ho, wo) that contain (h, w): ho*2 - 1 <= h <= ho*2 + 1
-    for (int ho = (h) / 2; ho <= (h + 1) / 2; ++ho) {
-      if (ho < 0 || ho >= Ho) continue;
-      const int r = h - ho * 2 + 1;
-      if (r < 0 || r > 2) continue;
-      for (int wo = (w) / 2; wo <= (w + 1) / 2; ++wo) {
-        if (wo < 0 || wo >= Wo) continue;
-        const int s = w - wo * 2 + 1;
-        if (s < 0 || s > 2) continue;
-        const long long o = ((n * Ho + ho) * Wo + wo) * C + c;
-        if (idx[o] == r * 3 + s) acc += __bfloat162float(dy[o]);
+    for (int ho = h / 2; ho <= (h + 1) / 2; ++ho) {
+      if (ho >= Ho) continue;
+      const uint32_t r = h - ho * 2 + 1;
+      for (int wo = w / 2; wo <= (w + 1) / 2; ++wo) {
+        if (wo >= Wo) continue;
+        const uint32_t tap = r * 3 + (w - wo * 2 + 1);
+        const long long o = ((n * Ho + ho) * Wo + wo) * C + c0;
+        const uint2 packed = *reinterpret_cast<const uint2*>(idx + o);
+        float g[8];
+        ld8(dy + o, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t a = ((j < 4 ? packed.x : packed.y) >> (8 * (j & 3))) & 0xFFu;
+          if (a == tap) acc[j] += g[j];
+        }
       }
     }
-    dx[i] = __float2bfloat16(acc);
+    st8(dx + pix * C + c0, acc);
   }
 }
 
@@ -449,11 +578,11 @@ int bn_fwd_launch(const void* x, const void* residual, const float* gamma, const
   if (C % 8) return -3;
   const int slices = bn_slices(rows);
   const int rps = static_cast<int>((rows + slices - 1) / slices);
-  dim3 grid((C / 2 + 31) / 32, slices);
+  dim3 grid((C / 8 + 7) / 8, slices);
   bn_stats_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), part, rows, C, rps);
   bn_stats_final_kernel<<<(C + 255) / 256, 256, 0, stream>>>(part, slices, C, rows, eps, momentum, mean, rstd,
                                                              run_mean, run_var);
-  bn_apply_kernel<<<grid_for(rows * (C / 8), num_sms), 256, 0, stream>>>(
+  bn_apply_kernel<<<bn_grid(rows, C, num_sms), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(residual), mean, rstd, gamma,
       beta, reinterpret_cast<__nv_bfloat16*>(y), rows, C, relu);
   return static_cast<int>(cudaGetLastError());
@@ -464,7 +593,7 @@ int bn_fwd_launch(const void* x, const void* residual, const float* gamma, const
 int bn_apply_launch(const void* x, const void* residual, const float* mean, const float* rstd, const float* gamma,
                     const float* beta, void* y, long long rows, int C, int relu, int num_sms, cudaStream_t stream) {
   if (C % 8) return -3;
-  bn_apply_kernel<<<grid_for(rows * (C / 8), num_sms), 256, 0, stream>>>(
+  bn_apply_kernel<<<bn_grid(rows, C, num_sms), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(residual), mean, rstd, gamma,
       beta, reinterpret_cast<__nv_bfloat16*>(y), rows, C, relu);
   return static_cast<int>(cudaGetLastError());
@@ -477,13 +606,13 @@ int bn_bwd_launch(const void* dy, const void* x, const void* y, const float* mea
   if (C % 8) return -3;
   const int slices = bn_slices(rows);
   const int rps = static_cast<int>((rows + slices - 1) / slices);
-  dim3 grid((C / 2 + 31) / 32, slices);
+  dim3 grid((C / 8 + 7) / 8, slices);
   bn_bwd_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
                                                   reinterpret_cast<const __nv_bfloat16*>(x),
                                                   reinterpret_cast<const __nv_bfloat16*>(y), mean, rstd, part, rows,
                                                   C, rps, relu);
   bn_bwd_final_kernel<<<(C + 255) / 256, 256, 0, stream>>>(part, slices, C, sums, dgamma, dbeta, accumulate);
-  bn_bwd_dx_kernel<<<grid_for(rows * (C / 8), num_sms), 256, 0, stream>>>(
+  bn_bwd_dx_kernel<<<bn_grid(rows, C, num_sms), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
       reinterpret_cast<const __nv_bfloat16*>(y), mean, rstd, gamma, sums, reinterpret_cast<__nv_bfloat16*>(dx),
       reinterpret_cast<__nv_bfloat16*>(dres), rows, C, relu);
@@ -491,7 +620,8 @@ int bn_bwd_launch(const void* dy, const void* x, const void* y, const float* mea
 }
 
 int maxpool_fwd_launch(const void* x, void* y, void* idx, int N, int H, int W, int C, int num_sms, cudaStream_t stream) {
-  const long long work = static_cast<long long>(N) * ((H + 1) / 2) * ((W + 1) / 2) * C;
+  if (C % 8) return -3;
+  const long long work = static_cast<long long>(N) * ((H + 1) / 2) * ((W + 1) / 2) * (C / 8);
   maxpool_fwd_kernel<<<grid_for(work, num_sms), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x),
                                                                   reinterpret_cast<__nv_bfloat16*>(y),
                                                                   reinterpret_cast<uint8_t*>(idx), N, H, W, C);
@@ -499,7 +629,8 @@ int maxpool_fwd_launch(const void* x, void* y, void* idx, int N, int H, int W, i
 }
 int maxpool_bwd_launch(const void* dy, const void* idx, void* dx, int N, int H, int W, int C, int num_sms,
                        cudaStream_t stream) {
-  const long long work = static_cast<long long>(N) * H * W * C;
+  if (C % 8) return -3;
+  const long long work = static_cast<long long>(N) * H * W * (C / 8);
   maxpool_bwd_kernel<<<grid_for(work, num_sms), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
                                                                   reinterpret_cast<const uint8_t*>(idx),
                                                                   reinterpret_cast<__nv_bfloat16*>(dx), N, H, W, C);

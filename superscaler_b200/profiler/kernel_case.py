@@ -5,6 +5,9 @@ check.  Inputs exceed the L2 cache so that memory counters stay meaningful, but 
     python -m superscaler_b200.profiler.kernel_case attention 2 16 2048 128 [--dropout 0.1]
     python -m superscaler_b200.profiler.kernel_case layernorm 32768 2048
     python -m superscaler_b200.profiler.kernel_case embedding 32768 2048 51200 [--dropout 0.1]
+    python -m superscaler_b200.profiler.kernel_case crossentropy 4096 51200
+    python -m superscaler_b200.profiler.kernel_case adam 100000000
+    python -m superscaler_b200.profiler.kernel_case convbn 32 56 640 [--filter 3]
 
 Prints one line per kernel family: milliseconds per call (CUDA events, after warm-up) and TFLOP/s.
 """
@@ -59,12 +62,13 @@ def run_attention(a) -> None:
     torch.manual_seed(0)
     qkv = (torch.randn(B_ * S, 3 * h, device="cuda") * 0.5).bfloat16()
     sc = HD ** -0.5
-    fwd = lambda: ext.attn_fwd(qkv, qkv, qkv, B_, NH, S, S, HD, 0, h, 2 * h, sc, True, None, a.dropout, 1234)
+    fwd = lambda: ext.attn_fwd(qkv, qkv, qkv, B_, NH, S, S, HD, 0, h, 2 * h, sc, True, None, a.dropout, 1234, None)
     o, lse = fwd()
     do = torch.randn_like(o)
     dqkv = torch.empty_like(qkv)
     bwd = lambda: ext.attn_bwd(qkv, qkv, qkv, o, lse, do, dqkv, dqkv, dqkv, B_, NH, S, S, HD, 0, h, 2 * h, 0, h, 2 * h,
-                               sc, True, None, a.dropout, 1234)
+                               sc, True, None, a.dropout, 1234, None, None)
+    ext.set_attn_bwd_deterministic(bool(a.pair))     # --pair: the dK/dV + dQ kernel pair instead of the fused kernel
     flops = 4 * B_ * NH * S * S * HD * 0.5    # causal
     for name, fn, mult in (("fwd", fwd, 1.0), ("bwd", bwd, 2.5)):
         ms = _time(fn, a.warmup, a.iters)
@@ -118,6 +122,60 @@ def run_embedding(a) -> None:
               f"{moved / ms / 1e6:.0f} GB/s (algorithmic bytes) status {int(ext.status().item())}")
 
 
+def run_crossentropy(a) -> None:
+    """Row statistics of bf16 logits, then loss + in-place gradient (the two passes of the LM-head loss)."""
+    ext = native.ext()
+    torch.manual_seed(0)
+    logits = (torch.randn(a.tokens, a.V, device="cuda") * 2).bfloat16()
+    tg = torch.randint(0, a.V, (a.tokens,), device="cuda")
+    st = ext.ce_stats(logits, tg, 0)
+    nbytes = logits.numel() * 2
+    for name, fn, moved in (("stats", lambda: ext.ce_stats(logits, tg, 0), nbytes),
+                            ("finalize", lambda: ext.ce_finalize(logits, tg, st, None, 0, 1.0, True), 2 * nbytes)):
+        ms = _time(fn, a.warmup, a.iters)
+        print(f"cross-entropy {name} tokens {a.tokens} V {a.V}: {ms:.4f} ms {moved / ms / 1e6:.0f} GB/s "
+              f"(algorithmic bytes) status {int(ext.status().item())}")
+
+
+def run_adam(a) -> None:
+    """Squared gradient norm, then the fused Adam step (fp32 master, moments, gradient zeroing, bf16 copy)."""
+    ext = native.ext()
+    torch.manual_seed(0)
+    n = a.n
+    p, g = torch.randn(n, device="cuda"), torch.randn(n, device="cuda") * 1e-3
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ss = torch.zeros(1, device="cuda")
+    step = lambda: ext.adam_step(p, m, v, g, p16, ss, None, 1e-4, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, 1.0, n, True)
+    for name, fn, moved in (("sumsq", lambda: ext.sumsq(g, ss, False), 4 * n), ("adam", step, (4 * 4 + 3 * 4 + 2) * n)):
+        ms = _time(fn, a.warmup, a.iters)
+        print(f"optimizer {name} n {n}: {ms:.4f} ms {moved / ms / 1e6:.0f} GB/s (algorithmic bytes) "
+              f"status {int(ext.status().item())}")
+
+
+def run_convbn(a) -> None:
+    """One Wide-ResNet bottleneck-sized k x k convolution (patch matrix + GEMM; dgrad + scatter back) and the
+    BatchNorm + ReLU around it, NHWC bf16."""
+    from ..ops import conv as C
+    ext = native.ext()
+    torch.manual_seed(0)
+    N, HW, Cn, k = a.N, a.HW, a.C, a.filter
+    x = torch.randn(N, HW, HW, Cn, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(Cn, C._pad8(k * k * Cn), device="cuda") * 0.02).bfloat16().requires_grad_(True)
+    gamma, beta = torch.ones(Cn, device="cuda", requires_grad=True), torch.zeros(Cn, device="cuda", requires_grad=True)
+    rm, rv = torch.zeros(Cn, device="cuda"), torch.ones(Cn, device="cuda")
+
+    def fwd_bwd():
+        y = C.batch_norm(C.conv2d(x, w, k, k, 1, k // 2), gamma, beta, None, rm, rv, relu=True)
+        y.backward(y.detach())
+        x.grad = w.grad = gamma.grad = beta.grad = None
+
+    ms = _time(fwd_bwd, a.warmup, a.iters)
+    flops = 3 * 2 * N * HW * HW * Cn * Cn * k * k
+    print(f"conv{k}x{k} + batch-norm + relu, forward and backward, N{N} {HW}x{HW}x{Cn}: {ms:.4f} ms "
+          f"{flops / ms / 1e9:.0f} TFLOP/s status {int(ext.status().item())}")
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="kind", required=True)
@@ -129,15 +187,24 @@ def main(argv=None) -> None:
     t = sub.add_parser("attention")
     t.add_argument("B", type=int), t.add_argument("NH", type=int), t.add_argument("S", type=int)
     t.add_argument("HD", type=int), t.add_argument("--dropout", type=float, default=0.0)
+    t.add_argument("--pair", action="store_true", help="backward as the dK/dV + dQ kernel pair")
     ln = sub.add_parser("layernorm")
     ln.add_argument("rows", type=int), ln.add_argument("H", type=int)
     e = sub.add_parser("embedding")
     e.add_argument("tokens", type=int), e.add_argument("H", type=int), e.add_argument("V", type=int)
     e.add_argument("--dropout", type=float, default=0.0)
-    for p in (g, t, ln, e):
+    ce = sub.add_parser("crossentropy")
+    ce.add_argument("tokens", type=int), ce.add_argument("V", type=int)
+    ad = sub.add_parser("adam")
+    ad.add_argument("n", type=int)
+    cb = sub.add_parser("convbn")
+    cb.add_argument("N", type=int), cb.add_argument("HW", type=int), cb.add_argument("C", type=int)
+    cb.add_argument("--filter", type=int, default=3)
+    for p in (g, t, ln, e, ce, ad, cb):
         p.add_argument("--warmup", type=int, default=3), p.add_argument("--iters", type=int, default=3)
     a = ap.parse_args(argv)
-    {"gemm": run_gemm, "attention": run_attention, "layernorm": run_layernorm, "embedding": run_embedding}[a.kind](a)
+    {"gemm": run_gemm, "attention": run_attention, "layernorm": run_layernorm, "embedding": run_embedding,
+     "crossentropy": run_crossentropy, "adam": run_adam, "convbn": run_convbn}[a.kind](a)
 
 
 if __name__ == "__main__":

@@ -43,13 +43,17 @@ def test_conv2d_fwd_bwd(cfg):
     assert native.check_status() == 0
 
 
+@pytest.mark.parametrize("shape", [(4, 9, 9, 64), (3, 29, 31, 88), (16, 56, 56, 320)])
 @pytest.mark.parametrize("relu,res", [(False, False), (True, False), (True, True)])
-def test_batch_norm(relu, res):
+def test_batch_norm(relu, res, shape):
+    """The middle shape has a column block that is only partly filled (88 channels = 11 groups of 8) and a row count
+    that no block or unrolling factor divides; the last one has more rows than one pass of the grid covers."""
     torch.manual_seed(1)
-    x = (torch.randn(4, 9, 9, 64, device=DEV) * 2 + 1).bfloat16()
+    Cn = shape[-1]
+    x = (torch.randn(*shape, device=DEV) * 2 + 1).bfloat16()
     r = torch.randn_like(x) if res else None
-    g = (torch.rand(64, device=DEV) + 0.5).requires_grad_(True)
-    b = torch.randn(64, device=DEV).requires_grad_(True)
+    g = (torch.rand(Cn, device=DEV) + 0.5).requires_grad_(True)
+    b = torch.randn(Cn, device=DEV).requires_grad_(True)
     xr = x.float().requires_grad_(True)
     rr = r.float().requires_grad_(True) if res else None
     gr, br = g.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
@@ -70,9 +74,10 @@ def test_batch_norm(relu, res):
         assert rel(rg.grad, rr.grad) < 1e-2
 
 
-def test_pooling():
+@pytest.mark.parametrize("shape", [(2, 12, 12, 16), (3, 13, 11, 24), (2, 112, 112, 320)])
+def test_pooling(shape):
     torch.manual_seed(2)
-    x = torch.randn(2, 12, 12, 16, device=DEV).bfloat16()
+    x = torch.randn(*shape, device=DEV).bfloat16()
     xr = x.float().requires_grad_(True)
     ref = TF.max_pool2d(xr.permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1)
     dy = torch.randn_like(ref)
@@ -84,4 +89,5 @@ def test_pooling():
     xa = x.clone().requires_grad_(True)
     ya = C.global_avg_pool(xa)
     ya.backward(torch.ones_like(ya))
-    assert rel(ya, x.float().mean((1, 2))) < 8e-3 and rel(xa.grad, torch.full_like(x.float(), 1 / 144)) < 8e-3
+    hw = shape[1] * shape[2]
+    assert rel(ya, x.float().mean((1, 2))) < 8e-3 and rel(xa.grad, torch.full_like(x.float(), 1 / hw)) < 8e-3
