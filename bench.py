@@ -217,6 +217,8 @@ def main():
 
     verbose = os.environ.get("SSB_BENCH_VERBOSE") == "1" and rank == 0
 
+    host_issue_ms = [0.0]
+
     def timed(step_fn, n_warm, n_steps):
         for i in range(n_warm):
             t_w = time.perf_counter()
@@ -234,12 +236,14 @@ def main():
         for i in range(n_steps):
             step_fn(n_warm + i)
         e1.record()
+        enqueue = (time.perf_counter() - t0) * 1000.0      # host time to issue the steps (the device runs behind)
         barrier()
         wall = (time.perf_counter() - t0) * 1000.0
         clocks = sampler.stop()
-        ms = torch.tensor([e0.elapsed_time(e1), wall], dtype=torch.float64, device="cuda")
+        ms = torch.tensor([e0.elapsed_time(e1), wall, enqueue], dtype=torch.float64, device="cuda")
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        host_issue_ms[0] = ms[2].item() / n_steps
         return ms[0].item() / n_steps, ms[1].item() / n_steps, clocks, native.launch_counter["kernels"]
 
     # ---- 2 or more GPUs: the fused compute + collective kernels against the NCCL path (untimed) --------------
@@ -259,6 +263,7 @@ def main():
         trainer.train_step(resident[i % 2])
 
     ms_dev, _, clocks, launches = timed(step_resident, args.warmup, args.steps)
+    issue_dev = host_issue_ms[0]
     del resident
 
     # ---- end-to-end region: pinned host batch -> device every step, loss read back every step ---
@@ -286,7 +291,7 @@ def main():
                        "global_batch": gbs, "seq_len": seq, "parallelism": describe_parallelism(plan),
                        "num_microbatches": trainer.num_microbatches, "l2": "inputs_exceed_l2 (2.6 GB of weights + "
                        "activations stream through every step)", "layers": layers if args.model == "gpt" else plan["num_layers"],
-                       "params": trainer.num_parameters(), "kernel_status": status, "last_loss": round(last_loss[0], 4),
+                       "params": trainer.num_parameters(), "host_issue_ms_per_step": round(issue_dev, 2), "kernel_status": status, "last_loss": round(last_loss[0], 4),
                        "max_allocated_mb": round(torch.cuda.max_memory_allocated() / 2 ** 20)},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 3), "unit": "samples/s", "ms_per_step": round(max(ms_e2e, wall_e2e), 2),

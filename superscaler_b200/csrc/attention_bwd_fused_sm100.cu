@@ -481,31 +481,48 @@ attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict_
   *reinterpret_cast<uint4*>(dq + (static_cast<size_t>(b) * SQ + q) * lddq + dq_col0 + head * HD + j * 8) = w;
 }
 
-// Row statistics in the form the fused kernel consumes: nd[b, h, q] = -sum_d dO O and lse2[b, h, q] = LSE log2(e);
-// one warp per (token, head).
+// Row statistics in the form the fused kernel consumes: nd[b, h, q] = -sum_d dO O and lse2[b, h, q] = LSE log2(e).
+// A warp takes one head and 32 consecutive queries of one sequence.  LPR = HD / 8 lanes read one (token, head) row
+// with 16-byte loads, so one load instruction of the warp covers 32 / LPR tokens; after the butterfly sum inside the
+// lane group every lane of the group holds the row's result, and lane L keeps token (L % LPR) * (32 / LPR) + L / LPR.
+template <int HD>
 __global__ void __launch_bounds__(128)
 attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, int ldo, int o_col0, const __nv_bfloat16* __restrict__ dout,
                      int lddo, const float* __restrict__ lse, float* __restrict__ nd, float* __restrict__ lse2, int B,
-                     int NH, int SQ, int HD) {
+                     int NH, int SQ) {
+  constexpr int LPR = HD / 8, TPI = 32 / LPR;
   const int lane = threadIdx.x & 31;
+  const int qblocks = (SQ + 31) / 32;
   const long long w = blockIdx.x * 4LL + (threadIdx.x >> 5);
-  const long long total = static_cast<long long>(B) * SQ * NH;
-  if (w >= total) return;
-  const int head = static_cast<int>(w % NH);
-  const long long tok = w / NH;
-  const __nv_bfloat16* orow = o + tok * ldo + o_col0 + head * HD;
-  const __nv_bfloat16* drow = dout + tok * lddo + o_col0 + head * HD;
-  float s = 0.f;
-  for (int d = lane * 2; d < HD; d += 64) {
-    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(orow + d));
-    const float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(drow + d));
-    s += a.x * g.x + a.y * g.y;
+  if (w >= static_cast<long long>(B) * NH * qblocks) return;
+  const int qb = static_cast<int>(w % qblocks);
+  const int head = static_cast<int>((w / qblocks) % NH);
+  const int b = static_cast<int>(w / (static_cast<long long>(qblocks) * NH));
+  const int sub = lane % LPR, grp = lane / LPR;
+  const size_t col = static_cast<size_t>(o_col0) + head * HD + sub * 8;
+  float mine = 0.f;
+  uint4 qo[LPR], qd[LPR];
+#pragma unroll
+  for (int i = 0; i < LPR; ++i) {       // all loads first: 2 * LPR independent 16-byte requests per lane
+    const int q = qb * 32 + i * TPI + grp;
+    const size_t tok = static_cast<size_t>(b) * SQ + min(q, SQ - 1);
+    qo[i] = *reinterpret_cast<const uint4*>(o + tok * ldo + col);
+    qd[i] = *reinterpret_cast<const uint4*>(dout + tok * lddo + col);
   }
-  s = warp_sum(s);
-  if (lane == 0) {
-    const long long bb = tok / SQ, q = tok % SQ;
-    const long long idx = (bb * NH + head) * SQ + q;
-    nd[idx] = -s;
+#pragma unroll
+  for (int i = 0; i < LPR; ++i) {
+    const float2 a0 = unpack_bf16x2(qo[i].x), a1 = unpack_bf16x2(qo[i].y), a2 = unpack_bf16x2(qo[i].z), a3 = unpack_bf16x2(qo[i].w);
+    const float2 g0 = unpack_bf16x2(qd[i].x), g1 = unpack_bf16x2(qd[i].y), g2 = unpack_bf16x2(qd[i].z), g3 = unpack_bf16x2(qd[i].w);
+    float t = (a0.x * g0.x + a0.y * g0.y) + (a1.x * g1.x + a1.y * g1.y) + (a2.x * g2.x + a2.y * g2.y) +
+              (a3.x * g3.x + a3.y * g3.y);
+#pragma unroll
+    for (int d = LPR / 2; d >= 1; d >>= 1) t += __shfl_xor_sync(0xffffffffu, t, d);
+    if (sub == i) mine = t;
+  }
+  const int q = qb * 32 + sub * TPI + grp;
+  if (q < SQ) {
+    const size_t idx = (static_cast<size_t>(b) * NH + head) * SQ + q;
+    nd[idx] = -mine;
     lse2[idx] = lse[idx] * kLog2e;
   }
 }
@@ -558,10 +575,15 @@ int attn_bwd_fused_launch(const void* q, int ldq, const void* k, int ldk, const 
   float* nd = scratch + acc_floats;
   float* lse2 = nd + stat_floats;
   {
-    const long long warps = static_cast<long long>(p.B) * p.SQ * p.NH;
-    attn_bwd_prep_kernel<<<static_cast<unsigned>((warps + 3) / 4), 128, 0, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(p.O), p.ldo, p.o_col0, reinterpret_cast<const __nv_bfloat16*>(dout),
-        lddo, p.LSE, nd, lse2, p.B, p.NH, p.SQ, p.HD);
+    if ((p.ldo % 8) || (p.o_col0 % 8)) return -3;
+    const long long warps = static_cast<long long>(p.B) * p.NH * ((p.SQ + 31) / 32);
+    const auto* ob = reinterpret_cast<const __nv_bfloat16*>(p.O);
+    const auto* db = reinterpret_cast<const __nv_bfloat16*>(dout);
+    const unsigned blocks = static_cast<unsigned>((warps + 3) / 4);
+    if (p.HD == 128)
+      attn_bwd_prep_kernel<128><<<blocks, 128, 0, stream>>>(ob, p.ldo, p.o_col0, db, lddo, p.LSE, nd, lse2, p.B, p.NH, p.SQ);
+    else
+      attn_bwd_prep_kernel<64><<<blocks, 128, 0, stream>>>(ob, p.ldo, p.o_col0, db, lddo, p.LSE, nd, lse2, p.B, p.NH, p.SQ);
   }
   if ((rc = static_cast<int>(cudaMemsetAsync(dq_acc, 0, sizeof(float) * acc_floats, stream)))) return rc;
   AttnParams pp = p;

@@ -24,7 +24,8 @@ int ln_bwd_part_rows(int rows, int H, int num_sms);
 int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
                          const void* dres, void* dx, float* dgamma, float* dbeta, float* part_g, float* part_b,
                          int accumulate_wgrad, int rows, int H, int num_sms, cudaStream_t stream);
-int colsum_launch(const void* a, int lda, float* out, float* part, int accumulate, int rows, int N,
+int colsum_tickets();
+int colsum_launch(const void* a, int lda, float* out, float* part, int* tickets, int accumulate, int rows, int N,
                   cudaStream_t stream);
 int elementwise_launch(int op, const void* x, const void* a, const void* bias, void* out, long long rows, int N,
                        float dropout_p, unsigned long long seed, int num_sms, cudaStream_t stream);
@@ -111,6 +112,15 @@ Tensor& status_tensor() {
   static std::vector<Tensor> st(64);
   int dev = at::cuda::current_device();
   if (!st[dev].defined()) st[dev] = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA, dev));
+  return st[dev];
+}
+
+// Zero-initialised ticket counters of the one-launch column sum (one set per device; every call leaves them zero).
+Tensor& ticket_tensor() {
+  static std::vector<Tensor> st(64);
+  int dev = at::cuda::current_device();
+  if (!st[dev].defined())
+    st[dev] = torch::zeros({ssb::colsum_tickets()}, torch::dtype(torch::kInt32).device(torch::kCUDA, dev));
   return st[dev];
 }
 
@@ -215,7 +225,8 @@ void colsum(const Tensor& a, Tensor& out, bool accumulate) {
   const int rows = static_cast<int>(a.size(0)), N = static_cast<int>(a.size(1));
   Tensor part = torch::empty({ssb::ln_bwd_slices(rows), N}, torch::dtype(torch::kFloat32).device(a.device()));
   check_launch(ssb::colsum_launch(a.data_ptr(), static_cast<int>(a.stride(0)), out.data_ptr<float>(),
-                                  part.data_ptr<float>(), accumulate, rows, N, cur_stream()),
+                                  part.data_ptr<float>(), ticket_tensor().data_ptr<int>(), accumulate, rows, N,
+                                  cur_stream()),
                "colsum");
 }
 

@@ -10,6 +10,9 @@
 #include "common.cuh"
 
 namespace ssb {
+
+constexpr int kColsumTickets = 4096;   // column blocks of 256 that one column-sum call may cover in one pass
+int colsum_tickets() { return kColsumTickets; }
 namespace {
 
 constexpr int kLnWarpsPerBlock = 4;
@@ -374,6 +377,92 @@ __global__ void fold_partials_kernel(const float* __restrict__ part, float* __re
   out[h] = accumulate ? out[h] + s : s;
 }
 
+// Both LayerNorm weight gradients in one launch: block (x, which) folds 64 columns of part_g (which = 0) or part_b
+// (which = 1); its 256 threads are 64 columns x 4 groups of slices, added in a fixed order.
+__global__ void __launch_bounds__(256)
+fold_partials2_kernel(const float* __restrict__ part_g, const float* __restrict__ part_b, float* __restrict__ dgamma,
+                      float* __restrict__ dbeta, int slices, int H, int accumulate) {
+  __shared__ float sm[4][64];
+  const float* part = blockIdx.y == 0 ? part_g : part_b;
+  float* out = blockIdx.y == 0 ? dgamma : dbeta;
+  const int c = threadIdx.x & 63, sg = threadIdx.x >> 6, h = blockIdx.x * 64 + c;
+  float s = 0.f;
+  if (h < H)
+    for (int k = sg; k < slices; k += 4) s += part[static_cast<size_t>(k) * H + h];
+  sm[sg][c] = s;
+  __syncthreads();
+  if (sg == 0 && h < H) {
+    const float t = (sm[0][c] + sm[1][c]) + (sm[2][c] + sm[3][c]);
+    out[h] = accumulate ? out[h] + t : t;
+  }
+}
+
+// Column sum of a bf16 matrix [rows, N] (bias gradients) in ONE launch, for 16-byte aligned rows (N, lda multiples
+// of 8).  A warp covers 512 contiguous bytes of a row (eight columns per lane), the eight warps of a block take
+// every eighth row of the block's slice, and the block writes one row of partials for its 256 columns.  The block
+// that finishes LAST for a column block (a ticket counter per column block, which it sets back to zero) adds the
+// partials of all slices in slice order, so the result does not depend on which block that is.  The counters are
+// shared by all calls on a device: calls must be ordered on one stream.
+__global__ void __launch_bounds__(256)
+colsum_onepass_kernel(const __nv_bfloat16* __restrict__ a, int lda, float* __restrict__ part, float* __restrict__ out,
+                      int* __restrict__ tickets, int rows, int N, int rows_per_slice, int accumulate) {
+  __shared__ float red[8][256 + 8];
+  __shared__ int is_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * 256 + lane * 8;
+  const int r0 = blockIdx.y * rows_per_slice;
+  const int r1 = min(rows, r0 + rows_per_slice);
+  float s[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = 0.f;
+  auto add = [&](const uint4& q) {
+    const float2 v0 = unpack_bf16x2(q.x), v1 = unpack_bf16x2(q.y), v2 = unpack_bf16x2(q.z), v3 = unpack_bf16x2(q.w);
+    s[0] += v0.x; s[1] += v0.y; s[2] += v1.x; s[3] += v1.y; s[4] += v2.x; s[5] += v2.y; s[6] += v3.x; s[7] += v3.y;
+  };
+  if (c0 < N) {
+    int r = r0 + warp;
+    for (; r + 24 < r1; r += 32) {                   // four independent rows in flight per thread
+      uint4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = *reinterpret_cast<const uint4*>(a + static_cast<size_t>(r + 8 * u) * lda + c0);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) add(q[u]);
+    }
+    for (; r < r1; r += 8) add(*reinterpret_cast<const uint4*>(a + static_cast<size_t>(r) * lda + c0));
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = s[j];
+  __syncthreads();
+  const int col = blockIdx.x * 256 + threadIdx.x;
+  if (col < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][threadIdx.x];
+    part[static_cast<size_t>(blockIdx.y) * N + col] = t;
+    __threadfence();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(&tickets[blockIdx.x], 1) == static_cast<int>(gridDim.y) - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (col < N) {
+    float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;      // four chains, joined in a fixed order
+    const int n = static_cast<int>(gridDim.y);
+    int k = 0;
+    for (; k + 3 < n; k += 4) {
+      t0 += __ldcg(part + static_cast<size_t>(k) * N + col);
+      t1 += __ldcg(part + static_cast<size_t>(k + 1) * N + col);
+      t2 += __ldcg(part + static_cast<size_t>(k + 2) * N + col);
+      t3 += __ldcg(part + static_cast<size_t>(k + 3) * N + col);
+    }
+    for (; k < n; ++k) t0 += __ldcg(part + static_cast<size_t>(k) * N + col);
+    const float tot = (t0 + t1) + (t2 + t3);
+    out[col] = accumulate ? out[col] + tot : tot;
+  }
+  if (threadIdx.x == 0) tickets[blockIdx.x] = 0;
+}
+
 // Column sum of a bf16 matrix [rows, N] into partials[slice][N] (bias gradients).
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const __nv_bfloat16* __restrict__ a, int lda, float* __restrict__ part, int rows, int N,
@@ -464,8 +553,8 @@ int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, cons
       ln_bwd_onepass_kernel<4, 1><<<g, b, 0, stream>>>(dyb, xb, gamma, mean, rstd, drb, dxb, part_g, part_b, rows, H);
     else
       ln_bwd_onepass_kernel<4, 2><<<g, b, 0, stream>>>(dyb, xb, gamma, mean, rstd, drb, dxb, part_g, part_b, rows, H);
-    fold_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(part_g, dgamma, nb, H, accumulate_wgrad);
-    fold_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(part_b, dbeta, nb, H, accumulate_wgrad);
+    fold_partials2_kernel<<<dim3((H + 63) / 64, 2), 256, 0, stream>>>(part_g, part_b, dgamma, dbeta, nb, H,
+                                                                      accumulate_wgrad);
     return static_cast<int>(cudaGetLastError());
   }
   const int blocks = min((rows + kLnWarpsPerBlock - 1) / kLnWarpsPerBlock, num_sms * 16);
@@ -477,17 +566,29 @@ int layernorm_bwd_launch(const void* dy, const void* x, const float* gamma, cons
   ln_bwd_gb_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dy),
                                                      reinterpret_cast<const __nv_bfloat16*>(x), mean, rstd, part_g,
                                                      part_b, rows, H, rps);
-  fold_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(part_g, dgamma, slices, H, accumulate_wgrad);
-  fold_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(part_b, dbeta, slices, H, accumulate_wgrad);
+  fold_partials2_kernel<<<dim3((H + 63) / 64, 2), 256, 0, stream>>>(part_g, part_b, dgamma, dbeta, slices, H,
+                                                                    accumulate_wgrad);
   return static_cast<int>(cudaGetLastError());
 }
 
-// out[N] (+)= column sums of a[rows, N]; `part` is scratch of ln_bwd_slices(rows) x N floats.
-int colsum_launch(const void* a, int lda, float* out, float* part, int accumulate, int rows, int N,
+// out[N] (+)= column sums of a[rows, N]; `part` is scratch of ln_bwd_slices(rows) x N floats; `tickets` holds
+// kColsumTickets zero-initialised counters that every call leaves at zero.
+int colsum_launch(const void* a, int lda, float* out, float* part, int* tickets, int accumulate, int rows, int N,
                   cudaStream_t stream) {
   if (N % 2 || lda % 2) return -3;
   const int slices = ln_bwd_slices(rows);
   const int rps = (rows + slices - 1) / slices;
+  const int colblocks = (N + 255) / 256;
+  if (N % 8 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 && colblocks <= kColsumTickets &&
+      tickets != nullptr) {
+    // about eight blocks per SM in all, and never more slices than the scratch has rows
+    int sl = (148 * 8 + colblocks - 1) / colblocks;
+    sl = sl < 1 ? 1 : (sl > slices ? slices : sl);
+    const int rows_per = (rows + sl - 1) / sl;
+    colsum_onepass_kernel<<<dim3(colblocks, sl), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(a), lda, part,
+                                                                   out, tickets, rows, N, rows_per, accumulate);
+    return static_cast<int>(cudaGetLastError());
+  }
   dim3 grid((N / 2 + 31) / 32, slices);
   colsum_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(a), lda, part, rows, N, rps);
   fold_partials_kernel<<<(N + 255) / 256, 256, 0, stream>>>(part, out, slices, N, accumulate);

@@ -35,11 +35,26 @@ def relative_position_bucket(distance: torch.Tensor, bidirectional: bool, num_bu
     return offset + torch.where(small, d, scaled)
 
 
+_BUCKETS_OF_DISTANCE = {}
+
+
+def buckets_of_distances(sq: int, sk: int, bidirectional: bool, num_buckets: int, max_distance: int,
+                         device) -> torch.Tensor:
+    """Bucket of every distance -(sq - 1) .. sk - 1, computed once per geometry and device (every layer of every
+    micro-batch asks for the same sq + sk - 1 integers)."""
+    key = (sq, sk, bool(bidirectional), num_buckets, max_distance, str(device))
+    idx = _BUCKETS_OF_DISTANCE.get(key)
+    if idx is None:
+        dist = torch.arange(-(sq - 1), sk, device=device)
+        idx = relative_position_bucket(dist, bidirectional, num_buckets, max_distance)
+        _BUCKETS_OF_DISTANCE[key] = idx
+    return idx
+
+
 def distance_table(weight: torch.Tensor, sq: int, sk: int, bidirectional: bool, num_buckets: int = 32,
                    max_distance: int = 128) -> torch.Tensor:
     """weight [heads, buckets] -> [heads, sq + sk - 1]; column c holds the bias of distance c - (sq - 1)."""
-    dist = torch.arange(-(sq - 1), sk, device=weight.device)
-    return weight[:, relative_position_bucket(dist, bidirectional, num_buckets, max_distance)]
+    return weight[:, buckets_of_distances(sq, sk, bidirectional, num_buckets, max_distance, weight.device)]
 
 
 def bias_from_table(table: torch.Tensor, sq: int, sk: int) -> torch.Tensor:

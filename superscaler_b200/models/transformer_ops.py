@@ -81,8 +81,10 @@ class LayerNormOp(Op):
     def forward(self, st):
         x = st["x"]
         if self.keep_residual:
-            st["residual"] = x
-        st["x"] = F.layernorm(x, self.p("layernorm.weight"), self.p("layernorm.bias"), self.env.cfg.layernorm_eps)
+            st["x"], st["residual"] = F.layernorm_keep_input(x, self.p("layernorm.weight"), self.p("layernorm.bias"),
+                                                             self.env.cfg.layernorm_eps)
+        else:
+            st["x"] = F.layernorm(x, self.p("layernorm.weight"), self.p("layernorm.bias"), self.env.cfg.layernorm_eps)
 
 
 class QKVOp(Op):

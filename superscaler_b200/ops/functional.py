@@ -364,10 +364,14 @@ def mlp(x, w1, b1, w2, b2, residual=None, act=ACT_GELU, dropout_p=0.0, seed=0):
 # --------------------------------------------------------------------------------------------
 class LayerNormFn(torch.autograd.Function):
     """LayerNorm over the last dim with fp32 gamma / beta (reference: fused_layer_norm.py MixedFusedLayerNorm
-    over runtime/megatron/fused_kernels/layer_norm_cuda_kernel.cu)."""
+    over runtime/megatron/fused_kernels/layer_norm_cuda_kernel.cu).
+
+    With `pass_through` the function also returns its input as a second output, for the residual branch that
+    skips the normalised sub-layer: the gradients of both branches then arrive together and the backward kernel adds
+    the residual branch's while it writes dx (instead of autograd adding two [tokens, hidden] tensors afterwards)."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, eps):
+    def forward(ctx, x, gamma, beta, eps, pass_through):
         if x.is_cuda:
             y, mean, rstd = native.ext().layernorm_fwd(x, None, gamma, beta, eps)
         else:
@@ -378,33 +382,47 @@ class LayerNormFn(torch.autograd.Function):
             y = ((xf - mean[:, None]) * rstd[:, None] * gamma.float() + beta.float()).to(x.dtype)
         ctx.save_for_backward(x, gamma, mean, rstd)
         ctx.params = (gamma, beta)
+        ctx.set_materialize_grads(False)
+        if pass_through:
+            return y, x.view_as(x)
         return y
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dres=None):
         x, gamma, mean, rstd = ctx.saved_tensors
         g_param, b_param = ctx.params
+        if dy is None:                      # only the residual branch was used
+            return dres, None, None, None, None
         dy = dy.contiguous()
+        if dres is not None:
+            dres = dres.contiguous()
         mg_g, mg_b = getattr(g_param, "main_grad", None), getattr(b_param, "main_grad", None)
         if x.is_cuda:
             if mg_g is not None and mg_b is not None:
-                dx = native.ext().layernorm_bwd(dy, x, gamma, mean, rstd, None, mg_g, mg_b, True)
-                return dx, None, None, None
+                dx = native.ext().layernorm_bwd(dy, x, gamma, mean, rstd, dres, mg_g, mg_b, True)
+                return dx, None, None, None, None
             dg = torch.empty_like(gamma, dtype=torch.float32)
             db = torch.empty_like(gamma, dtype=torch.float32)
-            dx = native.ext().layernorm_bwd(dy, x, gamma, mean, rstd, None, dg, db, False)
-            return dx, dg.to(gamma.dtype), db.to(gamma.dtype), None
+            dx = native.ext().layernorm_bwd(dy, x, gamma, mean, rstd, dres, dg, db, False)
+            return dx, dg.to(gamma.dtype), db.to(gamma.dtype), None, None
         xf, dyf = x.float(), dy.float()
         xhat = (xf - mean[:, None]) * rstd[:, None]
         dg = (dyf * xhat).sum(0)
         db = dyf.sum(0)
         dxhat = dyf * gamma.float()
         dx = rstd[:, None] * (dxhat - dxhat.mean(-1, keepdim=True) - xhat * (dxhat * xhat).mean(-1, keepdim=True))
-        return dx.to(x.dtype), _vec_grad(g_param, dg), _vec_grad(b_param, db), None
+        if dres is not None:
+            dx = dx + dres.float()
+        return dx.to(x.dtype), _vec_grad(g_param, dg), _vec_grad(b_param, db), None, None
 
 
 def layernorm(x, gamma, beta, eps=1e-5):
-    return LayerNormFn.apply(x, gamma, beta, eps)
+    return LayerNormFn.apply(x, gamma, beta, eps, False)
+
+
+def layernorm_keep_input(x, gamma, beta, eps=1e-5):
+    """(LayerNorm(x), x): the second value is x for the residual add behind the normalised sub-layer."""
+    return LayerNormFn.apply(x, gamma, beta, eps, True)
 
 
 # --------------------------------------------------------------------------------------------

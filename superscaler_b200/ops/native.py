@@ -43,7 +43,7 @@ def available() -> bool:
 
 
 # kernels launched by one call of each binding (for launch accounting in benchmarks)
-KERNELS_PER_CALL = {"gemm": 1, "layernorm_fwd": 1, "layernorm_bwd": 3, "colsum": 2, "elementwise": 1,
+KERNELS_PER_CALL = {"gemm": 1, "layernorm_fwd": 1, "layernorm_bwd": 2, "colsum": 1, "elementwise": 1,
                     "cast_f32_to_bf16": 1, "softmax_fwd": 1, "softmax_bwd": 1, "sumsq": 2, "adam_step": 1,
                     "sgd_step": 1, "embedding_fwd": 1, "embedding_bwd": 1, "ce_stats": 1, "ce_finalize": 1,
                     "attn_fwd": 1, "attn_bwd": 3, "im2col": 1, "col2im": 1, "subsample": 1, "bn_fwd": 3, "bn_bwd": 3, "bn_apply": 1,

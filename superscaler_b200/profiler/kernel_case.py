@@ -7,6 +7,7 @@ check.  Inputs exceed the L2 cache so that memory counters stay meaningful, but 
     python -m superscaler_b200.profiler.kernel_case embedding 32768 2048 51200 [--dropout 0.1]
     python -m superscaler_b200.profiler.kernel_case crossentropy 4096 51200
     python -m superscaler_b200.profiler.kernel_case adam 100000000
+    python -m superscaler_b200.profiler.kernel_case colsum 32768 8192
     python -m superscaler_b200.profiler.kernel_case convbn 32 56 640 [--filter 3]
 
 Prints one line per kernel family: milliseconds per call (CUDA events, after warm-up) and TFLOP/s.
@@ -137,6 +138,17 @@ def run_crossentropy(a) -> None:
               f"(algorithmic bytes) status {int(ext.status().item())}")
 
 
+def run_colsum(a) -> None:
+    """Column sums of a bf16 matrix (bias gradients)."""
+    ext = native.ext()
+    torch.manual_seed(0)
+    x = torch.randn(a.rows, a.N, device="cuda").bfloat16()
+    out = torch.zeros(a.N, device="cuda")
+    ms = _time(lambda: ext.colsum(x, out, True), a.warmup, a.iters)
+    print(f"colsum {a.rows}x{a.N}: {ms:.4f} ms {x.numel() * 2 / ms / 1e6:.0f} GB/s (algorithmic bytes) "
+          f"status {int(ext.status().item())}")
+
+
 def run_adam(a) -> None:
     """Squared gradient norm, then the fused Adam step (fp32 master, moments, gradient zeroing, bf16 copy)."""
     ext = native.ext()
@@ -200,11 +212,13 @@ def main(argv=None) -> None:
     cb = sub.add_parser("convbn")
     cb.add_argument("N", type=int), cb.add_argument("HW", type=int), cb.add_argument("C", type=int)
     cb.add_argument("--filter", type=int, default=3)
-    for p in (g, t, ln, e, ce, ad, cb):
+    cs = sub.add_parser("colsum")
+    cs.add_argument("rows", type=int), cs.add_argument("N", type=int)
+    for p in (g, t, ln, e, ce, ad, cb, cs):
         p.add_argument("--warmup", type=int, default=3), p.add_argument("--iters", type=int, default=3)
     a = ap.parse_args(argv)
     {"gemm": run_gemm, "attention": run_attention, "layernorm": run_layernorm, "embedding": run_embedding,
-     "crossentropy": run_crossentropy, "adam": run_adam, "convbn": run_convbn}[a.kind](a)
+     "crossentropy": run_crossentropy, "adam": run_adam, "convbn": run_convbn, "colsum": run_colsum}[a.kind](a)
 
 
 if __name__ == "__main__":

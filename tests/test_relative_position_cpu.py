@@ -53,7 +53,7 @@ def _t5_losses(plan, rank=0, world=1, fuse=True, steps=3):
 
 def _t5_worker(rank, world, plan, want):
     got, _, _ = _t5_losses(plan, rank, world)
-    assert max(abs(a - b) for a, b in zip(got, want)) < 3e-3, (rank, got, want)
+    assert max(abs(a - b) for a, b in zip(got, want)) < 6e-3, (rank, got, want)
 
 
 def test_t5_with_relative_position_bias_trains_and_matches_across_plans():

@@ -128,7 +128,9 @@ def test_recompute_segment_may_end_right_after_a_projection():
         rc[i] = 1
     plan["recompute_ops"] = [rc]
     got = losses(plan)
-    assert max(abs(a - b) for a, b in zip(got, base)) < 1e-4, (got, base)
+    # not bitwise: where a segment boundary separates a LayerNorm from its residual branch, the two gradient branches
+    # are added after bf16 rounding instead of inside the LayerNorm backward
+    assert max(abs(a - b) for a, b in zip(got, base)) < 3e-4, (got, base)
 
 
 def test_random_per_op_recompute_flags_do_not_change_training():
