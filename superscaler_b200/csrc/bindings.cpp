@@ -175,6 +175,17 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, con
   p.dropout_seed = static_cast<unsigned long long>(seed);
   TORCH_CHECK(dropout_p == 0.0 || d.stride(0) == N, "dropout epilogue needs a dense output");
   p.status = status_tensor().data_ptr<int>();
+  Tensor split_ws;
+  const bool plain = p.out_fp32 && alpha == 1.0 && !bias.has_value() && act == 0 && !aux.has_value() &&
+                     !preact_out.has_value() && !residual.has_value() && dropout_p == 0.0;
+  if (plain) {
+    const int splits = ssb::gemm_splitk_splits(p.M, p.N, p.K, num_sms());
+    if (splits > 1) {
+      split_ws = torch::empty({splits, M, N}, torch::dtype(torch::kFloat32).device(a.device()));
+      p.k_splits = splits;
+      p.split_ws = split_ws.data_ptr<float>();
+    }
+  }
   check_launch(ssb::gemm_bf16_launch(a.data_ptr(), static_cast<int>(a.stride(0)), a_mn, b.data_ptr(),
                                      static_cast<int>(b.stride(0)), b_mn, p, num_sms(), cur_stream()),
                "gemm");
@@ -775,6 +786,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_allreduce", &gemm_allreduce);
   m.def("allgather_gemm", &allgather_gemm);
+  m.def("gemm_splitk_splits", [](int64_t M, int64_t N, int64_t K) {
+    return ssb::gemm_splitk_splits(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), num_sms());
+  });
   m.def("gemm_set_pair_mode", &ssb::gemm_set_pair_mode);
   m.def("gemm_get_pair_mode", &ssb::gemm_get_pair_mode);
   m.def("layernorm_fwd", &layernorm_fwd);

@@ -79,6 +79,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
+  // split-K: work item w = (slice, tile); slice s reduces the K blocks [s * kb_per, min(num_kb, (s + 1) * kb_per))
+  const int splits = p.k_splits > 1 ? p.k_splits : 1;
+  const int kb_per = (num_kb + splits - 1) / splits;
+  const int num_work = num_tiles * splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -109,9 +113,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(tile, num_m, num_n);
-        for (int kb = 0; kb < num_kb; ++kb) {
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const TileCoord tc = tile_coord(w % num_tiles, num_m, num_n);
+        const int kb0 = (w / num_tiles) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             ok = false;
             break;
@@ -157,7 +162,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       int iter = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++iter) {
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1;
         if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
@@ -166,7 +171,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (w / num_tiles) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
             ok = false;
             break;
@@ -182,7 +188,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                      : umma_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? umma_desc_sw128(sb + k * 2048, 64 * BK * 2, 1024)
                                      : umma_desc_sw128(sb + k * 32, 16, 1024);
-            umma_f16_ss(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == kStages) {
@@ -200,8 +206,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const float drop_scale = p.dropout_p > 0.f ? 65536.0f / static_cast<float>(keep16) : 1.0f;
     int iter = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++iter) {
-      const TileCoord tc = tile_coord(tile, num_m, num_n);
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++iter) {
+      const TileCoord tc = tile_coord(w % num_tiles, num_m, num_n);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) {
@@ -211,6 +217,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after_sync();
       const int row = tc.m_blk * BM + quarter * 32 + lane;
       const bool row_ok = row < p.M;
+      const int out_row = row + (w / num_tiles) * p.M;   // split-K: the output is the slice's [M, N] workspace block
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -220,7 +227,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
         if (!row_ok) continue;
-        gemm_epilogue_chunk<32>(p, row, n0, r, keep16, drop_scale);
+        gemm_epilogue_chunk<32>(p, out_row, n0, r, keep16, drop_scale);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -303,6 +310,29 @@ int make_tma_2d_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
 
 namespace {
 
+// D[m][n] (+)= sum over the slices, in slice order, of ws[slice][m][n] (N a multiple of 4).
+__global__ void __launch_bounds__(256)
+splitk_fold_kernel(const float* __restrict__ ws, float* __restrict__ D, int ldd, int M, int N, int splits, int accumulate) {
+  const int nq = N / 4;
+  const long long quads = static_cast<long long>(M) * nq;
+  const size_t slice = static_cast<size_t>(M) * N;
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < quads; i += gridDim.x * 256LL) {
+    const int m = static_cast<int>(i / nq), c = static_cast<int>(i % nq) * 4;
+    const float* src = ws + static_cast<size_t>(m) * N + c;
+    float4 acc = *reinterpret_cast<const float4*>(src);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(src + s * slice);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float4* dst = reinterpret_cast<float4*>(D + static_cast<size_t>(m) * ldd + c);
+    if (accumulate) {
+      const float4 o = *dst;
+      acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+    }
+    *dst = acc;
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN>
 int launch_variant(const void* A, int lda, const void* B, int ldb, const GemmParams& p, int num_sms,
                    cudaStream_t stream) {
@@ -328,6 +358,21 @@ int launch_variant(const void* A, int lda, const void* B, int ldb, const GemmPar
     attr_done = true;
   }
   const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  if (p.k_splits > 1) {
+    // every slice writes a plain fp32 [M, N] block of the workspace; the fold adds them, in slice order, into D
+    GemmParams q = p;
+    q.D = p.split_ws;
+    q.ldd = p.N;
+    q.out_fp32 = 1;
+    q.accumulate = 0;
+    const int work = num_tiles * p.k_splits;
+    kernel<<<work < num_sms ? work : num_sms, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, q);
+    const long long quads = static_cast<long long>(p.M) * (p.N / 4);
+    const int blocks = static_cast<int>((quads + 255) / 256 < num_sms * 8LL ? (quads + 255) / 256 : num_sms * 8LL);
+    splitk_fold_kernel<<<blocks, 256, 0, stream>>>(p.split_ws, reinterpret_cast<float*>(p.D), p.ldd, p.M, p.N, p.k_splits,
+                                                   p.accumulate);
+    return static_cast<int>(cudaGetLastError());
+  }
   const int grid = num_tiles < num_sms ? num_tiles : num_sms;
   kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
@@ -343,6 +388,24 @@ static int g_pair_mode = 1;
 void gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
 int gemm_get_pair_mode() { return g_pair_mode; }
 
+int gemm_splitk_splits(int M, int N, int K, int num_sms) {
+  if (g_pair_mode) {
+    const int tiles_pair = ((M + 255) / 256) * ((N + 255) / 256);
+    if (M >= 256 && N >= 256 && tiles_pair >= num_sms / 4) return 1;     // the two-SM kernel takes it
+  }
+  if (N % 4) return 1;
+  const int tiles256 = ((M + BM - 1) / BM) * ((N + 255) / 256);
+  const bool bn128 = (N <= 128) || (tiles256 < num_sms);
+  const int tiles = ((M + BM - 1) / BM) * ((N + (bn128 ? 127 : 255)) / (bn128 ? 128 : 256));
+  const int num_kb = (K + BK - 1) / BK;
+  int s = num_sms / tiles;                 // slices until every SM has a work item
+  if (s > num_kb / 16) s = num_kb / 16;    // at least 16 K blocks (1024 reduction steps) per slice
+  if (s > 64) s = 64;
+  if (s < 2) return 1;
+  const int kb_per = (num_kb + s - 1) / s;
+  return (num_kb + kb_per - 1) / kb_per;   // no empty slice
+}
+
 // Launches the GEMM on `stream`.  Returns 0 or a CUDA / driver error code; argument errors are negative.
 int gemm_bf16_launch(const void* A, int lda, int a_mn_major, const void* B, int ldb, int b_mn_major,
                      const GemmParams& p, int num_sms, cudaStream_t stream) {
@@ -351,7 +414,13 @@ int gemm_bf16_launch(const void* A, int lda, int a_mn_major, const void* B, int 
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(p.D) & 15))
     return -4;
-  if (g_pair_mode) {
+  if (p.k_splits > 1) {
+    const bool plain = p.out_fp32 && p.alpha == 1.0f && p.bias == nullptr && p.act == 0 && p.aux == nullptr &&
+                       p.preact_out == nullptr && p.residual == nullptr && p.dropout_p == 0.f;
+    if (!plain || p.split_ws == nullptr || (p.N % 4) || (reinterpret_cast<uintptr_t>(p.split_ws) & 15) ||
+        p.k_splits > (p.K + BK - 1) / BK)
+      return -5;
+  } else if (g_pair_mode) {
     const int tiles_pair = ((p.M + 255) / 256) * ((p.N + 255) / 256);
     if (p.M >= 256 && p.N >= 256 && tiles_pair >= num_sms / 4)
       return gemm2_bf16_launch(A, lda, a_mn_major, B, ldb, b_mn_major, p, num_sms, stream);

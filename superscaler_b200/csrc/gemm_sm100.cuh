@@ -44,6 +44,15 @@ struct GemmParams {
   float dropout_p;         // 0 = off
   unsigned long long dropout_seed;
   int* status;             // device int, set to a StatusCode on failure (never cleared by the kernel)
+  // Split-K (one-CTA kernel, plain fp32 outputs only): k_splits > 1 divides the reduction into that many slices,
+  // each slice writes its [M, N] partial product into split_ws[slice] and a second kernel adds the slices in order
+  // into D.  0 or 1 = off.  gemm_splitk_splits() says when it pays.
+  int k_splits;
+  float* split_ws;
 };
+
+// Number of reduction slices gemm_bf16_launch would like for this problem (1 = none): small outputs with a long
+// reduction (weight gradients of narrow layers over many tokens or pixels) otherwise leave most SMs idle.
+int gemm_splitk_splits(int M, int N, int K, int num_sms);
 
 }  // namespace ssb

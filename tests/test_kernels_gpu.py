@@ -67,6 +67,29 @@ def test_gemm_variants(a_mn, b_mn, shape):
     close(acc, ref + 1, what="gemm fp32 accumulate", **FP32)
 
 
+@pytest.mark.parametrize("shape", [(640, 320, 50176), (1024, 1024, 16384), (96, 200, 4096)])
+def test_weight_gradient_gemm_with_split_reduction(shape):
+    """Small outputs with a long reduction are cut into K slices (one per otherwise idle SM) whose partial products
+    are added in slice order: the result accumulates into an fp32 buffer like any other weight gradient and is the
+    same on every run."""
+    M, N, K = shape
+    torch.manual_seed(17)
+    assert native.ext().gemm_splitk_splits(M, N, K) > 1
+    A = torch.randn(K, M, device=DEV).bfloat16()        # dY, MN-major
+    B = torch.randn(K, N, device=DEV).bfloat16()        # X, MN-major
+    ref = (A.double().t() @ B.double() + 1).float()
+    outs = []
+    for _ in range(2):
+        acc = torch.ones(M, N, device=DEV)
+        F.gemm(A, B, out=acc, a_mn=True, b_mn=True, accumulate=True)
+        outs.append(acc)
+    close(outs[0], ref, what="split-K wgrad", rtol=3e-4, atol_rms=3e-4)
+    assert torch.equal(outs[0], outs[1])
+    plain = torch.empty(M, N, device=DEV)
+    F.gemm(A, B, out=plain, a_mn=True, b_mn=True)
+    close(plain, ref - 1, what="split-K plain store", rtol=3e-4, atol_rms=3e-4)
+
+
 def test_gemm_strided_operands():
     torch.manual_seed(1)
     big = torch.randn(300, 1024, device=DEV).bfloat16()
