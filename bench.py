@@ -148,6 +148,13 @@ def run_reference(args):
             out["clocks"] = clocks
     if rank == 0:
         print(json.dumps(out), flush=True)
+    try:
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier()
+            dist.destroy_process_group()
+    except Exception:  # noqa: BLE001 - the line is printed; a failed teardown must not change the exit code
+        pass
 
 
 def main():

@@ -63,6 +63,7 @@ def main():
                         assert t.optimizer.sharded == (fused and shard), key
                         sd = t.optimizer.state_dict()             # collective: gathers the slices of a sharded run
                         masters[key] = (sd["master"].clone(), sd["exp_avg_sq"].clone(), t.store.model16.clone())
+                        decayed_end = t.store.wd_end
                         if t.optimizer.sharded and rank == 0:
                             print("slice", t.optimizer.shard_lo, t.optimizer.shard_hi, "wd_end", t.store.wd_end, "total",
                                   t.store.total, flush=True)
@@ -75,7 +76,12 @@ def main():
         diffs = [(a.float() - b.float()).abs().max().item() for a, b in zip(masters["dp_fused_sharded"], masters["dp_fused"])]
         d0 = (masters["dp_fused_sharded"][0] - masters["dp_fused"][0]).abs()
         where = (int(d0.argmax()), int((d0 > 1e-4).sum()), d0.numel())
-        assert diffs[0] < 2e-4 and diffs[1] < 1e-4 and diffs[2] < 1e-2, (diffs, where)      # master, second moment, bf16 copy
+        # Matrices (the weight-decayed front of the buffer): equal up to the rounding of the clip factor.  Biases and
+        # LayerNorm parameters behind them include elements whose gradient is rounding noise around zero (a key bias
+        # does not change a softmax); Adam turns that noise into steps of +-lr, so the last bit of the clip factor may
+        # send such an element the other way in each of the three steps: at most 2 * 3 * lr apart.
+        assert d0[:decayed_end].max().item() < 2e-4 and d0.max().item() < 6 * 1.5e-4 + 1e-5, (diffs, where)
+        assert diffs[1] < 1e-4 and diffs[2] < 1e-2, (diffs, where)                           # second moment, bf16 copy
         mine = masters["dp_fused_sharded"][2].float()
         other = mine.clone()
         dist.broadcast(other, src=0)

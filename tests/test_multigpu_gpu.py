@@ -43,3 +43,12 @@ def test_fused_allgather_gemm_matches_allgather_plus_gemm():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_gemm_reduce_scatter_matches_gemm_plus_nccl():
     assert "GEMM_RS_OK" in _launch("gemm_rs")
+
+
+@pytest.mark.parametrize("mode,ok", [("allreduce", "ALLREDUCE_OK"), ("gemm_ar", "GEMM_AR_OK"), ("ag_gemm", "AG_GEMM_OK"),
+                                     ("gemm_rs", "GEMM_RS_OK")])
+def test_fused_collective_kernels_on_four_gpus(mode, ok):
+    """The same checks at tensor-parallel degree 4: three peers per rank, four owners of output slices."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    assert ok in _launch(mode, n=4)
