@@ -37,23 +37,26 @@ struct ConvGeom {
 // C % 8 == 0: one thread moves 8 channels of one tap.  The small-C variant handles the 3-channel stem.
 __global__ void __launch_bounds__(256)
 im2col_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ cols, ConvGeom g) {
+  // A block takes one row of the patch matrix (one output pixel) at a time: the pixel's coordinates are worked out
+  // once per row, and a thread's element inside the row needs one 32-bit division (tap = e / cvec).
   const int cvec = g.C / 8;
-  const long long per_row = static_cast<long long>(g.KH) * g.KW * cvec;
-  const long long total = static_cast<long long>(g.N) * g.Ho * g.Wo * per_row;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long row = i / per_row;
-    int rem = static_cast<int>(i % per_row);
-    const int c8 = rem % cvec; rem /= cvec;
-    const int s = rem % g.KW, r = rem / g.KW;
-    const int wo = static_cast<int>(row % g.Wo);
-    const int ho = static_cast<int>((row / g.Wo) % g.Ho);
-    const int n = static_cast<int>(row / (static_cast<long long>(g.Wo) * g.Ho));
-    const int h = ho * g.stride + r - g.pad, w = wo * g.stride + s - g.pad;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (h >= 0 && h < g.H && w >= 0 && w < g.W)
-      v = *reinterpret_cast<const uint4*>(x + ((static_cast<long long>(n) * g.H + h) * g.W + w) * g.C + c8 * 8);
-    *reinterpret_cast<uint4*>(cols + row * g.Kpad + (static_cast<long long>(r) * g.KW + s) * g.C + c8 * 8) = v;
+  const int per_row = g.KH * g.KW * cvec;
+  const int rows = g.N * g.Ho * g.Wo;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int wo = row % g.Wo, t = row / g.Wo;
+    const int ho = t % g.Ho, n = t / g.Ho;
+    const int h0 = ho * g.stride - g.pad, w0 = wo * g.stride - g.pad;
+    const __nv_bfloat16* xin = x + static_cast<long long>(n) * g.H * g.W * g.C;
+    __nv_bfloat16* out = cols + static_cast<long long>(row) * g.Kpad;
+    for (int e = threadIdx.x; e < per_row; e += 256) {
+      const int tap = e / cvec, c8 = e - tap * cvec;
+      const int r = tap / g.KW, s2 = tap - r * g.KW;
+      const int h = h0 + r, w = w0 + s2;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (h >= 0 && h < g.H && w >= 0 && w < g.W)
+        v = *reinterpret_cast<const uint4*>(xin + (static_cast<long long>(h) * g.W + w) * g.C + c8 * 8);
+      *reinterpret_cast<uint4*>(out + e * 8) = v;     // (r, s, c) is the order of e: the row is written front to back
+    }
   }
 }
 
@@ -81,34 +84,37 @@ im2col_small_c_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __rest
 // dx[n, h, w, c] = sum over taps (r, s) with (h + pad - r) % stride == 0 ... of dcols[(n, ho, wo), (r, s, c)]
 __global__ void __launch_bounds__(256)
 col2im_kernel(const __nv_bfloat16* __restrict__ dcols, __nv_bfloat16* __restrict__ dx, ConvGeom g) {
+  // A block takes 256 / cvec input pixels at a time (one when a pixel has more than 256 channel groups); a thread
+  // keeps its pixel lane and first channel group for the whole kernel, so the flat-index divisions happen once.
   const int cvec = g.C / 8;
-  const long long total = static_cast<long long>(g.N) * g.H * g.W * cvec;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int c8 = static_cast<int>(i % cvec);
-    long long pix = i / cvec;
-    const int w = static_cast<int>(pix % g.W);
-    const int h = static_cast<int>((pix / g.W) % g.H);
-    const int n = static_cast<int>(pix / (static_cast<long long>(g.W) * g.H));
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int r = 0; r < g.KH; ++r) {
-      const int hn = h + g.pad - r;
-      if (hn < 0 || hn % g.stride) continue;
-      const int ho = hn / g.stride;
-      if (ho >= g.Ho) continue;
-      for (int s = 0; s < g.KW; ++s) {
-        const int wn = w + g.pad - s;
-        if (wn < 0 || wn % g.stride) continue;
-        const int wo = wn / g.stride;
-        if (wo >= g.Wo) continue;
-        float f[8];
-        ld8(dcols + ((static_cast<long long>(n) * g.Ho + ho) * g.Wo + wo) * g.Kpad +
-                (static_cast<long long>(r) * g.KW + s) * g.C + c8 * 8, f);
+  const int ppb = cvec >= 256 ? 1 : 256 / cvec;
+  const int pl = threadIdx.x / cvec, c_first = threadIdx.x - pl * cvec;
+  if (pl >= ppb) return;
+  const int c_step = ppb == 1 ? 256 : cvec;            // one group per thread unless the pixel is wider than the block
+  const int pixels = g.N * g.H * g.W;
+  for (int pix = blockIdx.x * ppb + pl; pix < pixels; pix += gridDim.x * ppb) {
+    const int w = pix % g.W, t = pix / g.W;
+    const int h = t % g.H, n = t / g.H;
+    for (int c8 = c_first; c8 < cvec; c8 += c_step) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int r = 0; r < g.KH; ++r) {
+        const int hn = h + g.pad - r;
+        if (hn < 0 || hn % g.stride) continue;
+        const int ho = hn / g.stride;
+        if (ho >= g.Ho) continue;
+        for (int s2 = 0; s2 < g.KW; ++s2) {
+          const int wn = w + g.pad - s2;
+          if (wn < 0 || wn % g.stride) continue;
+          const int wo = wn / g.stride;
+          if (wo >= g.Wo) continue;
+          float f[8];
+          ld8(dcols + ((static_cast<long long>(n) * g.Ho + ho) * g.Wo + wo) * g.Kpad + (r * g.KW + s2) * g.C + c8 * 8, f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+          for (int j = 0; j < 8; ++j) acc[j] += f[j];
+        }
       }
+      st8(dx + static_cast<long long>(pix) * g.C + c8 * 8, acc);
     }
-    st8(dx + pix * g.C + c8 * 8, acc);
   }
 }
 
@@ -199,17 +205,29 @@ bn_stats_partial_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__
   bn_fold_and_store(a, b, part, C, blockIdx.x * 64);
 }
 
-// mean / rstd per channel from the partials; also updates the running statistics.
-__global__ void bn_stats_final_kernel(const float* __restrict__ part, int slices, int C, long long rows, float eps,
-                                      float momentum, float* __restrict__ mean, float* __restrict__ rstd,
-                                      float* __restrict__ run_mean, float* __restrict__ run_var) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+// mean / rstd per channel from the partials; also updates the running statistics.  Block = 32 channels x 8 groups
+// of slices (a thread adds every eighth slice in double precision; the eight sums meet in shared memory).
+__global__ void __launch_bounds__(256)
+bn_stats_final_kernel(const float* __restrict__ part, int slices, int C, long long rows, float eps, float momentum,
+                      float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ run_mean,
+                      float* __restrict__ run_var) {
+  __shared__ double ss[8][32], qq[8][32];
+  const int cl = threadIdx.x & 31, sg = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cl;
   double s = 0.0, q = 0.0;
-  for (int k = 0; k < slices; ++k) {
-    s += part[static_cast<long long>(k) * 2 * C + c];
-    q += part[static_cast<long long>(k) * 2 * C + C + c];
-  }
+  if (c < C)
+    for (int k = sg; k < slices; k += 8) {
+      s += part[static_cast<long long>(k) * 2 * C + c];
+      q += part[static_cast<long long>(k) * 2 * C + C + c];
+    }
+  ss[sg][cl] = s;
+  qq[sg][cl] = q;
+  __syncthreads();
+  if (sg != 0 || c >= C) return;
+  s = 0.0;
+  q = 0.0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { s += ss[k][cl]; q += qq[k][cl]; }
   const double m = s / static_cast<double>(rows);
   double var = q / static_cast<double>(rows) - m * m;
   if (var < 0.0) var = 0.0;
@@ -348,16 +366,28 @@ bn_bwd_partial_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
   bn_fold_and_store(a, b, part, C, blockIdx.x * 64);
 }
 
-// sums[0][c] = sum g, sums[1][c] = sum g*xhat; dgamma (+)= sums[1], dbeta (+)= sums[0]
-__global__ void bn_bwd_final_kernel(const float* __restrict__ part, int slices, int C, float* __restrict__ sums,
-                                    float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+// sums[0][c] = sum g, sums[1][c] = sum g*xhat; dgamma (+)= sums[1], dbeta (+)= sums[0].  Same block layout as the
+// forward's final kernel; the eight group sums are added in a fixed order.
+__global__ void __launch_bounds__(256)
+bn_bwd_final_kernel(const float* __restrict__ part, int slices, int C, float* __restrict__ sums,
+                    float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
+  __shared__ float ss[8][32], qq[8][32];
+  const int cl = threadIdx.x & 31, sg = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cl;
   float s = 0.f, q = 0.f;
-  for (int k = 0; k < slices; ++k) {
-    s += part[static_cast<long long>(k) * 2 * C + c];
-    q += part[static_cast<long long>(k) * 2 * C + C + c];
-  }
+  if (c < C)
+    for (int k = sg; k < slices; k += 8) {
+      s += part[static_cast<long long>(k) * 2 * C + c];
+      q += part[static_cast<long long>(k) * 2 * C + C + c];
+    }
+  ss[sg][cl] = s;
+  qq[sg][cl] = q;
+  __syncthreads();
+  if (sg != 0 || c >= C) return;
+  s = 0.f;
+  q = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { s += ss[k][cl]; q += qq[k][cl]; }
   sums[c] = s;
   sums[C + c] = q;
   dbeta[c] = accumulate ? dbeta[c] + s : s;
@@ -542,8 +572,10 @@ int im2col_launch(const void* x, void* cols, int N, int H, int W, int C, int KH,
   const auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
   auto* cb = reinterpret_cast<__nv_bfloat16*>(cols);
   if (C % 8 == 0 && Kpad == KH * KW * C) {
-    const long long work = static_cast<long long>(N) * g.Ho * g.Wo * KH * KW * (C / 8);
-    im2col_kernel<<<grid_for(work, num_sms), 256, 0, stream>>>(xb, cb, g);
+    const long long rows = static_cast<long long>(N) * g.Ho * g.Wo;
+    if (rows > 0x7fffffffLL) return -3;
+    const int blocks = static_cast<int>(rows < num_sms * 16LL ? rows : num_sms * 16LL);
+    im2col_kernel<<<blocks, 256, 0, stream>>>(xb, cb, g);
   } else {
     const long long work = static_cast<long long>(N) * g.Ho * g.Wo * Kpad;
     im2col_small_c_kernel<<<grid_for(work, num_sms), 256, 0, stream>>>(xb, cb, g);
@@ -555,8 +587,11 @@ int col2im_launch(const void* dcols, void* dx, int N, int H, int W, int C, int K
                   int num_sms, cudaStream_t stream) {
   if (C % 8) return -3;
   ConvGeom g{N, H, W, C, KH, KW, stride, pad, (H + 2 * pad - KH) / stride + 1, (W + 2 * pad - KW) / stride + 1, Kpad};
-  const long long work = static_cast<long long>(N) * H * W * (C / 8);
-  col2im_kernel<<<grid_for(work, num_sms), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dcols),
+  const long long pixels = static_cast<long long>(N) * H * W;
+  if (pixels > 0x7fffffffLL) return -3;
+  const int cvec = C / 8, ppb = cvec >= 256 ? 1 : 256 / cvec;
+  const long long want = (pixels + ppb - 1) / ppb;
+  col2im_kernel<<<static_cast<int>(want < num_sms * 16LL ? want : num_sms * 16LL), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dcols),
                                                              reinterpret_cast<__nv_bfloat16*>(dx), g);
   return static_cast<int>(cudaGetLastError());
 }
@@ -580,7 +615,7 @@ int bn_fwd_launch(const void* x, const void* residual, const float* gamma, const
   const int rps = static_cast<int>((rows + slices - 1) / slices);
   dim3 grid((C / 8 + 7) / 8, slices);
   bn_stats_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), part, rows, C, rps);
-  bn_stats_final_kernel<<<(C + 255) / 256, 256, 0, stream>>>(part, slices, C, rows, eps, momentum, mean, rstd,
+  bn_stats_final_kernel<<<(C + 31) / 32, 256, 0, stream>>>(part, slices, C, rows, eps, momentum, mean, rstd,
                                                              run_mean, run_var);
   bn_apply_kernel<<<bn_grid(rows, C, num_sms), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(residual), mean, rstd, gamma,
@@ -611,7 +646,7 @@ int bn_bwd_launch(const void* dy, const void* x, const void* y, const float* mea
                                                   reinterpret_cast<const __nv_bfloat16*>(x),
                                                   reinterpret_cast<const __nv_bfloat16*>(y), mean, rstd, part, rows,
                                                   C, rps, relu);
-  bn_bwd_final_kernel<<<(C + 255) / 256, 256, 0, stream>>>(part, slices, C, sums, dgamma, dbeta, accumulate);
+  bn_bwd_final_kernel<<<(C + 31) / 32, 256, 0, stream>>>(part, slices, C, sums, dgamma, dbeta, accumulate);
   bn_bwd_dx_kernel<<<bn_grid(rows, C, num_sms), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
       reinterpret_cast<const __nv_bfloat16*>(y), mean, rstd, gamma, sums, reinterpret_cast<__nv_bfloat16*>(dx),
