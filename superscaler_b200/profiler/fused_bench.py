@@ -34,18 +34,29 @@ def gemm_peak_tflops() -> tuple:
         return 1590.0, "fallback"
 
 
+_L2_FLUSH = None
+
+
 def _timed(fn, warmup: int, iters: int) -> float:
+    """Mean device time of one call (CUDA events around every call, max over ranks).  Between calls a 256 MB buffer
+    is overwritten, outside the timed span, so that operands come from HBM and not from the 126 MB L2."""
+    global _L2_FLUSH
+    if _L2_FLUSH is None:
+        _L2_FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
+    pairs = []
     for _ in range(iters):
+        _L2_FLUSH.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
         fn()
-    e1.record()
+        e1.record()
+        pairs.append((e0, e1))
     torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    t = torch.tensor([sum(a.elapsed_time(b) for a, b in pairs) / iters], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
