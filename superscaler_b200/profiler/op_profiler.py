@@ -13,8 +13,10 @@ How it measures (reference: profiler/op_profiler.py:283-459 uses wall clock arou
   * ops are visited in order; each op's inputs are the detached outputs of its predecessor;
   * forward and backward are timed separately with CUDA events on the launching stream, after warm-up, as the
     device time per call of `--prof-repeat-times` calls launched back to back (the queue stays full, as in a
-    training step) with the L2 cache flushed before every call (inputs and weights come from HBM, as in a
-    training step); at tp > 1 the op's own collectives are inside the timed region;
+    training step); before every call the L2 cache is evicted and the op's direct inputs (forward: its input
+    tensors, backward: the incoming gradients) are read once, so that weights and saved activations come from HBM
+    while what the previous kernel would just have written is L2-resident as far as it fits -- the state a
+    training step leaves; at tp > 1 the op's own collectives are inside the timed region;
   * ops that the runtime executes as one fused kernel when co-located (flash attention; GEMM + epilogue) are
     timed fused: the first member carries the time, the others carry 0, which is what the runtime will see;
   * memory columns come from torch.cuda.memory_allocated / max_memory_allocated deltas around the calls.
@@ -67,6 +69,17 @@ def _flush_l2() -> None:
     _L2_FLUSH.zero_()
 
 
+def _evict_then_touch(tensors) -> None:
+    """The state a training step leaves in front of an op: weights and saved activations come from HBM (thousands of
+    kernels ran since they were last used), but what the PREVIOUS kernel just wrote is still in the 126 MB L2 as far
+    as it fits.  So: evict everything, then read the op's direct inputs once (one multi-tensor kernel)."""
+    _flush_l2()
+    if _FLUSH_ENABLED:
+        ts = [t for t in tensors if isinstance(t, torch.Tensor) and t.is_cuda and t.is_floating_point() and t.numel() > 0]
+        if ts:
+            torch._foreach_norm(ts)
+
+
 def _span_ms(body, n: int) -> float:
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -78,14 +91,14 @@ def _span_ms(body, n: int) -> float:
     return e0.elapsed_time(e1) / n
 
 
-def _event_ms(fn, repeat: int, warmup: int) -> float:
+def _event_ms(fn, repeat: int, warmup: int, inputs=()) -> float:
     """Device time per call of `repeat` calls launched back to back (the queue stays full, as in a training step,
-    so the launch latency of short kernels is not charged to the op), each preceded by an L2 flush whose own time
-    is measured the same way and subtracted."""
+    so the launch latency of short kernels is not charged to the op), each preceded by an L2 eviction and a read of
+    the op's direct inputs, whose own time is measured the same way and subtracted."""
     for _ in range(warmup):
         fn()
-    flush = _span_ms(lambda i: _flush_l2(), repeat)
-    both = _span_ms(lambda i: (_flush_l2(), fn()), repeat)
+    flush = _span_ms(lambda i: _evict_then_touch(inputs), repeat)
+    both = _span_ms(lambda i: (_evict_then_touch(inputs), fn()), repeat)
     return max(both - flush, 0.0)
 
 
@@ -116,7 +129,7 @@ def profile_plan(plan: dict, rank: int, world: int, overrides: dict, repeat: int
             return local
 
         with torch.no_grad():
-            t_fwd = _event_ms(fwd, repeat, warmup)
+            t_fwd = _event_ms(fwd, repeat, warmup, [snapshot.get(k) for k in op.reads])
         # backward: fresh forward (untimed) + timed backward of all floating outputs
         def fwd_bwd_setup():
             out = fwd()
@@ -130,10 +143,10 @@ def profile_plan(plan: dict, rank: int, world: int, overrides: dict, repeat: int
             if not prepared[0][1]:
                 return 0.0
             grads = [[torch.ones_like(o) if o.dim() == 0 else torch.randn_like(o) for o in outs] for _, outs in prepared]
-            flush = _span_ms(lambda i: _flush_l2(), n)
+            flush = _span_ms(lambda i: _evict_then_touch(grads[i]), n)
 
             def one(i):
-                _flush_l2()
+                _evict_then_touch(grads[i])     # the incoming gradients were just written; saved activations are cold
                 torch.autograd.backward(prepared[i][1], grads[i])
 
             return max(_span_ms(one, n) - flush, 0.0)
@@ -199,6 +212,8 @@ def model_table(model: str, size: str):
         shape = dict(model_size=size, num_layers=1, encoder_seq_length=es, decoder_seq_length=ds,
                      max_position_embeddings=es, num_attention_heads=heads, kv_channels=kv, hidden_size=hidden,
                      ffn_hidden_size=ffn, vocab_size=vocab)
+        if size in sc.B200_T5_SIZES:   # the B200 definition: ReLU feed-forward, relative-position buckets (as the search writes it)
+            shape.update(activation="relu", relative_position_bias=True, relative_attention_num_buckets=32)
         return (shape, {}, t5_op_names(1), opinfo.T5_TUNABLE,
                 lambda plan: syn.t5_batch(plan["global_batch_size"], es, ds, vocab, seed=1))
     if model == "resnet":
