@@ -33,8 +33,10 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
     shuffled sample order (a function of the seed and of --train-iters), so a run resumed with the same
     --train-iters continues where the data stopped."""
     import numpy as np
+    if trainer.model_name == "resnet":
+        return make_image_batch_fn(trainer, prefix, seed)
     from ..data.indexed import GPTSampleDataset, TokenCorpus
-    assert trainer.model_name == "gpt", "--data-path feeds the GPT entry point"
+    assert trainer.model_name == "gpt", "--data-path feeds the GPT and Wide-ResNet entry points"
     wide = os.path.exists(prefix + ".u32")
     corpus = TokenCorpus.from_files(prefix + (".u32" if wide else ".bin"), prefix + ".npy",
                                     dtype=np.uint32 if wide else np.uint16)
@@ -51,6 +53,24 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
             # runtime/megatron/utils.py)
             out["loss_mask"] = (out["ids"] != eod_token).to(torch.float32)
         return {k: v.pin_memory() for k, v in out.items()} if torch.cuda.is_available() else out
+
+    return batch
+
+
+def make_image_batch_fn(trainer: Trainer, root: str, seed: int):
+    """Batches of an image folder (`root/train/<class>/<file>`, or `root/<class>/<file>`): random-resized crop, flip,
+    colour jitter and the AutoAugment ImageNet policy, each decision a function of (seed, epoch, index) so that a
+    resumed run sees the same pictures (reference: runtime/megatron/data/vit_dataset.py:22-42)."""
+    from ..data.images import ImageFolder, batch_indices, image_batch
+    train_dir = os.path.join(root, "train")
+    data = ImageFolder(train_dir if os.path.isdir(train_dir) else root, size=trainer.cfg.image_size, train=True, seed=seed)
+    assert len(data.classes) <= trainer.cfg.num_classes, "more class directories than the model has classes"
+    gbs = trainer.plan["global_batch_size"]
+
+    def batch(i):
+        idx, epoch = batch_indices(len(data), gbs, i, seed)
+        data.set_epoch(epoch)
+        return image_batch(data, idx, pin=torch.cuda.is_available())
 
     return batch
 
