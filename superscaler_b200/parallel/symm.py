@@ -22,20 +22,32 @@ class SymmetricBuffer:
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
-        self.tensor = symm.empty(numel, dtype=dtype, device=device)
-        self.tensor.zero_()
-        self.handle = symm.rendezvous(self.tensor, self.group.group_name)
         nflags = native.ext().comm_max_blocks() * self.world
-        self.flags = symm.empty(nflags, dtype=torch.int32, device=device)
+        off = flag_off = 0
+        if os.environ.get("SSB_CANARIES", "0") == "1":
+            # guard words in front of and behind both buffers (parallel/guards.py); every rank does the same, so the
+            # payloads start at the same offset of the symmetric allocations
+            from .guards import REGISTRY, GuardedBuffer
+            alloc = lambda n, dtype, device: symm.empty(n, dtype=dtype, device=device)      # noqa: E731
+            data = REGISTRY.add(GuardedBuffer(numel, dtype, device, alloc=alloc, name=f"symmetric buffer of {numel}"))
+            flg = REGISTRY.add(GuardedBuffer(nflags, torch.int32, device, alloc=alloc, name="symmetric flag table"))
+            raw, self.tensor, off = data.raw, data.body, data.body_offset_bytes
+            raw_flags, self.flags, flag_off = flg.raw, flg.body, flg.body_offset_bytes
+        else:
+            raw = self.tensor = symm.empty(numel, dtype=dtype, device=device)
+            raw_flags = self.flags = symm.empty(nflags, dtype=torch.int32, device=device)
+        self.tensor.zero_()
         self.flags.zero_()
-        self.flag_handle = symm.rendezvous(self.flags, self.group.group_name)
-        self.peer_ptrs = torch.tensor(list(self.handle.buffer_ptrs), dtype=torch.int64, device=device)
-        self.flag_ptrs = torch.tensor(list(self.flag_handle.buffer_ptrs), dtype=torch.int64, device=device)
+        self.handle = symm.rendezvous(raw, self.group.group_name)
+        self.flag_handle = symm.rendezvous(raw_flags, self.group.group_name)
+        self.peer_ptrs = torch.tensor([p + off for p in self.handle.buffer_ptrs], dtype=torch.int64, device=device)
+        self.flag_ptrs = torch.tensor([p + flag_off for p in self.flag_handle.buffer_ptrs], dtype=torch.int64, device=device)
         use_nvls = os.environ.get("SSB_DISABLE_MULTIMEM", "0") != "1"
         mc = 0
         if use_nvls:
             try:
                 mc = int(self.handle.multicast_ptr or 0)
+                mc = mc + off if mc else 0
             except Exception:  # noqa: BLE001 - no multicast support on this fabric
                 mc = 0
         self.multicast_ptr = mc

@@ -249,11 +249,17 @@ class Trainer:
         saved.  Called where the host synchronises anyway: `loss_value` and `save_checkpoint`.  With a
         `health_monitor` attached the failure is published to the other ranks before the exception leaves."""
         code = self._read_device_status()
-        if code == 0:
+        from ..parallel.guards import REGISTRY
+        damaged = REGISTRY.check() if REGISTRY.buffers else []
+        if code == 0 and not damaged:
             return
         from .health import DeviceStatusError, device_status_message
-        err = DeviceStatusError(code, f"iteration {self.iteration}: {device_status_message(code)}; the results of "
-                                      "that kernel are undefined, later weights are not to be saved")
+        if damaged:      # guard words around a peer-written buffer were overwritten (SSB_CANARIES=1)
+            err = DeviceStatusError(code, f"iteration {self.iteration}: " + "; ".join(damaged) + "; memory next to a "
+                                    "symmetric buffer was written, later weights are not to be saved")
+        else:
+            err = DeviceStatusError(code, f"iteration {self.iteration}: {device_status_message(code)}; the results of "
+                                          "that kernel are undefined, later weights are not to be saved")
         monitor = getattr(self, "health_monitor", None)
         if monitor is not None:
             monitor.publish_failure(f"DeviceStatusError: {err}")

@@ -243,3 +243,41 @@ def test_device_status_word_stops_training_and_saving(tmp_path):
         HealthMonitor(store, rank=1, world=2).check_peers()
     checkpointing.save_checkpoint(t, str(tmp_path))      # status read and cleared: saving works again
     assert any(tmp_path.iterdir())
+
+
+def test_guard_words_report_the_first_overwritten_word_and_stop_training():
+    """Guard bands around a buffer (what SSB_CANARIES=1 puts around symmetric memory): intact after in-range writes,
+    a write one element past either end is reported with its position, and the trainer refuses to go on."""
+    import torch
+    from superscaler_b200.data.synthetic import gpt_batch
+    from superscaler_b200.parallel import guards
+    from superscaler_b200.runtime.health import DeviceStatusError
+    from superscaler_b200.runtime.trainer import Trainer
+    from helpers import tiny_gpt_plan
+    for dtype, n in ((torch.float32, 1000), (torch.bfloat16, 1001), (torch.int32, 7)):
+        b = guards.GuardedBuffer(n, dtype, "cpu", name="payload")
+        assert b.body.numel() == n and b.body_offset_bytes == guards.GUARD_BYTES
+        assert b.raw.data_ptr() + b.body_offset_bytes == b.body.data_ptr()
+        b.body.fill_(3)
+        assert b.check() == []
+        b.raw[b.guard_elems + n + b.tail_pad_elems] = 1                    # first element behind the payload
+        (line,) = b.check()
+        assert "guard word 0 behind the payload" in line
+        b.arm()
+        b.raw[b.guard_elems - 1] = 1                                       # last element in front of it
+        (line,) = b.check()
+        assert "in front of the payload" in line and f"guard word {guards.GUARD_BYTES // 4 - 1}" in line
+    reg = guards.REGISTRY
+    saved = list(reg.buffers)
+    try:
+        reg.buffers.clear()
+        t = Trainer(tiny_gpt_plan(), device="cpu", lr_warmup_steps=0,
+                    model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0))
+        buf = reg.add(guards.GuardedBuffer(64, torch.float32, "cpu", name="symmetric buffer of 64"))
+        stats = t.train_step(gpt_batch(4, 128, 512, seed=1))
+        t.loss_value(stats)                                                # guards intact: nothing happens
+        buf.raw[0] = 0.0
+        with pytest.raises(DeviceStatusError, match="guard word 0 in front of the payload"):
+            t.loss_value(stats)
+    finally:
+        reg.buffers[:] = saved
