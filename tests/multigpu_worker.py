@@ -97,7 +97,6 @@ def main():
                                                                 or "MLP-gelu" in n) else 1 for n in names]]
         mixed["data_parallel_size_of_each_op"] = [[world // t for t in mixed["model_parallel_size_of_each_op"][0]]]
         mixed["resharding_stages"] = [True]
-        import os
         for fused_gather in ("1", "0"):
             os.environ["SSB_FUSED_GATHER"] = fused_gather
             t = Trainer(mixed, rank=rank, world_size=world, model_overrides=nd, lr_warmup_steps=0, fused_comm=True)
@@ -206,6 +205,15 @@ def main():
         assert native.check_status() == 0
         if rank == 0:
             print("AG_GEMM_OK", worst, flush=True)
+    # guard words around the symmetric buffers (placed when SSB_CANARIES=1; none otherwise) must be intact
+    from superscaler_b200.parallel.guards import REGISTRY
+    torch.cuda.synchronize()
+    damaged = REGISTRY.check()
+    assert not damaged, damaged
+    if os.environ.get("SSB_CANARIES") == "1":
+        assert REGISTRY.buffers, "SSB_CANARIES=1 but no guarded buffer was allocated"
+        if rank == 0:
+            print("GUARDS_OK", len(REGISTRY.buffers), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -11,8 +11,8 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _launch(mode: str, n: int = 2):
-    env = dict(os.environ, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
+def _launch(mode: str, n: int = 2, **extra_env):
+    env = dict(os.environ, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"), **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", "29731", os.path.join(HERE, "multigpu_worker.py"), mode]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
@@ -52,3 +52,14 @@ def test_fused_collective_kernels_on_four_gpus(mode, ok):
     if torch.cuda.device_count() < 4:
         pytest.skip("needs 4 GPUs")
     assert ok in _launch(mode, n=4)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_guard_words_around_symmetric_buffers_survive_the_collectives():
+    """With SSB_CANARIES=1 the symmetric buffers sit 256 bytes into guarded allocations: the all-reduce, the
+    reduce-scatter / all-gather of the sharded update and a whole data-parallel training run must give the same
+    results through the shifted peer and multicast addresses and leave every guard word as it was."""
+    out = _launch("allreduce", SSB_CANARIES="1")
+    assert "ALLREDUCE_OK" in out and "GUARDS_OK" in out
+    out = _launch("train", SSB_CANARIES="1")
+    assert "TRAIN_OK" in out and "GUARDS_OK" in out
