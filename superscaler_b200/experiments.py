@@ -96,7 +96,7 @@ def search(a, system: str = "aceso") -> None:
                "--config-save-path", cfg, "--config-suffix", time.strftime("%Y-%m-%d-%H-%M-%S"), "--shapes", a.shapes,
                "--max-num-hops", "7", "--time-budget-total", str(a.budget), "--num-of-saved-configs", "3", *layers]
         if system == "aceso":
-            cmd += ["--initial-point", "balance"]
+            cmd += ["--initial-point", a.initial_point]
             if a.model == "resnet":
                 cmd += ["--finetune-after-trial", "1"]
         _run(cmd, a.dry_run)
@@ -248,6 +248,9 @@ def main(argv=None) -> None:
     ap.add_argument("--database", default=None, help="profiled database (default: profiled-time-b200/ with --shapes b200)")
     ap.add_argument("--shapes", default="b200", choices=["b200", "reference"])
     ap.add_argument("--results", default="./logs", help="root of search logs, plans, runtime CSVs, tables and figures")
+    ap.add_argument("--initial-point", default="balance",
+                       help="balance (the reference's scripts), imbalance_gpu, imbalance_op, grid (start from the best "
+                            "uniform plan: never slower than the baseline) or a plan JSON")
     ap.add_argument("--budget", type=int, default=200, help="search time budget per stage count (s)")
     ap.add_argument("--max-gpus", type=int, default=None, help="skip cases that need more GPUs than this")
     ap.add_argument("--top", type=int, default=3, help="how many saved plans per case `execute` runs")

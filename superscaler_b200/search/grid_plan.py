@@ -79,6 +79,27 @@ def grid_search(ctx: SearchContext) -> List[Plan]:
     return [by_time[t] for t in sorted(by_time)]
 
 
+def best_uniform_plan(ctx: SearchContext, pp: int):
+    """The fastest uniform plan with `pp` stages that fits the memory limit (None when there is none): the starting
+    point `--initial-point grid` gives the search, so that what the search returns is never slower than the grid."""
+    a = ctx.args
+    best, best_t = None, float("inf")
+    for tp in ctx.db.tp_list:
+        if tp > a.max_tp or a.num_gpus % (pp * tp):
+            continue
+        dp = a.num_gpus // (pp * tp)
+        for mbs in a.micro_batch_size:
+            if mbs % dp or mbs // dp not in a.micro_batch_size or a.global_batch_size % mbs:
+                continue
+            for recompute in (False, True):
+                for plan in uniform_plans(ctx, pp, tp, dp, mbs, recompute):
+                    ctx.cost.evaluate(plan)
+                    t = max(plan.time_list)
+                    if max(plan.memory_list) < a.memory_limit and t < best_t:
+                        best, best_t = plan, t
+    return best
+
+
 def main(argv=None) -> None:
     p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     add_cli_arguments(p)

@@ -43,6 +43,10 @@ def initial_plan(ctx: SearchContext, num_stages: int) -> Optional[Plan]:
         return imbalanced_op_plan(ops, num_stages, model_name=a.model_name, num_layers=a.num_layers,
                                   num_gpus=a.num_gpus, global_bs=a.global_batch_size, micro_bs=a.micro_batch_size[0],
                                   max_tp=a.max_tp, flex_recompute=a.flex_recompute)
+    if a.initial_point == "grid":
+        # not in the reference: start every stage count from its best uniform (Megatron-style) plan
+        from .grid_plan import best_uniform_plan
+        return best_uniform_plan(ctx, num_stages)
     return load_plan(a.initial_point, ops)[0]
 
 

@@ -126,6 +126,29 @@ def test_uniform_grid_baseline_and_predictor_on_the_reference_database(tmp_path)
     assert 512 / (best / 1000) < 512 / 58.76092 / 1.2          # the searched plan is more than 1.2x faster
 
 
+def test_search_started_from_the_grid_is_never_slower_than_the_grid(tmp_path):
+    """`--initial-point grid` (not in the reference) starts every stage count from its best uniform plan, so the
+    search's answer is at least as fast as the Megatron-style baseline; on the 4-GPU GPT database the search then
+    improves the 4-stage uniform plan further."""
+    from superscaler_b200.search.grid_plan import best_uniform_plan
+    out = str(tmp_path) + "/"
+    for sub in ("csv", "top_configs", "trends"):
+        os.makedirs(out + sub, exist_ok=True)
+    args = SearchArgs(model_name="gpt", model_size="1_3B", global_batch_size=512, micro_batch_size=[1, 2, 4, 8],
+                      num_nodes=1, num_gpus_per_node=4, memory_limit=12000, profiled_time_path=DB, config_save_path=out,
+                      log_path=out, config_suffix="t", max_num_hops=7, time_budget_total=200, multi_process=False,
+                      initial_point="grid").finalize()
+    ctx = SearchContext(args, verbose=False)
+    start = best_uniform_plan(ctx, 4)
+    assert start is not None and max(start.memory_list) < 12000
+    t_grid = max(start.time_list)
+    Searcher(ctx).run(4)
+    with open(f"{out}csv/info_gpt_1_3B_4stages_t.csv") as f:
+        t_search = max(float(r[1]) for r in list(csv.reader(f))[1:])
+    assert t_search <= t_grid + 1e-6
+    assert t_search < 0.9 * t_grid           # the per-op moves find more than 10 % over the uniform 4-stage plan
+
+
 def test_extrapolated_tables_scale_by_the_hidden_size_and_drive_a_search(tmp_path):
     """Tables for an unprofiled GPT size: linear-layer times and weights grow with the square of the hidden-size
     ratio, everything else linearly; the collective tables are re-keyed for the new tensor sizes, and a search
