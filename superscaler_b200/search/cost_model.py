@@ -2,9 +2,11 @@
 
 Reproduces the reference model term by term (search/aceso_cost_model.py) -- the arithmetic order is kept
 so that predictions on the reference's committed databases are bit-identical -- and extends it with one
-term: when the database carries the overlap columns written by this framework's profiler, the part of
-an op's own collective that the fused compute+collective kernels hide is subtracted (priced as
-max(compute, comm) instead of compute + comm).  Databases without those columns predict as before.
+optional term: when a database carries the columns `fwd_overlap_comm` / `bwd_overlap_comm` (communication time
+hidden behind an op's own compute), they are subtracted from the op's time.  This framework's op profiler times a
+tensor-parallel op WITH its fused collective inside the timed region, so its tables already hold the overlapped time
+and it writes zeros in those columns; they serve databases measured with unfused collectives.  Databases without
+the columns predict as before.
 
   stage time      = (sum fwd + sum bwd + boundary-in comm + boundary-out comm + recompute fwd) / 1000  [ms]
   pipeline time_i = stage_time_i * (num_microbatches - 1) + sum_j stage_time_j
