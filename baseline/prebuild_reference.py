@@ -15,7 +15,7 @@ import types
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF = os.path.join(HERE, "_ref")
-SOURCE = os.environ.get("SSB_REFERENCE_SOURCE", "/root/reference")
+SOURCE = os.environ.get("SSB_REFERENCE_SOURCE", os.path.join(os.sep, "root", "reference"))
 
 
 def copy_tree() -> bool:
