@@ -24,7 +24,7 @@ import csv
 import glob
 import os
 import sys
-from typing import Callable, Dict, Iterator, List, Optional, Sequence, Tuple
+from typing import Callable, Iterator, List, Optional, Tuple
 
 import numpy as np
 import torch

@@ -28,7 +28,6 @@ from __future__ import annotations
 import argparse
 import csv
 import glob
-import json
 import os
 import subprocess
 import sys
