@@ -377,6 +377,21 @@ class InverseClozeDataset:
                 "block_data": np.asarray([first, last, doc, block], dtype=np.int64)}
 
 
+def bert_batch_of(dataset: BertDataset, indices: Sequence[int]) -> Dict[str, torch.Tensor]:
+    """One global batch for the BERT trainer: ids, token types, the number of real tokens per sample, masked-LM
+    labels (-1 where nothing is predicted) with their loss mask, and the sentence-order flag."""
+    rows = [dataset[int(i) % len(dataset)] for i in indices]
+    out = {"ids": torch.from_numpy(np.stack([r["text"] for r in rows])),
+           "types": torch.from_numpy(np.stack([r["types"] for r in rows])),
+           "enc_lens": torch.tensor([int(r["padding_mask"].sum()) for r in rows], dtype=torch.int32),
+           "labels": torch.from_numpy(np.stack([r["labels"] for r in rows])),
+           "loss_mask": torch.from_numpy(np.stack([r["loss_mask"] for r in rows]).astype(np.float32)),
+           "nsp": torch.tensor([r["is_random"] for r in rows], dtype=torch.int64)}
+    if torch.cuda.is_available():
+        out = {k: v.pin_memory() for k, v in out.items()}
+    return out
+
+
 def t5_batches(dataset: T5Dataset, global_bs: int, steps: int, start: int = 0) -> Iterator[Dict[str, torch.Tensor]]:
     """Global batches for the T5 trainer: encoder ids, decoder ids, labels (padding positions 0 with loss_mask 0)
     and the number of real encoder tokens per sample, in pinned memory."""

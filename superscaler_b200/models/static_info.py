@@ -81,6 +81,8 @@ def op_io(name: str) -> Tuple[Tuple[str, ...], Tuple[str, ...]]:
         return ("x", "bias"), ("x",)
     if name in ("gpt-post-process", "t5-post-process"):
         return ("x", "labels", "loss_mask"), ("loss",)
+    if name == "bert-post-process":
+        return ("x", "labels", "loss_mask", "nsp"), ("loss",)
     raise KeyError(f"no static info for op {name}")
 
 
@@ -118,7 +120,7 @@ def required_layouts(name: str, algo: int) -> Dict[str, Layout]:
         return {"x": ROWS, "bias": VEC, "residual": ROWS}
     if n == "MLP-gelu":
         return {"x": COLS, "bias": VEC_COLS}
-    if name in ("gpt-post-process", "t5-post-process"):
+    if name in ("gpt-post-process", "t5-post-process", "bert-post-process"):
         return {"x": ROWS}
     raise KeyError(f"no static info for op {name}")
 
@@ -154,12 +156,12 @@ def produced_layouts(name: str, algo: int) -> Dict[str, Layout]:
         return {"x": ROWS}
     if n == "MLP-gelu":
         return {"x": COLS}
-    if name in ("gpt-post-process", "t5-post-process"):
+    if name in ("gpt-post-process", "t5-post-process", "bert-post-process"):
         return {}
     raise KeyError(f"no static info for op {name}")
 
 
-DATA_KEYS = ("ids", "dec_ids", "labels", "loss_mask", "images", "enc_lens")
+DATA_KEYS = ("ids", "dec_ids", "labels", "loss_mask", "images", "enc_lens", "types", "nsp")
 
 
 def live_keys_before(op_names, cut: int):

@@ -27,7 +27,7 @@ from .timers import Timers
 from .trainer import Trainer
 
 
-def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, eod_token=None):
+def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, eod_token=None, vocab_file=None):
     """Batches of a GPT token corpus: `prefix`.bin holds the token ids (uint16, or uint32 with `prefix`.u32 present
     instead), `prefix`.npy the document lengths.  Batch i is global samples [i * gbs, (i + 1) * gbs) of the
     shuffled sample order (a function of the seed and of --train-iters), so a run resumed with the same
@@ -35,8 +35,16 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
     import numpy as np
     if trainer.model_name == "resnet":
         return make_image_batch_fn(trainer, prefix, seed)
+    if trainer.model_name == "bert":
+        special = None
+        if vocab_file:      # ids of the special tokens from the WordPiece vocabulary the corpus was encoded with
+            from ..data.sentences import SpecialTokens
+            from ..tokenizer.wordpiece import load_vocab
+            v = load_vocab(vocab_file)
+            special = SpecialTokens(cls=v["[CLS]"], sep=v["[SEP]"], mask=v["[MASK]"], pad=v["[PAD]"])
+        return make_bert_batch_fn(trainer, prefix, train_iters, seed, special)
     from ..data.indexed import GPTSampleDataset, TokenCorpus
-    assert trainer.model_name == "gpt", "--data-path feeds the GPT and Wide-ResNet entry points"
+    assert trainer.model_name == "gpt", "--data-path feeds the GPT, BERT and Wide-ResNet entry points"
     wide = os.path.exists(prefix + ".u32")
     corpus = TokenCorpus.from_files(prefix + (".u32" if wide else ".bin"), prefix + ".npy",
                                     dtype=np.uint32 if wide else np.uint16)
@@ -55,6 +63,20 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
         return {k: v.pin_memory() for k, v in out.items()} if torch.cuda.is_available() else out
 
     return batch
+
+
+def make_bert_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, special=None):
+    """Batches of a sentence corpus written by `data.preprocess --split-sentences`: [CLS] A [SEP] B [SEP] samples with
+    masked-LM labels and the sentence-order flag (reference: runtime/megatron/data/bert_dataset.py).  `special`
+    names the ids of [CLS], [SEP], [MASK], [PAD]; the default is their place in a BERT WordPiece vocabulary
+    (101, 102, 103, 0)."""
+    from ..data.preprocess import load_sentence_corpus
+    from ..data.sentences import BertDataset, SpecialTokens, bert_batch_of
+    tokens = special or SpecialTokens(cls=101, sep=102, mask=103, pad=0)
+    cfg, gbs = trainer.cfg, trainer.plan["global_batch_size"]
+    data = BertDataset(load_sentence_corpus(prefix), tokens, cfg.vocab, num_samples=train_iters * gbs,
+                       max_seq_length=cfg.seq_length, seed=seed, binary_head=cfg.binary_head)
+    return lambda i: bert_batch_of(data, range(i * gbs, (i + 1) * gbs))
 
 
 def make_image_batch_fn(trainer: Trainer, root: str, seed: int):
@@ -82,6 +104,8 @@ def make_batch_fn(trainer: Trainer):
         return lambda i: synthetic.gpt_batch(gbs, cfg.seq_length, cfg.vocab, seed=1234 + i)
     if trainer.model_name == "t5":
         return lambda i: synthetic.t5_batch(gbs, cfg.seq_length, cfg.dec_seq_length, cfg.vocab, seed=1234 + i)
+    if trainer.model_name == "bert":
+        return lambda i: synthetic.bert_batch(gbs, cfg.seq_length, cfg.vocab, seed=1234 + i)
     return lambda i: synthetic.resnet_batch(gbs, cfg.image_size, cfg.num_classes, seed=1234 + i)
 
 
@@ -128,6 +152,8 @@ def main(argv=None) -> None:
     ap.add_argument("--deterministic", action="store_true",
                     help="bitwise-reproducible steps: attention backward as the dK/dV + dQ kernel pair instead of the "
                          "fused kernel that sums dQ in arrival order")
+    ap.add_argument("--vocab-file", default=None,
+                    help="BERT with --data-path: the WordPiece vocabulary of the corpus (ids of [CLS] [SEP] [MASK] [PAD])")
     ap.add_argument("--data-path", default=None,
                     help="GPT token corpus prefix (<prefix>.bin uint16 token ids + <prefix>.npy document lengths); "
                          "default: synthetic batches")
@@ -178,7 +204,8 @@ def main(argv=None) -> None:
         from torch.utils.tensorboard import SummaryWriter
         writer = SummaryWriter(log_dir=args.tensorboard_dir)
     t_start = time.time()
-    batch_fn = (make_dataset_batch_fn(trainer, args.data_path, args.train_iters, args.seed, args.eod_mask_loss)
+    batch_fn = (make_dataset_batch_fn(trainer, args.data_path, args.train_iters, args.seed, args.eod_mask_loss,
+                                      args.vocab_file)
                 if args.data_path
                 else make_batch_fn(trainer))
     # synthetic batches are generated on the host before the loop (a pool of up to 4, reused in turn): building

@@ -15,7 +15,8 @@ from typing import List, Tuple
 from ..parallel.relayout import Layout, Side, Transfer
 
 DECLARING_OPS = {
-    "word_embeddings": ("encoder-embedding", "decoder-embedding", "gpt-post-process", "t5-post-process"),
+    "word_embeddings": ("encoder-embedding", "decoder-embedding", "gpt-post-process", "t5-post-process",
+                        "bert-post-process"),
     "position_embeddings": ("encoder-embedding", "decoder-embedding"),
     # T5 relative-position tables [heads / tp, buckets]: one per stack, used by every layer of the stack
     "enc_relative_attention_bias": ("enc-attention-score",),

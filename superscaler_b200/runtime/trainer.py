@@ -41,6 +41,11 @@ def _model_factory(model_name: str):
         from ..models.fused import fuse_ops
         return (m.t5_config_from_plan, lambda c: m.t5_op_names(c.num_layers),
                 lambda i, c: m.t5_layer_of(i, c.num_layers), m.build_t5_op, fuse_ops)
+    if model_name == "bert":
+        from ..models import bert as m
+        from ..models.fused import fuse_ops
+        return (m.bert_config_from_plan, lambda c: m.bert_op_names(c.num_layers),
+                lambda i, c: m.bert_layer_of(i, c.num_layers), m.build_bert_op, fuse_ops)
     if model_name == "resnet":
         from ..models import resnet as m
         return (m.resnet_config_from_plan, m.resnet_op_names, m.resnet_layer_of, m.build_resnet_op,
@@ -50,7 +55,8 @@ def _model_factory(model_name: str):
 
 # ops that keep their activations whatever the plan says: the embeddings and the loss ops (the search never marks
 # them either, reference: search/model_ops_info.py:76-90)
-_NEVER_RECOMPUTED = ("encoder-embedding", "decoder-embedding", "gpt-post-process", "t5-post-process", "fc")
+_NEVER_RECOMPUTED = ("encoder-embedding", "decoder-embedding", "gpt-post-process", "t5-post-process",
+                     "bert-post-process", "fc")
 
 
 def _validate_plan(plan: dict) -> None:
@@ -186,7 +192,7 @@ class Trainer:
         lo = mb * self.micro_bs
         first, last = self.infos[0], self.infos[-1]
         for k, v in batch.items():
-            info = last if k in ("labels", "loss_mask") else first
+            info = last if k in ("labels", "loss_mask", "nsp") else first
             rows = self.local_rows(info, self.micro_bs)
             st[k] = v[lo + rows.start: lo + rows.stop]
         st["loss_scale"] = 1.0 / self.num_microbatches

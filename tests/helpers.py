@@ -80,3 +80,10 @@ def tiny_resnet_plan(blocks=(1, 1, 1, 1), in_channels=8, width_factor=2, global_
             "model_parallel_size_of_each_op": [[tp[s]] * ops_per_stage[s] for s in range(stages)],
             "data_parallel_size_of_each_op": [[dp[s]] * ops_per_stage[s] for s in range(stages)],
             "recompute_ops": rc, "algo_of_each_op": [[0] * c for c in ops_per_stage]}
+
+
+def tiny_bert_plan(**kw):
+    """The GPT helper's plan with the BERT op list (same op count: embedding + 13 per layer + final LayerNorm + head)."""
+    plan = tiny_gpt_plan(**kw)
+    plan["model_name"] = "bert"
+    return plan
