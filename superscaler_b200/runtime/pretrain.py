@@ -35,6 +35,8 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
     import numpy as np
     if trainer.model_name == "resnet":
         return make_image_batch_fn(trainer, prefix, seed)
+    if trainer.model_name == "t5":
+        return make_t5_batch_fn(trainer, prefix, train_iters, seed, vocab_file)
     if trainer.model_name == "bert":
         special = None
         if vocab_file:      # ids of the special tokens from the WordPiece vocabulary the corpus was encoded with
@@ -44,7 +46,7 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
             special = SpecialTokens(cls=v["[CLS]"], sep=v["[SEP]"], mask=v["[MASK]"], pad=v["[PAD]"])
         return make_bert_batch_fn(trainer, prefix, train_iters, seed, special)
     from ..data.indexed import GPTSampleDataset, TokenCorpus
-    assert trainer.model_name == "gpt", "--data-path feeds the GPT, BERT and Wide-ResNet entry points"
+    assert trainer.model_name == "gpt", "--data-path feeds the GPT, T5, BERT and Wide-ResNet entry points"
     wide = os.path.exists(prefix + ".u32")
     corpus = TokenCorpus.from_files(prefix + (".u32" if wide else ".bin"), prefix + ".npy",
                                     dtype=np.uint32 if wide else np.uint16)
@@ -77,6 +79,28 @@ def make_bert_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: in
     data = BertDataset(load_sentence_corpus(prefix), tokens, cfg.vocab, num_samples=train_iters * gbs,
                        max_seq_length=cfg.seq_length, seed=seed, binary_head=cfg.binary_head)
     return lambda i: bert_batch_of(data, range(i * gbs, (i + 1) * gbs))
+
+
+def make_t5_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, vocab_file: str, extra_ids: int = 100):
+    """Span-corruption batches of a sentence corpus written by `data.preprocess --split-sentences`: masked spans
+    become sentinels in the encoder input, the decoder predicts them (reference:
+    runtime/megatron/data/t5_dataset.py).  The sentinels, [BOS] and [EOS] are appended to the WordPiece vocabulary,
+    so the model's vocabulary has to cover `vocab + 2 + extra_ids` entries."""
+    from ..data.preprocess import load_sentence_corpus
+    from ..data.sentences import T5Dataset
+    from ..tokenizer import build_tokenizer
+    assert vocab_file, "T5 with --data-path needs --vocab-file (the WordPiece vocabulary of the corpus)"
+    tok = build_tokenizer("BertWordPieceLowerCase", vocab_file, None, vocab_extra_ids=extra_ids)
+    cfg, gbs = trainer.cfg, trainer.plan["global_batch_size"]
+    assert tok.vocab_size <= cfg.padded_vocab, f"model vocabulary {cfg.padded_vocab} < tokenizer's {tok.vocab_size}"
+    data = T5Dataset(load_sentence_corpus(prefix), tok.special_tokens(), tok.vocab_size, num_samples=train_iters * gbs,
+                     max_seq_length=cfg.seq_length, max_seq_length_dec=cfg.dec_seq_length, seed=seed)
+
+    def batch(i):
+        from ..data.sentences import t5_batches
+        return next(t5_batches(data, gbs, 1, start=i * gbs))
+
+    return batch
 
 
 def make_image_batch_fn(trainer: Trainer, root: str, seed: int):

@@ -118,3 +118,36 @@ def test_synthetic_run_resumed_past_iteration_four_sees_the_same_batches(tmp_pat
     pretrain.main(common + ["--train-iters", "7", "--load", str(tmp_path / "ckpt")])
     second = re.findall(r"lm loss: ([0-9.E+-]+)", capsys.readouterr().out)
     assert len(whole) == 7 and first + second == whole
+
+
+def test_t5_trains_on_span_corruption_batches_of_a_sentence_corpus(tmp_path):
+    """Text -> `data.preprocess --split-sentences` -> T5Dataset (sentinels appended to the WordPiece vocabulary) ->
+    the batches `runtime.pretrain --data-path --vocab-file` feeds a T5 plan."""
+    import math
+    import numpy as np
+    import torch
+    from helpers import tiny_t5_plan
+    from superscaler_b200.data import preprocess
+    from superscaler_b200.runtime.pretrain import make_dataset_batch_fn
+    from superscaler_b200.runtime.trainer import Trainer
+    words = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]"] + [f"w{i}" for i in range(60)] + [".", "!", "?"]
+    vocab = tmp_path / "vocab.txt"
+    vocab.write_text("\n".join(words) + "\n")
+    rs = np.random.RandomState(1)
+    docs = [" ".join(" ".join(rs.choice(words[5:65], size=rs.randint(5, 10))) + "." for _ in range(rs.randint(4, 8)))
+            for _ in range(10)]
+    (tmp_path / "docs.txt").write_text("\n".join(docs) + "\n")
+    prefix = str(tmp_path / "corpus")
+    preprocess.main(["--input", str(tmp_path / "docs.txt"), "--output", prefix, "--split-sentences", "--tokenizer-type",
+                     "BertWordPieceLowerCase", "--vocab-file", str(vocab)])
+    plan = tiny_t5_plan(vocab=256)                          # 68 words + [BOS] [EOS] + 100 sentinels fit
+    t = Trainer(plan, device="cpu", lr_warmup_steps=0, lr=2e-3,
+                model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0))
+    fn = make_dataset_batch_fn(t, prefix, train_iters=3, seed=7, vocab_file=str(vocab))
+    b = fn(0)
+    assert b["ids"].shape == (4, t.cfg.seq_length) and b["dec_ids"].shape == (4, t.cfg.dec_seq_length)
+    assert (b["dec_ids"][:, 0] == 68).all()                # [BOS] is the first id appended after the vocabulary
+    assert ((b["ids"] >= 70) & (b["ids"] < 170)).any()     # sentinels in the encoder input
+    assert torch.equal(fn(0)["ids"], b["ids"])
+    losses = [t.loss_value(t.train_step(fn(i))) for i in range(3)]
+    assert all(math.isfinite(v) for v in losses)
