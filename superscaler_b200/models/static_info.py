@@ -83,6 +83,10 @@ def op_io(name: str) -> Tuple[Tuple[str, ...], Tuple[str, ...]]:
         return ("x", "labels", "loss_mask"), ("loss",)
     if name == "bert-post-process":
         return ("x", "labels", "loss_mask", "nsp"), ("loss",)
+    if name == "vit-embedding":
+        return ("images",), ("x",)
+    if name == "vit-post-process":
+        return ("x", "labels"), ("loss",)
     raise KeyError(f"no static info for op {name}")
 
 
@@ -94,7 +98,7 @@ def required_layouts(name: str, algo: int) -> Dict[str, Layout]:
             return {}
         return {"x": ROWS, "residual": ROWS} if rk == "block-downsample" else {"x": ROWS}
     n = _strip(name)
-    if name == "encoder-embedding":
+    if name in ("encoder-embedding", "vit-embedding"):
         return {}
     if name == "decoder-embedding":
         return {"x": ROWS}
@@ -120,7 +124,7 @@ def required_layouts(name: str, algo: int) -> Dict[str, Layout]:
         return {"x": ROWS, "bias": VEC, "residual": ROWS}
     if n == "MLP-gelu":
         return {"x": COLS, "bias": VEC_COLS}
-    if name in ("gpt-post-process", "t5-post-process", "bert-post-process"):
+    if name in ("gpt-post-process", "t5-post-process", "bert-post-process", "vit-post-process"):
         return {"x": ROWS}
     raise KeyError(f"no static info for op {name}")
 
@@ -132,7 +136,7 @@ def produced_layouts(name: str, algo: int) -> Dict[str, Layout]:
             return {}
         return {"x": ROWS, "residual": ROWS} if rk == "block-conv1" else {"x": ROWS}
     n = _strip(name)
-    if name == "encoder-embedding":
+    if name in ("encoder-embedding", "vit-embedding"):
         return {"x": ROWS}
     if name == "decoder-embedding":
         return {"x": ROWS, "enc_out": ROWS}
@@ -156,7 +160,7 @@ def produced_layouts(name: str, algo: int) -> Dict[str, Layout]:
         return {"x": ROWS}
     if n == "MLP-gelu":
         return {"x": COLS}
-    if name in ("gpt-post-process", "t5-post-process", "bert-post-process"):
+    if name in ("gpt-post-process", "t5-post-process", "bert-post-process", "vit-post-process"):
         return {}
     raise KeyError(f"no static info for op {name}")
 

@@ -33,7 +33,7 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
     shuffled sample order (a function of the seed and of --train-iters), so a run resumed with the same
     --train-iters continues where the data stopped."""
     import numpy as np
-    if trainer.model_name == "resnet":
+    if trainer.model_name in ("resnet", "vit"):
         return make_image_batch_fn(trainer, prefix, seed)
     if trainer.model_name == "t5":
         return make_t5_batch_fn(trainer, prefix, train_iters, seed, vocab_file)

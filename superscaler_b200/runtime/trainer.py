@@ -46,6 +46,11 @@ def _model_factory(model_name: str):
         from ..models.fused import fuse_ops
         return (m.bert_config_from_plan, lambda c: m.bert_op_names(c.num_layers),
                 lambda i, c: m.bert_layer_of(i, c.num_layers), m.build_bert_op, fuse_ops)
+    if model_name == "vit":
+        from ..models import vit as m
+        from ..models.fused import fuse_ops
+        return (m.vit_config_from_plan, lambda c: m.vit_op_names(c.num_layers),
+                lambda i, c: m.vit_layer_of(i, c.num_layers), m.build_vit_op, fuse_ops)
     if model_name == "resnet":
         from ..models import resnet as m
         return (m.resnet_config_from_plan, m.resnet_op_names, m.resnet_layer_of, m.build_resnet_op,
@@ -56,7 +61,7 @@ def _model_factory(model_name: str):
 # ops that keep their activations whatever the plan says: the embeddings and the loss ops (the search never marks
 # them either, reference: search/model_ops_info.py:76-90)
 _NEVER_RECOMPUTED = ("encoder-embedding", "decoder-embedding", "gpt-post-process", "t5-post-process",
-                     "bert-post-process", "fc")
+                     "bert-post-process", "vit-embedding", "vit-post-process", "fc")
 
 
 def _validate_plan(plan: dict) -> None:

@@ -87,3 +87,10 @@ def tiny_bert_plan(**kw):
     plan = tiny_gpt_plan(**kw)
     plan["model_name"] = "bert"
     return plan
+
+
+def tiny_vit_plan(image_size=32, patch=8, num_classes=10, **kw):
+    """The GPT helper's plan with the ViT op list (same op count); seq / vocab arguments of the helper are unused."""
+    plan = tiny_gpt_plan(**kw)
+    plan.update(model_name="vit", image_size=image_size, patch_dim=patch, num_classes=num_classes)
+    return plan
