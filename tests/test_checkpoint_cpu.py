@@ -153,7 +153,13 @@ def test_checkpoints_of_parallel_plans_reload_on_one_rank(tmp_path, name, kw, wo
 
 def _model_bits(model):
     from superscaler_b200.data import synthetic as syn
-    from helpers import tiny_resnet_plan, tiny_t5_plan
+    from helpers import tiny_bert_plan, tiny_resnet_plan, tiny_t5_plan, tiny_vit_plan
+    if model == "bert":
+        return (lambda **kw: tiny_bert_plan(seq=32, vocab=256, **kw)), \
+            dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2), (lambda seed: syn.bert_batch(4, 32, 256, seed=seed))
+    if model == "vit":
+        return tiny_vit_plan, dict(hidden_dropout=0.0, attention_dropout=0.0), \
+            (lambda seed: syn.resnet_batch(4, 32, 10, seed=seed))
     if model == "gpt":
         return tiny_gpt_plan, dict(hidden_dropout=0.0, attention_dropout=0.0, max_tp=2), \
             (lambda seed: syn.gpt_batch(4, 128, 512, seed=seed))
@@ -176,10 +182,12 @@ def _load_worker(rank, world, model, kw, root, want):
 @pytest.mark.parametrize("model,kw,world", [("gpt", dict(num_gpus=(2,), tp=[2]), 2), ("gpt", dict(num_gpus=(1, 1)), 2),
                                             ("t5", dict(num_gpus=(2,), tp=[2]), 2), ("t5", dict(num_gpus=(1, 1)), 2),
                                             ("resnet", dict(num_gpus=(2,), tp=[2]), 2),
-                                            ("resnet", dict(num_gpus=(1, 1)), 2)])
+                                            ("resnet", dict(num_gpus=(1, 1)), 2),
+                                            ("bert", dict(num_gpus=(2,), tp=[2]), 2), ("bert", dict(num_gpus=(1, 1)), 2),
+                                            ("vit", dict(num_gpus=(2,), tp=[2]), 2), ("vit", dict(num_gpus=(1, 1)), 2)])
 def test_one_rank_checkpoint_loads_under_parallel_plans(tmp_path, model, kw, world):
     """The other direction: a checkpoint written by one rank is re-sliced for tensor / pipeline parallel plans of
-    all three models; the next step's loss equals the single-process continuation."""
+    every model family; the next step's loss equals the single-process continuation."""
     from dist_utils import run_ranks
     plan_fn, ov, batch_fn = _model_bits(model)
     root = str(tmp_path / "ckpt")
