@@ -23,7 +23,8 @@ import torch.distributed as dist
 from ..parallel.state import init_distributed
 
 PRIMS = {"gpt": ["all_gather", "all_reduce", "reduce_scatter", "all_to_all"], "resnet": ["all_gather", "all_to_all"],
-         "t5": []}
+         "bert": ["all_gather", "all_reduce", "reduce_scatter", "all_to_all"],
+         "vit": ["all_gather", "all_reduce", "reduce_scatter", "all_to_all"], "t5": []}
 
 
 def sizes_from_db(path: str, model: str, size: str, max_mb: float):

@@ -216,6 +216,20 @@ def model_table(model: str, size: str):
             shape.update(activation="relu", relative_position_bias=True, relative_attention_num_buckets=32)
         return (shape, {}, t5_op_names(1), opinfo.T5_TUNABLE,
                 lambda plan: syn.t5_batch(plan["global_batch_size"], es, ds, vocab, seed=1))
+    if model == "bert":
+        from ..models.bert import bert_op_names
+        L, seq, hidden, ffn, heads, kv, vocab, _ = sc.BERT_SIZES[size]
+        shape = dict(model_size=size, num_layers=1, seq_length=seq, max_position_embeddings=seq,
+                     num_attention_heads=heads, hidden_size=hidden, kv_channels=kv, ffn_hidden_size=ffn, vocab_size=vocab)
+        return (shape, {}, bert_op_names(1), opinfo.GPT_TUNABLE,
+                lambda plan: syn.bert_batch(plan["global_batch_size"], seq, vocab, seed=1))
+    if model == "vit":
+        from ..models.vit import vit_op_names
+        L, image, patch, hidden, ffn, heads, kv, classes, _ = sc.VIT_SIZES[size]
+        shape = dict(model_size=size, num_layers=1, image_size=image, patch_dim=patch, num_classes=classes,
+                     num_attention_heads=heads, hidden_size=hidden, kv_channels=kv, ffn_hidden_size=ffn)
+        return (shape, {}, vit_op_names(1), [op for op in opinfo.GPT_TUNABLE if op != "encoder-embedding"],
+                lambda plan: syn.resnet_batch(plan["global_batch_size"], image, classes, seed=1))
     if model == "resnet":
         from ..models.resnet import ResNetConfig, resnet_op_names
         blocks, cin, wf, _ = sc.RESNET_SIZES[size]

@@ -55,8 +55,21 @@ B200_GPT_SIZES: Dict[str, tuple] = {
 B200_T5_SIZES: Dict[str, tuple] = {
     "770M": (24, 512, 128, 1024, 4096, 16, 64, 32128, "bf16"),
 }
+# Encoder-only families that exist only in this framework (the reference has no op-list BERT / ViT):
+# model_size -> (layers, seq, hidden, ffn, heads, kv_channels, vocab, dtype)
+BERT_SIZES: Dict[str, tuple] = {
+    "110M": (12, 512, 768, 3072, 12, 64, 30592, "bf16"),
+    "340M": (24, 512, 1024, 4096, 16, 64, 30592, "bf16"),
+    "1_3B": (24, 512, 2048, 8192, 16, 128, 30592, "bf16"),
+}
+# model_size -> (layers, image size, patch, hidden, ffn, heads, kv_channels, classes, dtype)
+VIT_SIZES: Dict[str, tuple] = {
+    "base": (12, 224, 16, 768, 3072, 12, 64, 1000, "bf16"),
+    "large": (24, 224, 16, 1024, 4096, 16, 64, 1000, "bf16"),
+    "huge": (32, 224, 16, 1280, 5120, 20, 64, 1000, "bf16"),    # 16 x 16 patches (the published huge model uses 14 x 14)
+}
 # multiples of the weight bytes held besides weights and gradients: (fp32 main params, optimizer state)
-STATE_MULTIPLIERS = {"resnet": (0, 2), "gpt": (2, 4), "t5": (2, 4)}
+STATE_MULTIPLIERS = {"resnet": (0, 2), "gpt": (2, 4), "t5": (2, 4), "bert": (2, 4), "vit": (2, 4)}
 
 
 @dataclass
@@ -164,6 +177,15 @@ def plan_to_dict(plan: Plan, model_name: str, model_size: str, num_layers: int, 
             d["activation"] = "relu"
             d["relative_position_bias"] = True
             d["relative_attention_num_buckets"] = 32
+    elif model_name == "bert":
+        _, seq, hidden, ffn, heads, kv, vocab, _ = BERT_SIZES[model_size]
+        d.update(num_layers=num_layers, seq_length=seq, max_position_embeddings=seq, num_attention_heads=heads,
+                 hidden_size=hidden, kv_channels=kv, ffn_hidden_size=ffn, vocab_size=vocab)
+    elif model_name == "vit":
+        _, image, patch, hidden, ffn, heads, kv, classes, _ = VIT_SIZES[model_size]
+        d.update(num_layers=num_layers, image_size=image, patch_dim=patch, num_classes=classes,
+                 seq_length=(image // patch) ** 2 + 1, max_position_embeddings=(image // patch) ** 2 + 1,
+                 num_attention_heads=heads, hidden_size=hidden, kv_channels=kv, ffn_hidden_size=ffn)
     else:
         raise ValueError(f"unsupported model {model_name}")
     d["global_batch_size"] = plan.global_bs

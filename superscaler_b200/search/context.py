@@ -15,7 +15,7 @@ import time
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
-from .config import GPT_SIZES, RESNET_SIZES, STATE_MULTIPLIERS, T5_SIZES
+from .config import BERT_SIZES, GPT_SIZES, RESNET_SIZES, STATE_MULTIPLIERS, T5_SIZES, VIT_SIZES
 from .cost_model import CostModel, CostOptions
 from .database import ProfileDB
 from .opinfo import expand_op_list, never_recompute_ops, read_unique_ops, tunable_ops
@@ -84,7 +84,7 @@ class SearchArgs:
             with open(self.initial_point) as f:
                 d = json.load(f)
             self.model_name, self.model_size = d["model_name"], d["model_size"]
-        if self.model_name not in ("resnet", "gpt", "t5", "scale-layer"):
+        if self.model_name not in ("resnet", "gpt", "t5", "scale-layer", "bert", "vit"):
             raise RuntimeError(f"model {self.model_name} is not supported yet.")
         if self.num_layers is None:
             if self.model_name == "resnet":
@@ -93,6 +93,10 @@ class SearchArgs:
                 self.num_layers = GPT_SIZES[self.model_size][0]
             elif self.model_name == "t5":
                 self.num_layers = T5_SIZES[self.model_size][0]
+            elif self.model_name == "bert":
+                self.num_layers = BERT_SIZES[self.model_size][0]
+            elif self.model_name == "vit":
+                self.num_layers = VIT_SIZES[self.model_size][0]
             else:
                 raise RuntimeError("should provide --num-layers for scale-layer exp")
         if self.micro_batch_size is None:

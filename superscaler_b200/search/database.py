@@ -69,6 +69,8 @@ class ProfileDB:
         # collectives
         prims = {"gpt": ["all_gather", "all_reduce", "reduce_scatter", "all_to_all"],
                  "scale-layer": ["all_gather", "all_reduce", "reduce_scatter", "all_to_all"],
+                 "bert": ["all_gather", "all_reduce", "reduce_scatter", "all_to_all"],
+                 "vit": ["all_gather", "all_reduce", "reduce_scatter", "all_to_all"],
                  "t5": [], "resnet": ["all_gather", "all_to_all"]}[model_name]
         self.collective: Dict[str, Dict[int, Dict[str, float]]] = {}
         for prim in prims:

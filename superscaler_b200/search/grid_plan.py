@@ -21,12 +21,12 @@ def uniform_plans(ctx: SearchContext, pp: int, tp: int, dp: int, micro_bs: int, 
     ops = ctx.full_op_list
     n = len(ops)
     rc = [1 if recompute else 0] * n
-    if a.model_name in ("gpt", "t5", "scale-layer"):
+    if a.model_name in ("gpt", "t5", "scale-layer", "bert", "vit"):
         rc[0] = rc[-1] = 0
     flat_tp, flat_dp, algo = [tp] * n, [dp] * n, [0] * n
     mk = lambda counts: build_plan(counts, flat_tp, flat_dp, rc, micro_bs, a.global_batch_size, ops, algo)  # noqa: E731
     L = a.num_layers
-    if a.model_name in ("gpt", "scale-layer"):
+    if a.model_name in ("gpt", "scale-layer", "bert", "vit"):
         if L % pp:
             return []
         counts = [(L // pp) * 13] * pp

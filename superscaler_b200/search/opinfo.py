@@ -18,7 +18,11 @@ NEVER_RECOMPUTE = {
     "scale-layer": ["encoder-embedding", "gpt-post-process"],
     "t5": ["encoder-embedding", "decoder-embedding", "t5-post-process"],
     "resnet": ["conv1"],
+    "bert": ["encoder-embedding", "bert-post-process"],
+    "vit": ["vit-embedding", "vit-post-process"],
 }
+# families laid out like GPT: one head op, 13 ops per layer, final LayerNorm + post-process
+GPT_LIKE = ("gpt", "scale-layer", "bert", "vit")
 
 
 def read_unique_ops(profile_dir: str, model_name: str, model_size: str, first_mbs: int) -> List[str]:
@@ -36,7 +40,7 @@ def read_unique_ops(profile_dir: str, model_name: str, model_size: str, first_mb
 def expand_op_list(unique_ops: Sequence[str], model_name: str, num_layers: int) -> List[str]:
     """Full op list: head + layer ops x layers + tail (GPT), encoder / decoder blocks (T5), as-is (ResNet)."""
     u = list(unique_ops)
-    if model_name in ("gpt", "scale-layer"):
+    if model_name in GPT_LIKE:
         return u[:1] + u[1:14] * num_layers + u[14:]
     if model_name == "t5":
         return u[:1] + u[1:14] * num_layers + u[14:15] + u[15:16] + u[16:37] * num_layers + u[37:]
@@ -46,8 +50,10 @@ def expand_op_list(unique_ops: Sequence[str], model_name: str, num_layers: int) 
 
 
 def tunable_ops(model_name: str, unique_ops: Sequence[str]) -> List[str]:
-    if model_name in ("gpt", "scale-layer"):
+    if model_name in ("gpt", "scale-layer", "bert"):
         return list(GPT_TUNABLE)
+    if model_name == "vit":
+        return [op for op in GPT_TUNABLE if op != "encoder-embedding"]     # the patch projection is never sharded
     if model_name == "t5":
         return list(T5_TUNABLE)
     if model_name == "resnet":
@@ -68,7 +74,7 @@ def op_spec(op: str, tp: int, dp: int, algo: int, as_input: bool) -> Optional[di
     replicated_b = _spec(tp, 1, [1, dp, 1])       # replicated over tp, batch split over dp
     split_h = _spec(1, 1, [1, dp, tp])            # hidden dim split over tp
     heads = _spec(1, 1, [dp, tp, 1])              # [b, np, ...] attention layout
-    if op == "encoder-embedding":
+    if op in ("encoder-embedding", "vit-embedding"):
         return None if as_input else replicated_b
     if op in ("enc-1st-layernorm", "enc-2nd-layernorm", "enc-post-attention-dropout", "enc-post-MLP-dropout"):
         return replicated_b
@@ -92,7 +98,7 @@ def op_spec(op: str, tp: int, dp: int, algo: int, as_input: bool) -> Optional[di
         return replicated_b if as_input else split_h
     if op == "enc-MLP-gelu":
         return split_h
-    if op == "gpt-post-process":
+    if op in ("gpt-post-process", "bert-post-process", "vit-post-process"):
         return _spec(tp, 1, [dp, 1, 1]) if as_input else None
     if any(k in op for k in ("conv", "downsample", "bn", "relu", "pool", "fc")):
         return _spec(tp, 1, [dp, 1, 1])

@@ -193,3 +193,58 @@ def test_every_golden_plan_passes_the_trainers_shape_checks():
             plan = json.load(fh)
         _validate_plan(plan)
         assert plan["global_batch_size"] % plan["micro_batch_size"] == 0, f
+
+
+@pytest.mark.parametrize("model,size,post", [("bert", "340M", "bert-post-process"), ("vit", "large", "vit-post-process")])
+def test_encoder_only_families_go_through_search_and_into_the_trainer(tmp_path, model, size, post):
+    """BERT and ViT share the 13 layer ops of GPT.  With a database in their name (here: the committed GPT tables with
+    the head / tail rows renamed; a real one comes from `profiler.op_profiler --model-name bert|vit`) the search and
+    the grid planner write plans whose op counts, never-recomputed ops and shape keys the trainer accepts."""
+    import csv as _csv
+    import glob
+    import shutil
+    from superscaler_b200.runtime.trainer import Trainer
+    from superscaler_b200.search.grid_plan import grid_search
+    src = os.path.join(os.path.dirname(os.path.dirname(__file__)), "profiled-time-b200") + os.sep
+    db = str(tmp_path / "db") + os.sep
+    os.makedirs(db)
+    first = "vit-embedding" if model == "vit" else "encoder-embedding"
+    for f in glob.glob(src + "gpt_1_3B_mbs*_tp[12]_algo*.csv"):
+        rows = list(_csv.reader(open(f)))
+        for r in rows[1:]:
+            r[0] = {"encoder-embedding": first, "gpt-post-process": post}.get(r[0], r[0])
+        with open(db + os.path.basename(f).replace("gpt_1_3B", f"{model}_{size}"), "w", newline="") as out:
+            _csv.writer(out).writerows(rows)
+    for f in glob.glob(src + "prim_gpt_1_3B_*_2gpus.csv"):
+        shutil.copy(f, db + os.path.basename(f).replace("gpt_1_3B", f"{model}_{size}"))
+    shutil.copy(src + "p2p_intra_node.csv", db)
+    out = str(tmp_path / "out") + os.sep
+    for sub in ("csv", "top_configs", "trends"):
+        os.makedirs(out + sub, exist_ok=True)
+    args = SearchArgs(model_name=model, model_size=size, global_batch_size=64, micro_batch_size=[1, 2, 4, 8, 16],
+                      num_nodes=1, num_gpus_per_node=2, max_tp=2, memory_limit=170000, profiled_time_path=db,
+                      config_save_path=out, log_path=out, config_suffix="t", max_num_hops=3, time_budget_total=20,
+                      multi_process=False, shapes="b200").finalize()
+    ctx = SearchContext(args, verbose=False)
+    assert ctx.full_op_list[0] == first and ctx.full_op_list[-1] == post and len(ctx.full_op_list) == 13 * 24 + 3
+    assert grid_search(ctx), "the uniform grid found no feasible plan"
+    Searcher(ctx).run(2)
+    with open(f"{out}{model}_{size}_2stages_t.json") as f:
+        plan = json.load(f)
+    assert plan["model_name"] == model and sum(plan["num_ops_in_each_stage"]) == 315
+    if model == "vit":
+        assert plan["image_size"] == 224 and plan["patch_dim"] == 16 and plan["seq_length"] == 197
+    # the trainer builds the plan's model (narrow layers) on one CPU rank of the two: its checks accept the plan
+    from superscaler_b200.runtime.trainer import _validate_plan
+    _validate_plan(plan)
+    one = dict(plan, num_stages=1, num_gpus=[1], num_ops_in_each_stage=[315], checkpoint_activations=[False],
+               resharding_stages=[False], model_parallel_size_of_each_op=[[1] * 315],
+               data_parallel_size_of_each_op=[[1] * 315], recompute_ops=[[0] * 315], algo_of_each_op=[[0] * 315],
+               global_batch_size=2, micro_batch_size=2, hidden_size=32, num_attention_heads=2, kv_channels=16,
+               ffn_hidden_size=64, num_layers=24)
+    if model == "bert":
+        one.update(seq_length=16, max_position_embeddings=16, vocab_size=128)
+    else:
+        one.update(image_size=16, patch_dim=8, num_classes=4)
+    t = Trainer(one, device="cpu", model_overrides=dict(hidden_dropout=0.0, attention_dropout=0.0))
+    assert len(t.op_names) == 315
