@@ -83,6 +83,8 @@ def op_io(name: str) -> Tuple[Tuple[str, ...], Tuple[str, ...]]:
         return ("x", "labels", "loss_mask"), ("loss",)
     if name == "bert-post-process":
         return ("x", "labels", "loss_mask", "nsp"), ("loss",)
+    if name == "ict-post-process":
+        return ("x", "labels"), ("loss",)
     if name == "vit-embedding":
         return ("images",), ("x",)
     if name == "vit-post-process":
@@ -124,7 +126,7 @@ def required_layouts(name: str, algo: int) -> Dict[str, Layout]:
         return {"x": ROWS, "bias": VEC, "residual": ROWS}
     if n == "MLP-gelu":
         return {"x": COLS, "bias": VEC_COLS}
-    if name in ("gpt-post-process", "t5-post-process", "bert-post-process", "vit-post-process"):
+    if name in ("gpt-post-process", "t5-post-process", "bert-post-process", "vit-post-process", "ict-post-process"):
         return {"x": ROWS}
     raise KeyError(f"no static info for op {name}")
 
@@ -160,7 +162,7 @@ def produced_layouts(name: str, algo: int) -> Dict[str, Layout]:
         return {"x": ROWS}
     if n == "MLP-gelu":
         return {"x": COLS}
-    if name in ("gpt-post-process", "t5-post-process", "bert-post-process", "vit-post-process"):
+    if name in ("gpt-post-process", "t5-post-process", "bert-post-process", "vit-post-process", "ict-post-process"):
         return {}
     raise KeyError(f"no static info for op {name}")
 

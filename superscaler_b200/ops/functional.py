@@ -698,7 +698,7 @@ class EmbeddingFn(torch.autograd.Function):
             return native.ext().embedding_fwd(ids.contiguous().view(-1), pos.contiguous().view(-1) if pos is not None
                                               else None, W, P, v0, dropout_p, seed)
         assert dropout_p == 0.0, "dropout > 0 needs the GPU path"
-        flat = ids.view(-1)
+        flat = ids.reshape(-1)
         local = (flat >= v0) & (flat < v0 + W.shape[0])
         out = torch.where(local[:, None], W.float()[(flat - v0).clamp(0, W.shape[0] - 1)], torch.zeros(1))
         if P is not None:

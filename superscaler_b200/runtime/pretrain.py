@@ -130,6 +130,14 @@ def make_batch_fn(trainer: Trainer):
         return lambda i: synthetic.t5_batch(gbs, cfg.seq_length, cfg.dec_seq_length, cfg.vocab, seed=1234 + i)
     if trainer.model_name == "bert":
         return lambda i: synthetic.bert_batch(gbs, cfg.seq_length, cfg.vocab, seed=1234 + i)
+    if trainer.model_name == "ict":
+        def pairs(i):       # synthetic (query, block) pairs: rows 2 k and 2 k + 1 are two views of one token pattern
+            b = synthetic.bert_batch(gbs, cfg.seq_length, cfg.vocab, seed=1234 + i)
+            ids = b["ids"]
+            ids[1::2] = ids[0::2]
+            return {"ids": ids, "types": torch.zeros_like(ids), "enc_lens": b["enc_lens"],
+                    "labels": torch.arange(gbs // 2).repeat_interleave(2)}
+        return pairs
     return lambda i: synthetic.resnet_batch(gbs, cfg.image_size, cfg.num_classes, seed=1234 + i)
 
 

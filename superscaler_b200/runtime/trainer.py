@@ -46,6 +46,11 @@ def _model_factory(model_name: str):
         from ..models.fused import fuse_ops
         return (m.bert_config_from_plan, lambda c: m.bert_op_names(c.num_layers),
                 lambda i, c: m.bert_layer_of(i, c.num_layers), m.build_bert_op, fuse_ops)
+    if model_name == "ict":
+        from ..models import ict as m
+        from ..models.fused import fuse_ops
+        return (m.ict_config_from_plan, lambda c: m.ict_op_names(c.num_layers),
+                lambda i, c: m.ict_layer_of(i, c.num_layers), m.build_ict_op, fuse_ops)
     if model_name == "vit":
         from ..models import vit as m
         from ..models.fused import fuse_ops
@@ -61,7 +66,7 @@ def _model_factory(model_name: str):
 # ops that keep their activations whatever the plan says: the embeddings and the loss ops (the search never marks
 # them either, reference: search/model_ops_info.py:76-90)
 _NEVER_RECOMPUTED = ("encoder-embedding", "decoder-embedding", "gpt-post-process", "t5-post-process",
-                     "bert-post-process", "vit-embedding", "vit-post-process", "fc")
+                     "bert-post-process", "ict-post-process", "vit-embedding", "vit-post-process", "fc")
 
 
 def _validate_plan(plan: dict) -> None:
@@ -292,6 +297,22 @@ class Trainer:
         return float(t.item())
 
     @torch.no_grad()
+    @torch.no_grad()
+    def embed(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
+        """Inference forward of a ONE-stage plan on one rank's rows: the last op's `logits` entry for the given inputs
+        (an inverse-cloze plan: one embedding per sequence; BERT / ViT: their logits).  `batch` holds the model's input
+        keys (ids, types, enc_lens, images ...) and no labels.  Dropout is off."""
+        assert len(self.stage_bounds) == 1 and self.world_size == 1, "embed() runs one-stage plans on one rank"
+        was = self.env.training
+        self.env.training = False
+        try:
+            st: Dict[str, Any] = {k: (v.to(self.device) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()
+                                  if k not in ("labels", "loss_mask", "nsp")}
+            self.stage.forward(st)
+            return st["logits"]
+        finally:
+            self.env.training = was
+
     def logits(self, ids: torch.Tensor) -> torch.Tensor:
         """Inference forward of a GPT plan (one stage or a pipeline, any per-op tensor / data parallel layout; not
         interleaved): token ids [b, seq_length] -> logits [b, seq_length, padded vocabulary] on every rank.  Every

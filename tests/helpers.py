@@ -94,3 +94,9 @@ def tiny_vit_plan(image_size=32, patch=8, num_classes=10, **kw):
     plan = tiny_gpt_plan(**kw)
     plan.update(model_name="vit", image_size=image_size, patch_dim=patch, num_classes=num_classes)
     return plan
+
+
+def tiny_ict_plan(projection=16, **kw):
+    plan = tiny_gpt_plan(**kw)
+    plan.update(model_name="ict", biencoder_projection_dim=projection)
+    return plan

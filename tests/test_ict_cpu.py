@@ -1,0 +1,81 @@
+"""Inverse-cloze biencoder: the in-batch retrieval loss, learning to match queries with their blocks, data-parallel
+pairs staying together, and the trained encoder as the embedder of the evidence index."""
+import math
+
+import numpy as np
+import torch
+
+from dist_utils import run_ranks
+from helpers import tiny_ict_plan
+
+KW = dict(layers=2, seq=16, hidden=64, heads=2, head_dim=32, vocab=128, global_bs=16, micro_bs=16)
+OV = dict(hidden_dropout=0.0, attention_dropout=0.0)
+
+
+def _pairs(n, seed):
+    """Query i and block i share a random 'topic' token pattern; everything else is noise."""
+    g = torch.Generator().manual_seed(seed)
+    topic = torch.randint(10, 128, (n, 6), generator=g)
+    ids = torch.zeros(2 * n, 16, dtype=torch.int64)
+    for i in range(n):
+        for row in (2 * i, 2 * i + 1):
+            noise = torch.randint(10, 128, (9,), generator=g)
+            ids[row] = torch.cat([torch.tensor([2]), topic[i], noise])[:16]
+    return {"ids": ids, "types": torch.zeros_like(ids), "enc_lens": torch.full((2 * n,), 16, dtype=torch.int32),
+            "labels": torch.arange(n).repeat_interleave(2)}
+
+
+def _trainer(plan, rank=0, world=1, lr=3e-3):
+    from superscaler_b200.runtime.trainer import Trainer
+    return Trainer(plan, rank=rank, world_size=world, device="cpu", model_overrides=OV, lr_warmup_steps=0, lr=lr)
+
+
+def test_loss_is_the_in_batch_softmax_and_training_learns_the_pairs():
+    t = _trainer(tiny_ict_plan(**KW))
+    b = _pairs(8, seed=1)
+    first = t.loss_value(t.train_step(b))
+    assert abs(first - math.log(8)) < 0.5                     # untrained: near-uniform over the 8 blocks of the batch
+    emb = t.embed(b)
+    assert emb.shape == (16, 16)
+    q, c = emb[0::2].float(), emb[1::2].float()
+    want = float(torch.nn.functional.cross_entropy(q @ c.t(), torch.arange(8)))
+    again = t.loss_value(t.train_step(b))                      # the loss of the weights embed() just saw
+    assert abs(again - want) < 2e-2, (again, want)
+    for _ in range(40):
+        last = t.loss_value(t.train_step(b))
+    assert last < 0.5 * first, (first, last)
+    emb = t.embed(b).float()
+    assert ((emb[0::2] @ emb[1::2].t()).argmax(1) == torch.arange(8)).float().mean() >= 0.75
+
+
+def _dp_worker(rank, world, plan, want):
+    t = _trainer(plan, rank, world)
+    got = [t.loss_value(t.train_step(_pairs(8, seed=1))) for _ in range(2)]
+    # each rank scores its 4 queries against its own 4 blocks: ln 4 at the start instead of ln 8
+    assert abs(got[0] - math.log(4)) < 0.5 and all(math.isfinite(v) for v in got), (rank, got, want)
+
+
+def test_data_parallel_ranks_keep_query_and_block_together():
+    run_ranks(_dp_worker, 2, tiny_ict_plan(**KW, num_gpus=(2,), tp=[1]), None)
+
+
+def test_trained_encoder_is_the_embedder_of_the_evidence_index(tmp_path):
+    from superscaler_b200.data import retrieval as R
+    t = _trainer(tiny_ict_plan(**KW))
+    b = _pairs(8, seed=3)
+    for _ in range(30):
+        t.train_step(b)
+    blocks_ids = b["ids"][1::2]
+
+    def embed(ids, mask):
+        return t.embed({"ids": ids, "types": torch.zeros_like(ids), "enc_lens": mask.sum(1).to(torch.int32)})
+
+    store = R.EmbeddingStore(str(tmp_path), 0)
+    store.add(torch.arange(100, 108), embed(blocks_ids, torch.ones_like(blocks_ids, dtype=torch.bool)))
+    store.save_shard()
+    store.merge_shards_and_save(1)
+    ids, emb = R.EmbeddingStore.load(str(tmp_path))
+    index = R.MIPSIndex(ids, emb)
+    q = embed(b["ids"][0::2], torch.ones(8, 16, dtype=torch.bool))
+    _, found = index.search(q, 1)
+    assert (found[:, 0] == torch.arange(100, 108)).float().mean() >= 0.75
