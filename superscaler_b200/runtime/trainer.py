@@ -297,7 +297,6 @@ class Trainer:
         return float(t.item())
 
     @torch.no_grad()
-    @torch.no_grad()
     def embed(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
         """Inference forward of a ONE-stage plan on one rank's rows: the last op's `logits` entry for the given inputs
         (an inverse-cloze plan: one embedding per sequence; BERT / ViT: their logits).  `batch` holds the model's input
@@ -313,6 +312,7 @@ class Trainer:
         finally:
             self.env.training = was
 
+    @torch.no_grad()
     def logits(self, ids: torch.Tensor) -> torch.Tensor:
         """Inference forward of a GPT plan (one stage or a pipeline, any per-op tensor / data parallel layout; not
         interleaved): token ids [b, seq_length] -> logits [b, seq_length, padded vocabulary] on every rank.  Every
