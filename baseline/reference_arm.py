@@ -153,6 +153,9 @@ def parse_iteration_times(text: str) -> list:
 
 def run(args) -> dict:
     import torch
+    if getattr(args, "model", "gpt") != "gpt":
+        return {"impl": "reference", "unavailable": f"the reference arm runs the headline model (GPT-3 1.3B) only, not "
+                                                    f"--model {args.model}"}
     if not os.path.isfile(os.path.join(RUNTIME, "pretrain_gpt.py")):
         return {"impl": "reference", "unavailable": "no reference tree under baseline/_ref (run __graft_entry__.build())"}
     if not torch.cuda.is_available():
