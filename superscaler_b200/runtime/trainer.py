@@ -147,9 +147,12 @@ class Trainer:
         self.infos = [i for c in chunks for i in c]
         F.manual_seed(seed + 100 * self.pstate.stage)
         self.store = ParamStore(self.device, base_seed=seed)
+        # peer-mapped gradient / weight buffers need every rank of the data-parallel group on ONE node (NVLink);
+        # a job that spans nodes reduces its gradients with NCCL
         pure_dp = (len(counts) == 1 and world_size > 1 and self.device.type == "cuda" and
                    all(t == 1 for t in plan["model_parallel_size_of_each_op"][0]) and
-                   all(d == world_size for d in plan["data_parallel_size_of_each_op"][0]))
+                   all(d == world_size for d in plan["data_parallel_size_of_each_op"][0]) and
+                   self.pstate.same_node(range(world_size)))
         if fused_comm and pure_dp:
             from ..parallel.symm import SymmetricBuffer
             self.store.grad_allocator = lambda n: SymmetricBuffer(n, torch.float32, None, self.device)

@@ -383,3 +383,16 @@ def test_random_stage_cuts_of_wide_resnet_match_single_process():
         plans.append(plan)
     base = _other_model_losses("resnet", plan_fn(), steps=2)
     run_ranks(_resnet_fuzz_worker, 4, plans, base, timeout=600)
+
+
+def test_ranks_on_different_nodes_are_told_apart(monkeypatch):
+    """Peer-mapped buffers are only used inside a node: with LOCAL_WORLD_SIZE ranks per node, rank sets that cross a
+    node boundary are reported as such (tensor-parallel groups and the data-parallel gradient buffer then use NCCL)."""
+    from superscaler_b200.parallel.state import ParallelState
+    ps = ParallelState([4], rank=0, world_size=4)
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "2")
+    assert ps.same_node([0, 1]) and ps.same_node([2, 3]) and not ps.same_node([1, 2]) and not ps.same_node(range(4))
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "4")
+    assert ps.same_node(range(4))
+    monkeypatch.delenv("LOCAL_WORLD_SIZE")
+    assert ps.same_node(range(4))
