@@ -563,8 +563,10 @@ int attn_bwd_fused_launch(const void* q, int ldq, const void* k, int ldk, const 
                           int lddo, const AttnParams& p, float* scratch, cudaStream_t stream) {
   if (p.HD != 64 && p.HD != 128) return -2;
   if (p.causal && p.SQ != p.SK) return -2;
+  // 16-byte granularity everywhere: TMA x coordinates (column offsets of Q / K / V / dO), the 16-byte stores of dK /
+  // dV and the bulk reductions of dQ; a misaligned offset would fault on the device instead of failing here
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (lddo % 8) || (p.lddq % 8) || (p.lddk % 8) || (p.lddv % 8) ||
-      (p.dq_col0 % 8))
+      (p.dq_col0 % 8) || (p.dk_col0 % 8) || (p.dv_col0 % 8) || (p.q_col0 % 8) || (p.k_col0 % 8) || (p.v_col0 % 8))
     return -3;
   int rc;
   const int n_tiles = (p.SQ + 127) / 128;

@@ -992,7 +992,10 @@ int attn_bwd_launch(const void* q, int ldq, const void* k, int ldk, const void* 
   if (p.HD != 64 && p.HD != 128) return -2;
   if (p.causal && p.SQ != p.SK) return -2;
   if (p.bias_table != nullptr) return -2;  // the score bias exists in the forward and the fused backward kernel only
-  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (lddo % 8) || (p.lddq % 8) || (p.lddk % 8) || (p.lddv % 8)) return -3;
+  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (lddo % 8) || (p.lddq % 8) || (p.lddk % 8) || (p.lddv % 8) ||
+      (p.dq_col0 % 8) || (p.dk_col0 % 8) || (p.dv_col0 % 8) || (p.q_col0 % 8) || (p.k_col0 % 8) || (p.v_col0 % 8) ||
+      (p.ldo % 8) || (p.o_col0 % 8))
+    return -3;   // TMA x coordinates and 16-byte stores: every column offset and row pitch in units of 8 elements
   int rc;
   if ((rc = attn_delta_launch(p, dout, lddo, delta_scratch, stream))) return rc;
   AttnParams pp = p;
