@@ -87,13 +87,40 @@ def write_sentence_corpus(docs: Iterable[List[List[int]]], prefix: str, vocab_si
 
 
 def load_sentence_corpus(prefix: str):
-    """The SentenceCorpus written by --split-sentences (tokens memory-mapped)."""
+    """The SentenceCorpus written by --split-sentences (tokens memory-mapped), or a sentence-split corpus in
+    Megatron-LM's format (`<prefix>.idx`)."""
     import os
 
+    from . import mmap_format
     from .sentences import SentenceCorpus
+    if mmap_format.exists(prefix) and not os.path.exists(prefix + ".sent.npy"):
+        return mmap_format.sentence_corpus(prefix)
     wide = os.path.exists(prefix + ".u32")
     tokens = np.memmap(prefix + (".u32" if wide else ".bin"), dtype=np.uint32 if wide else np.uint16, mode="r")
     return SentenceCorpus(tokens, np.load(prefix + ".sent.npy"), np.load(prefix + ".docs.npy"))
+
+
+def write_megatron(a, tok) -> int:
+    """The same corpus in Megatron-LM's format: items are sentences with --split-sentences, else documents (closed
+    by the end-of-document id unless --no-append-eod)."""
+    from . import mmap_format
+    eod = None if a.no_append_eod else getattr(tok, "eod", getattr(tok, "sep", None))
+    doc_idx = [0]
+
+    def items():
+        for text in documents(a.input, a.json_key):
+            if a.split_sentences:
+                sents = [s for s in (tok.tokenize(t) for t in split_sentences(text)) if s]
+            else:
+                ids = tok.tokenize(text)
+                sents = [ids + [eod] if eod is not None else ids] if ids else []
+            if not sents:
+                continue
+            yield from sents
+            doc_idx.append(doc_idx[-1] + len(sents))
+
+    dtype = np.uint16 if tok.vocab_size < 65500 else np.int32      # the reference's choice of element type
+    return mmap_format.write(a.output, items(), doc_idx, dtype=dtype)     # doc_idx fills while the items are read
 
 
 def main(argv=None) -> None:
@@ -106,8 +133,14 @@ def main(argv=None) -> None:
     ap.add_argument("--merge-file", default=None)
     ap.add_argument("--no-append-eod", action="store_true")
     ap.add_argument("--split-sentences", action="store_true")
+    ap.add_argument("--output-format", choices=("native", "megatron"), default="native",
+                    help="megatron: <prefix>.bin + <prefix>.idx as Megatron-LM's preprocessing writes them")
     a = ap.parse_args(argv)
     tok = build_tokenizer(a.tokenizer_type, a.vocab_file, a.merge_file)
+    if a.output_format == "megatron":
+        n = write_megatron(a, tok)
+        print(f"wrote {a.output}.bin/.idx: {n} tokens, vocabulary {tok.vocab_size} (padded {tok.padded_vocab_size})")
+        return
     if a.split_sentences:
         n = write_sentence_corpus(([tok.tokenize(s) for s in split_sentences(text)] for text in documents(a.input, a.json_key)),
                                   a.output, tok.vocab_size)

@@ -29,7 +29,8 @@ from .trainer import Trainer
 
 def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, eod_token=None, vocab_file=None):
     """Batches of a GPT token corpus: `prefix`.bin holds the token ids (uint16, or uint32 with `prefix`.u32 present
-    instead), `prefix`.npy the document lengths.  Batch i is global samples [i * gbs, (i + 1) * gbs) of the
+    instead), `prefix`.npy the document lengths; a Megatron-LM corpus (`prefix`.bin + `prefix`.idx) is read as it
+    is.  Batch i is global samples [i * gbs, (i + 1) * gbs) of the
     shuffled sample order (a function of the seed and of --train-iters), so a run resumed with the same
     --train-iters continues where the data stopped."""
     import numpy as np
@@ -47,9 +48,13 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
         return make_bert_batch_fn(trainer, prefix, train_iters, seed, special)
     from ..data.indexed import GPTSampleDataset, TokenCorpus
     assert trainer.model_name == "gpt", "--data-path feeds the GPT, T5, BERT and Wide-ResNet entry points"
-    wide = os.path.exists(prefix + ".u32")
-    corpus = TokenCorpus.from_files(prefix + (".u32" if wide else ".bin"), prefix + ".npy",
-                                    dtype=np.uint32 if wide else np.uint16)
+    from ..data import mmap_format
+    if mmap_format.exists(prefix) and not os.path.exists(prefix + ".npy"):
+        corpus = mmap_format.token_corpus(prefix)       # a corpus preprocessed for Megatron-LM (<prefix>.idx)
+    else:
+        wide = os.path.exists(prefix + ".u32")
+        corpus = TokenCorpus.from_files(prefix + (".u32" if wide else ".bin"), prefix + ".npy",
+                                        dtype=np.uint32 if wide else np.uint16)
     gbs, seq = trainer.plan["global_batch_size"], trainer.cfg.seq_length
     data = GPTSampleDataset(corpus, seq, num_samples=train_iters * gbs, seed=seed)
 
