@@ -35,6 +35,28 @@ class TokenCorpus:
     def from_files(cls, token_file: str, lengths_file: str, dtype=np.uint16) -> "TokenCorpus":
         return cls(np.memmap(token_file, dtype=dtype, mode="r"), np.load(lengths_file))
 
+    def slice_docs(self, first: int, last: int) -> "TokenCorpus":
+        """Documents [first, last) as a corpus of their own (a view of the same tokens)."""
+        return TokenCorpus(self.tokens[self.doc_start[first]:self.doc_start[last]], self.sizes[first:last])
+
+
+def split_bounds(spec: str, n: int) -> List[int]:
+    """Document boundaries [0, a, b, n] of the train / validation / test parts for a weight string such as
+    "949,50,1" (also "98/2", or one number = everything trains).  Each part gets round(weight share x n)
+    documents and the rounding surplus is taken off all three upper boundaries, which is the reference's rule
+    (get_train_valid_test_split_, runtime/megatron/data/dataset_utils.py:606-632)."""
+    weights = [float(x) for x in spec.replace("/", ",").split(",") if x.strip()]
+    weights = (weights + [0.0, 0.0])[:3]
+    total = sum(weights)
+    assert total > 0 and min(weights) >= 0, f"--split {spec!r}: weights must be non-negative, not all zero"
+    bounds = [0]
+    for w in weights:
+        bounds.append(bounds[-1] + int(round(w / total * n)))
+    surplus = bounds[-1] - n
+    bounds = [0] + [b - surplus for b in bounds[1:]]
+    assert bounds == sorted(bounds) and bounds[-1] == n and bounds[1] >= 0, f"--split {spec!r} leaves a part negative"
+    return bounds
+
 
 def build_sample_idx_py(sizes, doc_idx, seq_length: int, num_epochs: int, tokens_per_epoch: int) -> np.ndarray:
     """Reference definition of the sample-start index (see dataset_helpers.cpp)."""

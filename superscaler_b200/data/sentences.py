@@ -60,6 +60,13 @@ class SentenceCorpus:
     def sentences(self, first: int, last: int) -> List[np.ndarray]:
         return [np.asarray(self.tokens[self.sent_start[i]:self.sent_start[i + 1]]) for i in range(first, last)]
 
+    def slice_docs(self, first: int, last: int) -> "SentenceCorpus":
+        """Documents [first, last) as a corpus of their own (a view of the same tokens)."""
+        s0, s1 = int(self.doc_starts[first]), int(self.doc_starts[last])
+        return SentenceCorpus(self.tokens[self.sent_start[s0]:self.sent_start[s1]], self.sizes[s0:s1],
+                              self.doc_starts[first:last + 1] - s0,
+                              None if self.title_sizes is None else self.title_sizes[first:last])
+
 
 def _usable(sizes, first, last, min_sent) -> bool:
     return last - first >= min_sent and not (sizes[first:last] > LONG_SENTENCE).any()

@@ -27,7 +27,28 @@ from .timers import Timers
 from .trainer import Trainer
 
 
-def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, eod_token=None, vocab_file=None):
+def _held_out(batch_of_part, parts, eval_samples: int):
+    """The training batch function of `parts[0]`, with `.valid` / `.test` = batch functions of the held-out parts
+    (None where --split gives that part no documents)."""
+    train = batch_of_part(parts[0], None)
+    train.valid = batch_of_part(parts[1], eval_samples) if parts[1] is not None else None
+    train.test = batch_of_part(parts[2], eval_samples) if parts[2] is not None else None
+    return train
+
+
+def _split_parts(corpus, num_docs: int, split):
+    """[train, validation, test] corpora for --split (documents in file order, contiguous ranges); without --split
+    everything trains."""
+    if not split:
+        return [corpus, None, None]
+    from ..data.indexed import split_bounds
+    b = split_bounds(split, num_docs)
+    assert b[1] > 0, f"--split {split} leaves no training documents out of {num_docs}"
+    return [corpus.slice_docs(b[i], b[i + 1]) if b[i + 1] > b[i] else None for i in range(3)]
+
+
+def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, eod_token=None, vocab_file=None,
+                          split=None, eval_samples: int = 0):
     """Batches of a GPT token corpus: `prefix`.bin holds the token ids (uint16, or uint32 with `prefix`.u32 present
     instead), `prefix`.npy the document lengths; a Megatron-LM corpus (`prefix`.bin + `prefix`.idx) is read as it
     is.  Batch i is global samples [i * gbs, (i + 1) * gbs) of the
@@ -37,7 +58,7 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
     if trainer.model_name in ("resnet", "vit"):
         return make_image_batch_fn(trainer, prefix, seed)
     if trainer.model_name == "t5":
-        return make_t5_batch_fn(trainer, prefix, train_iters, seed, vocab_file)
+        return make_t5_batch_fn(trainer, prefix, train_iters, seed, vocab_file, split=split, eval_samples=eval_samples)
     if trainer.model_name == "bert":
         special = None
         if vocab_file:      # ids of the special tokens from the WordPiece vocabulary the corpus was encoded with
@@ -45,7 +66,7 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
             from ..tokenizer.wordpiece import load_vocab
             v = load_vocab(vocab_file)
             special = SpecialTokens(cls=v["[CLS]"], sep=v["[SEP]"], mask=v["[MASK]"], pad=v["[PAD]"])
-        return make_bert_batch_fn(trainer, prefix, train_iters, seed, special)
+        return make_bert_batch_fn(trainer, prefix, train_iters, seed, special, split=split, eval_samples=eval_samples)
     from ..data.indexed import GPTSampleDataset, TokenCorpus
     assert trainer.model_name == "gpt", "--data-path feeds the GPT, T5, BERT and Wide-ResNet entry points"
     from ..data import mmap_format
@@ -56,23 +77,28 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
         corpus = TokenCorpus.from_files(prefix + (".u32" if wide else ".bin"), prefix + ".npy",
                                         dtype=np.uint32 if wide else np.uint16)
     gbs, seq = trainer.plan["global_batch_size"], trainer.cfg.seq_length
-    data = GPTSampleDataset(corpus, seq, num_samples=train_iters * gbs, seed=seed)
 
-    def batch(i):
-        rows = np.stack([data[(i * gbs + j) % len(data)] for j in range(gbs)])
-        t = torch.from_numpy(rows)
-        out = {"ids": t[:, :-1].contiguous(), "labels": t[:, 1:].contiguous()}
-        if eod_token is not None:
-            # positions whose INPUT is the end-of-document token would have to predict the first token of an
-            # unrelated document: they do not count (reference: eod_mask_loss of get_ltor_masks_and_position_ids,
-            # runtime/megatron/utils.py)
-            out["loss_mask"] = (out["ids"] != eod_token).to(torch.float32)
-        return {k: v.pin_memory() for k, v in out.items()} if torch.cuda.is_available() else out
+    def batches_of(part, num_samples):
+        data = GPTSampleDataset(part, seq, num_samples=num_samples or train_iters * gbs, seed=seed)
 
-    return batch
+        def batch(i):
+            rows = np.stack([data[(i * gbs + j) % len(data)] for j in range(gbs)])
+            t = torch.from_numpy(rows)
+            out = {"ids": t[:, :-1].contiguous(), "labels": t[:, 1:].contiguous()}
+            if eod_token is not None:
+                # positions whose INPUT is the end-of-document token would have to predict the first token of an
+                # unrelated document: they do not count (reference: eod_mask_loss of
+                # get_ltor_masks_and_position_ids, runtime/megatron/utils.py)
+                out["loss_mask"] = (out["ids"] != eod_token).to(torch.float32)
+            return {k: v.pin_memory() for k, v in out.items()} if torch.cuda.is_available() else out
+
+        return batch
+
+    return _held_out(batches_of, _split_parts(corpus, len(corpus.sizes), split), eval_samples)
 
 
-def make_bert_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, special=None):
+def make_bert_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, special=None, split=None,
+                       eval_samples: int = 0):
     """Batches of a sentence corpus written by `data.preprocess --split-sentences`: [CLS] A [SEP] B [SEP] samples with
     masked-LM labels and the sentence-order flag (reference: runtime/megatron/data/bert_dataset.py).  `special`
     names the ids of [CLS], [SEP], [MASK], [PAD]; the default is their place in a BERT WordPiece vocabulary
@@ -81,12 +107,18 @@ def make_bert_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: in
     from ..data.sentences import BertDataset, SpecialTokens, bert_batch_of
     tokens = special or SpecialTokens(cls=101, sep=102, mask=103, pad=0)
     cfg, gbs = trainer.cfg, trainer.plan["global_batch_size"]
-    data = BertDataset(load_sentence_corpus(prefix), tokens, cfg.vocab, num_samples=train_iters * gbs,
-                       max_seq_length=cfg.seq_length, seed=seed, binary_head=cfg.binary_head)
-    return lambda i: bert_batch_of(data, range(i * gbs, (i + 1) * gbs))
+
+    def batches_of(part, num_samples):
+        data = BertDataset(part, tokens, cfg.vocab, num_samples=num_samples or train_iters * gbs,
+                           max_seq_length=cfg.seq_length, seed=seed, binary_head=cfg.binary_head)
+        return lambda i: bert_batch_of(data, range(i * gbs, (i + 1) * gbs))
+
+    corpus = load_sentence_corpus(prefix)
+    return _held_out(batches_of, _split_parts(corpus, len(corpus.doc_starts) - 1, split), eval_samples)
 
 
-def make_t5_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, vocab_file: str, extra_ids: int = 100):
+def make_t5_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, vocab_file: str, extra_ids: int = 100,
+                     split=None, eval_samples: int = 0):
     """Span-corruption batches of a sentence corpus written by `data.preprocess --split-sentences`: masked spans
     become sentinels in the encoder input, the decoder predicts them (reference:
     runtime/megatron/data/t5_dataset.py).  The sentinels, [BOS] and [EOS] are appended to the WordPiece vocabulary,
@@ -98,14 +130,15 @@ def make_t5_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int,
     tok = build_tokenizer("BertWordPieceLowerCase", vocab_file, None, vocab_extra_ids=extra_ids)
     cfg, gbs = trainer.cfg, trainer.plan["global_batch_size"]
     assert tok.vocab_size <= cfg.padded_vocab, f"model vocabulary {cfg.padded_vocab} < tokenizer's {tok.vocab_size}"
-    data = T5Dataset(load_sentence_corpus(prefix), tok.special_tokens(), tok.vocab_size, num_samples=train_iters * gbs,
-                     max_seq_length=cfg.seq_length, max_seq_length_dec=cfg.dec_seq_length, seed=seed)
 
-    def batch(i):
+    def batches_of(part, num_samples):
         from ..data.sentences import t5_batches
-        return next(t5_batches(data, gbs, 1, start=i * gbs))
+        data = T5Dataset(part, tok.special_tokens(), tok.vocab_size, num_samples=num_samples or train_iters * gbs,
+                         max_seq_length=cfg.seq_length, max_seq_length_dec=cfg.dec_seq_length, seed=seed)
+        return lambda i: next(t5_batches(data, gbs, 1, start=i * gbs))
 
-    return batch
+    corpus = load_sentence_corpus(prefix)
+    return _held_out(batches_of, _split_parts(corpus, len(corpus.doc_starts) - 1, split), eval_samples)
 
 
 def make_image_batch_fn(trainer: Trainer, root: str, seed: int):
@@ -123,6 +156,12 @@ def make_image_batch_fn(trainer: Trainer, root: str, seed: int):
         data.set_epoch(epoch)
         return image_batch(data, idx, pin=torch.cuda.is_available())
 
+    batch.valid = batch.test = None
+    val_dir = os.path.join(root, "val")
+    if os.path.isdir(val_dir):         # held-out pictures: resize + centre crop, in file order
+        held = ImageFolder(val_dir, size=trainer.cfg.image_size, train=False, seed=seed)
+        batch.valid = lambda i: image_batch(held, [(i * gbs + j) % len(held) for j in range(gbs)],
+                                            pin=torch.cuda.is_available())
     return batch
 
 
@@ -194,6 +233,11 @@ def main(argv=None) -> None:
     ap.add_argument("--data-path", default=None,
                     help="GPT token corpus prefix (<prefix>.bin uint16 token ids + <prefix>.npy document lengths); "
                          "default: synthetic batches")
+    ap.add_argument("--split", default=None, metavar="TRAIN,VALID,TEST",
+                    help="with --data-path: weights of the training / validation / test parts of the corpus (whole "
+                         "documents, in file order), e.g. 949,50,1; --eval-interval then evaluates on the validation "
+                         "part and the end of training on the test part.  Default: everything trains and evaluation "
+                         "draws from the same corpus.  An image folder holds its validation part in <root>/val")
     ap.add_argument("--eod-mask-loss", type=int, default=None, metavar="EOD_TOKEN_ID",
                     help="with --data-path: positions whose input is this end-of-document token do not count in the loss")
     ap.add_argument("--interleave-factor", type=int, default=1,
@@ -241,8 +285,11 @@ def main(argv=None) -> None:
         from torch.utils.tensorboard import SummaryWriter
         writer = SummaryWriter(log_dir=args.tensorboard_dir)
     t_start = time.time()
+    gbs = plan["global_batch_size"]
+    eval_rounds = args.train_iters // args.eval_interval + 1 if args.eval_interval else 1
     batch_fn = (make_dataset_batch_fn(trainer, args.data_path, args.train_iters, args.seed, args.eod_mask_loss,
-                                      args.vocab_file)
+                                      args.vocab_file, split=args.split,
+                                      eval_samples=max(1, eval_rounds * args.eval_iters) * gbs)
                 if args.data_path
                 else make_batch_fn(trainer))
     # synthetic batches are generated on the host before the loop (a pool of up to 4, reused in turn): building
@@ -315,7 +362,12 @@ def main(argv=None) -> None:
         if args.save and args.save_interval and (it + 1) % args.save_interval == 0:
             checkpointing.save_checkpoint(trainer, args.save)
         if args.eval_interval and (it + 1) % args.eval_interval == 0:
-            ev = trainer.evaluate(batch_fn(10 ** 6 + it * args.eval_iters + j) for j in range(args.eval_iters))
+            held = getattr(batch_fn, "valid", None)
+            if held is not None:           # the validation part, continued from where the last evaluation stopped
+                first = ((it + 1) // args.eval_interval - 1) * args.eval_iters
+                ev = trainer.evaluate(held(first + j) for j in range(args.eval_iters))
+            else:
+                ev = trainer.evaluate(batch_fn(10 ** 6 + it * args.eval_iters + j) for j in range(args.eval_iters))
             if rank == world - 1:
                 print(f" validation loss at iteration {it + 1} | " +
                       " | ".join(f"{k} value: {v:.6E}" for k, v in ev.items()), flush=True)
@@ -336,6 +388,12 @@ def main(argv=None) -> None:
                 break
     if args.save:
         checkpointing.save_checkpoint(trainer, args.save)
+    held = getattr(batch_fn, "test", None)
+    if held is not None and args.eval_iters > 0:
+        ev = trainer.evaluate(held(j) for j in range(args.eval_iters))
+        if rank == world - 1:
+            print(" test loss at the end of training | " + " | ".join(f"{k} value: {v:.6E}" for k, v in ev.items()),
+                  flush=True)
     if writer is not None:
         writer.close()
     if world > 1:

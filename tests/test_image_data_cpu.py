@@ -94,3 +94,21 @@ def test_wide_resnet_trains_from_an_image_folder(tmp_path):
     fn = make_image_batch_fn(t, str(tmp_path), seed=11)
     losses = [t.loss_value(t.train_step(fn(i % 2))) for i in range(6)]
     assert all(np.isfinite(losses)) and losses[-1] < losses[0]
+
+
+def test_a_val_folder_becomes_the_held_out_batches(tmp_path):
+    import shutil
+    from helpers import tiny_resnet_plan
+    from superscaler_b200.runtime.pretrain import make_image_batch_fn
+    from superscaler_b200.runtime.trainer import Trainer
+    root = _make_folder(str(tmp_path), per_class=6, size=(48, 48))
+    t = Trainer(tiny_resnet_plan(), device="cpu", model_overrides=dict(image_size=64, num_classes=8))
+    assert make_image_batch_fn(t, str(tmp_path), seed=11).valid is None
+    shutil.copytree(root, os.path.join(str(tmp_path), "val"))
+    fn = make_image_batch_fn(t, str(tmp_path), seed=11)
+    a, b = fn.valid(0), fn.valid(0)
+    gbs = t.plan["global_batch_size"]
+    assert a["images"].shape == (gbs, 64, 64, 3) and torch.equal(a["images"], b["images"])
+    assert a["labels"].tolist() == ([0] * 6 + [1] * 6 + [2] * 6 + [0] * 6 + [1] * 6 + [2] * 6)[:gbs]    # file order, wrapped
+    ev = t.evaluate([t.to_device(a)])
+    assert all(np.isfinite(v) for v in ev.values())

@@ -75,3 +75,20 @@ def test_preprocess_writes_a_corpus_the_datasets_read(tmp_path):
     assert t.tokens[11] == 3 and t.tokens[-1] == 3
     data = GPTSampleDataset(t, 4, num_samples=8, seed=1)
     assert len(data) >= 8 and data[0].shape == (5,)
+
+
+def test_split_bounds_and_corpus_slices():
+    from superscaler_b200.data.indexed import TokenCorpus, split_bounds
+    from superscaler_b200.data.sentences import SentenceCorpus
+    assert split_bounds("949,50,1", 1000) == [0, 949, 999, 1000]
+    assert split_bounds("98/2", 50) == [0, 49, 50, 50]
+    assert split_bounds("1", 7) == [0, 7, 7, 7]
+    b = split_bounds("1,1,1", 10)                        # 3 + 3 + 3 = 9: the missing document moves every boundary up
+    assert b == [0, 4, 7, 10]
+    t = TokenCorpus(np.arange(10), [3, 2, 5])
+    part = t.slice_docs(1, 3)
+    assert part.tokens.tolist() == list(range(3, 10)) and part.sizes.tolist() == [2, 5]
+    s = SentenceCorpus(np.arange(12), [2, 3, 1, 4, 2], [0, 2, 3, 5], title_lengths=[1, 2, 3])
+    part = s.slice_docs(1, 3)
+    assert part.tokens.tolist() == list(range(5, 12)) and part.sizes.tolist() == [1, 4, 2]
+    assert part.doc_starts.tolist() == [0, 1, 3] and part.title_sizes.tolist() == [2, 3]

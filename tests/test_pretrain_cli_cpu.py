@@ -151,3 +151,32 @@ def test_t5_trains_on_span_corruption_batches_of_a_sentence_corpus(tmp_path):
     assert torch.equal(fn(0)["ids"], b["ids"])
     losses = [t.loss_value(t.train_step(fn(i))) for i in range(3)]
     assert all(math.isfinite(v) for v in losses)
+
+
+def test_split_holds_out_validation_and_test_documents(tmp_path, capsys):
+    """--split on a corpus in Megatron-LM's format: the first 30 documents (pattern A) train, the held-out parts hold
+    documents of a pattern the model never saw, so their loss stays far above the training loss."""
+    import re
+    import numpy as np
+    from superscaler_b200.data import mmap_format
+    rng = np.random.RandomState(0)
+    docs = []
+    for d in range(40):
+        n = int(rng.randint(200, 400))
+        if d < 30:
+            docs.append(((np.arange(n) + int(rng.randint(0, 16))) % 16 + 20).tolist())     # periodic, learnable
+        else:
+            docs.append(rng.randint(40, 60, size=n).tolist())                              # unseen token range
+    mmap_format.write(str(tmp_path / "corpus"), docs, list(range(41)), dtype=np.uint16)
+    plan_path = tmp_path / "gpt_tiny_1stages_split.json"
+    plan_path.write_text(json.dumps(tiny_gpt_plan(seq=64, hidden=64, heads=2, head_dim=32, vocab=64)))
+    pretrain.main(["--flexpipe-config", str(plan_path), "--data-path", str(tmp_path / "corpus"), "--lr", "3e-3",
+                   "--lr-decay-style", "constant", "--lr-warmup-fraction", "0", "--hidden-dropout", "0",
+                   "--attention-dropout", "0", "--log-interval", "10", "--train-iters", "40",
+                   "--split", "30,6,4", "--eval-interval", "20", "--eval-iters", "1"])
+    out = capsys.readouterr().out
+    train = [float(x) for x in re.findall(r"lm loss: ([0-9.E+-]+)", out)]
+    valid = [float(x) for x in re.findall(r"validation loss at iteration \d+ \| lm loss value: ([0-9.E+-]+)", out)]
+    test = [float(x) for x in re.findall(r"test loss at the end of training \| lm loss value: ([0-9.E+-]+)", out)]
+    assert len(valid) == 2 and len(test) == 1
+    assert train[-1] < 1.5 and min(valid + test) > 2.5
