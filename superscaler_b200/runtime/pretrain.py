@@ -13,6 +13,7 @@ import argparse
 import csv
 import contextlib
 import json
+import math
 import os
 import sys
 import time
@@ -55,6 +56,12 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
     shuffled sample order (a function of the seed and of --train-iters), so a run resumed with the same
     --train-iters continues where the data stopped."""
     import numpy as np
+    if not isinstance(prefix, str) and len(prefix) == 1:
+        prefix = prefix[0]
+    if trainer.model_name != "gpt":
+        assert isinstance(prefix, str), "a blend of several corpora is read for GPT only"
+    else:
+        assert isinstance(prefix, str) or len(prefix) % 2 == 0, "--data-path: one prefix, or weight prefix pairs"
     if trainer.model_name in ("resnet", "vit"):
         return make_image_batch_fn(trainer, prefix, seed)
     if trainer.model_name == "t5":
@@ -67,19 +74,41 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
             v = load_vocab(vocab_file)
             special = SpecialTokens(cls=v["[CLS]"], sep=v["[SEP]"], mask=v["[MASK]"], pad=v["[PAD]"])
         return make_bert_batch_fn(trainer, prefix, train_iters, seed, special, split=split, eval_samples=eval_samples)
-    from ..data.indexed import GPTSampleDataset, TokenCorpus
+    from ..data.indexed import BlendedDataset, GPTSampleDataset, TokenCorpus
     assert trainer.model_name == "gpt", "--data-path feeds the GPT, T5, BERT and Wide-ResNet entry points"
     from ..data import mmap_format
-    if mmap_format.exists(prefix) and not os.path.exists(prefix + ".npy"):
-        corpus = mmap_format.token_corpus(prefix)       # a corpus preprocessed for Megatron-LM (<prefix>.idx)
-    else:
-        wide = os.path.exists(prefix + ".u32")
-        corpus = TokenCorpus.from_files(prefix + (".u32" if wide else ".bin"), prefix + ".npy",
-                                        dtype=np.uint32 if wide else np.uint16)
+
+    def load(one: str) -> TokenCorpus:
+        if mmap_format.exists(one) and not os.path.exists(one + ".npy"):
+            return mmap_format.token_corpus(one)         # a corpus preprocessed for Megatron-LM (<prefix>.idx)
+        wide = os.path.exists(one + ".u32")
+        return TokenCorpus.from_files(one + (".u32" if wide else ".bin"), one + ".npy",
+                                      dtype=np.uint32 if wide else np.uint16)
+
+    # one corpus, or several blended by weight: [w1, prefix1, w2, prefix2, ...]; every corpus is split on its own
+    sources = [(1.0, prefix)] if isinstance(prefix, str) else \
+        [(float(prefix[k]), prefix[k + 1]) for k in range(0, len(prefix), 2)]
+    total_w = sum(w for w, _ in sources)
+    assert total_w > 0, "blending weights must not all be zero"
+    per_source = []
+    for w, one in sources:
+        corpus = load(one)
+        per_source.append((w / total_w, _split_parts(corpus, len(corpus.sizes), split)))
+    parts = []
+    for k in range(3):
+        have = [(w, p[k]) for w, p in per_source if p[k] is not None]
+        parts.append(have or None)
     gbs, seq = trainer.plan["global_batch_size"], trainer.cfg.seq_length
 
     def batches_of(part, num_samples):
-        data = GPTSampleDataset(part, seq, num_samples=num_samples or train_iters * gbs, seed=seed)
+        n = num_samples or train_iters * gbs
+        if len(part) == 1:
+            data = GPTSampleDataset(part[0][1], seq, num_samples=n, seed=seed)
+        else:   # every source a little over its share, so the interleaving never runs one dry (reference:
+            # build_train_valid_test_datasets with a blend, runtime/megatron/data/gpt_dataset.py)
+            share = sum(w for w, _ in part)
+            data = BlendedDataset([GPTSampleDataset(c, seq, num_samples=int(math.ceil(n * w / share * 1.005)), seed=seed)
+                                   for w, c in part], [w for w, _ in part], n)
 
         def batch(i):
             rows = np.stack([data[(i * gbs + j) % len(data)] for j in range(gbs)])
@@ -94,7 +123,7 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
 
         return batch
 
-    return _held_out(batches_of, _split_parts(corpus, len(corpus.sizes), split), eval_samples)
+    return _held_out(batches_of, parts, eval_samples)
 
 
 def make_bert_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, special=None, split=None,
@@ -230,9 +259,11 @@ def main(argv=None) -> None:
                          "fused kernel that sums dQ in arrival order")
     ap.add_argument("--vocab-file", default=None,
                     help="BERT with --data-path: the WordPiece vocabulary of the corpus (ids of [CLS] [SEP] [MASK] [PAD])")
-    ap.add_argument("--data-path", default=None,
-                    help="GPT token corpus prefix (<prefix>.bin uint16 token ids + <prefix>.npy document lengths); "
-                         "default: synthetic batches")
+    ap.add_argument("--data-path", default=None, nargs="+",
+                    help="corpus prefix (GPT: <prefix>.bin token ids + <prefix>.npy document lengths, or Megatron-LM's "
+                         "<prefix>.bin + <prefix>.idx; T5 / BERT: a sentence corpus; Wide-ResNet / ViT: an image "
+                         "folder).  GPT also takes a blend: WEIGHT1 PREFIX1 WEIGHT2 PREFIX2 ...  "
+                         "Default: synthetic batches")
     ap.add_argument("--split", default=None, metavar="TRAIN,VALID,TEST",
                     help="with --data-path: weights of the training / validation / test parts of the corpus (whole "
                          "documents, in file order), e.g. 949,50,1; --eval-interval then evaluates on the validation "

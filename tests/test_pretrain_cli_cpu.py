@@ -180,3 +180,29 @@ def test_split_holds_out_validation_and_test_documents(tmp_path, capsys):
     test = [float(x) for x in re.findall(r"test loss at the end of training \| lm loss value: ([0-9.E+-]+)", out)]
     assert len(valid) == 2 and len(test) == 1
     assert train[-1] < 1.5 and min(valid + test) > 2.5
+
+
+def test_blend_of_two_corpora_draws_from_both_by_weight(tmp_path):
+    """--data-path W1 P1 W2 P2: samples of the two corpora (told apart by their token ranges) arrive in the ratio
+    of the weights."""
+    import numpy as np
+    from superscaler_b200.runtime.trainer import Trainer
+    rng = np.random.RandomState(1)
+    for name, lo in (("a", 10), ("b", 40)):
+        docs = [rng.randint(lo, lo + 10, size=int(rng.randint(150, 300))).astype(np.uint16) for _ in range(12)]
+        np.concatenate(docs).tofile(tmp_path / f"{name}.bin")
+        np.save(tmp_path / f"{name}.npy", np.asarray([len(d) for d in docs], dtype=np.int32))
+    t = Trainer(tiny_gpt_plan(seq=32, hidden=64, heads=2, head_dim=32, vocab=64), device="cpu")
+    fn = pretrain.make_dataset_batch_fn(t, ["3", str(tmp_path / "a"), "1", str(tmp_path / "b")], train_iters=8, seed=5,
+                                        split="9,1,0", eval_samples=8)
+    gbs = t.plan["global_batch_size"]
+    rows = np.concatenate([fn(i)["ids"].numpy() for i in range(8)])
+    from_a = (rows < 30).all(axis=1)
+    from_b = (rows >= 30).all(axis=1)
+    assert (from_a | from_b).all()                       # no sample mixes the corpora
+    assert abs(from_a.mean() - 0.75) < 0.05
+    assert fn.valid is not None and fn.test is None
+    assert fn.valid(0)["ids"].shape == (gbs, 32)
+    again = pretrain.make_dataset_batch_fn(t, ["3", str(tmp_path / "a"), "1", str(tmp_path / "b")], train_iters=8, seed=5,
+                                           split="9,1,0", eval_samples=8)
+    assert np.array_equal(again(3)["ids"].numpy(), fn(3)["ids"].numpy())
