@@ -49,7 +49,7 @@ def _split_parts(corpus, num_docs: int, split):
 
 
 def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, eod_token=None, vocab_file=None,
-                          split=None, eval_samples: int = 0):
+                          split=None, eval_samples: int = 0, titles_prefix=None):
     """Batches of a GPT token corpus: `prefix`.bin holds the token ids (uint16, or uint32 with `prefix`.u32 present
     instead), `prefix`.npy the document lengths; a Megatron-LM corpus (`prefix`.bin + `prefix`.idx) is read as it
     is.  Batch i is global samples [i * gbs, (i + 1) * gbs) of the
@@ -66,16 +66,20 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
         return make_image_batch_fn(trainer, prefix, seed)
     if trainer.model_name == "t5":
         return make_t5_batch_fn(trainer, prefix, train_iters, seed, vocab_file, split=split, eval_samples=eval_samples)
-    if trainer.model_name == "bert":
+    if trainer.model_name in ("bert", "ict"):
         special = None
         if vocab_file:      # ids of the special tokens from the WordPiece vocabulary the corpus was encoded with
             from ..data.sentences import SpecialTokens
             from ..tokenizer.wordpiece import load_vocab
             v = load_vocab(vocab_file)
             special = SpecialTokens(cls=v["[CLS]"], sep=v["[SEP]"], mask=v["[MASK]"], pad=v["[PAD]"])
+        if trainer.model_name == "ict":
+            assert titles_prefix, "the inverse-cloze model with --data-path needs --titles-data-path"
+            return make_ict_batch_fn(trainer, prefix, titles_prefix, train_iters, seed, special, split=split,
+                                     eval_samples=eval_samples)
         return make_bert_batch_fn(trainer, prefix, train_iters, seed, special, split=split, eval_samples=eval_samples)
     from ..data.indexed import BlendedDataset, GPTSampleDataset, TokenCorpus
-    assert trainer.model_name == "gpt", "--data-path feeds the GPT, T5, BERT and Wide-ResNet entry points"
+    assert trainer.model_name == "gpt", f"--data-path does not feed the {trainer.model_name} model"
     from ..data import mmap_format
 
     def load(one: str) -> TokenCorpus:
@@ -144,6 +148,39 @@ def make_bert_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: in
 
     corpus = load_sentence_corpus(prefix)
     return _held_out(batches_of, _split_parts(corpus, len(corpus.doc_starts) - 1, split), eval_samples)
+
+
+def make_ict_batch_fn(trainer: Trainer, prefix: str, titles_prefix: str, train_iters: int, seed: int, special=None,
+                      split=None, eval_samples: int = 0, query_in_block_prob: float = 0.1):
+    """(query, block) pairs for the inverse-cloze biencoder from two sentence corpora with the same documents in
+    the same order: the text (`prefix`) and the titles (`titles_prefix`, all sentences of a document together are
+    its title).  A global batch of n sequences holds n / 2 pairs (reference: runtime/megatron/data/ict_dataset.py,
+    --titles-data-path and --query-in-block-prob of runtime/megatron/arguments.py)."""
+    import numpy as np
+    from ..data.indexed import split_bounds
+    from ..data.preprocess import load_sentence_corpus
+    from ..data.sentences import InverseClozeDataset, SentenceCorpus, SpecialTokens
+    from ..models.ict import ict_batch_of
+    tokens = special or SpecialTokens(cls=101, sep=102, mask=103, pad=0)
+    text, tc = load_sentence_corpus(prefix), load_sentence_corpus(titles_prefix)
+    docs = len(text.doc_starts) - 1
+    assert len(tc.doc_starts) - 1 == docs, (f"{titles_prefix} holds {len(tc.doc_starts) - 1} documents, "
+                                            f"{prefix} holds {docs}: titles and text must pair up")
+    titles = [np.asarray(tc.tokens[tc.sent_start[tc.doc_starts[d]]:tc.sent_start[tc.doc_starts[d + 1]]]) for d in range(docs)]
+    corpus = SentenceCorpus(text.tokens, text.sizes, text.doc_starts, title_lengths=[len(t) for t in titles])
+    cfg, gbs = trainer.cfg, trainer.plan["global_batch_size"]
+    assert gbs % 2 == 0, "the inverse-cloze batch holds (query, block) pairs"
+    pairs = gbs // 2
+    b = split_bounds(split, docs) if split else [0, docs, docs, docs]
+    parts = [(corpus.slice_docs(b[k], b[k + 1]), titles[b[k]:b[k + 1]]) if b[k + 1] > b[k] else None for k in range(3)]
+    assert parts[0] is not None, f"--split {split} leaves no training documents out of {docs}"
+
+    def batches_of(part, num_samples):
+        data = InverseClozeDataset(part[0], part[1], tokens, num_samples=(num_samples or train_iters * gbs) // 2,
+                                   max_seq_length=cfg.seq_length, query_in_block_prob=query_in_block_prob, seed=seed)
+        return lambda i: ict_batch_of(data, range(i * pairs, (i + 1) * pairs))
+
+    return _held_out(batches_of, parts, eval_samples)
 
 
 def make_t5_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, vocab_file: str, extra_ids: int = 100,
@@ -264,6 +301,9 @@ def main(argv=None) -> None:
                          "<prefix>.bin + <prefix>.idx; T5 / BERT: a sentence corpus; Wide-ResNet / ViT: an image "
                          "folder).  GPT also takes a blend: WEIGHT1 PREFIX1 WEIGHT2 PREFIX2 ...  "
                          "Default: synthetic batches")
+    ap.add_argument("--titles-data-path", default=None,
+                    help="inverse-cloze model: sentence corpus of the documents' titles, same documents in the same "
+                         "order as --data-path")
     ap.add_argument("--split", default=None, metavar="TRAIN,VALID,TEST",
                     help="with --data-path: weights of the training / validation / test parts of the corpus (whole "
                          "documents, in file order), e.g. 949,50,1; --eval-interval then evaluates on the validation "
@@ -320,7 +360,8 @@ def main(argv=None) -> None:
     eval_rounds = args.train_iters // args.eval_interval + 1 if args.eval_interval else 1
     batch_fn = (make_dataset_batch_fn(trainer, args.data_path, args.train_iters, args.seed, args.eod_mask_loss,
                                       args.vocab_file, split=args.split,
-                                      eval_samples=max(1, eval_rounds * args.eval_iters) * gbs)
+                                      eval_samples=max(1, eval_rounds * args.eval_iters) * gbs,
+                                      titles_prefix=args.titles_data_path)
                 if args.data_path
                 else make_batch_fn(trainer))
     # synthetic batches are generated on the host before the loop (a pool of up to 4, reused in turn): building

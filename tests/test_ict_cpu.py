@@ -79,3 +79,40 @@ def test_trained_encoder_is_the_embedder_of_the_evidence_index(tmp_path):
     q = embed(b["ids"][0::2], torch.ones(8, 16, dtype=torch.bool))
     _, found = index.search(q, 1)
     assert (found[:, 0] == torch.arange(100, 108)).float().mean() >= 0.75
+
+
+def test_pairs_from_a_text_corpus_and_a_titles_corpus(tmp_path):
+    """`make_ict_batch_fn`: text and titles preprocessed into two sentence corpora; every block opens with
+    [CLS] title [SEP], the query is a sentence of the same document, and a training step runs on the batch."""
+    import json
+    from superscaler_b200.data.preprocess import main as preprocess_main
+    from superscaler_b200.data.sentences import SpecialTokens
+    from superscaler_b200.runtime.pretrain import make_ict_batch_fn
+    words = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]", "."] + [f"w{i}" for i in range(40)] + [f"t{i}" for i in range(12)]
+    (tmp_path / "vocab.txt").write_text("\n".join(words) + "\n")
+    rng = np.random.RandomState(0)
+    rows = []
+    for d in range(12):
+        sents = [" ".join(f"w{int(x)}" for x in rng.randint(0, 40, size=4)) + " ." for _ in range(4)]
+        rows.append({"text": " ".join(sents), "title": f"t{d}"})
+    (tmp_path / "in.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    for key, name in (("text", "body"), ("title", "titles")):
+        preprocess_main(["--input", str(tmp_path / "in.jsonl"), "--json-key", key, "--output", str(tmp_path / name),
+                         "--split-sentences", "--tokenizer-type", "BertWordPieceLowerCase",
+                         "--vocab-file", str(tmp_path / "vocab.txt")])
+    t = _trainer(tiny_ict_plan(**{**KW, "global_bs": 8, "micro_bs": 8}))
+    special = SpecialTokens(cls=2, sep=3, mask=4, pad=0)
+    fn = make_ict_batch_fn(t, str(tmp_path / "body"), str(tmp_path / "titles"), train_iters=4, seed=3, special=special,
+                           split="10,2,0", eval_samples=8)
+    b = fn(0)
+    assert b["ids"].shape == (8, 16) and b["labels"].tolist() == [0, 0, 1, 1, 2, 2, 3, 3]
+    title_ids = set(range(46, 58))
+    for k in range(4):
+        query, block = b["ids"][2 * k].tolist(), b["ids"][2 * k + 1].tolist()
+        assert query[0] == 2 and block[0] == 2 and block[1] in title_ids and block[2] == 3
+        assert int(b["enc_lens"][2 * k]) == 7                    # [CLS] + 5 word pieces + [SEP]
+        assert 46 + 10 > block[1]                                 # training part: documents 0-9 only
+    held = fn.valid(0)
+    assert all(row[1] in (56, 57) for row in held["ids"][1::2].tolist())      # validation part: documents 10, 11
+    assert fn.test is None
+    assert math.isfinite(t.loss_value(t.train_step(b)))
