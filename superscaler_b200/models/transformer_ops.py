@@ -401,7 +401,17 @@ class SoftmaxOp(Op, _AttnDims):
 
     def forward(self, st):
         scale = 1.0 / math.sqrt(self.env.cfg.head_dim)
-        st["x"] = F.scaled_softmax(st["x"], scale, 1 if self.mode == "causal" else 0)
+        x = st["x"]
+        lens = st.get("enc_lens") if self.mode != "causal" else None
+        if lens is None:
+            st["x"] = F.scaled_softmax(x, scale, 1 if self.mode == "causal" else 0)
+            return
+        # padded keys (the encoder's, also for the decoder's cross attention) get no weight, as in the one-kernel
+        # attention, which takes the same lengths as kv_lens
+        b, _, sq, sk = x.shape
+        beyond = torch.arange(sk, device=x.device)[None, :] >= lens.to(x.device).view(b, 1)
+        mask = beyond.view(b, 1, 1, sk).expand(b, 1, sq, sk).to(torch.uint8).contiguous()
+        st["x"] = F.scaled_softmax(x, scale, 2, mask)
 
 
 class AttnDropoutOp(Op):

@@ -138,3 +138,21 @@ def test_text_to_sentence_corpus_to_bert_training(tmp_path):
     assert torch.equal(fn(0)["ids"], b["ids"])                           # batch i is a function of i
     losses = [t.loss_value(t.train_step(fn(i % 2))) for i in range(4)]
     assert all(math.isfinite(v) for v in losses)
+
+
+def test_separate_attention_ops_mask_the_padding_like_the_one_kernel_form():
+    """A plan that keeps score / softmax / dropout / context as four ops (here: fusion switched off) must give padded
+    keys no weight either: same loss and gradients as the fused attention, on a batch with padding."""
+    from superscaler_b200.runtime.trainer import Trainer
+    plan = tiny_bert_plan(**dict(KW, micro_bs=8))
+    b = _batch(seed=4)
+    assert int(b["enc_lens"].min()) < KW["seq"]
+    runs = []
+    for fuse in (True, False):
+        t = Trainer(plan, device="cpu", model_overrides=OV, lr_warmup_steps=0, fuse=fuse, seed=7)
+        loss = t.forward_backward(t.to_device(b))
+        t._fold_autograd_grads()
+        runs.append((float(loss), t.store.grad.clone()))
+    (la, ga), (lb, gb) = runs
+    assert abs(la - lb) < 2e-3 * abs(la)
+    assert float((ga - gb).norm()) < 2e-2 * float(ga.norm())
