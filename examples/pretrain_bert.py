@@ -1,5 +1,6 @@
-"""Counterpart of the reference's runtime/pretrain_bert.py (inherited there from Megatron-LM as a module tree; here an
-op-list model like the others): trains the plan given by --flexpipe-config, which must be a bert plan
+"""BERT entry point, beside the reference's runtime/pretrain_gpt.py / pretrain_t5.py / pretrain_resnet.py (the
+reference's tree holds BERT's data pipeline, runtime/megatron/data/bert_dataset.py, but no BERT entry point; here BERT
+is an op-list model like the others): trains the plan given by --flexpipe-config, which must be a bert plan
 (`"model_name": "bert"` with the GPT plan keys).  Synthetic two-segment batches by default; `--data-path <prefix>
 --vocab-file vocab.txt` trains on a sentence corpus written by `python -m superscaler_b200.data.preprocess
 --split-sentences`.  All three entry points share one implementation (superscaler_b200.runtime.pretrain); launch one rank per GPU:

@@ -1,5 +1,6 @@
-"""Counterpart of the reference's runtime/pretrain_vit.py (inherited there from Megatron-LM as a module tree; here an
-op-list model): trains the plan given by --flexpipe-config, which must be a vit plan (`"model_name": "vit"`, the GPT
+"""Vision-transformer entry point, beside the reference's runtime/pretrain_gpt.py / pretrain_t5.py /
+pretrain_resnet.py (the reference's tree holds the ViT data pipeline, runtime/megatron/data/vit_dataset.py, and its
+flags, but no ViT entry point; here it is an op-list model): trains the plan given by --flexpipe-config, which must be a vit plan (`"model_name": "vit"`, the GPT
 plan keys for the layers, plus `image_size`, `patch_dim`, `num_classes`).  Synthetic images by default; `--data-path
 <folder>` trains on `folder/train/<class>/<image>` with the AutoAugment pipeline.  All three entry points share one implementation (superscaler_b200.runtime.pretrain); launch one rank per GPU:
 

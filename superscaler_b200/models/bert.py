@@ -1,10 +1,11 @@
 """BERT as a flat op list: `encoder-embedding` (word + position + token-type), 13 ops per layer (the same names as
 the GPT / T5 encoder layers, so plans and profiled tables address them alike), `final-layernorm`, `bert-post-process`.
 
-The reference inherits BERT from Megatron-LM as a module tree (runtime/megatron/model/bert_model.py: BertModel,
-BertLMHead, bert_extended_attention_mask; runtime/pretrain_bert.py: loss = masked-LM loss + sentence-order loss) and
-cannot run it from a plan; here it is an op-list model like the others, so every plan feature (per-op tensor / data
-parallel degrees, pipeline stages, recompute) applies.
+The reference's tree holds BERT's data side, inherited from Megatron-LM (runtime/megatron/data/bert_dataset.py,
+dataset_utils.py, the WordPiece tokenizer, --bert-no-binary-head at runtime/megatron/arguments.py:319) but not the
+model file it was written for.  The model here follows Megatron-LM's BERT (LM head = dense + GeLU + LayerNorm + tied
+vocabulary projection; loss = masked-LM loss + sentence-order loss) as an op-list model like the others, so every
+plan feature (per-op tensor / data parallel degrees, pipeline stages, recompute) applies.
 
   * attention looks both ways; padding is masked by the number of real tokens per sample (`enc_lens`);
   * the head transforms the hidden states (dense + GeLU + LayerNorm), projects them with the tied word embedding
@@ -104,8 +105,8 @@ class BertEmbeddingOp(EmbeddingOp):
 
 class BertPostOp(Op):
     """LM head (dense + GeLU + LayerNorm + tied vocabulary projection + masked cross entropy) and, with
-    `binary_head`, pooler + two-class head + cross entropy (reference: BertLMHead / post_language_model_processing,
-    runtime/megatron/model/bert_model.py; loss_func of runtime/pretrain_bert.py)."""
+    `binary_head`, pooler + two-class head + cross entropy (Megatron-LM's BertLMHead and BERT loss; the labels are
+    the ones runtime/megatron/data/bert_dataset.py builds: `labels`, `loss_mask`, `is_random`)."""
     reads = ("x", "labels", "loss_mask", "nsp")
     writes = ("loss", "logits")
 

@@ -1,9 +1,13 @@
 """Inverse-cloze-task biencoder (the retriever pre-training of REALM / ORQA) as an op-list model: a BERT encoder
 embeds queries and evidence blocks, and every query has to pick its own block among the blocks of the batch.
 
-Reference: runtime/megatron/model/biencoder_model.py (BiEncoderModel with `biencoder_shared_query_context_model`,
-`biencoder_projection_dim`), runtime/pretrain_ict.py (in-batch softmax over query x block scores, optional scaling
-by sqrt(hidden)).  Taken over here: the SHARED-tower variant.  Queries and blocks travel as ONE batch of 2 b
+What the reference's tree holds of this model: its flags (`_add_biencoder_args`, runtime/megatron/arguments.py:703-740:
+--biencoder-projection-dim, --biencoder-shared-query-context-model, --titles-data-path, --query-in-block-prob,
+--retriever-score-scaling), its data (runtime/megatron/data/ict_dataset.py, biencoder_dataset_utils.py) and the index
+builder (runtime/megatron/indexer.py, which imports a `megatron.model.biencoder_model` the tree does not contain).
+The model itself follows Megatron-LM's biencoder, which those files were written for: a BERT encoder, the [CLS]
+state, an optional linear projection, in-batch softmax over query x block scores, optionally divided by
+sqrt(hidden).  Built here: the SHARED-tower variant.  Queries and blocks travel as ONE batch of 2 b
 sequences, row 2 i = query i and row 2 i + 1 = its block, so a data-parallel split of the rows keeps pairs together
 and the encoder runs once over both; the negatives of a query are the other blocks on the same rank (the reference
 all-gathers them over the data-parallel group first).  The op list is BERT's with `ict-post-process` at the end.

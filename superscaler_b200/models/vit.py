@@ -2,8 +2,10 @@
 token, learned positions), 13 ops per layer (the encoder layer names shared with GPT / T5 / BERT), `final-layernorm`,
 `vit-post-process` (MLP head on the class token + cross entropy).
 
-The reference inherits it from Megatron-LM as a module tree (runtime/megatron/model/vit_model.py: VitModel, VitMlpHead;
-runtime/pretrain_vit.py) and cannot run it from a plan.  Images arrive channels-last [b, H, W, 3], as for the
+The reference's tree holds this model's flags (`_add_vit_args`, runtime/megatron/arguments.py:760-772: --num-classes,
+--img-dim, --patch-dim) and its data pipeline (runtime/megatron/data/vit_dataset.py, autoaugment.py), inherited from
+Megatron-LM, but not the model file they were written for; the model here follows Megatron-LM's vision transformer
+(patch projection, class token, learned positions, MLP head) and, unlike it, runs from a plan.  Images arrive channels-last [b, H, W, 3], as for the
 Wide-ResNet; a patch is flattened in (row, column, channel) order.  seq_length = (image_size / patch)^2 + 1.
 """
 from __future__ import annotations
@@ -62,7 +64,8 @@ def vit_layer_of(index: int, num_layers: int) -> int:
 
 class VitEmbeddingOp(Op):
     """Patches -> linear projection; a learned class token in front; learned position embeddings; dropout
-    (reference: VitModel.forward, runtime/megatron/model/vit_model.py)."""
+    (Megatron-LM's VitModel.forward; patch and image sizes as --patch-dim / --img-dim of
+    runtime/megatron/arguments.py:760-772)."""
     reads = ("images",)
     writes = ("x",)
 
