@@ -17,7 +17,7 @@ The unmodified reference tree (runtime/, search/, profiler/) sits under baseline
 * the plan JSON is written here in the reference's schema (runtime/megatron/arguments.py:90-124) for the benchmark's
   model: GPT-3 1.3B with 24 layers, hidden 2048, 16 heads, sequence 2048, global batch 512, one stage, data parallel
   over all GPUs; `--make-vocab-size-divisible-by 1024` pads GPT-2's 50257 tokens to exactly 51200;
-* the command line is the stock one of runtime/scripts/run_gpt.sh:22-44, run in this process (one process per GPU,
+* the command line is the stock one of runtime/scripts/run_gpt.sh:22-43, run in this process (one process per GPU,
   RANK / WORLD_SIZE / MASTER_* from the environment) through `runpy`.
 
 The time is the reference's own: "elapsed time per iteration (ms)" of its training log
@@ -83,7 +83,7 @@ def gpt_plan(n_gpus: int, micro_batch_per_gpu: int, recompute: bool, layers: int
 
 
 def stock_argv(plan_path: str, log_path: str, train_iters: int, dtype: str) -> list:
-    """The command line of runtime/scripts/run_gpt.sh:22-44 (paths filled in, iteration count from the caller)."""
+    """The command line of runtime/scripts/run_gpt.sh:22-43 (paths filled in, iteration count from the caller)."""
     return ["pretrain_gpt.py",
             "--flexpipe-config", plan_path,
             "--train-iters", str(train_iters),

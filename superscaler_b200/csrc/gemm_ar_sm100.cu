@@ -3,7 +3,7 @@
 //   out = epilogue( sum over tp ranks r of  A_r . B_r^T )       (every rank ends up with the full `out`)
 //
 // Replaces RowParallelLinear.forward = F.linear + torch.distributed.all_reduce and the all-reduce of the
-// input gradient of ColumnParallelLinear (runtime/megatron/mpu/layers.py:459-470,593-604,
+// input gradient of ColumnParallelLinear (runtime/megatron/mpu/layers.py:359,459-470,
 // runtime/megatron/mpu/mappings.py:23-40 of the reference), which run the GEMM to completion and only then start
 // the collective.  Here the reduction of output tile t overlaps the tensor-core work of tile t+1:
 //

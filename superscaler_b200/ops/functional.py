@@ -209,7 +209,7 @@ class RowParallelLinearFusedFn(torch.autograd.Function):
     (csrc/gemm_ar_sm100.cu).  Backward needs no collective: dx_r = g W_r, dW_r = g^T x_r with g the masked dy.
 
     Reference counterpart: RowParallelLinear + reduce_from_tensor_model_parallel_region + bias-dropout-add
-    (runtime/megatron/mpu/layers.py:532-604, runtime/megatron/mpu/mappings.py:23-40)."""
+    (runtime/megatron/mpu/layers.py:373-468, runtime/megatron/mpu/mappings.py:23-40)."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, residual, dropout_p, seed, tpctx):
