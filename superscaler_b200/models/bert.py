@@ -98,7 +98,9 @@ class BertEmbeddingOp(EmbeddingOp):
             x = x + torch.nn.functional.embedding(pos, P)
         types = st.get("types")
         if types is not None:
-            x = x + torch.nn.functional.embedding(types.reshape(-1), self.p("tokentype_embeddings.weight")).to(x.dtype)
+            # looked up in fp32: the gradient of a row is the sum over all tokens of that type, which bf16 would round
+            # at every addition
+            x = x + torch.nn.functional.embedding(types.reshape(-1), self.p("tokentype_embeddings.weight").float()).to(x.dtype)
         p_drop = c.hidden_dropout if self.env.training else 0.0
         st["x"] = F.dropout(x, p_drop, self.seed()) if p_drop > 0.0 else x
 

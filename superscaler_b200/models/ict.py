@@ -9,8 +9,8 @@ The model itself follows Megatron-LM's biencoder, which those files were written
 state, an optional linear projection, in-batch softmax over query x block scores, optionally divided by
 sqrt(hidden).  Built here: the SHARED-tower variant.  Queries and blocks travel as ONE batch of 2 b
 sequences, row 2 i = query i and row 2 i + 1 = its block, so a data-parallel split of the rows keeps pairs together
-and the encoder runs once over both; the negatives of a query are the other blocks on the same rank (the reference
-all-gathers them over the data-parallel group first).  The op list is BERT's with `ict-post-process` at the end.
+and the encoder runs once over both; the negatives of a query are the other blocks of the micro-batch on ALL
+data-parallel ranks (the embeddings are all-gathered over the data-parallel group before the scores are taken).  The op list is BERT's with `ict-post-process` at the end.
 
 Without labels in the state (inference) the last op leaves the projected embedding of every sequence in
 `st["logits"]`; `Trainer.embed` returns it, which is the embedder `data.retrieval.build_index` takes.
@@ -22,6 +22,7 @@ from typing import List
 
 import torch
 
+from ..parallel import mappings as M
 from .base import Env, Op, OpInfo
 from .bert import BertConfig, bert_config_from_plan, build_bert_op
 from .gpt import GPT_LAYER_OPS
@@ -66,6 +67,15 @@ class IctPostOp(Op):
             st["logits"] = pooled
             return
         assert n % 2 == 0, "the inverse-cloze batch holds (query, block) pairs"
+        dp = self.pl.dp
+        if dp > 1:
+            # every query is scored against the blocks of ALL data-parallel ranks (rows arrive in rank order, pairs
+            # stay adjacent).  All ranks then hold the same loss, and the gradient averaging over the ranks would
+            # count each embedding's contribution 1 / dp times: the factor dp on the way back makes the averaged
+            # gradient the gradient of the one global loss
+            pooled = pooled.detach() + dp * (pooled - pooled.detach())
+            pooled = M.gather_from_group(pooled, 0, self.dp_group)
+            n = pooled.shape[0]
         q, blocks = pooled[0::2], pooled[1::2]
         scores = q @ blocks.t()
         if c.score_scaling:

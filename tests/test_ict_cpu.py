@@ -1,5 +1,5 @@
 """Inverse-cloze biencoder: the in-batch retrieval loss, learning to match queries with their blocks, data-parallel
-pairs staying together, and the trained encoder as the embedder of the evidence index."""
+ranks scoring against each other's blocks, and the trained encoder as the embedder of the evidence index."""
 import math
 
 import numpy as np
@@ -25,9 +25,9 @@ def _pairs(n, seed):
             "labels": torch.arange(n).repeat_interleave(2)}
 
 
-def _trainer(plan, rank=0, world=1, lr=3e-3):
+def _trainer(plan, rank=0, world=1, lr=3e-3, **kw):
     from superscaler_b200.runtime.trainer import Trainer
-    return Trainer(plan, rank=rank, world_size=world, device="cpu", model_overrides=OV, lr_warmup_steps=0, lr=lr)
+    return Trainer(plan, rank=rank, world_size=world, device="cpu", model_overrides=OV, lr_warmup_steps=0, lr=lr, **kw)
 
 
 def test_loss_is_the_in_batch_softmax_and_training_learns_the_pairs():
@@ -48,15 +48,32 @@ def test_loss_is_the_in_batch_softmax_and_training_learns_the_pairs():
     assert ((emb[0::2] @ emb[1::2].t()).argmax(1) == torch.arange(8)).float().mean() >= 0.75
 
 
+def _reduced_grad(t, batch):
+    t.forward_backward(t.to_device(batch))
+    t._fold_autograd_grads()
+    t.optimizer.reduce_gradients()
+    return t.store.grad.clone()
+
+
 def _dp_worker(rank, world, plan, want):
-    t = _trainer(plan, rank, world)
-    got = [t.loss_value(t.train_step(_pairs(8, seed=1))) for _ in range(2)]
-    # each rank scores its 4 queries against its own 4 blocks: ln 4 at the start instead of ln 8
-    assert abs(got[0] - math.log(4)) < 0.5 and all(math.isfinite(v) for v in got), (rank, got, want)
+    want_grad, want_losses = want
+    t = _trainer(plan, rank, world, shard_optimizer=False)      # every rank keeps the whole reduced gradient
+    # the embeddings of both ranks are gathered before the scores are taken: every query sees all 8 blocks, and the
+    # averaged gradient is the gradient of that one loss (same size, not half of it)
+    g = _reduced_grad(t, _pairs(8, seed=1))
+    assert float((g - want_grad).norm()) < 2e-2 * float(want_grad.norm()), (rank, float(g.norm()), float(want_grad.norm()))
+    t.store.zero_grad()
+    got = [t.loss_value(t.train_step(_pairs(8, seed=1))) for _ in range(3)]
+    assert all(abs(a - b) < 3e-2 for a, b in zip(got, want_losses)), (rank, got, want_losses)
 
 
-def test_data_parallel_ranks_keep_query_and_block_together():
-    run_ranks(_dp_worker, 2, tiny_ict_plan(**KW, num_gpus=(2,), tp=[1]), None)
+def test_data_parallel_ranks_score_against_the_blocks_of_all_ranks():
+    t = _trainer(tiny_ict_plan(**KW))
+    grad = _reduced_grad(t, _pairs(8, seed=1))
+    t.store.zero_grad()
+    losses = [t.loss_value(t.train_step(_pairs(8, seed=1))) for _ in range(3)]
+    assert abs(losses[0] - math.log(8)) < 0.5 and losses[2] < losses[0]
+    run_ranks(_dp_worker, 2, tiny_ict_plan(**KW, num_gpus=(2,), tp=[1]), (grad, losses))
 
 
 def test_trained_encoder_is_the_embedder_of_the_evidence_index(tmp_path):
