@@ -39,6 +39,7 @@ class Env:
     store: ParamStore
     micro_bs: int                    # stage-aggregate micro batch size of the plan
     fused_comm: bool = False         # use the in-kernel peer-memory collectives where available
+    distribute_saved_activations: bool = False   # recompute segments keep 1 / tp of inputs replicated over tp
     stage_ops: Sequence[OpInfo] = ()
     tp_contexts: Dict[Tuple[int, ...], Any] = field(default_factory=dict)
 

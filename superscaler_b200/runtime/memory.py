@@ -2,7 +2,7 @@
 
 `MemoryBuffer` hands out views of one flat allocation (bump allocation, reset per step); `RingMemBuffer` cycles
 through several of them (reference: runtime/megatron/memory.py:26-145, used there for distributed checkpointed
-activations).  `report_memory` / `debug_mem_report` are the reference's utils.report_memory and debug_mem_report
+activations; here `runtime/stage.py` keeps those shares as plain allocations and these classes serve user code).  `report_memory` / `debug_mem_report` are the reference's utils.report_memory and debug_mem_report
 (runtime/megatron/utils.py): allocator statistics in MB, and a walk over the live tensors grouped by shape."""
 from __future__ import annotations
 

@@ -291,6 +291,9 @@ def main(argv=None) -> None:
     ap.add_argument("--inject-failure", default=None, metavar="RANK:ITERATION",
                     help="host-side fault injection for tests: that rank raises at the start of that iteration")
     ap.add_argument("--no-fused-comm", action="store_true")
+    ap.add_argument("--distribute-checkpointed-activations", action="store_true",
+                    help="recomputed segments keep only this rank's 1 / tp share of inputs that the whole "
+                         "tensor-parallel group holds, and gather them again in the backward pass")
     ap.add_argument("--deterministic", action="store_true",
                     help="bitwise-reproducible steps: attention backward as the dK/dV + dQ kernel pair instead of the "
                          "fused kernel that sums dQ in arrival order")
@@ -338,7 +341,8 @@ def main(argv=None) -> None:
     trainer = Trainer(plan, model_overrides=overrides, rank=rank, world_size=world, seed=args.seed, lr=args.lr, min_lr=args.min_lr,
                       weight_decay=args.weight_decay, clip_grad=args.clip_grad, lr_decay_steps=args.lr_decay_iters,
                       lr_warmup_steps=int(args.lr_warmup_fraction * args.lr_decay_iters), lr_style=args.lr_decay_style,
-                      optimizer=args.optimizer, fused_comm=not args.no_fused_comm)
+                      optimizer=args.optimizer, fused_comm=not args.no_fused_comm,
+                      distribute_checkpointed_activations=args.distribute_checkpointed_activations)
     if args.load and args.load_resharded:
         trainer.iteration = 0 if args.finetune else checkpointing.load_under_plan(trainer, args.load)
         trainer.lr_schedule.step(trainer.iteration)      # the schedule continues where the old run stopped

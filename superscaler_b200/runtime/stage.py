@@ -23,10 +23,24 @@ class _CheckpointFn(torch.autograd.Function):
     bookkeeping, runtime/megatron/mpu/random.py:246-326)."""
 
     @staticmethod
-    def forward(ctx, run, in_keys, holder, *tensors):
+    def forward(ctx, run, in_keys, holder, split_groups, *tensors):
         ctx.run, ctx.in_keys = run, in_keys
         ctx.seed_state = F.seed_state().get_state()
-        ctx.save_for_backward(*tensors)
+        # an input every rank of a tensor-parallel group holds in full is kept as this rank's 1 / tp share and
+        # gathered again for the replay (--distribute-checkpointed-activations of the reference,
+        # runtime/megatron/mpu/random.py:262-276,291-294)
+        kept, ctx.shares = [], []
+        for t, g in zip(tensors, split_groups):
+            if g is None:
+                kept.append(t)
+                ctx.shares.append(None)
+                continue
+            n, r = torch.distributed.get_world_size(g), torch.distributed.get_rank(g)
+            flat = t.detach().reshape(-1)
+            share = flat.numel() // n
+            kept.append(flat[r * share:(r + 1) * share].clone())
+            ctx.shares.append((g, n, t.shape))
+        ctx.save_for_backward(*kept)
         ctx.req = [t.requires_grad for t in tensors]
         with torch.no_grad():
             st = dict(zip(in_keys, tensors))
@@ -45,7 +59,13 @@ class _CheckpointFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):
-        tensors = ctx.saved_tensors
+        tensors = list(ctx.saved_tensors)
+        for i, info in enumerate(ctx.shares):
+            if info is not None:
+                g, n, shape = info
+                whole = torch.empty(n * tensors[i].numel(), dtype=tensors[i].dtype, device=tensors[i].device)
+                torch.distributed.all_gather_into_tensor(whole, tensors[i], group=g)
+                tensors[i] = whole.view(shape)
         ins = []
         for t, r in zip(tensors, ctx.req):
             d = t.detach()
@@ -65,7 +85,7 @@ class _CheckpointFn(torch.autograd.Function):
                 gs.append(g)
         if outs:
             torch.autograd.backward(outs, gs)
-        return (None, None, None) + tuple(i.grad if i.requires_grad else None for i in ins)
+        return (None, None, None, None) + tuple(i.grad if i.requires_grad else None for i in ins)
 
 
 def _same_layout(side_a: Side, lay_a: Layout, side_b: Side, lay_b: Layout) -> bool:
@@ -131,6 +151,24 @@ class Segment:
     def __init__(self, ops: List[Op], recompute: bool):
         self.ops, self.recompute = ops, recompute
 
+    def _shared_inputs(self, st, in_keys, meta_in) -> list:
+        """Per input: the tensor-parallel group whose ranks all hold that tensor in full (so each may keep a share of
+        it for the replay), or None.  Only with `Env.distribute_saved_activations`."""
+        first = self.ops[0]
+        env = first.env
+        none = [None] * len(in_keys)
+        if not getattr(env, "distribute_saved_activations", False) or meta_in is None or first.pl.tp == 1:
+            return none
+        ps = env.pstate
+        here = Side(ps.stage_start[ps.stage], first.info.tp, first.info.dp)
+        out = []
+        for k in in_keys:
+            t, m = st[k], meta_in.get(k)
+            whole = (m is not None and m[0] == here and m[1].col == "rep" and t.is_floating_point() and t.dim() >= 2
+                     and t.numel() % first.pl.tp == 0)
+            out.append(first.tp_group if whole else None)
+        return out
+
     def _run(self, st):
         for op in self.ops:
             run_op(op, st)
@@ -154,7 +192,8 @@ class Segment:
                 meta_out.update(inner["_meta"])
 
         holder: dict = {}
-        outs = _CheckpointFn.apply(run, in_keys, holder, *[st[k] for k in in_keys])
+        outs = _CheckpointFn.apply(run, in_keys, holder, self._shared_inputs(st, in_keys, meta_in),
+                                   *[st[k] for k in in_keys])
         for k in in_keys:
             st.pop(k)
         for k, v in zip(holder["out_keys"], outs):

@@ -97,7 +97,8 @@ class Trainer:
                  model_overrides: Optional[dict] = None, lr: float = 1.5e-4, min_lr: float = 1e-5,
                  weight_decay: float = 0.01, clip_grad: float = 1.0, lr_decay_steps: int = 320000,
                  lr_warmup_steps: int = 3200, lr_style: str = "cosine", optimizer: str = "adam",
-                 fuse: bool = True, fused_comm: bool = True, training: bool = True, shard_optimizer: bool = True):
+                 fuse: bool = True, fused_comm: bool = True, training: bool = True, shard_optimizer: bool = True,
+                 distribute_checkpointed_activations: bool = False):
         self.plan = plan
         self.rank, self.world_size = rank, world_size
         if device is None:
@@ -161,7 +162,7 @@ class Trainer:
                 # result into every rank's copy
                 self.store.model16_allocator = lambda n: SymmetricBuffer(n, torch.bfloat16, None, self.device)
         self.env = Env(cfg=self.cfg, pstate=self.pstate, store=self.store, micro_bs=self.micro_bs,
-                       fused_comm=fused_comm)
+                       fused_comm=fused_comm, distribute_saved_activations=distribute_checkpointed_activations)
         self.env.training = training
         self.stage = Stage(chunks, self.env, build_fn, fuse_fn if fuse else None)
         self._tied = None

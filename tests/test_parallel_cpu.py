@@ -396,3 +396,45 @@ def test_ranks_on_different_nodes_are_told_apart(monkeypatch):
     assert ps.same_node(range(4))
     monkeypatch.delenv("LOCAL_WORLD_SIZE")
     assert ps.same_node(range(4))
+
+
+def _saved_bytes_worker(rank, world, plan, want):
+    """Losses as in the single-process run, with and without the 1 / tp shares; bytes kept by the recompute
+    segments for the backward pass are counted through autograd's saved-tensor hooks."""
+    kept = {}
+    for share in (False, True):
+        t = Trainer(plan, rank=rank, world_size=world, model_overrides=NODROP, lr_warmup_steps=0, device="cpu", lr=1e-3,
+                    distribute_checkpointed_activations=share)
+        total = [0]
+
+        def pack(x, total=total):
+            total[0] += x.numel() * x.element_size()
+            return x
+
+        batch = t.to_device(gpt_batch(8, 64, 256, seed=1))
+        with torch.autograd.graph.saved_tensors_hooks(pack, lambda x: x):
+            t.forward_backward(batch)
+        kept[share] = total[0]
+        t._fold_autograd_grads()
+        t.store.zero_grad()
+        got = [t.loss_value(t.train_step(gpt_batch(8, 64, 256, seed=1))) for _ in range(3)]
+        assert max(abs(a - b) for a, b in zip(got, want)) < 3e-3, (rank, share, got, want)
+    # each of the two layers keeps x [4 x 64 rows, 64] in bf16 per micro-batch: half of it with the shares
+    full_inputs = 2 * 2 * (4 * 64 * 64 * 2)
+    assert kept[False] - kept[True] == full_inputs // 2, (kept, full_inputs)
+
+
+def test_recompute_segments_keep_one_share_of_replicated_inputs_per_tensor_parallel_rank():
+    run_ranks(_saved_bytes_worker, 2, tiny_gpt_plan(**KW, recompute=1, num_gpus=(2,), tp=[2]), _base())
+
+
+def _shares_worker(rank, world, plan, want):
+    t = Trainer(plan, rank=rank, world_size=world, model_overrides=NODROP, lr_warmup_steps=0, device="cpu", lr=1e-3,
+                distribute_checkpointed_activations=True)
+    got = [t.loss_value(t.train_step(gpt_batch(8, 64, 256, seed=1))) for _ in range(3)]
+    assert max(abs(a - b) for a, b in zip(got, want)) < 3e-3, (rank, got, want)
+
+
+def test_shares_of_saved_inputs_in_a_pipeline_with_a_tensor_parallel_stage():
+    plan = tiny_gpt_plan(**KW, recompute=1, num_gpus=(1, 2, 1), tp=[1, 2, 1], ops_per_stage=[9, 12, 8])
+    run_ranks(_shares_worker, 4, plan, _base())
