@@ -13,6 +13,7 @@ reference all-reduces unweighted sums over the world group, clip_grads.py:79-81,
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -52,6 +53,7 @@ class StageOptimizer:
             replicated_over_tp = s.tp > 1 and s.shard_dim is None
             copies = s.dp * (s.tp if replicated_over_tp else 1)
             groups.setdefault(copies, []).append((off, (n + 127) // 128 * 128))
+        self._norm_exclude = set(norm_exclude)
         self.norm_groups = {c: _merge(r) for c, r in groups.items()}
         self.dp_buckets = store.buckets_by_dp()
         # Sharded update (pure data-parallel stage with peer-mapped gradient AND model buffers): the weight-decay
@@ -191,6 +193,37 @@ class StageOptimizer:
     def grad_norm(self) -> float:
         """Host read of the last global gradient norm (synchronises)."""
         return float(self.sumsq.sqrt())
+
+    def _per_parameter_total(self, value_of) -> float:
+        """Sum over the whole model of `value_of(spec, offset, numel)`, every parameter counted once however many
+        ranks hold a copy of it (the weights the norm groups use), reduced over the job."""
+        total = torch.zeros(1, dtype=torch.float64)
+        for s in self.store.specs:
+            if s.name in self._norm_exclude:
+                continue
+            off, n = self.store.offsets[s.name]
+            copies = s.dp * (s.tp if (s.tp > 1 and s.shard_dim is None) else 1)
+            total += float(value_of(s, off, n)) / copies
+        if self.pstate.world_size > 1:
+            t = total.to(self.store.device)
+            dist.all_reduce(t)
+            total = t.cpu()
+        return float(total)
+
+    def count_zeros_in_grad(self) -> int:
+        """Zero entries of the (reduced) gradients of the whole model; call it between `reduce_gradients` and
+        `step` (reference: count_zeros_fp32, runtime/megatron/optimizer/clip_grads.py:123-148).  With the sharded
+        update only this rank's slice of the large matrices is reduced, so the count is taken before sharding is
+        of use: it is refused there."""
+        assert not self.sharded, "--log-num-zeros-in-grad needs the unsharded update (Trainer(shard_optimizer=False))"
+        g = self.store.grad
+        return int(round(self._per_parameter_total(lambda s, off, n: (g[off:off + n] == 0).sum())))
+
+    def params_norm(self) -> float:
+        """L2 norm of the model's parameters, as the model computes with them (bf16 weights, fp32 norm
+        parameters); reference: calc_params_l2_norm, runtime/megatron/utils.py:59-84."""
+        params = self.store.params
+        return math.sqrt(self._per_parameter_total(lambda s, off, n: params[s.name].detach().float().pow(2).sum()))
 
     def sync_replicas(self) -> None:
         """After sharded steps: every rank fetches the other ranks' slices of the fp32 master weights and of the

@@ -265,6 +265,15 @@ def main(argv=None) -> None:
     ap.add_argument("--weight-decay", type=float, default=0.01)
     ap.add_argument("--clip-grad", type=float, default=1.0)
     ap.add_argument("--optimizer", default="adam", choices=["adam", "sgd"])
+    ap.add_argument("--adam-beta1", type=float, default=0.9)
+    ap.add_argument("--adam-beta2", type=float, default=0.999)
+    ap.add_argument("--adam-eps", type=float, default=1e-8)
+    ap.add_argument("--sgd-momentum", type=float, default=0.9)
+    ap.add_argument("--lr-warmup-iters", type=int, default=None, help="warm-up iterations (instead of --lr-warmup-fraction)")
+    ap.add_argument("--init-method-std", type=float, default=None, help="standard deviation of the weight initialisation")
+    ap.add_argument("--log-params-norm", action="store_true", help="L2 norm of the parameters in the iteration line")
+    ap.add_argument("--log-num-zeros-in-grad", action="store_true",
+                    help="number of zero gradient entries in the iteration line (turns the sharded update off)")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--hidden-dropout", type=float, default=None)
     ap.add_argument("--attention-dropout", type=float, default=None)
@@ -338,10 +347,15 @@ def main(argv=None) -> None:
         overrides["hidden_dropout"] = args.hidden_dropout
     if args.attention_dropout is not None:
         overrides["attention_dropout"] = args.attention_dropout
+    if args.init_method_std is not None:
+        overrides["init_std"] = args.init_method_std
+    warmup = args.lr_warmup_iters if args.lr_warmup_iters is not None else int(args.lr_warmup_fraction * args.lr_decay_iters)
     trainer = Trainer(plan, model_overrides=overrides, rank=rank, world_size=world, seed=args.seed, lr=args.lr, min_lr=args.min_lr,
                       weight_decay=args.weight_decay, clip_grad=args.clip_grad, lr_decay_steps=args.lr_decay_iters,
-                      lr_warmup_steps=int(args.lr_warmup_fraction * args.lr_decay_iters), lr_style=args.lr_decay_style,
+                      lr_warmup_steps=warmup, lr_style=args.lr_decay_style,
                       optimizer=args.optimizer, fused_comm=not args.no_fused_comm,
+                      adam_betas=(args.adam_beta1, args.adam_beta2), adam_eps=args.adam_eps,
+                      sgd_momentum=args.sgd_momentum, shard_optimizer=not args.log_num_zeros_in_grad,
                       distribute_checkpointed_activations=args.distribute_checkpointed_activations)
     if args.load and args.load_resharded:
         trainer.iteration = 0 if args.finetune else checkpointing.load_under_plan(trainer, args.load)
@@ -377,6 +391,8 @@ def main(argv=None) -> None:
     timers = Timers(trainer.device.type == "cuda")
     config_name = os.path.splitext(os.path.basename(args.flexpipe_config))[0]
     regions = ["iteration", "forward-backward", "backward-params-all-reduce", "optimizer"]
+    extra = {}             # further columns of the iteration line
+
     def one_step(it):
         timers("iteration").start()
         batch = trainer.to_device(batch_fn(it) if args.data_path else pool[it % 4])
@@ -389,6 +405,8 @@ def main(argv=None) -> None:
         if trainer._tied is not None:
             trainer._tied.sync_grads()
         timers("backward-params-all-reduce").stop()
+        if args.log_num_zeros_in_grad and (it + 1) % args.log_interval == 0:
+            extra["num zeros"] = trainer.optimizer.count_zeros_in_grad()
         timers("optimizer").start()
         lr = trainer.lr_schedule.get_lr()
         trainer.optimizer.step(lr=lr)
@@ -415,15 +433,20 @@ def main(argv=None) -> None:
             row = timers.row(regions)
             lv = trainer.loss_value({"loss_tensor": loss})
             mem = torch.cuda.max_memory_allocated() / 2 ** 20 if trainer.device.type == "cuda" else 0.0
+            if args.log_params_norm:
+                extra["params norm"] = trainer.optimizer.params_norm()
+            more = "".join(f" | {k}: {v:.3f}" if isinstance(v, float) else f" | {k}: {v}" for k, v in extra.items())
             if rank == world - 1:
                 print(f" iteration {it + 1:8d}/{args.train_iters:8d} | elapsed time per iteration (ms): "
                       f"{row['iteration']:.1f} | learning rate: {lr:.3E} | global batch size: "
-                      f"{plan['global_batch_size']:5d} | lm loss: {lv:.6E} | grad norm: {trainer.optimizer.grad_norm():.3f}",
-                      flush=True)
+                      f"{plan['global_batch_size']:5d} | lm loss: {lv:.6E} | grad norm: {trainer.optimizer.grad_norm():.3f}"
+                      + more, flush=True)
             if writer is not None:
                 writer.add_scalar("learning-rate", lr, it + 1)
                 writer.add_scalar("lm loss", lv, it + 1)
                 writer.add_scalar("grad-norm", trainer.optimizer.grad_norm(), it + 1)
+                for k, v in extra.items():
+                    writer.add_scalar(k.replace(" ", "-"), v, it + 1)
                 writer.add_scalar("samples per second", plan["global_batch_size"] / (row["iteration"] / 1e3), it + 1)
                 for r in regions:
                     writer.add_scalar(f"{r}-time", row[r], it + 1)

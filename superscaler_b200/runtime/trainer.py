@@ -98,7 +98,8 @@ class Trainer:
                  weight_decay: float = 0.01, clip_grad: float = 1.0, lr_decay_steps: int = 320000,
                  lr_warmup_steps: int = 3200, lr_style: str = "cosine", optimizer: str = "adam",
                  fuse: bool = True, fused_comm: bool = True, training: bool = True, shard_optimizer: bool = True,
-                 distribute_checkpointed_activations: bool = False):
+                 distribute_checkpointed_activations: bool = False, adam_betas=(0.9, 0.999), adam_eps: float = 1e-8,
+                 sgd_momentum: float = 0.9):
         self.plan = plan
         self.rank, self.world_size = rank, world_size
         if device is None:
@@ -173,7 +174,7 @@ class Trainer:
             tied = TiedWeights(self)
             self._tied = tied if tied.links else None
         self.optimizer = StageOptimizer(self.store, self.pstate, lr=lr, weight_decay=weight_decay, clip_grad=clip_grad,
-                                        kind=optimizer,
+                                        kind=optimizer, betas=tuple(adam_betas), eps=adam_eps, momentum=sgd_momentum,
                                         norm_exclude=self._tied.duplicate_param_names() if self._tied else ())
         self.lr_schedule = LRSchedule(lr, min_lr, lr_warmup_steps, lr_decay_steps, lr_style)
         self.iteration = 0

@@ -438,3 +438,19 @@ def _shares_worker(rank, world, plan, want):
 def test_shares_of_saved_inputs_in_a_pipeline_with_a_tensor_parallel_stage():
     plan = tiny_gpt_plan(**KW, recompute=1, num_gpus=(1, 2, 1), tp=[1, 2, 1], ops_per_stage=[9, 12, 8])
     run_ranks(_shares_worker, 4, plan, _base())
+
+
+def _norm_worker(rank, world, plan, want):
+    t = Trainer(plan, rank=rank, world_size=world, model_overrides=NODROP, lr_warmup_steps=0, device="cpu",
+                shard_optimizer=False)
+    assert abs(t.optimizer.params_norm() - want) < 1e-4 * want, (rank, t.optimizer.params_norm(), want)
+    t.store.grad.fill_(0.0)
+    total = sum(n for _, n in Trainer(tiny_gpt_plan(**KW), device="cpu", model_overrides=NODROP).store.offsets.values())
+    assert t.optimizer.count_zeros_in_grad() == total          # every entry of the whole model, each counted once
+
+
+@pytest.mark.parametrize("plan_kw,world", [(dict(num_gpus=(2,), tp=[2]), 2), (dict(num_gpus=(2,), tp=[1]), 2),
+                                           (dict(num_gpus=(1, 1)), 2)])
+def test_parameter_norm_and_zero_count_cover_the_model_once(plan_kw, world):
+    base = Trainer(tiny_gpt_plan(**KW), device="cpu", model_overrides=NODROP)
+    run_ranks(_norm_worker, world, tiny_gpt_plan(**KW, **plan_kw), base.optimizer.params_norm())

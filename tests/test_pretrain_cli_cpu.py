@@ -206,3 +206,37 @@ def test_blend_of_two_corpora_draws_from_both_by_weight(tmp_path):
     again = pretrain.make_dataset_batch_fn(t, ["3", str(tmp_path / "a"), "1", str(tmp_path / "b")], train_iters=8, seed=5,
                                            split="9,1,0", eval_samples=8)
     assert np.array_equal(again(3)["ids"].numpy(), fn(3)["ids"].numpy())
+
+
+def test_optimizer_flags_and_the_extra_columns_of_the_iteration_line(tmp_path, capsys):
+    import re
+    import torch
+    from superscaler_b200.runtime.trainer import Trainer
+    plan = tiny_gpt_plan()
+    plan_path = tmp_path / "gpt_tiny_1stages_flags.json"
+    plan_path.write_text(json.dumps(plan))
+    pretrain.main(["--flexpipe-config", str(plan_path), "--train-iters", "3", "--lr", "1e-2", "--lr-warmup-iters", "2",
+                   "--lr-decay-style", "constant", "--adam-beta1", "0.8", "--adam-beta2", "0.95", "--adam-eps", "1e-6",
+                   "--init-method-std", "0.05", "--log-params-norm", "--log-num-zeros-in-grad",
+                   "--hidden-dropout", "0", "--attention-dropout", "0"])
+    out = capsys.readouterr().out
+    lrs = [float(x) for x in re.findall(r"learning rate: ([0-9.E+-]+)", out)]
+    assert lrs == [0.0, 5e-3, 1e-2]                                   # two warm-up iterations, then the full rate
+    norms = [float(x) for x in re.findall(r"params norm: ([0-9.]+)", out)]
+    zeros = [int(x) for x in re.findall(r"num zeros: (\d+)", out)]
+    assert len(norms) == 3 and len(zeros) == 3
+    t = Trainer(plan, device="cpu", model_overrides=dict(init_std=0.05), adam_betas=(0.8, 0.95), adam_eps=1e-6)
+    assert t.optimizer.betas == (0.8, 0.95) and t.optimizer.eps == 1e-6
+    want = float(torch.sqrt(sum(p.detach().float().pow(2).sum() for p in t.store.params.values())))
+    assert abs(t.optimizer.params_norm() - want) < 1e-3 * want
+    assert abs(norms[0] - want) < 2e-2 * want                          # same seed, same initialisation; no step at lr 0
+    wide = Trainer(plan, device="cpu")
+    assert t.optimizer.params_norm() > 1.3 * wide.optimizer.params_norm()      # std 0.05 against 0.02 (LayerNorm gains stay 1)
+    assert min(zeros) > 0
+    # the count is over the parameters' own entries (no alignment padding), each parameter once
+    t.store.grad.fill_(1.0)
+    assert t.optimizer.count_zeros_in_grad() == 0
+    name = next(iter(t.store.offsets))
+    off, n = t.store.offsets[name]
+    t.store.grad[off:off + n] = 0.0
+    assert t.optimizer.count_zeros_in_grad() == n
