@@ -188,10 +188,15 @@ class ImageFolder:
         self.epoch = epoch
 
     def __getitem__(self, i: int):
+        return self.sample(i, self.epoch)
+
+    def sample(self, i: int, epoch: int):
+        """Sample i as epoch `epoch` shows it (no state of the dataset is read, so threads may call this side by
+        side for different epochs)."""
         path, label = self.samples[i]
         img = self._load(path)
         if self.train:
-            rng = random.Random((self.seed * 1000003 + self.epoch) * 1000003 + i)
+            rng = random.Random((self.seed * 1000003 + epoch) * 1000003 + i)
             img = random_resized_crop(img, self.size, rng)
             if rng.random() < 0.5:
                 from PIL import ImageOps
@@ -205,9 +210,12 @@ class ImageFolder:
         return to_normalised_tensor(img, self.dtype), label
 
 
-def image_batch(data: ImageFolder, indices: Sequence[int], pin: bool = False) -> Dict[str, torch.Tensor]:
-    """{"images": [n, H, W, 3], "labels": [n]} for the Wide-ResNet trainer."""
-    items = [data[int(i)] for i in indices]
+def image_batch(data: ImageFolder, indices: Sequence[int], pin: bool = False,
+                epoch: Optional[int] = None) -> Dict[str, torch.Tensor]:
+    """{"images": [n, H, W, 3], "labels": [n]} for the Wide-ResNet trainer; `epoch` (default: the dataset's current
+    one) selects the augmentation stream."""
+    e = data.epoch if epoch is None else epoch
+    items = [data.sample(int(i), e) for i in indices]
     out = {"images": torch.stack([x for x, _ in items]), "labels": torch.tensor([y for _, y in items], dtype=torch.int64)}
     return {k: v.pin_memory() for k, v in out.items()} if pin else out
 

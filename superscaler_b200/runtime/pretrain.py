@@ -219,8 +219,7 @@ def make_image_batch_fn(trainer: Trainer, root: str, seed: int):
 
     def batch(i):
         idx, epoch = batch_indices(len(data), gbs, i, seed)
-        data.set_epoch(epoch)
-        return image_batch(data, idx, pin=torch.cuda.is_available())
+        return image_batch(data, idx, pin=torch.cuda.is_available(), epoch=epoch)
 
     batch.valid = batch.test = None
     val_dir = os.path.join(root, "val")
@@ -313,6 +312,9 @@ def main(argv=None) -> None:
                          "<prefix>.bin + <prefix>.idx; T5 / BERT: a sentence corpus; Wide-ResNet / ViT: an image "
                          "folder).  GPT also takes a blend: WEIGHT1 PREFIX1 WEIGHT2 PREFIX2 ...  "
                          "Default: synthetic batches")
+    ap.add_argument("--num-workers", type=int, default=2,
+                    help="with --data-path: threads that prepare the coming batches while the device works (0: "
+                         "batches are built in the training loop)")
     ap.add_argument("--titles-data-path", default=None,
                     help="inverse-cloze model: sentence corpus of the documents' titles, same documents in the same "
                          "order as --data-path")
@@ -382,6 +384,9 @@ def main(argv=None) -> None:
                                       titles_prefix=args.titles_data_path)
                 if args.data_path
                 else make_batch_fn(trainer))
+    if args.data_path and args.num_workers > 0:
+        from ..data.prefetch import Prefetcher
+        batch_fn = Prefetcher(batch_fn, workers=args.num_workers, stop=args.train_iters)
     # synthetic batches are generated on the host before the loop (a pool of up to 4, reused in turn): building
     # a 768-image batch takes longer than a training step and is not part of what an iteration measures
     # batch of iteration `it` is batch_fn(it % 4) whether the run is fresh or resumed, so a resumed run sees the
@@ -466,7 +471,8 @@ def main(argv=None) -> None:
                 first = ((it + 1) // args.eval_interval - 1) * args.eval_iters
                 ev = trainer.evaluate(held(first + j) for j in range(args.eval_iters))
             else:
-                ev = trainer.evaluate(batch_fn(10 ** 6 + it * args.eval_iters + j) for j in range(args.eval_iters))
+                direct = getattr(batch_fn, "fn", batch_fn)        # not through the prefetcher: out of its sequence
+                ev = trainer.evaluate(direct(10 ** 6 + it * args.eval_iters + j) for j in range(args.eval_iters))
             if rank == world - 1:
                 print(f" validation loss at iteration {it + 1} | " +
                       " | ".join(f"{k} value: {v:.6E}" for k, v in ev.items()), flush=True)
@@ -495,6 +501,8 @@ def main(argv=None) -> None:
                   flush=True)
     if writer is not None:
         writer.close()
+    if hasattr(batch_fn, "close"):
+        batch_fn.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
