@@ -49,7 +49,7 @@ def _split_parts(corpus, num_docs: int, split):
 
 
 def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, eod_token=None, vocab_file=None,
-                          split=None, eval_samples: int = 0, titles_prefix=None):
+                          split=None, eval_samples: int = 0, titles_prefix=None, data_kw=None):
     """Batches of a GPT token corpus: `prefix`.bin holds the token ids (uint16, or uint32 with `prefix`.u32 present
     instead), `prefix`.npy the document lengths; a Megatron-LM corpus (`prefix`.bin + `prefix`.idx) is read as it
     is.  Batch i is global samples [i * gbs, (i + 1) * gbs) of the
@@ -65,7 +65,8 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
     if trainer.model_name in ("resnet", "vit"):
         return make_image_batch_fn(trainer, prefix, seed)
     if trainer.model_name == "t5":
-        return make_t5_batch_fn(trainer, prefix, train_iters, seed, vocab_file, split=split, eval_samples=eval_samples)
+        return make_t5_batch_fn(trainer, prefix, train_iters, seed, vocab_file, split=split, eval_samples=eval_samples,
+                                data_kw=data_kw)
     if trainer.model_name in ("bert", "ict"):
         special = None
         if vocab_file:      # ids of the special tokens from the WordPiece vocabulary the corpus was encoded with
@@ -76,8 +77,10 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
         if trainer.model_name == "ict":
             assert titles_prefix, "the inverse-cloze model with --data-path needs --titles-data-path"
             return make_ict_batch_fn(trainer, prefix, titles_prefix, train_iters, seed, special, split=split,
-                                     eval_samples=eval_samples)
-        return make_bert_batch_fn(trainer, prefix, train_iters, seed, special, split=split, eval_samples=eval_samples)
+                                     eval_samples=eval_samples, **{k: v for k, v in (data_kw or {}).items()
+                                                                   if k == "query_in_block_prob"})
+        return make_bert_batch_fn(trainer, prefix, train_iters, seed, special, split=split, eval_samples=eval_samples,
+                                  data_kw=data_kw)
     from ..data.indexed import BlendedDataset, GPTSampleDataset, TokenCorpus
     assert trainer.model_name == "gpt", f"--data-path does not feed the {trainer.model_name} model"
     from ..data import mmap_format
@@ -130,8 +133,14 @@ def make_dataset_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed:
     return _held_out(batches_of, parts, eval_samples)
 
 
+def _masking_kw(data_kw) -> dict:
+    """--mask-prob / --short-seq-prob as the sentence datasets name them; unset flags keep the datasets' defaults."""
+    names = {"mask_prob": "masked_lm_prob", "short_seq_prob": "short_seq_prob"}
+    return {names[k]: v for k, v in (data_kw or {}).items() if k in names and v is not None}
+
+
 def make_bert_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, special=None, split=None,
-                       eval_samples: int = 0):
+                       eval_samples: int = 0, data_kw=None):
     """Batches of a sentence corpus written by `data.preprocess --split-sentences`: [CLS] A [SEP] B [SEP] samples with
     masked-LM labels and the sentence-order flag (reference: runtime/megatron/data/bert_dataset.py).  `special`
     names the ids of [CLS], [SEP], [MASK], [PAD]; the default is their place in a BERT WordPiece vocabulary
@@ -143,7 +152,8 @@ def make_bert_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: in
 
     def batches_of(part, num_samples):
         data = BertDataset(part, tokens, cfg.vocab, num_samples=num_samples or train_iters * gbs,
-                           max_seq_length=cfg.seq_length, seed=seed, binary_head=cfg.binary_head)
+                           max_seq_length=cfg.seq_length, seed=seed, binary_head=cfg.binary_head,
+                           **_masking_kw(data_kw))
         return lambda i: bert_batch_of(data, range(i * gbs, (i + 1) * gbs))
 
     corpus = load_sentence_corpus(prefix)
@@ -184,7 +194,7 @@ def make_ict_batch_fn(trainer: Trainer, prefix: str, titles_prefix: str, train_i
 
 
 def make_t5_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int, vocab_file: str, extra_ids: int = 100,
-                     split=None, eval_samples: int = 0):
+                     split=None, eval_samples: int = 0, data_kw=None):
     """Span-corruption batches of a sentence corpus written by `data.preprocess --split-sentences`: masked spans
     become sentinels in the encoder input, the decoder predicts them (reference:
     runtime/megatron/data/t5_dataset.py).  The sentinels, [BOS] and [EOS] are appended to the WordPiece vocabulary,
@@ -200,7 +210,8 @@ def make_t5_batch_fn(trainer: Trainer, prefix: str, train_iters: int, seed: int,
     def batches_of(part, num_samples):
         from ..data.sentences import t5_batches
         data = T5Dataset(part, tok.special_tokens(), tok.vocab_size, num_samples=num_samples or train_iters * gbs,
-                         max_seq_length=cfg.seq_length, max_seq_length_dec=cfg.dec_seq_length, seed=seed)
+                         max_seq_length=cfg.seq_length, max_seq_length_dec=cfg.dec_seq_length, seed=seed,
+                         **_masking_kw(data_kw))
         return lambda i: next(t5_batches(data, gbs, 1, start=i * gbs))
 
     corpus = load_sentence_corpus(prefix)
@@ -315,6 +326,11 @@ def main(argv=None) -> None:
     ap.add_argument("--num-workers", type=int, default=2,
                     help="with --data-path: threads that prepare the coming batches while the device works (0: "
                          "batches are built in the training loop)")
+    ap.add_argument("--mask-prob", type=float, default=None, help="BERT / T5 corpora: share of tokens to mask (0.15)")
+    ap.add_argument("--short-seq-prob", type=float, default=None,
+                    help="BERT / T5 corpora: share of samples cut to a random shorter length (BERT 0.1, T5 0)")
+    ap.add_argument("--query-in-block-prob", type=float, default=None,
+                    help="inverse-cloze corpora: how often the query sentence stays inside its block (0.1)")
     ap.add_argument("--titles-data-path", default=None,
                     help="inverse-cloze model: sentence corpus of the documents' titles, same documents in the same "
                          "order as --data-path")
@@ -381,7 +397,11 @@ def main(argv=None) -> None:
     batch_fn = (make_dataset_batch_fn(trainer, args.data_path, args.train_iters, args.seed, args.eod_mask_loss,
                                       args.vocab_file, split=args.split,
                                       eval_samples=max(1, eval_rounds * args.eval_iters) * gbs,
-                                      titles_prefix=args.titles_data_path)
+                                      titles_prefix=args.titles_data_path,
+                                      data_kw={k: v for k, v in dict(mask_prob=args.mask_prob,
+                                                                      short_seq_prob=args.short_seq_prob,
+                                                                      query_in_block_prob=args.query_in_block_prob).items()
+                                               if v is not None})
                 if args.data_path
                 else make_batch_fn(trainer))
     if args.data_path and args.num_workers > 0:

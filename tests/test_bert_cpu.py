@@ -138,6 +138,10 @@ def test_text_to_sentence_corpus_to_bert_training(tmp_path):
     assert torch.equal(fn(0)["ids"], b["ids"])                           # batch i is a function of i
     losses = [t.loss_value(t.train_step(fn(i % 2))) for i in range(4)]
     assert all(math.isfinite(v) for v in losses)
+    # --mask-prob reaches the dataset: more positions to predict
+    more = make_bert_batch_fn(t, prefix, train_iters=4, seed=5, special=SpecialTokens(cls=2, sep=3, mask=4, pad=0),
+                              data_kw=dict(mask_prob=0.4))
+    assert float(more(0)["loss_mask"].sum()) > 1.5 * float(b["loss_mask"].sum())
 
 
 def test_separate_attention_ops_mask_the_padding_like_the_one_kernel_form():
