@@ -195,6 +195,15 @@ class _RelativeBias:
                               c.relative_attention_max_distance)
 
 
+def key_lengths(op: Op, st):
+    """Number of real (unpadded) encoder tokens of every sample this op sees, or None: its own data-parallel share
+    of the micro-batch's lengths when the trainer supplied them all (`enc_lens_all`), else `enc_lens` as given."""
+    full = st.get("enc_lens_all")
+    if full is None:
+        return st.get("enc_lens")
+    return full[op.pl.dp_rank * op.local_bs:(op.pl.dp_rank + 1) * op.local_bs]
+
+
 class AttentionCoreOp(Op, _AttnDims, _RelativeBias):
     """score + softmax + dropout + context as ONE flash-attention kernel (the fused form of the four
     reference ops flex_ops.py:711-1015).  mode: "causal" | "full" | "cross"."""
@@ -219,22 +228,22 @@ class AttentionCoreOp(Op, _AttnDims, _RelativeBias):
         if self.uses_relative_bias() and x.is_cuda:
             st["x"] = F.flash_attention(x, x, x, b, nh, self.sq, self.sq, hd, cols=(0, w, 2 * w), scale=scale,
                                         causal=self.mode == "causal",
-                                        kv_lens=st.get("enc_lens") if self.mode == "full" else None,
+                                        kv_lens=key_lengths(self, st) if self.mode == "full" else None,
                                         dropout_p=p_drop, seed=self.seed(sharded=True),
                                         bias_table=self.relative_bias_table(self.sq, self.sq))
         elif self.uses_relative_bias():
             st["x"] = F.attention_with_bias(x, b, nh, self.sq, hd, scale, self.mode == "causal",
-                                            st.get("enc_lens") if self.mode == "full" else None,
+                                            key_lengths(self, st) if self.mode == "full" else None,
                                             self.relative_bias(self.sq, self.sq), p_drop)
         elif self.mode == "cross":
             kv = st["kv"]
             st["x"] = F.flash_attention(x, kv, kv, b, nh, self.sq, self.sk, hd, cols=(0, 0, w), scale=scale,
-                                        causal=False, kv_lens=st.get("enc_lens"), dropout_p=p_drop,
+                                        causal=False, kv_lens=key_lengths(self, st), dropout_p=p_drop,
                                         seed=self.seed(sharded=True))
         else:
             st["x"] = F.flash_attention(x, x, x, b, nh, self.sq, self.sq, hd, cols=(0, w, 2 * w), scale=scale,
                                         causal=self.mode == "causal",
-                                        kv_lens=st.get("enc_lens") if self.mode == "full" else None,
+                                        kv_lens=key_lengths(self, st) if self.mode == "full" else None,
                                         dropout_p=p_drop, seed=self.seed(sharded=True))
 
 
@@ -402,7 +411,7 @@ class SoftmaxOp(Op, _AttnDims):
     def forward(self, st):
         scale = 1.0 / math.sqrt(self.env.cfg.head_dim)
         x = st["x"]
-        lens = st.get("enc_lens") if self.mode != "causal" else None
+        lens = key_lengths(self, st) if self.mode != "causal" else None
         if lens is None:
             st["x"] = F.scaled_softmax(x, scale, 1 if self.mode == "causal" else 0)
             return

@@ -90,6 +90,10 @@ def _validate_plan(plan: dict) -> None:
                 raise ValueError(f"stage {s} op {i}: tp {tp} x dp {dp} does not equal the stage's {g} GPUs")
             if plan["micro_batch_size"] % dp:
                 raise ValueError(f"stage {s} op {i}: dp {dp} does not divide the micro batch {plan['micro_batch_size']}")
+        if plan.get("model_name") == "t5" and len(set(plan["data_parallel_size_of_each_op"][s])) > 1:
+            # as in the reference (search/aceso_utils.py:523-526): the decoder's tokens enter in the middle of a
+            # stage, cut for the stage's first op
+            raise ValueError(f"stage {s}: a T5 stage keeps one tensor / data parallel layout for all its ops")
 
 
 class Trainer:
@@ -210,6 +214,10 @@ class Trainer:
             info = last if k in ("labels", "loss_mask", "nsp") else first
             rows = self.local_rows(info, self.micro_bs)
             st[k] = v[lo + rows.start: lo + rows.stop]
+        if "enc_lens" in batch:
+            # the lengths of the WHOLE micro-batch: an attention op whose data-parallel degree differs from the
+            # stage's first op (a plan that changes layouts inside a stage) cuts its own rows out of them
+            st["enc_lens_all"] = batch["enc_lens"][lo: lo + self.micro_bs]
         st["loss_scale"] = 1.0 / self.num_microbatches
         return st
 

@@ -103,6 +103,14 @@ def test_data_tensor_and_pipeline_parallel_plans_match_one_process():
     plans = {"dp": tiny_bert_plan(**KW, num_gpus=(2,), tp=[1]),
              "tp": tiny_bert_plan(**KW, num_gpus=(2,), tp=[2]),
              "pp": tiny_bert_plan(**KW, num_gpus=(1, 1))}
+    # layouts change inside the stage: tp 2 at the start, dp 2 from the middle of the first layer into the second
+    # (its attention sees half the samples and must take THEIR lengths for the padding mask), tp 2 again after
+    mixed = tiny_bert_plan(**KW, num_gpus=(2,), tp=[2])
+    n = mixed["num_ops_in_each_stage"][0]
+    tp = [1 if 9 <= i < 20 else 2 for i in range(n)]
+    mixed.update(model_parallel_size_of_each_op=[tp], data_parallel_size_of_each_op=[[2 // t for t in tp]],
+                 resharding_stages=[True])
+    plans["tp-dp-tp"] = mixed
     run_ranks(_worker, 2, plans, want, timeout=600)
 
 

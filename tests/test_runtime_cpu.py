@@ -104,6 +104,11 @@ def test_plan_validation_messages():
     bad["recompute_ops"][0].pop()
     with pytest.raises(ValueError, match="recompute_ops has"):
         Trainer(bad, device="cpu")
+    from helpers import tiny_t5_plan
+    bad = tiny_t5_plan(num_gpus=(2,), tp=[2])
+    bad["model_parallel_size_of_each_op"][0][5], bad["data_parallel_size_of_each_op"][0][5] = 1, 2
+    with pytest.raises(ValueError, match="a T5 stage keeps one"):
+        Trainer(bad, device="cpu", world_size=2)
 
 
 def test_recompute_segment_may_end_right_after_a_projection():
