@@ -133,3 +133,29 @@ def test_pairs_from_a_text_corpus_and_a_titles_corpus(tmp_path):
     assert all(row[1] in (56, 57) for row in held["ids"][1::2].tolist())      # validation part: documents 10, 11
     assert fn.test is None
     assert math.isfinite(t.loss_value(t.train_step(b)))
+
+
+def test_inverse_cloze_command_line_with_titles_and_a_held_out_part(tmp_path, capsys):
+    import json
+    import re
+    from superscaler_b200.data.preprocess import main as preprocess_main
+    from superscaler_b200.runtime import pretrain
+    words = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]", "."] + [f"w{i}" for i in range(40)] + [f"t{i}" for i in range(12)]
+    (tmp_path / "vocab.txt").write_text("\n".join(words) + "\n")
+    rng = np.random.RandomState(0)
+    rows = [{"text": " ".join(" ".join(f"w{int(x)}" for x in rng.randint(0, 40, size=4)) + " ." for _ in range(4)),
+             "title": f"t{d}"} for d in range(12)]
+    (tmp_path / "in.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    for key, name in (("text", "body"), ("title", "titles")):
+        preprocess_main(["--input", str(tmp_path / "in.jsonl"), "--json-key", key, "--output", str(tmp_path / name),
+                         "--split-sentences", "--output-format", "megatron", "--tokenizer-type", "BertWordPieceLowerCase",
+                         "--vocab-file", str(tmp_path / "vocab.txt")])
+    plan = tmp_path / "ict_tiny_1stages.json"
+    plan.write_text(json.dumps(tiny_ict_plan(**{**KW, "global_bs": 8, "micro_bs": 8})))
+    pretrain.main(["--flexpipe-config", str(plan), "--train-iters", "4", "--data-path", str(tmp_path / "body"),
+                   "--titles-data-path", str(tmp_path / "titles"), "--vocab-file", str(tmp_path / "vocab.txt"),
+                   "--split", "10,2,0", "--eval-interval", "2", "--eval-iters", "1", "--query-in-block-prob", "0.5",
+                   "--hidden-dropout", "0", "--attention-dropout", "0", "--num-workers", "2"])
+    out = capsys.readouterr().out
+    assert len(re.findall(r"lm loss: ([0-9.E+-]+)", out)) == 4
+    assert len(re.findall(r"validation loss at iteration", out)) == 2
