@@ -168,6 +168,11 @@ class StageOptimizer:
             return
         # CPU restatement
         norm = float(sumsq.sqrt()) * grad_scale
+        if not math.isfinite(norm):       # as the kernels do: a step with inf / nan gradients changes nothing
+            self.skipped += 1
+            if zero_grad:
+                st.grad.zero_()
+            return
         clip = min(1.0, self.clip_grad / (norm + 1e-6)) if self.clip_grad > 0 else 1.0
         g = st.grad * (grad_scale * clip)
         wd = torch.zeros_like(g)
@@ -193,6 +198,10 @@ class StageOptimizer:
     def grad_norm(self) -> float:
         """Host read of the last global gradient norm (synchronises)."""
         return float(self.sumsq.sqrt())
+
+    def skipped_steps(self) -> int:
+        """Steps left out so far because the gradients held inf or nan (host read, synchronises)."""
+        return int(self.skipped)
 
     def _per_parameter_total(self, value_of) -> float:
         """Sum over the whole model of `value_of(spec, offset, numel)`, every parameter counted once however many

@@ -460,6 +460,8 @@ def main(argv=None) -> None:
             mem = torch.cuda.max_memory_allocated() / 2 ** 20 if trainer.device.type == "cuda" else 0.0
             if args.log_params_norm:
                 extra["params norm"] = trainer.optimizer.params_norm()
+            if trainer.optimizer.skipped_steps():
+                extra["number of skipped iterations"] = trainer.optimizer.skipped_steps()
             more = "".join(f" | {k}: {v:.3f}" if isinstance(v, float) else f" | {k}: {v}" for k, v in extra.items())
             if rank == world - 1:
                 print(f" iteration {it + 1:8d}/{args.train_iters:8d} | elapsed time per iteration (ms): "

@@ -228,3 +228,19 @@ def test_masked_lm_loss_is_mean_over_unmasked_tokens():
     half = t.evaluate([dict(batch)])["lm loss"]
     assert abs(full - ones) < 1e-4
     assert abs(half - ones) < 0.5 and half > 0.7 * ones
+
+
+def test_a_step_with_non_finite_gradients_is_skipped_and_counted():
+    import torch
+    from superscaler_b200.runtime.trainer import Trainer
+    from helpers import tiny_gpt_plan
+    t = Trainer(tiny_gpt_plan(), device="cpu", lr_warmup_steps=0)
+    before = t.store.master.clone()
+    t.store.grad.fill_(1.0)
+    t.store.grad[3] = float("inf")
+    t.optimizer.step(lr=1e-3)
+    assert torch.equal(t.store.master, before) and t.optimizer.skipped_steps() == 1
+    assert float(t.store.grad.abs().sum()) == 0.0                       # the bad gradients do not leak into the next step
+    t.store.grad.fill_(1.0)
+    t.optimizer.step(lr=1e-3)
+    assert not torch.equal(t.store.master, before) and t.optimizer.skipped_steps() == 1
