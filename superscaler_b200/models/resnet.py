@@ -200,7 +200,7 @@ class FCLossOp(Op):
     """Classifier + mean cross entropy of the micro-batch (the reference computes the loss outside the op list,
     runtime/pretrain_resnet.py:62-70)."""
     reads = ("x", "labels")
-    writes = ("loss",)
+    writes = ("loss", "logits")
 
     def __init__(self, info, env, cin, classes):
         super().__init__(info, env)
@@ -212,6 +212,9 @@ class FCLossOp(Op):
 
     def forward(self, st):
         logits = F.linear(st["x"], self.p("fc.weight"), self.p("fc.bias"))
+        if "labels" not in st:            # inference: the class scores (Trainer.embed returns them)
+            st["logits"] = logits
+            return
         labels = st["labels"]
         st["loss"] = F.cross_entropy_sum(logits, labels, st.get("loss_scale", 1.0) / labels.numel())
 

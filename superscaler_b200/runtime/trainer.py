@@ -312,7 +312,7 @@ class Trainer:
     @torch.no_grad()
     def embed(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
         """Inference forward of a ONE-stage plan on one rank's rows: the last op's `logits` entry for the given inputs
-        (an inverse-cloze plan: one embedding per sequence; BERT / ViT: their logits).  `batch` holds the model's input
+        (an inverse-cloze plan: one embedding per sequence; BERT: vocabulary logits; ViT / Wide-ResNet: class scores).  `batch` holds the model's input
         keys (ids, types, enc_lens, images ...) and no labels.  Dropout is off."""
         assert len(self.stage_bounds) == 1 and self.world_size == 1, "embed() runs one-stage plans on one rank"
         was = self.env.training

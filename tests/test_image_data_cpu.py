@@ -112,3 +112,18 @@ def test_a_val_folder_becomes_the_held_out_batches(tmp_path):
     assert a["labels"].tolist() == ([0] * 6 + [1] * 6 + [2] * 6 + [0] * 6 + [1] * 6 + [2] * 6)[:gbs]    # file order, wrapped
     ev = t.evaluate([t.to_device(a)])
     assert all(np.isfinite(v) for v in ev.values())
+
+
+def test_wide_resnet_scores_pictures_without_labels(tmp_path):
+    """Inference through the public API: `Trainer.embed` on images alone returns one score per class, and the class of
+    a picture the model was trained on comes out on top."""
+    from helpers import tiny_resnet_plan
+    from superscaler_b200.data import synthetic as syn
+    from superscaler_b200.runtime.trainer import Trainer
+    t = Trainer(tiny_resnet_plan(), device="cpu", lr=1e-2, lr_warmup_steps=0, model_overrides=dict(image_size=64, num_classes=8))
+    b = syn.resnet_batch(t.plan["global_batch_size"], 64, 8, seed=3, dtype=torch.float32)
+    for _ in range(12):
+        t.train_step(b)
+    scores = t.embed({"images": b["images"]})
+    assert scores.shape == (t.plan["global_batch_size"], 8)
+    assert (scores.float().argmax(-1) == b["labels"]).float().mean() >= 0.75
