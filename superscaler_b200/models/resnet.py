@@ -216,7 +216,11 @@ class FCLossOp(Op):
             st["logits"] = logits
             return
         labels = st["labels"]
-        st["loss"] = F.cross_entropy_sum(logits, labels, st.get("loss_scale", 1.0) / labels.numel())
+        scale = st.get("loss_scale", 1.0)
+        hits = None if self.env.training else (logits.argmax(-1) == labels).float().mean() * scale
+        loss = F.cross_entropy_sum(logits, labels, scale / labels.numel())
+        # evaluation: [loss, share of samples whose best class is the label], both averaged the same way downstream
+        st["loss"] = loss if hits is None else torch.stack([loss.reshape(()), hits])
 
 
 class FusedBnAddRelu(FusedGroup):

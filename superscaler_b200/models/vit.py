@@ -92,7 +92,7 @@ class VitEmbeddingOp(Op):
 
 
 class VitPostOp(Op):
-    """Class-token head: dense + tanh + dense -> class logits, cross entropy (reference: VitMlpHead)."""
+    """Class-token head: dense + tanh + dense -> class logits, cross entropy (Megatron-LM's VitMlpHead)."""
     reads = ("x", "labels")
     writes = ("loss", "logits")
 
@@ -113,7 +113,11 @@ class VitPostOp(Op):
         if "labels" not in st:
             st["logits"] = logits
             return
-        st["loss"] = torch.nn.functional.cross_entropy(logits, st["labels"]) * st.get("loss_scale", 1.0)
+        scale = st.get("loss_scale", 1.0)
+        loss = torch.nn.functional.cross_entropy(logits, st["labels"]) * scale
+        if not self.env.training:         # evaluation: [loss, share of samples whose best class is the label]
+            loss = torch.stack([loss, (logits.argmax(-1) == st["labels"]).float().mean() * scale])
+        st["loss"] = loss
 
 
 def build_vit_op(info: OpInfo, env: Env) -> Op:

@@ -297,17 +297,20 @@ class Trainer:
     def loss_value(self, stats: Dict[str, Any]) -> float:
         """Host read of the iteration loss (synchronises); averaged over the last stage's DP group.  Also reads
         the kernels' status word and raises if a bounded wait ran out."""
+        return float(self._last_stage_mean(stats["loss_tensor"]).item())
+
+    def _last_stage_mean(self, values: torch.Tensor) -> torch.Tensor:
+        """Per-iteration values the last stage's ranks hold (each its data-parallel share's mean; tensor-parallel
+        replicas repeat it), averaged and made known to every rank.  Checks the kernels' status word first."""
         self.check_device_status()
-        t = stats["loss_tensor"].clone()
+        t = values.clone()
         if self.world_size > 1:
             last = len(self.stage_bounds) - 1
-            src_dp = self.plan["data_parallel_size_of_each_op"][last][-1]
             if not self.pstate.is_last_stage():
                 t.zero_()
             dist.all_reduce(t)
-            g = self.plan["num_gpus"][last]
-            t /= g  # every rank of the last stage holds its DP shard's mean; TP replicas repeat it
-        return float(t.item())
+            t /= self.plan["num_gpus"][last]
+        return t
 
     @torch.no_grad()
     def embed(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
@@ -387,26 +390,32 @@ class Trainer:
         (reference: evaluate / evaluate_and_print_results, runtime/megatron/training.py:1021-1098)."""
         was = self.env.training
         self.env.training = False
-        total, n = 0.0, 0
+        # the classifiers' heads report [loss, top-1 accuracy] in evaluation; both take the same route to the host
+        classifier = self.model_name in ("resnet", "vit")
+        buf = torch.zeros(2 if classifier else 1, dtype=torch.float32, device=self.device)
+        total, n = torch.zeros(buf.numel(), dtype=torch.float64), 0
         try:
             for batch in batches:
                 batch = self.to_device(batch)
-                self._loss_buf.zero_()
+                buf.zero_()
                 if self.pipeline is not None:
-                    self.pipeline.run_forward_only(batch, self._loss_buf)
+                    self.pipeline.run_forward_only(batch, buf)
                 else:
                     for mb in range(self.num_microbatches):
                         st = self.microbatch_inputs(batch, mb)
                         if self.world_size > 1:
                             st["_meta"] = {}
                         self.stage.forward(st)
-                        self._loss_buf += st["loss"]
-                total += self.loss_value({"loss_tensor": self._loss_buf})
+                        buf += st["loss"]
+                total += self._last_stage_mean(buf).double().cpu()
                 n += 1
         finally:
             self.env.training = was
-        mean = total / max(n, 1)
-        return {"lm loss": mean, "lm loss ppl": float(torch.exp(torch.tensor(min(mean, 20.0))))}
+        mean = float(total[0]) / max(n, 1)
+        out = {"lm loss": mean, "lm loss ppl": float(torch.exp(torch.tensor(min(mean, 20.0))))}
+        if classifier:
+            out = {"lm loss": mean, "accuracy": float(total[1]) / max(n, 1)}
+        return out
 
     def owned_op_indices(self) -> List[int]:
         """Global indices of the ops this rank's physical stage runs (all of its model chunks)."""

@@ -111,7 +111,7 @@ def test_a_val_folder_becomes_the_held_out_batches(tmp_path):
     assert a["images"].shape == (gbs, 64, 64, 3) and torch.equal(a["images"], b["images"])
     assert a["labels"].tolist() == ([0] * 6 + [1] * 6 + [2] * 6 + [0] * 6 + [1] * 6 + [2] * 6)[:gbs]    # file order, wrapped
     ev = t.evaluate([t.to_device(a)])
-    assert all(np.isfinite(v) for v in ev.values())
+    assert all(np.isfinite(v) for v in ev.values()) and 0.0 <= ev["accuracy"] <= 1.0
 
 
 def test_wide_resnet_scores_pictures_without_labels(tmp_path):

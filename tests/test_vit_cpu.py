@@ -82,3 +82,31 @@ def test_data_tensor_and_pipeline_parallel_plans_match_one_process():
              "tp": tiny_vit_plan(**KW, num_gpus=(2,), tp=[2]),
              "pp": tiny_vit_plan(**KW, num_gpus=(1, 1))}
     run_ranks(_worker, 2, plans, want, timeout=600)
+
+
+def _accuracy(plan, rank=0, world=1):
+    """Evaluation of the untrained and of the trained model on the training batch: loss and top-1 accuracy."""
+    from superscaler_b200.runtime.trainer import Trainer
+    t = Trainer(plan, rank=rank, world_size=world, device="cpu", model_overrides=OV, lr_warmup_steps=0, lr=2e-3)
+    before = t.evaluate([_batch(1)])
+    for _ in range(25):
+        t.train_step(_batch(1))
+    return before, t.evaluate([_batch(1)])
+
+
+def _accuracy_worker(rank, world, plans, want):
+    for name, plan in plans.items():
+        before, after = _accuracy(plan, rank, world)
+        for got, ref in ((before, want[0]), (after, want[1])):
+            assert set(got) == {"lm loss", "accuracy"}
+            close = abs(got["lm loss"] - ref["lm loss"]) < 3e-2 and abs(got["accuracy"] - ref["accuracy"]) <= 0.26
+            assert close, (rank, name, got, ref)
+
+
+def test_evaluation_reports_top1_accuracy_on_every_rank_of_any_plan():
+    before, after = _accuracy(tiny_vit_plan(**KW))
+    b = _batch(1)
+    assert 0.0 <= before["accuracy"] <= 0.5 and after["accuracy"] >= 0.75 and after["lm loss"] < before["lm loss"]
+    assert abs(after["accuracy"] * b["labels"].numel() - round(after["accuracy"] * b["labels"].numel())) < 1e-4
+    plans = {"dp": tiny_vit_plan(**KW, num_gpus=(2,), tp=[1]), "pp": tiny_vit_plan(**KW, num_gpus=(1, 1))}
+    run_ranks(_accuracy_worker, 2, plans, (before, after), timeout=600)
