@@ -95,7 +95,9 @@ class BertEmbeddingOp(EmbeddingOp):
         else:
             x = F.embedding(ids, None, W, None, self.pl.tp_rank * self.v_local, 0.0, 0)
             x = M.reduce_from_group(x, self.tp_group)
-            x = x + torch.nn.functional.embedding(pos, P)
+            # positions are 0 .. s-1 in every sample: add the first s rows to each sample (no gather; the gradient of
+            # a row is then a reduction over the batch, accumulated in fp32)
+            x = (x.view(b, s, -1) + P[:s]).view(b * s, -1)
         types = st.get("types")
         if types is not None:
             # looked up in fp32: the gradient of a row is the sum over all tokens of that type, which bf16 would round

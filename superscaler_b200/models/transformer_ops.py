@@ -57,7 +57,9 @@ class EmbeddingOp(Op):
         else:
             x = F.embedding(ids, None, W, None, self.pl.tp_rank * self.v_local, 0.0, 0)
             x = M.reduce_from_group(x, self.tp_group)
-            x = x + torch.nn.functional.embedding(pos, P)
+            # positions are 0 .. s-1 in every sample: add the first s rows to each sample (no gather; the gradient of
+            # a row is then a reduction over the batch, accumulated in fp32)
+            x = (x.view(b, s, -1) + P[:s]).view(b * s, -1)
             st["x"] = F.dropout(x, p_drop, self.seed())
 
 
