@@ -1,9 +1,9 @@
 """Longer fuzz runs of the plan space than the test suite affords (not collected by pytest):
 
-    python tests/fuzz_plans.py --first-seed 0 --seeds 20 [--kinds layouts cuts interleaved t5]
+    python tests/fuzz_plans.py --first-seed 0 --seeds 20 [--kinds layouts cuts interleaved t5 bert]
 
 Every seed draws random plans (per-op layouts + algorithms + recompute flags on two ranks; pipeline cuts with random
-GPU counts on four ranks; interleaved plans with random virtual-stage cuts; T5 cuts) and trains them on gloo ranks
+GPU counts on four ranks; interleaved plans with random virtual-stage cuts; T5 cuts; BERT layouts and cuts on a padded batch) and trains them on gloo ranks
 against the single-process run, with the workers and tolerances of tests/test_parallel_cpu.py and
 tests/test_interleaved_cpu.py.  Prints one line per (kind, seed); exit code 1 if any failed.
 """
@@ -80,7 +80,28 @@ def t5(seed):
     run_ranks(PP._t5_fuzz_worker, 4, plans, PP._other_model_losses("t5", tiny_t5_plan(layers=2), steps=2), timeout=400)
 
 
-KINDS = {"layouts": layouts, "cuts": cuts, "interleaved": interleaved, "t5": t5}
+def bert(seed):
+    """BERT on a padded batch: layouts, algorithms and recompute flags change inside the stage (so attention runs
+    both as one kernel and as four separate ops, on all or on half of the samples), or the ops are cut into stages."""
+    import test_bert_cpu as BT
+    from helpers import tiny_bert_plan
+    rng, plans = random.Random(seed), {}
+    n = len(tiny_bert_plan(**BT.KW)["algo_of_each_op"][0])
+    for k in range(3):
+        plan = tiny_bert_plan(**BT.KW, num_gpus=(2,), tp=[2])
+        tp = _runs(rng, n, [1, 2], 1, 9)
+        tp[-1] = 2      # the head sees the whole micro-batch: a data-parallel head averages per-rank means over the
+        # masked positions, which is a (slightly) different loss when the ranks hold different numbers of them
+        plan.update(model_parallel_size_of_each_op=[tp], data_parallel_size_of_each_op=[[2 // t for t in tp]],
+                    algo_of_each_op=[[rng.randint(0, 1) for _ in range(n)]], resharding_stages=[True],
+                    recompute_ops=[[0] + _runs(rng, n - 3, [0, 1], 1, 7) + [0, 0]])
+        plans[f"layouts{k}"] = plan
+    c = rng.randint(1, n - 1)
+    plans["cut"] = tiny_bert_plan(**BT.KW, num_gpus=(1, 1), ops_per_stage=[c, n - c], recompute=rng.randint(0, 1))
+    run_ranks(BT._worker, 2, plans, BT._losses(tiny_bert_plan(**BT.KW)), timeout=600)
+
+
+KINDS = {"layouts": layouts, "cuts": cuts, "interleaved": interleaved, "t5": t5, "bert": bert}
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
