@@ -261,6 +261,23 @@ def make_batch_fn(trainer: Trainer):
     return lambda i: synthetic.resnet_batch(gbs, cfg.image_size, cfg.num_classes, seed=1234 + i)
 
 
+class _TerminationRequest:
+    """Turns SIGTERM into a flag the training loop reads between iterations (the place of the reference's autoresume
+    termination check, runtime/megatron/utils.py:224-242, without its cluster-specific library)."""
+
+    def __init__(self):
+        import signal
+        self.requested = False
+        self._signal = signal
+        self._previous = signal.signal(signal.SIGTERM, self._note)
+
+    def _note(self, signum, frame):
+        self.requested = True
+
+    def restore(self) -> None:
+        self._signal.signal(self._signal.SIGTERM, self._previous)
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--flexpipe-config", required=True)
@@ -293,6 +310,9 @@ def main(argv=None) -> None:
     ap.add_argument("--exit-interval", type=int, default=None)
     ap.add_argument("--exit-duration-in-mins", type=float, default=None,
                     help="save a checkpoint and stop once the run has lasted this long")
+    ap.add_argument("--exit-signal-handler", action="store_true",
+                    help="on SIGTERM (a scheduler's notice of preemption) finish the iteration, save a checkpoint "
+                         "(with --save) and leave with exit code 0; all ranks leave at the same iteration")
     ap.add_argument("--finetune", action="store_true", help="load the weights only and restart at iteration 0")
     ap.add_argument("--load-resharded", action="store_true",
                     help="the checkpoint under --load was written under ANOTHER plan (other GPU count, tensor-parallel "
@@ -417,6 +437,7 @@ def main(argv=None) -> None:
     config_name = os.path.splitext(os.path.basename(args.flexpipe_config))[0]
     regions = ["iteration", "forward-backward", "backward-params-all-reduce", "optimizer"]
     extra = {}             # further columns of the iteration line
+    term = _TerminationRequest() if args.exit_signal_handler else None
 
     def one_step(it):
         timers("iteration").start()
@@ -513,6 +534,17 @@ def main(argv=None) -> None:
                 if rank == 0:
                     print(f"exiting after {(time.time() - t_start) / 60.0:.1f} minutes at iteration {it + 1}", flush=True)
                 break
+        if term is not None:
+            # a rank that got the signal tells the others: they all stop after the same iteration
+            asked = torch.tensor([float(term.requested)], device=trainer.device)
+            if world > 1:
+                dist.all_reduce(asked, op=dist.ReduceOp.MAX)
+            if asked.item() > 0:
+                if rank == 0:
+                    print(f"termination requested: stopping after iteration {it + 1}", flush=True)
+                break
+    if term is not None:
+        term.restore()
     if args.save:
         checkpointing.save_checkpoint(trainer, args.save)
     held = getattr(batch_fn, "test", None)

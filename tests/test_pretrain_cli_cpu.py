@@ -240,3 +240,39 @@ def test_optimizer_flags_and_the_extra_columns_of_the_iteration_line(tmp_path, c
     off, n = t.store.offsets[name]
     t.store.grad[off:off + n] = 0.0
     assert t.optimizer.count_zeros_in_grad() == n
+
+
+def test_sigterm_ends_the_run_after_an_iteration_with_a_checkpoint(tmp_path):
+    """--exit-signal-handler in a child process: the signal arrives in the middle of training, the run saves and
+    leaves with exit code 0, and a second run continues from that checkpoint."""
+    import signal
+    import subprocess
+    import sys
+    import time
+    plan_path = tmp_path / "gpt_tiny_1stages_term.json"
+    plan_path.write_text(json.dumps(tiny_gpt_plan()))
+    cmd = [sys.executable, "-u", "-m", "superscaler_b200.runtime.pretrain", "--flexpipe-config", str(plan_path),
+           "--train-iters", "100000", "--save", str(tmp_path / "ckpt"), "--exit-signal-handler", "--log-interval", "1",
+           "--hidden-dropout", "0", "--attention-dropout", "0"]
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
+    lines = []
+    try:
+        deadline = time.time() + 120
+        while time.time() < deadline:
+            line = p.stdout.readline()
+            lines.append(line)
+            assert line or p.poll() is None, "the run ended early:\n" + "".join(lines)
+            if " iteration        3/" in line:          # the handler is installed long before the third iteration
+                break
+        else:
+            raise AssertionError("no third iteration within two minutes:\\n" + "".join(lines))
+        p.send_signal(signal.SIGTERM)
+        rest, _ = p.communicate(timeout=120)
+    finally:
+        if p.poll() is None:
+            p.kill()
+    assert p.returncode == 0, rest
+    assert "termination requested: stopping after iteration" in rest
+    done = int((tmp_path / "ckpt" / "latest_checkpointed_iteration.txt").read_text())
+    assert 3 <= done < 100000
