@@ -485,7 +485,8 @@ def main(argv=None) -> None:
                 extra["number of skipped iterations"] = trainer.optimizer.skipped_steps()
             more = "".join(f" | {k}: {v:.3f}" if isinstance(v, float) else f" | {k}: {v}" for k, v in extra.items())
             if rank == world - 1:
-                print(f" iteration {it + 1:8d}/{args.train_iters:8d} | elapsed time per iteration (ms): "
+                print(f" iteration {it + 1:8d}/{args.train_iters:8d} | consumed samples: "
+                      f"{(it + 1) * plan['global_batch_size']:12d} | elapsed time per iteration (ms): "
                       f"{row['iteration']:.1f} | learning rate: {lr:.3E} | global batch size: "
                       f"{plan['global_batch_size']:5d} | lm loss: {lv:.6E} | grad norm: {trainer.optimizer.grad_norm():.3f}"
                       + more, flush=True)
