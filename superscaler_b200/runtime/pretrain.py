@@ -310,6 +310,10 @@ def main(argv=None) -> None:
     ap.add_argument("--exit-interval", type=int, default=None)
     ap.add_argument("--exit-duration-in-mins", type=float, default=None,
                     help="save a checkpoint and stop once the run has lasted this long")
+    ap.add_argument("--debug-dump", default=None, choices=["output", "grad", "all"],
+                    help="with --log-path: per-rank files with statistics of every op's outputs and / or of every "
+                         "parameter's weight and gradient, for the first --debug-dump-iters iterations")
+    ap.add_argument("--debug-dump-iters", type=int, default=1)
     ap.add_argument("--exit-signal-handler", action="store_true",
                     help="on SIGTERM (a scheduler's notice of preemption) finish the iteration, save a checkpoint "
                          "(with --save) and leave with exit code 0; all ranks leave at the same iteration")
@@ -437,6 +441,11 @@ def main(argv=None) -> None:
     config_name = os.path.splitext(os.path.basename(args.flexpipe_config))[0]
     regions = ["iteration", "forward-backward", "backward-params-all-reduce", "optimizer"]
     extra = {}             # further columns of the iteration line
+    dump = None
+    if args.debug_dump:
+        assert args.log_path, "--debug-dump writes under --log-path"
+        from .debug_dump import DebugDump
+        dump = DebugDump(trainer, args.log_path, config_name, args.debug_dump, args.debug_dump_iters)
     term = _TerminationRequest() if args.exit_signal_handler else None
 
     def one_step(it):
@@ -447,10 +456,14 @@ def main(argv=None) -> None:
         trainer._fold_autograd_grads()
         timers("forward-backward").stop()
         timers("backward-params-all-reduce").start()
+        if dump is not None:
+            dump.gradients("before the reduction")
         trainer.optimizer.reduce_gradients()
         if trainer._tied is not None:
             trainer._tied.sync_grads()
         timers("backward-params-all-reduce").stop()
+        if dump is not None:
+            dump.gradients("after the reduction and the tied-weight sync")
         if args.log_num_zeros_in_grad and (it + 1) % args.log_interval == 0:
             extra["num zeros"] = trainer.optimizer.count_zeros_in_grad()
         timers("optimizer").start()
@@ -546,6 +559,8 @@ def main(argv=None) -> None:
                 break
     if term is not None:
         term.restore()
+    if dump is not None:
+        dump.close()
     if args.save:
         checkpointing.save_checkpoint(trainer, args.save)
     held = getattr(batch_fn, "test", None)

@@ -112,12 +112,19 @@ def _rows_gather_in_gemm(op: Op, t: torch.Tensor, cur_side: Side, cur_lay: Layou
     return F.can_gather_in_gemm(t, op.tpctx())
 
 
+# Debugging: every entry is called as hook(op, state) right after an op's forward (the reference's post_forward_hook
+# under DEBUG_OUTPUT, runtime/megatron/model/flex_model.py:245-247).  Empty in normal runs.
+AFTER_OP_HOOKS: List[Callable] = []
+
+
 def run_op(op: Op, st: Dict[str, torch.Tensor]) -> None:
     """Brings every tensor the op reads to the layout it requires under the op's own (tp, dp) -- the in-stage
     resharding of the reference's pre_forward_tensor_adapter_hook (flex_model.py:250-300) -- then runs it."""
     meta = st.get("_meta")
     if meta is None:
         op.forward(st)
+        for hook in AFTER_OP_HOOKS:
+            hook(op, st)
         return
     ps = op.env.pstate
     side = Side(ps.stage_start[ps.stage], op.info.tp, op.info.dp)
@@ -145,6 +152,8 @@ def run_op(op: Op, st: Dict[str, torch.Tensor]) -> None:
     for k, lay in op.produced().items():
         if k in st:
             meta[k] = (side, lay)
+    for hook in AFTER_OP_HOOKS:
+        hook(op, st)
 
 
 class Segment:

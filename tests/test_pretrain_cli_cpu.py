@@ -276,3 +276,24 @@ def test_sigterm_ends_the_run_after_an_iteration_with_a_checkpoint(tmp_path):
     assert "termination requested: stopping after iteration" in rest
     done = int((tmp_path / "ckpt" / "latest_checkpointed_iteration.txt").read_text())
     assert 3 <= done < 100000
+
+
+def test_debug_dump_writes_op_outputs_and_gradient_statistics(tmp_path):
+    from superscaler_b200.runtime import stage
+    plan_path = tmp_path / "gpt_tiny_1stages_dump.json"
+    plan_path.write_text(json.dumps(tiny_gpt_plan()))
+    logs = str(tmp_path / "logs") + os.sep
+    pretrain.main(["--flexpipe-config", str(plan_path), "--train-iters", "2", "--log-path", logs, "--debug-dump", "all",
+                   "--hidden-dropout", "0", "--attention-dropout", "0"])
+    assert stage.AFTER_OP_HOOKS == []                                  # the hook is gone after the run
+    out = open(logs + "gpt_tiny_1stages_dump_debug_output_rank_0.log").read().splitlines()
+    grad = open(logs + "gpt_tiny_1stages_dump_debug_grad_rank_0.log").read().splitlines()
+    assert all(line.startswith("it 0 |") for line in out)             # the first iteration only
+    names = [line.split("|")[1].split()[2] for line in out]
+    assert names[0] == "encoder-embedding" and "gpt-post-process" in names and "enc-attention-qkv" in names
+    assert any("| loss () |" in line for line in out)
+    assert grad[0].startswith("=== iteration 0, before the reduction")
+    rows = [line for line in grad if line.startswith("it 0 |")]
+    assert len(rows) % 2 == 0 and any("word_embeddings.weight" in r for r in rows)
+    norms = [float(r.rsplit("grad norm", 1)[1]) for r in rows]
+    assert max(norms) > 0.0
