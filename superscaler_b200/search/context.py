@@ -148,7 +148,9 @@ def add_cli_arguments(p: argparse.ArgumentParser) -> None:
     a("--op-group-size", type=int, default=1)
     a("--max-op-move-steps", type=int, default=5)
     a("--memory-pred-type", type=str, default="MAX")
-    a("--initial-point", type=str, default="balance")
+    a("--initial-point", type=str, default="balance",
+      help="balance | imbalance_gpu | imbalance_op (the reference's), grid (best uniform plan of the stage count), "
+           "both (balance and grid, the faster result is kept), or the path of a plan JSON")
     a("--high-memory-rate", type=float, default=0.9)
     a("--print-debug-info", action="store_true")
     a("--do-not-consider-shared-tensor-space", action="store_false", dest="consider_shared_space")

@@ -265,8 +265,35 @@ class Searcher:
                 csv.writer(f).writerows([["search_time (s)", "config time (ms)"]] + [[x, y] for x, y in zip(accum, trend)])
 
 
+def search_stage_count(args: SearchArgs, num_stages: int):
+    """One search for this stage count; with `--initial-point both` (not in the reference) two, from the balanced
+    start and from the best uniform plan, of which the faster result and its saved plan are kept."""
+    if args.initial_point != "both":
+        return Searcher(SearchContext(args, verbose=False)).run(num_stages)
+    import copy
+    plan_file = None
+    if args.config_save_path is not None:
+        plan_file = f"{args.config_save_path}{args.model_name}_{args.model_size}_{num_stages}stages_{args.config_suffix}.json"
+    best, kept = None, None
+    for start in ("balance", "grid"):
+        one = copy.copy(args)
+        one.initial_point = start
+        res = Searcher(SearchContext(one, verbose=False)).run(num_stages)
+        better = res is not None and 0 < res[0] < BIG and (best is None or res[0] < best[0])
+        if better:
+            best = res
+            if plan_file is not None and os.path.exists(plan_file):
+                kept = plan_file + ".best"
+                shutil.copy(plan_file, kept)
+        elif best is None and res is not None:
+            best = res
+    if kept is not None:
+        shutil.move(kept, plan_file)
+    return best
+
+
 def _worker(args: SearchArgs, num_stages: int, queue) -> None:
-    res = Searcher(SearchContext(args, verbose=False)).run(num_stages)
+    res = search_stage_count(args, num_stages)
     d = queue.get()
     d[num_stages] = res
     queue.put(d)
@@ -292,7 +319,7 @@ def run_all(args: SearchArgs) -> dict:
         results = q.get()
     else:
         for n in counts:
-            results[n] = Searcher(SearchContext(args, verbose=False)).run(n)
+            results[n] = search_stage_count(args, n)
     return results
 
 

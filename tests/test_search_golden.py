@@ -149,6 +149,29 @@ def test_search_started_from_the_grid_is_never_slower_than_the_grid(tmp_path):
     assert t_search < 0.9 * t_grid           # the per-op moves find more than 10 % over the uniform 4-stage plan
 
 
+def test_both_starting_points_keep_the_faster_result_and_its_plan(tmp_path):
+    """`--initial-point both`: per stage count the result is the minimum of the two single-start searches, and the
+    plan file left behind is the one of that search."""
+    import json
+    from superscaler_b200.search.search import search_stage_count
+    times = {}
+    for start in ("balance", "grid", "both"):
+        out = str(tmp_path / start) + "/"
+        for sub in ("csv", "top_configs", "trends"):
+            os.makedirs(out + sub, exist_ok=True)
+        args = SearchArgs(model_name="gpt", model_size="1_3B", global_batch_size=512, micro_batch_size=[1, 2, 4, 8],
+                          num_nodes=1, num_gpus_per_node=4, memory_limit=12000, profiled_time_path=DB,
+                          config_save_path=out, log_path=out, config_suffix="t", max_num_hops=7, time_budget_total=200,
+                          multi_process=False, initial_point=start).finalize()
+        res = search_stage_count(args, 2)
+        plan = json.load(open(f"{out}gpt_1_3B_2stages_t.json"))
+        times[start] = (res[0], plan)
+        assert not os.path.exists(f"{out}gpt_1_3B_2stages_t.json.best")
+    assert times["both"][0] == min(times["balance"][0], times["grid"][0])
+    winner = "balance" if times["balance"][0] <= times["grid"][0] else "grid"
+    assert times["both"][1] == times[winner][1]
+
+
 def test_extrapolated_tables_scale_by_the_hidden_size_and_drive_a_search(tmp_path):
     """Tables for an unprofiled GPT size: linear-layer times and weights grow with the square of the hidden-size
     ratio, everything else linearly; the collective tables are re-keyed for the new tensor sizes, and a search
