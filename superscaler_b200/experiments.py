@@ -249,7 +249,8 @@ def main(argv=None) -> None:
     ap.add_argument("--results", default="./logs", help="root of search logs, plans, runtime CSVs, tables and figures")
     ap.add_argument("--initial-point", default="balance",
                        help="balance (the reference's scripts), imbalance_gpu, imbalance_op, grid (start from the best "
-                            "uniform plan: never slower than the baseline) or a plan JSON")
+                            "uniform plan: never slower than the baseline), both (balance and grid, the faster "
+                            "result is kept) or a plan JSON")
     ap.add_argument("--budget", type=int, default=200, help="search time budget per stage count (s)")
     ap.add_argument("--max-gpus", type=int, default=None, help="skip cases that need more GPUs than this")
     ap.add_argument("--top", type=int, default=3, help="how many saved plans per case `execute` runs")
