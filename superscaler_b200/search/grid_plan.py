@@ -111,6 +111,9 @@ def main(argv=None) -> None:
         return
     for i, plan in enumerate(plans[:args.num_of_saved_configs]):
         t = max(plan.time_list)
+        if args.config_save_path is None:       # nothing to write to: the prediction alone
+            print(f"best_{i}: {t:.2f} ms, {max(plan.memory_list):.0f} MB (no --config-save-path: plan not saved)")
+            continue
         path = f"{args.config_save_path}{args.model_name}_{args.model_size}_{args.num_layers}layers_megatron_est_{int(t)}.json"
         save_plan(plan, path, args.model_name, args.model_size, args.num_layers, getattr(args, "shapes", "reference"))
         print(f"best_{i}: {t:.2f} ms, {max(plan.memory_list):.0f} MB -> {path}")
